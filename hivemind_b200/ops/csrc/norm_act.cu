@@ -1,0 +1,336 @@
+// LayerNorm (with optional fused residual add) and bias + tanh-GELU, forward and backward.
+//
+// Shapes: x, y, residual are [rows, H] row-major in bf16 or fp32; gamma, beta, bias are fp32.
+// One warp owns one row at a time; a lane keeps its slice of the row in registers, so the row is read
+// from HBM exactly once in the forward pass and the statistics are exact two-pass (mean, then variance).
+// H must be a multiple of 8 and at most 8 * 32 * HM_LN_MAXV.
+//
+// Reference call sites replaced: hivemind/moe/server/layers/common.py:11-12 (gelu_fast),
+// :26-30 (LayerNorm(x + ffn(x)), eps 1e-12), and the LayerNorm/GELU of the user's transformer
+// (examples/albert/run_trainer.py uses transformers' ALBERT).
+#include "hm_common.cuh"
+
+#define HM_LN_MAXV 8
+#define HM_LN_WARPS 4
+
+template <typename T>
+__device__ __forceinline__ void ld8(const T* p, float v[8]);
+template <>
+__device__ __forceinline__ void ld8<float>(const float* p, float v[8]) {
+  float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float v[8]) {
+  uint4 r = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    v[2 * k] = __low2float(h[k]);
+    v[2 * k + 1] = __high2float(h[k]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void st8(T* p, const float v[8]);
+template <>
+__device__ __forceinline__ void st8<float>(float* p, const float v[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16* p, const float v[8]) {
+  uint4 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = r;
+}
+
+// y = LN(x + residual) * gamma + beta ; optionally stores z = x + residual (needed by backward when a
+// residual is given), and per-row mean / rstd.
+template <typename T, int NV>
+__global__ void __launch_bounds__(32 * HM_LN_WARPS)
+ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const float* __restrict__ gamma,
+              const float* __restrict__ beta, T* __restrict__ y, T* __restrict__ z, float* __restrict__ mean_out,
+              float* __restrict__ rstd_out, int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * HM_LN_WARPS + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * HM_LN_WARPS;
+  const float inv_h = 1.f / (float)H;
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const size_t base = (size_t)row * H;
+    float v[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        ld8<T>(x + base + col, v[j]);
+        if (residual) {
+          float r[8];
+          ld8<T>(residual + base + col, r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[j][k] += r[k];
+          if (z) st8<T>(z + base + col, v[j]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += v[j][k];
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j][k] = 0.f;
+      }
+    }
+    const float mean = hm_warp_sum(s) * inv_h;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float d = v[j][k] - mean;
+          q = fmaf(d, d, q);
+        }
+      }
+    }
+    const float rstd = rsqrtf(hm_warp_sum(q) * inv_h + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        float g[8], b[8], o[8];
+        ld8<float>(gamma + col, g);
+        ld8<float>(beta + col, b);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = fmaf((v[j][k] - mean) * rstd, g[k], b[k]);
+        st8<T>(y + base + col, o);
+      }
+    }
+  }
+}
+
+// Backward: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)); dgamma += sum dy*xhat; dbeta += sum dy.
+// `zin` is the normalised input (x, or x + residual). dgamma/dbeta are fp32 buffers zeroed by the caller;
+// each CTA adds its partial sums with atomics once at the end.
+template <typename T, int NV>
+__global__ void __launch_bounds__(32 * HM_LN_WARPS)
+ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ zin, const float* __restrict__ gamma,
+              const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+              float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int H) {
+  __shared__ float sg[HM_LN_WARPS][32 * 8 + 8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warp_global = blockIdx.x * HM_LN_WARPS + warp;
+  const int warps_total = gridDim.x * HM_LN_WARPS;
+  const float inv_h = 1.f / (float)H;
+  float ag[NV][8], ab[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ag[j][k] = ab[j][k] = 0.f;
+
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const size_t base = (size_t)row * H;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[NV][8], gd[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        float d[8], g[8];
+        ld8<T>(dy + base + col, d);
+        ld8<T>(zin + base + col, xh[j]);
+        ld8<float>(gamma + col, g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          xh[j][k] = (xh[j][k] - mean) * rstd;
+          ag[j][k] = fmaf(d[k], xh[j][k], ag[j][k]);
+          ab[j][k] += d[k];
+          gd[j][k] = d[k] * g[k];
+          s1 += gd[j][k];
+          s2 = fmaf(gd[j][k], xh[j][k], s2);
+        }
+      }
+    }
+    s1 = hm_warp_sum(s1) * inv_h;
+    s2 = hm_warp_sum(s2) * inv_h;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = rstd * (gd[j][k] - s1 - xh[j][k] * s2);
+        st8<T>(dx + base + col, o);
+      }
+    }
+  }
+  // reduce the per-warp column sums inside the CTA, then one atomic per column per CTA
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sg[warp][lane * 8 + k] = pass == 0 ? ag[j][k] : ab[j][k];
+      __syncthreads();
+      if (warp == 0 && col < H) {
+        float* dst = pass == 0 ? dgamma : dbeta;
+        if (dst) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < HM_LN_WARPS; ++w) t += sg[w][lane * 8 + k];
+            atomicAdd(dst + col + k, t);
+          }
+        }
+      }
+    }
+  }
+}
+
+// y = gelu_tanh(x + bias)
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_gelu_fwd_kernel(const T* __restrict__ x, const float* __restrict__ bias, T* __restrict__ y, long long rows,
+                     int H) {
+  const long long total8 = rows * (long long)(H / 8);
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total8; i += 256LL * gridDim.x) {
+    const int col = (int)(i % (H / 8)) * 8;
+    float v[8], b[8];
+    ld8<T>(x + i * 8, v);
+    if (bias) ld8<float>(bias + col, b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = hm_gelu_tanh(v[k] + (bias ? b[k] : 0.f));
+    st8<T>(y + i * 8, v);
+  }
+}
+
+// dx = dy * gelu'(x + bias); dbias += column sums of dx (fp32 atomics; zeroed by the caller).
+// Grid: (ceil(H / 256), row_blocks). A thread owns one column and walks rows, so the row sum stays in a register.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ bias,
+                     T* __restrict__ dx, float* __restrict__ dbias, long long rows, int H) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col >= H) return;
+  const float b = bias ? bias[col] : 0.f;
+  const long long per = (rows + gridDim.y - 1) / gridDim.y;
+  const long long r0 = per * blockIdx.y, r1 = r0 + per < rows ? r0 + per : rows;
+  float acc = 0.f;
+  for (long long r = r0; r < r1; ++r) {
+    const size_t idx = (size_t)r * H + col;
+    float xv, dv;
+    if constexpr (sizeof(T) == 2) {
+      xv = __bfloat162float(x[idx]);
+      dv = __bfloat162float(dy[idx]);
+    } else {
+      xv = x[idx];
+      dv = dy[idx];
+    }
+    const float g = dv * hm_gelu_tanh_grad(xv + b);
+    acc += g;
+    if constexpr (sizeof(T) == 2) dx[idx] = __float2bfloat16(g);
+    else dx[idx] = g;
+  }
+  if (dbias) atomicAdd(dbias + col, acc);
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T, int NV>
+static int ln_fwd_launch(const void* x, const void* res, const void* gamma, const void* beta, void* y, void* z,
+                         void* mean, void* rstd, int rows, int H, float eps, int sms, cudaStream_t stream) {
+  int blocks = (rows + HM_LN_WARPS - 1) / HM_LN_WARPS;
+  const int cap = sms * 8;
+  if (blocks > cap) blocks = cap;
+  ln_fwd_kernel<T, NV><<<blocks, 32 * HM_LN_WARPS, 0, stream>>>((const T*)x, (const T*)res, (const float*)gamma,
+                                                               (const float*)beta, (T*)y, (T*)z, (float*)mean,
+                                                               (float*)rstd, rows, H, eps);
+  return (int)cudaGetLastError();
+}
+template <typename T, int NV>
+static int ln_bwd_launch(const void* dy, const void* zin, const void* gamma, const void* mean, const void* rstd,
+                         void* dx, void* dgamma, void* dbeta, int rows, int H, int sms, cudaStream_t stream) {
+  int blocks = (rows + HM_LN_WARPS - 1) / HM_LN_WARPS;
+  const int cap = sms * 4;
+  if (blocks > cap) blocks = cap;
+  ln_bwd_kernel<T, NV><<<blocks, 32 * HM_LN_WARPS, 0, stream>>>((const T*)dy, (const T*)zin, (const float*)gamma,
+                                                               (const float*)mean, (const float*)rstd, (T*)dx,
+                                                               (float*)dgamma, (float*)dbeta, rows, H);
+  return (int)cudaGetLastError();
+}
+
+#define HM_LN_DISPATCH(FN, ...)                                                   \
+  do {                                                                            \
+    const int nv = (H + 255) / 256;                                               \
+    if (H % 8 != 0 || nv > HM_LN_MAXV) return -1;                                 \
+    if (dtype == HM_BF16) {                                                       \
+      if (nv <= 1) return FN<__nv_bfloat16, 1>(__VA_ARGS__);                      \
+      if (nv <= 2) return FN<__nv_bfloat16, 2>(__VA_ARGS__);                      \
+      if (nv <= 4) return FN<__nv_bfloat16, 4>(__VA_ARGS__);                      \
+      return FN<__nv_bfloat16, 8>(__VA_ARGS__);                                   \
+    } else if (dtype == HM_F32) {                                                 \
+      if (nv <= 1) return FN<float, 1>(__VA_ARGS__);                              \
+      if (nv <= 2) return FN<float, 2>(__VA_ARGS__);                              \
+      if (nv <= 4) return FN<float, 4>(__VA_ARGS__);                              \
+      return FN<float, 8>(__VA_ARGS__);                                           \
+    }                                                                             \
+    return -2;                                                                    \
+  } while (0)
+
+HM_API int hm_layernorm_fwd(const void* x, const void* residual, const void* gamma, const void* beta, void* y, void* z,
+                            void* mean, void* rstd, int rows, int H, float eps, int dtype, int sms,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  HM_LN_DISPATCH(ln_fwd_launch, x, residual, gamma, beta, y, z, mean, rstd, rows, H, eps, sms, stream);
+}
+
+HM_API int hm_layernorm_bwd(const void* dy, const void* zin, const void* gamma, const void* mean, const void* rstd,
+                            void* dx, void* dgamma, void* dbeta, int rows, int H, int dtype, int sms,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  HM_LN_DISPATCH(ln_bwd_launch, dy, zin, gamma, mean, rstd, dx, dgamma, dbeta, rows, H, sms, stream);
+}
+
+HM_API int hm_bias_gelu_fwd(const void* x, const void* bias, void* y, long long rows, int H, int dtype, int sms,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 != 0) return -1;
+  const long long total8 = rows * (long long)(H / 8);
+  long long blocks = (total8 + 255) / 256;
+  if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
+  if (dtype == HM_BF16)
+    bias_gelu_fwd_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (const float*)bias,
+                                                                        (__nv_bfloat16*)y, rows, H);
+  else if (dtype == HM_F32)
+    bias_gelu_fwd_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, (const float*)bias, (float*)y, rows, H);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
+HM_API int hm_bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx, void* dbias, long long rows,
+                            int H, int dtype, int sms, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int gx = (H + 255) / 256;
+  int gy = (sms * 8 + gx - 1) / gx;
+  if (gy > rows) gy = (int)rows;
+  if (gy < 1) gy = 1;
+  dim3 grid(gx, gy);
+  if (dtype == HM_BF16)
+    bias_gelu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                 (const float*)bias, (__nv_bfloat16*)dx, (float*)dbias,
+                                                                 rows, H);
+  else if (dtype == HM_F32)
+    bias_gelu_bwd_kernel<float><<<grid, 256, 0, stream>>>((const float*)dy, (const float*)x, (const float*)bias,
+                                                         (float*)dx, (float*)dbias, rows, H);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,560 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused epilogues.
+//
+//   D[M,N] (row-major) = epilogue( sum_k A(m,k) * B(n,k) )
+//
+// Operands are bf16 (kind::f16) or fp32 fed as tf32 (kind::tf32); accumulation is fp32 in TMEM.
+// Each operand is either K-major (stored [rows][K], K contiguous) or MN-major (stored [K][rows], rows
+// contiguous), so that y = x W^T, dx = dy W and dW = dy^T x all run without a transposed copy:
+//     forward   y [T,out] : A = x  [T,in]  K-major,  B = W  [out,in] K-major
+//     grad in   dx[T,in]  : A = dy [T,out] K-major,  B = W  [out,in] MN-major (contraction over `out`)
+//     grad w    dW[out,in]: A = dy [T,out] MN-major, B = x  [T,in]   MN-major (contraction over T)
+//
+// Structure (one CTA per SM, 192 threads, tiles 128 x BLOCK_N x 128 bytes of K):
+//   warp 0      : TMA producer — unicast cp.async.bulk.tensor loads into a STAGES-deep smem ring
+//   warp 1      : allocates TMEM, issues tcgen05.mma from one elected lane, commits to mbarriers
+//   warps 2..5  : epilogue — tcgen05.ld the accumulator (double-buffered in TMEM so that the next tile's
+//                 MMAs overlap), apply bias / tanh-GELU, stage in 128B-swizzled smem, TMA store
+//                 (or TMA reduce-add into an fp32 destination: split-K and gradient accumulation for free).
+// Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error word, lets
+// in-flight copies land, frees its TMEM and returns.
+//
+// Call sites served: the expert FFN of hivemind/moe/server/layers/common.py:17-30, the transformer
+// blocks of the ALBERT / GPT-2 shaped models, and PowerSGD's P = M Q, Q = M^T P
+// (hivemind/optim/power_sgd_averager.py:158-170).
+#include <cuda.h>
+#include "hm_common.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int ROW_BYTES = 128;           // one swizzle-128B row
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr unsigned long long WAIT_BUDGET_NS = 2000000000ull;  // 2 s per wait
+
+enum Epi : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles, num_splits, kblocks_per_split, total_kblocks;
+  int epi, out_f32, reduce_add, has_aux;
+  const float* bias;
+  float alpha;
+  int* err;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the budget ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = hm_globaltimer_ns();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (hm_globaltimer_ns() - t0 > WAIT_BUDGET_NS) return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
+               "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool TF32>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+//   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO is not used by swizzled K-major layouts.
+//   MN-major: 128 B = one run of contiguous MN elements; 8 K-rows form a 1024 B group (SBO); the next run
+//             of MN elements starts LBO bytes further on.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor: fp32 accumulate, A/B format (1 = bf16, 2 = tf32), majorness, N >> 3, M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(int fmt, bool a_mn, bool b_mn, int m, int n) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((a_mn ? 1u : 0u) << 15) |
+         ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BLOCK_N, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
+  static constexpr int B_BYTES = BLOCK_N * ROW_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int OUT_BYTES = BLOCK_M * ROW_BYTES;  // one staged box: 128 rows x 128 B
+  static constexpr int OUT_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = OUT_OFF + 2 * OUT_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
+};
+
+// ---------------------------------------------------------------------------------------------
+template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_aux,
+               const GemmParams p) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  constexpr int ELEM = TF32 ? 4 : 2;
+  constexpr int BLOCK_K = ROW_BYTES / ELEM;   // elements of K per stage (one 128 B swizzle row)
+  constexpr int UMMA_K = 32 / ELEM;
+  constexpr int RUN = ROW_BYTES / ELEM;       // contiguous MN elements per 128 B row of an MN-major tile
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N <= 32 ? 32 : (2 * BLOCK_N <= 64 ? 64 : (2 * BLOCK_N <= 128 ? 128 : (2 * BLOCK_N <= 256 ? 256 : 512)));
+  constexpr uint32_t IDESC = make_idesc(TF32 ? 2 : 1, A_MN, B_MN, BLOCK_M, BLOCK_N);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // 1024 B alignment for the swizzle atoms (dynamic smem base is only guaranteed 16 B aligned)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::BAR_OFF + L::NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BAR_OFF + L::NUM_BARS * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), EPI_THREADS);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int tile, int& m_tile, int& n_tile, int& split) {
+    split = tile % p.num_splits;
+    const int t = tile / p.num_splits;
+    n_tile = t % p.num_n_tiles;
+    m_tile = t / p.num_n_tiles;
+  };
+
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+        int m_tile, n_tile, split;
+        tile_coords(tile, m_tile, n_tile, split);
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.total_kblocks);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { failed = true; break; }
+          const uint32_t a_dst = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + L::A_BYTES;
+          mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int r = 0; r < BLOCK_M / RUN; ++r)
+              tma_load_2d(a_dst + r * (BLOCK_K * ROW_BYTES), &map_a, full_bar(stage), m_tile * BLOCK_M + r * RUN, k0);
+          } else {
+            tma_load_2d(a_dst, &map_a, full_bar(stage), k0, m_tile * BLOCK_M);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int r = 0; r < BLOCK_N / RUN; ++r)
+              tma_load_2d(b_dst + r * (BLOCK_K * ROW_BYTES), &map_b, full_bar(stage), n_tile * BLOCK_N + r * RUN, k0);
+          } else {
+            tma_load_2d(b_dst, &map_b, full_bar(stage), k0, n_tile * BLOCK_N);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
+        int m_tile, n_tile, split;
+        tile_coords(tile, m_tile, n_tile, split);
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.total_kblocks);
+        const int buf = local & 1;
+        const uint32_t use = (uint32_t)(local >> 1);
+        if (!mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BLOCK_N);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, 1024)
+                                         : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, 1024)
+                                         : make_smem_desc(b_addr + k * 32, 16, 1024);
+            tc_mma<TF32>(d_tmem, a_desc, b_desc, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        tc_commit(tfull_bar(buf));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;               // TMEM lane quarter this warp may read
+    const int row = quad * 32 + lane;        // row inside the tile
+    const int epi_tid = threadIdx.x - 64;
+    uint8_t* out_buf[2] = {smem + L::OUT_OFF, smem + L::OUT_OFF + L::OUT_BYTES};
+    constexpr int COLS_PER_BOX = 32;          // accumulator columns handled per tcgen05.ld
+    const int out_elem = p.out_f32 ? 4 : 2;
+    const int boxes_per_store = p.out_f32 ? 1 : 2;  // 128 B rows: 32 fp32 or 64 bf16
+    int local = 0;
+    int flip = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
+      int m_tile, n_tile, split;
+      tile_coords(tile, m_tile, n_tile, split);
+      const int buf = local & 1;
+      const uint32_t use = (uint32_t)(local >> 1);
+      // every epilogue thread waits; the four warps then agree on the outcome, so that the warp-wide
+      // tcgen05.ld and the named barriers below are never reached by only part of the group
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), use & 1, abort_flag));
+      if (!ok) *abort_flag = 1;
+      epi_bar_sync();
+      if (*abort_flag) { failed = true; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
+      const int n_valid = min(BLOCK_N, p.N - n_tile * BLOCK_N);
+      for (int c0 = 0; c0 < BLOCK_N; c0 += COLS_PER_BOX * boxes_per_store) {
+        if (c0 >= n_valid) break;  // columns beyond N: nothing to store (uniform across the CTA)
+        // the staging buffer we are about to fill must have been read by its previous TMA store
+        if (epi_tid == 0) {
+          if (p.has_aux) tma_wait_read<0>(); else tma_wait_read<1>();
+        }
+        epi_bar_sync();
+        uint8_t* stage_main = p.has_aux ? out_buf[0] : out_buf[flip];
+        uint8_t* stage_aux = out_buf[1];
+#pragma unroll 1
+        for (int half = 0; half < boxes_per_store; ++half) {
+          uint32_t r[32];
+          tc_ld32(t_addr + (uint32_t)(c0 + half * COLS_PER_BOX), r);
+          tc_wait_ld();
+          float v[32];
+          const int gcol0 = n_tile * BLOCK_N + c0 + half * COLS_PER_BOX;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r[j]) * p.alpha;
+            if (p.epi != EPI_NONE && p.bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(p.bias + gcol0 + j);
+          }
+          // 16-byte chunks of this thread's row, XOR-swizzled like the tensor map (chunk ^= row & 7)
+          if (p.out_f32) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              float4 o = make_float4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+              if (p.epi == EPI_BIAS_GELU) { o.x = hm_gelu_tanh(o.x); o.y = hm_gelu_tanh(o.y); o.z = hm_gelu_tanh(o.z); o.w = hm_gelu_tanh(o.w); }
+              *reinterpret_cast<float4*>(stage_main + row * ROW_BYTES + ((ch ^ (row & 7)) << 4)) = o;
+            }
+          } else {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const int pc = (half * 4 + ch) ^ (row & 7);
+              if (p.has_aux) {
+                uint4 a;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * ch], v[8 * ch + 1]), h1 = __floats2bfloat162_rn(v[8 * ch + 2], v[8 * ch + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * ch + 4], v[8 * ch + 5]), h3 = __floats2bfloat162_rn(v[8 * ch + 6], v[8 * ch + 7]);
+                a.x = *reinterpret_cast<uint32_t*>(&h0); a.y = *reinterpret_cast<uint32_t*>(&h1);
+                a.z = *reinterpret_cast<uint32_t*>(&h2); a.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(stage_aux + row * ROW_BYTES + (pc << 4)) = a;
+              }
+              float w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = p.epi == EPI_BIAS_GELU ? hm_gelu_tanh(v[8 * ch + j]) : v[8 * ch + j];
+              uint4 o;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(w[0], w[1]), h1 = __floats2bfloat162_rn(w[2], w[3]);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(w[4], w[5]), h3 = __floats2bfloat162_rn(w[6], w[7]);
+              o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+              o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(stage_main + row * ROW_BYTES + (pc << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          const int gc = n_tile * BLOCK_N + c0, gr = m_tile * BLOCK_M;
+          if (p.reduce_add) tma_reduce_add_2d(&map_d, smem_u32(stage_main), gc, gr);
+          else tma_store_2d(&map_d, smem_u32(stage_main), gc, gr);
+          if (p.has_aux) tma_store_2d(&map_aux, smem_u32(stage_aux), gc, gr);
+          tma_commit();
+        }
+        flip ^= 1;
+        (void)out_elem;
+      }
+      // all of this thread's tcgen05.ld for the buffer are complete: hand the accumulator back
+      tc_fence_before();
+      mbar_arrive(tempty_bar(buf));
+    }
+    if (epi_tid == 0) tma_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown (every thread gets here)
+  if (failed) {
+    *abort_flag = 1;
+    if (p.err) atomicExch(p.err, 1 + warp);
+    // let copies that are still in flight land before the CTA's shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tc_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+
+// 2-D map over a row-major matrix [rows][cols] with leading dimension ld (elements); box = box_cols x box_rows.
+int make_map(CUtensorMap* map, const void* base, int elem_bytes, bool is_f32, long long rows, long long cols,
+             long long ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return -11;
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)(ld * elem_bytes)};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+struct GemmCall {
+  const void *a, *b;
+  void *d, *aux;
+  const float* bias;
+  int M, N, K;
+  long long lda, ldb, ldd, ldaux;
+  int a_mn, b_mn, tf32, out_f32, epi, reduce_add, splits;
+  float alpha;
+  int* err;
+  int sms;
+};
+
+template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN>
+int launch(const GemmCall& c, cudaStream_t stream) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  constexpr int ELEM = TF32 ? 4 : 2;
+  constexpr int BLOCK_K = ROW_BYTES / ELEM;
+  constexpr int RUN = ROW_BYTES / ELEM;
+  CUtensorMap ma, mb, md, maux;
+  int rc;
+  // A: K-major -> matrix [M][K], box BLOCK_K x BLOCK_M. MN-major -> matrix [K][M], box RUN x BLOCK_K.
+  rc = A_MN ? make_map(&ma, c.a, ELEM, TF32, c.K, c.M, c.lda, RUN, BLOCK_K)
+            : make_map(&ma, c.a, ELEM, TF32, c.M, c.K, c.lda, BLOCK_K, BLOCK_M);
+  if (rc) return rc;
+  rc = B_MN ? make_map(&mb, c.b, ELEM, TF32, c.K, c.N, c.ldb, RUN, BLOCK_K)
+            : make_map(&mb, c.b, ELEM, TF32, c.N, c.K, c.ldb, BLOCK_K, BLOCK_N);
+  if (rc) return rc;
+  const int out_elem = c.out_f32 ? 4 : 2;
+  rc = make_map(&md, c.d, out_elem, c.out_f32 != 0, c.M, c.N, c.ldd, ROW_BYTES / out_elem, BLOCK_M);
+  if (rc) return rc;
+  if (c.aux) {
+    rc = make_map(&maux, c.aux, 2, false, c.M, c.N, c.ldaux, ROW_BYTES / 2, BLOCK_M);
+    if (rc) return rc;
+  } else {
+    maux = md;
+  }
+  GemmParams p;
+  p.M = c.M; p.N = c.N; p.K = c.K;
+  p.num_m_tiles = (c.M + BLOCK_M - 1) / BLOCK_M;
+  p.num_n_tiles = (c.N + BLOCK_N - 1) / BLOCK_N;
+  p.total_kblocks = (c.K + BLOCK_K - 1) / BLOCK_K;
+  int splits = c.splits < 1 ? 1 : c.splits;
+  if (splits > p.total_kblocks) splits = p.total_kblocks;
+  p.kblocks_per_split = (p.total_kblocks + splits - 1) / splits;
+  p.num_splits = (p.total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  if (p.num_splits > 1 && !c.reduce_add) return -13;
+  p.epi = c.epi; p.out_f32 = c.out_f32; p.reduce_add = c.reduce_add; p.has_aux = c.aux != nullptr;
+  p.bias = c.bias; p.alpha = c.alpha; p.err = c.err;
+  const int tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+  if (tiles <= 0 || p.total_kblocks <= 0) return 0;
+  const int grid = tiles < c.sms ? tiles : c.sms;
+  auto kern = tc_gemm_kernel<BLOCK_N, STAGES, TF32, A_MN, B_MN>;
+  const int smem = L::TOTAL + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, NUM_THREADS, smem, stream>>>(ma, mb, md, maux, p);
+  return (int)cudaGetLastError();
+}
+
+template <int BLOCK_N, int STAGES, bool TF32>
+int dispatch_major(const GemmCall& c, cudaStream_t s) {
+  if (c.a_mn) return c.b_mn ? launch<BLOCK_N, STAGES, TF32, true, true>(c, s) : launch<BLOCK_N, STAGES, TF32, true, false>(c, s);
+  return c.b_mn ? launch<BLOCK_N, STAGES, TF32, false, true>(c, s) : launch<BLOCK_N, STAGES, TF32, false, false>(c, s);
+}
+
+}  // namespace
+
+// D = epilogue(alpha * A B^T) on tensor cores. Returns 0, a CUDA error (> 0) or a negative argument error.
+//   a_mn / b_mn : 0 = operand stored [rows][K] (K contiguous), 1 = stored [K][rows] (rows contiguous)
+//   tf32        : operands are fp32 and multiplied as tf32; otherwise bf16
+//   out_f32     : D is fp32 (required for reduce_add); otherwise bf16
+//   epi         : 0 none, 1 + bias[N], 2 gelu_tanh(. + bias[N]); aux (bf16, optional) receives the pre-GELU values
+//   reduce_add  : D += result through TMA reduce-add (D must be fp32); needed when splits > 1
+//   block_n     : 256, 128, 64 or 32 (N tile); err: device int set non-zero if a bounded wait ran out
+HM_API int hm_tc_gemm(const void* a, const void* b, void* d, void* aux, const void* bias, int M, int N, int K,
+                      long long lda, long long ldb, long long ldd, long long ldaux, int a_mn, int b_mn, int tf32,
+                      int out_f32, int epi, int reduce_add, int splits, float alpha, int block_n, void* err, int sms,
+                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (reduce_add && !out_f32) return -14;
+  if (aux && out_f32) return -15;
+  GemmCall c{a, b, d, aux, (const float*)bias, M, N, K, lda, ldb, ldd, ldaux, a_mn, b_mn, tf32, out_f32, epi,
+             reduce_add, splits, alpha, (int*)err, sms};
+  if (tf32) {
+    switch (block_n) {
+      case 128: return dispatch_major<128, 4, true>(c, stream);
+      case 64: return dispatch_major<64, 6, true>(c, stream);
+      case 32: return dispatch_major<32, 8, true>(c, stream);
+      default: return -16;
+    }
+  }
+  switch (block_n) {
+    case 256: return dispatch_major<256, 4, false>(c, stream);
+    case 128: return dispatch_major<128, 6, false>(c, stream);
+    case 64: return dispatch_major<64, 8, false>(c, stream);
+    default: return -16;
+  }
+}

@@ -1,0 +1,127 @@
+"""LayerNorm (optionally fused with a residual add) and bias + tanh-GELU as autograd functions.
+
+CUDA tensors run the sm_100a kernels of ``csrc/norm_act.cu``; CPU tensors run the PyTorch formulas below, which
+double as the fp32 oracle of the GPU tests. The tanh form of GELU is the one the reference's ``ffn`` expert uses
+(hivemind/moe/server/layers/common.py:11-12).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from hivemind_b200.ops import _lib
+
+_MAX_H = 8 * 32 * 8
+
+
+def _kernel_ok(x: torch.Tensor, h: int) -> bool:
+    return _lib.use_kernels(x) and x.dtype in (torch.bfloat16, torch.float32) and h % 8 == 0 and h <= _MAX_H
+
+
+def gelu_tanh_reference(x: torch.Tensor) -> torch.Tensor:
+    return F.gelu(x, approximate="tanh")
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, gamma, beta, eps):
+        h = x.shape[-1]
+        x2 = x.reshape(-1, h).contiguous()
+        r2 = residual.reshape(-1, h).contiguous() if residual is not None else None
+        rows = x2.shape[0]
+        lib = _lib.load_library()
+        y = torch.empty_like(x2)
+        z = torch.empty_like(x2) if r2 is not None else None
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        g32 = gamma.detach().to(torch.float32).contiguous()
+        b32 = beta.detach().to(torch.float32).contiguous()
+        with torch.cuda.device(x.device):
+            code = lib.hm_layernorm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(g32), _lib.ptr(b32), _lib.ptr(y),
+                                        _lib.ptr(z), _lib.ptr(mean), _lib.ptr(rstd), rows, h, ctypes.c_float(eps),
+                                        _lib.dtype_code(x.dtype), _lib.sm_count(x.device), _lib.stream_ptr(x.device))
+        _lib.check(code, "hm_layernorm_fwd")
+        ctx.save_for_backward(z if z is not None else x2, g32, mean, rstd)
+        ctx.has_residual = r2 is not None
+        ctx.shape = x.shape
+        ctx.param_dtype = (gamma.dtype, beta.dtype)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        zin, g32, mean, rstd = ctx.saved_tensors
+        h = zin.shape[-1]
+        rows = zin.shape[0]
+        dy2 = dy.reshape(-1, h).contiguous()
+        if dy2.dtype != zin.dtype:
+            dy2 = dy2.to(zin.dtype)
+        lib = _lib.load_library()
+        dx = torch.empty_like(zin)
+        dgb = torch.zeros(2, h, dtype=torch.float32, device=zin.device)
+        with torch.cuda.device(zin.device):
+            code = lib.hm_layernorm_bwd(_lib.ptr(dy2), _lib.ptr(zin), _lib.ptr(g32), _lib.ptr(mean), _lib.ptr(rstd),
+                                        _lib.ptr(dx), _lib.ptr(dgb[0]), _lib.ptr(dgb[1]), rows, h,
+                                        _lib.dtype_code(zin.dtype), _lib.sm_count(zin.device),
+                                        _lib.stream_ptr(zin.device))
+        _lib.check(code, "hm_layernorm_bwd")
+        dx = dx.view(ctx.shape)
+        return dx, (dx if ctx.has_residual else None), dgb[0].to(ctx.param_dtype[0]), dgb[1].to(ctx.param_dtype[1]), None
+
+
+def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
+               residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``LayerNorm(x + residual)`` over the last dimension (``residual`` optional), statistics in fp32."""
+    h = x.shape[-1]
+    if _kernel_ok(x, h):
+        return _LayerNormFn.apply(x, residual, gamma, beta, eps)
+    z = x if residual is None else x + residual
+    return F.layer_norm(z.to(torch.float32), (h,), gamma.to(torch.float32), beta.to(torch.float32), eps).to(x.dtype)
+
+
+class _BiasGeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias):
+        h = x.shape[-1]
+        x2 = x.reshape(-1, h).contiguous()
+        rows = x2.shape[0]
+        lib = _lib.load_library()
+        y = torch.empty_like(x2)
+        b32 = bias.detach().to(torch.float32).contiguous() if bias is not None else None
+        with torch.cuda.device(x.device):
+            code = lib.hm_bias_gelu_fwd(_lib.ptr(x2), _lib.ptr(b32), _lib.ptr(y), ctypes.c_longlong(rows), h,
+                                        _lib.dtype_code(x.dtype), _lib.sm_count(x.device), _lib.stream_ptr(x.device))
+        _lib.check(code, "hm_bias_gelu_fwd")
+        ctx.save_for_backward(x2, b32)
+        ctx.shape = x.shape
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, b32 = ctx.saved_tensors
+        h = x2.shape[-1]
+        rows = x2.shape[0]
+        dy2 = dy.reshape(-1, h).contiguous()
+        if dy2.dtype != x2.dtype:
+            dy2 = dy2.to(x2.dtype)
+        lib = _lib.load_library()
+        dx = torch.empty_like(x2)
+        db = torch.zeros(h, dtype=torch.float32, device=x2.device) if b32 is not None else None
+        with torch.cuda.device(x2.device):
+            code = lib.hm_bias_gelu_bwd(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(b32), _lib.ptr(dx), _lib.ptr(db),
+                                        ctypes.c_longlong(rows), h, _lib.dtype_code(x2.dtype),
+                                        _lib.sm_count(x2.device), _lib.stream_ptr(x2.device))
+        _lib.check(code, "hm_bias_gelu_bwd")
+        return dx.view(ctx.shape), (db.to(ctx.bias_dtype) if db is not None else None)
+
+
+def bias_gelu(x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``gelu_tanh(x + bias)`` over the last dimension."""
+    h = x.shape[-1]
+    if _lib.use_kernels(x) and x.dtype in (torch.bfloat16, torch.float32) and h % 8 == 0:
+        return _BiasGeluFn.apply(x, bias)
+    z = x if bias is None else x + bias.to(x.dtype)
+    return gelu_tanh_reference(z)

@@ -1,0 +1,252 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same ops."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("h", [128, 1024, 1536])
+def test_layernorm_fwd_bwd(dtype, h):
+    from hivemind_b200.ops.norm_act import layer_norm
+
+    torch.manual_seed(0)
+    rows = 777
+    x = torch.randn(rows, h, device=_dev(), dtype=dtype, requires_grad=True)
+    r = torch.randn(rows, h, device=_dev(), dtype=dtype, requires_grad=True)
+    g = (torch.rand(h, device=_dev()) + 0.5).requires_grad_()
+    b = torch.randn(h, device=_dev()).requires_grad_()
+    y = layer_norm(x, g, b, 1e-12, residual=r)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, rr, gr, br = (t.detach().float().requires_grad_() for t in (x, r, g, b))
+    yr = F.layer_norm(xr + rr, (h,), gr, br, 1e-12)
+    yr.backward(dy.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)
+    assert torch.allclose(r.grad.float(), rr.grad, atol=tol, rtol=tol)
+    assert torch.allclose(g.grad, gr.grad, atol=tol * 30, rtol=tol)
+    assert torch.allclose(b.grad, br.grad, atol=tol * 30, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bias_gelu(dtype):
+    from hivemind_b200.ops.norm_act import bias_gelu
+
+    torch.manual_seed(1)
+    x = torch.randn(513, 4096, device=_dev(), dtype=dtype, requires_grad=True)
+    b = torch.randn(4096, device=_dev(), requires_grad=True)
+    y = bias_gelu(x, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, br = x.detach().float().requires_grad_(), b.detach().clone().requires_grad_()
+    yr = F.gelu(xr + br, approximate="tanh")
+    yr.backward(dy.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 2e-3
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)
+    assert torch.allclose(b.grad, br.grad, atol=0.5 if dtype == torch.bfloat16 else 1e-2, rtol=tol)
+
+
+def test_multi_tensor_elementwise():
+    from hivemind_b200.ops import multi_tensor as mt
+
+    torch.manual_seed(2)
+    shapes = [(1000,), (17, 33), (4096, 64), (3,), (1,)]
+    acc = [torch.randn(s, device=_dev()) for s in shapes]
+    grads = [torch.randn(s, device=_dev()).to(torch.bfloat16 if i % 2 else torch.float32) for i, s in enumerate(shapes)]
+    ref = [a.clone() + 0.25 * g.float() for a, g in zip(acc, grads)]
+    mt.axpy_(acc, grads, 0.25)
+    for a, r in zip(acc, ref):
+        assert torch.allclose(a, r, atol=1e-6)
+    out = [torch.empty(s, device=_dev(), dtype=torch.bfloat16) for s in shapes]
+    mt.scale_copy_(out, acc, 0.5)
+    for o, a in zip(out, acc):
+        assert torch.allclose(o.float(), (a * 0.5).to(torch.bfloat16).float())
+    assert mt.all_finite(acc)
+    acc[2][5, 7] = float("inf")
+    assert not mt.all_finite(acc)
+    acc[2][5, 7] = 0.0
+    sq = mt.sumsq(acc)
+    for i, a in enumerate(acc):
+        assert torch.allclose(sq[i], a.pow(2).sum(), rtol=1e-4)
+    total = math.sqrt(float(sq[-1]))
+    norm = mt.clip_grad_norm_(acc, total / 2)
+    assert abs(float(norm) - total) / total < 1e-4
+    assert abs(math.sqrt(float(mt.sumsq(acc)[-1])) - total / 2) / total < 1e-3
+    mt.zero_(acc)
+    assert all(float(a.abs().sum()) == 0 for a in acc)
+    local = [torch.randn(s, device=_dev()) for s in shapes]
+    new = [torch.randn(s, device=_dev()) for s in shapes]
+    old = [torch.randn(s, device=_dev()) for s in shapes]
+    ref = [l + (n - o) for l, n, o in zip(local, new, old)]
+    mt.delta_update_(local, new, old)
+    for l, r in zip(local, ref):
+        assert torch.allclose(l, r, atol=1e-6)
+
+
+def _clone_all(ts):
+    return [t.clone() for t in ts]
+
+
+@pytest.mark.parametrize("decoupled", [False, True])
+def test_adam_matches_torch(decoupled):
+    from hivemind_b200.ops import multi_tensor as mt
+
+    torch.manual_seed(3)
+    shapes = [(1024, 128), (77,), (30000, 16)]
+    params = [torch.randn(s, device=_dev()) for s in shapes]
+    ref_params = [p.clone().requires_grad_() for p in params]
+    opt_cls = torch.optim.AdamW if decoupled else torch.optim.Adam
+    ref_opt = opt_cls(ref_params, lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    m = [torch.zeros_like(p) for p in params]
+    v = [torch.zeros_like(p) for p in params]
+    for step in range(1, 4):
+        grads = [torch.randn_like(p) for p in params]
+        for rp, g in zip(ref_params, grads):
+            rp.grad = g.clone()
+        ref_opt.step()
+        mt.adam_step_(params, grads, m, v, step=step, lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1,
+                      decoupled=decoupled)
+    for p, rp in zip(params, ref_params):
+        assert torch.allclose(p, rp.detach(), atol=2e-5, rtol=1e-4)
+
+
+def test_lamb_matches_reference_formula():
+    from hivemind_b200.ops import multi_tensor as mt
+
+    torch.manual_seed(4)
+    shapes = [(512, 256), (1024,), (100, 100)]
+    params = [torch.randn(s, device=_dev()) for s in shapes]
+    cpu_params = [p.cpu().clone() for p in params]
+    state = [[torch.zeros_like(p) for p in params] for _ in range(3)]
+    cpu_state = [[torch.zeros_like(p) for p in cpu_params] for _ in range(3)]
+    lp = [torch.empty_like(p, dtype=torch.bfloat16) for p in params]
+    for step in range(1, 4):
+        grads = [torch.randn_like(p) for p in params]
+        kw = dict(step=step, lr=1.76e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, clamp_value=10000.0)
+        mt.lamb_step_(params, grads, state[0], state[1], state[2], model_copies=lp, **kw)
+        mt.lamb_step_(cpu_params, [g.cpu() for g in grads], cpu_state[0], cpu_state[1], cpu_state[2], **kw)
+    for p, cp, l in zip(params, cpu_params, lp):
+        assert torch.allclose(p.cpu(), cp, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(l.float(), p.to(torch.bfloat16).float())
+
+
+def test_sgd_momentum():
+    from hivemind_b200.ops import multi_tensor as mt
+
+    torch.manual_seed(5)
+    params = [torch.randn(300, 70, device=_dev())]
+    ref = [params[0].clone().requires_grad_()]
+    opt = torch.optim.SGD(ref, lr=0.1, momentum=0.9, weight_decay=0.01, nesterov=True)
+    buf = [torch.zeros_like(params[0])]
+    for step in range(3):
+        g = [torch.randn_like(params[0])]
+        ref[0].grad = g[0].clone()
+        opt.step()
+        mt.sgd_step_(params, g, buf, lr=0.1, momentum=0.9, weight_decay=0.01, nesterov=True, first_step=step == 0)
+    assert torch.allclose(params[0], ref[0].detach(), atol=1e-5)
+
+
+GEMM_CASES = [
+    # m, n, k, a_mn, b_mn
+    (128, 256, 64, False, False),
+    (256, 512, 256, False, False),
+    (300, 1000, 520, False, False),
+    (256, 256, 192, False, True),
+    (256, 256, 192, True, True),
+    (200, 328, 136, True, False),
+    (1024, 4096, 1024, False, False),
+    (4096, 1024, 2048, True, True),
+]
+
+
+@pytest.mark.parametrize("m,n,k,a_mn,b_mn", GEMM_CASES)
+@pytest.mark.parametrize("block_n", [None, 64, 128])
+def test_tc_gemm_bf16(m, n, k, a_mn, b_mn, block_n):
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn((k, m) if a_mn else (m, k), device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn((k, n) if b_mn else (n, k), device=_dev(), dtype=torch.bfloat16)
+    d = tc_gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=block_n)
+    check_kernel_errors()
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    err = (d.float() - ref).abs().max().item()
+    assert err <= 2e-2 * math.sqrt(k) + 1e-2 * ref.abs().max().item(), err
+
+
+def test_tc_gemm_epilogues():
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(7)
+    m, n, k = 384, 768, 256
+    a = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(n, k, device=_dev(), dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(n, device=_dev())
+    aux = torch.empty(m, n, device=_dev(), dtype=torch.bfloat16)
+    d = tc_gemm(a, b, bias=bias, gelu=True, aux=aux)
+    check_kernel_errors()
+    pre = a.float() @ b.float().t() + bias
+    assert torch.allclose(aux.float(), pre, atol=5e-2, rtol=2e-2)
+    assert torch.allclose(d.float(), F.gelu(pre, approximate="tanh"), atol=5e-2, rtol=2e-2)
+    # fp32 output with reduce-add and split-K
+    acc = torch.ones(m, n, device=_dev())
+    tc_gemm(a, b, out=acc, reduce_add=True, splits=4)
+    check_kernel_errors()
+    assert torch.allclose(acc, 1 + a.float() @ b.float().t(), atol=5e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True), (True, False)])
+@pytest.mark.parametrize("n", [32, 64, 128])
+def test_tc_gemm_tf32(a_mn, b_mn, n):
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(11)
+    m, k = 520, 328
+    a = torch.randn((k, m) if a_mn else (m, k), device=_dev())
+    b = torch.randn((k, n) if b_mn else (n, k), device=_dev())
+    d = tc_gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    check_kernel_errors()
+    ref = (a.t() if a_mn else a).double() @ (b if b_mn else b.t()).double()
+    assert d.dtype == torch.float32
+    assert (d.double() - ref).abs().max().item() < 5e-2 * math.sqrt(k) / 10 + 2e-2
+
+
+def test_linear_autograd():
+    from hivemind_b200.ops.gemm import check_kernel_errors, linear
+
+    torch.manual_seed(13)
+    x = torch.randn(6, 100, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(512, 256, device=_dev()) * 0.05).requires_grad_()
+    b = torch.randn(512, device=_dev()).requires_grad_()
+    for act in (None, "gelu"):
+        x.grad = w.grad = b.grad = None
+        y = linear(x, w, b, activation=act)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        check_kernel_errors()
+        xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+        yr = F.linear(xr, wr.to(torch.bfloat16).float(), br)
+        if act:
+            yr = F.gelu(yr, approximate="tanh")
+        yr.backward(dy.float())
+        assert torch.allclose(y.float(), yr, atol=5e-2, rtol=3e-2)
+        assert torch.allclose(x.grad.float(), xr.grad, atol=5e-2, rtol=3e-2)
+        assert torch.allclose(w.grad, wr.grad, atol=0.35, rtol=3e-2)
+        assert torch.allclose(b.grad, br.grad, atol=0.35, rtol=3e-2)
+    # accumulation straight into an existing fp32 .grad buffer
+    w.grad = torch.ones_like(w)
+    before = w.grad.data_ptr()
+    linear(x, w, b).sum().backward()
+    assert w.grad.data_ptr() == before
+    ref = 1 + x.detach().float().reshape(-1, 256).sum(0).expand(512, 256)
+    assert torch.allclose(w.grad, ref, atol=0.5, rtol=3e-2)
