@@ -159,13 +159,16 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" 
 //   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO is not used by swizzled K-major layouts.
 //   MN-major: 128 B = one run of contiguous MN elements; 8 K-rows form a 1024 B group (SBO); the next run
 //             of MN elements starts LBO bytes further on.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   MN-major tf32 must use the 128-byte swizzle with 32-byte atoms (layout type 1): K-rows come in groups
+//             of 4 (SBO = 512 B) and 32-byte chunks are XOR-ed with the row index modulo 4.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFF) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout_type << 61;
   return d;
 }
 // Instruction descriptor: fp32 accumulate, A/B format (1 = bf16, 2 = tf32), majorness, N >> 3, M >> 4.
@@ -302,9 +305,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t b_addr = a_addr + L::A_BYTES;
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, 1024)
+            constexpr uint32_t MN_SBO = TF32 ? 512 : 1024, MN_TYPE = TF32 ? 1 : 2;
+            const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, MN_SBO, MN_TYPE)
                                          : make_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, 1024)
+            const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, MN_SBO, MN_TYPE)
                                          : make_smem_desc(b_addr + k * 32, 16, 1024);
             tc_mma<TF32>(d_tmem, a_desc, b_desc, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           }
@@ -446,7 +450,7 @@ EncodeTiledFn get_encode_fn() {
 
 // 2-D map over a row-major matrix [rows][cols] with leading dimension ld (elements); box = box_cols x box_rows.
 int make_map(CUtensorMap* map, const void* base, int elem_bytes, bool is_f32, long long rows, long long cols,
-             long long ld, int box_cols, int box_rows) {
+             long long ld, int box_cols, int box_rows, bool atom32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -10;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return -11;
@@ -456,7 +460,8 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, bool is_f32, lo
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
@@ -481,10 +486,10 @@ int launch(const GemmCall& c, cudaStream_t stream) {
   CUtensorMap ma, mb, md, maux;
   int rc;
   // A: K-major -> matrix [M][K], box BLOCK_K x BLOCK_M. MN-major -> matrix [K][M], box RUN x BLOCK_K.
-  rc = A_MN ? make_map(&ma, c.a, ELEM, TF32, c.K, c.M, c.lda, RUN, BLOCK_K)
+  rc = A_MN ? make_map(&ma, c.a, ELEM, TF32, c.K, c.M, c.lda, RUN, BLOCK_K, TF32)
             : make_map(&ma, c.a, ELEM, TF32, c.M, c.K, c.lda, BLOCK_K, BLOCK_M);
   if (rc) return rc;
-  rc = B_MN ? make_map(&mb, c.b, ELEM, TF32, c.K, c.N, c.ldb, RUN, BLOCK_K)
+  rc = B_MN ? make_map(&mb, c.b, ELEM, TF32, c.K, c.N, c.ldb, RUN, BLOCK_K, TF32)
             : make_map(&mb, c.b, ELEM, TF32, c.N, c.K, c.ldb, BLOCK_K, BLOCK_N);
   if (rc) return rc;
   const int out_elem = c.out_f32 ? 4 : 2;

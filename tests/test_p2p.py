@@ -1,0 +1,220 @@
+"""Transport daemon + P2P wrapper + servicer reflection (cases modelled on the reference's tests/test_p2p_daemon.py
+and tests/test_p2p_servicer.py: unary and streaming handlers, errors, cancellation, replicas, balanced handlers)."""
+import asyncio
+from typing import AsyncIterator
+
+import pytest
+
+from hivemind_b200.p2p import P2P, P2PContext, P2PDaemonError, P2PHandlerError, PeerID, ServicerBase
+from hivemind_b200.proto import test_pb2
+
+
+def run(coro):
+    loop = asyncio.new_event_loop()
+    try:
+        return loop.run_until_complete(asyncio.wait_for(coro, 60))
+    finally:
+        loop.close()
+
+
+async def _pair():
+    server = await P2P.create()
+    client = await P2P.create(initial_peers=await server.get_visible_maddrs())
+    return server, client
+
+
+def test_daemon_start_identity_and_peers(tmp_path):
+    async def main():
+        ident = str(tmp_path / "id.key")
+        a = await P2P.create(identity_path=ident)
+        pid = a.peer_id
+        maddrs = await a.get_visible_maddrs()
+        assert maddrs and str(maddrs[0]).endswith(pid.to_base58())
+        b = await P2P.create(initial_peers=maddrs)
+        await b.wait_for_at_least_n_peers(1)
+        assert any(p.peer_id == pid for p in await b.list_peers())
+        await a.shutdown()
+        a2 = await P2P.create(identity_path=ident)
+        assert a2.peer_id == pid  # identity files make the id deterministic
+        await a2.shutdown()
+        await b.shutdown()
+        assert not a.is_alive and not b.is_alive
+
+    run(main())
+
+
+def test_unary_and_errors_and_cancel():
+    async def main():
+        server, client = await _pair()
+        cancelled = asyncio.Event()
+
+        async def square(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+            assert context.remote_id == client.peer_id
+            return test_pb2.TestResponse(number=request.number ** 2)
+
+        async def fail(request, context):
+            raise ValueError("boom")
+
+        async def slow(request, context):
+            try:
+                await asyncio.sleep(30)
+            except asyncio.CancelledError:
+                cancelled.set()
+                raise
+            return test_pb2.TestResponse(number=0)
+
+        await server.add_protobuf_handler("square", square, test_pb2.TestRequest)
+        await server.add_protobuf_handler("fail", fail, test_pb2.TestRequest)
+        await server.add_protobuf_handler("slow", slow, test_pb2.TestRequest)
+        out = await client.call_protobuf_handler(server.peer_id, "square", test_pb2.TestRequest(number=12), test_pb2.TestResponse)
+        assert out.number == 144
+        results = await asyncio.gather(*[client.call_protobuf_handler(server.peer_id, "square", test_pb2.TestRequest(number=i),
+                                                                     test_pb2.TestResponse) for i in range(50)])
+        assert [r.number for r in results] == [i * i for i in range(50)]
+        with pytest.raises(P2PHandlerError, match="boom"):
+            await client.call_protobuf_handler(server.peer_id, "fail", test_pb2.TestRequest(number=1), test_pb2.TestResponse)
+        with pytest.raises(P2PHandlerError):
+            await client.call_protobuf_handler(server.peer_id, "missing", test_pb2.TestRequest(number=1), test_pb2.TestResponse)
+        task = asyncio.create_task(client.call_protobuf_handler(server.peer_id, "slow", test_pb2.TestRequest(number=1),
+                                                                test_pb2.TestResponse))
+        await asyncio.sleep(0.3)
+        task.cancel()
+        await asyncio.wait_for(cancelled.wait(), 5)  # the cancel reaches the remote handler
+        # a large unary payload (1 MiB) survives the trip
+        big = test_pb2.TestRequest(number=7)
+        await server.remove_protobuf_handler("square")
+        with pytest.raises(P2PHandlerError):
+            await client.call_protobuf_handler(server.peer_id, "square", big, test_pb2.TestResponse)
+        await client.shutdown()
+        await server.shutdown()
+
+    run(main())
+
+
+class ExampleServicer(ServicerBase):
+    async def rpc_square(self, request: test_pb2.TestRequest, _context: P2PContext) -> test_pb2.TestResponse:
+        return test_pb2.TestResponse(number=request.number ** 2)
+
+    async def rpc_sum(self, stream: AsyncIterator[test_pb2.TestRequest], _context: P2PContext) -> test_pb2.TestResponse:
+        total = 0
+        async for item in stream:
+            total += item.number
+        return test_pb2.TestResponse(number=total)
+
+    async def rpc_count(self, request: test_pb2.TestRequest, _context: P2PContext) -> AsyncIterator[test_pb2.TestResponse]:
+        for i in range(request.number):
+            yield test_pb2.TestResponse(number=i)
+
+    async def rpc_running_sum(self, stream: AsyncIterator[test_pb2.TestRequest], _context: P2PContext
+                              ) -> AsyncIterator[test_pb2.TestResponse]:
+        total = 0
+        async for item in stream:
+            total += item.number
+            yield test_pb2.TestResponse(number=total)
+
+    async def rpc_fail_midway(self, request: test_pb2.TestRequest, _context: P2PContext) -> AsyncIterator[test_pb2.TestResponse]:
+        yield test_pb2.TestResponse(number=1)
+        raise RuntimeError("midway failure")
+
+
+def test_servicer_four_combinations():
+    async def main():
+        server, client = await _pair()
+        servicer = ExampleServicer()
+        await servicer.add_p2p_handlers(server, namespace="ns")
+        stub = ExampleServicer.get_stub(client, server.peer_id, namespace="ns")
+        assert (await stub.rpc_square(test_pb2.TestRequest(number=9), timeout=10)).number == 81
+
+        async def numbers(n):
+            for i in range(n):
+                yield test_pb2.TestRequest(number=i)
+
+        assert (await stub.rpc_sum(numbers(10))).number == 45
+        got = [r.number async for r in await stub.rpc_count(test_pb2.TestRequest(number=5))]
+        assert got == list(range(5))
+        got = [r.number async for r in await stub.rpc_running_sum(numbers(5))]
+        assert got == [0, 1, 3, 6, 10]
+        with pytest.raises(P2PHandlerError, match="midway failure"):
+            async for _ in await stub.rpc_fail_midway(test_pb2.TestRequest(number=1)):
+                pass
+        # wrong namespace is not served
+        other = ExampleServicer.get_stub(client, server.peer_id, namespace="other")
+        with pytest.raises(P2PHandlerError):
+            await other.rpc_square(test_pb2.TestRequest(number=2), timeout=10)
+        await servicer.remove_p2p_handlers(server, namespace="ns")
+        with pytest.raises(P2PHandlerError):
+            await stub.rpc_square(test_pb2.TestRequest(number=2), timeout=10)
+        await client.shutdown()
+        await server.shutdown()
+
+    run(main())
+
+
+def test_large_stream_and_binary_handlers():
+    async def main():
+        server, client = await _pair()
+
+        async def echo(info, reader, writer):
+            data = await P2P.receive_raw_data(reader)
+            await P2P.send_raw_data(data[::-1], writer)
+
+        await server.add_binary_stream_handler("echo", echo)
+        payload = bytes(range(256)) * (20 * 1024)  # 5 MiB, more than one socket buffer
+        _, reader, writer = await client.call_binary_stream_handler(server.peer_id, "echo")
+        await P2P.send_raw_data(payload, writer)
+        assert await P2P.receive_raw_data(reader) == payload[::-1]
+        writer.close()
+        with pytest.raises(P2PHandlerError):
+            await client.call_binary_stream_handler(server.peer_id, "nope")
+        await client.shutdown()
+        await server.shutdown()
+
+    run(main())
+
+
+def test_replicas_balanced_and_third_party_discovery():
+    async def main():
+        server = await P2P.create()
+        replica = await P2P.replicate(server.daemon_listen_maddr)
+        assert replica.peer_id == server.peer_id
+        hits = {"a": 0, "b": 0}
+
+        def make(tag):
+            async def handler(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+                hits[tag] += 1
+                return test_pb2.TestResponse(number=request.number)
+            return handler
+
+        await server.add_protobuf_handler("bal", make("a"), test_pb2.TestRequest, balanced=True)
+        await replica.add_protobuf_handler("bal", make("b"), test_pb2.TestRequest, balanced=True)
+        with pytest.raises(P2PDaemonError):
+            await replica.add_protobuf_handler("bal2", make("a"), test_pb2.TestRequest)
+            await server.add_protobuf_handler("bal2", make("b"), test_pb2.TestRequest)  # not balanced: second one refused
+        client = await P2P.create(initial_peers=await server.get_visible_maddrs())
+        for i in range(10):
+            await client.call_protobuf_handler(server.peer_id, "bal", test_pb2.TestRequest(number=i), test_pb2.TestResponse)
+        assert hits["a"] == 5 and hits["b"] == 5
+        # a third peer that only knows the server can reach `client` through address gossip / who-has
+        third = await P2P.create(initial_peers=await server.get_visible_maddrs())
+
+        async def hello(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+            return test_pb2.TestResponse(number=request.number + 1)
+
+        await client.add_protobuf_handler("hello", hello, test_pb2.TestRequest)
+        out = await third.call_protobuf_handler(client.peer_id, "hello", test_pb2.TestRequest(number=1), test_pb2.TestResponse)
+        assert out.number == 2
+        # calling oneself works too
+        out = await client.call_protobuf_handler(client.peer_id, "hello", test_pb2.TestRequest(number=5), test_pb2.TestResponse)
+        assert out.number == 6
+        for p in (third, client, replica, server):
+            await p.shutdown()
+
+    run(main())
+
+
+def test_peer_id_derivation_is_stable():
+    from cryptography.hazmat.primitives.asymmetric import rsa
+
+    key = rsa.generate_private_key(public_exponent=65537, key_size=2048)
+    a, b = PeerID.from_private_key(key), PeerID.from_private_key(key)
+    assert a == b and a.to_base58().startswith("Qm") and PeerID.from_base58(a.to_base58()) == a
