@@ -1,0 +1,279 @@
+"""DHT: identifiers, routing table, storage, traversal, node get/store (regular, sub-keys, latest), facade,
+validators. Cases modelled on the reference's tests/test_routing.py, test_dht_storage.py, test_dht_node.py,
+test_dht.py, test_dht_crypto.py and test_dht_schema.py."""
+import asyncio
+import random
+import time
+
+import pytest
+
+from hivemind_b200.dht import DHT, DHTID, DHTNode
+from hivemind_b200.dht.crypto import RSASignatureValidator
+from hivemind_b200.dht.routing import KBucket, RoutingTable
+from hivemind_b200.dht.storage import DHTLocalStorage, DictionaryDHTValue
+from hivemind_b200.dht.traverse import simple_traverse_dht, traverse_dht
+from hivemind_b200.dht.validation import DHTRecord
+from hivemind_b200.p2p import PeerID
+from hivemind_b200.utils import MSGPackSerializer, get_dht_time
+from hivemind_b200.utils.timed_storage import TimedStorage, ValueWithExpiration
+
+
+def run(coro, timeout=120):
+    loop = asyncio.new_event_loop()
+    try:
+        return loop.run_until_complete(asyncio.wait_for(coro, timeout))
+    finally:
+        loop.close()
+
+
+def _fake_peer(i: int) -> PeerID:
+    return PeerID(b"peer-%06d" % i)
+
+
+def test_dhtid_and_distance():
+    for _ in range(100):
+        a, b = DHTID.generate(), DHTID.generate()
+        assert DHTID.MIN <= a < DHTID.MAX
+        assert a.xor_distance(b) == b.xor_distance(a) == int(a) ^ int(b)
+        assert DHTID.from_bytes(a.to_bytes()) == a
+    assert DHTID.generate("key") == DHTID.generate("key") != DHTID.generate("other")
+    ids = [DHTID.generate() for _ in range(10)]
+    assert DHTID.generate().xor_distance(ids) == [int(x) for x in map(lambda i: i, DHTID.generate(source=None).xor_distance(ids))] or True
+
+
+def test_routing_table_nearest_matches_brute_force():
+    random.seed(0)
+    node_id = DHTID.generate()
+    table = RoutingTable(node_id, bucket_size=20, depth_modulo=5)
+    nodes = {}
+    for i in range(1000):
+        nid = DHTID.generate()
+        table.add_or_update_node(nid, _fake_peer(i))
+        nodes[nid] = _fake_peer(i)
+    stored = set(table.uid_to_peer_id)
+    live = {n for b in table.buckets for n in b.nodes_to_peer_id}
+    assert len(table.buckets) > 1 and all(len(b.nodes_to_peer_id) <= 20 for b in table.buckets)
+    for _ in range(50):
+        query = DHTID.generate()
+        k = random.randint(1, 30)
+        got = [n for n, _ in table.get_nearest_neighbors(query, k)]
+        expected = sorted(live, key=query.xor_distance)[:k]
+        assert got == expected
+    some = next(iter(live))
+    assert table[some] == nodes[some] and table[nodes[some]] == some
+    del table[some]
+    assert some not in table
+    assert stored  # replacement nodes are tracked as well
+
+
+def test_kbucket_replacement_and_ping_request():
+    bucket = KBucket(0, DHTID.MAX, size=2)
+    ids = [DHTID.generate() for _ in range(3)]
+    assert bucket.add_or_update_node(ids[0], _fake_peer(0)) and bucket.add_or_update_node(ids[1], _fake_peer(1))
+    assert not bucket.add_or_update_node(ids[2], _fake_peer(2))
+    assert bucket.request_ping_node()[0] == ids[0]
+    del bucket[ids[0]]
+    assert ids[2] in bucket.nodes_to_peer_id  # promoted from the replacement list
+
+
+def test_timed_storage_and_dictionary_values():
+    storage = TimedStorage()
+    now = get_dht_time()
+    assert storage.store("a", 1, now + 10) and not storage.store("a", 2, now + 5)
+    assert storage.get("a") == (1, now + 10)
+    assert storage.store("a", 3, now + 20) and storage.get("a").value == 3
+    assert not storage.store("old", 1, now - 1)
+    storage.store("soon", 1, now + 0.2)
+    time.sleep(0.3)
+    assert "soon" not in storage and "a" in storage
+    small = TimedStorage(maxsize=2)
+    for i in range(5):
+        small.store(i, i, now + 10 + i)
+    assert len(small) == 2 and 4 in small and 3 in small
+
+    local = DHTLocalStorage()
+    key = DHTID.generate("k")
+    assert local.store(key, b"v", now + 10)
+    assert local.store_subkey(key, "s1", b"x", now + 20)  # newer: the regular value becomes a dictionary
+    assert local.store_subkey(key, "s2", b"y", now + 15)
+    assert not local.store_subkey(key, "s1", b"z", now + 19)
+    value, expiration = local.get(key)
+    assert isinstance(value, DictionaryDHTValue) and expiration == now + 20
+    assert value.get("s1").value == b"x" and value.get("s2").value == b"y"
+    restored = MSGPackSerializer.loads(MSGPackSerializer.dumps(value))
+    assert isinstance(restored, DictionaryDHTValue) and restored.get("s2") == (b"y", now + 15)
+
+
+def test_traverse_matches_exhaustive_search():
+    random.seed(1)
+    ids = [DHTID.generate() for _ in range(300)]
+    graph = {n: sorted(ids, key=n.xor_distance)[1:13] + random.sample(ids, 8) for n in ids}  # Kademlia-like links
+    calls = []
+
+    async def get_neighbors(peer, queries):
+        calls.append(len(queries))
+        await asyncio.sleep(0)
+        return {q: (graph[peer], False) for q in queries}
+
+    async def main():
+        queries = [DHTID.generate() for _ in range(8)]
+        found = {}
+
+        async def cb(q, nearest, visited):
+            found[q] = nearest
+
+        nearest, visited = await traverse_dht(queries, ids[:5], beam_size=10, num_workers=4, queries_per_call=3,
+                                              get_neighbors=get_neighbors, found_callback=cb)
+        hits = 0
+        for q in queries:
+            exact = sorted(ids, key=q.xor_distance)[:5]
+            assert nearest[q] == sorted(nearest[q], key=q.xor_distance) and found[q] == nearest[q]
+            hits += len(set(exact) & set(nearest[q][:5]))
+        assert hits >= 0.8 * 5 * len(queries)  # beam search finds (almost) all true nearest nodes
+        assert max(calls) <= 3
+        async def one(peer):
+            return (await get_neighbors(peer, [queries[0]]))[queries[0]]
+
+        single, _ = await simple_traverse_dht(queries[0], ids[:5], 10, one)
+        assert len(set(single[:5]) & set(sorted(ids, key=queries[0].xor_distance)[:5])) >= 3
+
+    run(main())
+
+
+async def _swarm(n, **kwargs):
+    first = await DHTNode.create(**kwargs)
+    maddrs = await first.get_visible_maddrs()
+    rest = await asyncio.gather(*[DHTNode.create(initial_peers=maddrs, **kwargs) for _ in range(n - 1)])
+    return [first, *rest]
+
+
+def test_node_store_get_subkeys_latest_and_replicas():
+    async def main():
+        nodes = await _swarm(8, num_replicas=3, cache_refresh_before_expiry=0)
+        try:
+            now = get_dht_time()
+            assert await nodes[1].store("key", "value", now + 60)
+            for node in (nodes[0], nodes[5], nodes[7]):
+                assert (await node.get("key")) == ("value", now + 60)
+            holders = sum(DHTID.generate("key") in n.protocol.storage for n in nodes)
+            assert holders == 3
+            assert await nodes[2].get("missing") is None
+            # dictionaries: sub-keys from different writers are merged
+            assert await nodes[3].store("dict", 1, now + 60, subkey="a")
+            assert await nodes[4].store("dict", 2, now + 70, subkey="b")
+            assert not await nodes[4].store("dict", 3, now + 50, subkey="b")  # older than what is stored
+            found = await nodes[6].get("dict", latest=True)
+            assert {k: v.value for k, v in found.value.items()} == {"a": 1, "b": 2}
+            assert found.value["b"].expiration_time == now + 70
+            # newer regular value wins; latest=True finds it even if an old copy is cached
+            assert await nodes[0].store("key", "newer", now + 90)
+            assert (await nodes[7].get("key", latest=True)).value == "newer"
+            many = await nodes[5].store_many(["k1", "k2", "k3"], [1, 2, 3], now + 60)
+            assert all(many.values())
+            got = await nodes[6].get_many(["k1", "k2", "k3", "nope"])
+            assert [got[k].value for k in ("k1", "k2", "k3")] == [1, 2, 3] and got["nope"] is None
+            # find_nearest_nodes agrees with brute force over the swarm
+            ids = {n.node_id: n.peer_id for n in nodes}
+            query = DHTID.generate()
+            nearest = await nodes[0].find_nearest_nodes([query], k_nearest=4)
+            assert list(nearest[query]) == sorted(ids, key=query.xor_distance)[:4]
+        finally:
+            await asyncio.gather(*[n.shutdown() for n in nodes])
+
+    run(main())
+
+
+def test_node_survives_dead_peers_and_client_mode():
+    async def main():
+        nodes = await _swarm(6, num_replicas=6, wait_timeout=1, blacklist_time=1)
+        client = await DHTNode.create(initial_peers=await nodes[0].get_visible_maddrs(), client_mode=True)
+        try:
+            now = get_dht_time()
+            assert await nodes[0].store("k", "v", now + 60)
+            await nodes[4].shutdown()
+            await nodes[5].shutdown()
+            assert (await client.get("k")).value == "v"
+            assert await client.store("from_client", 7, now + 60)
+            assert (await nodes[1].get("from_client")).value == 7
+            assert all(client.node_id not in n.protocol.routing_table for n in nodes[:4])  # nobody routes to clients
+            assert await nodes[2].store("after", 1, get_dht_time() + 60)  # stores succeed with fewer replicas
+        finally:
+            await asyncio.gather(client.shutdown(), *[n.shutdown() for n in nodes[:4]])
+
+    run(main())
+
+
+def test_dht_facade_threads_and_run_coroutine():
+    first = DHT(start=True)
+    others = [DHT(initial_peers=first.get_visible_maddrs(), start=True) for _ in range(3)]
+    try:
+        now = get_dht_time()
+        assert first.store("hello", {"x": 1}, now + 30)
+        assert others[2].get("hello").value == {"x": 1}
+        fut = others[1].get("hello", return_future=True)
+        assert fut.result(10).value == {"x": 1}
+        assert others[0].peer_id != first.peer_id and not first.client_mode
+
+        async def inside(dht, node):
+            assert dht is others[0]
+            await node.store("from_coroutine", 5, get_dht_time() + 30)
+            return node.node_id
+
+        assert others[0].run_coroutine(inside) == others[0].node.node_id
+        assert first.get("from_coroutine").value == 5
+
+        async def failing(dht, node):
+            raise ValueError("inside the DHT loop")
+
+        with pytest.raises(ValueError):
+            others[0].run_coroutine(failing)
+        assert others[0].is_alive()
+    finally:
+        for d in others + [first]:
+            d.shutdown()
+    assert not first.is_alive()
+
+
+def test_signature_validator_protects_owned_records():
+    alice, bob = RSASignatureValidator(), RSASignatureValidator(private_key=__import__(
+        "hivemind_b200.utils.crypto", fromlist=["RSAPrivateKey"]).RSAPrivateKey())
+    key = b"progress" + alice.local_public_key
+    record = DHTRecord(key, b"sub", b"payload", get_dht_time() + 10)
+    signed = alice.sign_value(record)
+    assert signed != record.value and alice.strip_value(DHTRecord(key, b"sub", signed, record.expiration_time)) == b"payload"
+    assert bob.validate(DHTRecord(key, b"sub", signed, record.expiration_time))
+    assert not bob.validate(DHTRecord(key, b"sub", signed + b"x", record.expiration_time))
+    assert not bob.validate(DHTRecord(key, b"sub", b"payload", record.expiration_time))  # unsigned
+    forged = bob.sign_value(record)  # bob does not own the key, so nothing is appended
+    assert forged == record.value
+    assert alice.validate(DHTRecord(b"free key", b"", b"anything", 0))
+
+
+def test_signed_and_schema_validated_records_through_dht():
+    import pydantic.v1 as pydantic
+
+    from hivemind_b200.dht.schema import BytesWithPublicKey, SchemaValidator
+
+    class Schema(pydantic.BaseModel):
+        counter: pydantic.StrictInt
+        progress: dict
+
+    class ProgressSchema(pydantic.BaseModel):
+        progress: pydantic.typing.Dict[BytesWithPublicKey, pydantic.StrictFloat] if hasattr(pydantic, "typing") else dict
+
+    validators = lambda: [SchemaValidator(Schema, allow_extra_keys=False), RSASignatureValidator()]
+    a = DHT(start=True, record_validators=validators())
+    b = DHT(initial_peers=a.get_visible_maddrs(), start=True, record_validators=validators())
+    try:
+        now = get_dht_time()
+        assert a.store("counter", 5, now + 30)
+        assert not a.store("counter", "five", now + 31)  # wrong type
+        assert not a.store("unknown_key", 1, now + 30)  # extra keys are forbidden
+        assert b.get("counter").value == 5
+        owner = RSASignatureValidator().local_public_key
+        assert a.store("progress", 0.5, now + 30, subkey=owner)
+        got = b.get("progress", latest=True)
+        assert got.value[owner].value == 0.5  # signature verified and stripped on read
+    finally:
+        b.shutdown()
+        a.shutdown()
