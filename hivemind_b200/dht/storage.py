@@ -1,62 +1,71 @@
-"""Local key-value storage of a DHT node: regular values and dictionaries of sub-keys.
+"""What a DHT node keeps locally: plain values and dictionaries of sub-keys, all with expirations.
 
-A key holds either one binary value or a ``DictionaryDHTValue`` (sub-key -> value, each with its own expiration),
-msgpack ext 0x50 on the wire. A newer expiration wins per (key, sub-key) (reference: hivemind/dht/storage.py:11-69).
+Record model (behavioural contract of hivemind/dht/storage.py:11-69): one key maps either to a single binary value
+or to a ``DictionaryDHTValue`` whose entries expire independently; for the same (key, sub-key) the later expiration
+wins; a dictionary replaces a plain value only if it expires later. Dictionaries travel as msgpack ext 0x50.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional, Union
 
 from hivemind_b200.dht.routing import BinaryDHTValue, DHTID, Subkey
 from hivemind_b200.utils.serializer import MSGPackSerializer
-from hivemind_b200.utils.timed_storage import DHTExpiration, KeyType, TimedStorage, ValueType
+from hivemind_b200.utils.timed_storage import DHTExpiration, TimedStorage
 
 
 @MSGPackSerializer.ext_serializable(0x50)
 class DictionaryDHTValue(TimedStorage[Subkey, BinaryDHTValue]):
-    """A dictionary stored under one DHT key; tracks the latest expiration among its entries."""
+    """Sub-key -> (binary value, expiration). ``latest_expiration_time`` is the expiration of the whole record."""
 
-    latest_expiration_time = float("-inf")
+    def __init__(self, maxsize: Optional[int] = None):
+        super().__init__(maxsize)
+        self.latest_expiration_time = -math.inf
 
-    def store(self, key: KeyType, value: ValueType, expiration_time: DHTExpiration) -> bool:
-        self.latest_expiration_time = max(self.latest_expiration_time, expiration_time)
+    def store(self, key: Subkey, value: BinaryDHTValue, expiration_time: DHTExpiration) -> bool:
+        if expiration_time > self.latest_expiration_time:
+            self.latest_expiration_time = expiration_time
         return super().store(key, value, expiration_time)
 
     def packb(self) -> bytes:
-        """Serialize with expiry frozen so that the packed form is what a reader would have seen now."""
-        packed_items = [[key, value, expiration_time] for key, (value, expiration_time) in self.items()]
-        return MSGPackSerializer.dumps([self.maxsize, self.latest_expiration_time, packed_items])
+        entries = []
+        for subkey, entry in self.items():
+            entries.append([subkey, entry.value, entry.expiration_time])
+        return MSGPackSerializer.dumps([self.maxsize, self.latest_expiration_time, entries])
 
     @classmethod
     def unpackb(cls, raw: bytes) -> "DictionaryDHTValue":
-        maxsize, latest_expiration_time, items = MSGPackSerializer.loads(raw)
-        with DictionaryDHTValue(maxsize).freeze() as new_dict:
-            for key, value, expiration_time in items:
-                new_dict.store(key, value, expiration_time)
-            new_dict.latest_expiration_time = latest_expiration_time
-            return new_dict
+        maxsize, latest, entries = MSGPackSerializer.loads(raw)
+        restored = cls(maxsize)
+        with restored.freeze():  # keep entries that expire while we are unpacking: the reader decides what is stale
+            for subkey, value, expiration_time in entries:
+                restored.store(subkey, value, expiration_time)
+        restored.latest_expiration_time = latest
+        return restored
 
 
-class DHTLocalStorage(TimedStorage[DHTID, Union[BinaryDHTValue, DictionaryDHTValue]]):
+StoredValue = Union[BinaryDHTValue, DictionaryDHTValue]
+
+
+class DHTLocalStorage(TimedStorage[DHTID, StoredValue]):
     def store(self, key: DHTID, value: BinaryDHTValue, expiration_time: DHTExpiration,
               subkey: Optional[Subkey] = None) -> bool:
-        """Store a regular value, or (with ``subkey``) one entry of the dictionary under ``key``."""
-        if subkey is not None:
-            return self.store_subkey(key, subkey, value, expiration_time)
-        return super().store(key, value, expiration_time)
+        """Store a plain value, or one dictionary entry when ``subkey`` is given. Returns whether it was accepted."""
+        if subkey is None:
+            return super().store(key, value, expiration_time)
+        return self.store_subkey(key, subkey, value, expiration_time)
 
     def store_subkey(self, key: DHTID, subkey: Subkey, value: BinaryDHTValue, expiration_time: DHTExpiration) -> bool:
-        """
-        - no value or a regular value under ``key``: it is replaced by a dictionary if the new expiration is later;
-        - a dictionary under ``key``: the entry is added / refreshed if it is newer than the same sub-key's entry.
-        """
-        previous_value, previous_expiration_time = self.get(key) or (b"", -float("inf"))
-        if isinstance(previous_value, BinaryDHTValue) and expiration_time > previous_expiration_time:
-            new_storage = DictionaryDHTValue()
-            new_storage.store(subkey, value, expiration_time)
-            return super().store(key, new_storage, new_storage.latest_expiration_time)
-        if isinstance(previous_value, DictionaryDHTValue):
-            if expiration_time > previous_value.latest_expiration_time:
-                super().store(key, previous_value, expiration_time)  # bump the dictionary's own expiration
-            return previous_value.store(subkey, value, expiration_time)
-        return False
+        current = self.get(key)
+        if current is not None and isinstance(current.value, DictionaryDHTValue):
+            dictionary = current.value
+            if expiration_time > dictionary.latest_expiration_time:
+                # the record as a whole now lives longer: re-register it under the later expiration
+                super().store(key, dictionary, expiration_time)
+            return dictionary.store(subkey, value, expiration_time)
+        # nothing, or a plain value: a dictionary takes over only if it outlives what is there
+        if current is not None and expiration_time <= current.expiration_time:
+            return False
+        dictionary = DictionaryDHTValue()
+        dictionary.store(subkey, value, expiration_time)
+        return super().store(key, dictionary, dictionary.latest_expiration_time)
