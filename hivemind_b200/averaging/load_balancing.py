@@ -37,12 +37,16 @@ def optimize_parts_lp(vector_size: int, bandwidths: np.ndarray, min_size: int = 
     bandwidths = np.asarray(bandwidths, dtype=np.float64)
     permutation = np.argsort(-bandwidths)
     bandwidths = bandwidths[permutation]
+    bandwidths = bandwidths / bandwidths[0]  # only ratios matter; keeps the program well scaled
     is_nonzero = bandwidths != 0
     group_size = len(bandwidths)
     num_variables = group_size + 1  # [w_1, ..., w_N, xi]
 
     c = np.zeros(num_variables, dtype=np.float64)
     c[-1] = 1.0  # minimise xi
+    # the optimum is often degenerate (e.g. two peers: traffic does not depend on the split); among optimal
+    # solutions prefer loading faster peers, via a vanishing cost that grows with the bandwidth rank
+    c[:group_size] = 1e-6 * np.arange(group_size) / group_size
 
     # the shares sum to one
     a_eq, b_eq = np.ones((1, num_variables)), np.ones(1)

@@ -354,9 +354,11 @@ class P2P:
             if writer.can_write_eof():
                 writer.write_eof()
 
+        # requests start flowing right away, even if the caller reads the responses later
+        writing_task = asyncio.create_task(_write_to_stream())
+
         async def _read_from_stream() -> AsyncIterator[Message]:
             with closing(writer):
-                writing_task = asyncio.create_task(_write_to_stream())
                 try:
                     while True:
                         try:

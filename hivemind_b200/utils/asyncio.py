@@ -66,7 +66,8 @@ class LoopThread:
                 self.loop.run_until_complete(self.loop.shutdown_asyncgens())
             except Exception:
                 pass
-            self.loop.close()
+            # the loop object is deliberately not closed: late call_soon_threadsafe calls from other threads
+            # (future callbacks, destructors) must find a stopped loop, not a freed one
 
     @property
     def is_alive(self) -> bool:

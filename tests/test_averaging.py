@@ -1,0 +1,155 @@
+"""DecentralizedAverager over the RPC path on CPU: weighted averages, modes, codecs, state download, triggers.
+Cases modelled on the reference's tests/test_averaging.py and tests/test_allreduce.py."""
+import random
+import time
+
+import pytest
+import torch
+
+from hivemind_b200.averaging import AveragingStage, DecentralizedAverager
+from hivemind_b200.averaging.load_balancing import load_balance_peers
+from hivemind_b200.averaging.partition import compute_part_layout
+from hivemind_b200.compression import Float16Compression, Uniform8BitQuantization
+from hivemind_b200.dht import DHT
+
+
+def launch_dht_instances(n, **kwargs):
+    first = DHT(start=True, **kwargs)
+    maddrs = first.get_visible_maddrs()
+    return [first] + [DHT(initial_peers=maddrs, start=True, **kwargs) for _ in range(n - 1)]
+
+
+def _shutdown(*items):
+    for item in items:
+        item.shutdown()
+
+
+def test_load_balancing_properties():
+    assert load_balance_peers(100, (None, None)) == (50, 50)
+    assert load_balance_peers(100, (None, None, None, None, None)) == (20, 20, 20, 20, 20)
+    assert load_balance_peers(100, (0, 0, 0, None, None)) == (0, 0, 0, 50, 50)
+    shares = load_balance_peers(1000, (100, 100, 1, 1))
+    assert sum(shares) == 1000 and shares[2] + shares[3] < shares[0] + shares[1]
+    assert load_balance_peers(100, (1e3, 1.0), min_size=10)[1] == 0
+    for _ in range(20):
+        n = random.randint(2, 10)
+        bw = [random.choice([None, 0.0, random.random() * 100 + 1]) for _ in range(n)]
+        if all(b == 0.0 for b in bw):
+            bw[0] = 1.0
+        vec = random.randint(1, 10 ** 6)
+        shares = load_balance_peers(vec, bw)
+        assert sum(shares) == vec and all(s >= 0 for s in shares)
+        assert all(s == 0 for s, b in zip(shares, bw) if b == 0.0)
+
+
+def test_part_layout_respects_fractions_and_tensor_boundaries():
+    numels = [1000, 0, 37, 5000]
+    specs = compute_part_layout(numels, [4] * 4, [1.0] * 4, [0.25, 0.0, 0.75], part_size_bytes=1024)
+    assert sum(s.length for s in specs) == sum(numels)
+    per_peer = [sum(s.length for s in specs if s.owner == p) for p in range(3)]
+    assert per_peer[1] == 0 and abs(per_peer[0] - 0.25 * sum(numels)) <= 1
+    for s in specs:
+        assert 0 < s.length <= 256 and s.start + s.length <= numels[s.tensor_index]
+    owners = [s.owner for s in specs]
+    assert owners == sorted(owners)
+
+
+@pytest.mark.parametrize("n_clients,n_aux", [(0, 0), (1, 0), (1, 1)])
+def test_weighted_allreduce_with_modes(n_clients, n_aux):
+    n_peers = 4
+    dhts = launch_dht_instances(n_peers)
+    modes = ["client"] * n_clients + ["aux"] * n_aux + ["node"] * (n_peers - n_clients - n_aux)
+    random.shuffle(modes)
+    torch.manual_seed(0)
+    tensors = [[torch.randn(123), torch.randn(3, 50), torch.zeros(0)] for _ in range(n_peers)]
+    weights = [random.uniform(0.5, 2.0) for _ in range(n_peers)]
+    averagers = [DecentralizedAverager([t.clone() for t in tensors[i]], dhts[i], start=True, prefix="mygroup",
+                                       target_group_size=n_peers, min_matchmaking_time=2.0, request_timeout=1.0,
+                                       client_mode=modes[i] == "client", auxiliary=modes[i] == "aux",
+                                       part_size_bytes=256)
+                 for i in range(n_peers)]
+    try:
+        futures = [a.step(wait=False, weight=w, gather=dict(idx=i), timeout=30)
+                   for i, (a, w) in enumerate(zip(averagers, weights))]
+        gathered = [f.result(60) for f in futures]
+        senders = [i for i in range(n_peers) if modes[i] != "aux"]
+        total_w = sum(weights[i] for i in senders)
+        for k in range(3):
+            ref = sum(tensors[i][k] * weights[i] for i in senders) / total_w
+            for i in senders:
+                with averagers[i].get_tensors() as ts:
+                    assert torch.allclose(ts[k], ref, atol=1e-5), (i, k)
+        for i in range(n_peers):
+            assert len(gathered[i]) == n_peers
+            assert gathered[i][averagers[i].peer_id] == dict(idx=i)
+    finally:
+        _shutdown(*averagers, *dhts)
+
+
+def test_codec_error_bounds_between_two_peers():
+    dhts = launch_dht_instances(2)
+    torch.manual_seed(1)
+    x0, x1 = torch.randn(4096), torch.randn(4096)
+    results = {}
+    try:
+        for name, codec in (("fp16", Float16Compression()), ("uniform8", Uniform8BitQuantization())):
+            avs = [DecentralizedAverager([x.clone()], dht, start=True, prefix=f"codec{name}", target_group_size=2,
+                                         min_matchmaking_time=2.0, request_timeout=1.0, compression=codec)
+                   for x, dht in ((x0, dhts[0]), (x1, dhts[1]))]
+            futures = [a.step(wait=False, timeout=30) for a in avs]
+            [f.result(60) for f in futures]
+            with avs[0].get_tensors() as ts:
+                results[name] = (ts[0] - (x0 + x1) / 2).pow(2).mean().item()
+            _shutdown(*avs)
+        assert 0 < results["fp16"] <= 1e-5
+        assert 1e-5 < results["uniform8"] <= 1e-2
+    finally:
+        _shutdown(*dhts)
+
+
+def test_too_few_peers_fails_and_trigger_stages():
+    dhts = launch_dht_instances(2)
+    avs = [DecentralizedAverager([torch.ones(8) * i], dhts[i], start=True, prefix="trig", target_group_size=2,
+                                 min_matchmaking_time=1.0, request_timeout=0.5) for i in range(2)]
+    try:
+        with pytest.raises(Exception):
+            avs[0].step(timeout=2.0, allow_retries=False)  # nobody else is looking
+        controls = [a.step(wait=False, require_trigger=True, timeout=30) for a in avs]
+        deadline = time.time() + 20
+        while time.time() < deadline and not all(c.stage == AveragingStage.AWAITING_TRIGGER for c in controls):
+            time.sleep(0.05)
+        assert all(c.stage == AveragingStage.AWAITING_TRIGGER for c in controls)
+        controls[0].weight = 3.0  # weights stay mutable until all-reduce begins
+        for c in controls:
+            c.allow_allreduce()
+        [c.result(30) for c in controls]
+        with avs[1].get_tensors() as ts:
+            assert torch.allclose(ts[0], torch.full((8,), 0.25))  # (0*3 + 1*1) / 4
+        assert all(c.stage == AveragingStage.FINISHED for c in controls)
+        cancelled = avs[0].step(wait=False, timeout=30)
+        time.sleep(0.2)
+        cancelled.cancel()
+        assert cancelled.cancelled()
+    finally:
+        _shutdown(*avs, *dhts)
+
+
+def test_state_download_prefers_higher_priority():
+    dhts = launch_dht_instances(3)
+    avs = [DecentralizedAverager([torch.full((5,), float(i))], dhts[i], start=True, prefix="state", target_group_size=2,
+                                 declare_state_period=1.0) for i in range(3)]
+    try:
+        avs[0].state_sharing_priority, avs[1].state_sharing_priority = 5, 10
+        avs[2].allow_state_sharing = False
+        time.sleep(1.0)
+        metadata, tensors = avs[2].load_state_from_peers(timeout=10)
+        assert "group_key" in metadata and torch.allclose(tensors[0], torch.full((5,), 1.0))
+        avs[0].state_sharing_priority = 20
+        time.sleep(1.0)
+        _, tensors = avs[2].load_state_from_peers(timeout=10)
+        assert torch.allclose(tensors[0], torch.full((5,), 0.0))
+        avs[0].allow_state_sharing = avs[1].allow_state_sharing = False
+        time.sleep(1.5)
+        assert avs[2].load_state_from_peers(timeout=5) is None
+    finally:
+        _shutdown(*avs, *dhts)
