@@ -1,0 +1,197 @@
+"""Optimizer stack on CPU: gradient averager weighting, state averager, progress tracker, full Optimizer runs.
+Cases modelled on the reference's tests/test_optimizer.py."""
+import threading
+import time
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import hivemind_b200 as hivemind
+from hivemind_b200.optim import GradientAverager, Optimizer, ProgressTracker, TrainingStateAverager
+from hivemind_b200.optim.state_averager import dump_optimizer_state, load_optimizer_state
+
+
+def launch_dht_instances(n):
+    first = hivemind.DHT(start=True)
+    return [first] + [hivemind.DHT(initial_peers=first.get_visible_maddrs(), start=True) for _ in range(n - 1)]
+
+
+def test_grad_averager_accumulation_and_weighting():
+    dhts = launch_dht_instances(2)
+    p1, p2 = nn.Parameter(torch.zeros(3)), nn.Parameter(torch.zeros(3))
+    a1 = GradientAverager([p1], dht=dhts[0], prefix="grads", target_group_size=2, min_matchmaking_time=1.0,
+                          request_timeout=0.5, reuse_grad_buffers=False, start=True)
+    a2 = GradientAverager([p2], dht=dhts[1], prefix="grads", target_group_size=2, min_matchmaking_time=1.0,
+                          request_timeout=0.5, reuse_grad_buffers=True, start=True)
+    try:
+        c1 = a1.schedule_step(timeout=30)
+        c2 = a2.schedule_step(timeout=30)
+        for _ in range(10):
+            p1.grad = None
+            F.mse_loss(p1, torch.ones(3)).backward()
+            a1.accumulate_grads_(batch_size=2)  # 20 samples in total
+            F.mse_loss(p2, -torch.ones(3)).backward()  # accumulates in param.grad
+            a2.accumulate_grads_(batch_size=3)  # 30 samples
+        g1 = -2 / 3 * torch.ones(3)  # d/dp mean((p-1)^2) at p=0
+        g2 = 2 / 3 * torch.ones(3)
+        assert a1.local_samples_accumulated == 20 and a1.local_times_accumulated == 10
+        assert torch.allclose(next(a2._grad_accumulators()), g2 * 10)
+        t1 = threading.Thread(target=lambda: a1.step(control=c1, wait=True, timeout=30))
+        t1.start()
+        a2.step(control=c2, wait=True, timeout=30)
+        t1.join()
+        expected = (g1 * 20 + g2 * 30) / 50
+        for averager in (a1, a2):
+            with averager.use_averaged_gradients() as grads:
+                assert torch.allclose(grads[0], expected, atol=1e-6)
+            assert averager.local_samples_accumulated == 0
+        with a1.use_averaged_gradients():
+            assert torch.allclose(p1.grad, expected, atol=1e-6)
+        assert not torch.allclose(p1.grad, expected)  # original grad buffers are restored
+    finally:
+        for x in (a1, a2, *dhts):
+            x.shutdown()
+
+
+def test_optimizer_state_dump_roundtrip():
+    model = nn.Linear(4, 3)
+    opt = torch.optim.Adam(model.parameters(), lr=0.1)
+    model(torch.randn(2, 4)).sum().backward()
+    opt.step()
+    meta, tensors = dump_optimizer_state(opt)
+    assert all(m["type"] in ("tensor", "value") for m in meta) and len(tensors) >= 4
+    other = torch.optim.Adam(nn.Linear(4, 3).parameters(), lr=0.5)
+    for p in other.param_groups[0]["params"]:
+        p.grad = torch.zeros_like(p)
+    other.step()
+    load_optimizer_state(other, meta, tensors)
+    assert other.param_groups[0]["lr"] == 0.1
+    for (k1, s1), (k2, s2) in zip(opt.state_dict()["state"].items(), other.state_dict()["state"].items()):
+        assert torch.allclose(s1["exp_avg"], s2["exp_avg"])
+
+
+@pytest.mark.parametrize("offload,reuse", [(False, False), (True, True), (True, False)])
+def test_state_averager_step_and_averaging(offload, reuse):
+    dhts = launch_dht_instances(2)
+    torch.manual_seed(0)
+    models = [nn.Linear(3, 2), nn.Linear(3, 2)]
+    extras = [torch.full((2,), 1.0), torch.full((2,), 3.0)]
+    avgs = [TrainingStateAverager(dht=dht, optimizer=lambda p: torch.optim.SGD(p, lr=0.1), params=list(m.parameters()),
+                                  scheduler=lambda opt: torch.optim.lr_scheduler.LambdaLR(opt, lambda e: 1 / (1 + e)),
+                                  offload_optimizer=offload, reuse_tensors=reuse, extra_tensors=[e],
+                                  prefix="state", target_group_size=2, min_matchmaking_time=1.0, request_timeout=0.5,
+                                  start=True)
+            for dht, m, e in zip(dhts, models, extras)]
+    try:
+        before = [[p.detach().clone() for p in m.parameters()] for m in models]
+        for m in models:
+            m(torch.ones(1, 3)).sum().backward()
+        threads = [threading.Thread(target=lambda a=a: a.step(increment_epoch=True, optimizer_step=True, zero_grad=True,
+                                                              averaging_round=True, averaging_opts=dict(timeout=30)))
+                   for a in avgs]
+        [t.start() for t in threads]
+        [t.join(60) for t in threads]
+        assert all(a.local_epoch == 1 for a in avgs)
+        # every peer made one SGD step, then parameters were averaged
+        stepped = [[b - 0.1 * torch.ones_like(b) for b in bs] for bs in before]
+        for k, (pa, pb) in enumerate(zip(models[0].parameters(), models[1].parameters())):
+            expected = (stepped[0][k] + stepped[1][k]) / 2
+            assert torch.allclose(pa, expected, atol=1e-6) and torch.allclose(pb, expected, atol=1e-6)
+        assert all(torch.allclose(e, torch.full((2,), 2.0)) for e in extras)
+        assert abs(avgs[0].optimizer.param_groups[0]["lr"] - 0.05) < 1e-9  # scheduler follows the epoch
+        assert all(p.grad is None or float(p.grad.abs().sum()) == 0 for p in models[0].parameters())
+    finally:
+        for x in (*avgs, *dhts):
+            x.shutdown()
+
+
+def test_progress_tracker_counts_swarm_samples():
+    dhts = launch_dht_instances(3)
+    trackers = [ProgressTracker(dht, "run", target_batch_size=100, min_refresh_period=0.1, default_refresh_period=0.2,
+                                max_refresh_period=0.5, start=True) for dht in dhts]
+    try:
+        for i, tracker in enumerate(trackers):
+            tracker.report_local_progress(0, 10 * (i + 1))
+        deadline = time.time() + 15
+        while time.time() < deadline and not all(t.global_progress.samples_accumulated >= 60 and
+                                                 t.global_progress.num_peers == 3 for t in trackers):
+            time.sleep(0.1)
+        assert all(t.global_progress.num_peers == 3 for t in trackers)
+        assert all(t.global_progress.samples_accumulated == 60 for t in trackers)
+        trackers[1].report_local_progress(0, 70)  # 10 + 70 + 30 >= 100
+        deadline = time.time() + 15
+        while time.time() < deadline and not all(t.ready_to_update_epoch for t in trackers):
+            time.sleep(0.1)
+        assert all(t.ready_to_update_epoch for t in trackers)
+        with trackers[0].pause_updates():
+            assert trackers[0].update_epoch() == 1
+        deadline = time.time() + 15
+        while time.time() < deadline and trackers[2].global_epoch != 1:
+            time.sleep(0.1)
+        assert trackers[2].global_epoch == 1 and trackers[2].ready_to_update_epoch
+    finally:
+        for x in (*trackers, *dhts):
+            x.shutdown()
+
+
+def _run_peer(dht, seed, results, epochs, **opt_kwargs):
+    torch.manual_seed(seed)
+    model = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+    opt = Optimizer(dht=dht, run_id="test_run", target_batch_size=64, batch_size_per_step=8,
+                    params=model.parameters(), optimizer=lambda p: torch.optim.Adam(p, lr=3e-2),
+                    matchmaking_time=1.0, averaging_timeout=15.0, verbose=False,
+                    averager_opts=dict(request_timeout=0.5, target_group_size=2),
+                    tracker_opts=dict(min_refresh_period=0.1, default_refresh_period=0.3, max_refresh_period=0.5),
+                    **opt_kwargs)
+    gen = torch.Generator().manual_seed(1234)
+    w_true = torch.randn(16, 4, generator=gen)
+    losses = []
+    deadline = time.time() + 120
+    while opt.local_epoch < epochs and time.time() < deadline:
+        x = torch.randn(8, 16)
+        y = (x @ w_true).argmax(-1)
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        opt.step()
+        if not (opt.use_gradient_averaging and opt.grad_averager.reuse_grad_buffers):
+            opt.zero_grad()
+        losses.append(loss.item())
+        time.sleep(0.01)
+    first_loss, last_loss = sum(losses[:8]) / 8, sum(losses[-8:]) / 8
+    results[seed] = (opt.local_epoch, first_loss, last_loss, [p.detach().clone() for p in model.parameters()],
+                     opt.state_dict()["state"].get("local_epoch"))
+    opt.shutdown()
+
+
+@pytest.mark.parametrize("mode", ["sync", "delayed", "local_updates"])
+def test_optimizer_two_peers_converge_and_stay_in_sync(mode):
+    kwargs = dict(sync=dict(), delayed=dict(delay_optimizer_step=True, delay_grad_averaging=True, offload_optimizer=True),
+                  local_updates=dict(use_local_updates=True, delay_state_averaging=False))[mode]
+    dhts = launch_dht_instances(2)
+    results = {}
+    try:
+        threads = [threading.Thread(target=_run_peer, args=(dht, i, results, 8), kwargs=kwargs) for i, dht in enumerate(dhts)]
+        [t.start() for t in threads]
+        [t.join(180) for t in threads]
+        assert set(results) == {0, 1}
+        for epoch, first, last, params, saved_epoch in results.values():
+            assert epoch >= 8 and saved_epoch == epoch
+            assert last < first
+        if mode == "sync":
+            for pa, pb in zip(results[0][3], results[1][3]):
+                assert torch.allclose(pa, pb, atol=1e-3)
+    finally:
+        for dht in dhts:
+            dht.shutdown()
+
+
+def test_single_peer_proceeds_with_local_gradients():
+    dht = hivemind.DHT(start=True)
+    results = {}
+    try:
+        _run_peer(dht, 0, results, 6)
+        assert results[0][0] >= 6 and results[0][2] < results[0][1]
+    finally:
+        dht.shutdown()
