@@ -34,11 +34,11 @@ class PartSpec:
 
 
 def compute_part_layout(numels: Sequence[int], element_sizes: Sequence[int], compression_ratios: Sequence[float],
-                        peer_fractions: Sequence[float], part_size_bytes: int) -> List[PartSpec]:
+                        peer_fractions: Sequence[float], part_size_bytes: int, align: int = 1) -> List[PartSpec]:
     """Cut every tensor into parts and give each part to a peer.
 
     A part goes to the current peer until that peer's cumulative share (``pivot``) of all elements is used up;
-    a part that straddles the boundary is split there, so that peer shares are exact.
+    a part that straddles the boundary is split there, so that peer shares are exact (up to ``align`` elements).
     """
     total = int(sum(numels))
     fractions = np.asarray(peer_fractions, dtype=np.float64)
@@ -48,13 +48,22 @@ def compute_part_layout(numels: Sequence[int], element_sizes: Sequence[int], com
     peer, consumed = 0, 0
     for t, n in enumerate(numels):
         part_elems = max(1, int(part_size_bytes / (element_sizes[t] * compression_ratios[t])))
+        if align > 1:  # device path: keep every part boundary inside a tensor on an aligned element
+            part_elems = max(align, part_elems // align * align)
         offset = 0
         while offset < n:
             length = min(part_elems, n - offset)
             while peer < len(pivots) - 1 and consumed >= pivots[peer]:
                 peer += 1
             if consumed + length > pivots[peer] and peer < len(pivots) - 1:
-                length = int(pivots[peer] - consumed)  # finish this peer's share exactly
+                cut = int(pivots[peer] - consumed)  # finish this peer's share exactly
+                if align > 1:
+                    cut = cut // align * align
+                if cut > 0:
+                    length = cut
+                else:  # the aligned cut would be empty: the whole part goes to the next peer
+                    peer += 1
+                    continue
             specs.append(PartSpec(t, offset, length, peer))
             offset += length
             consumed += length

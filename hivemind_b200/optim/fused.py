@@ -1,0 +1,148 @@
+"""Fused optimizers: ``torch.optim.Optimizer`` subclasses whose step is one or two multi-tensor kernels.
+
+``FusedLAMB`` follows the LAMB variant that the reference's ALBERT example trains with
+(``torch_optimizer.Lamb(lr, betas, eps, weight_decay, clamp_value, debias)``,
+examples/albert/run_trainer.py:240-248): Adam moments, update ``m / (sqrt(v) + eps) + wd * p``, per-tensor trust
+ratio ``clamp(|p|, 0, clamp_value) / |update|`` (1 when either norm is zero), optional bias correction.
+``FusedAdam`` matches ``torch.optim.Adam`` / ``AdamW``; ``FusedSGD`` matches ``torch.optim.SGD``.
+State dict keys equal those of the PyTorch classes (``step``, ``exp_avg``, ``exp_avg_sq``, ``momentum_buffer``), so
+checkpoints and peer-to-peer state downloads stay interchangeable. CPU tensors run the same math in PyTorch.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional, Tuple
+
+import torch
+
+from hivemind_b200.ops import multi_tensor as mt
+
+
+def _bump_versions(params: Iterable[torch.Tensor]) -> None:
+    """Kernels write through raw pointers; tell autograd (and bf16 weight caches) that the tensors changed."""
+    for p in params:
+        torch.autograd.graph.increment_version(p)
+
+
+class _FusedBase(torch.optim.Optimizer):
+    def _collect(self, group) -> Tuple[List[torch.Tensor], List[torch.Tensor]]:
+        params, grads = [], []
+        for p in group["params"]:
+            if p.grad is None:
+                continue
+            if p.grad.is_sparse:
+                raise RuntimeError(f"{type(self).__name__} does not support sparse gradients")
+            params.append(p)
+            grads.append(p.grad if p.grad.is_contiguous() else p.grad.contiguous())
+        return params, grads
+
+    def _step_count(self, group, params) -> int:
+        """All parameters of a group advance together; the counter is kept per parameter for state-dict parity."""
+        step = 0
+        for p in params:
+            state = self.state[p]
+            value = state.get("step", 0)
+            value = int(value.item()) if isinstance(value, torch.Tensor) else int(value)
+            state["step"] = value + 1
+            step = value + 1
+        return step
+
+
+class FusedLAMB(_FusedBase):
+    def __init__(self, params, lr: float = 1e-3, betas: Tuple[float, float] = (0.9, 0.999), eps: float = 1e-6,
+                 weight_decay: float = 0.0, clamp_value: float = 10.0, debias: bool = False):
+        if lr <= 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0 or clamp_value < 0:
+            raise ValueError("invalid LAMB hyper-parameters")
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, clamp_value=clamp_value,
+                                      debias=debias))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            params, grads = self._collect(group)
+            if not params:
+                continue
+            for p in params:
+                state = self.state[p]
+                if "exp_avg" not in state:
+                    state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                if "_update" not in self.__dict__.setdefault("_scratch", {}).setdefault(id(p), {}):
+                    self._scratch[id(p)]["_update"] = torch.empty_like(p, dtype=torch.float32)
+            step = self._step_count(group, params)
+            mt.lamb_step_(params, grads, [self.state[p]["exp_avg"] for p in params],
+                          [self.state[p]["exp_avg_sq"] for p in params],
+                          [self._scratch[id(p)]["_update"] for p in params], step=step, lr=group["lr"],
+                          betas=group["betas"], eps=group["eps"], weight_decay=group["weight_decay"],
+                          clamp_value=group["clamp_value"], debias=group["debias"])
+            _bump_versions(params)
+        return loss
+
+
+class FusedAdam(_FusedBase):
+    def __init__(self, params, lr: float = 1e-3, betas: Tuple[float, float] = (0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, decoupled_weight_decay: bool = False):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                      decoupled_weight_decay=decoupled_weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            params, grads = self._collect(group)
+            if not params:
+                continue
+            for p in params:
+                state = self.state[p]
+                if "exp_avg" not in state:
+                    state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            step = self._step_count(group, params)
+            mt.adam_step_(params, grads, [self.state[p]["exp_avg"] for p in params],
+                          [self.state[p]["exp_avg_sq"] for p in params], step=step, lr=group["lr"], betas=group["betas"],
+                          eps=group["eps"], weight_decay=group["weight_decay"],
+                          decoupled=group["decoupled_weight_decay"])
+            _bump_versions(params)
+        return loss
+
+
+class FusedAdamW(FusedAdam):
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2):
+        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, decoupled_weight_decay=True)
+
+
+class FusedSGD(_FusedBase):
+    def __init__(self, params, lr: float = 1e-3, momentum: float = 0.0, dampening: float = 0.0,
+                 weight_decay: float = 0.0, nesterov: bool = False):
+        if nesterov and (momentum <= 0 or dampening != 0):
+            raise ValueError("Nesterov momentum requires a momentum and zero dampening")
+        super().__init__(params, dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay,
+                                      nesterov=nesterov))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            params, grads = self._collect(group)
+            if not params:
+                continue
+            bufs, first = None, False
+            if group["momentum"] != 0:
+                first = any("momentum_buffer" not in self.state[p] for p in params)
+                for p in params:
+                    if "momentum_buffer" not in self.state[p]:
+                        self.state[p]["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32)
+                bufs = [self.state[p]["momentum_buffer"] for p in params]
+            mt.sgd_step_(params, grads, bufs, lr=group["lr"], momentum=group["momentum"], dampening=group["dampening"],
+                         weight_decay=group["weight_decay"], nesterov=group["nesterov"], first_step=first)
+            _bump_versions(params)
+        return loss

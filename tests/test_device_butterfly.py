@@ -1,0 +1,114 @@
+"""Device butterfly against a CPU oracle built from the reference math: several ranks emulated on one GPU."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from hivemind_b200.averaging.allreduce import AveragingMode
+from hivemind_b200.compression import (BlockwiseQuantization, CompressionInfo, Float16Compression, NoCompression,
+                                       Quantile8BitQuantization, ScaledFloat16Compression, Uniform8BitQuantization,
+                                       deserialize_torch_tensor)
+
+CODECS = [NoCompression(), Float16Compression(), ScaledFloat16Compression(), Uniform8BitQuantization(),
+          Quantile8BitQuantization(), BlockwiseQuantization()]
+TOL = {"NoCompression": 1e-6, "Float16Compression": 2e-3, "ScaledFloat16Compression": 2e-3,
+       "Uniform8BitQuantization": 0.08, "Quantile8BitQuantization": 0.08, "BlockwiseQuantization": 0.08}
+
+
+def _make_endpoints(n, shapes, codec, part_size_bytes, seed=0):
+    from hivemind_b200.parallel.device_butterfly import DeviceEndpoint
+
+    torch.manual_seed(seed)
+    dev = torch.device("cuda", 0)
+    originals = [[torch.randn(s) * (1 + i) + 0.1 * r for i, s in enumerate(shapes)] for r in range(n)]
+    endpoints = []
+    for r in range(n):
+        tensors = [t.to(dev) for t in originals[r]]
+        infos = [CompressionInfo.from_tensor(t, key=i) for i, t in enumerate(tensors)]
+        endpoints.append(DeviceEndpoint(tensors, codec, infos, part_size_bytes))
+    return endpoints, originals
+
+
+@pytest.mark.parametrize("codec", CODECS, ids=lambda c: type(c).__name__)
+@pytest.mark.parametrize("n", [2, 3, 4])
+def test_weighted_average_all_codecs(codec, n):
+    from hivemind_b200.parallel.device_butterfly import run_group_emulated
+
+    shapes = [(1000, 37), (5,), (70000,), (123, 4)]
+    endpoints, originals = _make_endpoints(n, shapes, codec, part_size_bytes=2 ** 15)
+    weights = [0.5 + 0.5 * r for r in range(n)]
+    fractions = [1.0 / n] * n
+    statuses = run_group_emulated(endpoints, weights=weights, peer_fractions=fractions)
+    torch.cuda.synchronize()
+    assert all(s.failed_elements == 0 and not s.banned_senders for s in statuses)
+    tol = TOL[type(codec).__name__]
+    for k in range(len(shapes)):
+        ref = sum(w * originals[r][k] for r, w in enumerate(weights)) / sum(weights)
+        scale = max(ref.abs().max().item(), originals[0][k].std().item() if originals[0][k].numel() > 1 else 1.0)
+        for r in range(n):
+            got = endpoints[r].tensor_views[k].cpu()
+            err = (got - ref).abs().max().item()
+            assert err <= tol * max(scale, 1.0), (type(codec).__name__, k, r, err)
+    if isinstance(codec, NoCompression):
+        for k in range(len(shapes)):
+            assert torch.allclose(endpoints[0].tensor_views[k], endpoints[n - 1].tensor_views[k], atol=1e-5)
+
+
+def test_modes_fractions_and_alpha():
+    from hivemind_b200.parallel.device_butterfly import run_group_emulated
+
+    shapes = [(50000,), (333,)]
+    endpoints, originals = _make_endpoints(4, shapes, NoCompression(), part_size_bytes=2 ** 14)
+    modes = [AveragingMode.NODE, AveragingMode.AUX, AveragingMode.NODE, AveragingMode.NODE]
+    weights = [1.0, 0.0, 2.0, 3.0]
+    fractions = [0.5, 0.25, 0.25, 0.0]  # the last peer reduces nothing, the auxiliary one only reduces
+    run_group_emulated(endpoints, weights=weights, peer_fractions=fractions, modes=modes, alpha=0.5)
+    torch.cuda.synchronize()
+    for k in range(len(shapes)):
+        ref = (originals[0][k] * 1 + originals[2][k] * 2 + originals[3][k] * 3) / 6
+        for r in (0, 2, 3):
+            expected = originals[r][k] + 0.5 * (ref - originals[r][k])
+            assert torch.allclose(endpoints[r].tensor_views[k].cpu(), expected, atol=1e-5)
+        assert torch.allclose(endpoints[1].tensor_views[k].cpu(), originals[1][k])  # auxiliaries keep their data
+
+
+def test_missing_and_stalled_senders_are_excluded_without_hanging():
+    """Host-side fault injection: one rank never publishes, another publishes only half of its parts.
+    The waits run out after ``sender_timeout`` and the survivors average among themselves."""
+    from hivemind_b200.parallel.device_butterfly import run_group_emulated
+
+    shapes = [(200000,)]
+    endpoints, originals = _make_endpoints(4, shapes, Float16Compression(), part_size_bytes=2 ** 14)
+    statuses = run_group_emulated(endpoints, weights=[1.0] * 4, peer_fractions=[0.25] * 4, sender_timeout=0.5,
+                                  reducer_timeout=1.0, skip_send_of=[3])
+    torch.cuda.synchronize()
+    ref = (originals[0][0] + originals[1][0] + originals[2][0]) / 3
+    for r in range(3):
+        assert 3 in statuses[r].banned_senders
+        got = endpoints[r].tensor_views[0].cpu()
+        own = slice(r * 50000, (r + 1) * 50000)
+        # everything except the span reduced by the absent peer is the survivors' average
+        assert torch.allclose(got[:150000], ref[:150000], atol=5e-3)
+    # the absent peer still reduced its own span with what the others sent, so nobody loses that span either
+    assert torch.allclose(endpoints[0].tensor_views[0].cpu()[150000:], ((originals[0][0] + originals[1][0] +
+                          originals[2][0] + originals[3][0]) / 4)[150000:], atol=5e-3)
+
+
+def test_device_codecs_match_cpu_codecs():
+    torch.manual_seed(3)
+    x = torch.randn(128, 128, 64)
+    xc = x.cuda()
+    for codec, bound in [(Float16Compression(), 5e-8), (ScaledFloat16Compression(), 5e-8),
+                         (Uniform8BitQuantization(), 8e-4), (Quantile8BitQuantization(), 8e-4),
+                         (BlockwiseQuantization(), 8e-4)]:
+        msg = codec.compress(xc, CompressionInfo.from_tensor(xc))
+        restored = deserialize_torch_tensor(msg)
+        assert restored.shape == x.shape
+        assert (restored - x).pow(2).mean().item() < bound, type(codec).__name__
+        cpu_msg = codec.compress(x, CompressionInfo.from_tensor(x))
+        assert len(cpu_msg.buffer) == len(msg.buffer)
+    u_gpu = deserialize_torch_tensor(Uniform8BitQuantization().compress(xc, CompressionInfo.from_tensor(xc)))
+    u_cpu = deserialize_torch_tensor(Uniform8BitQuantization().compress(x, CompressionInfo.from_tensor(x)))
+    assert (u_gpu - u_cpu).abs().max().item() < 0.05  # same bins up to rounding at bin edges
