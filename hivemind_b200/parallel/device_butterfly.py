@@ -166,7 +166,7 @@ class DeviceEndpoint:
         min_part = min([max(ALIGN, int(part_size_bytes / (4 * r)) // ALIGN * ALIGN) for r in self.ratios] or [ALIGN])
         self.max_parts = sum((n + min_part - 1) // min_part for n in self.numels) + MAX_PEERS + len(tensors)
         self.cap_outbox = self.total * 4 + self.max_parts * 1088
-        self.cap_delta = int(self.cap_outbox * 1.25) + (1 << 16)
+        self.cap_delta = int(self.cap_outbox * 2.5) + (1 << 16)  # room for uneven spans; larger groups fall back to RPC
         self.layout = {}
         cursor = 0
         for name, nbytes in (("data", self.total * 4), ("avg", self.total * 4), ("outbox", self.cap_outbox),

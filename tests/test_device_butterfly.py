@@ -44,13 +44,20 @@ def test_weighted_average_all_codecs(codec, n):
     torch.cuda.synchronize()
     assert all(s.failed_elements == 0 and not s.banned_senders for s in statuses)
     tol = TOL[type(codec).__name__]
+    lossy8 = type(codec).__name__ in ("Uniform8BitQuantization", "Quantile8BitQuantization", "BlockwiseQuantization")
     for k in range(len(shapes)):
         ref = sum(w * originals[r][k] for r, w in enumerate(weights)) / sum(weights)
-        scale = max(ref.abs().max().item(), originals[0][k].std().item() if originals[0][k].numel() > 1 else 1.0)
+        spread = max(originals[0][k].std().item() if originals[0][k].numel() > 1 else 1.0, 1e-3)
         for r in range(n):
             got = endpoints[r].tensor_views[k].cpu()
-            err = (got - ref).abs().max().item()
-            assert err <= tol * max(scale, 1.0), (type(codec).__name__, k, r, err)
+            if lossy8:
+                # 8-bit codebooks represent outliers by their bin mean, so judge by RMS error, like the
+                # reference's MSE thresholds (tests/test_compression.py:33-46), not by the worst element
+                rms = (got - ref).pow(2).mean().sqrt().item()
+                assert rms <= 0.05 * spread, (type(codec).__name__, k, r, rms, spread)
+            else:
+                err = (got - ref).abs().max().item()
+                assert err <= tol * max(ref.abs().max().item(), spread, 1.0), (type(codec).__name__, k, r, err)
     if isinstance(codec, NoCompression):
         for k in range(len(shapes)):
             assert torch.allclose(endpoints[0].tensor_views[k], endpoints[n - 1].tensor_views[k], atol=1e-5)
