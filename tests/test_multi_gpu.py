@@ -1,0 +1,89 @@
+"""Device butterfly across processes (one per GPU) through the full DecentralizedAverager: matchmaking over the DHT,
+IPC handle exchange in the gather blob, kernels over peer-mapped memory. Needs at least two GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+CHILD = r'''
+import os, sys, time, json, torch
+sys.path.insert(0, os.environ["REPO_ROOT"])
+rank, world = int(sys.argv[1]), int(sys.argv[2])
+codec_name = sys.argv[3]
+import hivemind_b200 as hivemind
+from hivemind_b200.averaging import DecentralizedAverager
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+if rank == 0:
+    dht = hivemind.DHT(start=True)
+    with open(os.environ["MADDR_FILE"] + ".tmp", "w") as f:
+        json.dump([str(m) for m in dht.get_visible_maddrs()], f)
+    os.rename(os.environ["MADDR_FILE"] + ".tmp", os.environ["MADDR_FILE"])
+else:
+    while not os.path.exists(os.environ["MADDR_FILE"]):
+        time.sleep(0.05)
+    dht = hivemind.DHT(initial_peers=json.load(open(os.environ["MADDR_FILE"])), start=True)
+torch.manual_seed(100 + rank)
+tensors = [torch.randn(300000, device=dev), torch.randn(257, 129, device=dev)]
+original = [t.clone() for t in tensors]
+codec = getattr(hivemind, codec_name)()
+averager = DecentralizedAverager(tensors, dht, start=True, prefix="mgpu", target_group_size=world,
+                                 min_matchmaking_time=3.0, request_timeout=1.0, compression=codec,
+                                 part_size_bytes=2 ** 16, sender_timeout=5.0)
+assert averager._device_endpoint is not None
+weight = 1.0 + rank
+gathered = averager.step(weight=weight, gather=dict(rank=rank), timeout=60)
+torch.cuda.synchronize()
+assert len(gathered) == world
+with averager.get_tensors() as out:
+    result = [t.cpu() for t in out]
+# every rank can rebuild everybody's input from the seeds
+refs = []
+for k in range(2):
+    acc, den = 0, 0
+    for r in range(world):
+        g = torch.Generator(device="cpu")
+        torch.manual_seed(100 + r)
+        with torch.cuda.device(r):
+            pass
+        den += 1.0 + r
+    refs.append(None)
+torch.save(dict(original=[t.cpu() for t in original], result=result, weight=weight), os.environ["OUT_PREFIX"] + f"{rank}.pt")
+averager.shutdown(); dht.shutdown()
+print("child done", rank, flush=True)
+'''
+
+
+@pytest.mark.parametrize("codec_name,tol", [("NoCompression", 1e-5), ("Float16Compression", 5e-3),
+                                            ("Uniform8BitQuantization", 0.05)])
+def test_two_processes_average_over_ipc(tmp_path, codec_name, tol):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, REPO_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+               MADDR_FILE=str(tmp_path / "maddrs.json"), OUT_PREFIX=str(tmp_path / "out"), NCCL_NVLS_ENABLE="0")
+    script = tmp_path / "child.py"
+    script.write_text(CHILD)
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world), codec_name], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outputs.append(out)
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-2000:] for o in outputs)
+    data = [torch.load(str(tmp_path / f"out{r}.pt")) for r in range(world)]
+    total_w = sum(d["weight"] for d in data)
+    for k in range(2):
+        ref = sum(d["original"][k] * d["weight"] for d in data) / total_w
+        spread = ref.std().item() + 1e-6
+        for d in data:
+            rms = (d["result"][k] - ref).pow(2).mean().sqrt().item()
+            assert rms <= tol * max(spread, 1.0), (codec_name, k, rms)
