@@ -416,6 +416,9 @@ class DecentralizedAverager(ServicerBase):
         my_index = group_info.peer_ids.index(self.peer_id)
         # every member needs every member's weight up front: exchange them through a tiny unary RPC round
         weights = await self._exchange_weights(group_info, weight)
+        pending = self._running_groups.get(group_info.group_id)
+        if pending is not None and not pending.done():
+            pending.set_result(None)  # no RPC runner in this round: the data moves through peer-mapped memory
         loop = asyncio.get_event_loop()
         async with enter_asynchronously(self.lock_averaged_tensors):
             status = await loop.run_in_executor(None, lambda: endpoint.run_round(
@@ -483,6 +486,9 @@ class DecentralizedAverager(ServicerBase):
             yield averaging_pb2.AveragingData(code=averaging_pb2.BAD_GROUP_ID)
             return
         group = await future
+        if group is None:  # this round runs on the device path; nobody should stream parts to us
+            yield averaging_pb2.AveragingData(code=averaging_pb2.PROTOCOL_VIOLATION)
+            return
         async for message in group.rpc_aggregate_part(achain(as_aiter(request), stream), context):
             yield message
 
