@@ -396,3 +396,64 @@ HM_API int hm_mt_lamb(const void* tensors, const void* chunks, int num_chunks, i
                                                                   (const float*)norms);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free gradient clipping (declared in hm_noalloc.h). Scratch lives in this file-scope device array.
+#include <mutex>
+#include <cstdio>
+#include "hm_noalloc.h"
+
+static __device__ __align__(256) float hm_noalloc_sumsq[HM_NOALLOC_MAX_TENSORS + 1];
+
+__global__ void mt_write_norm_kernel(const float* __restrict__ sumsq, int num_tensors, float* __restrict__ out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) out[0] = sqrtf(sumsq[num_tensors]);
+}
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device. In host code the array's name is only a handle for
+// the runtime, never an address a kernel may use; the real address differs per device and is looked up once.
+int noalloc_scratch_for_current_device(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -21;
+  std::lock_guard<std::mutex> guard(g_noalloc_mutex);
+  if (g_noalloc_scratch[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, hm_noalloc_sumsq);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_scratch[dev] = ptr;
+  }
+  *out = g_noalloc_scratch[dev];
+  return 0;
+}
+}  // namespace
+
+HM_API int hm_mt_clip_grad_norm_noalloc(const void* tensors, const void* chunks, int num_chunks, int num_tensors,
+                                        float max_norm, float* total_norm_out, cudaStream_t stream) {
+  if (num_tensors < 0 || num_chunks < 0) return -22;
+  if (num_tensors > HM_NOALLOC_MAX_TENSORS) {
+    fprintf(stderr, "hm_mt_clip_grad_norm_noalloc: %d tensors exceed the built-in scratch (at most %d per call); "
+                    "split the call or use hm_mt_sumsq + hm_mt_clip with a caller-owned buffer\n",
+            num_tensors, HM_NOALLOC_MAX_TENSORS);
+    return -20;
+  }
+  float* scratch = nullptr;
+  int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // the array still holds the previous call's sums: everything this call accumulates into starts from zero
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * (size_t)(num_tensors + 1), stream);
+  if (e != cudaSuccess) return (int)e;
+  if (num_chunks > 0) {
+    mt_sumsq_kernel<<<num_chunks, HM_MT_THREADS, 0, stream>>>((const long long*)tensors, (const int*)chunks, 0,
+                                                              num_tensors, scratch);
+    mt_clip_kernel<<<num_chunks, HM_MT_THREADS, 0, stream>>>((const long long*)tensors, (const int*)chunks, scratch,
+                                                             num_tensors, max_norm);
+  }
+  if (total_norm_out != nullptr) mt_write_norm_kernel<<<1, 32, 0, stream>>>(scratch, num_tensors, total_norm_out);
+  return (int)cudaGetLastError();
+}
