@@ -293,7 +293,7 @@ class DecentralizedAverager(ServicerBase):
         assert scheduled_time < deadline, "Scheduled start time does not fit within timeout"
 
         user_data_for_gather = self.serializer.dumps(gather)
-        device_info = self._device_endpoint.describe() if self._device_endpoint is not None else None
+        device_info = self._describe_device()
         data_for_gather = self.serializer.dumps([self.bandwidth, self.mode.value, user_data_for_gather, device_info])
         step = StepControl(scheduled_time=scheduled_time, deadline=deadline, allow_retries=allow_retries, weight=weight,
                            data_for_gather=data_for_gather)
@@ -303,6 +303,10 @@ class DecentralizedAverager(ServicerBase):
         assert self._thread is not None, "the averager is not running"
         self._thread.submit(self._step(step=step))
         return step.result() if wait else step
+
+    def _describe_device(self) -> Optional[dict]:
+        """What groupmates need to map this averager's device arena(s); None if it averages through RPC only."""
+        return self._device_endpoint.describe() if self._device_endpoint is not None else None
 
     async def _step(self, *, step: StepControl) -> None:
         try:
@@ -410,19 +414,22 @@ class DecentralizedAverager(ServicerBase):
                 raise ValueError("aux peers should not receive averaged tensors")
 
     async def _run_device_allreduce_(self, group_info: GroupInfo, peer_fractions, modes, device_infos, *, weight: float,
-                                     sender_timeout=None, reducer_timeout=None, **_unused) -> None:
+                                     sender_timeout=None, reducer_timeout=None, endpoint=None, group_id=None,
+                                     weights=None, lock: bool = True, **_unused) -> None:
         """Device data path: launch the butterfly kernels over peer-mapped arenas and wait for the stream."""
-        endpoint = self._device_endpoint
+        endpoint = endpoint if endpoint is not None else self._device_endpoint
+        group_id = group_id if group_id is not None else group_info.group_id
         my_index = group_info.peer_ids.index(self.peer_id)
         # every member needs every member's weight up front: exchange them through a tiny unary RPC round
-        weights = await self._exchange_weights(group_info, weight)
-        pending = self._running_groups.get(group_info.group_id)
+        if weights is None:
+            weights = await self._exchange_weights(group_info, weight)
+        pending = self._running_groups.get(group_id)
         if pending is not None and not pending.done():
             pending.set_result(None)  # no RPC runner in this round: the data moves through peer-mapped memory
         loop = asyncio.get_event_loop()
-        async with enter_asynchronously(self.lock_averaged_tensors):
+        async with (enter_asynchronously(self.lock_averaged_tensors) if lock else contextlib.AsyncExitStack()):
             status = await loop.run_in_executor(None, lambda: endpoint.run_round(
-                group_id=group_info.group_id, my_index=my_index, device_infos=device_infos, modes=modes,
+                group_id=group_id, my_index=my_index, device_infos=device_infos, modes=modes,
                 peer_fractions=peer_fractions, weights=weights, alpha=self._averaging_alpha,
                 sender_timeout=sender_timeout, reducer_timeout=reducer_timeout))
         self._state_updated.set()

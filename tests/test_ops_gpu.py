@@ -250,3 +250,44 @@ def test_linear_autograd():
     assert w.grad.data_ptr() == before
     ref = 1 + x.detach().float().reshape(-1, 256).sum(0).expand(512, 256)
     assert torch.allclose(w.grad, ref, atol=0.5, rtol=3e-2)
+
+
+def test_orthogonalize_matches_gram_schmidt():
+    from hivemind_b200.ops.powersgd import orthogonalize_batch_
+    from hivemind_b200.utils.math import orthogonalize_reference_
+
+    torch.manual_seed(17)
+    mats = [torch.randn(m, 32, device=_dev()) for m in (1024, 4096, 50257, 100)]
+    mats[1][:, 5] = 0  # a dead column stays dead
+    refs = [orthogonalize_reference_(m.double().cpu().clone()) for m in mats]
+    orthogonalize_batch_(mats)
+    for got, ref in zip(mats, refs):
+        assert torch.allclose(got.cpu().double(), ref, atol=2e-4), (got.cpu().double() - ref).abs().max()
+        gram = got.t() @ got
+        live = gram.diag() > 0.5
+        assert torch.allclose(gram[live][:, live], torch.eye(int(live.sum()), device=_dev()), atol=1e-4)
+
+
+@pytest.mark.parametrize("m,n,r", [(1024, 4096, 32), (50257, 1024, 32), (1000, 520, 8), (768, 768, 64)])
+def test_powersgd_products(m, n, r):
+    from hivemind_b200.ops import powersgd as ps
+    from hivemind_b200.ops.gemm import check_kernel_errors
+
+    torch.manual_seed(19)
+    M = torch.randn(m, n, device=_dev())
+    Q = torch.randn(n, r, device=_dev())
+    P = torch.empty(m, r, device=_dev())
+    ps.compute_p_(P, M, Q)
+    check_kernel_errors()
+    ref_p = M.double() @ Q.double()
+    assert (P.double() - ref_p).abs().max().item() <= 2e-3 * ref_p.abs().max().item() + 1e-2
+    Q2 = torch.empty(n, r, device=_dev())
+    ps.compute_q_(Q2, M, P)
+    check_kernel_errors()
+    ref_q = M.double().t() @ P.double()
+    assert (Q2.double() - ref_q).abs().max().item() <= 2e-3 * ref_q.abs().max().item() + 1e-2
+    out = torch.empty(m, n, device=_dev())
+    ps.reconstruct_(out, P, Q)
+    check_kernel_errors()
+    ref_o = P.double() @ Q.double().t()
+    assert (out.double() - ref_o).abs().max().item() <= 2e-3 * ref_o.abs().max().item() + 1e-2

@@ -196,3 +196,37 @@ def test_single_peer_proceeds_with_local_gradients():
         assert results[0][0] >= 6 and results[0][2] < results[0][1]
     finally:
         dht.shutdown()
+
+
+def test_power_sgd_rank1_recovers_rank1_gradients():
+    """With rank-1 gradients, rank-1 PowerSGD reproduces the sample-weighted mean (reference: tests/test_optimizer.py:28-87)."""
+    from hivemind_b200.optim import PowerSGDGradientAverager
+
+    dhts = launch_dht_instances(2)
+    torch.manual_seed(0)
+    u, v = torch.randn(12, 1), torch.randn(1, 9)
+    params = [[nn.Parameter(torch.zeros(12, 9)), nn.Parameter(torch.zeros(7))] for _ in range(2)]
+    avs = [PowerSGDGradientAverager(p, averager_rank=1, dht=dht, prefix="psgd", target_group_size=2,
+                                    min_matchmaking_time=1.0, request_timeout=0.5, min_compression_ratio=0.0, start=True)
+           for p, dht in zip(params, dhts)]
+    try:
+        scales, samples = [1.0, 3.0], [8, 18]
+        for p, scale in zip(params, scales):
+            p[0].grad = scale * (u @ v)
+            p[1].grad = torch.full((7,), scale)
+        controls = [a.schedule_step(timeout=30) for a in avs]
+        for a, n in zip(avs, samples):
+            a.accumulate_grads_(batch_size=n)
+        threads = [threading.Thread(target=lambda a=a, c=c: a.step(control=c, wait=True, timeout=30)) for a, c in zip(avs, controls)]
+        [t.start() for t in threads]
+        [t.join(60) for t in threads]
+        mean_scale = (scales[0] * samples[0] + scales[1] * samples[1]) / sum(samples)
+        for a, scale in zip(avs, scales):
+            # error feedback keeps what the average does not explain: local gradient minus averaged gradient
+            assert torch.allclose(a._ms[0], (scale - mean_scale) * (u @ v), atol=1e-4)
+            with a.use_averaged_gradients() as grads:
+                assert torch.allclose(grads[0], mean_scale * (u @ v), atol=1e-4)
+                assert torch.allclose(grads[1], torch.full((7,), mean_scale), atol=1e-5)
+    finally:
+        for x in (*avs, *dhts):
+            x.shutdown()
