@@ -55,7 +55,7 @@ class DHT:
         self._ready = MPFuture()
         self._peer_id: Optional[PeerID] = None
         self._client_mode: Optional[bool] = None
-        self._p2p_replica: Optional[P2P] = None
+        self._p2p_replicas = {}  # event loop -> P2P client attached to the same daemon
         self._origin_p2p = p2p
         self._thread: Optional[LoopThread] = None
         self._node: Optional[DHTNode] = None
@@ -109,11 +109,13 @@ class DHT:
                 thread.run(self._node.shutdown(), timeout=self.shutdown_timeout)
             except Exception as e:
                 logger.debug(f"DHT did not shut down cleanly: {e!r}")
-        if self._p2p_replica is not None:
-            try:
-                thread.run(self._p2p_replica.shutdown(), timeout=self.shutdown_timeout)
-            except Exception:
-                pass
+        replicas, self._p2p_replicas = self._p2p_replicas, {}
+        for loop, replica in replicas.items():
+            try:  # close each replica on the loop that owns its sockets, if that loop still runs
+                if loop.is_running():
+                    asyncio.run_coroutine_threadsafe(replica.shutdown(), loop).result(self.shutdown_timeout)
+            except Exception as e:
+                logger.debug(f"Could not close a transport replica: {e!r}")
         thread.stop()
 
     def __del__(self):
@@ -215,10 +217,13 @@ class DHT:
 
     async def replicate_p2p(self) -> P2P:
         """A ``P2P`` client attached to the same transport daemon, usable from the calling event loop."""
-        if self._p2p_replica is not None:
-            return self._p2p_replica
-        daemon_listen_maddr = self.run_coroutine(DHT._get_p2p_daemon_listen_maddr)
-        return await P2P.replicate(daemon_listen_maddr)
+        loop = asyncio.get_running_loop()
+        replica = self._p2p_replicas.get(loop)
+        if replica is None:
+            # one replica per calling loop: its sockets belong to that loop
+            daemon_listen_maddr = self.run_coroutine(DHT._get_p2p_daemon_listen_maddr)
+            replica = self._p2p_replicas[loop] = await P2P.replicate(daemon_listen_maddr)
+        return replica
 
     @staticmethod
     async def _get_p2p_daemon_listen_maddr(_dht: "DHT", node: DHTNode) -> Multiaddr:
