@@ -105,7 +105,8 @@ def benchmark_server(num_experts=16, num_handlers=None, num_clients=128, num_bat
     server = Server(dht=server_dht, module_backends=backends, num_connection_handlers=num_handlers, device=device)
     try:
         server.start()
-        server.ready.wait()
+        if not server.ready.wait(timeout=300):
+            raise TimeoutError("the server did not become ready")
         ready.wait(timeout=300)  # every client process has imported, connected and fetched the schema
         stamps["server_ready"] = time.perf_counter()
         can_start.set()

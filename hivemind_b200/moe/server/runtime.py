@@ -49,10 +49,12 @@ class Runtime(threading.Thread):
         for pool in self.pools:
             pool.start()
         if self.device is not None:
+            if self.device.type == "cuda":
+                if self.device.index is None:  # "cuda" means the current device; pools and tensors need an index
+                    self.device = torch.device("cuda", torch.cuda.current_device())
+                torch.cuda.set_device(self.device)
             for backend in self.module_backends.values():
                 backend.module.to(self.device)
-            if self.device.type == "cuda":
-                torch.cuda.set_device(self.device)
         if self.stats_reporter is not None:
             self.stats_reporter.start()
         self.ready.set()

@@ -127,8 +127,11 @@ __global__ void moe_count_kernel(const int* __restrict__ idx, long long n, int n
   rank[i] = (e >= 0 && e < num_experts) ? atomicAdd(&counts[e], 1) : -1;
 }
 
+// `align` > 1 pads every expert's row range to a multiple of `align` rows (128 for the grouped GEMM, whose M tiles
+// must not straddle experts); tile_group[m] then names the expert that owns rows 128*m .. 128*m+127 (-1: none).
 __global__ void __launch_bounds__(1024) moe_scan_kernel(const int* __restrict__ counts, int num_experts,
-                                                        int* __restrict__ offsets) {
+                                                        int* __restrict__ offsets, int align,
+                                                        int* __restrict__ tile_group, int max_tiles) {
   __shared__ int warp_tot[32];
   __shared__ int carry;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(1024) moe_scan_kernel(const int* __restrict__ 
   __syncthreads();
   for (int base = 0; base < num_experts; base += blockDim.x) {
     const int e = base + threadIdx.x;
-    const int c = (e < num_experts) ? counts[e] : 0;
+    const int c = (e < num_experts) ? ((counts[e] + align - 1) / align) * align : 0;
     int incl = c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -163,6 +166,22 @@ __global__ void __launch_bounds__(1024) moe_scan_kernel(const int* __restrict__ 
     __syncthreads();
   }
   if (threadIdx.x == 0) offsets[num_experts] = carry;
+  if (tile_group == nullptr) return;
+  __syncthreads();  // the offsets written above by this block are read back below
+  const int total = carry;
+  for (int m = threadIdx.x; m < max_tiles; m += blockDim.x) {
+    const int row = m << 7;
+    int g = -1;
+    if (row < total) {
+      int lo = 0, hi = num_experts;  // last e with offsets[e] <= row (the non-empty one among equal offsets)
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (offsets[mid] <= row) lo = mid; else hi = mid;
+      }
+      g = lo;
+    }
+    tile_group[m] = g;
+  }
 }
 
 // One block per token: the row is read once and written to each of its (up to k) packed positions.
@@ -375,18 +394,31 @@ HM_API int hm_moe_gate_topk(const float* scores, int T, int ld, int ndim, const 
   return (int)cudaGetLastError();
 }
 
-// counts must be zeroed by this call's memset; rank/pos are int32 [T*k]; src is int32 [T*k]; offsets int32 [E+1].
+// rank/pos are int32 [T*k]; src is int32 [packed_rows] (-1 for rows that hold no token); offsets int32 [E+1].
+// align = 1: experts' rows are dense. align = 128: every expert's range is padded to whole 128-row tiles, the pad
+// rows of `packed` are zero, and tile_group (int32 [max_tiles], max_tiles = packed_rows / 128) is filled.
 HM_API int hm_moe_dispatch(const void* x, long long ldx, int H, int dtype, const int* idx, int T, int k,
-                           int num_experts, int* counts, int* offsets, int* rank, void* packed, int* pos, int* src,
-                           cudaStream_t stream) {
+                           int num_experts, int* counts, int* offsets, int* rank, void* packed, long long packed_rows,
+                           int* pos, int* src, int align, int* tile_group, int max_tiles, cudaStream_t stream) {
   if (k < 1 || k > MOE_MAX_K) return -10;
+  if (align != 1 && align != 128) return -12;
+  if (align == 128 && (tile_group == nullptr || (long long)max_tiles * 128 > packed_rows ||
+                       packed_rows < (long long)T * k + (long long)num_experts * 127))
+    return -12;
   const int esize = (dtype == HM_F32) ? 4 : 2;
   if (dtype == HM_F16 || (H * esize) % 16 != 0 || (ldx * esize) % 16 != 0) return -11;
   cudaError_t err = cudaMemsetAsync(counts, 0, sizeof(int) * num_experts, stream);
   if (err != cudaSuccess) return (int)err;
+  err = cudaMemsetAsync(src, 0xff, sizeof(int) * packed_rows, stream);
+  if (err != cudaSuccess) return (int)err;
+  if (align > 1) {
+    err = cudaMemsetAsync(packed, 0, (size_t)packed_rows * H * esize, stream);
+    if (err != cudaSuccess) return (int)err;
+  }
   const long long n = (long long)T * k;
   if (n > 0) moe_count_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(idx, n, num_experts, counts, rank);
-  moe_scan_kernel<<<1, 1024, 0, stream>>>(counts, num_experts, offsets);
+  moe_scan_kernel<<<1, 1024, 0, stream>>>(counts, num_experts, offsets, align, align > 1 ? tile_group : nullptr,
+                                          max_tiles);
   if (T > 0) {
     if (dtype == HM_BF16)
       moe_permute_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)x, ldx, H, idx, rank, offsets, k,

@@ -52,12 +52,21 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(32 * HM_LN_WARPS)
 ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const float* __restrict__ gamma,
               const float* __restrict__ beta, T* __restrict__ y, T* __restrict__ z, float* __restrict__ mean_out,
-              float* __restrict__ rstd_out, int rows, int H, float eps) {
+              float* __restrict__ rstd_out, int rows, int H, float eps,
+              const int* __restrict__ tile_group = nullptr) {
   const int lane = threadIdx.x & 31;
   const int warp_global = blockIdx.x * HM_LN_WARPS + (threadIdx.x >> 5);
   const int warps_total = gridDim.x * HM_LN_WARPS;
   const float inv_h = 1.f / (float)H;
+  const float* gamma0 = gamma;
+  const float* beta0 = beta;
   for (int row = warp_global; row < rows; row += warps_total) {
+    if (tile_group != nullptr) {  // grouped: every 128-row tile has its own gamma / beta; tiles of group -1 are skipped
+      const int g = __ldg(tile_group + (row >> 7));
+      if (g < 0) continue;
+      gamma = gamma0 + (size_t)g * H;
+      beta = beta0 + (size_t)g * H;
+    }
     const size_t base = (size_t)row * H;
     float v[NV][8];
     float s = 0.f;
@@ -195,6 +204,126 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ zin, const float* 
   }
 }
 
+// Grouped backward: rows come in 128-row tiles and tile_group[tile] names the parameter set (group) of the tile
+// (-1: skip). A CTA walks whole tiles, keeps the column sums of one tile in registers and adds them to that group's
+// dgamma / dbeta (and dxsum = column sums of dx, the bias gradient of the layer that produced the input) when the
+// tile ends.
+template <typename T, int NV>
+__global__ void __launch_bounds__(32 * HM_LN_WARPS)
+ln_bwd_grouped_kernel(const T* __restrict__ dy, const T* __restrict__ zin, const float* __restrict__ gamma0,
+                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+                      float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ dxsum, int rows,
+                      int H, const int* __restrict__ tile_group) {
+  __shared__ float sg[HM_LN_WARPS][32 * 8 + 8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_h = 1.f / (float)H;
+  const int num_tiles = (rows + 127) >> 7;
+  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    const int group = __ldg(tile_group + tile);
+    if (group < 0) continue;  // uniform across the CTA
+    const float* gamma = gamma0 + (size_t)group * H;
+    float ag[NV][8], ab[NV][8], ac[NV][8];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ag[j][k] = ab[j][k] = ac[j][k] = 0.f;
+    const int row_end = min(rows, (tile + 1) << 7);
+    for (int row = (tile << 7) + warp; row < row_end; row += HM_LN_WARPS) {
+      const size_t base = (size_t)row * H;
+      const float mean = mean_in[row], rstd = rstd_in[row];
+      float xh[NV][8], gd[NV][8];
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int col = (j * 32 + lane) * 8;
+        if (col < H) {
+          float d[8], g[8];
+          ld8<T>(dy + base + col, d);
+          ld8<T>(zin + base + col, xh[j]);
+          ld8<float>(gamma + col, g);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            xh[j][k] = (xh[j][k] - mean) * rstd;
+            ag[j][k] = fmaf(d[k], xh[j][k], ag[j][k]);
+            ab[j][k] += d[k];
+            gd[j][k] = d[k] * g[k];
+            s1 += gd[j][k];
+            s2 = fmaf(gd[j][k], xh[j][k], s2);
+          }
+        }
+      }
+      s1 = hm_warp_sum(s1) * inv_h;
+      s2 = hm_warp_sum(s2) * inv_h;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int col = (j * 32 + lane) * 8;
+        if (col < H) {
+          float o[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            o[k] = rstd * (gd[j][k] - s1 - xh[j][k] * s2);
+            ac[j][k] += o[k];
+          }
+          st8<T>(dx + base + col, o);
+        }
+      }
+    }
+#pragma unroll
+    for (int pass = 0; pass < 3; ++pass) {
+      float* dst0 = pass == 0 ? dgamma : (pass == 1 ? dbeta : dxsum);
+      if (dst0 == nullptr) continue;
+      float* dst = dst0 + (size_t)group * H;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int col = (j * 32 + lane) * 8;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sg[warp][lane * 8 + k] = pass == 0 ? ag[j][k] : (pass == 1 ? ab[j][k] : ac[j][k]);
+        __syncthreads();
+        if (warp == 0 && col < H) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < HM_LN_WARPS; ++w) t += sg[w][lane * 8 + k];
+            atomicAdd(dst + col + k, t);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// dx = dy * gelu'(x [+ bias]) with the bias-gradient column sums of each 128-row tile added to dbias[group].
+template <typename T>
+__global__ void __launch_bounds__(256)
+gelu_bwd_grouped_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx,
+                        float* __restrict__ dbias, long long rows, int H, const int* __restrict__ tile_group) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  const int tile = blockIdx.y;
+  const int group = __ldg(tile_group + tile);
+  if (group < 0 || col >= H) return;
+  const long long r0 = (long long)tile << 7, r1 = r0 + 128 < rows ? r0 + 128 : rows;
+  float acc = 0.f;
+  for (long long r = r0; r < r1; ++r) {
+    const size_t idx = (size_t)r * H + col;
+    float xv, dv;
+    if constexpr (sizeof(T) == 2) {
+      xv = __bfloat162float(x[idx]);
+      dv = __bfloat162float(dy[idx]);
+    } else {
+      xv = x[idx];
+      dv = dy[idx];
+    }
+    const float g = dv * hm_gelu_tanh_grad(xv);
+    acc += g;
+    if constexpr (sizeof(T) == 2) dx[idx] = __float2bfloat16(g);
+    else dx[idx] = g;
+  }
+  if (dbias) atomicAdd(dbias + (size_t)group * H + col, acc);
+}
+
 // y = gelu_tanh(x + bias)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -245,13 +374,26 @@ bias_gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 // ------------------------------------------------------------------------------------------------
 template <typename T, int NV>
 static int ln_fwd_launch(const void* x, const void* res, const void* gamma, const void* beta, void* y, void* z,
-                         void* mean, void* rstd, int rows, int H, float eps, int sms, cudaStream_t stream) {
+                         void* mean, void* rstd, int rows, int H, float eps, int sms, cudaStream_t stream,
+                         const int* tile_group = nullptr) {
   int blocks = (rows + HM_LN_WARPS - 1) / HM_LN_WARPS;
   const int cap = sms * 8;
   if (blocks > cap) blocks = cap;
   ln_fwd_kernel<T, NV><<<blocks, 32 * HM_LN_WARPS, 0, stream>>>((const T*)x, (const T*)res, (const float*)gamma,
                                                                (const float*)beta, (T*)y, (T*)z, (float*)mean,
-                                                               (float*)rstd, rows, H, eps);
+                                                               (float*)rstd, rows, H, eps, tile_group);
+  return (int)cudaGetLastError();
+}
+template <typename T, int NV>
+static int ln_bwd_grouped_launch(const void* dy, const void* zin, const void* gamma, const void* mean,
+                                 const void* rstd, void* dx, void* dgamma, void* dbeta, void* dxsum, int rows, int H,
+                                 int sms, cudaStream_t stream, const int* tile_group) {
+  int blocks = (rows + 127) / 128;
+  const int cap = sms * 4;
+  if (blocks > cap) blocks = cap;
+  ln_bwd_grouped_kernel<T, NV><<<blocks, 32 * HM_LN_WARPS, 0, stream>>>(
+      (const T*)dy, (const T*)zin, (const float*)gamma, (const float*)mean, (const float*)rstd, (T*)dx,
+      (float*)dgamma, (float*)dbeta, (float*)dxsum, rows, H, tile_group);
   return (int)cudaGetLastError();
 }
 template <typename T, int NV>
@@ -330,6 +472,57 @@ HM_API int hm_bias_gelu_bwd(const void* dy, const void* x, const void* bias, voi
   else if (dtype == HM_F32)
     bias_gelu_bwd_kernel<float><<<grid, 256, 0, stream>>>((const float*)dy, (const float*)x, (const float*)bias,
                                                          (float*)dx, (float*)dbias, rows, H);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
+// Grouped variants: rows are split into 128-row tiles, tile_group[tile] selects the group's gamma / beta / bias
+// (stacked [groups][H]); tiles of group -1 are not touched. Gradient buffers are fp32, stacked the same way and
+// accumulated into (the caller zeroes them or passes existing gradients).
+HM_API int hm_layernorm_fwd_grouped(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                                    void* z, void* mean, void* rstd, int rows, int H, float eps, int dtype,
+                                    const int* tile_group, int sms, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (tile_group == nullptr) return -3;
+  HM_LN_DISPATCH(ln_fwd_launch, x, residual, gamma, beta, y, z, mean, rstd, rows, H, eps, sms, stream, tile_group);
+}
+
+HM_API int hm_layernorm_bwd_grouped(const void* dy, const void* zin, const void* gamma, const void* mean,
+                                    const void* rstd, void* dx, void* dgamma, void* dbeta, void* dxsum, int rows,
+                                    int H, int dtype, const int* tile_group, int sms, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (tile_group == nullptr) return -3;
+  // three sets of per-column accumulators live in registers: hidden sizes above 1024 would spill
+  const int nv = (H + 255) / 256;
+  if (H % 8 != 0 || nv > 4) return -1;
+#define HM_LN_GROUPED(T)                                                                                           \
+  do {                                                                                                             \
+    if (nv <= 1) return ln_bwd_grouped_launch<T, 1>(dy, zin, gamma, mean, rstd, dx, dgamma, dbeta, dxsum, rows, H, \
+                                                    sms, stream, tile_group);                                      \
+    if (nv <= 2) return ln_bwd_grouped_launch<T, 2>(dy, zin, gamma, mean, rstd, dx, dgamma, dbeta, dxsum, rows, H, \
+                                                    sms, stream, tile_group);                                      \
+    return ln_bwd_grouped_launch<T, 4>(dy, zin, gamma, mean, rstd, dx, dgamma, dbeta, dxsum, rows, H, sms, stream, \
+                                       tile_group);                                                                \
+  } while (0)
+  if (dtype == HM_BF16) HM_LN_GROUPED(__nv_bfloat16);
+  if (dtype == HM_F32) HM_LN_GROUPED(float);
+#undef HM_LN_GROUPED
+  return -2;
+}
+
+HM_API int hm_gelu_bwd_grouped(const void* dy, const void* x, void* dx, void* dbias, long long rows, int H, int dtype,
+                               const int* tile_group, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (tile_group == nullptr) return -3;
+  dim3 grid((H + 255) / 256, (unsigned)((rows + 127) / 128));
+  if (dtype == HM_BF16)
+    gelu_bwd_grouped_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                    (__nv_bfloat16*)dx, (float*)dbias, rows, H,
+                                                                    tile_group);
+  else if (dtype == HM_F32)
+    gelu_bwd_grouped_kernel<float><<<grid, 256, 0, stream>>>((const float*)dy, (const float*)x, (float*)dx,
+                                                            (float*)dbias, rows, H, tile_group);
   else
     return -2;
   return (int)cudaGetLastError();

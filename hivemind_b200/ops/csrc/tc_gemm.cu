@@ -41,6 +41,17 @@ struct GemmParams {
   const float* bias;
   float alpha;
   int* err;
+  // Grouped problems (many experts in one launch). Mode 1: the rows of A and D are split into groups of whole
+  // M tiles; group_table[m_tile] names the group (-1: skip the tile) and selects that group's slice of B
+  // (group * group_b_rows along B's row coordinate) and of the bias. Mode 2: every group owns a range of K
+  // (rows group_table[g] .. group_table[g+1] of both MN-major operands, multiples of BLOCK_K) and a slice of D
+  // (group * group_d_rows along D's rows); tiles enumerate (group, m_tile, n_tile).
+  int group_mode, num_groups, group_b_rows, group_d_rows, group_bias;
+  const int* group_table;
+};
+
+struct TileInfo {
+  int m_tile, n_tile, kb0, kb1, group;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -216,7 +227,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BAR_OFF + L::NUM_BARS * 8 + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles * (p.group_mode == 2 ? p.num_groups : p.num_splits);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -239,11 +250,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto tile_coords = [&](int tile, int& m_tile, int& n_tile, int& split) {
-    split = tile % p.num_splits;
+  // Decodes a tile index; returns false if the tile has no work (an empty group). Every role calls this with the
+  // same arguments and therefore skips the same tiles.
+  auto tile_info = [&](int tile, TileInfo& ti) -> bool {
+    if (p.group_mode == 2) {
+      const int per_group = p.num_m_tiles * p.num_n_tiles;
+      ti.group = tile / per_group;
+      const int t = tile - ti.group * per_group;
+      ti.n_tile = t % p.num_n_tiles;
+      ti.m_tile = t / p.num_n_tiles;
+      ti.kb0 = __ldg(p.group_table + ti.group) / BLOCK_K;
+      ti.kb1 = __ldg(p.group_table + ti.group + 1) / BLOCK_K;
+      return ti.kb1 > ti.kb0;
+    }
+    const int split = tile % p.num_splits;
     const int t = tile / p.num_splits;
-    n_tile = t % p.num_n_tiles;
-    m_tile = t / p.num_n_tiles;
+    ti.n_tile = t % p.num_n_tiles;
+    ti.m_tile = t / p.num_n_tiles;
+    ti.kb0 = split * p.kblocks_per_split;
+    ti.kb1 = min(ti.kb0 + p.kblocks_per_split, p.total_kblocks);
+    ti.group = 0;
+    if (p.group_mode == 1) {
+      ti.group = __ldg(p.group_table + ti.m_tile);
+      return ti.group >= 0;
+    }
+    return true;
   };
 
   bool failed = false;
@@ -254,11 +285,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
-        int m_tile, n_tile, split;
-        tile_coords(tile, m_tile, n_tile, split);
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(kb0 + p.kblocks_per_split, p.total_kblocks);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        TileInfo ti;
+        if (!tile_info(tile, ti)) continue;
+        const int m_tile = ti.m_tile, n_tile = ti.n_tile;
+        const int b_row_off = (p.group_mode == 1) ? ti.group * p.group_b_rows : 0;
+        for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { failed = true; break; }
           const uint32_t a_dst = smem_base + stage * L::STAGE_BYTES;
           const uint32_t b_dst = a_dst + L::A_BYTES;
@@ -274,9 +305,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if constexpr (B_MN) {
 #pragma unroll
             for (int r = 0; r < BLOCK_N / RUN; ++r)
-              tma_load_2d(b_dst + r * (BLOCK_K * ROW_BYTES), &map_b, full_bar(stage), n_tile * BLOCK_N + r * RUN, k0);
+              tma_load_2d(b_dst + r * (BLOCK_K * ROW_BYTES), &map_b, full_bar(stage), n_tile * BLOCK_N + r * RUN, k0 + b_row_off);
           } else {
-            tma_load_2d(b_dst, &map_b, full_bar(stage), k0, n_tile * BLOCK_N);
+            tma_load_2d(b_dst, &map_b, full_bar(stage), k0, n_tile * BLOCK_N + b_row_off);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -288,11 +319,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
-        int m_tile, n_tile, split;
-        tile_coords(tile, m_tile, n_tile, split);
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(kb0 + p.kblocks_per_split, p.total_kblocks);
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+        TileInfo ti;
+        if (!tile_info(tile, ti)) continue;
+        const int kb0 = ti.kb0, kb1 = ti.kb1;
         const int buf = local & 1;
         const uint32_t use = (uint32_t)(local >> 1);
         if (!mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag)) { failed = true; break; }
@@ -317,6 +347,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (failed) break;
         tc_commit(tfull_bar(buf));  // accumulator complete
+        ++local;
       }
     }
   } else {
@@ -330,9 +361,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int boxes_per_store = p.out_f32 ? 1 : 2;  // 128 B rows: 32 fp32 or 64 bf16
     int local = 0;
     int flip = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++local) {
-      int m_tile, n_tile, split;
-      tile_coords(tile, m_tile, n_tile, split);
+    for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+      TileInfo ti;
+      if (!tile_info(tile, ti)) continue;
+      const int m_tile = ti.m_tile, n_tile = ti.n_tile;
+      const float* bias = (p.bias != nullptr) ? p.bias + (long long)ti.group * p.group_bias : nullptr;
+      const int d_row_off = (p.group_mode == 2) ? ti.group * p.group_d_rows : 0;
       const int buf = local & 1;
       const uint32_t use = (uint32_t)(local >> 1);
       // every epilogue thread waits; the four warps then agree on the outcome, so that the warp-wide
@@ -363,7 +397,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             v[j] = __uint_as_float(r[j]) * p.alpha;
-            if (p.epi != EPI_NONE && p.bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(p.bias + gcol0 + j);
+            if (p.epi != EPI_NONE && bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(bias + gcol0 + j);
           }
           // 16-byte chunks of this thread's row, XOR-swizzled like the tensor map (chunk ^= row & 7)
           if (p.out_f32) {
@@ -400,7 +434,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         fence_proxy_async_smem();
         epi_bar_sync();
         if (epi_tid == 0) {
-          const int gc = n_tile * BLOCK_N + c0, gr = m_tile * BLOCK_M;
+          const int gc = n_tile * BLOCK_N + c0, gr = m_tile * BLOCK_M + d_row_off;
           if (p.reduce_add) tma_reduce_add_2d(&map_d, smem_u32(stage_main), gc, gr);
           else tma_store_2d(&map_d, smem_u32(stage_main), gc, gr);
           if (p.has_aux) tma_store_2d(&map_aux, smem_u32(stage_aux), gc, gr);
@@ -412,6 +446,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // all of this thread's tcgen05.ld for the buffer are complete: hand the accumulator back
       tc_fence_before();
       mbar_arrive(tempty_bar(buf));
+      ++local;
     }
     if (epi_tid == 0) tma_wait_all<0>();
   }
@@ -475,6 +510,8 @@ struct GemmCall {
   float alpha;
   int* err;
   int sms;
+  int group_mode = 0, num_groups = 1;
+  const int* group_table = nullptr;
 };
 
 template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN>
@@ -489,11 +526,15 @@ int launch(const GemmCall& c, cudaStream_t stream) {
   rc = A_MN ? make_map(&ma, c.a, ELEM, TF32, c.K, c.M, c.lda, RUN, BLOCK_K, TF32)
             : make_map(&ma, c.a, ELEM, TF32, c.M, c.K, c.lda, BLOCK_K, BLOCK_M);
   if (rc) return rc;
-  rc = B_MN ? make_map(&mb, c.b, ELEM, TF32, c.K, c.N, c.ldb, RUN, BLOCK_K, TF32)
-            : make_map(&mb, c.b, ELEM, TF32, c.N, c.K, c.ldb, BLOCK_K, BLOCK_N);
+  // grouped mode 1 stacks the groups' B matrices along B's row coordinate; mode 2 stacks the outputs along D's rows
+  const long long b_groups = c.group_mode == 1 ? c.num_groups : 1, d_groups = c.group_mode == 2 ? c.num_groups : 1;
+  if (c.group_mode == 2 && (!A_MN || !B_MN || (c.num_groups > 1 && c.M % BLOCK_M != 0) || c.aux)) return -17;
+  if (c.group_mode == 1 && c.splits > 1) return -17;
+  rc = B_MN ? make_map(&mb, c.b, ELEM, TF32, c.K * b_groups, c.N, c.ldb, RUN, BLOCK_K, TF32)
+            : make_map(&mb, c.b, ELEM, TF32, c.N * b_groups, c.K, c.ldb, BLOCK_K, BLOCK_N);
   if (rc) return rc;
   const int out_elem = c.out_f32 ? 4 : 2;
-  rc = make_map(&md, c.d, out_elem, c.out_f32 != 0, c.M, c.N, c.ldd, ROW_BYTES / out_elem, BLOCK_M);
+  rc = make_map(&md, c.d, out_elem, c.out_f32 != 0, c.M * d_groups, c.N, c.ldd, ROW_BYTES / out_elem, BLOCK_M);
   if (rc) return rc;
   if (c.aux) {
     rc = make_map(&maux, c.aux, 2, false, c.M, c.N, c.ldaux, ROW_BYTES / 2, BLOCK_M);
@@ -513,7 +554,10 @@ int launch(const GemmCall& c, cudaStream_t stream) {
   if (p.num_splits > 1 && !c.reduce_add) return -13;
   p.epi = c.epi; p.out_f32 = c.out_f32; p.reduce_add = c.reduce_add; p.has_aux = c.aux != nullptr;
   p.bias = c.bias; p.alpha = c.alpha; p.err = c.err;
-  const int tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+  p.group_mode = c.group_mode; p.num_groups = c.num_groups; p.group_table = c.group_table;
+  p.group_b_rows = B_MN ? c.K : c.N; p.group_d_rows = c.M; p.group_bias = c.N;
+  if (c.group_mode == 2) { p.num_splits = 1; p.kblocks_per_split = p.total_kblocks; }
+  const int tiles = p.num_m_tiles * p.num_n_tiles * (c.group_mode == 2 ? c.num_groups : p.num_splits);
   if (tiles <= 0 || p.total_kblocks <= 0) return 0;
   const int grid = tiles < c.sms ? tiles : c.sms;
   auto kern = tc_gemm_kernel<BLOCK_N, STAGES, TF32, A_MN, B_MN>;
@@ -556,6 +600,33 @@ HM_API int hm_tc_gemm(const void* a, const void* b, void* d, void* aux, const vo
       default: return -16;
     }
   }
+  switch (block_n) {
+    case 256: return dispatch_major<256, 4, false>(c, stream);
+    case 128: return dispatch_major<128, 6, false>(c, stream);
+    case 64: return dispatch_major<64, 8, false>(c, stream);
+    default: return -16;
+  }
+}
+
+// Grouped variants of hm_tc_gemm for bf16 operands (see GemmParams for the two modes). `group_table` is a device
+// array: mode 1 -> int[ceil(M / 128)] group of every M tile (-1 = skip; M is the padded row count of A and D, B is
+// the stack of num_groups matrices of N x K, bias the stack of num_groups vectors of N); mode 2 -> int[num_groups + 1]
+// row offsets (multiples of 64) into the shared K extent of the MN-major operands A [K][M] and B [K][N], D is the
+// stack of num_groups outputs of M x N (M a multiple of 128).
+HM_API int hm_tc_gemm_grouped(const void* a, const void* b, void* d, void* aux, const void* bias, int M, int N, int K,
+                              long long lda, long long ldb, long long ldd, long long ldaux, int a_mn, int b_mn,
+                              int out_f32, int epi, int reduce_add, float alpha, int block_n, void* err, int sms,
+                              int group_mode, int num_groups, const int* group_table, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (group_mode != 1 && group_mode != 2) return -17;
+  if (group_table == nullptr) return -17;
+  if (reduce_add && !out_f32) return -14;
+  if (aux && out_f32) return -15;
+  GemmCall c{a, b, d, aux, (const float*)bias, M, N, K, lda, ldb, ldd, ldaux, a_mn, b_mn, 0, out_f32, epi,
+             reduce_add, 1, alpha, (int*)err, sms};
+  c.group_mode = group_mode;
+  c.num_groups = num_groups;
+  c.group_table = group_table;
   switch (block_n) {
     case 256: return dispatch_major<256, 4, false>(c, stream);
     case 128: return dispatch_major<128, 6, false>(c, stream);

@@ -117,83 +117,124 @@ def gate_topk(scores: torch.Tensor, grid_size: Sequence[int], k: int, alive: Opt
 # ------------------------------------------------------------------------------------------------------ dispatch
 
 
+TILE_ROWS = 128  # M tile of the grouped GEMM; aligned dispatch pads every expert's rows to a multiple of it
+
+
 class Dispatch:
-    """Result of ``dispatch``: rows sorted by expert. ``packed[offsets[e]:offsets[e+1]]`` are expert ``e``'s rows."""
-    __slots__ = ("packed", "pos", "counts", "offsets", "src", "num_experts")
+    """
+    Result of ``dispatch``: rows sorted by expert. Expert ``e`` owns ``packed[offsets[e]:offsets[e+1]]``, of which
+    the first ``counts[e]`` rows hold tokens (with ``align=1`` that is all of them; with ``align=128`` the rest is
+    zero padding). ``tile_group[m]`` (aligned dispatch only) is the expert that owns rows ``128*m .. 128*m+127``.
+    """
+    __slots__ = ("packed", "pos", "counts", "offsets", "src", "num_experts", "tile_group")
 
-    def __init__(self, packed, pos, counts, offsets, src, num_experts):
+    def __init__(self, packed, pos, counts, offsets, src, num_experts, tile_group=None):
         self.packed, self.pos, self.counts, self.offsets, self.src = packed, pos, counts, offsets, src
-        self.num_experts = num_experts
+        self.num_experts, self.tile_group = num_experts, tile_group
 
 
-def _dispatch_reference(x: torch.Tensor, idx: torch.Tensor, num_experts: int):
+def packed_capacity(tokens: int, k: int, num_experts: int, align: int) -> int:
+    """Rows to allocate for the packed buffer (an upper bound that needs no knowledge of the routing)."""
+    if align == 1:
+        return tokens * k
+    worst = tokens * k + num_experts * (align - 1)
+    return (worst + align - 1) // align * align
+
+
+def _dispatch_reference(x: torch.Tensor, idx: torch.Tensor, num_experts: int, align: int = 1):
     tokens, k = idx.shape
+    device = x.device
     flat = idx.reshape(-1).to(torch.int64)
     routed = flat >= 0
     key = torch.where(routed, flat, torch.full_like(flat, num_experts))
     order = torch.argsort(key, stable=True)
     n_routed = int(routed.sum())
     src = order[:n_routed]
-    pos = torch.full((tokens * k,), -1, dtype=torch.int32, device=x.device)
-    pos[src] = torch.arange(n_routed, dtype=torch.int32, device=x.device)
     counts = torch.bincount(flat[routed], minlength=num_experts).to(torch.int32)
-    offsets = torch.zeros(num_experts + 1, dtype=torch.int32, device=x.device)
-    offsets[1:] = torch.cumsum(counts, 0)
-    packed = torch.zeros(tokens * k, x.shape[1], dtype=x.dtype, device=x.device)
-    packed[:n_routed] = x[src // k]
-    src_full = torch.full((tokens * k,), -1, dtype=torch.int32, device=x.device)
-    src_full[:n_routed] = src.to(torch.int32)
-    return packed, pos.view(tokens, k), counts, offsets, src_full
+    padded = (counts + align - 1) // align * align
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int32, device=device)
+    offsets[1:] = torch.cumsum(padded, 0)
+    dense_start = torch.zeros(num_experts, dtype=torch.int64, device=device)
+    dense_start[1:] = torch.cumsum(counts, 0)[:-1]
+    expert_of = flat[src]
+    row = offsets[:-1].to(torch.int64)[expert_of] + (torch.arange(n_routed, device=device) - dense_start[expert_of])
+    capacity = packed_capacity(tokens, k, num_experts, align)
+    pos = torch.full((tokens * k,), -1, dtype=torch.int32, device=device)
+    pos[src] = row.to(torch.int32)
+    packed = torch.zeros(capacity, x.shape[1], dtype=x.dtype, device=device)
+    packed[row] = x[src // k]
+    src_full = torch.full((capacity,), -1, dtype=torch.int32, device=device)
+    src_full[row] = src.to(torch.int32)
+    tile_group = None
+    if align > 1:
+        tile_group = torch.full((capacity // TILE_ROWS,), -1, dtype=torch.int32, device=device)
+        starts = torch.arange(capacity // TILE_ROWS, device=device) * TILE_ROWS
+        owner = torch.searchsorted(offsets[1:].to(torch.int64), starts, right=True)
+        valid = starts < int(offsets[-1])
+        tile_group[valid] = owner[valid].to(torch.int32)
+    return packed, pos.view(tokens, k), counts, offsets, src_full, tile_group
 
 
-def _dispatch_raw(x: torch.Tensor, idx: torch.Tensor, num_experts: int):
+def _dispatch_raw(x: torch.Tensor, idx: torch.Tensor, num_experts: int, align: int = 1):
     if not _lib.use_kernels(x):
-        return _dispatch_reference(x, idx, num_experts)
+        return _dispatch_reference(x, idx, num_experts, align)
     tokens, k = idx.shape
     hidden = x.shape[1]
-    assert x.stride(1) == 1 and idx.dtype == torch.int32 and idx.is_contiguous()
+    assert x.stride(1) == 1 and idx.dtype == torch.int32 and idx.is_contiguous() and align in (1, TILE_ROWS)
     device = x.device
-    packed = torch.empty(tokens * k, hidden, dtype=x.dtype, device=device)
-    meta = torch.empty(3 * tokens * k + 2 * num_experts + 1, dtype=torch.int32, device=device)
-    pos, rank, src = meta[:tokens * k], meta[tokens * k:2 * tokens * k], meta[2 * tokens * k:3 * tokens * k]
-    counts = meta[3 * tokens * k:3 * tokens * k + num_experts]
-    offsets = meta[3 * tokens * k + num_experts:]
-    src.fill_(-1)
+    capacity = packed_capacity(tokens, k, num_experts, align)
+    max_tiles = capacity // TILE_ROWS if align > 1 else 0
+    packed = torch.empty(capacity, hidden, dtype=x.dtype, device=device)
+    meta = torch.empty(2 * tokens * k + capacity + 2 * num_experts + 1 + max_tiles, dtype=torch.int32, device=device)
+    cursor = 0
+
+    def take(n):
+        nonlocal cursor
+        part = meta[cursor:cursor + n]
+        cursor += n
+        return part
+
+    pos, rank, src = take(tokens * k), take(tokens * k), take(capacity)
+    counts, offsets, tile_group = take(num_experts), take(num_experts + 1), take(max_tiles)
     lib = _lib.load_library()
     with torch.cuda.device(device):
         code = lib.hm_moe_dispatch(_lib.ptr(x), ctypes.c_longlong(x.stride(0)), hidden, _lib.dtype_code(x.dtype),
                                    _lib.ptr(idx), tokens, k, num_experts, _lib.ptr(counts), _lib.ptr(offsets),
-                                   _lib.ptr(rank), _lib.ptr(packed), _lib.ptr(pos), _lib.ptr(src),
+                                   _lib.ptr(rank), _lib.ptr(packed), ctypes.c_longlong(capacity), _lib.ptr(pos),
+                                   _lib.ptr(src), align, _lib.ptr(tile_group if align > 1 else None), max_tiles,
                                    _lib.stream_ptr(device))
     _check(code, "hm_moe_dispatch", kernels=3)
-    return packed, pos.view(tokens, k), counts, offsets, src
+    return packed, pos.view(tokens, k), counts, offsets, src, (tile_group if align > 1 else None)
 
 
 class _DispatchFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, idx, num_experts):
-        packed, pos, counts, offsets, src = _dispatch_raw(x, idx, num_experts)
+    def forward(ctx, x, idx, num_experts, align):
+        packed, pos, counts, offsets, src, tile_group = _dispatch_raw(x, idx, num_experts, align)
         ctx.save_for_backward(pos)
-        ctx.mark_non_differentiable(pos, counts, offsets, src)
-        return packed, pos, counts, offsets, src
+        if tile_group is None:
+            tile_group = torch.empty(0, dtype=torch.int32, device=x.device)
+        ctx.mark_non_differentiable(pos, counts, offsets, src, tile_group)
+        return packed, pos, counts, offsets, src, tile_group
 
     @staticmethod
     def backward(ctx, grad_packed, *unused):
         (pos,) = ctx.saved_tensors
         grad_x = _combine_raw(grad_packed.contiguous(), pos, None, None, None, MODE_SUM)[0]
-        return grad_x, None, None
+        return grad_x, None, None, None
 
 
-def dispatch(x: torch.Tensor, idx: torch.Tensor, num_experts: int) -> Dispatch:
+def dispatch(x: torch.Tensor, idx: torch.Tensor, num_experts: int, align: int = 1) -> Dispatch:
     """
     Sort token rows by their chosen experts (each token appears once per routed slot).
 
     :param x: ``[tokens, hidden]`` (bf16 or fp32, rows 16-byte aligned)
     :param idx: ``int32 [tokens, k]`` expert ids, -1 for an empty slot
+    :param align: 1 = dense rows; 128 = pad every expert to whole 128-row tiles (what ``grouped_ffn`` needs)
     :returns: a ``Dispatch``; gradient flows from ``packed`` back to ``x`` (sum over a token's slots)
     """
-    packed, pos, counts, offsets, src = _DispatchFn.apply(x, idx.contiguous(), num_experts)
-    return Dispatch(packed, pos, counts, offsets, src, num_experts)
+    packed, pos, counts, offsets, src, tile_group = _DispatchFn.apply(x, idx.contiguous(), num_experts, align)
+    return Dispatch(packed, pos, counts, offsets, src, num_experts, tile_group if align > 1 else None)
 
 
 # ------------------------------------------------------------------------------------------------------- combine

@@ -22,6 +22,7 @@ import torch.nn as nn
 
 from hivemind_b200.moe.server.layers import name_to_block
 from hivemind_b200.ops import moe as moe_ops
+from hivemind_b200.ops.grouped_ffn import GroupedFeedforward
 
 
 class _GroupedExperts(torch.autograd.Function):
@@ -101,7 +102,13 @@ class DeviceMixtureOfExperts(nn.Module):
         self.compute_dtype = compute_dtype
         self.train_experts = train_experts
         self.proj = nn.Linear(in_features, sum(self.grid_size))
-        self.experts = nn.ModuleList([name_to_block[expert_cls](in_features) for _ in range(self.experts_per_rank)])
+        # "ffn" experts share one set of stacked parameters and run as grouped GEMMs; any other registered class
+        # runs expert by expert over its contiguous rows
+        self.grouped = expert_cls == "ffn"
+        if self.grouped:
+            self.experts = GroupedFeedforward(self.experts_per_rank, in_features)
+        else:
+            self.experts = nn.ModuleList([name_to_block[expert_cls](in_features) for _ in range(self.experts_per_rank)])
         self.register_buffer("alive", torch.ones(self.num_experts, dtype=torch.uint8))
         uniform = torch.cat([torch.full((size,), 1.0 / size) for size in self.grid_size])
         self.register_buffer("grid_utilization", uniform)
@@ -137,7 +144,8 @@ class DeviceMixtureOfExperts(nn.Module):
 
         dtype = self.compute_dtype or (torch.bfloat16 if tokens.is_cuda else tokens.dtype)
         rows = tokens.to(dtype)
-        routed = moe_ops.dispatch(rows, idx, self.num_experts)
+        align = moe_ops.TILE_ROWS if (self.grouped and self.world == 1) else 1
+        routed = moe_ops.dispatch(rows, idx, self.num_experts, align=align)
         answers = self._run_experts(routed)
         residual = rows if self.switch else None
         mixed = moe_ops.combine(answers, routed.pos, gate, "prob" if self.switch else "softmax", residual=residual)
@@ -147,10 +155,28 @@ class DeviceMixtureOfExperts(nn.Module):
         return out, self._balancing_loss(scores, idx)
 
     def _run_experts(self, routed: moe_ops.Dispatch) -> torch.Tensor:
-        if self.world == 1:
-            bounds = routed.offsets.tolist()  # one small device-to-host read: the GEMM launches need the row counts
-            return _GroupedExperts.apply(routed.packed, bounds, list(self.experts), self.train_experts)
-        return _AllToAllExperts.apply(routed.packed, routed.counts, self)
+        if self.world > 1:
+            return _AllToAllExperts.apply(routed.packed, routed.counts, self)
+        return self._run_local(routed)
+
+    def _run_local(self, routed: moe_ops.Dispatch) -> torch.Tensor:
+        """Apply this rank's experts to the rows that a dispatch over ``len(self.experts)`` experts assigned them."""
+        if self.grouped:
+            return self.experts(routed.packed, routed)  # no host synchronisation: empty tiles are skipped on the device
+        bounds = routed.offsets.tolist()  # one small device-to-host read: per-expert launches need the row counts
+        return _GroupedExperts.apply(routed.packed, bounds, list(self.experts), self.train_experts)
+
+    def run_single_expert(self, local_index: int, rows: torch.Tensor) -> torch.Tensor:
+        """Expert ``local_index`` of this rank applied to ``rows`` directly (for tests and debugging)."""
+        if not self.grouped:
+            return self.experts[local_index](rows)
+        e = self.experts
+        compute = rows.to(e.w1.dtype)
+        hidden = torch.nn.functional.gelu(torch.nn.functional.linear(compute, e.w1[local_index], e.b1[local_index]),
+                                          approximate="tanh")
+        out = torch.nn.functional.linear(hidden, e.w2[local_index], e.b2[local_index])
+        out = torch.nn.functional.layer_norm(compute + out, (e.hid_dim,), e.gamma[local_index], e.beta[local_index], 1e-12)
+        return out.to(rows.dtype)
 
     def _balancing_loss(self, scores: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         """Switch load balancing: per dimension, mean(probability mass * routed fraction) * size^2, summed."""
@@ -196,9 +222,9 @@ class _AllToAllExperts(torch.autograd.Function):
             received.reshape(-1).to(device), output_size=sum(recv_splits)).view(-1, 1)
         with torch.enable_grad():
             incoming.requires_grad_(packed.requires_grad)
-            regrouped = moe_ops.dispatch(incoming, local_expert, per_rank)
-            bounds = regrouped.offsets.tolist()
-            answers = _GroupedExperts.apply(regrouped.packed, bounds, list(layer.experts), layer.train_experts)
+            regrouped = moe_ops.dispatch(incoming, local_expert, per_rank,
+                                         align=moe_ops.TILE_ROWS if layer.grouped else 1)
+            answers = layer._run_local(regrouped)
             back = moe_ops.combine(answers, regrouped.pos, None, "sum")
         outgoing = torch.zeros_like(packed)
         dist.all_to_all_single(outgoing[:sum(send_splits)], back.detach(), send_splits, recv_splits, group=group)
