@@ -74,3 +74,136 @@ async def deserialize_tensor_stream(stream: AsyncIterator[Iterable[runtime_pb2.T
     if parts:
         tensors.append(deserialize_torch_tensor(combine_from_streaming(parts)))
     return tensors
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Copy-light streaming of large tensors. A chunk message on the wire is ordinary protobuf (any peer can parse it
+# with ``runtime_pb2``), but the sender never builds a protobuf object around the payload: the message is emitted as
+# a short hand-encoded prefix followed by a ``memoryview`` into the tensor's own memory, and the receiver copies each
+# chunk once, straight into the (optionally pinned) destination tensor.
+# ---------------------------------------------------------------------------------------------------------------
+
+
+def _varint(value: int) -> bytes:
+    out = bytearray()
+    while True:
+        low = value & 0x7F
+        value >>= 7
+        if value:
+            out.append(low | 0x80)
+        else:
+            out.append(low)
+            return bytes(out)
+
+
+class RawMessage:
+    """A serialized protobuf message kept as a list of byte pieces; ``P2P.send_protobuf`` writes the pieces as is."""
+    __slots__ = ("raw_parts",)
+
+    def __init__(self, *parts):
+        self.raw_parts = parts
+
+    def ByteSize(self) -> int:
+        return sum(len(p) for p in self.raw_parts)
+
+    def SerializeToString(self) -> bytes:
+        return b"".join(bytes(p) for p in self.raw_parts)
+
+
+def _uncompressed_payload(tensor: torch.Tensor) -> Optional[memoryview]:
+    """A byte view of a tensor that NoCompression would send verbatim, or None if it needs conversion."""
+    if tensor.dtype == torch.bfloat16 or tensor.is_sparse:
+        return None
+    payload = tensor.detach()
+    if payload.device.type != "cpu":
+        payload = payload.cpu()
+    if not payload.is_contiguous():
+        payload = payload.contiguous()
+    try:
+        return memoryview(payload.numpy()).cast("B")
+    except (TypeError, ValueError):
+        return None
+
+
+def stream_tensor_messages(tensor: torch.Tensor, compression_type: int, chunk_size_bytes: int, *,
+                           outer_field: int = 2, outer_prefix: bytes = b"") -> Iterator[RawMessage]:
+    """
+    Serialized messages ``Outer{<outer_prefix fields>, tensors(field outer_field) = [chunk]}``, one per chunk of
+    ``tensor``, equivalent to wrapping ``split_for_streaming(serialize_torch_tensor(tensor, ...))`` chunk by chunk
+    (``ExpertRequest`` / ``ExpertResponse`` keep their tensors in field 2). Uncompressed CPU tensors are sent from
+    their own memory; every other case serializes once and slices that buffer.
+    """
+    payload = _uncompressed_payload(tensor) if compression_type == CompressionType.NONE else None
+    if payload is not None:
+        header = runtime_pb2.Tensor(compression=CompressionType.NONE, size=tensor.shape,
+                                    dtype=str(tensor.dtype).replace("torch.", ""), requires_grad=tensor.requires_grad)
+    else:
+        whole = serialize_torch_tensor(tensor, compression_type)
+        payload = memoryview(whole.buffer)
+        header = runtime_pb2.Tensor(compression=whole.compression, size=whole.size, dtype=whole.dtype,
+                                    requires_grad=whole.requires_grad)
+    total = len(payload)
+    header.chunks = max(1, len(range(0, total, chunk_size_bytes)))
+    outer_tag = _varint((outer_field << 3) | 2)
+    first = True
+    for start in range(0, max(total, 1), chunk_size_bytes):
+        piece = payload[start:start + chunk_size_bytes]
+        meta = header.SerializeToString() if first else b""
+        first = False
+        inner_prefix = meta + b"\x0a" + _varint(len(piece))  # Tensor.buffer is field 1, length-delimited
+        inner_len = len(inner_prefix) + len(piece)
+        yield RawMessage(outer_prefix + outer_tag + _varint(inner_len) + inner_prefix, piece)
+
+
+def _direct_dtype(name: str):
+    try:
+        dtype = getattr(torch, name)
+    except AttributeError:
+        return None
+    return dtype if isinstance(dtype, torch.dtype) and dtype != torch.bfloat16 else None
+
+
+async def deserialize_tensor_stream_into(stream: AsyncIterator[Iterable[runtime_pb2.Tensor]], pin_memory: bool = False
+                                         ) -> List[torch.Tensor]:
+    """
+    Like ``deserialize_tensor_stream``, but uncompressed tensors are assembled with one copy per chunk directly in
+    their destination (page-locked when ``pin_memory``, so a later host-to-device copy needs no staging).
+    """
+    tensors: List[torch.Tensor] = []
+    parts: List[runtime_pb2.Tensor] = []
+    target = None  # (tensor, flat uint8 view, bytes filled) while a directly assembled tensor is in progress
+
+    def finish():
+        nonlocal parts, target
+        if target is not None:
+            tensor, _, filled = target
+            if filled != tensor.numel() * tensor.element_size():
+                raise ValueError("tensor stream ended before all bytes of a tensor arrived")
+            tensors.append(tensor)
+            target = None
+        elif parts:
+            tensors.append(deserialize_torch_tensor(combine_from_streaming(parts)))
+            parts = []
+
+    async for batch in stream:
+        for chunk in batch:
+            if chunk.dtype:
+                finish()
+                dtype = _direct_dtype(chunk.dtype) if chunk.compression == CompressionType.NONE else None
+                if dtype is not None:
+                    tensor = torch.empty(tuple(chunk.size), dtype=dtype, pin_memory=pin_memory)
+                    if tensor.is_floating_point() and chunk.requires_grad:
+                        tensor.requires_grad_(True)
+                    flat = tensor.detach().view(-1).view(torch.uint8).numpy()
+                    target = (tensor, flat, 0)
+            if target is not None:
+                tensor, flat, filled = target
+                size = len(chunk.buffer)
+                if filled + size > flat.shape[0]:
+                    raise ValueError("tensor stream carries more bytes than the tensor's shape allows")
+                flat[filled:filled + size] = memoryview(chunk.buffer)
+                target = (tensor, flat, filled + size)
+            else:
+                parts.append(chunk)
+    finish()
+    return tensors

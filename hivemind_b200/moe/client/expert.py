@@ -14,7 +14,8 @@ import torch
 import torch.nn as nn
 from torch.autograd.function import once_differentiable
 
-from hivemind_b200.compression import deserialize_tensor_stream, deserialize_torch_tensor, serialize_torch_tensor
+from hivemind_b200.compression import deserialize_torch_tensor, serialize_torch_tensor
+from hivemind_b200.compression.serialization import _varint, deserialize_tensor_stream_into, stream_tensor_messages
 from hivemind_b200.dht import DHT
 from hivemind_b200.moe.client.remote_expert_worker import RemoteExpertWorker
 from hivemind_b200.moe.expert_uid import ExpertInfo
@@ -22,7 +23,6 @@ from hivemind_b200.p2p import P2P, PeerID, StubBase
 from hivemind_b200.p2p.control import DEFAULT_MAX_MSG_SIZE, MAX_UNARY_PAYLOAD_SIZE
 from hivemind_b200.proto import runtime_pb2
 from hivemind_b200.utils import MPFuture, MSGPackSerializer, nested_compare, nested_flatten, nested_pack
-from hivemind_b200.utils.streaming import split_for_streaming
 
 DUMMY = torch.empty(0, requires_grad=True)  # keeps the remote call in the graph when no input requires grad
 
@@ -112,37 +112,48 @@ def _payload_bytes(tensors: Sequence[torch.Tensor]) -> int:
     return sum(t.element_size() * t.nelement() for t in tensors)
 
 
-async def _call_expert(uid: str, method: str, tensors: Sequence[torch.Tensor],
-                       serialized: Sequence[runtime_pb2.Tensor], stub) -> List[torch.Tensor]:
-    """One forward or backward exchange; unary if the raw payload fits into one message, streamed otherwise."""
+async def _call_expert(uid: str, method: str, tensors: Sequence[torch.Tensor], compressions: Sequence[int], stub
+                       ) -> List[torch.Tensor]:
+    """One forward or backward exchange; unary if the raw payload fits into one message, streamed otherwise.
+    Streamed tensors are written chunk by chunk from their own memory (no intermediate protobuf objects)."""
     if _payload_bytes(tensors) <= MAX_UNARY_PAYLOAD_SIZE:
-        reply = await getattr(stub, f"rpc_{method}")(runtime_pb2.ExpertRequest(uid=uid, tensors=list(serialized)))
+        serialized = [serialize_torch_tensor(t, c) for t, c in zip(tensors, compressions)]
+        reply = await getattr(stub, f"rpc_{method}")(runtime_pb2.ExpertRequest(uid=uid, tensors=serialized))
         return [deserialize_torch_tensor(t) for t in reply.tensors]
 
     async def _requests():
-        for tensor in serialized:
-            for part in split_for_streaming(tensor, DEFAULT_MAX_MSG_SIZE):
-                yield runtime_pb2.ExpertRequest(uid=uid, tensors=[part])
+        uid_bytes = uid.encode()
+        uid_field = b"\x0a" + _varint(len(uid_bytes)) + uid_bytes  # ExpertRequest.uid is field 1
+        for tensor, compression in zip(tensors, compressions):
+            for message in stream_tensor_messages(tensor, compression, DEFAULT_MAX_MSG_SIZE, outer_field=2,
+                                                  outer_prefix=uid_field):
+                yield message
 
     async def _reply_parts(stream):
         async for message in stream:
             yield message.tensors
 
     stream = await _maybe_await(getattr(stub, f"rpc_{method}_stream")(_requests()))
-    return await deserialize_tensor_stream(_reply_parts(stream))
+    return await deserialize_tensor_stream_into(_reply_parts(stream))
 
 
 async def _maybe_await(value):
     return await value if hasattr(value, "__await__") else value
 
 
-async def expert_forward(uid: str, inputs: Sequence[torch.Tensor], serialized_tensors, stub) -> List[torch.Tensor]:
-    return await _call_expert(uid, "forward", inputs, list(serialized_tensors), stub)
+def _compressions(schema) -> List[int]:
+    return [descr.compression for descr in nested_flatten(schema)]
 
 
-async def expert_backward(uid: str, inputs_and_grads: Sequence[torch.Tensor], serialized_tensors, stub
+async def expert_forward(uid: str, inputs: Sequence[torch.Tensor], compressions: Sequence[int], stub
+                         ) -> List[torch.Tensor]:
+    """Forward pass of a remote expert; ``compressions[i]`` is the wire codec of ``inputs[i]``."""
+    return await _call_expert(uid, "forward", inputs, compressions, stub)
+
+
+async def expert_backward(uid: str, inputs_and_grads: Sequence[torch.Tensor], compressions: Sequence[int], stub
                           ) -> List[torch.Tensor]:
-    return await _call_expert(uid, "backward", inputs_and_grads, list(serialized_tensors), stub)
+    return await _call_expert(uid, "backward", inputs_and_grads, compressions, stub)
 
 
 class _RemoteModuleCall(torch.autograd.Function):
@@ -154,9 +165,8 @@ class _RemoteModuleCall(torch.autograd.Function):
         inputs = tuple(t.detach().cpu() for t in inputs)
         ctx.uid, ctx.stub, ctx.info = uid, stub, info
         ctx.save_for_backward(*inputs)
-        serialized = [serialize_torch_tensor(t, descr.compression)
-                      for t, descr in zip(inputs, nested_flatten(info["forward_schema"]))]
-        outputs = RemoteExpertWorker.run_coroutine(expert_forward(uid, inputs, serialized, stub))
+        outputs = RemoteExpertWorker.run_coroutine(
+            expert_forward(uid, inputs, _compressions(info["forward_schema"]), stub))
         return tuple(outputs)
 
     @staticmethod
@@ -164,7 +174,6 @@ class _RemoteModuleCall(torch.autograd.Function):
     def backward(ctx, *grad_outputs) -> Tuple[Optional[torch.Tensor], ...]:
         grads_cpu = tuple(g.cpu() for g in grad_outputs)
         payload = tuple(nested_flatten((ctx.saved_tensors, grads_cpu)))
-        schema = tuple(nested_flatten((ctx.info["forward_schema"], ctx.info["outputs_schema"])))
-        serialized = [serialize_torch_tensor(t, descr.compression) for t, descr in zip(payload, schema)]
-        grad_inputs = RemoteExpertWorker.run_coroutine(expert_backward(ctx.uid, payload, serialized, ctx.stub))
+        compressions = _compressions((ctx.info["forward_schema"], ctx.info["outputs_schema"]))
+        grad_inputs = RemoteExpertWorker.run_coroutine(expert_backward(ctx.uid, payload, compressions, ctx.stub))
         return (DUMMY, None, None, None, *grad_inputs)

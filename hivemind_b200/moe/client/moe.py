@@ -22,7 +22,6 @@ import torch
 import torch.nn as nn
 from torch.autograd.function import once_differentiable
 
-from hivemind_b200.compression import serialize_torch_tensor
 from hivemind_b200.dht import DHT
 from hivemind_b200.moe.client.beam_search import MoEBeamSearcher
 from hivemind_b200.moe.client.expert import DUMMY, RemoteExpert, expert_backward, expert_forward, get_server_stub
@@ -208,15 +207,14 @@ class _RemoteCallMany(torch.autograd.Function):
             flat_inputs_cpu.append(tensor.detach().cpu())
         assert all(len(t) == num_samples for t in flat_inputs_cpu)
 
-        forward_schema = list(nested_flatten(info["forward_schema"]))
+        forward_compressions = [descr.compression for descr in nested_flatten(info["forward_schema"])]
         calls = _group_calls(experts_per_sample, max_rows_per_call)
         pending: Dict[Future, _Call] = {}
         for call in calls:
             index = torch.as_tensor(call.samples, dtype=torch.long)
             rows = [t.index_select(0, index) for t in flat_inputs_cpu]
-            serialized = [serialize_torch_tensor(t, descr.compression) for t, descr in zip(rows, forward_schema)]
             stub = get_server_stub(call.expert.p2p, call.expert.peer_id)
-            future = RemoteExpertWorker.run_coroutine(expert_forward(call.expert.uid, rows, serialized, stub),
+            future = RemoteExpertWorker.run_coroutine(expert_forward(call.expert.uid, rows, forward_compressions, stub),
                                                       return_future=True)
             pending[future] = call
 
@@ -270,7 +268,8 @@ class _RemoteCallMany(torch.autograd.Function):
             grads_cpu.append(tensor.cpu())
         num_samples, max_experts = mask_grad.shape
         pairs = list(zip(alive_ii.cpu().tolist(), alive_jj.cpu().tolist()))
-        backward_schema = tuple(nested_flatten((info["forward_schema"], info["outputs_schema"])))
+        backward_compressions = [descr.compression
+                                 for descr in nested_flatten((info["forward_schema"], info["outputs_schema"]))]
 
         calls = _group_calls(experts_per_sample, max_rows_per_call, pairs)
         pending: Dict[Future, _Call] = {}
@@ -279,10 +278,9 @@ class _RemoteCallMany(torch.autograd.Function):
             slots_index = torch.as_tensor(call.slots, dtype=torch.long)
             payload = tuple(t.index_select(0, rows_index) for t in flat_inputs_cpu) + \
                 tuple(g[rows_index, slots_index] for g in grads_cpu)
-            serialized = [serialize_torch_tensor(t, descr.compression) for t, descr in zip(payload, backward_schema)]
             stub = get_server_stub(call.expert.p2p, call.expert.peer_id)
-            future = RemoteExpertWorker.run_coroutine(expert_backward(call.expert.uid, payload, serialized, stub),
-                                                      return_future=True)
+            future = RemoteExpertWorker.run_coroutine(
+                expert_backward(call.expert.uid, payload, backward_compressions, stub), return_future=True)
             pending[future] = call
 
         done = cls._collect_responses(pending, num_samples, backward_k_min, backward_timeout, timeout_after_k_min,

@@ -14,7 +14,8 @@ from typing import AsyncIterator, Dict, List, Optional, Sequence
 
 import torch
 
-from hivemind_b200.compression import deserialize_tensor_stream, deserialize_torch_tensor, serialize_torch_tensor
+from hivemind_b200.compression import deserialize_torch_tensor, serialize_torch_tensor
+from hivemind_b200.compression.serialization import deserialize_tensor_stream_into, stream_tensor_messages
 from hivemind_b200.dht import DHT
 from hivemind_b200.moe.server.module_backend import ModuleBackend
 from hivemind_b200.moe.server.task_pool import TaskPool
@@ -23,7 +24,6 @@ from hivemind_b200.p2p.control import DEFAULT_MAX_MSG_SIZE
 from hivemind_b200.proto import runtime_pb2
 from hivemind_b200.utils import MPFuture, MSGPackSerializer, get_logger, nested_flatten
 from hivemind_b200.utils.asyncio import LoopThread
-from hivemind_b200.utils.streaming import split_for_streaming
 
 logger = get_logger(__name__)
 
@@ -40,6 +40,7 @@ class ConnectionHandler(ServicerBase):
         self.dht, self.module_backends = dht, module_backends
         self.balanced, self.shutdown_timeout = balanced, shutdown_timeout
         self._p2p: Optional[P2P] = None
+        self._pin_inputs = torch.cuda.is_available()  # streamed inputs land in page-locked memory for the H2D copy
         self._thread = LoopThread("ConnectionHandler")
         self.ready = MPFuture()
         if start:
@@ -105,6 +106,13 @@ class ConnectionHandler(ServicerBase):
         return [serialize_torch_tensor(result, descr.compression, allow_inplace=True)
                 for result, descr in zip(outputs, nested_flatten(schema))]
 
+    async def _run_pool_streamed(self, pool: TaskPool, tensors: Sequence[torch.Tensor], schema):
+        """Like ``_run_pool`` for large results: yields response messages chunk by chunk from the tensors' memory."""
+        outputs = await pool.submit_task(*tensors)
+        for result, descr in zip(outputs, nested_flatten(schema)):
+            for message in stream_tensor_messages(result, descr.compression, DEFAULT_MAX_MSG_SIZE, outer_field=2):
+                yield message
+
     async def _gather_stream(self, requests: AsyncIterator[runtime_pb2.ExpertRequest]):
         """Reassemble the tensors of a chunked request; every message must name the same expert."""
         uid: Optional[str] = None
@@ -118,7 +126,7 @@ class ConnectionHandler(ServicerBase):
                     raise ValueError("Expert uids differ in one request")
                 yield message.tensors
 
-        tensors = await deserialize_tensor_stream(_tensor_parts())
+        tensors = await deserialize_tensor_stream_into(_tensor_parts(), pin_memory=self._pin_inputs)
         return uid, tensors
 
     async def rpc_forward(self, request: runtime_pb2.ExpertRequest, context: P2PContext) -> runtime_pb2.ExpertResponse:
@@ -130,9 +138,8 @@ class ConnectionHandler(ServicerBase):
                                  ) -> AsyncIterator[runtime_pb2.ExpertResponse]:
         uid, inputs = await self._gather_stream(requests)
         backend = self.module_backends[uid]
-        for tensor in await self._run_pool(backend.forward_pool, inputs, backend.outputs_schema):
-            for part in split_for_streaming(tensor, DEFAULT_MAX_MSG_SIZE):
-                yield runtime_pb2.ExpertResponse(tensors=[part])
+        async for message in self._run_pool_streamed(backend.forward_pool, inputs, backend.outputs_schema):
+            yield message
 
     async def rpc_backward(self, request: runtime_pb2.ExpertRequest, context: P2PContext) -> runtime_pb2.ExpertResponse:
         backend = self.module_backends[request.uid]
@@ -144,6 +151,5 @@ class ConnectionHandler(ServicerBase):
                                   ) -> AsyncIterator[runtime_pb2.ExpertResponse]:
         uid, inputs_and_grads = await self._gather_stream(requests)
         backend = self.module_backends[uid]
-        for tensor in await self._run_pool(backend.backward_pool, inputs_and_grads, backend.grad_inputs_schema):
-            for part in split_for_streaming(tensor, DEFAULT_MAX_MSG_SIZE):
-                yield runtime_pb2.ExpertResponse(tensors=[part])
+        async for message in self._run_pool_streamed(backend.backward_pool, inputs_and_grads, backend.grad_inputs_schema):
+            yield message

@@ -7,6 +7,7 @@ logs batches/s and examples/s per pool.
 """
 from __future__ import annotations
 
+import queue
 import threading
 import time
 from collections import defaultdict
@@ -57,6 +58,16 @@ class Runtime(threading.Thread):
                 backend.module.to(self.device)
         if self.stats_reporter is not None:
             self.stats_reporter.start()
+        use_cuda = self.device is not None and self.device.type == "cuda"
+        sender = None
+        if use_cuda:
+            # three streams: inputs are uploaded while the previous batch computes, results are downloaded (and the
+            # callers' futures resolved) by a helper thread while the next batch computes
+            self._h2d_stream = torch.cuda.Stream(self.device)
+            self._d2h_stream = torch.cuda.Stream(self.device)
+            self._finished: "queue.Queue" = queue.Queue(maxsize=max(2, min(self.prefetch_batches, 8)))
+            sender = threading.Thread(target=self._deliver_outputs, name="Runtime.sender", daemon=True)
+            sender.start()
         self.ready.set()
         logger.info("Started")
         try:
@@ -64,26 +75,67 @@ class Runtime(threading.Thread):
                 pool = self._wait_for_ready_pool()
                 if pool is None:
                     continue
-                batch_index, batch = pool.load_batch_to_runtime(device=self.device)
+                start = time.perf_counter()
+                if use_cuda:
+                    compute = torch.cuda.current_stream(self.device)
+                    with torch.cuda.stream(self._h2d_stream):
+                        batch_index, batch = pool.load_batch_to_runtime(device=self.device)
+                    compute.wait_stream(self._h2d_stream)
+                    for tensor in batch:
+                        tensor.record_stream(compute)
+                else:
+                    batch_index, batch = pool.load_batch_to_runtime(device=self.device)
                 if not batch:
                     continue
-                start = time.perf_counter()
                 try:
                     outputs = pool.process_func(*batch)
-                    if self.device is not None and self.device.type == "cuda":
-                        torch.cuda.current_stream(self.device).synchronize()
                     batch_size = outputs[0].size(0) if outputs else batch[0].size(0)
-                    pool.send_outputs_from_runtime(batch_index, list(outputs))
-                    if self.stats_reporter is not None:
-                        self.stats_reporter.report_stats(pool.name, batch_size, time.perf_counter() - start)
+                    if use_cuda:
+                        done = torch.cuda.Event()
+                        done.record(torch.cuda.current_stream(self.device))
+                        self._finished.put((pool, batch_index, list(outputs), done, batch_size, start))
+                    else:
+                        pool.send_outputs_from_runtime(batch_index, list(outputs))
+                        if self.stats_reporter is not None:
+                            self.stats_reporter.report_stats(pool.name, batch_size, time.perf_counter() - start)
                 except KeyboardInterrupt:
                     raise
                 except BaseException as exception:
                     logger.exception(f"Caught {exception!r}, attempting to recover")
                     pool.send_exception_from_runtime(batch_index, exception)
         finally:
+            if sender is not None:
+                self._finished.put(None)
+                sender.join(timeout=10)
             if not self.shutdown_trigger.is_set():
                 self.shutdown()
+
+    def _deliver_outputs(self) -> None:
+        """Helper thread of a CUDA runtime: wait for a batch, copy its outputs to page-locked memory, resolve futures."""
+        torch.cuda.set_device(self.device)
+        while True:
+            item = self._finished.get()
+            if item is None:
+                return
+            pool, batch_index, outputs, done, batch_size, start = item
+            try:
+                done.synchronize()
+                with torch.cuda.stream(self._d2h_stream):
+                    host = []
+                    for out in outputs:
+                        if isinstance(out, torch.Tensor) and out.is_cuda:
+                            page_locked = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+                            page_locked.copy_(out.detach(), non_blocking=True)
+                            host.append(page_locked)
+                        else:
+                            host.append(out)
+                self._d2h_stream.synchronize()
+                pool.send_outputs_from_runtime(batch_index, host)
+                if self.stats_reporter is not None:
+                    self.stats_reporter.report_stats(pool.name, batch_size, time.perf_counter() - start)
+            except BaseException as exception:
+                logger.exception(f"Caught {exception!r} while returning outputs")
+                pool.send_exception_from_runtime(batch_index, exception)
 
     def _wait_for_ready_pool(self):
         """Block until a pool has a batch to run (or a batching timeout is about to make one ready)."""

@@ -177,10 +177,17 @@ class TaskPool(TaskPoolBase):
         batch_inputs = []
         for i in range(num_inputs):
             parts = [task.args[i] for task in batch_tasks]
-            merged = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
-            if device is not None and merged.device != device:
-                if merged.device.type == "cpu" and device.type == "cuda" and not merged.is_pinned():
+            to_cuda = device is not None and device.type == "cuda" and parts[0].device.type == "cpu"
+            if len(parts) == 1:
+                merged = parts[0].detach()
+                if to_cuda and not merged.is_pinned():
                     merged = merged.pin_memory()
+            elif to_cuda:  # concatenate straight into page-locked memory: one host copy instead of two
+                merged = torch.empty((rows, *parts[0].shape[1:]), dtype=parts[0].dtype, pin_memory=True)
+                torch.cat([p.detach() for p in parts], dim=0, out=merged)
+            else:
+                merged = torch.cat(parts, dim=0)
+            if device is not None and merged.device != device:
                 merged = merged.to(device, non_blocking=True)
             batch_inputs.append(merged)
         return batch_id, batch_inputs

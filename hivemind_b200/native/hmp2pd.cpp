@@ -155,6 +155,9 @@ struct Daemon {
     c->fd = fd;
     c->kind = kind;
     set_nonblock(fd);
+    int sockbuf = 4 << 20;  // large tensors move through these sockets: ask for deep kernel buffers (best effort)
+    setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &sockbuf, sizeof(sockbuf));
+    setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &sockbuf, sizeof(sockbuf));
     epoll_event ev{};
     ev.events = EPOLLIN;
     ev.data.u64 = c->id;
@@ -176,10 +179,24 @@ struct Daemon {
     ev.data.u64 = c->id;
     epoll_ctl(ep, EPOLL_CTL_MOD, c->fd, &ev);
   }
-  void send_bytes(Conn* c, const std::string& data) {
+  void send_bytes(Conn* c, const std::string& data) { send_raw(c, data.data(), data.size()); }
+  // Queue bytes for a connection. With an empty queue the bytes go straight to the socket and only what the kernel
+  // did not take is copied into the queue (the common case for spliced streams moving large tensors).
+  void send_raw(Conn* c, const char* data, size_t len) {
     if (c->wr_closed) return;
     if (c->out_off > 0 && c->out_off == c->out.size()) { c->out.clear(); c->out_off = 0; }
-    c->out.append(data);
+    if (!c->connecting && c->out_off == c->out.size()) {
+      while (len > 0) {
+        ssize_t n = ::send(c->fd, data, len, MSG_NOSIGNAL);
+        if (n > 0) { data += n; len -= (size_t)n; continue; }
+        if (n < 0 && errno == EINTR) continue;
+        if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) break;
+        close_conn(c->id, "send failed");
+        return;
+      }
+      if (len == 0) return;
+    }
+    c->out.append(data, len);
     if (!c->connecting) flush(c);
     else rearm(c);
   }
@@ -901,7 +918,7 @@ struct Daemon {
   }
 
   void on_readable(Conn* c) {
-    char buf[1 << 16];
+    static char buf[1 << 20];  // the daemon is single-threaded and on_readable never nests
     uint64_t id = c->id;
     while (true) {
       c = get(id);
@@ -911,7 +928,7 @@ struct Daemon {
         if (c->kind == Kind::SPLICE) {
           Conn* p = get(c->partner);
           if (!p) continue;  // partner gone: discard
-          send_bytes(p, std::string(buf, (size_t)n));
+          send_raw(p, buf, (size_t)n);
           c = get(id);
           p = c ? get(c->partner) : nullptr;
           if (c && p && p->out.size() - p->out_off > SPLICE_HIGH_WATER) { c->read_paused = true; rearm(c); return; }

@@ -226,7 +226,7 @@ class P2P:
 
     # ------------------------------------------------------------------------------------------ framing
     @staticmethod
-    async def send_raw_data(data: bytes, writer: asyncio.StreamWriter, *, chunk_size: int = 2 ** 16) -> None:
+    async def send_raw_data(data: bytes, writer: asyncio.StreamWriter, *, chunk_size: int = 2 ** 20) -> None:
         writer.write(len(data).to_bytes(P2P.HEADER_LEN, P2P.BYTEORDER))
         view = memoryview(data)
         for offset in range(0, len(data), chunk_size):
@@ -241,7 +241,15 @@ class P2P:
     @staticmethod
     async def send_protobuf(protobuf: Union[Message, RPCError], writer: asyncio.StreamWriter) -> None:
         writer.write(P2P.ERROR_MARKER if isinstance(protobuf, RPCError) else P2P.MESSAGE_MARKER)
-        await P2P.send_raw_data(protobuf.SerializeToString(), writer)
+        pieces = getattr(protobuf, "raw_parts", None)
+        if pieces is None:
+            await P2P.send_raw_data(protobuf.SerializeToString(), writer)
+            return
+        # a message that is already serialized as several byte pieces (large tensor chunks): no joining, no copies
+        writer.write(sum(len(piece) for piece in pieces).to_bytes(P2P.HEADER_LEN, P2P.BYTEORDER))
+        for piece in pieces:
+            writer.write(piece)
+        await writer.drain()
 
     @staticmethod
     async def receive_protobuf(input_protobuf_type: Type[Message], reader: asyncio.StreamReader

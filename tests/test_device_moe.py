@@ -342,7 +342,7 @@ def test_grouped_ffn_matches_fp32_reference():
     x = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     routed = moe_ops.dispatch(x, idx, experts, align=128)
     y = module(routed.packed, routed)
-    probe = torch.randn_like(y)
+    probe = torch.randn_like(y) * (routed.src >= 0).unsqueeze(1)  # pad rows receive no gradient, as after combine
     (y.float() * probe.float()).sum().backward()
     x_ref = x.detach().float().cpu().requires_grad_(True)
     routed_ref = moe_ops.dispatch(x_ref, idx.cpu(), experts, align=128)
