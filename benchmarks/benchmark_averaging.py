@@ -1,0 +1,235 @@
+"""Averaging benchmarks.
+
+``--mode swarm`` (default) is the reference's benchmarks/benchmark_averaging.py: ``num_peers`` averagers (threads of
+this process, CPU tensors shaped like a small transformer) find groups of ``target_group_size`` through the DHT for
+``num_rounds`` rounds; the result is the success rate and the wall time.
+
+``--mode device`` measures the device butterfly all-reduce between GPUs of one box, one process per GPU under
+``torchrun`` (peer arenas mapped through CUDA IPC): for each tensor size and codec it times whole rounds (encode,
+publish, pull + reduce, delta encode, pull + apply) with CUDA events on the round's stream, takes the max over ranks
+and reports the bus bandwidth ``2 (n - 1) / n * bytes / time`` next to NCCL's all_reduce of the same fp32 tensor.
+With one GPU, ``--emulate-ranks N`` runs an N-rank group stage by stage on that GPU (no NVLink traffic: it measures
+the kernels only).
+"""
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+from hivemind_b200 import DHT, DecentralizedAverager
+from hivemind_b200.compression import (BlockwiseQuantization, CompressionInfo, Float16Compression, NoCompression,
+                                       Quantile8BitQuantization, ScaledFloat16Compression, Uniform8BitQuantization)
+from hivemind_b200.utils.limits import increase_file_limit
+from hivemind_b200.utils.logging import get_logger
+
+logger = get_logger(__name__)
+CODECS = {"none": NoCompression, "float16": Float16Compression, "meanstd16": ScaledFloat16Compression,
+          "uniform8": Uniform8BitQuantization, "quantile8": Quantile8BitQuantization, "blockwise8": BlockwiseQuantization}
+
+
+def sample_tensors(hid_size, num_layers):
+    tensors = []
+    for _ in range(num_layers):
+        tensors += [torch.randn(hid_size, 3 * hid_size), torch.randn(3 * hid_size), torch.randn(3 * hid_size),
+                    torch.randn(hid_size, hid_size), torch.ones(hid_size), torch.zeros(hid_size),
+                    torch.randn(hid_size, 4 * hid_size), torch.randn(4 * hid_size), torch.ones(4 * hid_size),
+                    torch.randn(2, hid_size, hid_size, 2), torch.randn(hid_size), torch.randn(hid_size),
+                    torch.randn(hid_size)]
+    return tuple(tensors)
+
+
+def benchmark_swarm(num_peers, target_group_size, num_rounds, min_matchmaking_time, request_timeout, round_timeout,
+                    hid_size, num_layers, spawn_dtime):
+    dht_root = DHT(start=True)
+    initial_peers = dht_root.get_visible_maddrs()
+    num_groups = 2 ** int(round(math.log2(num_peers / target_group_size)))
+    nbits = int(round(math.log2(num_groups)))
+    peer_tensors = [sample_tensors(hid_size, num_layers) for _ in range(num_peers)]
+    to_close = [dht_root]
+    lock = threading.Lock()
+    stats = dict(ok=0, total=0)
+
+    def run_averager(index):
+        dht = DHT(initial_peers=initial_peers, start=True)
+        bits = bin(index % num_groups)[2:].rjust(nbits, "0") if nbits else ""
+        averager = DecentralizedAverager(peer_tensors[index], dht, prefix="my_tensor", initial_group_bits=bits,
+                                         compression=Float16Compression(), target_group_size=target_group_size,
+                                         min_matchmaking_time=min_matchmaking_time, request_timeout=request_timeout,
+                                         start=True)
+        with lock:
+            to_close.extend([averager, dht])
+        for step in range(num_rounds):
+            try:
+                success = averager.step(timeout=round_timeout) is not None
+            except Exception:
+                success = False
+            with lock:
+                stats["ok"] += int(success)
+                stats["total"] += 1
+            logger.info(f"Averager {index}: {'finished' if success else 'failed'} step #{step}")
+
+    threads = []
+    for i in range(num_peers):
+        thread = threading.Thread(target=run_averager, args=[i])
+        threads.append(thread)
+        thread.start()
+        time.sleep(spawn_dtime)
+    started = time.time()
+    for thread in threads:
+        thread.join()
+    elapsed = time.time() - started
+    print(json.dumps({"benchmark": "averaging_swarm", "success_rate": stats["ok"] / max(stats["total"], 1),
+                      "successful_steps": stats["ok"], "total_steps": stats["total"], "seconds": elapsed,
+                      "config": dict(num_peers=num_peers, target_group_size=target_group_size, num_rounds=num_rounds,
+                                     hid_size=hid_size, num_layers=num_layers)}), flush=True)
+    for item in reversed(to_close):
+        item.shutdown()
+
+
+def _time_rounds(endpoint, plan_args, rounds, warmup):
+    """Device time per round on the endpoint's stream (ms), with a fresh group id (epoch) every round."""
+    stream = torch.cuda.ExternalStream(endpoint.stream.value, device=endpoint.device)
+    times = []
+    for i in range(warmup + rounds):
+        plan = endpoint._prepare(group_id=f"bench-{plan_args['tag']}-{i}".encode(), stream=endpoint.stream,
+                                 **plan_args["kwargs"])
+        if plan_args["barrier"] is not None:
+            plan_args["barrier"]()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        endpoint._stage_send(plan, endpoint.stream)
+        endpoint._stage_reduce(plan, endpoint.stream)
+        endpoint._stage_apply(plan, endpoint.stream)
+        stop.record(stream)
+        status = endpoint._read_status(plan, endpoint.stream)
+        stop.synchronize()
+        if status.banned or status.failed:
+            raise RuntimeError(f"round failed: {status.banned} {status.failed}")
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    return sum(times) / len(times)
+
+
+def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_bytes):
+    import torch.distributed as dist
+    from hivemind_b200.averaging.allreduce import AveragingMode
+    from hivemind_b200.parallel.device_butterfly import DeviceEndpoint, run_group_emulated
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    results = []
+    for size_mb in sizes_mb:
+        numel = int(size_mb * 2 ** 20 / 4)
+        nccl_ms = None
+        if world > 1:
+            buf = torch.randn(numel, device=device)
+            for _ in range(warmup):
+                dist.all_reduce(buf)
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            start.record()
+            for _ in range(rounds):
+                dist.all_reduce(buf)
+            stop.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([start.elapsed_time(stop) / rounds], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            nccl_ms = float(t)
+            del buf
+        for codec_name in codecs:
+            codec = CODECS[codec_name]()
+            if world > 1:
+                tensor = torch.randn(numel, device=device)
+                endpoint = DeviceEndpoint([tensor], codec, [CompressionInfo.from_tensor(tensor, key=0)], part_size_bytes)
+                infos = [None] * world
+                dist.all_gather_object(infos, endpoint.describe())
+                n = world
+                kwargs = dict(my_index=rank, device_infos=infos, modes=[AveragingMode.NODE] * n,
+                              peer_fractions=[1.0 / n] * n, weights=[1.0] * n, alpha=1.0, sender_timeout=10.0,
+                              reducer_timeout=20.0)
+                ms = _time_rounds(endpoint, dict(tag=f"{size_mb}-{codec_name}", kwargs=kwargs, barrier=dist.barrier),
+                                  rounds, warmup)
+                t = torch.tensor([ms], device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t)
+                dist.barrier()
+                endpoint.close()
+            else:
+                n = emulate_ranks
+                endpoints = []
+                for r in range(n):
+                    tensor = torch.randn(numel, device=device)
+                    endpoints.append(DeviceEndpoint([tensor], codec, [CompressionInfo.from_tensor(tensor, key=0)],
+                                                    part_size_bytes))
+                for i in range(warmup):
+                    run_group_emulated(endpoints, weights=[1.0] * n, peer_fractions=[1.0 / n] * n,
+                                       group_id=f"w{size_mb}{codec_name}{i}".encode())
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                for i in range(rounds):
+                    run_group_emulated(endpoints, weights=[1.0] * n, peer_fractions=[1.0 / n] * n,
+                                       group_id=f"t{size_mb}{codec_name}{i}".encode())
+                stop.record()
+                torch.cuda.synchronize()
+                ms = start.elapsed_time(stop) / rounds / n  # n ranks share one GPU: per-rank share of the time
+                for e in endpoints:
+                    e.close()
+            nbytes = numel * 4
+            bus = 2 * (n - 1) / n * nbytes / (ms / 1e3) / 1e9
+            row = {"size_mb": size_mb, "codec": codec_name, "n_ranks": n, "ms_per_round": ms, "bus_gb_s": bus,
+                   "algo_gb_s": nbytes / (ms / 1e3) / 1e9}
+            if nccl_ms is not None:
+                row["nccl_fp32_ms"] = nccl_ms
+                row["nccl_fp32_bus_gb_s"] = 2 * (n - 1) / n * nbytes / (nccl_ms / 1e3) / 1e9
+            results.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+    if rank == 0:
+        print(json.dumps({"benchmark": "averaging_device_butterfly", "emulated": world == 1, "n_gpus": world,
+                          "rounds": rounds, "warmup": warmup, "part_size_bytes": part_size_bytes, "rows": results}),
+              flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--mode", choices=["swarm", "device"], default="swarm")
+    parser.add_argument("--num_peers", type=int, default=16)
+    parser.add_argument("--target_group_size", type=int, default=4)
+    parser.add_argument("--num_rounds", type=int, default=5)
+    parser.add_argument("--hid_size", type=int, default=256)
+    parser.add_argument("--num_layers", type=int, default=3)
+    parser.add_argument("--min_matchmaking_time", type=float, default=5)
+    parser.add_argument("--round_timeout", type=float, default=15)
+    parser.add_argument("--request_timeout", type=float, default=1)
+    parser.add_argument("--spawn_dtime", type=float, default=0.1)
+    parser.add_argument("--increase_file_limit", action="store_true")
+    parser.add_argument("--sizes-mb", type=float, nargs="+", default=[1, 16, 64, 256])
+    parser.add_argument("--codecs", nargs="+", default=["none", "float16", "uniform8"])
+    parser.add_argument("--rounds", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--emulate-ranks", type=int, default=4)
+    parser.add_argument("--part-size-bytes", type=int, default=2 ** 19)
+    args = parser.parse_args()
+    if args.increase_file_limit:
+        increase_file_limit()
+    if args.mode == "device":
+        benchmark_device(args.sizes_mb, args.codecs, args.rounds, args.warmup, args.emulate_ranks, args.part_size_bytes)
+    else:
+        benchmark_swarm(args.num_peers, args.target_group_size, args.num_rounds, args.min_matchmaking_time,
+                        args.request_timeout, args.round_timeout, args.hid_size, args.num_layers, args.spawn_dtime)

@@ -48,6 +48,7 @@ class _LayerNormFn(torch.autograd.Function):
         ctx.has_residual = r2 is not None
         ctx.shape = x.shape
         ctx.param_dtype = (gamma.dtype, beta.dtype)
+        ctx.params = (gamma, beta)
         return y.view(x.shape)
 
     @staticmethod
@@ -60,15 +61,26 @@ class _LayerNormFn(torch.autograd.Function):
             dy2 = dy2.to(zin.dtype)
         lib = _lib.load_library()
         dx = torch.empty_like(zin)
-        dgb = torch.zeros(2, h, dtype=torch.float32, device=zin.device)
+        gamma, beta = ctx.params
+        # the kernel adds its column sums with atomics: when fp32 .grad buffers exist they are the target
+        # (no zero-fill, cast and add per call); otherwise fresh buffers are returned to autograd
+        direct = all(p.grad is not None and p.grad.dtype == torch.float32 and p.grad.is_contiguous()
+                     and p.requires_grad for p in (gamma, beta))
+        if direct:
+            dgamma, dbeta = gamma.grad, beta.grad
+        else:
+            dgb = torch.zeros(2, h, dtype=torch.float32, device=zin.device)
+            dgamma, dbeta = dgb[0], dgb[1]
         with torch.cuda.device(zin.device):
             code = lib.hm_layernorm_bwd(_lib.ptr(dy2), _lib.ptr(zin), _lib.ptr(g32), _lib.ptr(mean), _lib.ptr(rstd),
-                                        _lib.ptr(dx), _lib.ptr(dgb[0]), _lib.ptr(dgb[1]), rows, h,
+                                        _lib.ptr(dx), _lib.ptr(dgamma), _lib.ptr(dbeta), rows, h,
                                         _lib.dtype_code(zin.dtype), _lib.sm_count(zin.device),
                                         _lib.stream_ptr(zin.device))
         _lib.check(code, "hm_layernorm_bwd")
         dx = dx.view(ctx.shape)
-        return dx, (dx if ctx.has_residual else None), dgb[0].to(ctx.param_dtype[0]), dgb[1].to(ctx.param_dtype[1]), None
+        if direct:
+            return dx, (dx if ctx.has_residual else None), None, None, None
+        return dx, (dx if ctx.has_residual else None), dgamma.to(ctx.param_dtype[0]), dbeta.to(ctx.param_dtype[1]), None
 
 
 def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
