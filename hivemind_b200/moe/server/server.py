@@ -205,7 +205,12 @@ class Server(threading.Thread):
 
 @contextmanager
 def background_server(*args, shutdown_timeout: float = 5, **kwargs):
-    """Context manager: ``Server.create(..., start=True)`` on entry (yields the server's ``PeerInfo``), shutdown on exit."""
+    """Context manager: ``Server.create(..., start=True)`` on entry (yields the server's ``PeerInfo``), shutdown on exit.
+
+    The server runs as threads of the calling process. Do not call its CUDA experts from a client layer's backward
+    pass in the same process: the client blocks autograd's worker thread of that GPU while it waits for the experts,
+    and the experts' own backward pass needs the same thread. Run the server as its own process in that case
+    (``python -m hivemind_b200.hivemind_cli.run_server``), as the reference always does."""
     server = Server.create(*args, start=True, **kwargs)
     try:
         yield PeerInfo(server.dht.peer_id, server.dht.get_visible_maddrs())

@@ -362,20 +362,67 @@ def test_grouped_ffn_matches_fp32_reference():
         assert g_gpu[2].abs().max() == 0  # the expert without rows gets no gradient
 
 
-@pytest.mark.gpu
-def test_server_with_experts_on_gpu():
-    from hivemind_b200.dht import DHT
-    from hivemind_b200.moe import RemoteMixtureOfExperts, background_server
+def _cli_server_roundtrip(tmp_path, device):
+    """An expert server (a child process started through the CLI) called from CUDA client tensors.
 
-    with background_server(expert_uids=[f"gpu.{i}" for i in range(4)], expert_cls="ffn", hidden_dim=256, device="cuda",
-                           num_handlers=2, optim_cls=lambda p: torch.optim.SGD(p, lr=0.01)) as info:
-        dht = DHT(initial_peers=info.addrs, start=True)
+    The server runs in its own process on purpose: a client layer blocks autograd's CUDA worker thread while it waits
+    for the experts' backward pass, and a server in the same process would need that very thread for its own backward.
+    """
+    import re
+    import signal
+    import subprocess
+    import sys
+    import time
+
+    from hivemind_b200.dht import DHT
+    from hivemind_b200.moe import RemoteMixtureOfExperts
+
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), PYTHONUNBUFFERED="1")
+    log_path = tmp_path / "server.log"
+    with open(log_path, "w") as log:
+        proc = subprocess.Popen([sys.executable, "-m", "hivemind_b200.hivemind_cli.run_server", "--expert_uids", "gpu.0",
+                                 "gpu.1", "gpu.2", "gpu.3", "--hidden_dim", "256", "--device", device, "--optimizer", "sgd",
+                                 "--num_handlers", "2", "--host_maddrs", "/ip4/127.0.0.1/tcp/0"],
+                                stderr=log, stdout=log, env=env, cwd=str(tmp_path))
+    try:
+        maddr, deadline = None, time.time() + 120
+        while time.time() < deadline and proc.poll() is None:
+            text = log_path.read_text()
+            found = re.search(r"Running DHT node on \['(/ip4/127\.0\.0\.1/tcp/\d+/p2p/\S+?)'", text)
+            if found and " Started" in text:
+                maddr = found.group(1)
+                break
+            time.sleep(0.5)
+        assert maddr is not None, log_path.read_text()[-2000:]
+        dht = DHT(initial_peers=[maddr], start=True)
         try:
-            moe = RemoteMixtureOfExperts(in_features=256, grid_size=(4,), dht=dht, uid_prefix="gpu.", k_best=2).cuda()
-            x = torch.randn(32, 256, device="cuda", requires_grad=True)
-            out = moe(x)
-            assert out.shape == x.shape and out.is_cuda and out.isfinite().all()
+            moe = RemoteMixtureOfExperts(in_features=256, grid_size=(4,), dht=dht, uid_prefix="gpu.", k_best=2,
+                                         forward_timeout=60, backward_timeout=60).to(device)
+            x = torch.randn(32, 256, device=device, requires_grad=True)
+            out = None
+            for attempt in range(20):  # declarations reach the DHT a moment after the server reports "Started"
+                try:
+                    out = moe(x)
+                    break
+                except RuntimeError:
+                    time.sleep(0.5)
+            assert out is not None and out.shape == x.shape and out.device.type == device and out.isfinite().all()
             out.pow(2).mean().backward()
             assert x.grad is not None and x.grad.isfinite().all() and moe.proj.weight.grad.norm() > 0
         finally:
             dht.shutdown()
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        try:
+            proc.wait(30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+
+
+def test_cli_server_roundtrip_cpu(tmp_path):
+    _cli_server_roundtrip(tmp_path, "cpu")
+
+
+@pytest.mark.gpu
+def test_server_with_experts_on_gpu(tmp_path):
+    _cli_server_roundtrip(tmp_path, "cuda")
