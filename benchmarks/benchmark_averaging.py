@@ -110,8 +110,8 @@ def _time_rounds(endpoint, plan_args, rounds, warmup):
         stop.record(stream)
         status = endpoint._read_status(plan, endpoint.stream)
         stop.synchronize()
-        if status.banned or status.failed:
-            raise RuntimeError(f"round failed: {status.banned} {status.failed}")
+        if status.banned_senders or status.failed_reducers:
+            raise RuntimeError(f"round failed: {status.banned_senders} {status.failed_reducers}")
         if i >= warmup:
             times.append(start.elapsed_time(stop))
     return sum(times) / len(times)

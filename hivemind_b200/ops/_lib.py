@@ -84,7 +84,12 @@ def check(code: int, what: str, kernels: int = 1) -> None:
     _launch_count += kernels
     if code != 0:
         if code > 0:
-            name = torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), "cudaGetErrorString") else ""
+            name = ""
+            try:
+                rt = torch.cuda.cudart()
+                name = rt.cudaGetErrorString(rt.cudaError(code))
+            except Exception:
+                pass
             raise RuntimeError(f"{what}: CUDA error {code} {name}")
         raise RuntimeError(f"{what}: unsupported arguments (code {code})")
 

@@ -204,6 +204,136 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ zin, const float* 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Split LayerNorm backward (the default path). Keeping the per-column sums of dgamma / dbeta in the registers of a
+// warp-per-row kernel costs ~64 registers per thread and leaves only 12 warps per SM, too few to cover HBM latency.
+// Here the row pass writes dx only, and the column sums are taken by a second, column-strip pass that re-reads dy
+// and the normalised input with 16-byte loads (5 tensor passes over HBM instead of 3, each near the copy rate).
+template <typename T, int NV>
+__global__ void __launch_bounds__(32 * HM_LN_WARPS)
+ln_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ zin, const float* __restrict__ gamma,
+                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx, int rows,
+                 int H) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * HM_LN_WARPS + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * HM_LN_WARPS;
+  const float inv_h = 1.f / (float)H;
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const size_t base = (size_t)row * H;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[NV][8], gd[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        ld8<T>(dy + base + col, gd[j]);
+        ld8<T>(zin + base + col, xh[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        float g[8];
+        ld8<float>(gamma + col, g);  // 4 KB, stays in L1
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          xh[j][k] = (xh[j][k] - mean) * rstd;
+          gd[j][k] *= g[k];
+          s1 += gd[j][k];
+          s2 = fmaf(gd[j][k], xh[j][k], s2);
+        }
+      }
+    }
+    s1 = hm_warp_sum(s1) * inv_h;
+    s2 = hm_warp_sum(s2) * inv_h;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = (j * 32 + lane) * 8;
+      if (col < H) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = rstd * (gd[j][k] - s1 - xh[j][k] * s2);
+        st8<T>(dx + base + col, o);
+      }
+    }
+  }
+}
+
+// Column-strip pass: block = 32 column groups (8 columns each, one 16-byte load per row) x 8 row lanes; blockIdx.y
+// selects a strip of rows. MODE 0: dgamma += sum dy * xhat, dbeta += sum dy (LayerNorm). MODE 1: dx = dy * gelu'(x),
+// dbias += sum dx (GELU backward; also writes dx).
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+colstrip_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean_in,
+                const float* __restrict__ rstd_in, T* __restrict__ dx, float* __restrict__ out_a,
+                float* __restrict__ out_b, long long rows, int H, int rows_per_strip) {
+  __shared__ float red[2][8][32 * 8 + 8];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + cx) * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_strip;
+  const long long r1 = r0 + rows_per_strip < rows ? r0 + rows_per_strip : rows;
+  float a[8], b[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = b[k] = 0.f;
+  if (col < H) {
+    for (long long r = r0 + ry; r < r1; r += 8) {
+      const size_t idx = (size_t)r * H + col;
+      float d[8], v[8];
+      ld8<T>(dy + idx, d);
+      ld8<T>(x + idx, v);
+      if (MODE == 0) {
+        const float mean = mean_in[r], rstd = rstd_in[r];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          a[k] = fmaf(d[k], (v[k] - mean) * rstd, a[k]);
+          b[k] += d[k];
+        }
+      } else {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          o[k] = d[k] * hm_gelu_tanh_grad(v[k]);
+          a[k] += o[k];
+        }
+        st8<T>(dx + idx, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    red[0][ry][cx * 8 + k] = a[k];
+    if (MODE == 0) red[1][ry][cx * 8 + k] = b[k];
+  }
+  __syncthreads();
+  // 256 threads, 256 columns of this block: one column sum each
+  const int c = threadIdx.x;
+  const int gcol = blockIdx.x * 256 + c;
+  if (gcol < H) {
+    float ta = 0.f, tb = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      ta += red[0][w][c];
+      if (MODE == 0) tb += red[1][w][c];
+    }
+    if (out_a) atomicAdd(out_a + gcol, ta);
+    if (MODE == 0 && out_b) atomicAdd(out_b + gcol, tb);
+  }
+}
+
+template <typename T>
+static int colstrip_grid(long long rows, int H, int sms, dim3* grid, int* rows_per_strip) {
+  const int gx = (H + 255) / 256;
+  long long gy = ((long long)sms * 4 + gx - 1) / gx;
+  if (gy > (rows + 7) / 8) gy = (rows + 7) / 8;
+  if (gy < 1) gy = 1;
+  *rows_per_strip = (int)((rows + gy - 1) / gy);
+  gy = (rows + *rows_per_strip - 1) / *rows_per_strip;
+  *grid = dim3(gx, (unsigned)gy);
+  return 0;
+}
+
 // Grouped backward: rows come in 128-row tiles and tile_group[tile] names the parameter set (group) of the tile
 // (-1: skip). A CTA walks whole tiles, keeps the column sums of one tile in registers and adds them to that group's
 // dgamma / dbeta (and dxsum = column sums of dx, the bias gradient of the layer that produced the input) when the
@@ -400,11 +530,19 @@ template <typename T, int NV>
 static int ln_bwd_launch(const void* dy, const void* zin, const void* gamma, const void* mean, const void* rstd,
                          void* dx, void* dgamma, void* dbeta, int rows, int H, int sms, cudaStream_t stream) {
   int blocks = (rows + HM_LN_WARPS - 1) / HM_LN_WARPS;
-  const int cap = sms * 4;
+  const int cap = sms * 8;
   if (blocks > cap) blocks = cap;
-  ln_bwd_kernel<T, NV><<<blocks, 32 * HM_LN_WARPS, 0, stream>>>((const T*)dy, (const T*)zin, (const float*)gamma,
-                                                               (const float*)mean, (const float*)rstd, (T*)dx,
-                                                               (float*)dgamma, (float*)dbeta, rows, H);
+  ln_bwd_dx_kernel<T, NV><<<blocks, 32 * HM_LN_WARPS, 0, stream>>>((const T*)dy, (const T*)zin, (const float*)gamma,
+                                                                  (const float*)mean, (const float*)rstd, (T*)dx, rows,
+                                                                  H);
+  if (dgamma != nullptr || dbeta != nullptr) {
+    dim3 grid;
+    int rows_per_strip;
+    colstrip_grid<T>(rows, H, sms, &grid, &rows_per_strip);
+    colstrip_kernel<T, 0><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)zin, (const float*)mean,
+                                                    (const float*)rstd, nullptr, (float*)dgamma, (float*)dbeta, rows,
+                                                    H, rows_per_strip);
+  }
   return (int)cudaGetLastError();
 }
 
@@ -460,6 +598,24 @@ HM_API int hm_bias_gelu_fwd(const void* x, const void* bias, void* y, long long 
 HM_API int hm_bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx, void* dbias, long long rows,
                             int H, int dtype, int sms, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (bias == nullptr && H % 8 == 0) {
+    // x already holds the pre-activation (bias added by the producing GEMM): vectorised column-strip kernel
+    dim3 grid;
+    int rows_per_strip;
+    if (dtype == HM_BF16) {
+      colstrip_grid<__nv_bfloat16>(rows, H, sms, &grid, &rows_per_strip);
+      colstrip_kernel<__nv_bfloat16, 1><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                 nullptr, nullptr, (__nv_bfloat16*)dx, (float*)dbias,
+                                                                 nullptr, rows, H, rows_per_strip);
+    } else if (dtype == HM_F32) {
+      colstrip_grid<float>(rows, H, sms, &grid, &rows_per_strip);
+      colstrip_kernel<float, 1><<<grid, 256, 0, stream>>>((const float*)dy, (const float*)x, nullptr, nullptr,
+                                                         (float*)dx, (float*)dbias, nullptr, rows, H, rows_per_strip);
+    } else {
+      return -2;
+    }
+    return (int)cudaGetLastError();
+  }
   const int gx = (H + 255) / 256;
   int gy = (sms * 8 + gx - 1) / gx;
   if (gy > rows) gy = (int)rows;

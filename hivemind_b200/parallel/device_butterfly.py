@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import time
 import socket
 import threading
 import zlib
@@ -36,6 +37,7 @@ from hivemind_b200.utils.logging import get_logger
 
 logger = get_logger(__name__)
 
+EXIT_GRACE_SECONDS = 2.0  # how long after a round peers may still read this arena (see DeviceEndpoint.close)
 MAX_PEERS = 16
 ALIGN = 16  # elements: tensor starts and part boundaries are multiples of this, so every access is 16-byte aligned
 PH_STATS, PH_BORDERS, PH_ENCODE, PH_PUBLISH, PH_REDUCE, PH_APPLY = range(6)
@@ -197,6 +199,10 @@ class DeviceEndpoint:
         with torch.cuda.device(self.device):
             _lib.check(self.lib.hm_stream_create(ctypes.byref(stream)), "hm_stream_create", 0)
         self.stream = stream
+        # torch-side handle of the same stream: every tensor that the round's kernels read is created under it, so
+        # that its initialisation is ordered before the kernels (the round's stream does not synchronise with the
+        # default stream, where unrelated training work may be queued)
+        self._torch_stream = torch.cuda.ExternalStream(stream.value, device=self.device)
         self._mappings: Dict[Tuple[int, bytes], int] = {}
         self._plans: Dict[Tuple, _Plan] = {}
         self._host_status = (ctypes.c_ulonglong * 4)()
@@ -243,6 +249,11 @@ class DeviceEndpoint:
         if self._closed:
             return
         self._closed = True
+        # groupmates pull their deltas out of this arena after this GPU has finished its own part of a round:
+        # do not let the process go (and the memory with it) right after a round
+        since_round = time.monotonic() - getattr(self, "_last_round_end", -1e9)
+        if since_round < EXIT_GRACE_SECONDS:
+            time.sleep(EXIT_GRACE_SECONDS - since_round)
         with torch.cuda.device(self.device):
             self.lib.hm_stream_sync(self.stream)
             for ptr in self._mappings.values():
@@ -257,6 +268,15 @@ class DeviceEndpoint:
         plan = self._plans.get(key)
         if plan is not None:
             return plan
+        with torch.cuda.stream(self._torch_stream):
+            plan = self._build_plan(n_peers, my_index, peer_fractions, sends)
+            self._torch_stream.synchronize()  # once per layout: tables and zeroed scratch are in place before any launch
+        if len(self._plans) > 8:
+            self._plans.pop(next(iter(self._plans)))
+        self._plans[key] = plan
+        return plan
+
+    def _build_plan(self, n_peers: int, my_index: int, peer_fractions: Sequence[float], sends: Sequence[bool]) -> _Plan:
         lib = self.lib
         chunk = lib.hm_bf_chunk()
         specs = compute_part_layout(self.numels, [4] * len(self.numels), self.ratios, peer_fractions,
@@ -314,12 +334,8 @@ class DeviceEndpoint:
             scratch[name] = blob[cursor:cursor + nbytes]
             cursor += (nbytes + 255) // 256 * 256
         group_dev = torch.zeros(ctypes.sizeof(_HbGroup), dtype=torch.uint8, device=self.device)
-        plan = _Plan(n_parts, max_local, delta_stride, parts_dev, items, counts, scratch, blob, group_dev, enc_cursor,
+        return _Plan(n_parts, max_local, delta_stride, parts_dev, items, counts, scratch, blob, group_dev, enc_cursor,
                      needed_delta)
-        if len(self._plans) > 8:
-            self._plans.pop(next(iter(self._plans)))
-        self._plans[key] = plan
-        return plan
 
     def _prepare(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weights, alpha,
                  sender_timeout, reducer_timeout, stream) -> _Plan:
@@ -403,7 +419,9 @@ class DeviceEndpoint:
         self._stage_send(plan, self.stream)
         self._stage_reduce(plan, self.stream)
         self._stage_apply(plan, self.stream)
-        return self._read_status(plan, self.stream)
+        status = self._read_status(plan, self.stream)
+        self._last_round_end = time.monotonic()
+        return status
 
 
 def run_group_emulated(endpoints: Sequence[DeviceEndpoint], *, weights: Sequence[float],

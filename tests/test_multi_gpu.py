@@ -41,18 +41,12 @@ torch.cuda.synchronize()
 assert len(gathered) == world
 with averager.get_tensors() as out:
     result = [t.cpu() for t in out]
-# every rank can rebuild everybody's input from the seeds
-refs = []
-for k in range(2):
-    acc, den = 0, 0
-    for r in range(world):
-        g = torch.Generator(device="cpu")
-        torch.manual_seed(100 + r)
-        with torch.cuda.device(r):
-            pass
-        den += 1.0 + r
-    refs.append(None)
-torch.save(dict(original=[t.cpu() for t in original], result=result, weight=weight), os.environ["OUT_PREFIX"] + f"{rank}.pt")
+torch.save(dict(original=[t.cpu() for t in original], result=result, weight=weight), os.environ["OUT_PREFIX"] + f"{rank}.pt.tmp")
+os.rename(os.environ["OUT_PREFIX"] + f"{rank}.pt.tmp", os.environ["OUT_PREFIX"] + f"{rank}.pt")
+# groupmates may still be pulling deltas out of this process's arena: leave (and free GPU memory) only when all are done
+deadline = time.time() + 120
+while time.time() < deadline and not all(os.path.exists(os.environ["OUT_PREFIX"] + f"{r}.pt") for r in range(world)):
+    time.sleep(0.05)
 averager.shutdown(); dht.shutdown()
 print("child done", rank, flush=True)
 '''
