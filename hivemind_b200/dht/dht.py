@@ -1,7 +1,7 @@
 """``DHT``: the user-facing handle of a DHT node that runs on its own event-loop thread.
 
 The reference forks a process for this (hivemind/dht/dht.py:22-337) and talks to it through a pipe and MPFutures.
-A forked process cannot share a CUDA context, so here the node lives on a daemon thread with a private uvloop;
+A forked process cannot share a CUDA context, so here the node lives on a daemon thread with a private event loop;
 the public methods (``get``, ``store``, ``run_coroutine``, ``add_validators``, ``peer_id``, ``client_mode``,
 ``get_visible_maddrs``, ``replicate_p2p``, ``shutdown``) keep their signatures, ``return_future=True`` returns an
 ``MPFuture``, and ``run_coroutine(coro)`` still runs ``coro(dht, node)`` inside the DHT's own loop.

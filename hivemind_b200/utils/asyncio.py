@@ -21,8 +21,15 @@ logger = get_logger(__name__)
 
 
 def new_event_loop() -> asyncio.AbstractEventLoop:
-    """A fresh event loop (uvloop when installed) that is not yet bound to any thread."""
-    if uvloop is not None and os.getenv("HIVEMIND_DISABLE_UVLOOP", "0") != "1":
+    """
+    A fresh event loop that is not yet bound to any thread.
+
+    Components are threads of one process here, each with its own loop. uvloop finalises its handles in whichever
+    thread happens to run the garbage collector, which is not safe while the handle's own loop is running in
+    another thread, so the default is the standard library's loop. ``HIVEMIND_B200_UVLOOP=1`` opts into uvloop
+    (about 20 % more RPC throughput) for processes that accept that risk, e.g. benchmark clients.
+    """
+    if uvloop is not None and os.getenv("HIVEMIND_B200_UVLOOP", "0") == "1":
         return uvloop.new_event_loop()
     return asyncio.new_event_loop()
 
