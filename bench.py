@@ -113,9 +113,13 @@ def main() -> None:
     assert world == args.gpus, f"launched with WORLD_SIZE={world} but --gpus {args.gpus}"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    host_group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+        # barriers and the final reductions of the timing go over a host-side group: a NCCL barrier would put a
+        # kernel that waits for every rank into the stream that the background averaging rounds synchronise with
+        host_group = dist.new_group(backend="gloo")
     warmup = max(3, args.warmup)
 
     torch.manual_seed(1234)  # identical initial weights on every peer
@@ -131,7 +135,7 @@ def main() -> None:
         maddrs = None
     if world > 1:
         box = [maddrs]
-        dist.broadcast_object_list(box, src=0)
+        dist.broadcast_object_list(box, src=0, group=host_group)
         maddrs = box[0]
         if rank != 0:
             dht = hivemind.DHT(initial_peers=maddrs, start=True)
@@ -167,9 +171,9 @@ def main() -> None:
         return float(loss.item()) if end_to_end else loss
 
     def barrier():
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=host_group)
 
     def run_epochs(num_epochs: int, end_to_end: bool):
         """Run micro-steps until this peer has finished ``num_epochs`` more collaborative steps."""
@@ -187,11 +191,11 @@ def main() -> None:
         steps, last = run_epochs(num_epochs, end_to_end)
         end.record()
         barrier()
-        ms = torch.tensor([start.elapsed_time(end)], device=device, dtype=torch.float64)
-        samples = torch.tensor([float(steps * args.micro_batch)], device=device, dtype=torch.float64)
+        ms = torch.tensor([start.elapsed_time(end)], dtype=torch.float64)
+        samples = torch.tensor([float(steps * args.micro_batch)], dtype=torch.float64)
         if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            dist.all_reduce(samples, op=dist.ReduceOp.SUM)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=host_group)
+            dist.all_reduce(samples, op=dist.ReduceOp.SUM, group=host_group)
         return float(ms.item()), float(samples.item()), _lib.launch_count() - launches0, last
 
     run_epochs(warmup, end_to_end=False)

@@ -412,7 +412,11 @@ class DeviceEndpoint:
     def run_round(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weights, alpha: float,
                   sender_timeout: Optional[float], reducer_timeout: Optional[float]) -> RoundStatus:
         """Run one all-reduce round with the mapped groupmates; blocks the calling thread until this GPU is done."""
-        torch.cuda.current_stream(self.device).synchronize()  # the caller's writes to the tensors must have landed
+        # the caller's writes to the tensors must land before the round reads them: order the round's stream after the
+        # caller's stream on the device (no host wait: that stream may hold work that depends on other ranks)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        self._torch_stream.wait_event(ready)
         plan = self._prepare(group_id=group_id, my_index=my_index, device_infos=device_infos, modes=modes,
                              peer_fractions=peer_fractions, weights=weights, alpha=alpha,
                              sender_timeout=sender_timeout, reducer_timeout=reducer_timeout, stream=self.stream)
