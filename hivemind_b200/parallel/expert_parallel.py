@@ -78,12 +78,16 @@ class DeviceMixtureOfExperts(nn.Module):
       connection; ``forward`` then returns ``(output, balancing_loss)``
     :param group: process group over which experts are sharded (None = all experts on this device)
     :param compute_dtype: dtype of the rows sent to experts (bf16 on CUDA by default)
+    :param exchange: how rows reach experts on other ranks: ``"all_to_all"`` (NCCL / gloo collectives) or ``"peer"``
+      (kernels that pull rows straight out of the other GPUs' memory over NVLink; CUDA only, one box)
+    :param max_tokens: for ``exchange="peer"``: the most tokens one forward pass will carry (sizes the arenas)
     """
 
     def __init__(self, *, in_features: int, grid_size: Sequence[int], k_best: int, expert_cls: str = "ffn",
                  k_min: int = 0, check_k_min: bool = False, switch: bool = False, jitter_eps: float = 1e-2,
                  grid_dropout: float = 1.0, utilization_alpha: float = 0.9, group: Optional[dist.ProcessGroup] = None,
-                 compute_dtype: Optional[torch.dtype] = None, train_experts: bool = True):
+                 compute_dtype: Optional[torch.dtype] = None, train_experts: bool = True,
+                 exchange: str = "all_to_all", max_tokens: int = 0, exchange_timeout: float = 10.0):
         super().__init__()
         assert 1 <= k_best <= moe_ops.MAX_K and 1 <= len(grid_size) <= 3
         self.grid_size = tuple(int(g) for g in grid_size)
@@ -101,6 +105,9 @@ class DeviceMixtureOfExperts(nn.Module):
         self.first_expert = self.rank * self.experts_per_rank
         self.compute_dtype = compute_dtype
         self.train_experts = train_experts
+        assert exchange in ("all_to_all", "peer")
+        self.exchange_kind, self.max_tokens, self.exchange_timeout = exchange, max_tokens, exchange_timeout
+        self._exchange = None  # PeerExpertExchange, created at the first CUDA forward
         self.proj = nn.Linear(in_features, sum(self.grid_size))
         # "ffn" experts share one set of stacked parameters and run as grouped GEMMs; any other registered class
         # runs expert by expert over its contiguous rows
@@ -146,18 +153,46 @@ class DeviceMixtureOfExperts(nn.Module):
         rows = tokens.to(dtype)
         align = moe_ops.TILE_ROWS if (self.grouped and self.world == 1) else 1
         routed = moe_ops.dispatch(rows, idx, self.num_experts, align=align)
-        answers = self._run_experts(routed)
+        answers, row_ok = self._run_experts(routed)
+        keep = None
+        if row_ok is not None:  # rows whose expert host did not answer in time count as failed experts
+            keep = row_ok[routed.pos.clamp(min=0).long()] & (routed.pos >= 0)
         residual = rows if self.switch else None
-        mixed = moe_ops.combine(answers, routed.pos, gate, "prob" if self.switch else "softmax", residual=residual)
+        mixed = moe_ops.combine(answers, routed.pos, gate, "prob" if self.switch else "softmax", keep=keep,
+                                residual=residual)
         out = mixed.to(x.dtype).view(shape)
         if not self.switch:
             return out
         return out, self._balancing_loss(scores, idx)
 
     def _run_experts(self, routed: moe_ops.Dispatch) -> torch.Tensor:
+        if self.world > 1 and self.exchange_kind == "peer" and routed.packed.is_cuda:
+            from hivemind_b200.parallel.expert_exchange import PeerExchangeExperts
+
+            exchange = self._get_exchange(routed.packed)
+            answers, ok = PeerExchangeExperts.apply(routed.packed, routed.offsets, exchange,
+                                                    lambda rows, gathered: self._run_local(gathered))
+            return answers, ok.bool()
         if self.world > 1:
-            return _AllToAllExperts.apply(routed.packed, routed.counts, self)
-        return self._run_local(routed)
+            return _AllToAllExperts.apply(routed.packed, routed.counts, self), None
+        return self._run_local(routed), None
+
+    def _get_exchange(self, packed: torch.Tensor):
+        if self._exchange is None:
+            from hivemind_b200.parallel.expert_exchange import PeerExpertExchange
+
+            assert self.max_tokens > 0, 'exchange="peer" needs max_tokens (the largest batch of tokens per forward)'
+
+            def all_descriptors(mine):
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, mine, group=self.group)
+                return gathered
+
+            self._exchange = PeerExpertExchange(
+                rank=self.rank, world=self.world, experts_per_rank=self.experts_per_rank, hidden=packed.shape[1],
+                max_rows=self.max_tokens * self.k_best, device=packed.device, dtype=packed.dtype,
+                exchange_descriptors=all_descriptors, timeout=self.exchange_timeout)
+        return self._exchange
 
     def _run_local(self, routed: moe_ops.Dispatch) -> torch.Tensor:
         """Apply this rank's experts to the rows that a dispatch over ``len(self.experts)`` experts assigned them."""

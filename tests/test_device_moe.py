@@ -426,3 +426,66 @@ def test_cli_server_roundtrip_cpu(tmp_path):
 @pytest.mark.gpu
 def test_server_with_experts_on_gpu(tmp_path):
     _cli_server_roundtrip(tmp_path, "cuda")
+
+
+@pytest.mark.gpu
+def test_peer_exchange_stages_emulated_on_one_gpu():
+    """Three ranks of the peer-memory exchange on one GPU, stage by stage (no launch ever waits for a later one)."""
+    from hivemind_b200.parallel.expert_exchange import BACKWARD, FORWARD, PeerExpertExchange
+
+    torch.manual_seed(8)
+    world, per_rank, hidden, k = 3, 2, 128, 2
+    experts = world * per_rank
+    dev = torch.device("cuda", 0)
+    tokens = [50, 0, 300]  # one client sends nothing
+    exchanges = [PeerExpertExchange(rank=r, world=world, experts_per_rank=per_rank, hidden=hidden, max_rows=300 * k,
+                                    device=dev, timeout=1.0) for r in range(world)]
+    descriptors = [e.descriptor for e in exchanges]
+    for e in exchanges:
+        e.connect(descriptors)
+    xs = [torch.randn(t, hidden, device=dev, dtype=torch.bfloat16) for t in tokens]
+    idxs = [torch.randint(-1, experts, (t, k), dtype=torch.int32, device=dev) for t in tokens]
+    routed = [moe_ops.dispatch(x, idx, experts) for x, idx in zip(xs, idxs)]
+    for phase in (FORWARD, BACKWARD):
+        for r, e in enumerate(exchanges):
+            e.client_publish(routed[r].packed * (1 if phase == FORWARD else -1), routed[r].offsets if phase == FORWARD else None,
+                             phase, epoch=1)
+        torch.cuda.synchronize()
+        gathered = [e.server_gather(phase, epoch=1) for e in exchanges]
+        torch.cuda.synchronize()
+        for d, g in enumerate(gathered):
+            assert int(g.status[0]) == 0
+            offs = g.offsets.tolist()
+            assert all(o % 128 == 0 for o in offs)
+            for el in range(per_rank):
+                ge = d * per_rank + el
+                want = torch.cat([(routed[s].packed * (1 if phase == FORWARD else -1))[int(routed[s].offsets[ge]):int(routed[s].offsets[ge + 1])]
+                                  for s in range(world)])
+                got = g.packed[offs[el]:offs[el] + want.shape[0]]
+                assert torch.equal(got, want), (phase, d, el)
+                assert (g.packed[offs[el] + want.shape[0]:offs[el + 1]] == 0).all()
+                assert (g.tile_group[offs[el] // 128:offs[el + 1] // 128] == el).all()
+            assert (g.tile_group[offs[-1] // 128:] == -1).all()
+        # the "experts": scale every row by (1 + global expert id)
+        for d, (e, g) in enumerate(zip(exchanges, gathered)):
+            offs = g.offsets.tolist()
+            answers = torch.zeros_like(g.packed)
+            for el in range(per_rank):
+                answers[offs[el]:offs[el + 1]] = g.packed[offs[el]:offs[el + 1]] * (1 + d * per_rank + el)
+            e.server_publish(answers, phase, epoch=1)
+        torch.cuda.synchronize()
+        for r, e in enumerate(exchanges):
+            total = int(routed[r].offsets[-1])
+            out, ok = e.client_pull(routed[r].offsets, routed[r].packed.shape[0], phase, epoch=1)
+            torch.cuda.synchronize()
+            scale = 1 + torch.repeat_interleave(torch.arange(experts, device=dev), routed[r].counts.long())
+            want = (routed[r].packed[:total] * (1 if phase == FORWARD else -1)).float() * scale[:, None]
+            assert torch.allclose(out[:total].float(), want, rtol=1e-2, atol=1e-2) and ok[:total].all()
+    # a server that never answers: the client gives up after the timeout and reports the rows as failed
+    exchanges[0].client_publish(routed[0].packed, routed[0].offsets, FORWARD, epoch=2)
+    out, ok = exchanges[0].client_pull(routed[0].offsets, routed[0].packed.shape[0], FORWARD, epoch=2)
+    torch.cuda.synchronize()
+    total = int(routed[0].offsets[-1])
+    assert not ok[:total].any() and (out[:total] == 0).all()
+    for e in exchanges:
+        e.close()
