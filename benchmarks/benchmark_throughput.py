@@ -132,7 +132,7 @@ def benchmark_server(num_experts=16, num_handlers=None, num_clients=128, num_bat
 
 
 def benchmark_device(grid=(8, 8), k_best=4, tokens=4096, hid_dim=1024, steps=20, warmup=5, switch=False,
-                     backprop=True):
+                     backprop=True, exchange="all_to_all"):
     import torch.distributed as dist
     from hivemind_b200.ops import _lib
     from hivemind_b200.parallel.expert_parallel import DeviceMixtureOfExperts
@@ -146,7 +146,7 @@ def benchmark_device(grid=(8, 8), k_best=4, tokens=4096, hid_dim=1024, steps=20,
         group = dist.group.WORLD
     torch.manual_seed(1234 + local_rank)
     layer = DeviceMixtureOfExperts(in_features=hid_dim, grid_size=grid, k_best=1 if switch else k_best, switch=switch,
-                                   group=group).cuda()
+                                   group=group, exchange=exchange, max_tokens=tokens).cuda()
     optimizer = torch.optim.Adam(layer.parameters(), lr=1e-4, fused=True)
     x = torch.randn(tokens, hid_dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
 
@@ -185,7 +185,7 @@ def benchmark_device(grid=(8, 8), k_best=4, tokens=4096, hid_dim=1024, steps=20,
                           "own_kernel_launches": _lib.launch_count() - launches_before,
                           "config": dict(grid=list(grid), k_best=layer.k_best, tokens_per_gpu=tokens, hid_dim=hid_dim,
                                          switch=switch, steps=steps, warmup=warmup, dtype="bf16",
-                                         exchange="all_to_all" if world > 1 else "local")}), flush=True)
+                                         exchange=exchange if world > 1 else "local")}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -202,9 +202,12 @@ if __name__ == "__main__":
     parser.add_argument("--tokens", type=int, default=4096)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--device", default=None)
+    parser.add_argument("--exchange", default="all_to_all", choices=["all_to_all", "peer"],
+                        help="device mode with several GPUs: NCCL all-to-all or our kernels over peer-mapped memory")
     args = parser.parse_args()
     if args.mode == "device":
-        benchmark_device(tokens=args.tokens, steps=args.steps, switch=args.switch, backprop=not args.no_backprop)
+        benchmark_device(tokens=args.tokens, steps=args.steps, switch=args.switch, backprop=not args.no_backprop,
+                         exchange=args.exchange)
     else:
         increase_file_limit()
         common = dict(num_batches_per_client=args.num_batches_per_client, device=args.device,
