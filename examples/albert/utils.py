@@ -11,22 +11,29 @@ from hivemind_b200.dht.validation import RecordValidatorBase
 
 
 class LocalMetrics(BaseModel):
-    step: conint(ge=0, strict=True)
+    """One trainer's progress report, published under ``{run_id}_metrics`` with the trainer's public key as subkey."""
+    step: conint(ge=0, strict=True)  # collaborative step (epoch) this report belongs to
     samples_per_second: confloat(ge=0.0, strict=True)
     samples_accumulated: conint(ge=0, strict=True)
-    loss: StrictFloat
-    mini_steps: conint(ge=0, strict=True)
+    loss: StrictFloat  # mean loss over mini_steps
+    mini_steps: conint(ge=0, strict=True)  # forward/backward passes since the previous report
 
 
-class MetricSchema(BaseModel):
-    metrics: Dict[BytesWithPublicKey, LocalMetrics]
+def metrics_schema():
+    """The pydantic model that validates the whole ``metrics`` dictionary (field name = DHT key without prefix)."""
+
+    class MetricSchema(BaseModel):
+        metrics: Dict[BytesWithPublicKey, LocalMetrics]
+
+    return MetricSchema
 
 
 def make_validators(run_id: str) -> Tuple[List[RecordValidatorBase], bytes]:
-    """Records under ``{run_id}_metrics`` must match the schema and be signed by the peer whose key is the subkey."""
-    signature_validator = RSASignatureValidator()
-    validators = [SchemaValidator(MetricSchema, prefix=run_id), signature_validator]
-    return validators, signature_validator.local_public_key
+    """Validators for a trainer's DHT: schema check of the metrics key plus RSA ownership of every subkey.
+    Returns them together with this process's public key (the subkey to publish under)."""
+    ownership = RSASignatureValidator()
+    schema = SchemaValidator(metrics_schema(), prefix=run_id)
+    return [schema, ownership], ownership.local_public_key
 
 
 COMPRESSIONS = {

@@ -1,48 +1,61 @@
-"""Dropout whose mask is an explicit input, so that backward can replay it (reference: layers/dropout.py:7-53)."""
-import torch.autograd
-from torch import nn as nn
+"""``det_dropout``: an expert with dropout whose keep-mask is an INPUT of the expert.
+
+A server recomputes the forward pass during backward (see ``ModuleBackend.backward``), so a random mask drawn inside
+the expert would differ between the two passes. The client draws the mask and sends it along; the same behaviour as
+the reference's deterministic dropout expert (hivemind/moe/server/layers/dropout.py:7-53).
+"""
+import torch
+from torch import nn
 
 from hivemind_b200.moe.server.layers.custom_experts import register_expert_class
 
 
-class DeterministicDropoutFunction(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, keep_prob, mask):
-        ctx.keep_prob = keep_prob
-        ctx.save_for_backward(mask)
-        return x * mask / keep_prob
+class _MaskedScale(torch.autograd.Function):
+    """y = x * mask / keep_prob, with the mask treated as a constant."""
 
     @staticmethod
-    def backward(ctx, grad_output):
-        return ctx.saved_tensors[0] * grad_output / ctx.keep_prob, None, None
+    def forward(ctx, x: torch.Tensor, mask: torch.Tensor, inverse_keep: float) -> torch.Tensor:
+        scale = mask.to(x.dtype) * inverse_keep
+        ctx.save_for_backward(scale)
+        return x * scale
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        (scale,) = ctx.saved_tensors
+        return grad_output * scale, None, None
 
 
 class DeterministicDropout(nn.Module):
-    """Custom dropout module that takes the mask as a second input (the server re-runs forward during backward)."""
+    """Dropout with a caller-supplied keep-mask (1 = keep); identity in eval mode."""
 
-    def __init__(self, drop_prob):
+    def __init__(self, drop_prob: float):
         super().__init__()
-        self.keep_prob = 1 - drop_prob
+        assert 0.0 <= drop_prob < 1.0
+        self.keep_prob = 1.0 - drop_prob
 
-    def forward(self, x, mask):
-        if self.training:
-            return DeterministicDropoutFunction.apply(x, self.keep_prob, mask)
-        return x
+    def forward(self, x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        if not self.training:
+            return x
+        return _MaskedScale.apply(x, mask, 1.0 / self.keep_prob)
 
 
-dropout_sample_input = lambda batch_size, hid_dim: (torch.empty((batch_size, hid_dim)),
-                                                    torch.randint(0, 1, (batch_size, hid_dim)))
+DeterministicDropoutFunction = _MaskedScale  # the name used by the reference
+
+
+def dropout_sample_input(batch_size: int, hid_dim: int):
+    return torch.empty((batch_size, hid_dim)), torch.randint(0, 1, (batch_size, hid_dim))
 
 
 @register_expert_class("det_dropout", dropout_sample_input)
 class DeterministicDropoutNetwork(nn.Module):
-    def __init__(self, hid_dim, dropout_prob=0.2):
+    """dropout(x, mask) -> Linear(h, 2h) -> ReLU -> Linear(2h, h)."""
+
+    def __init__(self, hid_dim: int, dropout_prob: float = 0.2):
         super().__init__()
-        self.linear_in = nn.Linear(hid_dim, 2 * hid_dim)
-        self.activation = nn.ReLU()
         self.dropout = DeterministicDropout(dropout_prob)
+        self.linear_in = nn.Linear(hid_dim, 2 * hid_dim)
         self.linear_out = nn.Linear(2 * hid_dim, hid_dim)
 
-    def forward(self, x, mask):
-        x = self.linear_in(self.dropout(x, mask))
-        return self.linear_out(self.activation(x))
+    def forward(self, x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        hidden = torch.relu(self.linear_in(self.dropout(x, mask)))
+        return self.linear_out(hidden)

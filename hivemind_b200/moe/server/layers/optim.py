@@ -1,41 +1,40 @@
-"""Optimizer wrappers for experts (reference: hivemind/moe/server/layers/optim.py:4-57).
+"""Optimizer wrappers for experts.
 
-``ClippingWrapper`` clips the global gradient norm before every step; on GPU the norm and the scaling are the
-multi-tensor kernels of ``ops/csrc/multi_tensor.cu`` (two launches for all parameters)."""
+``OptimizerWrapper`` delegates the whole ``torch.optim.Optimizer`` interface to an inner optimizer (attribute access
+falls through, so state, param_groups, hooks and schedulers see the inner object); ``ClippingWrapper`` clips the
+global gradient norm before every step, as the reference's wrapper does for ``--clip_grad_norm``
+(hivemind/moe/server/layers/optim.py:4-57). On a GPU the norm and the scaling are two launches of the multi-tensor
+kernels in ``ops/csrc/multi_tensor.cu`` for all parameters together.
+"""
+from typing import Iterable, List
+
 import torch
 
 from hivemind_b200.ops import multi_tensor as mt
 
+_DELEGATED = ("defaults", "state", "param_groups")
+
 
 class OptimizerWrapper(torch.optim.Optimizer):
-    """Forwards everything to the wrapped optimizer; subclasses override what they need."""
+    """Behaves like ``optim``; subclasses override the methods they want to change."""
 
     def __init__(self, optim: torch.optim.Optimizer):
-        object.__init__(self)
-        self.optim = optim
+        # deliberately no Optimizer.__init__: there are no parameters of our own, everything lives in ``optim``
+        object.__setattr__(self, "optim", optim)
 
-    @property
-    def defaults(self):
-        return self.optim.defaults
+    def __getattribute__(self, name: str):
+        if name in _DELEGATED:
+            return getattr(object.__getattribute__(self, "optim"), name)
+        return object.__getattribute__(self, name)
 
-    @property
-    def state(self):
-        return self.optim.state
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({self.optim!r})"
 
     def __getstate__(self):
         return self.optim.__getstate__()
 
-    def __setstate__(self, state):
+    def __setstate__(self, state) -> None:
         self.optim.__setstate__(state)
-
-    def __repr__(self):
-        return f"{self.__class__.__name__}({repr(self.optim)})"
-
-    def state_dict(self):
-        return self.optim.state_dict()
-
-    def load_state_dict(self, state_dict: dict) -> None:
-        return self.optim.load_state_dict(state_dict)
 
     def step(self, *args, **kwargs):
         return self.optim.step(*args, **kwargs)
@@ -43,26 +42,34 @@ class OptimizerWrapper(torch.optim.Optimizer):
     def zero_grad(self, *args, **kwargs):
         return self.optim.zero_grad(*args, **kwargs)
 
-    @property
-    def param_groups(self):
-        return self.optim.param_groups
+    def state_dict(self) -> dict:
+        return self.optim.state_dict()
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        self.optim.load_state_dict(state_dict)
 
     def add_param_group(self, param_group: dict) -> None:
-        return self.optim.add_param_group(param_group)
+        self.optim.add_param_group(param_group)
+
+
+def _gradients(groups: Iterable[dict]) -> List[torch.Tensor]:
+    return [p.grad for group in groups for p in group["params"] if p.grad is not None]
 
 
 class ClippingWrapper(OptimizerWrapper):
-    """A wrapper that clips gradients to ``clip_grad_norm`` (global L2 norm) before each optimizer step."""
+    """Clips gradients to a global L2 norm of ``clip_grad_norm`` before each step of the wrapped optimizer."""
 
-    def __init__(self, optim: torch.optim.Optimizer, clip_grad_norm):
+    def __init__(self, optim: torch.optim.Optimizer, clip_grad_norm: float):
         super().__init__(optim)
         self.clip_grad_norm = clip_grad_norm
 
     def step(self, *args, **kwargs):
-        grads = [p.grad for group in self.param_groups for p in group["params"] if p.grad is not None]
-        if grads and all(g.is_contiguous() and g.is_floating_point() for g in grads) and len({g.device for g in grads}) == 1:
+        grads = _gradients(self.param_groups)
+        fusable = grads and len({g.device for g in grads}) == 1 and all(
+            g.is_floating_point() and g.is_contiguous() for g in grads)
+        if fusable:
             mt.clip_grad_norm_(grads, self.clip_grad_norm)
-        else:
-            parameters = tuple(param for group in self.param_groups for param in group["params"])
-            torch.nn.utils.clip_grad_norm_(parameters, self.clip_grad_norm)
+        elif grads:
+            torch.nn.utils.clip_grad_norm_([p for group in self.param_groups for p in group["params"]],
+                                           self.clip_grad_norm)
         return super().step(*args, **kwargs)
