@@ -545,8 +545,18 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
     const unsigned char* remote = g.peer[s].outbox + part.enc_off;
     unsigned char* local = g.peer[me].deltabox + (size_t)s * g.delta_stride + part.span_off;
     const size_t b0 = (size_t)lo * eb, b1 = ((size_t)hi * eb + 15) / 16 * 16;
-    for (size_t b = b0 + 16 * (size_t)threadIdx.x; b < b1; b += 16 * (size_t)HB_THREADS)
-      *reinterpret_cast<uint4*>(local + hdr + b) = *reinterpret_cast<const uint4*>(remote + hdr + b);
+    {
+      // four independent 16-byte loads per thread before the first store: NVLink latency is paid once per batch
+      const uint4* __restrict__ rsrc = reinterpret_cast<const uint4*>(remote + hdr + b0);
+      uint4* __restrict__ ldst = reinterpret_cast<uint4*>(local + hdr + b0);
+      const int n16 = (int)((b1 - b0) / 16);
+      int q = threadIdx.x;
+      for (; q + 3 * HB_THREADS < n16; q += 4 * HB_THREADS) {
+        const uint4 a0 = rsrc[q], a1 = rsrc[q + HB_THREADS], a2 = rsrc[q + 2 * HB_THREADS], a3 = rsrc[q + 3 * HB_THREADS];
+        ldst[q] = a0; ldst[q + HB_THREADS] = a1; ldst[q + 2 * HB_THREADS] = a2; ldst[q + 3 * HB_THREADS] = a3;
+      }
+      for (; q < n16; q += HB_THREADS) ldst[q] = rsrc[q];
+    }
     if (codec == HB_UNIFORM8 || codec == HB_QUANTILE8) {
       const float cv = reinterpret_cast<const float*>(remote)[threadIdx.x];
       cbs[s][threadIdx.x] = cv;
@@ -574,8 +584,14 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       const int i = b0 + (r * HB_THREADS + threadIdx.x) * 4;
+      if (i_send && i + 4 <= len) {
+        const float4 own = *reinterpret_cast<const float4*>(x_local + i);  // part starts are 16-byte aligned
+        const float wm = g.weight[me];
+        acc[r][0] = wm * own.x; acc[r][1] = wm * own.y; acc[r][2] = wm * own.z; acc[r][3] = wm * own.w;
+      } else {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc[r][k] = (i_send && i + k < len) ? g.weight[me] * x_local[i + k] : 0.f;
+        for (int k = 0; k < 4; ++k) acc[r][k] = (i_send && i + k < len) ? g.weight[me] * x_local[i + k] : 0.f;
+      }
     }
     for (int s = 0; s < g.n_peers; ++s) {
       if (!inc[s]) continue;
@@ -602,9 +618,13 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
     for (int r = 0; r < 4; ++r) {
       const int i = b0 + (r * HB_THREADS + threadIdx.x) * 4;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        acc[r][k] *= inv_den;
-        if (i + k < len) avg_out[i + k] = acc[r][k];
+      for (int k = 0; k < 4; ++k) acc[r][k] *= inv_den;
+      if (i + 4 <= len) {
+        *reinterpret_cast<float4*>(avg_out + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (i + k < len) avg_out[i + k] = acc[r][k];
       }
     }
     if (need_stats) {
@@ -659,9 +679,33 @@ hb_apply_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) 
   const int lo = it.y * HB_CHUNK, hi = min(lo + HB_CHUNK, len);
   if (!g.sends[me]) return;
   float* x = g.peer[me].data + part.start;
+  const float alpha = g.alpha;
   if (owner == me) {
-    const float* avg = g.avg + part.avg_off;
-    for (int i = lo + threadIdx.x; i < hi; i += HB_THREADS) x[i] = fmaf(g.alpha, avg[i] - x[i], x[i]);
+    const float* __restrict__ avg = g.avg + part.avg_off;
+    // chunk starts are multiples of 16 elements: float4 accesses, four per thread in flight
+    const int n4 = (hi - lo) / 4;
+    float4* x4 = reinterpret_cast<float4*>(x + lo);
+    const float4* a4 = reinterpret_cast<const float4*>(avg + lo);
+    int q = threadIdx.x;
+    for (; q + 3 * HB_THREADS < n4; q += 4 * HB_THREADS) {
+      float4 xv[4], av[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { xv[u] = x4[q + u * HB_THREADS]; av[u] = a4[q + u * HB_THREADS]; }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        xv[u].x = fmaf(alpha, av[u].x - xv[u].x, xv[u].x); xv[u].y = fmaf(alpha, av[u].y - xv[u].y, xv[u].y);
+        xv[u].z = fmaf(alpha, av[u].z - xv[u].z, xv[u].z); xv[u].w = fmaf(alpha, av[u].w - xv[u].w, xv[u].w);
+        x4[q + u * HB_THREADS] = xv[u];
+      }
+    }
+    for (; q < n4; q += HB_THREADS) {
+      float4 xv = x4[q];
+      const float4 av = a4[q];
+      xv.x = fmaf(alpha, av.x - xv.x, xv.x); xv.y = fmaf(alpha, av.y - xv.y, xv.y);
+      xv.z = fmaf(alpha, av.z - xv.z, xv.z); xv.w = fmaf(alpha, av.w - xv.w, xv.w);
+      x4[q] = xv;
+    }
+    for (int i = lo + n4 * 4 + threadIdx.x; i < hi; i += HB_THREADS) x[i] = fmaf(alpha, avg[i] - x[i], x[i]);
     return;
   }
   const unsigned long long deadline = hb_phase_start(g.t_start + 1) + g.reducer_timeout_ns;
@@ -678,12 +722,29 @@ hb_apply_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) 
   HbDecode dec;
   hb_decode_setup(dec, part.codec, rec, len, cb);
   __syncthreads();
-  for (int i = lo + 4 * threadIdx.x; i < hi; i += 4 * HB_THREADS) {
+  int i = lo + 4 * threadIdx.x;
+  for (; i + 12 * HB_THREADS + 4 <= hi; i += 16 * HB_THREADS) {
+    // four groups of 4 elements per thread: all delta and x loads are issued before the first store
+    float v[4][4];
+    float4 xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      hb_decode4(dec, cb, i + u * 4 * HB_THREADS, len, v[u]);
+      xv[u] = *reinterpret_cast<const float4*>(x + i + u * 4 * HB_THREADS);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xv[u].x = fmaf(alpha, v[u][0], xv[u].x); xv[u].y = fmaf(alpha, v[u][1], xv[u].y);
+      xv[u].z = fmaf(alpha, v[u][2], xv[u].z); xv[u].w = fmaf(alpha, v[u][3], xv[u].w);
+      *reinterpret_cast<float4*>(x + i + u * 4 * HB_THREADS) = xv[u];
+    }
+  }
+  for (; i < hi; i += 4 * HB_THREADS) {
     float v[4];
     hb_decode4(dec, cb, i, len, v);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      if (i + k < hi) x[i + k] = fmaf(g.alpha, v[k], x[i + k]);
+      if (i + k < hi) x[i + k] = fmaf(alpha, v[k], x[i + k]);
   }
 }
 
