@@ -29,6 +29,7 @@ def main():
     parser.add_argument("--hidden", type=int, default=1024)
     parser.add_argument("--iters", type=int, default=5)
     parser.add_argument("--warmup", type=int, default=2)
+    parser.add_argument("--pair", action="store_true", help="gemm kernels: use the two-CTA (cta_group::2) kernel")
     args = parser.parse_args()
     dev = torch.device("cuda")
     torch.manual_seed(0)
@@ -38,14 +39,14 @@ def main():
         a = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)
         b = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16)
         out = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
-        run = lambda: tc_gemm(a, b, out=out)
+        run = lambda: tc_gemm(a, b, out=out, pair=args.pair)
         work = 2.0 * args.m * args.n * args.k
         unit = "TFLOP/s"
     elif args.kernel == "gemm_dw":
         a = torch.randn(args.k, args.m, device=dev, dtype=torch.bfloat16)  # [tokens, out]
         b = torch.randn(args.k, args.n, device=dev, dtype=torch.bfloat16)  # [tokens, in]
         out = torch.zeros(args.m, args.n, device=dev, dtype=torch.float32)
-        run = lambda: tc_gemm(a, b, a_mn=True, b_mn=True, out=out, reduce_add=True, splits=4)
+        run = lambda: tc_gemm(a, b, a_mn=True, b_mn=True, out=out, reduce_add=True, splits=4, pair=args.pair)
         work = 2.0 * args.m * args.n * args.k
         unit = "TFLOP/s"
     else:

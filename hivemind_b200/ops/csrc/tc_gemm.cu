@@ -466,6 +466,327 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Two-CTA form (tcgen05 cta_group::2). A 128x256 tile per SM is bound by shared-memory bandwidth: every
+// 128x256x16 MMA reads 12 KB of operands that TMA also had to write. Here two CTAs of a cluster (two SMs) share one
+// 256x256 tile: each CTA stages its own 128 rows of A and HALF of B (128 of the 256 columns), the leader CTA issues
+// one MMA that spans both SMs, and each SM keeps the accumulator rows of its own half of M in its TMEM. Per SM and
+// k-block that is 32 KB written and read instead of 48 KB.
+//
+// Protocol (barriers live at the same shared-memory offsets in both CTAs; "leader" = cluster rank 0):
+//   full[s]   (leader's, 1 arrival + bytes): both CTAs' TMA loads report their bytes to the LEADER's barrier
+//   empty[s]  (each CTA's own, 1 arrival): the leader's MMA warp commits to its own and to the peer's barrier
+//   tfull[b]  (each CTA's own, 1 arrival): committed by the leader when a tile's accumulation is complete
+//   tempty[b] (leader's, 2 x 128 arrivals): the epilogue threads of both CTAs hand the accumulator buffer back
+// All loads are unicast; every wait is bounded as in the one-CTA kernel; the two CTAs meet at a cluster barrier
+// before either leaves (a CTA must not exit while its peer may still read its shared memory).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+constexpr int PAIR_N = 256;       // N of the shared tile
+constexpr int PAIR_BN = 128;      // columns of B staged by each CTA
+constexpr int PAIR_M = 256;       // M of the shared tile (128 rows per CTA)
+
+template <int STAGES>
+struct PairSmem {
+  static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
+  static constexpr int B_BYTES = PAIR_BN * ROW_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int OUT_BYTES = BLOCK_M * ROW_BYTES;
+  static constexpr int OUT_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = OUT_OFF + 2 * OUT_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
+};
+
+template <int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_aux,
+                    const GemmParams p) {
+  using L = PairSmem<STAGES>;
+  constexpr int ELEM = 2;
+  constexpr int BLOCK_K = ROW_BYTES / ELEM;
+  constexpr int UMMA_K = 32 / ELEM;
+  constexpr int RUN = ROW_BYTES / ELEM;
+  constexpr int BLOCK_N = PAIR_N;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t IDESC = make_idesc(1, A_MN, B_MN, PAIR_M, PAIR_N);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::BAR_OFF + L::NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BAR_OFF + L::NUM_BARS * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 2 * EPI_THREADS);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (warp == 1) {  // the same warp of both CTAs allocates collectively
+    tc_alloc_pair(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised and the allocation is visible
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_info = [&](int tile, TileInfo& ti) {
+    const int split = tile % p.num_splits;
+    const int t = tile / p.num_splits;
+    ti.n_tile = t % p.num_n_tiles;
+    ti.m_tile = t / p.num_n_tiles;
+    ti.kb0 = split * p.kblocks_per_split;
+    ti.kb1 = min(ti.kb0 + p.kblocks_per_split, p.total_kblocks);
+    ti.group = 0;
+  };
+
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const int m_off = (int)rank * BLOCK_M, n_off = (int)rank * PAIR_BN;
+      for (int tile = pair_id; tile < num_tiles && !failed; tile += num_pairs) {
+        TileInfo ti;
+        tile_info(tile, ti);
+        const int m0 = ti.m_tile * PAIR_M + m_off, n0 = ti.n_tile * PAIR_N + n_off;
+        for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { failed = true; break; }
+          const uint32_t a_dst = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + L::A_BYTES;
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);  // bytes of both CTAs land on this barrier
+          const int k0 = kb * BLOCK_K;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int r = 0; r < BLOCK_M / RUN; ++r)
+              tma_load_2d_pair(a_dst + r * (BLOCK_K * ROW_BYTES), &map_a, leader_full, m0 + r * RUN, k0);
+          } else {
+            tma_load_2d_pair(a_dst, &map_a, leader_full, k0, m0);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int r = 0; r < PAIR_BN / RUN; ++r)
+              tma_load_2d_pair(b_dst + r * (BLOCK_K * ROW_BYTES), &map_b, leader_full, n0 + r * RUN, k0);
+          } else {
+            tma_load_2d_pair(b_dst, &map_b, leader_full, k0, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int tile = pair_id; tile < num_tiles && !failed; tile += num_pairs) {
+        TileInfo ti;
+        tile_info(tile, ti);
+        const int buf = local & 1;
+        const uint32_t use = (uint32_t)(local >> 1);
+        if (!mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BLOCK_N);
+        for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, 1024, 2)
+                                         : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * UMMA_K * ROW_BYTES, BLOCK_K * ROW_BYTES, 1024, 2)
+                                         : make_smem_desc(b_addr + k * 32, 16, 1024);
+            tc_mma_pair(d_tmem, a_desc, b_desc, IDESC, (kb > ti.kb0 || k > 0) ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          tc_commit_pair(map_to_cta(empty_bar(stage), 0));
+          tc_commit_pair(map_to_cta(empty_bar(stage), 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        tc_commit_pair(map_to_cta(tfull_bar(buf), 0));  // accumulator complete: tell both epilogues
+        tc_commit_pair(map_to_cta(tfull_bar(buf), 1));
+        ++local;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    uint8_t* out_buf[2] = {smem + L::OUT_OFF, smem + L::OUT_OFF + L::OUT_BYTES};
+    constexpr int COLS_PER_BOX = 32;
+    const int boxes_per_store = p.out_f32 ? 1 : 2;
+    int local = 0;
+    int flip = 0;
+    for (int tile = pair_id; tile < num_tiles && !failed; tile += num_pairs) {
+      TileInfo ti;
+      tile_info(tile, ti);
+      const int m_tile_row = ti.m_tile * PAIR_M + (int)rank * BLOCK_M, n_tile = ti.n_tile;
+      const float* bias = p.bias;
+      const int buf = local & 1;
+      const uint32_t use = (uint32_t)(local >> 1);
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), use & 1, abort_flag));
+      if (!ok) *abort_flag = 1;
+      epi_bar_sync();
+      if (*abort_flag) { failed = true; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
+      const int n_valid = min(BLOCK_N, p.N - n_tile * BLOCK_N);
+      for (int c0 = 0; c0 < BLOCK_N; c0 += COLS_PER_BOX * boxes_per_store) {
+        if (c0 >= n_valid) break;
+        if (epi_tid == 0) {
+          if (p.has_aux) tma_wait_read<0>(); else tma_wait_read<1>();
+        }
+        epi_bar_sync();
+        uint8_t* stage_main = p.has_aux ? out_buf[0] : out_buf[flip];
+        uint8_t* stage_aux = out_buf[1];
+#pragma unroll 1
+        for (int half = 0; half < boxes_per_store; ++half) {
+          uint32_t r[32];
+          tc_ld32(t_addr + (uint32_t)(c0 + half * COLS_PER_BOX), r);
+          tc_wait_ld();
+          float v[32];
+          const int gcol0 = n_tile * BLOCK_N + c0 + half * COLS_PER_BOX;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r[j]) * p.alpha;
+            if (p.epi != EPI_NONE && bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(bias + gcol0 + j);
+          }
+          if (p.out_f32) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              float4 o = make_float4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+              if (p.epi == EPI_BIAS_GELU) { o.x = hm_gelu_tanh(o.x); o.y = hm_gelu_tanh(o.y); o.z = hm_gelu_tanh(o.z); o.w = hm_gelu_tanh(o.w); }
+              *reinterpret_cast<float4*>(stage_main + row * ROW_BYTES + ((ch ^ (row & 7)) << 4)) = o;
+            }
+          } else {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const int pc = (half * 4 + ch) ^ (row & 7);
+              if (p.has_aux) {
+                uint4 a;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * ch], v[8 * ch + 1]), h1 = __floats2bfloat162_rn(v[8 * ch + 2], v[8 * ch + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * ch + 4], v[8 * ch + 5]), h3 = __floats2bfloat162_rn(v[8 * ch + 6], v[8 * ch + 7]);
+                a.x = *reinterpret_cast<uint32_t*>(&h0); a.y = *reinterpret_cast<uint32_t*>(&h1);
+                a.z = *reinterpret_cast<uint32_t*>(&h2); a.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(stage_aux + row * ROW_BYTES + (pc << 4)) = a;
+              }
+              float w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = p.epi == EPI_BIAS_GELU ? hm_gelu_tanh(v[8 * ch + j]) : v[8 * ch + j];
+              uint4 o;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(w[0], w[1]), h1 = __floats2bfloat162_rn(w[2], w[3]);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(w[4], w[5]), h3 = __floats2bfloat162_rn(w[6], w[7]);
+              o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+              o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(stage_main + row * ROW_BYTES + (pc << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          const int gc = n_tile * BLOCK_N + c0, gr = m_tile_row;
+          if (p.reduce_add) tma_reduce_add_2d(&map_d, smem_u32(stage_main), gc, gr);
+          else tma_store_2d(&map_d, smem_u32(stage_main), gc, gr);
+          if (p.has_aux) tma_store_2d(&map_aux, smem_u32(stage_aux), gc, gr);
+          tma_commit();
+        }
+        flip ^= 1;
+      }
+      // hand this CTA's half of the accumulator buffer back to the leader's MMA warp
+      tc_fence_before();
+      if (leader) mbar_arrive(tempty_bar(buf));
+      else mbar_arrive_remote(map_to_cta(tempty_bar(buf), 0));
+      ++local;
+    }
+    if (epi_tid == 0) tma_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown (every thread of both CTAs gets here)
+  if (failed) {
+    *abort_flag = 1;
+    if (p.err) atomicExch(p.err, 1 + warp);
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();  // neither CTA leaves, or frees tensor memory, while the other may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tc_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -568,6 +889,74 @@ int launch(const GemmCall& c, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
+
+template <int STAGES, bool A_MN, bool B_MN>
+int launch_pair(const GemmCall& c, cudaStream_t stream) {
+  using L = PairSmem<STAGES>;
+  constexpr int ELEM = 2;
+  constexpr int BLOCK_K = ROW_BYTES / ELEM;
+  constexpr int RUN = ROW_BYTES / ELEM;
+  CUtensorMap ma, mb, md, maux;
+  int rc;
+  rc = A_MN ? make_map(&ma, c.a, ELEM, false, c.K, c.M, c.lda, RUN, BLOCK_K)
+            : make_map(&ma, c.a, ELEM, false, c.M, c.K, c.lda, BLOCK_K, BLOCK_M);
+  if (rc) return rc;
+  rc = B_MN ? make_map(&mb, c.b, ELEM, false, c.K, c.N, c.ldb, RUN, BLOCK_K)
+            : make_map(&mb, c.b, ELEM, false, c.N, c.K, c.ldb, BLOCK_K, PAIR_BN);
+  if (rc) return rc;
+  const int out_elem = c.out_f32 ? 4 : 2;
+  rc = make_map(&md, c.d, out_elem, c.out_f32 != 0, c.M, c.N, c.ldd, ROW_BYTES / out_elem, BLOCK_M);
+  if (rc) return rc;
+  if (c.aux) {
+    rc = make_map(&maux, c.aux, 2, false, c.M, c.N, c.ldaux, ROW_BYTES / 2, BLOCK_M);
+    if (rc) return rc;
+  } else {
+    maux = md;
+  }
+  GemmParams p;
+  p.M = c.M; p.N = c.N; p.K = c.K;
+  p.num_m_tiles = (c.M + PAIR_M - 1) / PAIR_M;
+  p.num_n_tiles = (c.N + PAIR_N - 1) / PAIR_N;
+  p.total_kblocks = (c.K + BLOCK_K - 1) / BLOCK_K;
+  int splits = c.splits < 1 ? 1 : c.splits;
+  if (splits > p.total_kblocks) splits = p.total_kblocks;
+  p.kblocks_per_split = (p.total_kblocks + splits - 1) / splits;
+  p.num_splits = (p.total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  if (p.num_splits > 1 && !c.reduce_add) return -13;
+  p.epi = c.epi; p.out_f32 = c.out_f32; p.reduce_add = c.reduce_add; p.has_aux = c.aux != nullptr;
+  p.bias = c.bias; p.alpha = c.alpha; p.err = c.err;
+  p.group_mode = 0; p.num_groups = 1; p.group_table = nullptr;
+  p.group_b_rows = 0; p.group_d_rows = 0; p.group_bias = 0;
+  const int tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+  if (tiles <= 0 || p.total_kblocks <= 0) return 0;
+  auto kern = tc_gemm_pair_kernel<STAGES, A_MN, B_MN>;
+  const int smem = L::TOTAL + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // how many CTA pairs can be resident at once (SM counts per GPC need not be even)
+  cfg.gridDim = dim3(2 * (c.sms / 2));
+  int max_clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+  if (e != cudaSuccess) return (int)e;
+  if (max_clusters < 1) return -18;
+  int pairs = tiles < max_clusters ? tiles : max_clusters;
+  cfg.gridDim = dim3(2 * pairs);
+  e = cudaLaunchKernelEx(&cfg, kern, ma, mb, md, maux, p);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+
 template <int BLOCK_N, int STAGES, bool TF32>
 int dispatch_major(const GemmCall& c, cudaStream_t s) {
   if (c.a_mn) return c.b_mn ? launch<BLOCK_N, STAGES, TF32, true, true>(c, s) : launch<BLOCK_N, STAGES, TF32, true, false>(c, s);
@@ -633,4 +1022,20 @@ HM_API int hm_tc_gemm_grouped(const void* a, const void* b, void* d, void* aux, 
     case 64: return dispatch_major<64, 8, false>(c, stream);
     default: return -16;
   }
+}
+
+// Two-CTA (cta_group::2) variant of hm_tc_gemm for bf16 operands: one 256x256 tile per pair of SMs.
+// Same arguments as hm_tc_gemm without `tf32` and `block_n`. Requirements: N and M arbitrary (edges are clipped by
+// TMA), the usual 16-byte alignment of leading dimensions.
+HM_API int hm_tc_gemm_pair(const void* a, const void* b, void* d, void* aux, const void* bias, int M, int N, int K,
+                           long long lda, long long ldb, long long ldd, long long ldaux, int a_mn, int b_mn,
+                           int out_f32, int epi, int reduce_add, int splits, float alpha, void* err, int sms,
+                           cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (reduce_add && !out_f32) return -14;
+  if (aux && out_f32) return -15;
+  GemmCall c{a, b, d, aux, (const float*)bias, M, N, K, lda, ldb, ldd, ldaux, a_mn, b_mn, 0, out_f32, epi,
+             reduce_add, splits, alpha, (int*)err, sms};
+  if (a_mn) return b_mn ? launch_pair<5, true, true>(c, stream) : launch_pair<5, true, false>(c, stream);
+  return b_mn ? launch_pair<5, false, true>(c, stream) : launch_pair<5, false, false>(c, stream);
 }

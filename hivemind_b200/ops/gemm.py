@@ -12,6 +12,7 @@ buffer already exists, which also sums the uses of a shared weight and successiv
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -41,6 +42,9 @@ def check_kernel_errors() -> None:
             raise RuntimeError(f"tc_gemm on cuda:{idx}: a bounded wait ran out (role code {code}); results are invalid")
 
 
+_PAIR_DEFAULT = os.environ.get("HIVEMIND_B200_GEMM_PAIR", "0") == "1"  # opt-in until validated everywhere
+
+
 def _pick_block_n(n: int, m: int, tf32: bool, sms: int) -> int:
     options = (128, 64, 32) if tf32 else (256, 128, 64)
     for bn in options:
@@ -56,7 +60,7 @@ def tc_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool 
             out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
             bias: Optional[torch.Tensor] = None, gelu: bool = False, aux: Optional[torch.Tensor] = None,
             reduce_add: bool = False, splits: int = 1, alpha: float = 1.0,
-            block_n: Optional[int] = None) -> torch.Tensor:
+            block_n: Optional[int] = None, pair: Optional[bool] = None) -> torch.Tensor:
     """``D[M,N] = epi(alpha * sum_k A(m,k) B(n,k))``.
 
     :param a: ``[M, K]`` (or ``[K, M]`` when ``a_mn``), bf16 or fp32 (fp32 is multiplied as tf32)
@@ -64,6 +68,8 @@ def tc_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool 
     :param out: destination ``[M, N]`` (bf16 or fp32); with ``reduce_add`` the result is added to it (fp32 only)
     :param bias: fp32 ``[N]`` added before the optional tanh-GELU; ``aux`` (bf16) receives the pre-GELU values
     :param splits: split-K factor (needs ``reduce_add``)
+    :param pair: use the two-CTA kernel (one 256x256 tile per pair of SMs, bf16 only); default: when the problem
+      has at least one full 256x256 tile and ``HIVEMIND_B200_GEMM_PAIR`` is not ``0``
     """
     assert a.dim() == 2 and b.dim() == 2 and a.dtype == b.dtype
     m, k = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -102,6 +108,19 @@ def tc_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool 
     if block_n is None:
         block_n = _pick_block_n(n, m, tf32, sms)
     epi = EPI_BIAS_GELU if gelu else (EPI_BIAS if bias is not None else EPI_NONE)
+    if pair is None:
+        pair = _PAIR_DEFAULT and not tf32 and m >= 256 and n >= 256 and block_n == 256
+    if pair:
+        assert not tf32, "the two-CTA kernel multiplies bf16 operands"
+        with torch.cuda.device(a.device):
+            code = lib.hm_tc_gemm_pair(
+                _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(aux), _lib.ptr(bias), m, n, k,
+                ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(out.stride(0)),
+                ctypes.c_longlong(aux.stride(0) if aux is not None else 0), int(a_mn), int(b_mn),
+                int(out.dtype == torch.float32), epi, int(reduce_add), splits, ctypes.c_float(alpha),
+                _lib.ptr(_err_flag(a.device)), sms, _lib.stream_ptr(a.device))
+        _lib.check(code, "hm_tc_gemm_pair")
+        return out
     with torch.cuda.device(a.device):
         code = lib.hm_tc_gemm(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(aux), _lib.ptr(bias), m, n, k,

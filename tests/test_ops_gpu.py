@@ -184,6 +184,42 @@ def test_tc_gemm_bf16(m, n, k, a_mn, b_mn, block_n):
     assert err <= 2e-2 * math.sqrt(k) + 1e-2 * ref.abs().max().item(), err
 
 
+@pytest.mark.parametrize("m,n,k,a_mn,b_mn", [c for c in GEMM_CASES if c[0] >= 256 and c[1] >= 256] + [
+    (2048, 768, 4096, False, True), (1024, 1024, 2048, True, True), (260, 300, 72, False, False)])
+def test_tc_gemm_pair_bf16(m, n, k, a_mn, b_mn):
+    """The two-CTA (cta_group::2) kernel against fp32 matmul, all operand layouts."""
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn((k, m) if a_mn else (m, k), device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn((k, n) if b_mn else (n, k), device=_dev(), dtype=torch.bfloat16)
+    d = tc_gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=True)
+    check_kernel_errors()
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    err = (d.float() - ref).abs().max().item()
+    assert err <= 2e-2 * math.sqrt(k) + 1e-2 * ref.abs().max().item(), err
+
+
+def test_tc_gemm_pair_epilogues():
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(8)
+    m, n, k = 640, 768, 320
+    a = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(n, k, device=_dev(), dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(n, device=_dev())
+    aux = torch.empty(m, n, device=_dev(), dtype=torch.bfloat16)
+    d = tc_gemm(a, b, bias=bias, gelu=True, aux=aux, pair=True)
+    check_kernel_errors()
+    pre = a.float() @ b.float().t() + bias
+    assert torch.allclose(aux.float(), pre, atol=5e-2, rtol=2e-2)
+    assert torch.allclose(d.float(), F.gelu(pre, approximate="tanh"), atol=5e-2, rtol=2e-2)
+    acc = torch.ones(m, n, device=_dev())
+    tc_gemm(a, b, out=acc, reduce_add=True, splits=3, pair=True)
+    check_kernel_errors()
+    assert torch.allclose(acc, 1 + a.float() @ b.float().t(), atol=5e-2, rtol=2e-2)
+
+
 def test_tc_gemm_epilogues():
     from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
 
