@@ -185,7 +185,7 @@ def test_tc_gemm_bf16(m, n, k, a_mn, b_mn, block_n):
 
 
 @pytest.mark.parametrize("m,n,k,a_mn,b_mn", [c for c in GEMM_CASES if c[0] >= 256 and c[1] >= 256] + [
-    (2048, 768, 4096, False, True), (1024, 1024, 2048, True, True), (260, 300, 72, False, False)])
+    (2048, 768, 4096, False, True), (1024, 1024, 2048, True, True), (260, 304, 72, False, False)])
 def test_tc_gemm_pair_bf16(m, n, k, a_mn, b_mn):
     """The two-CTA (cta_group::2) kernel against fp32 matmul, all operand layouts."""
     from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
