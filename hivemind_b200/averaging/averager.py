@@ -396,12 +396,16 @@ class DecentralizedAverager(ServicerBase):
                 raise MatchmakingException(f"Unable to run All-Reduce: {e!r}")
             raise
 
+    def _make_allreduce_runner(self, **kwargs) -> AllReduceRunner:
+        """Factory of the RPC round's runner (a seam for subclasses, e.g. tests that inject host-side faults)."""
+        return AllReduceRunner(**kwargs)
+
     async def _run_allreduce_inplace_(self, tensors: Sequence[torch.Tensor], group_info: GroupInfo,
                                       group_id: Optional[bytes] = None, **kwargs) -> None:
         """RPC data path: stream parts to groupmates and add the averaged deltas to ``tensors`` in place."""
         group_id = group_info.group_id if group_id is None else group_id
         host_tensors = [t if not t.is_cuda else t.detach().to("cpu", torch.float32) for t in tensors]
-        runner = AllReduceRunner(p2p=self._p2p, servicer_type=type(self), prefix=self.prefix, tensors=host_tensors,
+        runner = self._make_allreduce_runner(p2p=self._p2p, servicer_type=type(self), prefix=self.prefix, tensors=host_tensors,
                                  group_id=group_id, ordered_peer_ids=group_info.peer_ids, **kwargs)
         assert group_id in self._running_groups, f"Group id {group_id} was not registered in _register_allreduce_group"
         self._running_groups[group_id].set_result(runner)

@@ -230,3 +230,82 @@ def test_power_sgd_rank1_recovers_rank1_gradients():
     finally:
         for x in (*avs, *dhts):
             x.shutdown()
+
+
+def test_training_averager_averages_parameters_and_statistics():
+    """Legacy TrainingAverager: two peers with different parameters / Adam statistics meet in the middle."""
+    from hivemind_b200.optim import TrainingAverager
+
+    dht_root = hivemind.DHT(start=True)
+    peers, averagers, models = [dht_root, hivemind.DHT(initial_peers=dht_root.get_visible_maddrs(), start=True)], [], []
+    try:
+        for i, dht in enumerate(peers):
+            torch.manual_seed(i)
+            model = torch.nn.Linear(8, 4)
+            opt = torch.optim.Adam(model.parameters(), lr=0.1)
+            model(torch.randn(16, 8)).pow(2).sum().backward()
+            opt.step()
+            models.append(model)
+            averagers.append(TrainingAverager(opt, average_parameters=True, average_gradients=True,
+                                              average_opt_statistics=["exp_avg_sq"], dht=dht, prefix="legacy",
+                                              target_group_size=2, min_matchmaking_time=1.0, request_timeout=1.0,
+                                              start=True))
+        expected_weight = (models[0].weight.detach() + models[1].weight.detach()) / 2
+        expected_grad = (models[0].weight.grad + models[1].weight.grad) / 2
+        results = [None, None]
+
+        def run(i):
+            results[i] = averagers[i].step(timeout=30)
+
+        threads = [threading.Thread(target=run, args=(i,)) for i in range(2)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(60)
+        assert all(r is not None for r in results)
+        for model in models:
+            assert torch.allclose(model.weight, expected_weight, atol=1e-5)
+            assert torch.allclose(model.weight.grad, expected_grad, atol=1e-5)
+        stats = [averagers[i].opt.state[models[i].weight]["exp_avg_sq"] for i in range(2)]
+        assert torch.allclose(stats[0], stats[1], atol=1e-6)
+    finally:
+        for averager in averagers:
+            averager.shutdown()
+        for dht in reversed(peers):
+            dht.shutdown()
+
+
+def test_grad_scaler_defers_unscale_and_update_to_the_global_step():
+    """With reuse_grad_buffers the scaler must not unscale or step between global steps, and must survive overflows."""
+    dht = hivemind.DHT(start=True)
+    try:
+        model = torch.nn.Linear(4, 2)
+        opt = hivemind.Optimizer(dht=dht, run_id="scaler", target_batch_size=8, batch_size_per_step=4,
+                                 params=model.parameters(), optimizer=lambda p: torch.optim.SGD(p, lr=0.1),
+                                 reuse_grad_buffers=True, matchmaking_time=0.5, averaging_timeout=5.0,
+                                 tracker_opts=dict(min_refresh_period=0.05, default_refresh_period=0.05,
+                                                   max_refresh_period=0.1), verbose=False)
+        scaler = hivemind.GradScaler("cpu", init_scale=4.0, growth_interval=1)
+        before = model.weight.detach().clone()
+        for micro_step in range(2):
+            loss = model(torch.ones(4, 4)).sum()
+            scaler.scale(loss).backward()
+            assert scaler.unscale_(opt) is False  # between global steps gradients stay scaled
+            scaler.step(opt)
+            scaler.update()
+            time.sleep(0.3)
+        deadline = time.time() + 20
+        while opt.local_epoch < 1 and time.time() < deadline:
+            loss = model(torch.ones(4, 4)).sum()
+            scaler.scale(loss).backward()
+            scaler.unscale_(opt)
+            scaler.step(opt)
+            scaler.update()
+            time.sleep(0.2)
+        assert opt.local_epoch >= 1 and not torch.allclose(model.weight, before)
+        assert torch.isfinite(model.weight).all()
+        # the applied update corresponds to unscaled gradients: |delta| = lr * |grad| = 0.1 * 4 per weight at most x small factor
+        assert (model.weight.detach() - before).abs().max() < 2.0
+        opt.shutdown()
+    finally:
+        dht.shutdown()
