@@ -67,6 +67,7 @@ class TrainingArguments:
         "help": "a torch file with int64 'input_ids' [n, seq]; default: synthetic token ids"})
     output_dir: str = field(default="outputs", metadata={"help": "where local checkpoints are written"})
     save_steps: int = field(default=500, metadata={"help": "save a local checkpoint every N collaborative steps (0 = never)"})
+    backup_every_steps: int = field(default=10, metadata={"help": "keep an in-memory copy of the weights every N collaborative steps (rolled back to on NaN)"})
     seed: int = field(default=0)
     device: Optional[str] = field(default=None, metadata={"help": "torch device; default: cuda if present"})
     statistics_expiration: float = field(default=600, metadata={"help": "lifetime of this peer's metrics record in the DHT"})

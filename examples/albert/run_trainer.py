@@ -123,6 +123,13 @@ def main():
     if base.initial_peers:
         optimizer.load_state_from_peers()  # catch up with the swarm before contributing
 
+    def params_are_finite() -> bool:
+        return all(bool(torch.isfinite(p).all()) for p in model.parameters())
+
+    def make_backup():
+        return {"model": {k: v.detach().clone() for k, v in model.state_dict().items()}, "epoch": optimizer.local_epoch}
+
+    backup = make_backup()  # restored if a collaborative step leaves non-finite weights behind
     source = BatchSource(cfg, args, seed=args.seed + 1 + hash(str(dht.peer_id)) % 10 ** 6)
     os.makedirs(args.output_dir, exist_ok=True)
     local_steps = samples = 0
@@ -141,6 +148,13 @@ def main():
                 if not optimizer.grad_averager or not getattr(optimizer.grad_averager, "reuse_grad_buffers", False):
                     optimizer.zero_grad()
             if optimizer.local_epoch != last_epoch:  # a collaborative step has just been applied
+                if not params_are_finite():
+                    logger.warning("non-finite parameters after a collaborative step: restoring the last good state")
+                    model.load_state_dict(backup["model"])
+                    if base.initial_peers:
+                        optimizer.load_state_from_peers()
+                elif optimizer.local_epoch % args.backup_every_steps == 0:
+                    backup = make_backup()
                 now = time.perf_counter()
                 record = utils.LocalMetrics(step=optimizer.local_epoch, samples_per_second=samples / max(now - last_report, 1e-9),
                                             samples_accumulated=samples, loss=loss_sum / max(mini_steps, 1),
