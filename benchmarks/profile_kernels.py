@@ -21,7 +21,8 @@ from hivemind_b200.ops.norm_act import layer_norm
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--kernel", required=True, choices=["gemm", "gemm_dw", "ln_fwd", "ln_bwd", "gelu_bwd"])
+    parser.add_argument("--kernel", required=True,
+                        choices=["gemm", "gemm_dw", "gemm_compare", "ln_fwd", "ln_bwd", "gelu_bwd"])
     parser.add_argument("--m", type=int, default=16384)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -35,6 +36,29 @@ def main():
     torch.manual_seed(0)
     flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
 
+    if args.kernel == "gemm_compare":
+        # one-CTA kernel, two-CTA kernel and torch.matmul (cuBLAS) on the same tensors, back to back
+        a = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+        variants = {"one_cta": lambda: tc_gemm(a, b, out=out, pair=False), "two_cta": lambda: tc_gemm(a, b, out=out, pair=True),
+                    "cublas": lambda: torch.matmul(a, b.t(), out=out)}
+        result = {}
+        for name, fn in variants.items():
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(args.iters):
+                fn()
+            stop.record()
+            torch.cuda.synchronize()
+            result[name] = 2.0 * args.m * args.n * args.k / (start.elapsed_time(stop) / args.iters / 1e3) / 1e12
+        check_kernel_errors()
+        print(json.dumps({"kernel": "gemm_compare", "tflops": result, "m": args.m, "n": args.n, "k": args.k,
+                          "iters": args.iters, "note": "launches back to back, no L2 flush"}))
+        return
     if args.kernel == "gemm":
         a = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)
         b = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16)
