@@ -569,7 +569,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles * (p.group_mode == 2 ? p.num_groups : p.num_splits);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -593,7 +593,18 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto tile_info = [&](int tile, TileInfo& ti) {
+  // false = the tile has no work (an empty group); both CTAs and all roles skip the same tiles
+  auto tile_info = [&](int tile, TileInfo& ti) -> bool {
+    if (p.group_mode == 2) {
+      const int per_group = p.num_m_tiles * p.num_n_tiles;
+      ti.group = tile / per_group;
+      const int t = tile - ti.group * per_group;
+      ti.n_tile = t % p.num_n_tiles;
+      ti.m_tile = t / p.num_n_tiles;
+      ti.kb0 = __ldg(p.group_table + ti.group) / BLOCK_K;
+      ti.kb1 = __ldg(p.group_table + ti.group + 1) / BLOCK_K;
+      return ti.kb1 > ti.kb0;
+    }
     const int split = tile % p.num_splits;
     const int t = tile / p.num_splits;
     ti.n_tile = t % p.num_n_tiles;
@@ -601,6 +612,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     ti.kb0 = split * p.kblocks_per_split;
     ti.kb1 = min(ti.kb0 + p.kblocks_per_split, p.total_kblocks);
     ti.group = 0;
+    return true;
   };
 
   bool failed = false;
@@ -613,7 +625,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m_off = (int)rank * BLOCK_M, n_off = (int)rank * PAIR_BN;
       for (int tile = pair_id; tile < num_tiles && !failed; tile += num_pairs) {
         TileInfo ti;
-        tile_info(tile, ti);
+        if (!tile_info(tile, ti)) continue;
         const int m0 = ti.m_tile * PAIR_M + m_off, n0 = ti.n_tile * PAIR_N + n_off;
         for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { failed = true; break; }
@@ -648,7 +660,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int local = 0;
       for (int tile = pair_id; tile < num_tiles && !failed; tile += num_pairs) {
         TileInfo ti;
-        tile_info(tile, ti);
+        if (!tile_info(tile, ti)) continue;
         const int buf = local & 1;
         const uint32_t use = (uint32_t)(local >> 1);
         if (!mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag)) { failed = true; break; }
@@ -690,8 +702,9 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int flip = 0;
     for (int tile = pair_id; tile < num_tiles && !failed; tile += num_pairs) {
       TileInfo ti;
-      tile_info(tile, ti);
-      const int m_tile_row = ti.m_tile * PAIR_M + (int)rank * BLOCK_M, n_tile = ti.n_tile;
+      if (!tile_info(tile, ti)) continue;
+      const int m_tile_row = ti.m_tile * PAIR_M + (int)rank * BLOCK_M + (p.group_mode == 2 ? ti.group * p.group_d_rows : 0);
+      const int n_tile = ti.n_tile;
       const float* bias = p.bias;
       const int buf = local & 1;
       const uint32_t use = (uint32_t)(local >> 1);
@@ -905,7 +918,10 @@ int launch_pair(const GemmCall& c, cudaStream_t stream) {
             : make_map(&mb, c.b, ELEM, false, c.N, c.K, c.ldb, BLOCK_K, PAIR_BN);
   if (rc) return rc;
   const int out_elem = c.out_f32 ? 4 : 2;
-  rc = make_map(&md, c.d, out_elem, c.out_f32 != 0, c.M, c.N, c.ldd, ROW_BYTES / out_elem, BLOCK_M);
+  if (c.group_mode != 0 && c.group_mode != 2) return -17;
+  if (c.group_mode == 2 && (!A_MN || !B_MN || c.aux || (c.num_groups > 1 && c.M % PAIR_M != 0))) return -17;
+  const long long d_groups = c.group_mode == 2 ? c.num_groups : 1;
+  rc = make_map(&md, c.d, out_elem, c.out_f32 != 0, c.M * d_groups, c.N, c.ldd, ROW_BYTES / out_elem, BLOCK_M);
   if (rc) return rc;
   if (c.aux) {
     rc = make_map(&maux, c.aux, 2, false, c.M, c.N, c.ldaux, ROW_BYTES / 2, BLOCK_M);
@@ -925,9 +941,10 @@ int launch_pair(const GemmCall& c, cudaStream_t stream) {
   if (p.num_splits > 1 && !c.reduce_add) return -13;
   p.epi = c.epi; p.out_f32 = c.out_f32; p.reduce_add = c.reduce_add; p.has_aux = c.aux != nullptr;
   p.bias = c.bias; p.alpha = c.alpha; p.err = c.err;
-  p.group_mode = 0; p.num_groups = 1; p.group_table = nullptr;
-  p.group_b_rows = 0; p.group_d_rows = 0; p.group_bias = 0;
-  const int tiles = p.num_m_tiles * p.num_n_tiles * p.num_splits;
+  p.group_mode = c.group_mode; p.num_groups = c.num_groups; p.group_table = c.group_table;
+  p.group_b_rows = 0; p.group_d_rows = c.M; p.group_bias = 0;
+  if (c.group_mode == 2) { p.num_splits = 1; p.kblocks_per_split = p.total_kblocks; }
+  const int tiles = p.num_m_tiles * p.num_n_tiles * (c.group_mode == 2 ? c.num_groups : p.num_splits);
   if (tiles <= 0 || p.total_kblocks <= 0) return 0;
   auto kern = tc_gemm_pair_kernel<STAGES, A_MN, B_MN>;
   const int smem = L::TOTAL + 1024;
@@ -1038,4 +1055,20 @@ HM_API int hm_tc_gemm_pair(const void* a, const void* b, void* d, void* aux, con
              reduce_add, splits, alpha, (int*)err, sms};
   if (a_mn) return b_mn ? launch_pair<5, true, true>(c, stream) : launch_pair<5, true, false>(c, stream);
   return b_mn ? launch_pair<5, false, true>(c, stream) : launch_pair<5, false, false>(c, stream);
+}
+
+// Two-CTA variant of grouped mode 2 (per-group K ranges over MN-major operands; see hm_tc_gemm_grouped): the
+// weight-gradient products of many experts in one launch. M must be a multiple of 256 when there are several groups.
+HM_API int hm_tc_gemm_pair_grouped_k(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
+                                     long long ldb, long long ldd, int out_f32, int reduce_add, float alpha, void* err,
+                                     int sms, int num_groups, const int* group_table, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (group_table == nullptr) return -17;
+  if (reduce_add && !out_f32) return -14;
+  GemmCall c{a, b, d, nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, 1, 1, 0, out_f32, EPI_NONE, reduce_add, 1, alpha,
+             (int*)err, sms};
+  c.group_mode = 2;
+  c.num_groups = num_groups;
+  c.group_table = group_table;
+  return launch_pair<5, true, true>(c, stream);
 }

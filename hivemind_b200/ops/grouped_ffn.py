@@ -42,6 +42,17 @@ def tc_gemm_grouped(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, table: 
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
     lib = _lib.load_library()
     sms = _lib.sm_count(a.device)
+    if mode == 2 and a_mn and b_mn and bias is None and aux is None and m % 256 == 0 and n >= 256:
+        # weight gradients: the two-CTA kernel is about 1.5x faster on MN-major x MN-major products
+        out2 = out.view(-1, out.shape[-1])
+        with torch.cuda.device(a.device):
+            code = lib.hm_tc_gemm_pair_grouped_k(
+                _lib.ptr(a), _lib.ptr(b), _lib.ptr(out2), m, n, k, ctypes.c_longlong(a.stride(-2)),
+                ctypes.c_longlong(b.stride(-2)), ctypes.c_longlong(out2.stride(0)), int(out.dtype == torch.float32),
+                int(reduce_add), ctypes.c_float(1.0), _lib.ptr(_err_flag(a.device)), sms, num_groups, _lib.ptr(table),
+                _lib.stream_ptr(a.device))
+        _lib.check(code, "hm_tc_gemm_pair_grouped_k")
+        return out
     if block_n is None:
         block_n = 256 if n >= 256 else (128 if n >= 128 else 64)
     epi = EPI_BIAS_GELU if gelu else (EPI_BIAS if bias is not None else EPI_NONE)
