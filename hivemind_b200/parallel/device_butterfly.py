@@ -25,6 +25,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from hivemind_b200.utils.profiling import device_range
+
 from hivemind_b200.averaging.allreduce import AveragingMode
 from hivemind_b200.averaging.partition import compute_part_layout
 from hivemind_b200.compression import (BlockwiseQuantization, CompressionBase, CompressionInfo, Float16Compression,
@@ -37,6 +39,8 @@ from hivemind_b200.utils.logging import get_logger
 
 logger = get_logger(__name__)
 
+GUARD_BYTES, GUARD_PATTERN = 256, 0xA5  # canary zones between the regions of an arena
+DEBUG_CHECKS = os.environ.get("HIVEMIND_B200_DEBUG", "0") == "1"
 EXIT_GRACE_SECONDS = 2.0  # how long after a round peers may still read this arena (see DeviceEndpoint.close)
 MAX_PEERS = 16
 ALIGN = 16  # elements: tensor starts and part boundaries are multiples of this, so every access is 16-byte aligned
@@ -169,13 +173,15 @@ class DeviceEndpoint:
         self.max_parts = sum((n + min_part - 1) // min_part for n in self.numels) + MAX_PEERS + len(tensors)
         self.cap_outbox = self.total * 4 + self.max_parts * 1088
         self.cap_delta = int(self.cap_outbox * 2.5) + (1 << 16)  # room for uneven spans; larger groups fall back to RPC
-        self.layout = {}
+        self.layout, self._guards = {}, {}
         cursor = 0
         for name, nbytes in (("data", self.total * 4), ("avg", self.total * 4), ("outbox", self.cap_outbox),
                              ("deltabox", self.cap_delta), ("ready", self.max_parts * 4),
                              ("delta_ready", MAX_PEERS * self.max_parts * 4)):
             self.layout[name] = cursor
             cursor += (nbytes + 255) // 256 * 256
+            self._guards[name] = cursor  # a canary zone follows every region (see check_canaries)
+            cursor += GUARD_BYTES
         self.arena_bytes = cursor
         base = ctypes.c_void_p()
         with torch.cuda.device(self.device):
@@ -187,6 +193,8 @@ class DeviceEndpoint:
         self.ipc_handle = bytes(handle) if rc == 0 else None
         self._raw = _RawCuda(self.base, self.arena_bytes, self)
         self._bytes = torch.as_tensor(self._raw, device=self.device)
+        for guard in self._guards.values():
+            self._bytes[guard:guard + GUARD_BYTES].fill_(GUARD_PATTERN)
         flat = self._bytes[self.layout["data"]:self.layout["data"] + self.total * 4].view(torch.float32)
         self.flat = flat
         self.tensor_views = []
@@ -244,6 +252,21 @@ class DeviceEndpoint:
                 _lib.check(self.lib.hm_ipc_open(buf, ctypes.byref(out)), "hm_ipc_open", 0)
             self._mappings[key] = out.value
         return self._mappings[key]
+
+    def check_canaries(self) -> None:
+        """Raise if any kernel (of this GPU or of a groupmate) wrote past the end of one of the arena's regions.
+
+        Every region of the arena is followed by ``GUARD_BYTES`` of a fixed pattern that no kernel has a reason to
+        touch. Tests call this after their rounds; with ``HIVEMIND_B200_DEBUG=1`` every round ends with it (one
+        small device-to-host copy and a synchronisation of the device).
+        """
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.stream(self._torch_stream):
+            zones = torch.stack([self._bytes[g:g + GUARD_BYTES] for g in self._guards.values()])
+            damaged = (zones != GUARD_PATTERN).any(dim=1).cpu()
+        names = [name for name, bad in zip(self._guards, damaged.tolist()) if bad]
+        if names:
+            raise RuntimeError(f"device butterfly: memory past the end of region(s) {names} was overwritten")
 
     def close(self) -> None:
         if self._closed:
@@ -420,11 +443,16 @@ class DeviceEndpoint:
         plan = self._prepare(group_id=group_id, my_index=my_index, device_infos=device_infos, modes=modes,
                              peer_fractions=peer_fractions, weights=weights, alpha=alpha,
                              sender_timeout=sender_timeout, reducer_timeout=reducer_timeout, stream=self.stream)
-        self._stage_send(plan, self.stream)
-        self._stage_reduce(plan, self.stream)
-        self._stage_apply(plan, self.stream)
+        with device_range("butterfly.send", self._torch_stream):
+            self._stage_send(plan, self.stream)
+        with device_range("butterfly.reduce", self._torch_stream):
+            self._stage_reduce(plan, self.stream)
+        with device_range("butterfly.apply", self._torch_stream):
+            self._stage_apply(plan, self.stream)
         status = self._read_status(plan, self.stream)
         self._last_round_end = time.monotonic()
+        if DEBUG_CHECKS:
+            self.check_canaries()
         return status
 
 

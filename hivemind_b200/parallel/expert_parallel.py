@@ -23,6 +23,7 @@ import torch.nn as nn
 from hivemind_b200.moe.server.layers import name_to_block
 from hivemind_b200.ops import moe as moe_ops
 from hivemind_b200.ops.grouped_ffn import GroupedFeedforward
+from hivemind_b200.utils.profiling import device_range
 
 
 class _GroupedExperts(torch.autograd.Function):
@@ -143,8 +144,9 @@ class DeviceMixtureOfExperts(nn.Module):
             kept = torch.rand(scores.shape[1], device=scores.device) < self.grid_dropout
             scores = scores.masked_fill(~kept, float("-inf"))
         mode = "prob" if self.switch else "sum"
-        idx, _ = moe_ops.gate_topk(scores, self.grid_size, self.k_best, self.alive, mode)
-        gate = moe_ops.expert_values(scores, idx, self.grid_size, mode)
+        with device_range("moe.gate"):
+            idx, _ = moe_ops.gate_topk(scores, self.grid_size, self.k_best, self.alive, mode)
+            gate = moe_ops.expert_values(scores, idx, self.grid_size, mode)
         if self.check_k_min and self.k_min > 0:
             if int(((idx >= 0).sum(1) < self.k_min).any()):
                 raise RuntimeError(f"some tokens have fewer than {self.k_min} live experts")
@@ -152,14 +154,17 @@ class DeviceMixtureOfExperts(nn.Module):
         dtype = self.compute_dtype or (torch.bfloat16 if tokens.is_cuda else tokens.dtype)
         rows = tokens.to(dtype)
         align = moe_ops.TILE_ROWS if (self.grouped and self.world == 1) else 1
-        routed = moe_ops.dispatch(rows, idx, self.num_experts, align=align)
-        answers, row_ok = self._run_experts(routed)
+        with device_range("moe.dispatch"):
+            routed = moe_ops.dispatch(rows, idx, self.num_experts, align=align)
+        with device_range("moe.experts"):
+            answers, row_ok = self._run_experts(routed)
         keep = None
         if row_ok is not None:  # rows whose expert host did not answer in time count as failed experts
             keep = row_ok[routed.pos.clamp(min=0).long()] & (routed.pos >= 0)
         residual = rows if self.switch else None
-        mixed = moe_ops.combine(answers, routed.pos, gate, "prob" if self.switch else "softmax", keep=keep,
-                                residual=residual)
+        with device_range("moe.combine"):
+            mixed = moe_ops.combine(answers, routed.pos, gate, "prob" if self.switch else "softmax", keep=keep,
+                                    residual=residual)
         out = mixed.to(x.dtype).view(shape)
         if not self.switch:
             return out

@@ -43,6 +43,8 @@ def test_weighted_average_all_codecs(codec, n):
     statuses = run_group_emulated(endpoints, weights=weights, peer_fractions=fractions)
     torch.cuda.synchronize()
     assert all(s.failed_elements == 0 and not s.banned_senders for s in statuses)
+    for endpoint in endpoints:
+        endpoint.check_canaries()  # no kernel wrote past the end of a region of any arena
     tol = TOL[type(codec).__name__]
     lossy8 = type(codec).__name__ in ("Uniform8BitQuantization", "Quantile8BitQuantization", "BlockwiseQuantization")
     for k in range(len(shapes)):
@@ -101,6 +103,39 @@ def test_missing_and_stalled_senders_are_excluded_without_hanging():
     # the absent peer still reduced its own span with what the others sent, so nobody loses that span either
     assert torch.allclose(endpoints[0].tensor_views[0].cpu()[150000:], ((originals[0][0] + originals[1][0] +
                           originals[2][0] + originals[3][0]) / 4)[150000:], atol=5e-3)
+
+
+def test_canaries_report_a_write_past_a_region():
+    """The guard zones after each arena region: intact after a round, reported once something overwrites one
+    (here the host does the overwriting with an ordinary fill of a slice that it owns)."""
+    from hivemind_b200.parallel.device_butterfly import GUARD_BYTES, run_group_emulated
+
+    endpoints, _ = _make_endpoints(2, [(4096,)], NoCompression(), part_size_bytes=2 ** 14)
+    run_group_emulated(endpoints, weights=[1.0, 1.0], peer_fractions=[0.5, 0.5])
+    for endpoint in endpoints:
+        endpoint.check_canaries()
+    guard = endpoints[0]._guards["outbox"]
+    endpoints[0]._bytes[guard:guard + 8].zero_()
+    with pytest.raises(RuntimeError, match="outbox"):
+        endpoints[0].check_canaries()
+    endpoints[1].check_canaries()
+    assert GUARD_BYTES >= 256
+
+
+def test_stage_timers_record_device_time():
+    from hivemind_b200.utils import profiling
+
+    profiling.enable(nvtx=True, timing=True)
+    try:
+        profiling.timing_summary(reset=True)
+        x = torch.randn(1 << 20, device="cuda")
+        for _ in range(3):
+            with profiling.device_range("test.stage"):
+                x = x * 1.0001
+        summary = profiling.timing_summary()
+        assert summary["test.stage"]["count"] == 3 and summary["test.stage"]["total_ms"] > 0
+    finally:
+        profiling.enable(nvtx=False, timing=False)
 
 
 def test_device_codecs_match_cpu_codecs():

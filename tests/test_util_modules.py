@@ -221,3 +221,12 @@ def test_multiaddr_text_binary_and_manipulation():
     for bad in ("ip4/1.2.3.4", "/ip4/999.1.1.1/tcp/1", "/tcp/70000", "/nosuchproto/1", "/ip4"):
         with pytest.raises(Exception):
             Multiaddr(bad)
+
+
+def test_device_range_is_a_no_op_without_a_gpu_or_when_disabled():
+    from hivemind_b200.utils import profiling
+
+    profiling.enable(nvtx=False, timing=False)
+    with profiling.device_range("anything"):
+        pass
+    assert "anything" not in profiling.timing_summary()
