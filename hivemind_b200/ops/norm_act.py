@@ -27,7 +27,9 @@ def gelu_tanh_reference(x: torch.Tensor) -> torch.Tensor:
 
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, gamma, beta, eps):
+    def forward(ctx, x, residual, gamma, beta, eps, return_sum=False):
+        ctx.set_materialize_grads(False)
+        ctx.return_sum = return_sum
         h = x.shape[-1]
         x2 = x.reshape(-1, h).contiguous()
         r2 = residual.reshape(-1, h).contiguous() if residual is not None else None
@@ -49,13 +51,18 @@ class _LayerNormFn(torch.autograd.Function):
         ctx.shape = x.shape
         ctx.param_dtype = (gamma.dtype, beta.dtype)
         ctx.params = (gamma, beta)
+        if return_sum:
+            return y.view(x.shape), (z if z is not None else x2).view(x.shape)
         return y.view(x.shape)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dz=None):
         zin, g32, mean, rstd = ctx.saved_tensors
         h = zin.shape[-1]
         rows = zin.shape[0]
+        if dy is None:  # only the sum was used downstream
+            dz = dz if dz is not None else torch.zeros(ctx.shape, dtype=zin.dtype, device=zin.device)
+            return dz, (dz if ctx.has_residual else None), None, None, None, None
         dy2 = dy.reshape(-1, h).contiguous()
         if dy2.dtype != zin.dtype:
             dy2 = dy2.to(zin.dtype)
@@ -78,19 +85,27 @@ class _LayerNormFn(torch.autograd.Function):
                                         _lib.stream_ptr(zin.device))
         _lib.check(code, "hm_layernorm_bwd")
         dx = dx.view(ctx.shape)
+        if dz is not None:
+            dx.add_(dz.reshape(ctx.shape))
         if direct:
-            return dx, (dx if ctx.has_residual else None), None, None, None
-        return dx, (dx if ctx.has_residual else None), dgamma.to(ctx.param_dtype[0]), dbeta.to(ctx.param_dtype[1]), None
+            return dx, (dx if ctx.has_residual else None), None, None, None, None
+        return (dx, (dx if ctx.has_residual else None), dgamma.to(ctx.param_dtype[0]), dbeta.to(ctx.param_dtype[1]),
+                None, None)
 
 
 def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
-               residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``LayerNorm(x + residual)`` over the last dimension (``residual`` optional), statistics in fp32."""
+               residual: Optional[torch.Tensor] = None, return_sum: bool = False):
+    """``LayerNorm(x + residual)`` over the last dimension (``residual`` optional), statistics in fp32.
+
+    With ``return_sum`` the result is ``(LayerNorm(x + residual), x + residual)``: the second tensor is the updated
+    residual stream of a pre-LayerNorm transformer, produced by the same kernel pass.
+    """
     h = x.shape[-1]
     if _kernel_ok(x, h):
-        return _LayerNormFn.apply(x, residual, gamma, beta, eps)
+        return _LayerNormFn.apply(x, residual, gamma, beta, eps, return_sum)
     z = x if residual is None else x + residual
-    return F.layer_norm(z.to(torch.float32), (h,), gamma.to(torch.float32), beta.to(torch.float32), eps).to(x.dtype)
+    y = F.layer_norm(z.to(torch.float32), (h,), gamma.to(torch.float32), beta.to(torch.float32), eps).to(x.dtype)
+    return (y, z) if return_sum else y
 
 
 class _BiasGeluFn(torch.autograd.Function):

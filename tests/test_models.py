@@ -1,0 +1,102 @@
+"""Model families against plain PyTorch fp32 restatements of the same architecture."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from hivemind_b200.models.gpt2 import GPT2Config, GPT2LMHeadModel, make_lm_batch
+
+
+def _gpt2_reference_loss(cfg: GPT2Config, p, input_ids, labels):
+    """Textbook pre-LayerNorm GPT-2 in fp64 over a dict of parameters named like the model's."""
+    b, s = input_ids.shape
+    x = p["wte"][input_ids] + p["wpe"][:s]
+    mask = torch.ones(s, s, dtype=torch.bool, device=x.device).tril()
+    for i in range(cfg.n_layer):
+        g = lambda name: p[f"blocks.{i}.{name}"]
+        h = F.layer_norm(x, (cfg.n_embd,), g("ln_1_weight"), g("ln_1_bias"), cfg.layer_norm_eps)
+        qkv = (h @ g("qkv_weight").T + g("qkv_bias")).view(b, s, 3, cfg.n_head, -1)
+        q, k, v = (qkv[:, :, j].transpose(1, 2) for j in range(3))
+        att = (q @ k.transpose(-1, -2)) / q.shape[-1] ** 0.5
+        att = att.masked_fill(~mask, float("-inf")).softmax(-1)
+        ctx = (att @ v).transpose(1, 2).reshape(b, s, cfg.n_embd)
+        x = x + ctx @ g("attn_out_weight").T + g("attn_out_bias")
+        h = F.layer_norm(x, (cfg.n_embd,), g("ln_2_weight"), g("ln_2_bias"), cfg.layer_norm_eps)
+        h = F.gelu(h @ g("ffn_weight").T + g("ffn_bias"), approximate="tanh")
+        x = x + h @ g("ffn_out_weight").T + g("ffn_out_bias")
+    x = F.layer_norm(x, (cfg.n_embd,), p["ln_f_weight"], p["ln_f_bias"], cfg.layer_norm_eps)
+    logits = x @ p["wte"][:cfg.vocab_size].T
+    return F.cross_entropy(logits.view(b * s, -1), labels.reshape(-1), ignore_index=-100)
+
+
+def _autograd_reference(model, batch):
+    params = {name: q.detach().double().requires_grad_(True) for name, q in model.named_parameters()}
+    loss = _gpt2_reference_loss(model.cfg, params, batch["input_ids"], batch["labels"])
+    loss.backward()
+    return loss.detach(), {name: q.grad for name, q in params.items()}
+
+
+def _check_model(device, loss_tol, grad_tol):
+    torch.manual_seed(0)
+    cfg = GPT2Config.tiny()
+    model = GPT2LMHeadModel(cfg).to(device)
+    with torch.no_grad():  # make the biases and norms non-trivial
+        for name, q in model.named_parameters():
+            if q.ndim == 1:
+                q.add_(0.1 * torch.randn_like(q))
+    batch = {k: v.to(device) for k, v in make_lm_batch(cfg, 3, 48, generator=torch.Generator().manual_seed(1)).items()}
+    loss = model(batch["input_ids"], batch["labels"])
+    loss.backward()
+    ref_loss, ref_grads = _autograd_reference(model, batch)
+    assert abs(loss.item() - ref_loss.item()) <= loss_tol * abs(ref_loss.item()), (loss.item(), ref_loss.item())
+    for name, q in model.named_parameters():
+        assert q.grad is not None, name
+        ref = ref_grads[name].to(q.grad.dtype)
+        err = (q.grad - ref).norm() / ref.norm().clamp_min(1e-6)
+        assert err.item() <= grad_tol, (name, err.item())
+    assert model.wte.grad[cfg.vocab_size:].abs().max().item() < 1e-6  # padded vocabulary rows get no gradient
+    # the default labels are the inputs shifted by one
+    assert torch.allclose(model(batch["input_ids"]).float(), loss.detach().float(), rtol=5 * loss_tol + 1e-6)
+    assert model.logits(batch["input_ids"]).shape == (3, 48, cfg.vocab_size)
+
+
+def test_gpt2_matches_reference_cpu():
+    _check_model(torch.device("cpu"), loss_tol=1e-5, grad_tol=1e-4)
+
+
+@pytest.mark.gpu
+def test_gpt2_matches_reference_gpu():
+    from hivemind_b200.ops import _lib
+    before = _lib.launch_count()
+    _check_model(torch.device("cuda"), loss_tol=5e-3, grad_tol=4e-2)
+    assert _lib.launch_count() > before  # the native kernels ran, not a fallback
+
+
+def test_layer_norm_return_sum_cpu():
+    from hivemind_b200.ops.norm_act import layer_norm
+    x, r = torch.randn(5, 32, requires_grad=True), torch.randn(5, 32, requires_grad=True)
+    g, b = torch.randn(32, requires_grad=True), torch.randn(32, requires_grad=True)
+    y, z = layer_norm(x, g, b, 1e-5, residual=r, return_sum=True)
+    assert torch.allclose(z, x + r)
+    assert torch.allclose(y, F.layer_norm(x + r, (32,), g, b, 1e-5), atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_layer_norm_return_sum_gpu():
+    from hivemind_b200.ops.norm_act import layer_norm
+    torch.manual_seed(0)
+    x = torch.randn(300, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(300, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(1024, device="cuda", requires_grad=True)
+    b = torch.randn(1024, device="cuda", requires_grad=True)
+    y, z = layer_norm(x, g, b, 1e-5, residual=r, return_sum=True)
+    wy, wz = torch.randn_like(y), torch.randn_like(z)
+    ((y * wy).sum() + (z * wz).sum()).backward()
+    xf, rf = x.detach().float().requires_grad_(True), r.detach().float().requires_grad_(True)
+    gf, bf = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    zf = xf + rf
+    yf = F.layer_norm(zf, (1024,), gf, bf, 1e-5)
+    ((yf * wy.float()).sum() + (zf * wz.float()).sum()).backward()
+    assert torch.allclose(z.float(), zf, atol=2e-2)
+    assert torch.allclose(y.float(), yf, atol=5e-2, rtol=2e-2)
+    for got, ref in ((x.grad, xf.grad), (r.grad, rf.grad), (g.grad, gf.grad), (b.grad, bf.grad)):
+        assert ((got.float() - ref).norm() / ref.norm()).item() < 2e-2

@@ -144,3 +144,88 @@ def test_moe_peer_exchange_matches_all_to_all(tmp_path):
             out, _ = p.communicate()
         outputs.append(out)
     assert all(p.returncode == 0 for p in procs), "\n".join(o[-2000:] for o in outputs)
+
+
+POWERSGD_CHILD = r'''
+import os, sys, time, json, torch
+sys.path.insert(0, os.environ["REPO_ROOT"])
+rank, world = int(sys.argv[1]), int(sys.argv[2])
+import hivemind_b200 as hivemind
+from hivemind_b200.optim import PowerSGDGradientAverager
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+if rank == 0:
+    dht = hivemind.DHT(start=True)
+    with open(os.environ["MADDR_FILE"] + ".tmp", "w") as f:
+        json.dump([str(m) for m in dht.get_visible_maddrs()], f)
+    os.rename(os.environ["MADDR_FILE"] + ".tmp", os.environ["MADDR_FILE"])
+else:
+    while not os.path.exists(os.environ["MADDR_FILE"]):
+        time.sleep(0.05)
+    dht = hivemind.DHT(initial_peers=json.load(open(os.environ["MADDR_FILE"])), start=True)
+torch.manual_seed(0)  # the same low-rank factors on every rank; the ranks differ by a scale and a sample count
+u, v = torch.randn(256, 8).to(dev), torch.randn(8, 128).to(dev)
+scales, samples = [1.0 + r for r in range(world)], [8 + 10 * r for r in range(world)]
+params = [torch.nn.Parameter(torch.zeros(256, 128, device=dev)), torch.nn.Parameter(torch.zeros(64, device=dev))]
+averager = PowerSGDGradientAverager(params, averager_rank=8, dht=dht, prefix="psgd_gpu", target_group_size=world,
+                                    min_matchmaking_time=3.0, request_timeout=1.0, min_compression_ratio=0.0,
+                                    q_init="normal", sender_timeout=5.0, start=True)
+assert averager._p_endpoint is not None and averager._q_endpoint is not None, "the device path must be active"
+torch.manual_seed(10 + rank)  # different starting Q on every rank, as in a real swarm
+for q in averager._qs:
+    q.copy_(torch.randn_like(q))
+mean_scale = sum(s * n for s, n in zip(scales, samples)) / sum(samples)
+ok = True
+for round_index in range(2):  # the second round reuses the arenas and starts from the error feedback of the first
+    params[0].grad = scales[rank] * (u @ v)
+    params[1].grad = torch.full((64,), scales[rank], device=dev)
+    control = averager.schedule_step(timeout=60)
+    averager.accumulate_grads_(batch_size=samples[rank])
+    averager.step(control=control, wait=True, timeout=60)
+    torch.cuda.synchronize()
+    expected = mean_scale * (u @ v)
+    with averager.use_averaged_gradients():
+        got_w, got_b = params[0].grad.clone(), params[1].grad.clone()
+    if round_index == 0:
+        err_w = ((got_w - expected).norm() / expected.norm()).item()
+        err_b = (got_b - mean_scale).abs().max().item()
+        residual = ((averager._ms[0] - (scales[rank] - mean_scale) * (u @ v)).norm() / expected.norm()).item()
+        ok = ok and err_w < 2e-2 and err_b < 1e-4 and residual < 2e-2
+        print("powersgd child", rank, "round 0", err_w, err_b, residual, flush=True)
+    else:
+        # every rank adds its residual (scale - mean) u v to the same new gradient: the average is again mean_scale u v
+        err_w = ((got_w - expected).norm() / expected.norm()).item()
+        ok = ok and err_w < 4e-2
+        print("powersgd child", rank, "round 1", err_w, flush=True)
+    averager.reset_accumulated_grads_()
+with open(os.environ["OUT_PREFIX"] + f"{rank}.done", "w") as f:
+    f.write("ok" if ok else "mismatch")
+deadline = time.time() + 120
+while time.time() < deadline and not all(os.path.exists(os.environ["OUT_PREFIX"] + f"{r}.done") for r in range(world)):
+    time.sleep(0.05)
+averager.shutdown(); dht.shutdown()
+sys.exit(0 if ok else 1)
+'''
+
+
+def test_powersgd_factors_average_over_peer_memory(tmp_path):
+    """PowerSGDGradientAverager with its P and Q arenas on two GPUs: gradients that share a rank-8 subspace are
+    recovered as their sample-weighted mean, and the error feedback keeps what the mean does not explain."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    env = dict(os.environ, REPO_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+               MADDR_FILE=str(tmp_path / "maddrs.json"), OUT_PREFIX=str(tmp_path / "out"), NCCL_NVLS_ENABLE="0")
+    script = tmp_path / "powersgd_child.py"
+    script.write_text(POWERSGD_CHILD)
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world)], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outputs.append(out)
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-2000:] for o in outputs)
