@@ -93,28 +93,50 @@ def benchmark_swarm(num_peers, target_group_size, num_rounds, min_matchmaking_ti
         item.shutdown()
 
 
+VERBOSE_ROUNDS = False
+
+
 def _time_rounds(endpoint, plan_args, rounds, warmup):
-    """Device time per round on the endpoint's stream (ms), with a fresh group id (epoch) every round."""
+    """Device time per round on the endpoint's stream (ms), with a fresh group id (epoch) every round.
+    Returns the mean round time and the mean time from each launch's predecessor to its end, by launch name."""
     stream = torch.cuda.ExternalStream(endpoint.stream.value, device=endpoint.device)
-    times = []
+    times, per_launch = [], {}
     for i in range(warmup + rounds):
         plan = endpoint._prepare(group_id=f"bench-{plan_args['tag']}-{i}".encode(), stream=endpoint.stream,
                                  **plan_args["kwargs"])
+        # fresh values every round: repeated averaging of the same tensors converges, and the deltas of converged
+        # peers are an unrepresentative (degenerate) input for the quantising codecs
+        with torch.cuda.stream(stream):
+            endpoint.tensor_views[0].normal_()
+        stream.synchronize()
         if plan_args["barrier"] is not None:
             plan_args["barrier"]()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
+        marks = []
+
+        def mark(name):
+            marks.append((name, torch.cuda.Event(enable_timing=True)))
+            marks[-1][1].record(stream)
+
+        endpoint.launch_hook = mark
+        mark("start")
         endpoint._stage_send(plan, endpoint.stream)
         endpoint._stage_reduce(plan, endpoint.stream)
         endpoint._stage_apply(plan, endpoint.stream)
-        stop.record(stream)
+        endpoint.launch_hook = None
         status = endpoint._read_status(plan, endpoint.stream)
-        stop.synchronize()
+        marks[-1][1].synchronize()
         if status.banned_senders or status.failed_reducers:
             raise RuntimeError(f"round failed: {status.banned_senders} {status.failed_reducers}")
         if i >= warmup:
-            times.append(start.elapsed_time(stop))
-    return sum(times) / len(times)
+            times.append(marks[0][1].elapsed_time(marks[-1][1]))
+            for (_, before), (name, after) in zip(marks, marks[1:]):
+                per_launch.setdefault(name, []).append(before.elapsed_time(after))
+        if plan_args.get("verbose"):  # warm-up rounds too
+            print(f"rank {plan_args['kwargs']['my_index']} {plan_args['tag']} round {i}: " + " ".join(
+                f"{name}={before.elapsed_time(after) * 1e3:.0f}us"
+                for (_, before), (name, after) in zip(marks, marks[1:])), flush=True)
+    stages = {name + "_ms": sum(v) / len(v) for name, v in per_launch.items()}
+    return sum(times) / len(times), stages
 
 
 def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_bytes):
@@ -160,11 +182,12 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
                 kwargs = dict(my_index=rank, device_infos=infos, modes=[AveragingMode.NODE] * n,
                               peer_fractions=[1.0 / n] * n, weights=[1.0] * n, alpha=1.0, sender_timeout=10.0,
                               reducer_timeout=20.0)
-                ms = _time_rounds(endpoint, dict(tag=f"{size_mb}-{codec_name}", kwargs=kwargs, barrier=dist.barrier),
-                                  rounds, warmup)
-                t = torch.tensor([ms], device=device)
+                ms, stages = _time_rounds(endpoint, dict(tag=f"{size_mb}-{codec_name}", kwargs=kwargs,
+                                                         barrier=dist.barrier, verbose=VERBOSE_ROUNDS), rounds, warmup)
+                t = torch.tensor([ms] + list(stages.values()), device=device)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t)
+                ms = float(t[0])
+                stages = {name: float(v) for name, v in zip(stages, t[1:])}
                 dist.barrier()
                 endpoint.close()
             else:
@@ -179,19 +202,26 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
                                        group_id=f"w{size_mb}{codec_name}{i}".encode())
                 torch.cuda.synchronize()
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                start.record()
+                total_ms = 0.0
                 for i in range(rounds):
+                    for e in endpoints:
+                        e.tensor_views[0].normal_()  # fresh values every round (see _time_rounds)
+                    start.record()
                     run_group_emulated(endpoints, weights=[1.0] * n, peer_fractions=[1.0 / n] * n,
                                        group_id=f"t{size_mb}{codec_name}{i}".encode())
-                stop.record()
-                torch.cuda.synchronize()
-                ms = start.elapsed_time(stop) / rounds / n  # n ranks share one GPU: per-rank share of the time
+                    stop.record()
+                    torch.cuda.synchronize()
+                    total_ms += start.elapsed_time(stop)
+                ms = total_ms / rounds / n  # n ranks share one GPU: per-rank share of the time
                 for e in endpoints:
                     e.close()
+                stages = None
             nbytes = numel * 4
             bus = 2 * (n - 1) / n * nbytes / (ms / 1e3) / 1e9
             row = {"size_mb": size_mb, "codec": codec_name, "n_ranks": n, "ms_per_round": ms, "bus_gb_s": bus,
                    "algo_gb_s": nbytes / (ms / 1e3) / 1e9}
+            if stages is not None:
+                row["launches_max_over_ranks"] = stages
             if nccl_ms is not None:
                 row["nccl_fp32_ms"] = nccl_ms
                 row["nccl_fp32_bus_gb_s"] = 2 * (n - 1) / n * nbytes / (nccl_ms / 1e3) / 1e9
@@ -225,7 +255,9 @@ if __name__ == "__main__":
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--emulate-ranks", type=int, default=4)
     parser.add_argument("--part-size-bytes", type=int, default=2 ** 19)
+    parser.add_argument("--verbose-rounds", action="store_true", help="print every launch of every timed round")
     args = parser.parse_args()
+    VERBOSE_ROUNDS = args.verbose_rounds
     if args.increase_file_limit:
         increase_file_limit()
     if args.mode == "device":

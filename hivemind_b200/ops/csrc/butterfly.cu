@@ -14,6 +14,11 @@
 // deltas into its delta box, flags into its flag page) and reads peers' memory with plain loads through
 // peer-mapped pointers (cudaIpc / peer access), CTA by CTA. Nothing here uses TMA or cluster-wide loads.
 //
+// Uncompressed parts (codec NONE) are lossless, so they skip both staging copies: the reducer reads the senders'
+// vectors in place (a sender modifies a part only after the part's owner has published the result for it) and the
+// senders read the owner's average instead of a per-sender delta record; x += alpha * (avg - x) is the same number.
+// Every reducer applies the average to its own span inside the reduce kernel.
+//
 // Phases (separate launches on one stream per GPU; a phase that consumes remote data first waits, bounded, on the
 // producer's flag):  [stats] -> [borders] -> encode -> publish   |   reduce -> [delta borders] -> encode deltas ->
 // publish deltas   |   apply.  One launch can cover one rank (normal operation, one process per GPU) or, for
@@ -36,6 +41,7 @@ struct HbPeer {
   unsigned char* deltabox;     // as reducer: region of sender s starts at deltabox + s * delta_stride
   unsigned int* ready;         // [n_parts] == epoch once the outbox record of part p is complete
   unsigned int* delta_ready;   // [HB_MAX_PEERS][max_local_parts]: epoch (| HB_FAIL_BIT) once the delta is complete
+  float* avg;                  // as reducer: averages of its own span (read by senders of uncompressed parts)
 };
 
 struct HbPart {
@@ -371,8 +377,11 @@ hb_encode_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items,
   __shared__ float red[32];
   __shared__ float cb[256];          // codebook of the record being replaced (mode 1)
   __shared__ float table[256];       // quantile borders
-  __shared__ float hsum[256];
-  __shared__ int hcnt[256];
+  // per-warp bin sums and counts: a skewed distribution (most values in a few bins) would otherwise serialise the
+  // whole CTA on a handful of shared-memory addresses
+  __shared__ float hsum[HB_THREADS / 32][256];
+  __shared__ int hcnt[HB_THREADS / 32][256];
+  const int warp = threadIdx.x >> 5;
   const HbGroup& g = *gp;
   const int4 it = items[blockIdx.x];
   const HbItemCtx c = hb_item_ctx(g, it.x, it.z, mode);
@@ -381,7 +390,7 @@ hb_encode_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items,
   hb_source_setup(src, g, c, mode, cb);
   const bool binned = codec == HB_UNIFORM8 || codec == HB_QUANTILE8;
   if (binned) {
-    for (int i = threadIdx.x; i < 256; i += HB_THREADS) { hsum[i] = 0.f; hcnt[i] = 0; }
+    for (int i = threadIdx.x; i < 256 * (HB_THREADS / 32); i += HB_THREADS) { (&hsum[0][0])[i] = 0.f; (&hcnt[0][0])[i] = 0; }
     if (codec == HB_QUANTILE8)
       for (int i = threadIdx.x; i < 256; i += HB_THREADS) table[i] = c.borders[i];
   }
@@ -453,8 +462,8 @@ hb_encode_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items,
           b = b < 0 ? 0 : (b > 255 ? 255 : b);
           q[k] = (unsigned char)b;
           if (binned && k < valid) {
-            atomicAdd(&hsum[b], v[r][k]);
-            atomicAdd(&hcnt[b], 1);
+            atomicAdd(&hsum[warp][b], v[r][k]);
+            atomicAdd(&hcnt[warp][b], 1);
           }
         }
         if (valid == 4) *reinterpret_cast<uchar4*>(payload + i) = make_uchar4(q[0], q[1], q[2], q[3]);
@@ -465,9 +474,13 @@ hb_encode_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items,
   if (binned) {
     __syncthreads();
     for (int i = threadIdx.x; i < 256; i += HB_THREADS) {
-      if (hcnt[i]) {
-        atomicAdd(c.bins + i, hsum[i]);
-        atomicAdd(c.cnt + i, hcnt[i]);
+      float total = 0.f;
+      int count = 0;
+#pragma unroll
+      for (int w = 0; w < HB_THREADS / 32; ++w) { total += hsum[w][i]; count += hcnt[w][i]; }
+      if (count) {
+        atomicAdd(c.bins + i, total);
+        atomicAdd(c.cnt + i, count);
       }
     }
   }
@@ -507,7 +520,7 @@ hb_publish_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items
 // Reduce (the reduce-scatter half): for one chunk of one of my parts, wait (bounded) for every sender's record,
 // pull the chunk over NVLink once into the local delta box, average, store the average and accumulate the
 // statistics that the per-sender delta encoders will need.
-__global__ void __launch_bounds__(HB_THREADS)
+__global__ void __launch_bounds__(HB_THREADS, 4)
 hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) {
   __shared__ float cbs[HB_MAX_PEERS][256];
   __shared__ float red[32];
@@ -539,9 +552,10 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
   }
   __syncthreads();
 
+  const bool direct = codec == HB_NONE;  // lossless part: accumulate straight from the senders' vectors
   // pull: remote record chunk -> local copy (each byte crosses NVLink once), headers as far as this CTA needs them
   for (int s = 0; s < g.n_peers; ++s) {
-    if (!inc[s]) continue;
+    if (!inc[s] || direct) continue;
     const unsigned char* remote = g.peer[s].outbox + part.enc_off;
     unsigned char* local = g.peer[me].deltabox + (size_t)s * g.delta_stride + part.span_off;
     const size_t b0 = (size_t)lo * eb, b1 = ((size_t)hi * eb + 15) / 16 * 16;
@@ -575,8 +589,9 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
   float den = i_send ? g.weight[me] : 0.f;
   for (int s = 0; s < g.n_peers; ++s) if (inc[s]) den += g.weight[s];
   const float inv_den = den > 0.f ? 1.f / den : 0.f;
-  const float* x_local = g.peer[me].data + part.start;
+  float* x_local = g.peer[me].data + part.start;
   float* avg_out = g.avg + part.avg_off;
+  const float alpha = g.alpha;
   const bool need_stats = codec == HB_MEANSTD16 || codec == HB_UNIFORM8;
 
   for (int b0 = lo; b0 < hi; b0 += HB_BLOCK) {
@@ -595,6 +610,30 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
     }
     for (int s = 0; s < g.n_peers; ++s) {
       if (!inc[s]) continue;
+      const float w = g.weight[s];
+      if (direct) {
+        // four independent 16-byte loads from the sender's memory per thread, issued before the first use
+        const float* __restrict__ rx = g.peer[s].data + part.start;
+        float4 rv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int i = b0 + (r * HB_THREADS + threadIdx.x) * 4;
+          if (i + 4 <= len) {
+            rv[r] = *reinterpret_cast<const float4*>(rx + i);
+          } else {
+            rv[r].x = i < len ? rx[i] : 0.f;
+            rv[r].y = i + 1 < len ? rx[i + 1] : 0.f;
+            rv[r].z = i + 2 < len ? rx[i + 2] : 0.f;
+            rv[r].w = 0.f;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          acc[r][0] = fmaf(w, rv[r].x, acc[r][0]); acc[r][1] = fmaf(w, rv[r].y, acc[r][1]);
+          acc[r][2] = fmaf(w, rv[r].z, acc[r][2]); acc[r][3] = fmaf(w, rv[r].w, acc[r][3]);
+        }
+        continue;
+      }
       const unsigned char* rec = g.peer[me].deltabox + (size_t)s * g.delta_stride + part.span_off;
       HbDecode dec;
       dec.codec = codec;
@@ -605,7 +644,6 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
         const float* rh = reinterpret_cast<const float*>(g.peer[s].outbox + part.enc_off);
         dec.mean = rh[0]; dec.std = rh[1];
       }
-      const float w = g.weight[s];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         float v[4];
@@ -619,12 +657,23 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
       const int i = b0 + (r * HB_THREADS + threadIdx.x) * 4;
 #pragma unroll
       for (int k = 0; k < 4; ++k) acc[r][k] *= inv_den;
+      // store the average (senders' deltas are computed from it) and apply it to this reducer's own values
       if (i + 4 <= len) {
         *reinterpret_cast<float4*>(avg_out + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        if (i_send) {
+          float4 own = *reinterpret_cast<const float4*>(x_local + i);
+          own.x = fmaf(alpha, acc[r][0] - own.x, own.x); own.y = fmaf(alpha, acc[r][1] - own.y, own.y);
+          own.z = fmaf(alpha, acc[r][2] - own.z, own.z); own.w = fmaf(alpha, acc[r][3] - own.w, own.w);
+          *reinterpret_cast<float4*>(x_local + i) = own;
+        }
       } else {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (i + k < len) avg_out[i + k] = acc[r][k];
+        for (int k = 0; k < 4; ++k) {
+          if (i + k < len) {
+            avg_out[i + k] = acc[r][k];
+            if (i_send) x_local[i + k] = fmaf(alpha, acc[r][k] - x_local[i + k], x_local[i + k]);
+          }
+        }
       }
     }
     if (need_stats) {
@@ -667,7 +716,8 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
   }
 }
 
-// Apply (the all-gather half): x += alpha * (avg - x) on my own span, x += alpha * decode(delta) elsewhere.
+// Apply (the all-gather half) for the parts that other peers reduced: x += alpha * decode(delta), or
+// x += alpha * (avg - x) with the owner's average for uncompressed parts.
 __global__ void __launch_bounds__(HB_THREADS)
 hb_apply_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) {
   __shared__ float cb[256];
@@ -680,9 +730,20 @@ hb_apply_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) 
   if (!g.sends[me]) return;
   float* x = g.peer[me].data + part.start;
   const float alpha = g.alpha;
-  if (owner == me) {
-    const float* __restrict__ avg = g.avg + part.avg_off;
-    // chunk starts are multiples of 16 elements: float4 accesses, four per thread in flight
+  if (owner == me) return;  // the reduce kernel has already applied the average to this GPU's own span
+  const unsigned long long deadline = hb_phase_start(g.t_start + 1) + g.reducer_timeout_ns;
+  const unsigned int* flag = g.peer[owner].delta_ready + (size_t)me * g.max_local_parts + part.local_idx;
+  const int d = hb_wait_decide(flag, g.epoch, g.apply_decision + it.x, nullptr, deadline, &wait_out);
+  if (d != 1) {
+    if (threadIdx.x == 0) {
+      atomicOr(g.status + 1, 1ull << owner);
+      atomicAdd(g.status + 2, (unsigned long long)(hi - lo));
+    }
+    return;  // zero delta: keep local values
+  }
+  if (part.codec == HB_NONE) {
+    // uncompressed part: pull the owner's average itself; chunk starts are multiples of 16 elements
+    const float* __restrict__ avg = g.peer[owner].avg + part.avg_off;
     const int n4 = (hi - lo) / 4;
     float4* x4 = reinterpret_cast<float4*>(x + lo);
     const float4* a4 = reinterpret_cast<const float4*>(avg + lo);
@@ -690,7 +751,7 @@ hb_apply_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) 
     for (; q + 3 * HB_THREADS < n4; q += 4 * HB_THREADS) {
       float4 xv[4], av[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) { xv[u] = x4[q + u * HB_THREADS]; av[u] = a4[q + u * HB_THREADS]; }
+      for (int u = 0; u < 4; ++u) { av[u] = a4[q + u * HB_THREADS]; xv[u] = x4[q + u * HB_THREADS]; }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         xv[u].x = fmaf(alpha, av[u].x - xv[u].x, xv[u].x); xv[u].y = fmaf(alpha, av[u].y - xv[u].y, xv[u].y);
@@ -707,16 +768,6 @@ hb_apply_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items) 
     }
     for (int i = lo + n4 * 4 + threadIdx.x; i < hi; i += HB_THREADS) x[i] = fmaf(alpha, avg[i] - x[i], x[i]);
     return;
-  }
-  const unsigned long long deadline = hb_phase_start(g.t_start + 1) + g.reducer_timeout_ns;
-  const unsigned int* flag = g.peer[owner].delta_ready + (size_t)me * g.max_local_parts + part.local_idx;
-  const int d = hb_wait_decide(flag, g.epoch, g.apply_decision + it.x, nullptr, deadline, &wait_out);
-  if (d != 1) {
-    if (threadIdx.x == 0) {
-      atomicOr(g.status + 1, 1ull << owner);
-      atomicAdd(g.status + 2, (unsigned long long)(hi - lo));
-    }
-    return;  // zero delta: keep local values
   }
   const unsigned char* rec = g.peer[owner].deltabox + (size_t)me * g.delta_stride + part.span_off;
   HbDecode dec;

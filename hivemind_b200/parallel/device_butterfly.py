@@ -48,6 +48,7 @@ PH_STATS, PH_BORDERS, PH_ENCODE, PH_PUBLISH, PH_REDUCE, PH_APPLY = range(6)
 _CODEC_IDS = {NoCompression: 0, ScaledFloat16Compression: 1, Float16Compression: 2, Quantile8BitQuantization: 3,
               Uniform8BitQuantization: 4, BlockwiseQuantization: 5}
 _NEEDS_STATS, _NEEDS_BORDERS = (1, 4), (3,)
+CODEC_NONE = 0  # uncompressed parts take the in-place path (no outbox record, no delta record)
 
 
 def codec_id(compression: CompressionBase, info: CompressionInfo) -> Optional[int]:
@@ -59,7 +60,7 @@ def codec_id(compression: CompressionBase, info: CompressionInfo) -> Optional[in
 
 class _HbPeer(ctypes.Structure):
     _fields_ = [("data", ctypes.c_void_p), ("outbox", ctypes.c_void_p), ("deltabox", ctypes.c_void_p),
-                ("ready", ctypes.c_void_p), ("delta_ready", ctypes.c_void_p)]
+                ("ready", ctypes.c_void_p), ("delta_ready", ctypes.c_void_p), ("avg", ctypes.c_void_p)]
 
 
 class _HbGroup(ctypes.Structure):
@@ -215,6 +216,7 @@ class DeviceEndpoint:
         self._plans: Dict[Tuple, _Plan] = {}
         self._host_status = (ctypes.c_ulonglong * 4)()
         self._closed = False
+        self.launch_hook = None
         self.uid = os.urandom(8)
 
     # ---------------------------------------------------------------------------------------------- handles
@@ -332,15 +334,17 @@ class DeviceEndpoint:
         theirs = [p for p in range(n_parts) if table[p]["owner"] != my_index] if i_send else []
         senders = [s for s in range(n_peers) if s != my_index and sends[s]]
         lists = {
-            "enc": [(p, c, 0, 0) for p in theirs for c in chunks_of(p)],
+            # uncompressed parts have no records: reducers read the vector in place, senders read the average
+            "enc": [(p, c, 0, 0) for p in theirs if table[p]["codec"] != CODEC_NONE for c in chunks_of(p)],
             "enc_stats": [(p, c, 0, 0) for p in theirs if table[p]["codec"] in _NEEDS_STATS for c in chunks_of(p)],
             "enc_borders": [(p, 0, 0, 0) for p in theirs if table[p]["codec"] in _NEEDS_BORDERS],
             "enc_publish": [(p, 0, 0, 0) for p in theirs],
             "reduce": [(p, c, 0, 0) for p in mine for c in chunks_of(p)],
-            "delta": [(p, c, s, 0) for s in senders for p in mine for c in chunks_of(p)],
+            "delta": [(p, c, s, 0) for s in senders for p in mine if table[p]["codec"] != CODEC_NONE
+                      for c in chunks_of(p)],
             "delta_borders": [(p, 0, s, 0) for s in senders for p in mine if table[p]["codec"] in _NEEDS_BORDERS],
             "delta_publish": [(p, 0, s, 0) for s in senders for p in mine],
-            "apply": [(p, c, 0, 0) for p in range(n_parts) for c in chunks_of(p)] if i_send else [],
+            "apply": [(p, c, 0, 0) for p in theirs for c in chunks_of(p)],  # own span: applied by the reduce kernel
         }
         items = {k: torch.tensor(v if v else [(0, 0, 0, 0)], dtype=torch.int32).to(self.device) for k, v in lists.items()}
         counts = {k: len(v) for k, v in lists.items()}
@@ -385,6 +389,7 @@ class DeviceEndpoint:
             g.peer[r].deltabox = base + lay["deltabox"]
             g.peer[r].ready = base + lay["ready"]
             g.peer[r].delta_ready = base + lay["delta_ready"]
+            g.peer[r].avg = base + lay["avg"]
         g.parts = plan.parts_dev.data_ptr()
         for name in ("part_stats", "dstats", "bins", "bin_cnt", "dbins", "dbin_cnt", "borders", "dborders", "include",
                      "apply_decision", "ban", "t_start", "status"):
@@ -407,6 +412,8 @@ class DeviceEndpoint:
             code = self.lib.hm_bf_launch(phase, ctypes.c_void_p(plan.group_dev.data_ptr()),
                                          ctypes.c_void_p(plan.items[items].data_ptr()), count, mode, stream)
         _lib.check(code, f"hm_bf_launch(phase={phase}, {items})")
+        if self.launch_hook is not None:
+            self.launch_hook(items)  # benchmarks record an event after every launch of a round
 
     # the three stages of a round; in normal operation they are launched back to back on one stream
     def _stage_send(self, plan, stream) -> None:
