@@ -250,7 +250,7 @@ if __name__ == "__main__":
     parser.add_argument("--spawn_dtime", type=float, default=0.1)
     parser.add_argument("--increase_file_limit", action="store_true")
     parser.add_argument("--sizes-mb", type=float, nargs="+", default=[1, 16, 64, 256])
-    parser.add_argument("--codecs", nargs="+", default=["none", "float16", "uniform8"])
+    parser.add_argument("--codecs", nargs="+", default=["none", "float16", "uniform8"], choices=sorted(CODECS))
     parser.add_argument("--rounds", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--emulate-ranks", type=int, default=4)

@@ -132,6 +132,9 @@ __device__ __forceinline__ void hb_decode_setup(HbDecode& d, int codec, const un
     d.std = reinterpret_cast<const float*>(rec)[1];
   } else if (codec == HB_UNIFORM8 || codec == HB_QUANTILE8) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) codebook_smem[i] = reinterpret_cast<const float*>(rec)[i];
+  } else if (codec == HB_BLOCKWISE8) {
+    // constant memory serialises lanes that index it differently: look the code up in shared memory instead
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) codebook_smem[i] = hb_code[i];
   }
 }
 
@@ -164,7 +167,8 @@ __device__ __forceinline__ void hb_decode4(const HbDecode& d, const float* codeb
       default: {  // HB_BLOCKWISE8
         uchar4 q = *reinterpret_cast<const uchar4*>(d.payload + i);
         const float a = d.absmax[i / HB_BLOCK];
-        v[0] = hb_code[q.x] * a; v[1] = hb_code[q.y] * a; v[2] = hb_code[q.z] * a; v[3] = hb_code[q.w] * a;
+        v[0] = codebook_smem[q.x] * a; v[1] = codebook_smem[q.y] * a;
+        v[2] = codebook_smem[q.z] * a; v[3] = codebook_smem[q.w] * a;
         return;
       }
     }
@@ -179,7 +183,7 @@ __device__ __forceinline__ void hb_decode4(const HbDecode& d, const float* codeb
       case HB_MEANSTD16: v[k] = fmaf(__half2float(reinterpret_cast<const __half*>(d.payload)[e]), d.std, d.mean); break;
       case HB_UNIFORM8:
       case HB_QUANTILE8: v[k] = codebook_smem[d.payload[e]]; break;
-      default: v[k] = hb_code[d.payload[e]] * d.absmax[e / HB_BLOCK]; break;
+      default: v[k] = codebook_smem[d.payload[e]] * d.absmax[e / HB_BLOCK]; break;
     }
   }
 }
@@ -394,6 +398,8 @@ hb_encode_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items,
     if (codec == HB_QUANTILE8)
       for (int i = threadIdx.x; i < 256; i += HB_THREADS) table[i] = c.borders[i];
   }
+  if (codec == HB_BLOCKWISE8)
+    for (int i = threadIdx.x; i < 256; i += HB_THREADS) table[i] = hb_code_mid[i];
   float mean = 0.f, inv_scale = 1.f;
   if (codec == HB_MEANSTD16 || codec == HB_UNIFORM8) {
     const double n = (double)len, s1 = c.stats[0], s2 = c.stats[1];
@@ -458,7 +464,7 @@ hb_encode_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items,
           int b;
           if (codec == HB_UNIFORM8) b = (int)rintf((v[r][k] - mean) * inv_scale) + 128;
           else if (codec == HB_QUANTILE8) b = hb_bucketize(table, v[r][k]);
-          else b = hb_bucketize(hb_code_mid, v[r][k] * inv_absmax);
+          else b = hb_bucketize(table, v[r][k] * inv_absmax);
           b = b < 0 ? 0 : (b > 255 ? 255 : b);
           q[k] = (unsigned char)b;
           if (binned && k < valid) {
@@ -578,6 +584,7 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
     } else if (codec == HB_MEANSTD16) {
       if (it.y == 0 && threadIdx.x < 2) reinterpret_cast<float*>(local)[threadIdx.x] = reinterpret_cast<const float*>(remote)[threadIdx.x];
     } else if (codec == HB_BLOCKWISE8) {
+      cbs[s][threadIdx.x] = hb_code[threadIdx.x];  // shared-memory copy of the code (see hb_decode_setup)
       const int blk0 = lo / HB_BLOCK, blk1 = (hi + HB_BLOCK - 1) / HB_BLOCK;
       if (threadIdx.x < blk1 - blk0)
         reinterpret_cast<float*>(local)[blk0 + threadIdx.x] = reinterpret_cast<const float*>(remote)[blk0 + threadIdx.x];
