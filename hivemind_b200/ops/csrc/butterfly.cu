@@ -559,8 +559,12 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
   __syncthreads();
 
   const bool direct = codec == HB_NONE;  // lossless part: accumulate straight from the senders' vectors
+  // every reducer walks the senders in its own rotation (and every chunk starts one further), so that at any moment
+  // the reducers of a group read from different GPUs instead of all draining the same sender's links
+  const int rot = (me + 1 + (int)(blockIdx.x % (unsigned)g.n_peers)) % g.n_peers;
   // pull: remote record chunk -> local copy (each byte crosses NVLink once), headers as far as this CTA needs them
-  for (int s = 0; s < g.n_peers; ++s) {
+  for (int t = 0; t < g.n_peers; ++t) {
+    const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
     if (!inc[s] || direct) continue;
     const unsigned char* remote = g.peer[s].outbox + part.enc_off;
     unsigned char* local = g.peer[me].deltabox + (size_t)s * g.delta_stride + part.span_off;
@@ -615,7 +619,8 @@ hb_reduce_kernel(const HbGroup* __restrict__ gp, const int4* __restrict__ items)
         for (int k = 0; k < 4; ++k) acc[r][k] = (i_send && i + k < len) ? g.weight[me] * x_local[i + k] : 0.f;
       }
     }
-    for (int s = 0; s < g.n_peers; ++s) {
+    for (int t = 0; t < g.n_peers; ++t) {
+      const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
       if (!inc[s]) continue;
       const float w = g.weight[s];
       if (direct) {

@@ -149,6 +149,29 @@ class _Plan:
     needed_delta: int
 
 
+def _interleave_by_owner(items: List[Tuple[int, int, int, int]], owners: List[int], first_owner: int,
+                         n_peers: int) -> List[Tuple[int, int, int, int]]:
+    """Order work items round-robin over the GPUs they read from, starting at ``first_owner``.
+
+    CTAs start in list order. With items grouped by owner, every member of a group would pull from owner 0 first,
+    then from owner 1, ...: at any moment one GPU's outgoing links serve all readers while the others idle. Rotated
+    and interleaved, concurrent reads are spread evenly over all owners.
+    """
+    queues: Dict[int, List[Tuple[int, int, int, int]]] = {}
+    for item, owner in zip(items, owners):
+        queues.setdefault(owner, []).append(item)
+    order = [(first_owner + t) % n_peers for t in range(n_peers)]
+    cursors = {owner: 0 for owner in queues}
+    merged = []
+    while len(merged) < len(items):
+        for owner in order:
+            queue = queues.get(owner)
+            if queue is not None and cursors[owner] < len(queue):
+                merged.append(queue[cursors[owner]])
+                cursors[owner] += 1
+    return merged
+
+
 class DeviceEndpoint:
     """The device-side state of one averager: arena, mappings of groupmates' arenas, cached plans."""
 
@@ -344,7 +367,9 @@ class DeviceEndpoint:
                       for c in chunks_of(p)],
             "delta_borders": [(p, 0, s, 0) for s in senders for p in mine if table[p]["codec"] in _NEEDS_BORDERS],
             "delta_publish": [(p, 0, s, 0) for s in senders for p in mine],
-            "apply": [(p, c, 0, 0) for p in theirs for c in chunks_of(p)],  # own span: applied by the reduce kernel
+            "apply": _interleave_by_owner([(p, c, 0, 0) for p in theirs for c in chunks_of(p)],  # own span: applied
+                                          [int(table[p]["owner"]) for p in theirs for _ in chunks_of(p)],  # by reduce
+                                          first_owner=(my_index + 1) % n_peers, n_peers=n_peers),
         }
         items = {k: torch.tensor(v if v else [(0, 0, 0, 0)], dtype=torch.int32).to(self.device) for k, v in lists.items()}
         counts = {k: len(v) for k, v in lists.items()}
