@@ -79,3 +79,16 @@ class ScaledFloat16Compression(Float16Compression):
         half = np.frombuffer(buf[:-8 * stats_count], dtype=np.float16)
         out = torch.as_tensor(np.asarray(half, dtype=np.float32)).reshape(shape).mul_(stds).add_(means)
         return out.to(getattr(torch, serialized_tensor.dtype)).requires_grad_(serialized_tensor.requires_grad)
+
+
+def get_num_bits(dtype: torch.dtype) -> int:
+    """Storage bits of one element of ``dtype`` (reference: hivemind/compression/floating.py:94-104)."""
+    if dtype == torch.bool:
+        return 8  # a bool tensor spends a whole byte per element
+    info = torch.finfo(dtype) if dtype.is_floating_point else None
+    if info is not None:
+        return info.bits
+    try:
+        return torch.iinfo(dtype).bits
+    except TypeError:
+        raise TypeError(f"cannot tell the width of {dtype}") from None

@@ -151,3 +151,9 @@ class TrainingAverager(DecentralizedAverager):
                 local_param[...] = loaded_param.to(local_param.device, local_param.dtype)
             load_optimizer_state(self.opt, metadata["optimizer_metadata"], loaded_opt_tensors)
         self.local_step = max(self.local_step, metadata["step"])
+
+
+def initialize_optimizer_state(opt: torch.optim.Optimizer) -> None:
+    """Make ``opt`` allocate its statistics by taking one step with zero gradients
+    (reference: hivemind/optim/training_averager.py:220-225)."""
+    initialize_optimizer_state_(opt)

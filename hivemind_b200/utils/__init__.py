@@ -6,4 +6,5 @@ from hivemind_b200.utils.nested import nested_compare, nested_flatten, nested_ma
 from hivemind_b200.utils.performance_ema import PerformanceEMA
 from hivemind_b200.utils.serializer import MSGPackSerializer, SerializerBase
 from hivemind_b200.utils.tensor_descr import BatchTensorDescriptor, TensorDescriptor
-from hivemind_b200.utils.timed_storage import DHTExpiration, TimedStorage, ValueWithExpiration, get_dht_time
+from hivemind_b200.utils.timed_storage import (MAX_DHT_TIME_DISCREPANCY_SECONDS, DHTExpiration, TimedStorage,
+                                               ValueWithExpiration, get_dht_time)

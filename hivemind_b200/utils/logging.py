@@ -130,3 +130,40 @@ def daemon_level_to_python(level: str) -> int:
 def python_level_to_daemon(level: str) -> str:
     level = level.upper()
     return {"WARNING": "WARN", "CRITICAL": "FATAL"}.get(level, level)
+
+
+TRUE_CONSTANTS = ("1", "true", "yes", "on")  # accepted spellings of a set boolean environment variable
+
+_GOLOG_TO_PYTHON = {"DPANIC": logging.CRITICAL, "PANIC": logging.CRITICAL, "FATAL": logging.CRITICAL,
+                    "WARN": logging.WARNING}
+
+
+def golog_level_to_python(level: str) -> int:
+    """Map a level name of the Go logging convention (used by libp2p daemons) to a ``logging`` level
+    (reference: hivemind/utils/logging.py:192-201)."""
+    level = level.upper()
+    if level in _GOLOG_TO_PYTHON:
+        return _GOLOG_TO_PYTHON[level]
+    value = logging.getLevelName(level)
+    if not isinstance(value, int):
+        raise ValueError(f"unknown log level: {level}")
+    return value
+
+
+def python_level_to_golog(level: Union[str, int]) -> str:
+    """The inverse mapping (reference: hivemind/utils/logging.py:204-212); ``level`` is a name or a number."""
+    if isinstance(level, int):
+        level = logging.getLevelName(level)
+    if not isinstance(level, str):
+        raise ValueError(f"unknown log level: {level}")
+    level = level.upper()
+    return {"WARNING": "WARN", "CRITICAL": "FATAL"}.get(level, level)
+
+
+def in_ipython() -> bool:
+    """True inside IPython / Jupyter, where the coloured handler should keep to the notebook's own stream."""
+    try:
+        get_ipython  # noqa: F821  (defined by IPython in its namespaces)
+        return True
+    except NameError:
+        return False

@@ -9,7 +9,7 @@ from __future__ import annotations
 from typing import Any, Iterator
 
 
-def _is_namedtuple(x: Any) -> bool:
+def is_namedtuple(x: Any) -> bool:
     return isinstance(x, tuple) and hasattr(type(x), "_fields") and all(isinstance(f, str) for f in type(x)._fields)
 
 
@@ -26,7 +26,7 @@ def nested_flatten(t: Any) -> Iterator[Any]:
 
 
 def _pack(it: Iterator[Any], structure: Any) -> Any:
-    if _is_namedtuple(structure):
+    if is_namedtuple(structure):
         return type(structure)(*[_pack(it, s) for s in structure])
     if isinstance(structure, (list, tuple)):
         return type(structure)(_pack(it, s) for s in structure)

@@ -230,3 +230,29 @@ def test_device_range_is_a_no_op_without_a_gpu_or_when_disabled():
     with profiling.device_range("anything"):
         pass
     assert "anything" not in profiling.timing_summary()
+
+
+def test_small_parity_helpers():
+    import collections
+    import logging
+
+    import torch
+
+    from hivemind_b200.compression.floating import get_num_bits
+    from hivemind_b200.optim.training_averager import initialize_optimizer_state
+    from hivemind_b200.utils import MAX_DHT_TIME_DISCREPANCY_SECONDS
+    from hivemind_b200.utils.logging import golog_level_to_python, in_ipython, python_level_to_golog
+    from hivemind_b200.utils.nested import is_namedtuple
+
+    assert MAX_DHT_TIME_DISCREPANCY_SECONDS > 0
+    assert get_num_bits(torch.bool) == 8 and get_num_bits(torch.bfloat16) == 16 and get_num_bits(torch.int64) == 64
+    point = collections.namedtuple("point", "x y")(1, 2)
+    assert is_namedtuple(point) and not is_namedtuple((1, 2))
+    assert golog_level_to_python("warn") == logging.WARNING and golog_level_to_python("PANIC") == logging.CRITICAL
+    assert python_level_to_golog(logging.WARNING) == "WARN" and python_level_to_golog("debug") == "DEBUG"
+    assert in_ipython() is False
+    layer = torch.nn.Linear(3, 2)
+    before = layer.weight.detach().clone()
+    opt = torch.optim.Adam(layer.parameters(), lr=0.1)
+    initialize_optimizer_state(opt)
+    assert len(opt.state) == 2 and torch.equal(layer.weight, before)
