@@ -240,6 +240,8 @@ class TensorPartReducer:
         """Add a sender's part; resolves to the average of that part once every live sender has contributed."""
         assert 0 <= sender_index < self.num_senders, "invalid sender index"
         assert 0 <= part_index < self.num_parts, "invalid part index"
+        if self.finished.is_set():  # a straggler after the last part (or after a shutdown) gets a clean error
+            raise AllreduceException(f"attempted to aggregate part in a finalized {self.__class__.__name__}")
         self.num_parts_received[sender_index] += 1
         while part_index > self.current_part_index:
             # wait for previous parts to finish; a sender may run ahead of the others
