@@ -244,9 +244,14 @@ struct Daemon {
         p->partner = 0;
         if (p->kind == Kind::SPLICE) {
           // let queued bytes drain, then finish the partner's write side
+          const uint64_t partner_id = p->id;
           p->wr_shutdown_pending = true;
           p->rd_closed = true;
           flush(p);
+          // if the partner's write side had been finished earlier (its stream had already sent EOF), flush() has
+          // nothing left to trigger on: close it here, so that the far end learns that nobody reads any more
+          Conn* q = get(partner_id);
+          if (q && q->wr_closed && q->out_off == q->out.size()) close_conn(partner_id, "stream partner closed");
         } else {
           close_conn(p->id, "stream partner closed");
         }

@@ -316,8 +316,9 @@ class P2P:
                     yield request
 
             async def _process_stream() -> None:
+                responses = handler(_read_stream(), context)
                 try:
-                    async for response in handler(_read_stream(), context):
+                    async for response in responses:
                         try:
                             await P2P.send_protobuf(response, writer)
                         except Exception:
@@ -327,6 +328,13 @@ class P2P:
                     logger.warning(f"handler {name} failed:", exc_info=True)
                     with suppress(Exception):
                         await P2P.send_protobuf(RPCError(str(e) or repr(e)), writer)
+                finally:
+                    # a caller that walked away must not leave the handler's generator suspended until it is
+                    # garbage-collected: close it now, so that its ``finally`` blocks run
+                    close = getattr(responses, "aclose", None)
+                    if close is not None:
+                        with suppress(Exception):
+                            await close()
 
             with closing(writer):
                 processing_task = asyncio.create_task(_process_stream())

@@ -1,6 +1,7 @@
 """Transport daemon + P2P wrapper + servicer reflection (cases modelled on the reference's tests/test_p2p_daemon.py
 and tests/test_p2p_servicer.py: unary and streaming handlers, errors, cancellation, replicas, balanced handlers)."""
 import asyncio
+import contextlib
 from typing import AsyncIterator
 
 import pytest
@@ -218,3 +219,64 @@ def test_peer_id_derivation_is_stable():
     key = rsa.generate_private_key(public_exponent=65537, key_size=2048)
     a, b = PeerID.from_private_key(key), PeerID.from_private_key(key)
     assert a == b and a.to_base58().startswith("Qm") and PeerID.from_base58(a.to_base58()) == a
+
+
+class _EndlessServicer(ServicerBase):
+    def __init__(self):
+        self.started, self.cancelled = asyncio.Event(), asyncio.Event()
+
+    async def rpc_ticks(self, request: test_pb2.TestRequest, _context: P2PContext) -> AsyncIterator[test_pb2.TestResponse]:
+        self.started.set()
+        try:
+            i = 0
+            while True:
+                yield test_pb2.TestResponse(number=i)
+                i += 1
+                await asyncio.sleep(0.05)
+        except (asyncio.CancelledError, GeneratorExit):
+            self.cancelled.set()
+            raise
+        finally:
+            self.cancelled.set()
+
+
+def test_streaming_handler_stops_when_the_caller_walks_away():
+    """A client that abandons a response stream (reference: test_unary_stream_cancel in tests/test_p2p_servicer.py):
+    the server-side generator is closed instead of producing forever."""
+    async def main():
+        server, client = await _pair()
+        servicer = _EndlessServicer()
+        await servicer.add_p2p_handlers(server)
+        stub = _EndlessServicer.get_stub(client, server.peer_id)
+
+        async def consume_three():
+            received = []
+            async with contextlib.aclosing(await stub.rpc_ticks(test_pb2.TestRequest(number=0))) as ticks:
+                async for item in ticks:
+                    received.append(item.number)
+                    if len(received) == 3:
+                        break
+            return received
+
+        assert await consume_three() == [0, 1, 2]
+        await asyncio.wait_for(servicer.started.wait(), 5)
+        await asyncio.wait_for(servicer.cancelled.wait(), 10)
+        # the connection pair stays usable afterwards
+        servicer.started.clear()
+        servicer.cancelled.clear()
+        assert (await consume_three()) == [0, 1, 2]
+        await client.shutdown()
+        await server.shutdown()
+
+    run(main())
+
+
+def test_dead_daemon_is_reported_and_shutdown_is_idempotent():
+    async def main():
+        node = await P2P.create()
+        assert node.is_alive
+        await node.shutdown()
+        await node.shutdown()  # second call is a no-op
+        assert not node.is_alive
+
+    run(main())
