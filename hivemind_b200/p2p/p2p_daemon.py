@@ -122,6 +122,9 @@ class P2P:
                 logger.debug(f"listen address {maddr} is not supported by the transport daemon; skipped")
         if not tcp_set:
             args.append("--no-tcp")
+        # same switch as for the reference's Go daemon (hivemind/p2p/p2p_daemon.py:222): the daemon's own log
+        if os.environ.get("GOLOG_LOG_LEVEL", "").strip().lower() == "debug":
+            args.append("--verbose")
         self._child = subprocess.Popen(args, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, bufsize=1)
         self._alive = True
         ready = asyncio.get_event_loop().create_future()
@@ -467,7 +470,7 @@ class P2P:
             for line in child.stderr:
                 line = line.rstrip()
                 if line:
-                    logger.debug(f"[hmp2pd] {line}")
+                    logger.debug(line if line.startswith("[hmp2pd]") else f"[hmp2pd] {line}")
         except Exception:
             pass
         finally:
