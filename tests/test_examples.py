@@ -44,3 +44,24 @@ def test_albert_example_trainers_and_monitor(tmp_path):
         for proc in procs:
             if proc.poll() is None:
                 proc.kill()
+
+
+def test_powersgd_benchmark_runs_on_cpu_with_two_ranks():
+    """benchmarks/benchmark_powersgd.py end to end on the tiny GPT-2 (gloo ranks, host timers): the PowerSGD
+    averager finishes its steps and the script prints one JSON line with positive throughput."""
+    import json
+
+    for averager in ("powersgd",):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", "29577", os.path.join(ROOT, "benchmarks/benchmark_powersgd.py"),
+               "--model", "tiny", "--steps", "2", "--warmup", "3", "--rank-r", "4", "--batch", "2", "--seq-len", "32",
+               "--averager", averager]
+        done = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
+        assert done.returncode == 0, done.stderr[-2000:]
+        lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+        assert len(lines) == 1, done.stdout[-2000:]
+        row = json.loads(lines[0])
+        assert row["n_gpus"] == 2 and row["value"] > 0 and row["steps"] == 2
+        assert row["config"]["model"] == "gpt2-tiny"
+        if averager == "powersgd":
+            assert row["averaged_elements_per_round"] < row["parameters"]  # factors are smaller than the gradients
