@@ -245,8 +245,11 @@ class TensorPartReducer:
         self.num_parts_received[sender_index] += 1
         while part_index > self.current_part_index:
             # wait for previous parts to finish; a sender may run ahead of the others
-            await asyncio.wait({self.current_part_future, asyncio.create_task(self.finished.wait())},
-                               return_when=asyncio.FIRST_COMPLETED)
+            finished = asyncio.create_task(self.finished.wait())
+            try:
+                await asyncio.wait({self.current_part_future, finished}, return_when=asyncio.FIRST_COMPLETED)
+            finally:
+                finished.cancel()  # otherwise one pending task per wait outlives the round
             if self.finished.is_set():
                 raise AllreduceException(f"attempted to aggregate part in a finalized {self.__class__.__name__}")
         if self.sender_failed_after[sender_index] != float("inf"):

@@ -161,9 +161,10 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
             wake.set()
 
     workers = [asyncio.create_task(worker()) for _ in range(max(1, num_workers))]
+    finished_wait = asyncio.create_task(search_finished.wait())
     try:
         # every worker parks only while some query is still active elsewhere; the last one to idle finishes them
-        await asyncio.wait(workers + [asyncio.create_task(search_finished.wait())], return_when=asyncio.FIRST_COMPLETED)
+        await asyncio.wait(workers + [finished_wait], return_when=asyncio.FIRST_COMPLETED)
         while unfinished:
             if all(w.done() for w in workers):
                 for q in list(unfinished):
@@ -176,6 +177,7 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
         if await_all_tasks and pending_tasks:
             await asyncio.gather(*list(pending_tasks), return_exceptions=True)
     finally:
+        finished_wait.cancel()
         for w in workers:
             w.cancel()
     result_nearest = {q: [n for _, n in heapq.nlargest(beam_size, nearest[q])] for q in queries}
