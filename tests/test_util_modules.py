@@ -256,3 +256,15 @@ def test_small_parity_helpers():
     opt = torch.optim.Adam(layer.parameters(), lr=0.1)
     initialize_optimizer_state(opt)
     assert len(opt.state) == 2 and torch.equal(layer.weight, before)
+
+
+def test_reference_import_paths_of_the_daemon_bindings():
+    import hivemind_b200.p2p as p2p
+    from hivemind_b200.p2p.p2p_daemon_bindings.control import ControlClient
+    from hivemind_b200.p2p.p2p_daemon_bindings.datastructures import PeerID, PeerInfo, StreamInfo
+    from hivemind_b200.p2p.p2p_daemon_bindings.p2pclient import Client
+    from hivemind_b200.p2p.p2p_daemon_bindings.utils import ControlFailure, P2PDaemonError, P2PHandlerError
+
+    assert PeerID is p2p.PeerID and Client is ControlClient
+    assert issubclass(ControlFailure, P2PDaemonError) and P2PHandlerError is p2p.P2PHandlerError
+    assert PeerInfo is not None and StreamInfo is not None
