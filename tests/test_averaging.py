@@ -153,3 +153,23 @@ def test_state_download_prefers_higher_priority():
         assert avs[2].load_state_from_peers(timeout=5) is None
     finally:
         _shutdown(*avs, *dhts)
+
+
+def test_remote_work_items_are_interleaved_over_owners():
+    """Work lists of the device butterfly: same items, but consecutive items read from different GPUs and every GPU
+    starts its walk at the peer after itself."""
+    from hivemind_b200.parallel.device_butterfly import _interleave_by_owner
+
+    n_peers, me = 4, 1
+    owners_of_parts = [0, 0, 0, 2, 2, 3, 3, 3, 3]  # parts of the other three peers (peer 1 owns none of these)
+    items = [(part, chunk, 0, 0) for part in range(len(owners_of_parts)) for chunk in range(2)]
+    owners = [owners_of_parts[part] for part, _, _, _ in items]
+    merged = _interleave_by_owner(items, owners, first_owner=(me + 1) % n_peers, n_peers=n_peers)
+    assert sorted(merged) == sorted(items)
+    walk = [owners_of_parts[part] for part, _, _, _ in merged]
+    assert walk[:6] == [2, 3, 0, 2, 3, 0]  # round-robin starting at peer 2
+    assert walk[-2:] == [3, 3]  # the longest queue drains last
+    for owner in set(owners_of_parts):  # order inside one owner's queue is kept
+        assert [item for item in merged if owners_of_parts[item[0]] == owner] == \
+               [item for item in items if owners_of_parts[item[0]] == owner]
+    assert _interleave_by_owner([], [], first_owner=0, n_peers=4) == []
