@@ -18,6 +18,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from hivemind_b200.ops import _lib
+from hivemind_b200.utils.profiling import traced
 
 MT_AXPY, MT_SCALE_COPY, MT_ZERO, MT_SCALE_CHECK, MT_DELTA, MT_COPY2 = range(6)
 NUM_SLOTS = 6
@@ -114,6 +115,7 @@ def _elementwise(table: TensorTable, op: int, alpha: float, flag: Optional[torch
     _lib.check(code, "hm_mt_elementwise")
 
 
+@traced("grads.axpy")
 def axpy_(dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor], alpha: float = 1.0) -> None:
     """dst[i] += alpha * src[i] (dst fp32 accumulators, src of any float dtype)."""
     if not len(dst):
@@ -126,6 +128,7 @@ def axpy_(dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor], alpha: float
             d.add_(s.to(d.dtype), alpha=alpha)
 
 
+@traced("grads.scale_copy")
 def scale_copy_(dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor], alpha: float = 1.0) -> None:
     """dst[i] = alpha * src[i] (dtype conversion included)."""
     if not len(dst):
@@ -222,6 +225,7 @@ def sumsq(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
     return out
 
 
+@traced("grads.clip_norm")
 def clip_grad_norm_(tensors: Sequence[torch.Tensor], max_norm: float) -> torch.Tensor:
     """Scale all tensors so that their global L2 norm is at most ``max_norm``; returns the norm before clipping."""
     n = len(tensors)
@@ -254,6 +258,7 @@ def _opt_args(**kw) -> _OptArgs:
     return a
 
 
+@traced("optimizer.adam")
 def adam_step_(params, grads, exp_avgs, exp_avg_sqs, *, step: int, lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
                weight_decay: float = 0.0, decoupled: bool = False, grad_scale: float = 1.0,
                model_copies: Optional[Sequence[torch.Tensor]] = None) -> None:
@@ -286,6 +291,7 @@ def adam_step_(params, grads, exp_avgs, exp_avg_sqs, *, step: int, lr: float, be
             model_copies[i].copy_(p)
 
 
+@traced("optimizer.sgd")
 def sgd_step_(params, grads, momentum_bufs=None, *, lr: float, momentum: float = 0.0, dampening: float = 0.0,
               weight_decay: float = 0.0, nesterov: bool = False, first_step: bool = False, grad_scale: float = 1.0,
               model_copies: Optional[Sequence[torch.Tensor]] = None) -> None:
@@ -317,6 +323,7 @@ def sgd_step_(params, grads, momentum_bufs=None, *, lr: float, momentum: float =
             model_copies[i].copy_(p)
 
 
+@traced("optimizer.lamb")
 def lamb_step_(params, grads, exp_avgs, exp_avg_sqs, update_scratch, *, step: int, lr: float, betas=(0.9, 0.999),
                eps: float = 1e-6, weight_decay: float = 0.0, clamp_value: float = 1e4, debias: bool = True,
                grad_scale: float = 1.0, model_copies: Optional[Sequence[torch.Tensor]] = None,

@@ -31,6 +31,7 @@ from hivemind_b200.ops import powersgd as ps_ops
 from hivemind_b200.optim.grad_averager import GradientAverager
 from hivemind_b200.utils import get_logger
 from hivemind_b200.utils.asyncio import enter_asynchronously
+from hivemind_b200.utils.profiling import traced
 from hivemind_b200.utils.math import get_flatten_greedy_dims, orthogonalize_
 
 GatheredData = Any
@@ -174,6 +175,7 @@ class PowerSGDGradientAverager(GradientAverager):
             raise
 
     # ---------------------------------------------------------------------------------------------- the three stages
+    @traced("powersgd.compress_p")
     @torch.no_grad()
     def _begin_round(self, compressed: Sequence[torch.Tensor]) -> None:
         """m += g;  P = M Q."""
@@ -189,6 +191,7 @@ class PowerSGDGradientAverager(GradientAverager):
         if self._ms[0].is_cuda:
             torch.cuda.current_stream(self._ms[0].device).synchronize()
 
+    @traced("powersgd.orthogonalize_q")
     @torch.no_grad()
     def _middle_round(self) -> None:
         """orthogonalise P;  Q = M^T P."""
@@ -204,6 +207,7 @@ class PowerSGDGradientAverager(GradientAverager):
         if self._ps[0].is_cuda:
             torch.cuda.current_stream(self._ps[0].device).synchronize()
 
+    @traced("powersgd.reconstruct")
     @torch.no_grad()
     def _finish_round(self, compressed: Sequence[torch.Tensor]) -> None:
         """g^ = P Q^T;  m -= g^;  averaged gradient = g^."""

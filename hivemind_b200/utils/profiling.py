@@ -2,7 +2,8 @@
 
 The reference has no tracing beyond samples-per-second estimates and the server's ``StatsReporter``
 (hivemind/utils/performance_ema.py:7-70, hivemind/moe/server/runtime.py:161-199). Here every device stage of a round
-(butterfly send / reduce / apply, expert dispatch / FFN / combine, optimizer kernels) can be wrapped in
+(butterfly send / reduce / apply, expert dispatch / FFN / combine, multi-tensor optimizer and gradient kernels,
+PowerSGD compress / orthogonalise / reconstruct) can be wrapped in
 ``device_range(name)``: with ``HIVEMIND_B200_NVTX=1`` it pushes an NVTX range (visible in profiler timelines); with
 ``HIVEMIND_B200_TIMING=1`` it also brackets the stage with CUDA events on the current stream and accumulates the
 elapsed device time per name, readable with ``timing_summary()``. With neither variable set the context manager
@@ -11,6 +12,7 @@ costs one dictionary lookup.
 from __future__ import annotations
 
 import contextlib
+import functools
 import os
 import threading
 from collections import defaultdict
@@ -56,6 +58,22 @@ def device_range(name: str, stream: Optional["torch.cuda.Stream"] = None):
                 _pending.append((name, events[0], events[1]))
         if _NVTX:
             torch.cuda.nvtx.range_pop()
+
+
+def traced(name: str):
+    """Decorator form of ``device_range`` for functions that enqueue one stage of device work."""
+
+    def wrap(fn):
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            if not (_NVTX or _TIMING):
+                return fn(*args, **kwargs)
+            with device_range(name):
+                return fn(*args, **kwargs)
+
+        return inner
+
+    return wrap
 
 
 def _collect(wait: bool) -> None:
