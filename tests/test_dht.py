@@ -277,3 +277,61 @@ def test_signed_and_schema_validated_records_through_dht():
     finally:
         b.shutdown()
         a.shutdown()
+
+
+def test_blacklist_backs_off_exponentially():
+    from hivemind_b200.dht.node import Blacklist
+
+    blacklist = Blacklist(base_time=0.2, backoff_rate=3.0)
+    peer, other = _fake_peer(1), _fake_peer(2)
+    assert peer not in blacklist
+    blacklist.register_failure(peer)
+    assert peer in blacklist and other not in blacklist
+    time.sleep(0.3)
+    assert peer not in blacklist  # first ban: 0.2 s
+    blacklist.register_failure(peer)
+    time.sleep(0.3)
+    assert peer in blacklist  # second ban: 0.6 s
+    time.sleep(0.45)
+    assert peer not in blacklist
+    blacklist.register_failure(peer)
+    blacklist.register_success(peer)  # a reply clears the ban and the history
+    assert peer not in blacklist and blacklist.ban_counter.get(peer, 0) == 0
+    disabled = Blacklist(base_time=0, backoff_rate=2.0)
+    disabled.register_failure(peer)
+    assert peer not in disabled
+
+
+def test_node_caches_found_values_and_shares_concurrent_gets():
+    async def main():
+        nodes = await _swarm(6, num_replicas=1, cache_locally=True, cache_nearest=1, cache_refresh_before_expiry=0)
+        try:
+            now = get_dht_time()
+            writer, reader = nodes[0], nodes[5]
+            assert await writer.store("cached_key", "payload", now + 30)
+            key_id = DHTID.generate("cached_key")
+            assert (await reader.get("cached_key")).value == "payload"
+            await asyncio.sleep(0.5)  # caching happens when the traversal winds down, after the value is returned
+            # the reader keeps a local copy (unless it happens to be the storing replica itself)
+            assert key_id in reader.protocol.cache or key_id in reader.protocol.storage
+            # ... and so does one more node near the key that did not have it
+            holders = sum(key_id in n.protocol.storage or key_id in n.protocol.cache for n in nodes)
+            assert holders >= 2
+            # concurrent gets of one key are answered by a single search
+            calls = 0
+            original = reader.find_nearest_nodes
+
+            async def counting(*args, **kwargs):
+                nonlocal calls
+                calls += 1
+                return await original(*args, **kwargs)
+
+            reader.find_nearest_nodes = counting
+            assert await writer.store("shared_key", 123, now + 30)
+            results = await asyncio.gather(*[reader.get("shared_key", latest=True) for _ in range(5)])
+            assert all(r.value == 123 for r in results)
+            assert calls <= 2, calls
+        finally:
+            await asyncio.gather(*[n.shutdown() for n in nodes])
+
+    run(main())
