@@ -231,6 +231,20 @@ def test_device_range_is_a_no_op_without_a_gpu_or_when_disabled():
         pass
     assert "anything" not in profiling.timing_summary()
 
+    @profiling.traced("stage.name")
+    def add(a, b=1):
+        """doc"""
+        return a + b
+
+    assert add(2, b=3) == 5 and add.__name__ == "add" and add.__doc__ == "doc"
+    profiling.enable(timing=True)  # without a GPU the range stays a no-op even when switched on
+    try:
+        assert add(1) == 2
+        if not __import__("torch").cuda.is_available():
+            assert "stage.name" not in profiling.timing_summary()
+    finally:
+        profiling.enable(timing=False)
+
 
 def test_small_parity_helpers():
     import collections
