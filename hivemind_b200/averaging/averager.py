@@ -232,10 +232,12 @@ class DecentralizedAverager(ServicerBase):
             if not self.client_mode:
                 self._declare_task = asyncio.create_task(self._declare_for_download_periodically())
             self._ready.set_result(None)
-        except Exception as e:
+        except BaseException as e:  # a cancellation must not leave the constructor waiting forever either
             logger.exception(e)
             if not self._ready.done():
-                self._ready.set_exception(e)
+                self._ready.set_exception(e if isinstance(e, Exception) else RuntimeError(f"averager setup failed: {e!r}"))
+            if not isinstance(e, Exception):
+                raise
 
     def shutdown(self) -> None:
         """Stop the background thread; pending steps fail with an exception."""

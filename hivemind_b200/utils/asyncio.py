@@ -49,6 +49,7 @@ class LoopThread:
         self.loop: Optional[asyncio.AbstractEventLoop] = None
         self._thread: Optional[threading.Thread] = None
         self._started = threading.Event()
+        self._outstanding: set = set()  # strong references to submitted work, see submit()
 
     def start(self) -> "LoopThread":
         if self._thread is not None:
@@ -83,7 +84,14 @@ class LoopThread:
     def submit(self, coro: Coroutine) -> concurrent.futures.Future:
         """Schedule ``coro`` on the loop; returns a ``concurrent.futures.Future``."""
         assert self.loop is not None, "loop thread is not running"
-        return asyncio.run_coroutine_threadsafe(coro, self.loop)
+        future = asyncio.run_coroutine_threadsafe(coro, self.loop)
+        # The event loop keeps only weak references to its tasks. A caller that drops the returned future leaves
+        # the task reachable only through whatever it is awaiting; if that is itself reachable only from the task
+        # (objects created inside the coroutine), the garbage collector destroys the pending task in mid-flight.
+        # Holding the future here keeps the task alive until it is done.
+        self._outstanding.add(future)
+        future.add_done_callback(self._outstanding.discard)
+        return future
 
     def run(self, coro: Coroutine, timeout: Optional[float] = None):
         """Run ``coro`` on the loop and wait for its result from a foreign thread."""
