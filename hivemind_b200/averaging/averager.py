@@ -25,6 +25,7 @@ from typing import Any, AsyncIterator, Dict, Optional, Sequence, Tuple, Union
 import numpy as np
 import torch
 
+from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.averaging.allreduce import AllreduceException, AllReduceRunner, AveragingMode, GroupID
 from hivemind_b200.averaging.control import AveragingStage, StepControl
 from hivemind_b200.averaging.group_info import GroupInfo
@@ -514,7 +515,7 @@ class DecentralizedAverager(ServicerBase):
             expiration_time = get_dht_time() + self.declare_state_period
             if self.allow_state_sharing or sharing_was_allowed:
                 # a record with the value None retracts an earlier offer
-                asyncio.create_task(asyncio.wait_for(self.dht.store(
+                spawn(asyncio.wait_for(self.dht.store(
                     download_key, subkey=self.peer_id.to_bytes(),
                     value=self.state_sharing_priority if self.allow_state_sharing else None,
                     expiration_time=expiration_time, return_future=True), timeout=expiration_time - get_dht_time()))

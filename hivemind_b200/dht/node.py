@@ -20,6 +20,7 @@ from typing import (Any, Awaitable, Callable, Collection, DefaultDict, Dict, Ite
 
 from sortedcontainers import SortedSet
 
+from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.dht.crypto import DHTRecord, RecordValidatorBase
 from hivemind_b200.dht.protocol import DHTProtocol
 from hivemind_b200.dht.routing import BinaryDHTValue, DHTID, DHTKey, DHTValue, Subkey
@@ -220,7 +221,7 @@ class DHTNode:
                                 asyncio.create_task(asyncio.sleep(bootstrap_timeout - get_dht_time() + start_time))],
                                return_when=asyncio.FIRST_COMPLETED)
         if self.refresh_timeout is not None:
-            asyncio.create_task(self._refresh_routing_table(period=self.refresh_timeout))
+            spawn(self._refresh_routing_table(period=self.refresh_timeout))
         return self
 
     def __init__(self, *, _initialized_with_create: bool = False):
@@ -472,7 +473,7 @@ class DHTNode:
             search_results[key_id].finish_search()  # finish with whatever we have (possibly nothing)
             self._cache_new_result(search_results[key_id], nearest_nodes, node_to_peer_id, _is_refresh=_is_refresh)
 
-        asyncio.create_task(traverse_dht(
+        spawn(traverse_dht(
             queries=list(unfinished_key_ids), initial_nodes=list(node_to_peer_id), beam_size=beam_size,
             num_workers=num_workers, queries_per_call=min(int(len(unfinished_key_ids) ** 0.5), self.chunk_size),
             get_neighbors=get_neighbors, visited_nodes={key_id: {self.node_id} for key_id in unfinished_key_ids},
@@ -575,7 +576,7 @@ class DHTNode:
                     for node_id in nearest_nodes:
                         if node_id == search.source_node_id:
                             continue
-                        asyncio.create_task(self.protocol.call_store(
+                        spawn(self.protocol.call_store(
                             node_to_peer_id[node_id], [search.key_id], [search.binary_value], [search.expiration_time],
                             in_cache=True))
                         num_cached_nodes += 1

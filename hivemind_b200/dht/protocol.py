@@ -10,6 +10,7 @@ from __future__ import annotations
 import asyncio
 from typing import Collection, Dict, List, Optional, Sequence, Tuple, Union
 
+from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.dht.crypto import DHTRecord, RecordValidatorBase
 from hivemind_b200.dht.routing import BinaryDHTValue, DHTID, RoutingTable, Subkey
 from hivemind_b200.dht.storage import DHTLocalStorage, DictionaryDHTValue
@@ -104,7 +105,7 @@ class DHTProtocol(ServicerBase):
                     raise
                 logger.warning(repr(e))
         peer_id = DHTID.from_bytes(response.peer.node_id) if responded else None
-        asyncio.create_task(self.update_routing_table(peer_id, peer, responded=responded))
+        spawn(self.update_routing_table(peer_id, peer, responded=responded))
         return peer_id
 
     async def rpc_ping(self, request: dht_pb2.PingRequest, context: P2PContext) -> dht_pb2.PingResponse:
@@ -113,7 +114,7 @@ class DHTProtocol(ServicerBase):
             sender_id = DHTID.from_bytes(request.peer.node_id)
             if request.validate:
                 response.available = await self.call_ping(context.remote_id, validate=False) == sender_id
-            asyncio.create_task(self.update_routing_table(sender_id, context.remote_id,
+            spawn(self.update_routing_table(sender_id, context.remote_id,
                                                           responded=response.available or not request.validate))
         return response
 
@@ -147,16 +148,16 @@ class DHTProtocol(ServicerBase):
                 response = await self.get_stub(peer).rpc_store(store_request, timeout=self.wait_timeout)
             if response.peer and response.peer.node_id:
                 peer_id = DHTID.from_bytes(response.peer.node_id)
-                asyncio.create_task(self.update_routing_table(peer_id, peer, responded=True))
+                spawn(self.update_routing_table(peer_id, peer, responded=True))
             return list(response.store_ok)
         except Exception as e:
             logger.debug(f"DHTProtocol failed to store at {peer}: {e!r}")
-            asyncio.create_task(self.update_routing_table(self.routing_table.get(peer_id=peer), peer, responded=False))
+            spawn(self.update_routing_table(self.routing_table.get(peer_id=peer), peer, responded=False))
             return None
 
     async def rpc_store(self, request: dht_pb2.StoreRequest, context: P2PContext) -> dht_pb2.StoreResponse:
         if request.peer and request.peer.node_id:
-            asyncio.create_task(self.update_routing_table(DHTID.from_bytes(request.peer.node_id), context.remote_id))
+            spawn(self.update_routing_table(DHTID.from_bytes(request.peer.node_id), context.remote_id))
         assert len(request.keys) == len(request.values) == len(request.expiration_time) == len(request.in_cache)
         response = dht_pb2.StoreResponse(store_ok=[], peer=self.node_info)
         for key, tag, value_bytes, expiration_time, in_cache in zip(
@@ -196,7 +197,7 @@ class DHTProtocol(ServicerBase):
                 response = await self.get_stub(peer).rpc_find(find_request, timeout=self.wait_timeout)
             if response.peer and response.peer.node_id:
                 peer_id = DHTID.from_bytes(response.peer.node_id)
-                asyncio.create_task(self.update_routing_table(peer_id, peer, responded=True))
+                spawn(self.update_routing_table(peer_id, peer, responded=True))
             assert len(keys) == len(response.results), "DHTProtocol: response is not aligned with keys"
             output = {}
             for key_id, result in zip(keys, response.results):
@@ -221,12 +222,12 @@ class DHTProtocol(ServicerBase):
             return output
         except Exception as e:
             logger.debug(f"DHTProtocol failed to find at {peer}: {e!r}")
-            asyncio.create_task(self.update_routing_table(self.routing_table.get(peer_id=peer), peer, responded=False))
+            spawn(self.update_routing_table(self.routing_table.get(peer_id=peer), peer, responded=False))
             return None
 
     async def rpc_find(self, request: dht_pb2.FindRequest, context: P2PContext) -> dht_pb2.FindResponse:
         if request.peer and request.peer.node_id:
-            asyncio.create_task(self.update_routing_table(DHTID.from_bytes(request.peer.node_id), context.remote_id))
+            spawn(self.update_routing_table(DHTID.from_bytes(request.peer.node_id), context.remote_id))
         response = dht_pb2.FindResponse(results=[], peer=self.node_info)
         for i, key_id in enumerate(map(DHTID.from_bytes, request.keys)):
             maybe_item = self.storage.get(key_id)
@@ -267,11 +268,11 @@ class DHTProtocol(ServicerBase):
                     if not neighbors or (new_node_should_store and this_node_is_responsible):
                         data_to_send.append((key, item.value, item.expiration_time))
                 if data_to_send:
-                    asyncio.create_task(self.call_store(peer_id, *zip(*data_to_send), in_cache=False))
+                    spawn(self.call_store(peer_id, *zip(*data_to_send), in_cache=False))
             maybe_node_to_ping = self.routing_table.add_or_update_node(node_id, peer_id)
             if maybe_node_to_ping is not None:
                 # the bucket is full: check whether its least-recently-seen node is still there
-                asyncio.create_task(self.call_ping(maybe_node_to_ping[1]))
+                spawn(self.call_ping(maybe_node_to_ping[1]))
         else:
             if node_id is not None and node_id in self.routing_table:
                 del self.routing_table[node_id]

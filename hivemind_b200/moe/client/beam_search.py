@@ -15,6 +15,7 @@ from collections import deque
 from functools import partial
 from typing import Deque, Dict, Iterator, List, Optional, Sequence, Set, Tuple, Union
 
+from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.dht import DHT, DHTNode
 from hivemind_b200.moe.client.expert import RemoteExpert, batch_create_remote_experts, create_remote_experts
 from hivemind_b200.moe.expert_uid import (FLAT_EXPERT, PREFIX_PATTERN, UID_DELIMITER, Coordinate, ExpertInfo,
@@ -92,7 +93,7 @@ class MoEBeamSearcher:
     @staticmethod
     def _store_negative(node: DHTNode, prefix: ExpertPrefix, cache_expiration: DHTExpiration) -> None:
         logger.debug(f"DHT negative caching: storing a 'no prefix' entry for {prefix}")
-        asyncio.create_task(node.store(prefix, subkey=FLAT_EXPERT, value=None,
+        spawn(node.store(prefix, subkey=FLAT_EXPERT, value=None,
                                        expiration_time=get_dht_time() + cache_expiration))
 
     @staticmethod

@@ -107,6 +107,18 @@ class LoopThread:
         self._thread = None
 
 
+_background_tasks: set = set()
+
+
+def spawn(coro: Coroutine) -> "asyncio.Task":
+    """``asyncio.create_task`` for work whose result nobody awaits: the task is kept alive until it is done (the
+    event loop itself only holds weak references to its tasks)."""
+    task = asyncio.create_task(coro)
+    _background_tasks.add(task)
+    task.add_done_callback(_background_tasks.discard)
+    return task
+
+
 async def anext(aiter: AsyncIterator[T]) -> T:
     return await aiter.__anext__()
 
