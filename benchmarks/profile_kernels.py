@@ -22,7 +22,11 @@ from hivemind_b200.ops.norm_act import layer_norm
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", required=True,
-                        choices=["gemm", "gemm_dw", "gemm_compare", "ln_fwd", "ln_bwd", "gelu_bwd"])
+                        choices=["gemm", "gemm_dw", "gemm_compare", "ln_fwd", "ln_bwd", "gelu_bwd", "attention_compare"])
+    parser.add_argument("--batch", type=int, default=32)
+    parser.add_argument("--seq", type=int, default=512)
+    parser.add_argument("--heads", type=int, default=16)
+    parser.add_argument("--causal", action="store_true")
     parser.add_argument("--m", type=int, default=16384)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -58,6 +62,50 @@ def main():
         check_kernel_errors()
         print(json.dumps({"kernel": "gemm_compare", "tflops": result, "m": args.m, "n": args.n, "k": args.k,
                           "iters": args.iters, "note": "launches back to back, no L2 flush"}))
+        return
+    if args.kernel == "attention_compare":
+        # this package's tcgen05 attention and PyTorch's scaled_dot_product_attention (library kernels) on the same
+        # packed projections, forward and forward+backward, L2 rewritten before every timed call
+        from hivemind_b200.ops.attention import attention
+
+        b, s, nh = args.batch, args.seq, args.heads
+        qkv = torch.randn(b, s, 3 * nh * 64, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        dout = torch.randn(b, s, nh * 64, device=dev, dtype=torch.bfloat16)
+
+        def ours():
+            return attention(qkv, nh, causal=args.causal)
+
+        def library():
+            q, k, v = (t.transpose(1, 2) for t in qkv.view(b, s, 3, nh, 64).unbind(2))
+            ctx = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=args.causal)
+            return ctx.transpose(1, 2).reshape(b, s, nh * 64)
+
+        def timed(fn):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            total = 0.0
+            for _ in range(args.iters):
+                flush.fill_(1)
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                fn()
+                stop.record()
+                torch.cuda.synchronize()
+                total += start.elapsed_time(stop)
+            return total / args.iters
+
+        flops_fwd = 4.0 * b * nh * s * s * 64 * (0.5 if args.causal else 1.0)
+        result = {}
+        for name, fn in (("ours", ours), ("library", library)):
+            fwd_ms = timed(fn)
+            both_ms = timed(lambda: torch.autograd.grad(fn(), qkv, dout))
+            result[name] = {"fwd_ms": fwd_ms, "fwd_tflops": flops_fwd / fwd_ms / 1e9, "fwd_bwd_ms": both_ms,
+                            "bwd_ms": both_ms - fwd_ms, "bwd_tflops": 2.5 * flops_fwd / max(both_ms - fwd_ms, 1e-6) / 1e9}
+        check_kernel_errors()
+        print(json.dumps({"kernel": "attention_compare", "batch": b, "seq": s, "heads": nh, "causal": args.causal,
+                          "result": result, "note": "library = scaled_dot_product_attention including the transposes "
+                                                    "and the stacked q/k/v gradient that surround it in a model"}))
         return
     if args.kernel == "gemm":
         a = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)

@@ -20,6 +20,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from hivemind_b200.ops.attention import attention
 from hivemind_b200.ops.gemm import linear
 from hivemind_b200.ops.norm_act import layer_norm
 
@@ -44,7 +45,7 @@ class AlbertConfig:
 
     @classmethod
     def tiny(cls) -> "AlbertConfig":
-        return cls(vocab_size=512, embedding_size=64, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+        return cls(vocab_size=512, embedding_size=64, hidden_size=128, num_hidden_layers=2, num_attention_heads=2,
                    intermediate_size=256, max_position_embeddings=64)
 
 
@@ -92,10 +93,7 @@ class AlbertLayer(nn.Module):
         b, s, h = x.shape
         nh = self.num_heads
         qkv = linear(x, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight))
-        qkv = qkv.view(b, s, 3, nh, h // nh)
-        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))  # unbind: one stacked gradient instead of three sums
-        ctx = F.scaled_dot_product_attention(q, k, v)  # [b, nh, s, d]
-        ctx = ctx.transpose(1, 2).reshape(b, s, h)
+        ctx = attention(qkv, nh)  # reads the packed projections, writes [b, s, h]: no transposes around it
         attn = linear(ctx, self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight))
         x = layer_norm(attn, self.attn_ln_weight, self.attn_ln_bias, self.eps, residual=x)
         inter = linear(x, self.ffn_weight, self.ffn_bias, activation="gelu", weight_lp=lp.get(self.ffn_weight))

@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from hivemind_b200.models.albert import _LowPrecisionCache
+from hivemind_b200.ops.attention import attention
 from hivemind_b200.ops.gemm import linear
 from hivemind_b200.ops.norm_act import layer_norm
 
@@ -46,7 +47,7 @@ class GPT2Config:
 
     @classmethod
     def tiny(cls) -> "GPT2Config":
-        return cls(vocab_size=509, n_positions=64, n_embd=128, n_layer=2, n_head=4, n_inner=256)
+        return cls(vocab_size=509, n_positions=64, n_embd=128, n_layer=2, n_head=2, n_inner=256)
 
     @property
     def padded_vocab_size(self) -> int:
@@ -83,8 +84,7 @@ class GPT2Block(nn.Module):
         b, s, h = normed.shape
         nh = self.num_heads
         qkv = linear(normed, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight))
-        q, k, v = (t.transpose(1, 2) for t in qkv.view(b, s, 3, nh, h // nh).unbind(2))
-        ctx = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(b, s, h)
+        ctx = attention(qkv, nh, causal=True)
         attn = linear(ctx, self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight))
         normed, stream = layer_norm(attn, self.ln_2_weight, self.ln_2_bias, self.eps, residual=stream, return_sum=True)
         inter = linear(normed, self.ffn_weight, self.ffn_bias, activation="gelu", weight_lp=lp.get(self.ffn_weight))
