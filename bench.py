@@ -89,7 +89,12 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=3, help="timed collaborative optimizer steps (epochs)")
     parser.add_argument("--warmup", type=int, default=3, help="untimed warm-up epochs")
-    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_nccl"],
+                        help="ours: this framework; reference: the unmodified reference (unavailable offline); "
+                             "torch_nccl: plain PyTorch + NCCL baseline of the same workload")
+    parser.add_argument("--context-steps", type=int, default=1,
+                        help="with --impl ours: collaborative steps of the plain PyTorch + NCCL baseline to time "
+                             "afterwards for context (0 = skip)")
     parser.add_argument("--micro-batch", type=int, default=32)
     parser.add_argument("--seq-len", type=int, default=512)
     parser.add_argument("--target-batch-size", type=int, default=4096)
@@ -120,11 +125,43 @@ def main() -> None:
         # barriers and the final reductions of the timing go over a host-side group: a NCCL barrier would put a
         # kernel that waits for every rank into the stream that the background averaging rounds synchronise with
         host_group = dist.new_group(backend="gloo")
-    warmup = max(3, args.warmup)
+    warmup = args.warmup
 
     torch.manual_seed(1234)  # identical initial weights on every peer
     cfg = AlbertConfig.large() if args.model == "large" else AlbertConfig.tiny()
     seq_len = min(args.seq_len, cfg.max_position_embeddings)
+
+    def baseline(steps: int, warmup_steps: int, end_to_end: bool = False) -> dict:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks"))
+        import torch_albert_baseline
+
+        gen_b = torch.Generator().manual_seed(2000 + rank)
+        return torch_albert_baseline.run(
+            device=device, world=world, rank=rank, host_group=host_group, micro_batch=args.micro_batch, seq_len=seq_len,
+            target_batch_size=args.target_batch_size, steps=steps, warmup_steps=warmup_steps, end_to_end=end_to_end,
+            make_batch=lambda i: make_mlm_batch(AlbertConfig.large(), args.micro_batch, seq_len, generator=gen_b, pin=True))
+
+    if args.impl == "torch_nccl":
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        res = baseline(args.steps, warmup)
+        clocks = sampler.stop() if rank == 0 else {}
+        e2e = baseline(args.steps, 1, end_to_end=True) if not args.no_e2e else None
+        if rank == 0:
+            print(json.dumps({
+                "metric": "Optimizer samples/s (ALBERT-large)", "value": res["value"], "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": res["value"] / BASELINE_SAMPLES_PER_SEC,
+                "dtype": "bf16", "data": "synthetic", "impl": "torch_nccl", "clocks": clocks,
+                "e2e": None if e2e is None else {"value": e2e["value"], "unit": "samples/s"},
+                "config": {"model": "albert-large, plain PyTorch modules", "global_batch": args.target_batch_size,
+                           "micro_batch_per_gpu": args.micro_batch, "seq_len": seq_len, "parallelism": f"dp{world}",
+                           "what": res["what"]}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     model = AlbertForMaskedLM(cfg).to(device)
 
     # one DHT per peer; rank 0 bootstraps the others
@@ -143,14 +180,16 @@ def main() -> None:
     total_steps, warmup_steps = 125000, 5000
     opt = hivemind.Optimizer(
         dht=dht, run_id="albert_bench", target_batch_size=args.target_batch_size, batch_size_per_step=args.micro_batch,
-        params=list(model.parameters()),
+        # biases and LayerNorm weights are not decayed (examples/albert/run_trainer.py:250-260)
+        params=[dict(params=[p for p in model.parameters() if p.ndim > 1], weight_decay=0.01),
+                dict(params=[p for p in model.parameters() if p.ndim <= 1], weight_decay=0.0)],
         optimizer=lambda params: FusedLAMB(params, lr=1.76e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01,
                                            clamp_value=10000.0, debias=True),
         scheduler=lambda o: torch.optim.lr_scheduler.LambdaLR(
             o, lambda step: min((step + 1) / warmup_steps, max(0.0, (total_steps - step) / (total_steps - warmup_steps)))),
         grad_compression=hivemind.Uniform8BitQuantization(), state_averaging_compression=hivemind.Float16Compression(),
         reuse_grad_buffers=True, offload_optimizer=True, delay_optimizer_step=True, delay_grad_averaging=True,
-        matchmaking_time=1.0, averaging_timeout=30.0, next_chunk_timeout=5.0, average_state_every=10 ** 9,
+        matchmaking_time=1.0, averaging_timeout=30.0, next_chunk_timeout=5.0, average_state_every=1,
         averager_opts=dict(request_timeout=0.5, target_group_size=world if world > 1 else None),
         tracker_opts=dict(min_refresh_period=0.02, default_refresh_period=0.05, max_refresh_period=0.2),
         verbose=False)

@@ -98,35 +98,36 @@ VERBOSE_ROUNDS = False
 
 def _time_rounds(endpoint, plan_args, rounds, warmup):
     """Device time per round on the endpoint's stream (ms), with a fresh group id (epoch) every round.
-    Returns the mean round time and the mean time from each launch's predecessor to its end, by launch name."""
+
+    All rounds are enqueued back to back without waiting on the host (like the NCCL column, which times consecutive
+    ``all_reduce`` calls): the gate kernel in front of every round keeps the ranks in step on the device. Returns the
+    mean time from the launch of a round's gate kernel to the end of its round kernel, and the mean duration of each
+    launch by name (the gate's share is mostly waiting for the slowest rank)."""
     stream = torch.cuda.ExternalStream(endpoint.stream.value, device=endpoint.device)
-    times, per_launch = [], {}
+    all_marks = []
+    if plan_args["barrier"] is not None:
+        plan_args["barrier"]()
     for i in range(warmup + rounds):
-        plan = endpoint._prepare(group_id=f"bench-{plan_args['tag']}-{i}".encode(), stream=endpoint.stream,
-                                 **plan_args["kwargs"])
         # fresh values every round: repeated averaging of the same tensors converges, and the deltas of converged
         # peers are an unrepresentative (degenerate) input for the quantising codecs
         with torch.cuda.stream(stream):
             endpoint.tensor_views[0].normal_()
-        stream.synchronize()
-        if plan_args["barrier"] is not None:
-            plan_args["barrier"]()
         marks = []
 
-        def mark(name):
+        def mark(name, marks=marks):
             marks.append((name, torch.cuda.Event(enable_timing=True)))
             marks[-1][1].record(stream)
 
         endpoint.launch_hook = mark
         mark("start")
-        endpoint._stage_send(plan, endpoint.stream)
-        endpoint._stage_reduce(plan, endpoint.stream)
-        endpoint._stage_apply(plan, endpoint.stream)
+        endpoint.run_round(group_id=f"bench-{plan_args['tag']}-{i}".encode(), wait=False, **plan_args["kwargs"])
         endpoint.launch_hook = None
-        status = endpoint._read_status(plan, endpoint.stream)
-        marks[-1][1].synchronize()
-        if status.banned_senders or status.failed_reducers:
-            raise RuntimeError(f"round failed: {status.banned_senders} {status.failed_reducers}")
+        all_marks.append(marks)
+    status = endpoint.wait_round()
+    if status.banned_senders or status.failed_reducers:
+        raise RuntimeError(f"round failed: {status.banned_senders} {status.failed_reducers}")
+    times, per_launch = [], {}
+    for i, marks in enumerate(all_marks):
         if i >= warmup:
             times.append(marks[0][1].elapsed_time(marks[-1][1]))
             for (_, before), (name, after) in zip(marks, marks[1:]):
@@ -180,7 +181,7 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
                 dist.all_gather_object(infos, endpoint.describe())
                 n = world
                 kwargs = dict(my_index=rank, device_infos=infos, modes=[AveragingMode.NODE] * n,
-                              peer_fractions=[1.0 / n] * n, weights=[1.0] * n, alpha=1.0, sender_timeout=10.0,
+                              peer_fractions=[1.0 / n] * n, weight=1.0, alpha=1.0, sender_timeout=10.0,
                               reducer_timeout=20.0)
                 ms, stages = _time_rounds(endpoint, dict(tag=f"{size_mb}-{codec_name}", kwargs=kwargs,
                                                          barrier=dist.barrier, verbose=VERBOSE_ROUNDS), rounds, warmup)

@@ -79,6 +79,11 @@ class DecentralizedAverager(ServicerBase):
     :param declare_state_period: how often to re-announce that we can share state
     :param client_mode: never accept incoming requests (send only)
     :param shutdown_timeout: seconds to wait for a clean stop
+    :param use_device_path: average CUDA fp32 tensors with the device butterfly when the whole group shares an NVLink
+      box (default: yes, unless ``HIVEMIND_DEVICE_BUTTERFLY=0``). The tensors are then COPIED into a peer-mappable arena
+      and ``get_tensors()`` yields the arena views: the tensors passed in are no longer the averaged ones. Pass
+      False to keep averaging the caller's own tensors in place (through the RPC butterfly)
+    :param device_endpoint: an existing ``DeviceEndpoint`` whose ``tensor_views`` are ``averaged_tensors``
     """
 
     _matchmaking: Matchmaking
@@ -97,7 +102,7 @@ class DecentralizedAverager(ServicerBase):
                  tensor_infos: Optional[Sequence[CompressionInfo]] = None, bandwidth: Optional[float] = None,
                  min_vector_size: int = 0, auxiliary: bool = False, allow_state_sharing: Optional[bool] = None,
                  declare_state_period: float = 30, client_mode: Optional[bool] = None, daemon: bool = True,
-                 shutdown_timeout: float = 5, use_device_path: Optional[bool] = None):
+                 shutdown_timeout: float = 5, use_device_path: Optional[bool] = None, device_endpoint=None):
         assert "." not in prefix, "group prefix must be a string without trailing '.'"
         assert bandwidth is None or (bandwidth >= 0 and np.isfinite(np.float32(bandwidth))), \
             "bandwidth must be a non-negative float32"
@@ -141,13 +146,14 @@ class DecentralizedAverager(ServicerBase):
         self.state_compression = state_compression
         self.tensor_infos = tensor_infos
 
-        # device data path: re-home CUDA tensors into one peer-mappable arena
-        self._device_endpoint = None
+        # device data path: CUDA tensors live in one peer-mappable arena. A subclass that needs the arena before this
+        # constructor runs (its optimizer works on the arena views) passes the endpoint whose views it handed in
+        self._device_endpoint = device_endpoint
         all_cuda_fp32 = len(self._averaged_tensors) > 0 and all(
             t.is_cuda and t.dtype == torch.float32 for t in self._averaged_tensors)
         if use_device_path is None:
             use_device_path = all_cuda_fp32 and os.environ.get("HIVEMIND_DEVICE_BUTTERFLY", "1") != "0"
-        if use_device_path and all_cuda_fp32 and self.mode != AveragingMode.CLIENT:
+        if device_endpoint is None and use_device_path and all_cuda_fp32:
             from hivemind_b200.parallel.device_butterfly import DeviceEndpoint
 
             infos = tensor_infos or tuple(CompressionInfo.from_tensor(t, key=i) for i, t in enumerate(self._averaged_tensors))
@@ -422,14 +428,14 @@ class DecentralizedAverager(ServicerBase):
 
     async def _run_device_allreduce_(self, group_info: GroupInfo, peer_fractions, modes, device_infos, *, weight: float,
                                      sender_timeout=None, reducer_timeout=None, endpoint=None, group_id=None,
-                                     weights=None, lock: bool = True, **_unused) -> None:
-        """Device data path: launch the butterfly kernels over peer-mapped arenas and wait for the stream."""
+                                     lock: bool = True, **_unused) -> None:
+        """Device data path: launch the round's kernels over peer-mapped arenas and wait for the stream.
+
+        Every member's weight travels inside the flags that its kernel publishes, so nothing is exchanged up front.
+        """
         endpoint = endpoint if endpoint is not None else self._device_endpoint
         group_id = group_id if group_id is not None else group_info.group_id
         my_index = group_info.peer_ids.index(self.peer_id)
-        # every member needs every member's weight up front: exchange them through a tiny unary RPC round
-        if weights is None:
-            weights = await self._exchange_weights(group_info, weight)
         pending = self._running_groups.get(group_id)
         if pending is not None and not pending.done():
             pending.set_result(None)  # no RPC runner in this round: the data moves through peer-mapped memory
@@ -437,43 +443,12 @@ class DecentralizedAverager(ServicerBase):
         async with (enter_asynchronously(self.lock_averaged_tensors) if lock else contextlib.AsyncExitStack()):
             status = await loop.run_in_executor(None, lambda: endpoint.run_round(
                 group_id=group_id, my_index=my_index, device_infos=device_infos, modes=modes,
-                peer_fractions=peer_fractions, weights=weights, alpha=self._averaging_alpha,
+                peer_fractions=peer_fractions, weight=weight, alpha=self._averaging_alpha,
                 sender_timeout=sender_timeout, reducer_timeout=reducer_timeout))
         self._state_updated.set()
-        if status.failed_fraction > 0:
+        if status.failed_fraction > 0 or status.banned_senders:
             logger.warning(f"Averaging: received {(1 - status.failed_fraction) * 100:.1f}% results "
                            f"(banned senders: {status.banned_senders}, failed reducers: {status.failed_reducers})")
-
-    async def _exchange_weights(self, group_info: GroupInfo, my_weight: float) -> Sequence[float]:
-        """Collect the averaging weight of every group member (the leader's gather blob predates final weights)."""
-        group_id = group_info.group_id
-        holder = self._device_weight_boxes.setdefault(group_id, {}) if hasattr(self, "_device_weight_boxes") else None
-        if holder is None:
-            self._device_weight_boxes = {group_id: {}}
-            holder = self._device_weight_boxes[group_id]
-        holder[self.peer_id] = my_weight
-
-        async def ask(peer: PeerID) -> float:
-            stub = type(self).get_stub(self._p2p, peer, namespace=self.prefix)
-            for _ in range(200):
-                reply = await stub.rpc_get_weight(averaging_pb2.AveragingData(group_id=group_id), timeout=self.request_timeout)
-                if reply.code == averaging_pb2.AVERAGED_PART:
-                    return reply.weight
-                await asyncio.sleep(0.005)
-            raise AllreduceException(f"{peer} never announced its weight for this round")
-
-        try:
-            others = await asyncio.gather(*[ask(p) for p in group_info.peer_ids if p != self.peer_id])
-        finally:
-            asyncio.get_event_loop().call_later(30.0, self._device_weight_boxes.pop, group_id, None)
-        it = iter(others)
-        return [my_weight if p == self.peer_id else next(it) for p in group_info.peer_ids]
-
-    async def rpc_get_weight(self, request: averaging_pb2.AveragingData, context: P2PContext) -> averaging_pb2.AveragingData:
-        box = getattr(self, "_device_weight_boxes", {}).get(request.group_id)
-        if box is None or self.peer_id not in box:
-            return averaging_pb2.AveragingData(code=averaging_pb2.NOT_DECLARED)
-        return averaging_pb2.AveragingData(code=averaging_pb2.AVERAGED_PART, weight=box[self.peer_id])
 
     @contextlib.contextmanager
     def get_tensors(self) -> Sequence[torch.Tensor]:

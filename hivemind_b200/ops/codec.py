@@ -1,6 +1,6 @@
 """Tensor codecs on the GPU: fp16, mean/std-scaled fp16, uniform / quantile / block-wise 8-bit.
 
-These are the encode kernels of the device butterfly (``csrc/butterfly.cu``) driven as a one-rank "group" whose
+These are the whole-tensor encode kernels of ``csrc/codec.cu`` driven as a one-rank "group" whose
 outbox is a scratch buffer: the tensor (or each of its last-axis rows, for the scaled codec) is one part. They serve
 the compression classes when those are handed CUDA tensors (state downloads, expert RPC payloads), so that only
 compressed bytes cross PCIe. Math: hivemind/compression/floating.py:18-64, quantization.py:60-93,130-153.
@@ -8,7 +8,8 @@ compressed bytes cross PCIe. Math: hivemind/compression/floating.py:18-64, quant
 from __future__ import annotations
 
 import ctypes
-from typing import List, Tuple
+import threading
+from typing import Dict, List, Tuple
 
 import numpy as np
 import torch
@@ -16,13 +17,63 @@ import torch
 from hivemind_b200.ops import _lib
 
 _HALF_MIN, _HALF_MAX = -65504.0, 65504.0
+_MAX_PEERS = 16
+PH_STATS, PH_BORDERS, PH_ENCODE, PH_PUBLISH = range(4)
+
+
+class _HbPeer(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("outbox", ctypes.c_void_p), ("deltabox", ctypes.c_void_p),
+                ("ready", ctypes.c_void_p), ("delta_ready", ctypes.c_void_p), ("avg", ctypes.c_void_p)]
+
+
+class _HbGroup(ctypes.Structure):
+    """Mirror of ``HbGroup`` in ``csrc/codec.cu`` (a one-rank group whose outbox is the output buffer)."""
+
+    _fields_ = [("n_peers", ctypes.c_int), ("n_parts", ctypes.c_int), ("me", ctypes.c_int),
+                ("max_local_parts", ctypes.c_int), ("epoch", ctypes.c_uint), ("alpha", ctypes.c_float),
+                ("sender_timeout_ns", ctypes.c_ulonglong), ("reducer_timeout_ns", ctypes.c_ulonglong),
+                ("delta_stride", ctypes.c_ulonglong), ("weight", ctypes.c_float * _MAX_PEERS),
+                ("sends", ctypes.c_int * _MAX_PEERS), ("peer", _HbPeer * _MAX_PEERS), ("parts", ctypes.c_void_p),
+                ("part_stats", ctypes.c_void_p), ("dstats", ctypes.c_void_p), ("bins", ctypes.c_void_p),
+                ("bin_cnt", ctypes.c_void_p), ("dbins", ctypes.c_void_p), ("dbin_cnt", ctypes.c_void_p),
+                ("borders", ctypes.c_void_p), ("dborders", ctypes.c_void_p), ("include", ctypes.c_void_p),
+                ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p), ("t_start", ctypes.c_void_p),
+                ("status", ctypes.c_void_p), ("avg", ctypes.c_void_p)]
+
+
+_PART_DTYPE = np.dtype([("start", "<i8"), ("enc_off", "<i8"), ("span_off", "<i8"), ("avg_off", "<i8"), ("len", "<i4"),
+                        ("owner", "<i4"), ("local_idx", "<i4"), ("codec", "<i4")])
+_code_uploaded: Dict[int, bool] = {}
+_code_lock = threading.Lock()
+
+
+def _ensure_code_table(device_index: int) -> None:
+    """Upload the block-wise code table into the library's constant memory of this device (once)."""
+    from hivemind_b200.compression.quantization import dynamic_code_table
+
+    with _code_lock:
+        if _code_uploaded.get(device_index):
+            return
+        lib = _lib.load_library()
+        assert lib.hm_bf_sizeof_group() == ctypes.sizeof(_HbGroup), "HbGroup layout mismatch between C and Python"
+        assert lib.hm_bf_sizeof_part() == _PART_DTYPE.itemsize, "HbPart layout mismatch between C and Python"
+        code = dynamic_code_table().numpy().astype(np.float32)
+        with torch.cuda.device(device_index):
+            _lib.check(lib.hm_bf_set_blockwise_code(code.ctypes.data_as(ctypes.c_void_p)), "hm_bf_set_blockwise_code", 0)
+        _code_uploaded[device_index] = True
+
+
+def record_bytes(codec: int, length: int) -> int:
+    """Bytes of a whole-tensor record: header (statistics or codebook) + payload rounded up to 16 bytes."""
+    header = {1: 16, 3: 1024, 4: 1024}.get(codec, 0)
+    if codec == 5:
+        header = ((length + 4095) // 4096 * 4 + 15) // 16 * 16
+    elem = 4 if codec == 0 else (2 if codec in (1, 2) else 1)
+    return header + (length * elem + 15) // 16 * 16
 
 
 def _run_encode(flat: torch.Tensor, parts: List[Tuple[int, int]], codec: int) -> Tuple[torch.Tensor, List[int]]:
     """Encode ``flat[start:start+len]`` for every (start, len) into one byte buffer; returns it and record offsets."""
-    from hivemind_b200.parallel.device_butterfly import (_HbGroup, _PART_DTYPE, PH_BORDERS, PH_ENCODE, PH_PUBLISH,
-                                                         PH_STATS, _ensure_code_table, record_bytes)
-
     device = flat.device
     lib = _lib.load_library()
     _ensure_code_table(device.index)

@@ -30,6 +30,7 @@
 //
 // Every mbarrier wait is bounded (tc_ptx.cuh); when one runs out the CTA records an error word, skips its
 // stores, lets copies in flight land, frees its tensor memory and returns.
+#include <cstdio>
 #include "tc_ptx.cuh"
 
 namespace {
@@ -152,6 +153,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
   bool failed = false;
+  int where = 0;   // source line of the wait in progress: reported if it runs out
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -160,7 +162,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       tma_load_3d(smem_base + L::Q_OFF, &map_qkv, q_full, head * HD, q0, batch);
       for (int t = 0; t < 2 * n_blocks; ++t) {
         const int stage = t % L::RING, use = t / L::RING;
-        if (!mbar_wait(kv_empty(stage), (use & 1) ^ 1, abort_flag)) { failed = true; break; }
+        if (!(where = __LINE__, mbar_wait(kv_empty(stage), (use & 1) ^ 1, abort_flag))) { failed = true; break; }
         mbar_expect_tx(kv_full(stage), TILE_BYTES);
         const int col = ((t & 1) ? 2 * hidden : hidden) + head * HD;
         tma_load_3d(smem_base + L::RING_OFF + stage * TILE_BYTES, &map_qkv, kv_full(stage), col, (t >> 1) * TILE, batch);
@@ -171,9 +173,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     if (lane == 0) {
       auto issue_pv = [&](int j) -> bool {
         const int t = 2 * j + 1, stage = t % L::RING, use = t / L::RING;
-        if (!mbar_wait(kv_full(stage), use & 1, abort_flag)) return false;
-        if (!mbar_wait(p_full, j & 1, abort_flag)) return false;
-        if (j > 0 && !mbar_wait(o_empty, (j - 1) & 1, abort_flag)) return false;
+        if (!(where = __LINE__, mbar_wait(kv_full(stage), use & 1, abort_flag))) return false;
+        if (!(where = __LINE__, mbar_wait(p_full, j & 1, abort_flag))) return false;
+        if (j > 0 && !(where = __LINE__, mbar_wait(o_empty, (j - 1) & 1, abort_flag))) return false;
         tc_fence_after();
         const uint32_t v_addr = smem_base + L::RING_OFF + stage * TILE_BYTES;
         const uint32_t p_addr = smem_base + L::P_OFF;
@@ -187,11 +189,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         tc_commit(o_full);
         return true;
       };
-      if (!mbar_wait(q_full, 0, abort_flag)) failed = true;
+      if (!(where = __LINE__, mbar_wait(q_full, 0, abort_flag))) failed = true;
       for (int j = 0; j < n_blocks && !failed; ++j) {
         const int t = 2 * j, stage = t % L::RING, use = t / L::RING;
-        if (!mbar_wait(kv_full(stage), use & 1, abort_flag)) { failed = true; break; }
-        if (j > 0 && !mbar_wait(s_empty, (j - 1) & 1, abort_flag)) { failed = true; break; }
+        if (!(where = __LINE__, mbar_wait(kv_full(stage), use & 1, abort_flag))) { failed = true; break; }
+        if (j > 0 && !(where = __LINE__, mbar_wait(s_empty, (j - 1) & 1, abort_flag))) { failed = true; break; }
         tc_fence_after();
         const uint32_t k_addr = smem_base + L::RING_OFF + stage * TILE_BYTES;
 #pragma unroll
@@ -221,7 +223,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     const float c = p.scale_log2;
 
     for (int j = 0; j < n_blocks; ++j) {
-      if (!warp_wait(s_full, j & 1, abort_flag)) { failed = true; break; }
+      if (!(where = __LINE__, warp_wait(s_full, j & 1, abort_flag))) { failed = true; break; }
       tc_fence_after();
       const int key0 = j * TILE;
       const bool need_mask = (key0 + TILE > p.S) || (p.causal && j == q_tile);
@@ -247,7 +249,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       m_run = mx;
       // fold in the previous block's P V (also tells us that the P buffer may be overwritten)
       if (j > 0) {
-        if (!warp_wait(o_full, (j - 1) & 1, abort_flag)) { failed = true; break; }
+        if (!(where = __LINE__, warp_wait(o_full, (j - 1) & 1, abort_flag))) { failed = true; break; }
         tc_fence_after();
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -298,7 +300,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       mbar_arrive(p_full);
     }
     if (!failed) {
-      if (!warp_wait(o_full, (n_blocks - 1) & 1, abort_flag)) failed = true;
+      if (!(where = __LINE__, warp_wait(o_full, (n_blocks - 1) & 1, abort_flag))) failed = true;
     }
     if (!failed) {
       tc_fence_after();
@@ -338,7 +340,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 
   if (failed) {
     *abort_flag = 1;
-    if (p.err) atomicExch(p.err, 100 + warp);
+    if (p.err) atomicCAS(p.err, 0, 1000000 + warp * 10000 + where);   // the first failure is kept
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   tc_fence_before();
@@ -415,7 +417,7 @@ struct BwdSmem {
   static constexpr int DS_OFF = P_OFF + 2 * TILE_BYTES;           // dS : two slabs by key half
   static constexpr int DQ_OFF = DS_OFF + 2 * TILE_BYTES;          // fp32 staging: two boxes of 128 rows x 32 columns
   static constexpr int BAR_OFF = DQ_OFF + 2 * TILE_BYTES;
-  static constexpr int NUM_BARS = 1 + 2 * RING + 6;
+  static constexpr int NUM_BARS = 1 + 2 * RING + 7;
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
 };
 
@@ -437,8 +439,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   auto qdo_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto qdo_empty = [&](int s) { return bar_base + 8u * (1 + L::RING + s); };
   const uint32_t s_full = bar_base + 8u * (1 + 2 * L::RING);
-  const uint32_t s_empty = s_full + 8, pds_full = s_full + 16, grads_done = s_full + 24, dq_empty = s_full + 32,
-                 all_done = s_full + 40;
+  const uint32_t s_empty = s_full + 8, pds_full = s_full + 16, grads_done = s_full + 24, all_done = s_full + 32;
+  // one barrier per dQ buffer in TMEM: a barrier shared by both buffers could complete two phases between two looks
+  // of the MMA thread, which a parity wait cannot tell from none
+  auto dq_empty = [&](int it) { return s_full + 40u + 8u * (uint32_t)(it & 1); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::BAR_OFF + L::NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BAR_OFF + L::NUM_BARS * 8 + 4);
 
@@ -461,7 +465,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     mbar_init(s_empty, BWD_COMPUTE);
     mbar_init(pds_full, BWD_COMPUTE);
     mbar_init(grads_done, 1);
-    mbar_init(dq_empty, BWD_COMPUTE);
+    mbar_init(dq_empty(0), BWD_COMPUTE);
+    mbar_init(dq_empty(1), BWD_COMPUTE);
     mbar_init(all_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -478,6 +483,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   auto tmem_dq = [&](int it) { return tmem_base + 384u + 64u * (uint32_t)(it & 1); };
 
   bool failed = false;
+  int where = 0;   // source line of the wait in progress: reported if it runs out
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -487,7 +493,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       tma_load_3d(smem_base + L::V_OFF, &map_qkv, kv_full, 2 * hidden + head * HD, key0, batch);
       for (int it = 0; it < n_iter; ++it) {
         const int stage = it % L::RING, use = it / L::RING;
-        if (!mbar_wait(qdo_empty(stage), (use & 1) ^ 1, abort_flag)) { failed = true; break; }
+        if (!(where = __LINE__, mbar_wait(qdo_empty(stage), (use & 1) ^ 1, abort_flag))) { failed = true; break; }
         mbar_expect_tx(qdo_full(stage), 2 * TILE_BYTES);
         const uint32_t dst = smem_base + L::RING_OFF + stage * 2 * TILE_BYTES;
         tma_load_3d(dst, &map_qkv, qdo_full(stage), head * HD, (i0 + it) * TILE, batch);
@@ -501,8 +507,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       const uint32_t p_addr = smem_base + L::P_OFF, ds_addr = smem_base + L::DS_OFF;
       auto issue_grads = [&](int it) -> bool {
         const int stage = it % L::RING;
-        if (!mbar_wait(pds_full, it & 1, abort_flag)) return false;
-        if (it >= 2 && !mbar_wait(dq_empty, it & 1, abort_flag)) return false;   // drain of iteration it - 2
+        if (!(where = __LINE__, mbar_wait(pds_full, it & 1, abort_flag))) return false;
+        if (it >= 2 && !(where = __LINE__, mbar_wait(dq_empty(it), ((it >> 1) - 1) & 1, abort_flag))) return false;   // drain of iteration it - 2
         tc_fence_after();
         const uint32_t q_addr = smem_base + L::RING_OFF + stage * 2 * TILE_BYTES, do_addr = q_addr + TILE_BYTES;
 #pragma unroll
@@ -527,11 +533,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         tc_commit(grads_done);
         return true;
       };
-      if (!mbar_wait(kv_full, 0, abort_flag)) failed = true;
+      if (!(where = __LINE__, mbar_wait(kv_full, 0, abort_flag))) failed = true;
       for (int it = 0; it < n_iter && !failed; ++it) {
         const int stage = it % L::RING, use = it / L::RING;
-        if (!mbar_wait(qdo_full(stage), use & 1, abort_flag)) { failed = true; break; }
-        if (it > 0 && !mbar_wait(s_empty, (it - 1) & 1, abort_flag)) { failed = true; break; }
+        if (!(where = __LINE__, mbar_wait(qdo_full(stage), use & 1, abort_flag))) { failed = true; break; }
+        if (it > 0 && !(where = __LINE__, mbar_wait(s_empty, (it - 1) & 1, abort_flag))) { failed = true; break; }
         tc_fence_after();
         const uint32_t q_addr = smem_base + L::RING_OFF + stage * 2 * TILE_BYTES, do_addr = q_addr + TILE_BYTES;
 #pragma unroll
@@ -569,14 +575,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 
     // moves the finished dQ tile of iteration `it` (64 fp32 columns, 32 per warpgroup) into the global accumulator
     auto drain_dq = [&](int it, bool need_wait) {
-      if (ok && need_wait) ok = warp_wait(grads_done, it & 1, abort_flag);
+      if (ok && need_wait) ok = (where = __LINE__, warp_wait(grads_done, it & 1, abort_flag));
       uint32_t r[32];
       if (ok) {
         tc_fence_after();
         tc_ld32(tmem_dq(it) + lane_base + (uint32_t)(half * 32), r);
         tc_wait_ld();
         tc_fence_before();
-        mbar_arrive(dq_empty);
+        mbar_arrive(dq_empty(it));
       }
       if (threadIdx.x == 64) tma_wait_read<0>();   // the staging buffer has been read by the previous reduce-add
       named_bar_sync<BWD_COMPUTE>();
@@ -601,7 +607,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       const float lse = row_ok ? __ldg(p.lse + stat_base + q_idx) : 0.f;
       const float dlt = row_ok ? __ldg(p.delta + stat_base + q_idx) * p.scale : 0.f;
       uint32_t pk[32], dk[32];   // this thread's 64 P and 64 dS values as packed bf16 pairs
-      if (ok) ok = warp_wait(s_full, it & 1, abort_flag);
+      if (ok) ok = (where = __LINE__, warp_wait(s_full, it & 1, abort_flag));
       if (ok) {
         tc_fence_after();
         const bool need_mask = (key0 + TILE > p.S) || (p.causal && (i0 + it) == kv_tile) || ((i0 + it) * TILE + TILE > p.S);
@@ -631,7 +637,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         tc_fence_before();
         mbar_arrive(s_empty);
         // the operand buffers are free once the gradient products of the previous iteration have completed
-        if (it > 0) ok = warp_wait(grads_done, (it - 1) & 1, abort_flag);
+        if (it > 0) ok = (where = __LINE__, warp_wait(grads_done, (it - 1) & 1, abort_flag));
       }
       if (ok) {
         uint8_t* p_row = smem + L::P_OFF + half * TILE_BYTES + row * 128;
@@ -649,7 +655,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     }
     drain_dq(n_iter - 1, true);
     // dK (first warpgroup) and dV (second warpgroup): 128 keys x 64 columns each, staged over the P / dS buffers
-    if (ok) ok = warp_wait(all_done, 0, abort_flag);
+    if (ok) ok = (where = __LINE__, warp_wait(all_done, 0, abort_flag));
     if (ok) {
       tc_fence_after();
       uint8_t* stage_row = smem + (half == 0 ? L::P_OFF : L::DS_OFF) + row * 128;
@@ -686,7 +692,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 
   if (failed) {
     *abort_flag = 1;
-    if (p.err) atomicExch(p.err, 200 + warp);
+    if (p.err) atomicCAS(p.err, 0, 2000000 + warp * 10000 + where);   // the first failure is kept
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   tc_fence_before();
@@ -718,6 +724,7 @@ EncodeTiledFn attn_encode_fn() {
 int make_map_3d(CUtensorMap* map, const void* base, bool is_f32, int B, int S, long long cols, int box_cols) {
   EncodeTiledFn fn = attn_encode_fn();
   if (!fn) return -10;
+  ensure_context_on_this_thread();
   const int elem = is_f32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * elem) % 16 != 0) return -11;
   cuuint64_t gdim[3] = {(cuuint64_t)cols, (cuuint64_t)S, (cuuint64_t)B};
@@ -727,7 +734,12 @@ int make_map_3d(CUtensorMap* map, const void* base, bool is_f32, int B, int S, l
   CUresult r = fn(map, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "attention: cuTensorMapEncodeTiled failed (%d): base %p f32 %d dims (%lld, %d, %d) box %d\n", (int)r, base,
+            (int)is_f32, cols, S, B, box_cols);
+    return -12;
+  }
+  return 0;
 }
 
 }  // namespace

@@ -688,6 +688,7 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, bool is_f32, lo
              long long ld, int box_cols, int box_rows, bool atom32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -10;
+  ensure_context_on_this_thread();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return -11;
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)(ld * elem_bytes)};

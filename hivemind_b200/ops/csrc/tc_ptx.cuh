@@ -7,7 +7,7 @@
 
 namespace {
 
-constexpr unsigned long long WAIT_BUDGET_NS = 2000000000ull;  // 2 s per wait
+constexpr unsigned long long WAIT_BUDGET_NS = 500000000ull;   // 0.5 s per wait
 constexpr int EPI_THREADS = 128;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -140,6 +140,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 __host__ __device__ constexpr uint32_t make_idesc(int fmt, bool a_mn, bool b_mn, int m, int n) {
   return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((a_mn ? 1u : 0u) << 15) |
          ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// cuTensorMapEncodeTiled is a driver call: it needs a CUDA context that is current on the calling thread. Threads
+// that have made no runtime call yet (an autograd worker whose first node is one of these kernels) have none; any
+// runtime call binds the device's primary context.
+inline void ensure_context_on_this_thread() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
 }
 
 }  // namespace

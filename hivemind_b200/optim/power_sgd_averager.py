@@ -146,11 +146,10 @@ class PowerSGDGradientAverager(GradientAverager):
                 compressed = [g for i, g in enumerate(averaged_grads) if i not in self._uncompressed_gradients_indexes]
                 plain = [g for i, g in enumerate(averaged_grads) if i in self._uncompressed_gradients_indexes]
                 await loop.run_in_executor(None, self._begin_round, compressed)
-                weights = await self._exchange_weights(group_info, weight) if use_device else None
                 if use_device:
                     await self._run_device_allreduce_(group_info, p_fractions, modes, [d["p"] for d in device_infos],
                                                       weight=weight, endpoint=self._p_endpoint, group_id=p_group_id,
-                                                      weights=weights, lock=False,
+                                                      lock=False,
                                                       sender_timeout=kwargs.get("sender_timeout"),
                                                       reducer_timeout=kwargs.get("reducer_timeout"))
                 else:
@@ -160,7 +159,7 @@ class PowerSGDGradientAverager(GradientAverager):
                 if use_device:
                     await self._run_device_allreduce_(group_info, q_fractions, modes, [d["q"] for d in device_infos],
                                                       weight=weight, endpoint=self._q_endpoint, group_id=q_group_id,
-                                                      weights=weights, lock=False,
+                                                      lock=False,
                                                       sender_timeout=kwargs.get("sender_timeout"),
                                                       reducer_timeout=kwargs.get("reducer_timeout"))
                 else:

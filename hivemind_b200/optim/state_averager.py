@@ -1,57 +1,83 @@
-"""``TrainingStateAverager``: owns the optimizer, the LR schedule and the averaged copy of the training state.
+"""``TrainingStateAverager``: owns the optimizer, the LR schedule and the copy of the training state that peers average.
 
-State = parameters (+ selected optimizer statistics + extra tensors). The same state machine as the reference
-(hivemind/optim/state_averager.py:37-740): one ``step(...)`` call can run, in order and each optionally in the
-background, an optimizer step, ``zero_grad``, a scheduler step and an averaging round; results of background work
-are applied by a later call with ``apply_delayed_updates=True``.
+Contract (hivemind/optim/state_averager.py:37-740): the *state* is the parameters, optionally some optimizer
+statistics and extra tensors. One ``step(...)`` call may, in this order and each optionally in the background, run an
+optimizer step, ``zero_grad``, a scheduler step and an averaging round with peers; what finished in the background is
+copied into the model by a later call. Peers that fell behind download the whole state (``load_state_from_peers``),
+whose layout is fixed by ``get_current_state``.
 
-B200 design notes: averaged copies stay on the parameters' device (for CUDA in the averager's peer-mappable arena),
-so "offloading" means "the optimizer updates the fp32 arena copy while the model keeps training on its own
-tensors" instead of a round trip through host memory; copies between the model and the arena and the delta rule
-are single multi-tensor kernels.
+How the tensors are kept here. There are up to three sets, all on the parameters' own device:
+
+* ``main_parameters`` — the tensors the model trains with;
+* the optimizer's parameters — the same tensors, or with ``offload_optimizer`` separate fp32 "shadow" copies, so that
+  a delayed optimizer step never races with the next forward pass;
+* the averaged tensors — with ``reuse_tensors`` the optimizer's tensors themselves, otherwise one more copy.
+
+On CUDA the averaged tensors live in the averager's peer-mappable arena, and with ``offload_optimizer`` +
+``reuse_tensors`` (the default pairing) the shadow copies ARE arena views: the fused optimizer updates the arena in
+place and the butterfly kernels average it in place, with no staging copy in between. Copies between the sets and the
+delta rule are single multi-tensor launches.
 """
 from __future__ import annotations
 
 import logging
+import os
 import threading
 import time
-from concurrent.futures import ThreadPoolExecutor
-from contextlib import nullcontext
-from itertools import chain
-from typing import Any, Callable, Dict, Iterable, Iterator, Optional, Sequence, Tuple, Union
+from concurrent.futures import Future, ThreadPoolExecutor
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import torch
 
 from hivemind_b200.averaging import DecentralizedAverager, StepControl
-from hivemind_b200.compression import CompressionInfo, TensorRole
+from hivemind_b200.compression import CompressionInfo, NoCompression, TensorRole
 from hivemind_b200.dht import DHT
 from hivemind_b200.ops import multi_tensor as mt
-from hivemind_b200.utils import DHTExpiration, PerformanceEMA, get_dht_time, get_logger, nested_flatten, nested_pack
+from hivemind_b200.utils import DHTExpiration, PerformanceEMA, get_logger, nested_flatten, nested_pack
 
 logger = get_logger(__name__)
 
 Parameters = Iterable[torch.Tensor]
 ParamGroups = Iterable[Dict[str, Any]]
 TorchOptimizer = torch.optim.Optimizer
-try:
-    LRSchedulerBase = torch.optim.lr_scheduler.LRScheduler
-except AttributeError:  # pragma: no cover
-    LRSchedulerBase = torch.optim.lr_scheduler._LRScheduler
+LRSchedulerBase = getattr(torch.optim.lr_scheduler, "LRScheduler", None) or torch.optim.lr_scheduler._LRScheduler
 OptimizerFactory = Callable[[Union[Parameters, ParamGroups]], TorchOptimizer]
 SchedulerFactory = Callable[[TorchOptimizer], LRSchedulerBase]
 
 
-def _copy_all_(dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor]) -> None:
-    """dst[i] <- src[i]; one kernel when all pairs share a device, plain copies otherwise."""
-    pairs = [(d, s) for d, s in zip(dst, src) if d.data_ptr() != s.data_ptr() or d.device != s.device]
-    if not pairs:
+def _bulk_copy(dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor]) -> None:
+    """``dst[i] <- src[i]`` for all pairs that are not already the same memory; one launch when the kernels apply."""
+    todo = [(d, s) for d, s in zip(dst, src) if d.data_ptr() != s.data_ptr() or d.device != s.device]
+    if not todo:
         return
-    if all(d.device == s.device and d.is_contiguous() and s.is_contiguous() and d.is_floating_point()
-           and s.is_floating_point() for d, s in pairs):
-        mt.scale_copy_([d for d, _ in pairs], [s for _, s in pairs], 1.0)
+    fusable = all(d.device == s.device and d.is_contiguous() and s.is_contiguous() and d.is_floating_point()
+                  and s.is_floating_point() for d, s in todo)
+    if fusable:
+        mt.scale_copy_([d for d, _ in todo], [s for _, s in todo], 1.0)
     else:
-        for d, s in pairs:
+        for d, s in todo:
             d.copy_(s, non_blocking=True)
+
+
+def _bump_versions(tensors: Iterable[torch.Tensor]) -> None:
+    """Tell autograd-side caches (e.g. bf16 weight copies keyed by ``_version``) that the tensors changed."""
+    for t in tensors:
+        torch.autograd.graph.increment_version(t)
+
+
+@dataclass
+class _Request:
+    """What one ``step`` call asked the background worker to do."""
+
+    trigger: Optional[Callable[[], Any]]
+    optimizer_step: bool
+    zero_grad: bool
+    averaging_round: bool
+    control: Optional[StepControl]
+    grad_scaler: Any
+    set_to_none: bool
+    averaging_opts: Dict[str, Any]
 
 
 class TrainingStateAverager(DecentralizedAverager):
@@ -60,7 +86,7 @@ class TrainingStateAverager(DecentralizedAverager):
     :param params: parameters or param groups (default: the optimizer's groups)
     :param scheduler: an LR scheduler or a factory ``optimizer -> scheduler``
     :param initialize_optimizer: run one zero-gradient step so that optimizer statistics exist (default: if needed)
-    :param offload_optimizer: the optimizer updates the averaged copies instead of the model's own tensors
+    :param offload_optimizer: the optimizer updates shadow copies instead of the model's own tensors
     :param custom_gradients: with offloading, the caller writes gradients into the optimizer's tensors itself
     :param reuse_tensors: average the optimizer's tensors in place instead of keeping separate averaged copies
     :param delta_rule_averaging: apply ``local += averaged_new - averaged_old`` so that local progress made while
@@ -81,152 +107,149 @@ class TrainingStateAverager(DecentralizedAverager):
                  sync_epoch_when_averaging: bool = False, parameter_names: Optional[Sequence[str]] = None,
                  average_opt_statistics: Sequence[str] = (), extra_tensors: Sequence[torch.Tensor] = (),
                  status_loglevel: int = logging.DEBUG, **kwargs):
-        average_opt_statistics = tuple(average_opt_statistics)
-        assert all(isinstance(key, str) for key in average_opt_statistics)
+        self.opt_keys_for_averaging = tuple(average_opt_statistics)
+        if not all(isinstance(key, str) for key in self.opt_keys_for_averaging):
+            raise TypeError("average_opt_statistics must be names of optimizer statistics")
+        self.extra_tensors = tuple(extra_tensors)
         if reuse_tensors is None:
             reuse_tensors = offload_optimizer and not delta_rule_averaging
-        if custom_gradients and not offload_optimizer:
-            logger.warning("Setting custom_gradients=True has no effect because the optimizer is not offloaded")
         if reuse_tensors and delta_rule_averaging:
             raise ValueError("reuse_tensors and delta_rule_averaging are mutually exclusive")
-        param_groups, main_parameters, parameter_names = self._check_params(optimizer, params, parameter_names)
+        if custom_gradients and not offload_optimizer:
+            logger.warning("custom_gradients=True has no effect unless the optimizer is offloaded")
         self.status_loglevel = status_loglevel
         self.offload_optimizer, self.custom_gradients = offload_optimizer, custom_gradients
         self.reuse_tensors, self.delta_rule_averaging = reuse_tensors, delta_rule_averaging
-        self._old_tensors: Optional[Sequence[torch.Tensor]] = None
-        self.main_parameters, self.parameter_names = main_parameters, parameter_names
-        self._averaged_parameters = self._make_averaged_parameters(main_parameters)
-        self.optimizer, self.scheduler = self._init_components(param_groups, optimizer, scheduler, initialize_optimizer)
-        self.opt_keys_for_averaging, self.extra_tensors = average_opt_statistics, extra_tensors
         self.sync_epoch_when_averaging = sync_epoch_when_averaging
         self.local_epoch = 0
+
+        groups, self.main_parameters, self.parameter_names = self._normalise_params(optimizer, params, parameter_names)
+        optimizer_is_factory = callable(optimizer) and not isinstance(optimizer, TorchOptimizer)
+        scheduler_is_factory = callable(scheduler) and not isinstance(scheduler, LRSchedulerBase)
+        if offload_optimizer and not optimizer_is_factory:
+            raise ValueError("offload_optimizer needs an optimizer factory: the optimizer must be built on the copies")
+        if optimizer_is_factory and scheduler is not None and not scheduler_is_factory:
+            raise ValueError("with an optimizer factory the scheduler must be a factory too")
+
+        # the optimizer's tensors: the model's own, or shadow copies (in the device arena when they are also averaged)
+        endpoint = None
+        if offload_optimizer:
+            shadow = [p.detach().to(torch.float32, copy=True) for p in self.main_parameters]
+            endpoint = self._maybe_arena_for(shadow, kwargs)
+            if endpoint is not None:
+                shadow = [v.detach() for v in endpoint.tensor_views]
+            shadow = [s.requires_grad_(p.requires_grad) for s, p in zip(shadow, self.main_parameters)]
+            for s in shadow:
+                s.grad = torch.zeros_like(s)
+            groups_for_optimizer, cursor = [], 0
+            for group in groups:
+                count = len(group["params"])
+                groups_for_optimizer.append(dict(group, params=shadow[cursor:cursor + count]))
+                cursor += count
+        else:
+            groups_for_optimizer = list(groups)
+        self.optimizer = optimizer(groups_for_optimizer) if optimizer_is_factory else optimizer
+        if not isinstance(self.optimizer, TorchOptimizer) or len(self.optimizer.param_groups) != len(groups):
+            raise TypeError("the optimizer (factory) must yield a torch optimizer with the given parameter groups")
+        if initialize_optimizer is None:
+            initialize_optimizer = not any(torch.is_tensor(x) for x in nested_flatten(self.optimizer.state_dict()))
+        if initialize_optimizer:
+            logger.log(status_loglevel, "Creating optimizer statistics with one zero-gradient step")
+            initialize_optimizer_state_(self.optimizer)
+        self.scheduler = scheduler(self.optimizer) if scheduler_is_factory else scheduler
+        if self.scheduler is not None and self.scheduler.optimizer is not self.optimizer:
+            raise ValueError("the scheduler must belong to this optimizer")
+
+        tracked = self._tracked_tensors()
+        if reuse_tensors:
+            averaged = [t.detach() if endpoint is None else t for t in tracked]
+        else:
+            averaged = [t.detach().to(torch.float32, copy=True) for t in tracked]
+        if reuse_tensors and endpoint is None:
+            # tensors that other code holds on to cannot move into an arena
+            kwargs.setdefault("use_device_path", False)
+        self._rounds_lock = threading.Lock()            # held while a round may modify the averaged tensors
+        self._optimizer_lock = threading.Lock()
+        self._snapshot: Optional[List[torch.Tensor]] = None   # averaged tensors as they were when the round began
         self.delay_before_averaging = PerformanceEMA(alpha=performance_ema_alpha)
-        self.step_executor = ThreadPoolExecutor(max_workers=2 if self.delta_rule_averaging else 1)
+        self._worker = ThreadPoolExecutor(max_workers=2 if delta_rule_averaging else 1,
+                                          thread_name_prefix="state-averager")
         self.finished_optimizer_step = threading.Event()
         self.finished_averaging_round = threading.Event()
-        self.lock_optimizer = threading.Lock()
-        self.lock_averaging = threading.Lock()
-        self.pending_updates = set()
-        # the device data path re-homes averaged tensors into an arena, which would break tensor sharing
-        if reuse_tensors:
-            kwargs.setdefault("use_device_path", False)
-        super().__init__(dht=dht, averaged_tensors=self._init_averaged_tensors(), tensor_infos=self._init_tensor_infos(),
-                         **kwargs)
+        self.pending_updates: set = set()
+        super().__init__(dht=dht, averaged_tensors=averaged, tensor_infos=self._describe_tensors(),
+                         device_endpoint=endpoint, **kwargs)
 
+    # ---------------------------------------------------------------------------------------------- set-up helpers
     @staticmethod
-    def _check_params(optimizer, param_groups, parameter_names):
-        if param_groups is None:
-            assert hasattr(optimizer, "param_groups"), "Must provide param_groups or an optimizer with .param_groups"
-            param_groups = optimizer.param_groups
-        param_groups = tuple(param_groups)
-        if all(isinstance(p, torch.Tensor) for p in param_groups):
-            param_groups = (dict(params=param_groups),)
-        for group in param_groups:
-            assert isinstance(group, dict) and group.get("params") is not None
-            assert all(isinstance(p, torch.Tensor) for p in group["params"])
-        parameters = tuple(chain(*(group["params"] for group in param_groups)))
-        if parameter_names is None:
-            parameter_names = tuple(i for i in range(len(parameters)))
-        parameter_names = tuple(nested_flatten(parameter_names))
-        assert len(parameters) == len(parameter_names), f"Expected {len(parameters)} names, got {len(parameter_names)}"
-        assert len(set(parameters)) == len(parameters), "Found duplicate parameters in param_groups"
-        with_grad = sum(p.numel() for p in parameters if p.requires_grad)
-        without_grad = sum(p.numel() for p in parameters if not p.requires_grad)
-        if without_grad >= with_grad:
-            logger.warning("Most parameters have requires_grad=False but are still synchronized with peers; "
-                           "leave frozen parameters out of the optimizer to save communication")
-        return param_groups, parameters, parameter_names
+    def _normalise_params(optimizer, params, names) -> Tuple[Tuple[dict, ...], Tuple[torch.Tensor, ...], Tuple]:
+        if params is None:
+            if not hasattr(optimizer, "param_groups"):
+                raise ValueError("pass params, or an optimizer instance whose param_groups can be used")
+            params = optimizer.param_groups
+        params = tuple(params)
+        groups = (dict(params=list(params)),) if all(torch.is_tensor(p) for p in params) else params
+        flat: List[torch.Tensor] = []
+        for group in groups:
+            if not isinstance(group, dict) or not all(torch.is_tensor(p) for p in group.get("params", [None])):
+                raise TypeError("params must be tensors or dicts with a 'params' list of tensors")
+            flat.extend(group["params"])
+        if len({id(p) for p in flat}) != len(flat):
+            raise ValueError("a parameter appears in more than one group")
+        names = tuple(range(len(flat))) if names is None else tuple(nested_flatten(names))
+        if len(names) != len(flat):
+            raise ValueError(f"{len(flat)} parameters but {len(names)} names")
+        frozen = sum(p.numel() for p in flat if not p.requires_grad)
+        if frozen and frozen >= sum(p.numel() for p in flat) - frozen:
+            logger.warning("most synchronised parameters are frozen; leave them out of the optimizer to save traffic")
+        return tuple(groups), tuple(flat), names
 
-    def _make_averaged_parameters(self, main_parameters: Sequence[torch.Tensor]):
-        return tuple(self._make_averaged_tensor(param, force_copy=self.offload_optimizer) for param in main_parameters)
+    def _maybe_arena_for(self, shadow: Sequence[torch.Tensor], averager_kwargs: Dict[str, Any]):
+        """An arena that holds the shadow parameters, if they are also the averaged tensors and the device data
+        path applies (CUDA, nothing but parameters to average); None otherwise."""
+        wanted = averager_kwargs.get("use_device_path")
+        if wanted is None:
+            wanted = os.environ.get("HIVEMIND_DEVICE_BUTTERFLY", "1") != "0"
+        if not (wanted and self.reuse_tensors and shadow and all(s.is_cuda for s in shadow)):
+            return None
+        if self.opt_keys_for_averaging or self.extra_tensors:
+            return None
+        from hivemind_b200.parallel.device_butterfly import DeviceEndpoint
 
-    def _make_averaged_tensor(self, source_tensor: torch.Tensor, force_copy: bool = False) -> torch.Tensor:
-        """A new fp32 tensor on the same device for averaging, or the source itself when tensors are reused."""
-        if self.reuse_tensors and not force_copy:
-            return source_tensor
-        averaged = source_tensor.detach().to(dtype=torch.float32, copy=True)
-        return averaged.requires_grad_(source_tensor.requires_grad)
+        infos = [CompressionInfo.from_tensor(s, key=name, role=TensorRole.PARAMETER)
+                 for s, name in zip(shadow, self.parameter_names)]
+        return DeviceEndpoint(shadow, averager_kwargs.get("compression", NoCompression()), infos,
+                              averager_kwargs.get("part_size_bytes", 2 ** 19))
 
-    def _init_components(self, param_groups, optimizer_or_factory, scheduler_or_factory, initialize_optimizer):
-        assert hasattr(self, "_averaged_parameters"), "Internal error: must initialize averaged parameters first"
-        optimizer_is_factory = callable(optimizer_or_factory) and not isinstance(optimizer_or_factory, TorchOptimizer)
-        scheduler_is_factory = callable(scheduler_or_factory) and not isinstance(scheduler_or_factory, LRSchedulerBase)
-        if optimizer_is_factory and not scheduler_is_factory and scheduler_or_factory is not None:
-            raise ValueError("If optimizer is created internally, scheduler must also be initialized internally")
-        if self.offload_optimizer and not optimizer_is_factory:
-            raise ValueError("Using offload_optimizer requires creating optimizer inside hivemind")
-        if optimizer_is_factory:
-            if self.offload_optimizer:
-                if self.reuse_tensors:
-                    parameters_for_optimizer = self._averaged_parameters
-                else:
-                    parameters_for_optimizer = tuple(t.detach().clone().requires_grad_(t.requires_grad)
-                                                     for t in self._averaged_parameters)
-                next_index, groups_for_optimizer = 0, []
-                for group in param_groups:
-                    count = len(group["params"])
-                    groups_for_optimizer.append(dict(group, params=parameters_for_optimizer[next_index:next_index + count]))
-                    next_index += count
-                assert next_index == len(parameters_for_optimizer)
-                for param in parameters_for_optimizer:
-                    if param.grad is None:
-                        param.grad = torch.zeros_like(param)
-            else:
-                groups_for_optimizer = param_groups
-            optimizer = optimizer_or_factory(groups_for_optimizer)
-        else:
-            optimizer = optimizer_or_factory
-        if initialize_optimizer is None:
-            initialize_optimizer = not any(isinstance(x, torch.Tensor) for x in nested_flatten(optimizer.state_dict()))
-            logger.log(self.status_loglevel, "Initializing optimizer manually since it has no tensors in state dict. "
-                                             "To override this, provide initialize_optimizer=False")
-        if initialize_optimizer:
-            initialize_optimizer_state_(optimizer)  # note: runs one optimizer step with zero gradients
-        scheduler = scheduler_or_factory(optimizer) if scheduler_is_factory else scheduler_or_factory
-        assert isinstance(optimizer, TorchOptimizer) and len(optimizer.param_groups) == len(list(param_groups))
-        assert isinstance(scheduler, (LRSchedulerBase, type(None)))
-        if scheduler is not None:
-            assert scheduler.optimizer == optimizer
-        return optimizer, scheduler
+    def _optimizer_parameters(self) -> List[torch.Tensor]:
+        return [p for group in self.optimizer.param_groups for p in group["params"]]
 
-    def _local_tensors(self) -> Iterator[torch.Tensor]:
-        """The trainer's own tensors that correspond, one to one, to the averaged tensors."""
-        for group in self.optimizer.param_groups:
-            yield from group["params"]
-        for stats in self.opt_keys_for_averaging:
-            for group in self.optimizer.param_groups:
-                for param in group["params"]:
-                    yield self.optimizer.state[param][stats]
-        yield from self.extra_tensors
+    def _tracked_tensors(self) -> List[torch.Tensor]:
+        """The trainer-side tensors that correspond one to one to the averaged tensors: optimizer parameters, the
+        chosen optimizer statistics (statistic by statistic), extra tensors."""
+        tensors = self._optimizer_parameters()
+        for key in self.opt_keys_for_averaging:
+            tensors += [self.optimizer.state[p][key] for p in self._optimizer_parameters()]
+        return tensors + list(self.extra_tensors)
 
-    @torch.no_grad()
-    def _init_averaged_tensors(self) -> Sequence[torch.Tensor]:
-        assert hasattr(self, "optimizer") and hasattr(self, "_averaged_parameters")
-        local_tensors = tuple(self._local_tensors())
-        local_non_parameters = local_tensors[len(self._averaged_parameters):]
-        averaged = tuple(map(torch.Tensor.detach, self._averaged_parameters))
-        averaged += tuple(map(self._make_averaged_tensor, local_non_parameters))
-        assert len(averaged) == len(local_tensors)
-        for local_tensor, averaged_tensor in zip(local_tensors, averaged):
-            assert local_tensor.shape == averaged_tensor.shape
-        return averaged
-
-    def _init_tensor_infos(self) -> Sequence[CompressionInfo]:
-        infos = [CompressionInfo.from_tensor(param, key=name, role=TensorRole.PARAMETER)
-                 for param, name in zip(self.main_parameters, self.parameter_names)]
-        for stats_name in self.opt_keys_for_averaging:
-            opt_parameters = [param for group in self.optimizer.param_groups for param in group["params"]]
-            assert len(opt_parameters) == len(self.parameter_names)
-            for param, name in zip(opt_parameters, self.parameter_names):
-                infos.append(CompressionInfo.from_tensor(self.optimizer.state[param][stats_name], key=(name, stats_name),
-                                                         role=TensorRole.OPTIMIZER))
-        for i, extra_tensor in enumerate(self.extra_tensors):
-            infos.append(CompressionInfo.from_tensor(extra_tensor, key=i, role=TensorRole.UNSPECIFIED))
+    def _describe_tensors(self) -> Tuple[CompressionInfo, ...]:
+        infos = [CompressionInfo.from_tensor(p, key=name, role=TensorRole.PARAMETER)
+                 for p, name in zip(self.main_parameters, self.parameter_names)]
+        for key in self.opt_keys_for_averaging:
+            infos += [CompressionInfo.from_tensor(self.optimizer.state[p][key], key=(name, key), role=TensorRole.OPTIMIZER)
+                      for p, name in zip(self._optimizer_parameters(), self.parameter_names)]
+        infos += [CompressionInfo.from_tensor(t, key=i, role=TensorRole.UNSPECIFIED) for i, t in enumerate(self.extra_tensors)]
         return tuple(infos)
+
+    # ---------------------------------------------------------------------------------------------- public API
+    @property
+    def averaging_in_progress(self) -> bool:
+        return self._rounds_lock.locked()
 
     def schedule_step(self, scheduled_time: Optional[DHTExpiration] = None, **kwargs) -> StepControl:
         """Begin matchmaking for a state-averaging round ahead of time (see ``step(averaging_control=...)``)."""
-        assert kwargs.get("weight") is None, "setting weight in schedule_step is not supported"
+        if kwargs.get("weight") is not None:
+            raise ValueError("a pre-scheduled state averaging round cannot carry a weight")
         return super().step(scheduled_time=scheduled_time, wait=False, require_trigger=True, **kwargs)
 
     def step(self, wait_for_delayed_updates: bool = None, apply_delayed_updates: bool = True,
@@ -238,7 +261,7 @@ class TrainingStateAverager(DecentralizedAverager):
 
         :param wait_for_delayed_updates: wait for background work started by earlier calls
         :param apply_delayed_updates: copy finished background results into the model
-        :param increment_epoch: ``local_epoch += 1`` (also steps the scheduler)
+        :param increment_epoch: ``local_epoch += 1`` (the scheduler follows the epoch)
         :param optimizer_step / zero_grad: run these on the (possibly offloaded) optimizer
         :param delay_optimizer_step: run them in the background (needs ``offload_optimizer``)
         :param averaging_round: average state with peers; ``delay_averaging`` runs it in the background
@@ -249,319 +272,304 @@ class TrainingStateAverager(DecentralizedAverager):
         """
         if delay_averaging is None:
             delay_averaging = delay_optimizer_step
-        should_wait = averaging_round or optimizer_step or zero_grad if self.delta_rule_averaging else averaging_round
+        touches_state = averaging_round or (self.delta_rule_averaging and (optimizer_step or zero_grad))
         if wait_for_delayed_updates is None:
-            wait_for_delayed_updates = should_wait
-        if should_wait and not (wait_for_delayed_updates and apply_delayed_updates):
-            raise ValueError("Should wait for background operation to finish before scheduling new one")
-        assert not delay_optimizer_step or delay_averaging, "Delayed optimizer step requires delayed averaging"
-        if delay_optimizer_step:
-            assert self.offload_optimizer, "Delayed optimizer step is only available with offload_optimizer"
-            assert not averaging_round or delay_averaging, "Averaging after delayed optimizer should also be delayed"
+            wait_for_delayed_updates = touches_state
+        if touches_state and not (wait_for_delayed_updates and apply_delayed_updates):
+            raise ValueError("earlier background work must be awaited and applied before new work is scheduled")
+        if delay_optimizer_step and not self.offload_optimizer:
+            raise ValueError("a delayed optimizer step needs offload_optimizer")
+        if delay_optimizer_step and not delay_averaging:
+            raise ValueError("averaging that follows a delayed optimizer step must be delayed too")
+        if averaging_control is not None and not averaging_round:
+            raise ValueError("averaging_control was given but no averaging round was requested")
         if averaging_opts and not averaging_round:
-            logger.warning(f"Averaging parameters not used because averaging_round=False: {averaging_opts}")
-        if averaging_control is not None:
-            assert averaging_round, "averaging_control is unused if averaging_round is not performed"
+            logger.warning(f"averaging_opts ignored without an averaging round: {averaging_opts}")
         if wait_for_trigger is not None:
-            assert optimizer_step or zero_grad or averaging_round, "trigger is only used for updating parameters"
+            if not (optimizer_step or zero_grad or averaging_round):
+                raise ValueError("wait_for_trigger only makes sense with work that modifies the state")
             if not (self.reuse_tensors or self.custom_gradients):
-                # the trigger fires in the background, i.e. possibly after the caller has overwritten its gradients:
-                # only safe when the optimizer has its own gradient buffers that the caller fills explicitly
-                raise ValueError("wait_for_trigger requires reuse_tensors or custom_gradients (manual gradient handling)")
-        output = None
+                # the trigger fires in the background, possibly after the caller has overwritten its gradients: only
+                # safe when the optimizer has its own gradient buffers that the caller fills explicitly
+                raise ValueError("wait_for_trigger requires reuse_tensors or custom_gradients")
 
+        result = None
         if wait_for_delayed_updates:
-            for pending_update in list(self.pending_updates):
+            limit = (averaging_opts or {}).get("averaging_timeout", self._allreduce_timeout)
+            for job in list(self.pending_updates):
                 try:
-                    timeout = (averaging_opts or {}).get("averaging_timeout", self._allreduce_timeout)
-                    logger.log(self.status_loglevel, "Waiting for delayed updates to finish...")
-                    output = pending_update.result(timeout)
+                    logger.log(self.status_loglevel, "Waiting for background updates to finish")
+                    result = job.result(limit)
                 except BaseException:
-                    if not pending_update.done():
-                        pending_update.cancel()
-        finished = {update for update in self.pending_updates if update.done()}
-        self.pending_updates = {update for update in self.pending_updates if not update.done()}
-        for update in finished:
-            if update.cancelled() or update.exception():
-                logger.log(self.status_loglevel, f"Background update failed: {update}")
+                    job.cancel()
+        for job in [j for j in self.pending_updates if j.done()]:
+            self.pending_updates.discard(job)
+            if job.cancelled() or job.exception() is not None:
+                logger.log(self.status_loglevel, f"A background update failed: {job}")
 
         if apply_delayed_updates:
-            if self.finished_averaging_round.is_set():
-                if not self.reuse_tensors:
-                    self._apply_averaging_results_()
-                if self.offload_optimizer and not self.finished_optimizer_step.is_set():
-                    self._apply_optimizer_parameters_()
-                logger.log(self.status_loglevel, "Received parameters from background averaging round")
-                self.finished_averaging_round.clear()
-            if self.finished_optimizer_step.is_set():
-                if self.offload_optimizer:
-                    self._apply_optimizer_parameters_()
-                logger.debug("Received parameters from background optimizer step")
-                self.finished_optimizer_step.clear()
-
+            self._collect_background_results()
         if increment_epoch:
             self.local_epoch += 1
+        if not (optimizer_step or zero_grad or averaging_round):
+            return result
 
-        if optimizer_step or zero_grad or averaging_round:
-            if self.offload_optimizer and not self.custom_gradients:
-                self._load_local_grads_into_optimizer_()
-            pending_update = self.step_executor.submit(self._do, wait_for_trigger, optimizer_step, zero_grad,
-                                                       averaging_round, averaging_control, grad_scaler, set_to_none,
-                                                       **averaging_opts or {})
-            self.pending_updates.add(pending_update)
-            should_await_optimizer = (optimizer_step or zero_grad) and not delay_optimizer_step
-            should_await_averaging = averaging_round and not delay_averaging
-            if should_await_optimizer:
-                self.finished_optimizer_step.wait()
-                self.finished_optimizer_step.clear()
-                if self.offload_optimizer and not should_await_averaging:
-                    self._apply_optimizer_parameters_()
-                logger.debug("Finished optimizer step")
-            if should_await_averaging:
-                self.finished_averaging_round.wait()
-                self.finished_averaging_round.clear()
-                if not self.reuse_tensors:
-                    self._apply_averaging_results_()
-                if self.offload_optimizer:
-                    self._apply_optimizer_parameters_()
-                logger.log(self.status_loglevel, "Finished averaging round")
-            async_averaging = averaging_round and delay_averaging
-            async_optimizer = (optimizer_step or zero_grad) and delay_optimizer_step
-            if not (async_averaging or async_optimizer):
-                try:
-                    output = pending_update.result()
-                finally:
-                    self.pending_updates.discard(pending_update)
-        return output
+        if self.offload_optimizer and not self.custom_gradients:
+            self._hand_gradients_to_optimizer()
+        request = _Request(wait_for_trigger, optimizer_step, zero_grad, averaging_round, averaging_control, grad_scaler,
+                           set_to_none, dict(averaging_opts or {}))
+        job: Future = self._worker.submit(self._background, request)
+        self.pending_updates.add(job)
+        optimizer_in_foreground = (optimizer_step or zero_grad) and not delay_optimizer_step
+        averaging_in_foreground = averaging_round and not delay_averaging
+        if optimizer_in_foreground:
+            self.finished_optimizer_step.wait()
+            self.finished_optimizer_step.clear()
+            if self.offload_optimizer and not averaging_in_foreground:
+                self._publish_optimizer_parameters()
+        if averaging_in_foreground:
+            self.finished_averaging_round.wait()
+            self.finished_averaging_round.clear()
+            self._take_over_averaged_state()
+            logger.log(self.status_loglevel, "Finished the averaging round")
+        everything_awaited = (optimizer_in_foreground or not (optimizer_step or zero_grad)) and \
+                             (averaging_in_foreground or not averaging_round)
+        if everything_awaited:
+            try:
+                result = job.result()
+            finally:
+                self.pending_updates.discard(job)
+        return result
 
-    def _do(self, wait_for_trigger, optimizer_step: bool, zero_grad: bool, averaging_round: bool,
-            averaging_control: Optional[StepControl], grad_scaler, set_to_none: bool, timeout: Optional[float] = None,
-            **kwargs):
-        """Background worker: (trigger) -> optimizer step -> zero_grad -> scheduler -> averaging round."""
-        if averaging_control is not None and (averaging_control.triggered or averaging_control.done()):
-            logger.log(self.status_loglevel, f"Discarding failed matchmaking results: {averaging_control}")
-            averaging_control = None
-        start_time = time.perf_counter()
-        began_running = False
+    def _collect_background_results(self) -> None:
+        """Bring what the worker has finished since the last call into the model."""
+        if self.finished_averaging_round.is_set():
+            self._take_over_averaged_state(optimizer_too=not self.finished_optimizer_step.is_set())
+            self.finished_averaging_round.clear()
+            logger.log(self.status_loglevel, "Took over parameters from a background averaging round")
+        if self.finished_optimizer_step.is_set():
+            if self.offload_optimizer:
+                self._publish_optimizer_parameters()
+            self.finished_optimizer_step.clear()
+
+    def _take_over_averaged_state(self, optimizer_too: bool = True) -> None:
+        if not self.reuse_tensors:
+            self._adopt_averaged_tensors()
+        if self.offload_optimizer and optimizer_too:
+            self._publish_optimizer_parameters()
+
+    # ---------------------------------------------------------------------------------------------- background
+    def _background(self, req: _Request):
+        """Worker body: (trigger) -> optimizer step -> zero_grad -> scheduler -> averaging round."""
+        control = req.control
+        if control is not None and (control.triggered or control.done()):
+            logger.log(self.status_loglevel, f"The pre-scheduled round is of no use any more: {control}")
+            control = None
+        began, started_at = False, time.perf_counter()
+        timeout = req.averaging_opts.pop("timeout", None)
         try:
-            if averaging_round and averaging_control is None:
-                averaging_control = super().step(gather=self.local_epoch, require_trigger=True, timeout=timeout,
-                                                 wait=False, **kwargs)
-            if wait_for_trigger is not None:
-                wait_for_trigger()
-            began_running = True
-            with self.lock_optimizer:
-                if optimizer_step:
-                    with self.lock_averaged_tensors if self.reuse_tensors else nullcontext():
-                        logger.debug("Running optimizer step")
-                        if grad_scaler is None:
+            if req.averaging_round and control is None:
+                control = super().step(gather=self.local_epoch, require_trigger=True, timeout=timeout, wait=False,
+                                       **req.averaging_opts)
+            if req.trigger is not None:
+                req.trigger()
+            began = True
+            with self._optimizer_lock:
+                if req.optimizer_step:
+                    guard = self.lock_averaged_tensors if self.reuse_tensors else threading.Lock()
+                    with guard:
+                        if req.grad_scaler is None:
                             self.optimizer.step()
                         else:
-                            with grad_scaler.running_global_step():
-                                assert grad_scaler.step(self.optimizer)
-                if zero_grad:
-                    logger.debug("Running zero grad")
+                            with req.grad_scaler.running_global_step():
+                                if not req.grad_scaler.step(self.optimizer):
+                                    raise RuntimeError("the gradient scaler refused a global optimizer step")
+                if req.zero_grad:
                     self.optimizer.zero_grad()
                     if self.offload_optimizer:
-                        for parameter in self.main_parameters:
-                            if set_to_none:
-                                parameter.grad = None
-                            elif parameter.grad is not None:
-                                parameter.grad.zero_()
+                        for p in self.main_parameters:
+                            if req.set_to_none:
+                                p.grad = None
+                            elif p.grad is not None:
+                                p.grad.zero_()
                 self._update_scheduler()
                 self.finished_optimizer_step.set()
-            if averaging_round:
-                with self.lock_averaging:
-                    if not self.reuse_tensors:
-                        self._load_local_tensors_into_averager_()
-                    if self.delta_rule_averaging:
-                        with torch.no_grad(), self.get_tensors() as averaged_tensors:
-                            self._old_tensors = tuple(x.clone() for x in averaged_tensors)
-                    self.delay_before_averaging.update(task_size=1, interval=time.perf_counter() - start_time)
-                    try:
-                        averaging_control.allow_allreduce()
-                        gathered = averaging_control.result(timeout=timeout)
-                        logger.log(self.status_loglevel, f"Averaged parameters with {len(gathered)} peers")
-                    except BaseException as e:
-                        logger.log(self.status_loglevel, f"Averaging failed with {type(e)}")
-                        gathered = {}
-                    self.finished_averaging_round.set()
+            if req.averaging_round:
+                gathered = self._averaging_round(control, timeout, started_at)
                 if self.sync_epoch_when_averaging:
-                    old_epoch = self.local_epoch
-                    for peer_epoch in gathered.values():
-                        self.local_epoch = max(self.local_epoch, peer_epoch)
-                    if self.local_epoch != old_epoch:
-                        logger.log(self.status_loglevel, f"Found peer with newer epoch ({self.local_epoch})")
+                    newest = max([self.local_epoch, *[e for e in gathered.values() if isinstance(e, int)]])
+                    if newest != self.local_epoch:
+                        logger.log(self.status_loglevel, f"A groupmate is at epoch {newest}; catching up")
+                        self.local_epoch = newest
                         self._update_scheduler()
         except Exception as e:
-            if not began_running:
-                logger.error(f"Aborted {self.__class__.__name__}.step because wait_for_trigger raised exception")
+            if not began:
+                logger.error(f"{type(self).__name__}: the trigger failed, nothing was modified")
             logger.exception(e)
-            if averaging_control is not None and not averaging_control.done():
-                logger.error("Cancelled scheduled state averaging round")
-                averaging_control.cancel()
+            if control is not None and not control.done():
+                control.cancel()
             self.finished_optimizer_step.set()
             self.finished_averaging_round.set()
 
+    def _averaging_round(self, control: StepControl, timeout: Optional[float], started_at: float) -> Dict:
+        with self._rounds_lock:
+            if not self.reuse_tensors:
+                self._refresh_averaged_tensors()
+            if self.delta_rule_averaging:
+                with torch.no_grad(), self.get_tensors() as averaged:
+                    self._snapshot = [t.clone() for t in averaged]
+            self.delay_before_averaging.update(task_size=1, interval=time.perf_counter() - started_at)
+            try:
+                control.allow_allreduce()
+                gathered = control.result(timeout=timeout)
+                logger.log(self.status_loglevel, f"Averaged state with {len(gathered)} peers")
+            except BaseException as e:
+                logger.log(self.status_loglevel, f"State averaging failed: {e!r}")
+                gathered = {}
+            self.finished_averaging_round.set()
+        return gathered
+
     # ---------------------------------------------------------------------------------------------- copies
-    def _optimizer_parameters(self):
-        return [param for group in self.optimizer.param_groups for param in group["params"]]
-
     @torch.no_grad()
-    def _load_local_grads_into_optimizer_(self) -> None:
-        """Copy the model's gradients into the gradient buffers of the offloaded optimizer."""
-        assert self.offload_optimizer
+    def _hand_gradients_to_optimizer(self) -> None:
+        """Model gradients -> gradient buffers of the offloaded optimizer."""
         dst, src = [], []
-        for main_param, opt_param in zip(self.main_parameters, self._optimizer_parameters()):
-            if main_param.grad is not None:
-                if opt_param.grad is None:
-                    opt_param.grad = main_param.grad.detach().to(opt_param.dtype, copy=True)
-                else:
-                    dst.append(opt_param.grad)
-                    src.append(main_param.grad)
-        _copy_all_(dst, src)
-
-    @torch.no_grad()
-    def _apply_optimizer_parameters_(self) -> None:
-        """Copy parameters from the offloaded optimizer into the model."""
-        assert self.offload_optimizer
-        offloaded = self._optimizer_parameters()
-        assert len(offloaded) == len(self.main_parameters), "Optimizer parameters changed during training"
-        _copy_all_(list(self.main_parameters), offloaded)
-        for p in self.main_parameters:
-            torch.autograd.graph.increment_version(p)
-
-    @torch.no_grad()
-    def _load_local_tensors_into_averager_(self) -> None:
-        assert not self.reuse_tensors
-        with self.get_tensors() as averaged_tensors:
-            _copy_all_(list(averaged_tensors), list(self._local_tensors()))
-
-    @torch.no_grad()
-    def _apply_averaging_results_(self) -> None:
-        """Copy averaged tensors into the local ones (or add the change since the round began: the delta rule)."""
-        assert not self.reuse_tensors
-        if self.delta_rule_averaging and self._old_tensors is None:
-            logger.warning("Using delta_rule_averaging, but old tensors were not found. Averaging may have failed")
-        with self.get_tensors() as averaged_tensors:
-            local_tensors = list(self._local_tensors())
-            assert len(local_tensors) == len(averaged_tensors), "Tensor structure changed during training"
-            if not self.delta_rule_averaging or self._old_tensors is None:
-                _copy_all_(local_tensors, list(averaged_tensors))
+        for model_p, opt_p in zip(self.main_parameters, self._optimizer_parameters()):
+            if model_p.grad is None:
+                continue
+            if opt_p.grad is None:
+                opt_p.grad = model_p.grad.detach().to(opt_p.dtype, copy=True)
             else:
-                assert len(self._old_tensors) == len(local_tensors)
-                if all(l.device == n.device and l.dtype == torch.float32 for l, n in zip(local_tensors, averaged_tensors)):
-                    mt.delta_update_(local_tensors, list(averaged_tensors), list(self._old_tensors))
-                else:
-                    for local_tensor, new_tensor, old_tensor in zip(local_tensors, averaged_tensors, self._old_tensors):
-                        local_tensor.add_((new_tensor - old_tensor).to(local_tensor.device, local_tensor.dtype))
-            for t in local_tensors:
-                torch.autograd.graph.increment_version(t)
+                dst.append(opt_p.grad)
+                src.append(model_p.grad)
+        _bulk_copy(dst, src)
 
-    @property
-    def averaging_in_progress(self) -> bool:
-        return self.lock_averaging.locked()
+    @torch.no_grad()
+    def _publish_optimizer_parameters(self) -> None:
+        """Offloaded optimizer parameters -> model."""
+        shadow = self._optimizer_parameters()
+        if len(shadow) != len(self.main_parameters):
+            raise RuntimeError("the optimizer's parameters changed during training")
+        _bulk_copy(list(self.main_parameters), shadow)
+        _bump_versions(self.main_parameters)
+
+    @torch.no_grad()
+    def _refresh_averaged_tensors(self) -> None:
+        """Trainer-side tensors -> averaged copies (only when they are separate)."""
+        with self.get_tensors() as averaged:
+            _bulk_copy(list(averaged), self._tracked_tensors())
+
+    @torch.no_grad()
+    def _adopt_averaged_tensors(self) -> None:
+        """Averaged copies -> trainer-side tensors; with the delta rule, only what the round changed is added."""
+        if self.delta_rule_averaging and self._snapshot is None:
+            logger.warning("delta_rule_averaging is on but there is no snapshot; did the averaging round fail?")
+        with self.get_tensors() as averaged:
+            local = self._tracked_tensors()
+            if len(local) != len(averaged):
+                raise RuntimeError("the set of averaged tensors changed during training")
+            if not self.delta_rule_averaging or self._snapshot is None:
+                _bulk_copy(local, list(averaged))
+            elif all(l.device == a.device and l.dtype == torch.float32 for l, a in zip(local, averaged)):
+                mt.delta_update_(local, list(averaged), list(self._snapshot))
+            else:
+                for l, new, old in zip(local, averaged, self._snapshot):
+                    l.add_((new - old).to(l.device, l.dtype))
+            _bump_versions(local)
 
     # ---------------------------------------------------------------------------------------------- state exchange
     def get_current_state(self):
         """(metadata, tensors, infos) for peers that download our state.
 
-        Layout contract (hivemind/optim/state_averager.py:627-656): metadata = {epoch, group_bits,
-        optimizer_metadata}; tensors = parameters, extra tensors, then optimizer tensors in ``nested_flatten``
-        order of the optimizer's ``state_dict()``.
+        Layout (hivemind/optim/state_averager.py:627-656): metadata = {epoch, group_bits, optimizer_metadata};
+        tensors = parameters, extra tensors, then the optimizer's tensors in ``nested_flatten`` order of its
+        ``state_dict()``. CUDA tensors are handed over as they are: the state codecs have device encoders, so only
+        compressed bytes travel to the host.
         """
         with torch.no_grad(), self.lock_averaged_tensors:
-            optimized_parameters = tuple(param.detach().cpu() for param in self._optimizer_parameters())
-            parameter_infos = [CompressionInfo.from_tensor(param, key=key, role=TensorRole.PARAMETER)
-                               for param, key in zip(optimized_parameters, self.parameter_names)]
-            extra_tensors = tuple(tensor.detach().cpu() for tensor in self.extra_tensors)
-            extra_infos = [CompressionInfo.from_tensor(extra_tensor, key=i, role=TensorRole.UNSPECIFIED)
-                           for i, extra_tensor in enumerate(extra_tensors)]
-            optimizer_metadata, optimizer_tensors = dump_optimizer_state(self.optimizer)
-            optimizer_infos = [CompressionInfo.from_tensor(opt_tensor, key=i, role=TensorRole.OPTIMIZER)
-                               for i, opt_tensor in enumerate(optimizer_tensors)]
-        metadata = dict(epoch=self.local_epoch, group_bits=self.get_group_bits(), optimizer_metadata=optimizer_metadata)
-        all_tensors = list(chain(optimized_parameters, extra_tensors, optimizer_tensors))
-        all_tensor_infos = list(chain(parameter_infos, extra_infos, optimizer_infos))
-        return metadata, all_tensors, all_tensor_infos
+            params = [p.detach().clone() for p in self._optimizer_parameters()]
+            extras = [t.detach().clone() for t in self.extra_tensors]
+            opt_meta, opt_tensors = dump_optimizer_state(self.optimizer, to_cpu=False)
+        infos = [CompressionInfo.from_tensor(p, key=name, role=TensorRole.PARAMETER)
+                 for p, name in zip(params, self.parameter_names)]
+        infos += [CompressionInfo.from_tensor(t, key=i, role=TensorRole.UNSPECIFIED) for i, t in enumerate(extras)]
+        infos += [CompressionInfo.from_tensor(t, key=i, role=TensorRole.OPTIMIZER) for i, t in enumerate(opt_tensors)]
+        metadata = dict(epoch=self.local_epoch, group_bits=self.get_group_bits(), optimizer_metadata=opt_meta)
+        return metadata, params + extras + list(opt_tensors), infos
 
     def load_state_from_peers(self, **kwargs) -> None:
-        """Download the latest training state from a peer and load it into the model, optimizer and scheduler."""
-        opt_parameters = tuple(self._optimizer_parameters())
-        main_parameters_and_extras = tuple(chain(opt_parameters, self.extra_tensors))
-        num_parameters_and_extras = len(main_parameters_and_extras)
-        loaded_state = super().load_state_from_peers(**kwargs)
-        if loaded_state is None:
+        """Download the newest training state on offer and load it into model, optimizer and scheduler."""
+        targets = self._optimizer_parameters() + list(self.extra_tensors)
+        downloaded = super().load_state_from_peers(**kwargs)
+        if downloaded is None:
             return
-        metadata, flat_tensors = loaded_state
-        if (not isinstance(metadata.get("epoch"), int)) or metadata["epoch"] < self.local_epoch:
-            logger.warning("Cowardly refusing to load state from peer: peer's epoch is behind our local epoch")
+        metadata, tensors = downloaded
+        epoch = metadata.get("epoch")
+        if not isinstance(epoch, int) or epoch < self.local_epoch:
+            logger.warning("Not loading a peer's state: it is older than ours")
             return
-        loaded_parameters_and_extras = flat_tensors[:num_parameters_and_extras]
-        loaded_opt_tensors = flat_tensors[num_parameters_and_extras:]
-        if num_parameters_and_extras != len(loaded_parameters_and_extras):
-            logger.error("Failed to load state from peer, received parameters, extras or metadata")
+        if len(tensors) < len(targets):
+            logger.error("Not loading a peer's state: it has fewer tensors than we have parameters")
             return
         with torch.no_grad(), self.lock_averaged_tensors:
             try:
-                load_optimizer_state(self.optimizer, metadata["optimizer_metadata"], loaded_opt_tensors)
-            except StopIteration:
-                logger.warning("Failed to load state from peer, received inconsistent number of optimizer statistics")
+                load_optimizer_state(self.optimizer, metadata["optimizer_metadata"], tensors[len(targets):])
+            except (StopIteration, KeyError, ValueError):
+                logger.warning("Not loading a peer's state: its optimizer statistics do not match ours")
                 return
-            for local_param, loaded_param in zip(main_parameters_and_extras, loaded_parameters_and_extras):
-                local_param.copy_(loaded_param.to(local_param.device, local_param.dtype), non_blocking=True)
+            for mine, theirs in zip(targets, tensors):
+                mine.copy_(theirs.to(mine.device, mine.dtype), non_blocking=True)
         if self.offload_optimizer:
-            self._apply_optimizer_parameters_()
+            self._publish_optimizer_parameters()
         if not self.reuse_tensors:
-            self._load_local_tensors_into_averager_()
-        self.local_epoch = metadata["epoch"]
+            self._refresh_averaged_tensors()
+        self.local_epoch = epoch
         self._update_scheduler()
 
     def _update_scheduler(self) -> None:
-        """Bring the LR schedule to ``local_epoch`` (one scheduler step per epoch)."""
-        if self.scheduler:
+        """One scheduler step per epoch: catch the schedule up with ``local_epoch``."""
+        if self.scheduler is not None:
             while self.scheduler._step_count <= self.local_epoch:
                 self.scheduler.step()
 
     def shutdown(self) -> None:
-        self.step_executor.shutdown(wait=False)
+        self._worker.shutdown(wait=False)
         super().shutdown()
 
 
 def initialize_optimizer_state_(opt: torch.optim.Optimizer) -> None:
-    """Create optimizer statistics by running one step with zero gradients (parameters are restored afterwards)."""
-    flat_params = tuple(param for group in opt.param_groups for param in group["params"])
-    old_grads, old_values = [], []
-    for param in flat_params:
-        old_grads.append(param.grad)
-        old_values.append(param.detach().clone())
-        param.grad = torch.zeros_like(param)
+    """Make the optimizer allocate its statistics: one step on zero gradients, after which parameters and
+    gradients are put back as they were."""
+    saved = [(p, p.grad, p.detach().clone()) for group in opt.param_groups for p in group["params"]]
+    for p, _, _ in saved:
+        p.grad = torch.zeros_like(p)
     opt.step()
     with torch.no_grad():
-        for param, old_grad, old_value in zip(flat_params, old_grads, old_values):
-            param.grad = old_grad
-            param.copy_(old_value)
+        for p, grad, value in saved:
+            p.grad = grad
+            p.copy_(value)
 
 
-def dump_optimizer_state(opt: torch.optim.Optimizer):
-    """Split an optimizer ``state_dict`` into msgpack-friendly metadata and a list of CPU tensors."""
+def dump_optimizer_state(opt: torch.optim.Optimizer, to_cpu: bool = True):
+    """Flatten ``opt.state_dict()`` into msgpack-friendly metadata plus the list of tensors it refers to."""
+    metadata, tensors = [], []
     with torch.no_grad():
-        flat_metadata, flat_tensors = [], []
-        for elem in nested_flatten(opt.state_dict()):
-            if isinstance(elem, torch.Tensor):
-                flat_metadata.append(dict(type="tensor", index=len(flat_tensors)))
-                flat_tensors.append(elem.cpu())
+        for leaf in nested_flatten(opt.state_dict()):
+            if torch.is_tensor(leaf):
+                metadata.append(dict(type="tensor", index=len(tensors)))
+                tensors.append(leaf.cpu() if to_cpu else leaf.detach().clone())
             else:
-                flat_metadata.append(dict(type="value", value=elem))
-        return flat_metadata, flat_tensors
+                metadata.append(dict(type="value", value=leaf))
+    return metadata, tensors
 
 
 def load_optimizer_state(optimizer: torch.optim.Optimizer, flat_metadata, flat_tensors: Sequence[torch.Tensor]):
     """Inverse of ``dump_optimizer_state``: rebuild the state dict in the optimizer's own structure and load it."""
-    flat_optimizer_state = []
-    for elem in flat_metadata:
-        if elem.get("type") == "tensor" and isinstance(elem.get("index"), int):
-            flat_optimizer_state.append(flat_tensors[elem["index"]])
-        elif elem.get("type") == "value" and "value" in elem:
-            flat_optimizer_state.append(elem["value"])
-    return optimizer.load_state_dict(nested_pack(flat_optimizer_state, structure=optimizer.state_dict()))
+    leaves = []
+    for entry in flat_metadata:
+        kind = entry.get("type")
+        if kind == "tensor" and isinstance(entry.get("index"), int):
+            leaves.append(flat_tensors[entry["index"]])
+        elif kind == "value" and "value" in entry:
+            leaves.append(entry["value"])
+    return optimizer.load_state_dict(nested_pack(leaves, structure=optimizer.state_dict()))

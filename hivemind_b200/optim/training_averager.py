@@ -18,7 +18,7 @@ import torch
 from hivemind_b200.averaging import DecentralizedAverager
 from hivemind_b200.compression import CompressionInfo, TensorRole
 from hivemind_b200.ops import multi_tensor as mt
-from hivemind_b200.optim.state_averager import (_copy_all_, dump_optimizer_state, initialize_optimizer_state_,
+from hivemind_b200.optim.state_averager import (_bulk_copy, dump_optimizer_state, initialize_optimizer_state_,
                                                 load_optimizer_state)
 from hivemind_b200.utils import get_logger
 
@@ -66,7 +66,7 @@ class TrainingAverager(DecentralizedAverager):
                 assert len(local_tensors) == len(averaged_tensors), "The number of optimized parameters should not change."
                 if use_old_local_tensors:
                     old_local_tensors = tuple(x.detach().float().clone() for x in local_tensors)
-                _copy_all_(list(averaged_tensors), local_tensors)
+                _bulk_copy(list(averaged_tensors), local_tensors)
             self.pending_updates_done.set()
             gathered = super().step(**kwargs)
             if gathered is not None:
@@ -83,7 +83,7 @@ class TrainingAverager(DecentralizedAverager):
                             for local, new, old in zip(local_tensors, averaged_tensors, old_local_tensors):
                                 local.add_((new - old).to(local.device, local.dtype))
                     else:
-                        _copy_all_(local_tensors, list(averaged_tensors))
+                        _bulk_copy(local_tensors, list(averaged_tensors))
                 self.pending_updates_done.set()
             self.local_step += 1
             return gathered

@@ -1,31 +1,35 @@
-"""Host side of the device butterfly: arenas, handle exchange, part tables and kernel launches.
+"""Host side of the device butterfly: arenas, handle exchange, part tables and the launches of a round.
 
-One ``DeviceEndpoint`` belongs to one averager (one GPU). It owns a single device allocation ("arena") that holds
-the averaged tensors as one flat fp32 vector plus the staging areas that other GPUs read: the outbox with encoded
-parts, the delta box with encoded averages-minus-input, and the flag pages. At group assembly every member's
-``describe()`` blob travels in the matchmaking ``gather`` field; members map each other's arenas (CUDA IPC across
-processes, peer access inside one process) and then each runs ``run_round``: a fixed sequence of kernel launches
-(``ops/csrc/butterfly.cu``) on a private stream, with no host synchronisation until the end.
+One ``DeviceEndpoint`` belongs to one averager (one GPU). It owns a single device allocation ("arena") that holds the
+averaged tensors as one flat fp32 vector plus the staging areas that other GPUs read: the outbox with encoded chunk
+records, the delta box with encoded averages-minus-input, the averages of uncompressed parts and the flag pages. The
+staging areas exist twice and alternate between this endpoint's rounds (``parity``), so that a groupmate that is
+still reading the results of round r is not disturbed when this endpoint begins round r + 1 with somebody else; before
+a staging copy is used again (round r + 2) the gate kernel checks that the readers of round r have acknowledged.
+
+At group assembly every member's ``describe()`` blob travels in the matchmaking ``gather`` field; members map each
+other's arenas (CUDA IPC across processes, peer access inside one process) and then each runs ``run_round``: a gate
+kernel and ONE persistent round kernel (``ops/csrc/butterfly_round.cu``) on a private stream, with no host
+synchronisation until the end. Averaging weights travel inside the senders' flags, so no extra RPC precedes a round.
 
 Division of labour with the reference: ``TensorPartContainer`` / ``TensorPartReducer`` / ``AllReduceRunner``
 (hivemind/averaging/partition.py, allreduce.py) become a part table in device memory, bounded flag waits and
-per-part inclusion decisions; load balancing, modes, weights and timeouts keep their meaning.
+per-part inclusion decisions; load balancing, modes, weights and timeouts keep their meaning. A client-mode peer is
+an ordinary member with an empty span here: its arena can be read like anybody else's.
 """
 from __future__ import annotations
 
 import ctypes
 import os
-import time
 import socket
 import threading
+import time
 import zlib
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
-
-from hivemind_b200.utils.profiling import device_range
 
 from hivemind_b200.averaging.allreduce import AveragingMode
 from hivemind_b200.averaging.partition import compute_part_layout
@@ -36,6 +40,7 @@ from hivemind_b200.compression.adaptive import AdaptiveCompressionBase
 from hivemind_b200.compression.quantization import dynamic_code_table
 from hivemind_b200.ops import _lib
 from hivemind_b200.utils.logging import get_logger
+from hivemind_b200.utils.profiling import device_range
 
 logger = get_logger(__name__)
 
@@ -44,11 +49,17 @@ DEBUG_CHECKS = os.environ.get("HIVEMIND_B200_DEBUG", "0") == "1"
 EXIT_GRACE_SECONDS = 2.0  # how long after a round peers may still read this arena (see DeviceEndpoint.close)
 MAX_PEERS = 16
 ALIGN = 16  # elements: tensor starts and part boundaries are multiples of this, so every access is 16-byte aligned
-PH_STATS, PH_BORDERS, PH_ENCODE, PH_PUBLISH, PH_REDUCE, PH_APPLY = range(6)
+CHUNK = 16384  # elements per chunk record (HR_CHUNK in butterfly_round.cu)
+ACK_RING = 8
+DELTA_BOX_FACTOR = 1.5  # delta box capacity relative to the outbox: 1.0 suffices for equal spans
 _CODEC_IDS = {NoCompression: 0, ScaledFloat16Compression: 1, Float16Compression: 2, Quantile8BitQuantization: 3,
               Uniform8BitQuantization: 4, BlockwiseQuantization: 5}
-_NEEDS_STATS, _NEEDS_BORDERS = (1, 4), (3,)
-CODEC_NONE = 0  # uncompressed parts take the in-place path (no outbox record, no delta record)
+CODEC_NONE = 0  # uncompressed parts are read in place: no outbox record, no delta record
+_HEADER_BYTES = {0: 0, 1: 16, 2: 0, 3: 1024, 4: 1024, 5: 16}
+_ELEM_BYTES = {0: 4, 1: 2, 2: 2, 3: 1, 4: 1, 5: 1}
+
+# distinguishes processes reliably (pids repeat across containers that share a boot id)
+_PROCESS_TOKEN = os.urandom(16)
 
 
 def codec_id(compression: CompressionBase, info: CompressionInfo) -> Optional[int]:
@@ -58,42 +69,69 @@ def codec_id(compression: CompressionBase, info: CompressionInfo) -> Optional[in
     return _CODEC_IDS.get(type(compression))
 
 
-class _HbPeer(ctypes.Structure):
-    _fields_ = [("data", ctypes.c_void_p), ("outbox", ctypes.c_void_p), ("deltabox", ctypes.c_void_p),
-                ("ready", ctypes.c_void_p), ("delta_ready", ctypes.c_void_p), ("avg", ctypes.c_void_p)]
+def chunk_stride(codec: int) -> int:
+    """Bytes of one chunk record: header + a full chunk of payload (also for the last, shorter chunk of a part)."""
+    return _HEADER_BYTES[codec] + CHUNK * _ELEM_BYTES[codec]
 
 
-class _HbGroup(ctypes.Structure):
+def record_bytes(codec: int, length: int) -> int:
+    """Bytes of all chunk records of one part (0 for uncompressed parts, which have no records)."""
+    if codec == CODEC_NONE:
+        return 0
+    return chunk_stride(codec) * ((length + CHUNK - 1) // CHUNK)
+
+
+class _HrLayout(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_ulonglong), ("avg", ctypes.c_ulonglong * 2), ("outbox", ctypes.c_ulonglong * 2),
+                ("deltabox", ctypes.c_ulonglong * 2), ("ready", ctypes.c_ulonglong * 2),
+                ("dready", ctypes.c_ulonglong * 2), ("hello", ctypes.c_ulonglong), ("done_ring", ctypes.c_ulonglong)]
+
+
+class _HrRound(ctypes.Structure):
     _fields_ = [("n_peers", ctypes.c_int), ("n_parts", ctypes.c_int), ("me", ctypes.c_int),
-                ("max_local_parts", ctypes.c_int), ("epoch", ctypes.c_uint), ("alpha", ctypes.c_float),
+                ("max_local_parts", ctypes.c_int), ("epoch", ctypes.c_uint), ("parity", ctypes.c_int),
+                ("alpha", ctypes.c_float), ("my_weight", ctypes.c_float),
                 ("sender_timeout_ns", ctypes.c_ulonglong), ("reducer_timeout_ns", ctypes.c_ulonglong),
-                ("delta_stride", ctypes.c_ulonglong), ("weight", ctypes.c_float * MAX_PEERS),
-                ("sends", ctypes.c_int * MAX_PEERS), ("peer", _HbPeer * MAX_PEERS), ("parts", ctypes.c_void_p),
-                ("part_stats", ctypes.c_void_p), ("dstats", ctypes.c_void_p), ("bins", ctypes.c_void_p),
-                ("bin_cnt", ctypes.c_void_p), ("dbins", ctypes.c_void_p), ("dbin_cnt", ctypes.c_void_p),
-                ("borders", ctypes.c_void_p), ("dborders", ctypes.c_void_p), ("include", ctypes.c_void_p),
-                ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p), ("t_start", ctypes.c_void_p),
-                ("status", ctypes.c_void_p), ("avg", ctypes.c_void_p)]
+                ("delta_stride", ctypes.c_ulonglong), ("sends", ctypes.c_int * MAX_PEERS),
+                ("base", ctypes.c_void_p * MAX_PEERS), ("lay", _HrLayout), ("parts", ctypes.c_void_p),
+                ("items", ctypes.c_void_p), ("pub_list", ctypes.c_void_p), ("n_send", ctypes.c_int),
+                ("n_reduce", ctypes.c_int), ("n_apply", ctypes.c_int), ("item_begin", ctypes.c_int),
+                ("item_end", ctypes.c_int), ("queue_slot", ctypes.c_int), ("final_stage", ctypes.c_int),
+                ("include", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p),
+                ("t_start", ctypes.c_void_p), ("status", ctypes.c_void_p), ("status_out", ctypes.c_void_p),
+                ("part_done", ctypes.c_void_p), ("dpart_done", ctypes.c_void_p), ("queue", ctypes.c_void_p),
+                ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint)]
+
+
+class _HrGate(ctypes.Structure):
+    _fields_ = [("n_peers", ctypes.c_int), ("me", ctypes.c_int), ("parity", ctypes.c_int), ("n_prev", ctypes.c_int),
+                ("epoch", ctypes.c_uint), ("prev_epoch", ctypes.c_uint), ("ack_timeout_ns", ctypes.c_ulonglong),
+                ("hello_timeout_ns", ctypes.c_ulonglong), ("base", ctypes.c_void_p * MAX_PEERS),
+                ("prev_base", ctypes.c_void_p * MAX_PEERS), ("lay", _HrLayout), ("gate_status", ctypes.c_void_p)]
 
 
 _PART_DTYPE = np.dtype([("start", "<i8"), ("enc_off", "<i8"), ("span_off", "<i8"), ("avg_off", "<i8"), ("len", "<i4"),
                         ("owner", "<i4"), ("local_idx", "<i4"), ("codec", "<i4")])
 
-_code_uploaded: Dict[int, bool] = {}
+_code_tables: Dict[int, torch.Tensor] = {}
 _code_lock = threading.Lock()
 
 
-def _ensure_code_table(device_index: int) -> None:
+def _code_table_on(device: torch.device) -> torch.Tensor:
+    """[512] fp32 on the device: the block-wise code (sorted) and the midpoints between consecutive entries."""
     with _code_lock:
-        if _code_uploaded.get(device_index):
-            return
-        lib = _lib.load_library()
-        assert lib.hm_bf_sizeof_group() == ctypes.sizeof(_HbGroup), "HbGroup layout mismatch between C and Python"
-        assert lib.hm_bf_sizeof_part() == _PART_DTYPE.itemsize, "HbPart layout mismatch between C and Python"
-        code = dynamic_code_table().numpy().astype(np.float32)
-        with torch.cuda.device(device_index):
-            _lib.check(lib.hm_bf_set_blockwise_code(code.ctypes.data_as(ctypes.c_void_p)), "hm_bf_set_blockwise_code", 0)
-        _code_uploaded[device_index] = True
+        table = _code_tables.get(device.index)
+        if table is None:
+            lib = _lib.load_library()
+            assert lib.hm_br_sizeof_round() == ctypes.sizeof(_HrRound), "HrRound layout mismatch between C and Python"
+            assert lib.hm_br_sizeof_gate() == ctypes.sizeof(_HrGate), "HrGate layout mismatch between C and Python"
+            assert lib.hm_br_sizeof_part() == _PART_DTYPE.itemsize, "HrPart layout mismatch between C and Python"
+            assert lib.hm_br_chunk() == CHUNK
+            code = dynamic_code_table().to(torch.float32)
+            mid = torch.cat([(code[:-1] + code[1:]) * 0.5, torch.tensor([float("inf")])])
+            table = torch.cat([code, mid]).to(device)
+            _code_tables[device.index] = table
+        return table
 
 
 class _RawCuda:
@@ -124,38 +162,34 @@ class RoundStatus:
         return self.failed_elements / max(self.total_elements, 1)
 
 
-def record_bytes(codec: int, length: int) -> int:
-    header = {1: 16, 3: 1024, 4: 1024}.get(codec, 0)
-    if codec == 5:
-        header = ((length + 4095) // 4096 * 4 + 15) // 16 * 16
-    elem = 4 if codec == 0 else (2 if codec in (1, 2) else 1)
-    return header + (length * elem + 15) // 16 * 16
-
-
 @dataclass
 class _Plan:
-    """Everything about one (group shape, my index): part table, work lists, capacities."""
+    """Everything about one (group shape, my index): part table, the ordered work list, scratch."""
 
     n_parts: int
     max_local_parts: int
     delta_stride: int
     parts_dev: torch.Tensor
-    items: Dict[str, torch.Tensor]
-    counts: Dict[str, int]
+    items_dev: torch.Tensor
+    pub_dev: torch.Tensor
+    n_send: int
+    n_reduce: int
+    n_apply: int
+    send_cut: int  # number of send items that cover the first half of the parts this rank sends (fault injection)
     scratch: Dict[str, torch.Tensor]
     scratch_blob: torch.Tensor
-    group_dev: torch.Tensor
     needed_outbox: int
     needed_delta: int
+    needed_avg: int
 
 
 def _interleave_by_owner(items: List[Tuple[int, int, int, int]], owners: List[int], first_owner: int,
                          n_peers: int) -> List[Tuple[int, int, int, int]]:
     """Order work items round-robin over the GPUs they read from, starting at ``first_owner``.
 
-    CTAs start in list order. With items grouped by owner, every member of a group would pull from owner 0 first,
-    then from owner 1, ...: at any moment one GPU's outgoing links serve all readers while the others idle. Rotated
-    and interleaved, concurrent reads are spread evenly over all owners.
+    CTAs take items in list order. With items grouped by owner, every member of a group would pull from owner 0
+    first, then from owner 1, ...: at any moment one GPU's outgoing links serve all readers while the others idle.
+    Rotated and interleaved, concurrent reads are spread evenly over all owners.
     """
     queues: Dict[int, List[Tuple[int, int, int, int]]] = {}
     for item, owner in zip(items, owners):
@@ -172,6 +206,26 @@ def _interleave_by_owner(items: List[Tuple[int, int, int, int]], owners: List[in
     return merged
 
 
+def peers_can_share_memory(mine: dict, infos: Sequence[Optional[dict]]) -> bool:
+    """Whether a group described by ``infos`` can run on the device path from the point of view of ``mine``.
+
+    The rule is symmetric, so that every member reaches the same verdict: same machine, identical arena layouts, and
+    for every pair of members that live in different processes BOTH sides exported an IPC handle. Processes are told
+    apart by a random per-process token (pids and device indices repeat across containers of one host).
+    """
+    if len(infos) < 2 or len(infos) > MAX_PEERS or any(info is None for info in infos):
+        return False
+    if any(not info.get("supported", True) for info in infos):
+        return False
+    for info in infos:
+        if info["machine"] != mine["machine"] or info["layout"] != mine["layout"] or info["total"] != mine["total"]:
+            return False
+    procs = {bytes(info["proc"]) for info in infos}
+    if len(procs) > 1 and any(not info.get("handle") for info in infos):
+        return False
+    return True
+
+
 class DeviceEndpoint:
     """The device-side state of one averager: arena, mappings of groupmates' arenas, cached plans."""
 
@@ -181,27 +235,40 @@ class DeviceEndpoint:
         self.device = tensors[0].device
         assert all(t.device == self.device for t in tensors), "all averaged tensors must live on one GPU"
         self.lib = _lib.load_library()
-        _ensure_code_table(self.device.index)
+        self._code = _code_table_on(self.device)
         self.part_size_bytes = part_size_bytes
         self.numels = [t.numel() for t in tensors]
         self.codecs = [codec_id(compression, info) for info in tensor_infos]
         self.supported = all(c is not None for c in self.codecs)
-        self.ratios = [{0: 1.0, 1: 0.5, 2: 0.5}.get(c, 0.25) for c in self.codecs]
-        # flat layout: every tensor starts on an ALIGN-element boundary
-        self.offsets, cursor = [], 0
-        for n in self.numels:
+        codecs = [c if c is not None else 0 for c in self.codecs]
+        self.ratios = [{0: 1.0, 1: 0.5, 2: 0.5}.get(c, 0.25) for c in codecs]
+        # flat layout: every tensor starts on an ALIGN-element boundary; uncompressed tensors also get a place in
+        # the (compact) average buffer
+        self.offsets, self.avg_offsets, cursor, avg_cursor = [], [], 0, 0
+        for n, c in zip(self.numels, codecs):
+            padded = (n + ALIGN - 1) // ALIGN * ALIGN
             self.offsets.append(cursor)
-            cursor += (n + ALIGN - 1) // ALIGN * ALIGN
+            self.avg_offsets.append(avg_cursor)
+            cursor += padded
+            if c == CODEC_NONE:
+                avg_cursor += padded
         self.total = max(cursor, ALIGN)
-        min_part = min([max(ALIGN, int(part_size_bytes / (4 * r)) // ALIGN * ALIGN) for r in self.ratios] or [ALIGN])
-        self.max_parts = sum((n + min_part - 1) // min_part for n in self.numels) + MAX_PEERS + len(tensors)
-        self.cap_outbox = self.total * 4 + self.max_parts * 1088
-        self.cap_delta = int(self.cap_outbox * 2.5) + (1 << 16)  # room for uneven spans; larger groups fall back to RPC
-        self.layout, self._guards = {}, {}
+        part_lens = [max(ALIGN, int(part_size_bytes / (4 * r)) // ALIGN * ALIGN) for r in self.ratios]
+        self.max_parts = sum((n + pl - 1) // pl for n, pl in zip(self.numels, part_lens)) + MAX_PEERS + len(tensors)
+        # staging capacities by codec: records exist only for compressed tensors, averages only for uncompressed ones
+        self.cap_avg = max(avg_cursor * 4, 256)
+        self.cap_outbox = max(256, sum(((n + CHUNK - 1) // CHUNK + (n + pl - 1) // pl + MAX_PEERS + 1) * chunk_stride(c)
+                                       for n, pl, c in zip(self.numels, part_lens, codecs) if c != CODEC_NONE))
+        self.cap_delta = int(self.cap_outbox * DELTA_BOX_FACTOR) + (1 << 12) if self.cap_outbox > 256 else 256
+        self.layout: Dict[str, int] = {}
+        self._guards: Dict[str, int] = {}
         cursor = 0
-        for name, nbytes in (("data", self.total * 4), ("avg", self.total * 4), ("outbox", self.cap_outbox),
-                             ("deltabox", self.cap_delta), ("ready", self.max_parts * 4),
-                             ("delta_ready", MAX_PEERS * self.max_parts * 4)):
+        regions = [("data", self.total * 4)]
+        for par in (0, 1):
+            regions += [(f"avg{par}", self.cap_avg), (f"outbox{par}", self.cap_outbox), (f"deltabox{par}", self.cap_delta),
+                        (f"ready{par}", self.max_parts * 8), (f"dready{par}", MAX_PEERS * self.max_parts * 4)]
+        regions += [("hello", 16), ("done_ring", ACK_RING * 4)]
+        for name, nbytes in regions:
             self.layout[name] = cursor
             cursor += (nbytes + 255) // 256 * 256
             self._guards[name] = cursor  # a canary zone follows every region (see check_canaries)
@@ -219,6 +286,9 @@ class DeviceEndpoint:
         self._bytes = torch.as_tensor(self._raw, device=self.device)
         for guard in self._guards.values():
             self._bytes[guard:guard + GUARD_BYTES].fill_(GUARD_PATTERN)
+        for name in ("ready0", "ready1", "dready0", "dready1", "hello", "done_ring"):  # flags start out as "no round"
+            lo = self.layout[name]
+            self._bytes[lo:self._guards[name]].zero_()
         flat = self._bytes[self.layout["data"]:self.layout["data"] + self.total * 4].view(torch.float32)
         self.flat = flat
         self.tensor_views = []
@@ -235,41 +305,46 @@ class DeviceEndpoint:
         # that its initialisation is ordered before the kernels (the round's stream does not synchronise with the
         # default stream, where unrelated training work may be queued)
         self._torch_stream = torch.cuda.ExternalStream(stream.value, device=self.device)
-        self._mappings: Dict[Tuple[int, bytes], int] = {}
+        with torch.cuda.stream(self._torch_stream):
+            self._status_out = torch.zeros(4, dtype=torch.int64, device=self.device)
+            self._gate_status = torch.zeros(2, dtype=torch.int64, device=self.device)
+            self._torch_stream.synchronize()
+        self._mappings: Dict[Tuple[bytes, bytes], int] = {}
         self._plans: Dict[Tuple, _Plan] = {}
         self._host_status = (ctypes.c_ulonglong * 4)()
         self._closed = False
         self.launch_hook = None
         self.uid = os.urandom(8)
+        self._round_seq = 0
+        self._history: Dict[int, Tuple[int, List[int]]] = {}  # parity -> (epoch, bases of that round's groupmates)
+        self._sms = _lib.sm_count(self.device)
+        self.fault_publish_half = False  # host-side fault injection: publish only the first half of the parts sent
 
     # ---------------------------------------------------------------------------------------------- handles
     def describe(self) -> Optional[dict]:
         """What groupmates need in order to map this arena (sent in the matchmaking gather blob)."""
         if not self.supported:
             return None
-        return dict(machine=_machine_id(), pid=os.getpid(), dev=self.device.index, ptr=self.base,
+        return dict(machine=_machine_id(), proc=_PROCESS_TOKEN, dev=self.device.index, ptr=self.base,
                     handle=self.ipc_handle, layout=self.layout, total=self.total, max_parts=self.max_parts,
-                    cap_outbox=self.cap_outbox, cap_delta=self.cap_delta, uid=self.uid)
+                    cap_outbox=self.cap_outbox, cap_delta=self.cap_delta, cap_avg=self.cap_avg, uid=self.uid,
+                    supported=True)
 
     def can_run_with(self, device_infos: Sequence[Optional[dict]], modes: Sequence[AveragingMode]) -> bool:
-        if not self.supported or len(device_infos) > MAX_PEERS or len(device_infos) < 2:
+        """True if this round can use the device path; every member of the group reaches the same verdict."""
+        if not self.supported or self._closed:
             return False
-        if any(info is None for info in device_infos) or any(m == AveragingMode.CLIENT for m in modes):
-            return False
-        mine = self.describe()
-        return all(info["machine"] == mine["machine"] and info["total"] == mine["total"]
-                   and info["max_parts"] == mine["max_parts"] and (info["pid"] == mine["pid"] or info["handle"])
-                   for info in device_infos)
+        return peers_can_share_memory(self.describe(), device_infos)
 
     def _map_peer(self, info: dict) -> int:
         """Base address of a groupmate's arena as seen from this GPU."""
-        if info["pid"] == os.getpid():
+        if bytes(info["proc"]) == _PROCESS_TOKEN:
             if info["dev"] != self.device.index:
                 rc = self.lib.hm_enable_peer_access(self.device.index, info["dev"])
                 if rc != 0:
                     raise RuntimeError(f"GPU {self.device.index} cannot access GPU {info['dev']} (code {rc})")
             return info["ptr"]
-        key = (info["pid"], bytes(info["handle"]))
+        key = (bytes(info["proc"]), bytes(info["handle"]))
         if key not in self._mappings:
             out = ctypes.c_void_p()
             buf = (ctypes.c_ubyte * 64).from_buffer_copy(bytes(info["handle"]))
@@ -277,6 +352,16 @@ class DeviceEndpoint:
                 _lib.check(self.lib.hm_ipc_open(buf, ctypes.byref(out)), "hm_ipc_open", 0)
             self._mappings[key] = out.value
         return self._mappings[key]
+
+    def map_group(self, device_infos: Sequence[dict], my_index: int) -> List[int]:
+        """Map every groupmate's arena. If that fails, this endpoint stops offering the device path (its later
+        ``describe()`` blobs say so, and whole groups then use the RPC butterfly) and the error is re-raised."""
+        try:
+            return [self.base if r == my_index else self._map_peer(info) for r, info in enumerate(device_infos)]
+        except Exception:
+            self.supported = False
+            logger.warning("could not map a groupmate's device arena; this peer uses the RPC butterfly from now on")
+            raise
 
     def check_canaries(self) -> None:
         """Raise if any kernel (of this GPU or of a groupmate) wrote past the end of one of the arena's regions.
@@ -325,8 +410,6 @@ class DeviceEndpoint:
         return plan
 
     def _build_plan(self, n_peers: int, my_index: int, peer_fractions: Sequence[float], sends: Sequence[bool]) -> _Plan:
-        lib = self.lib
-        chunk = lib.hm_bf_chunk()
         specs = compute_part_layout(self.numels, [4] * len(self.numels), self.ratios, peer_fractions,
                                     self.part_size_bytes, align=ALIGN)
         specs = [s for s in specs if s.length > 0]
@@ -334,14 +417,13 @@ class DeviceEndpoint:
         if n_parts > self.max_parts:
             raise RuntimeError("too many parts for the arena's flag pages")
         table = np.zeros(n_parts, dtype=_PART_DTYPE)
-        local_count = [0] * n_peers
-        span_bytes = [0] * n_peers
-        enc_cursor = 0
+        local_count, span_bytes, enc_cursor = [0] * n_peers, [0] * n_peers, 0
         for p, s in enumerate(specs):
             codec = self.codecs[s.tensor_index]
             rec = record_bytes(codec, s.length)
             start = self.offsets[s.tensor_index] + s.start
-            table[p] = (start, enc_cursor, span_bytes[s.owner], start, s.length, s.owner, local_count[s.owner], codec)
+            avg_off = self.avg_offsets[s.tensor_index] + s.start if codec == CODEC_NONE else 0
+            table[p] = (start, enc_cursor, span_bytes[s.owner], avg_off, s.length, s.owner, local_count[s.owner], codec)
             enc_cursor += rec
             span_bytes[s.owner] += rec
             local_count[s.owner] += 1
@@ -350,138 +432,161 @@ class DeviceEndpoint:
         needed_delta = n_peers * delta_stride
 
         def chunks_of(p):
-            return range((int(table[p]["len"]) + chunk - 1) // chunk)
+            return range((int(table[p]["len"]) + CHUNK - 1) // CHUNK)
 
         i_send = sends[my_index]
         mine = [p for p in range(n_parts) if table[p]["owner"] == my_index]
         theirs = [p for p in range(n_parts) if table[p]["owner"] != my_index] if i_send else []
-        senders = [s for s in range(n_peers) if s != my_index and sends[s]]
-        lists = {
-            # uncompressed parts have no records: reducers read the vector in place, senders read the average
-            "enc": [(p, c, 0, 0) for p in theirs if table[p]["codec"] != CODEC_NONE for c in chunks_of(p)],
-            "enc_stats": [(p, c, 0, 0) for p in theirs if table[p]["codec"] in _NEEDS_STATS for c in chunks_of(p)],
-            "enc_borders": [(p, 0, 0, 0) for p in theirs if table[p]["codec"] in _NEEDS_BORDERS],
-            "enc_publish": [(p, 0, 0, 0) for p in theirs],
-            "reduce": [(p, c, 0, 0) for p in mine for c in chunks_of(p)],
-            "delta": [(p, c, s, 0) for s in senders for p in mine if table[p]["codec"] != CODEC_NONE
-                      for c in chunks_of(p)],
-            "delta_borders": [(p, 0, s, 0) for s in senders for p in mine if table[p]["codec"] in _NEEDS_BORDERS],
-            "delta_publish": [(p, 0, s, 0) for s in senders for p in mine],
-            "apply": _interleave_by_owner([(p, c, 0, 0) for p in theirs for c in chunks_of(p)],  # own span: applied
-                                          [int(table[p]["owner"]) for p in theirs for _ in chunks_of(p)],  # by reduce
-                                          first_owner=(my_index + 1) % n_peers, n_peers=n_peers),
-        }
-        items = {k: torch.tensor(v if v else [(0, 0, 0, 0)], dtype=torch.int32).to(self.device) for k, v in lists.items()}
-        counts = {k: len(v) for k, v in lists.items()}
+        # send items in part order; runs of uncompressed parts become "publish the flags of pub_list[a : a + n]" items
+        send_items: List[Tuple[int, int, int, int]] = []
+        pub_list: List[int] = []
+        half_index, send_cut = len(theirs) // 2, 0
+        for rank, p in enumerate(theirs):
+            if rank == half_index:
+                send_cut = len(send_items)
+            if table[p]["codec"] == CODEC_NONE:
+                last = send_items[-1] if send_items else None
+                if last is not None and last[0] == -1 and last[1] + last[2] == len(pub_list) and last[2] < 512 \
+                        and rank != half_index:
+                    send_items[-1] = (-1, last[1], last[2] + 1, 0)
+                else:
+                    send_items.append((-1, len(pub_list), 1, 0))
+                pub_list.append(p)
+            else:
+                send_items += [(p, c, 0, 0) for c in chunks_of(p)]
+        reduce_items = [(p, c, 0, 0) for p in mine for c in chunks_of(p)]
+        apply_items = _interleave_by_owner([(p, c, 0, 0) for p in theirs for c in chunks_of(p)],
+                                           [int(table[p]["owner"]) for p in theirs for _ in chunks_of(p)],
+                                           first_owner=(my_index + 1) % n_peers, n_peers=n_peers)
+        items = send_items + reduce_items + apply_items
+        items_dev = torch.tensor(items if items else [(0, 0, 0, 0)], dtype=torch.int32).to(self.device)
+        pub_dev = torch.tensor(pub_list if pub_list else [0], dtype=torch.int32).to(self.device)
         parts_dev = torch.from_numpy(table.view(np.uint8).copy()).to(self.device)
         slots = MAX_PEERS * max_local
-        sizes = [("part_stats", n_parts * 16), ("dstats", slots * 16), ("bins", n_parts * 1024), ("bin_cnt", n_parts * 1024),
-                 ("dbins", slots * 1024), ("dbin_cnt", slots * 1024), ("include", max_local * MAX_PEERS * 4),
-                 ("apply_decision", n_parts * 4), ("ban", MAX_PEERS * 4), ("t_start", 16), ("status", 32),
-                 ("borders", n_parts * 1024), ("dborders", slots * 1024)]
+        sizes = [("include", slots * 4), ("dpart_done", slots * 4), ("apply_decision", n_parts * 4),
+                 ("part_done", n_parts * 4), ("ban", MAX_PEERS * 4), ("t_start", 16), ("status", 32), ("queue", 16)]
         total = sum((b + 255) // 256 * 256 for _, b in sizes)
         blob = torch.zeros(total, dtype=torch.uint8, device=self.device)
         scratch, cursor = {}, 0
         for name, nbytes in sizes:
             scratch[name] = blob[cursor:cursor + nbytes]
             cursor += (nbytes + 255) // 256 * 256
-        group_dev = torch.zeros(ctypes.sizeof(_HbGroup), dtype=torch.uint8, device=self.device)
-        return _Plan(n_parts, max_local, delta_stride, parts_dev, items, counts, scratch, blob, group_dev, enc_cursor,
-                     needed_delta)
+        needed_avg = max([(int(table[p]["avg_off"]) + int(table[p]["len"])) * 4 for p in range(n_parts)
+                          if table[p]["codec"] == CODEC_NONE] or [0])
+        return _Plan(n_parts, max_local, delta_stride, parts_dev, items_dev, pub_dev, len(send_items), len(reduce_items),
+                     len(apply_items), send_cut, scratch, blob, enc_cursor, needed_delta, needed_avg)
 
-    def _prepare(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weights, alpha,
-                 sender_timeout, reducer_timeout, stream) -> _Plan:
+    def _layout_struct(self) -> _HrLayout:
+        lay = _HrLayout()
+        lay.data = self.layout["data"]
+        for par in (0, 1):
+            lay.avg[par] = self.layout[f"avg{par}"]
+            lay.outbox[par] = self.layout[f"outbox{par}"]
+            lay.deltabox[par] = self.layout[f"deltabox{par}"]
+            lay.ready[par] = self.layout[f"ready{par}"]
+            lay.dready[par] = self.layout[f"dready{par}"]
+        lay.hello, lay.done_ring = self.layout["hello"], self.layout["done_ring"]
+        return lay
+
+    def _prepare(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weight: float, alpha,
+                 sender_timeout, reducer_timeout) -> Tuple[_Plan, _HrRound, List[int]]:
+        """Part table, work list and the kernel parameter block of one round; also advances the round counter."""
         n = len(device_infos)
         sends = [m != AveragingMode.AUX for m in modes]
         plan = self._make_plan(n, my_index, peer_fractions, sends)
-        for info in device_infos:
-            if plan.needed_outbox > info["cap_outbox"] or plan.needed_delta > info["cap_delta"]:
-                raise RuntimeError("the staging areas of the arenas are too small for this group layout")
-        g = _HbGroup()
+        if plan.needed_outbox > self.cap_outbox or plan.needed_delta > self.cap_delta or plan.needed_avg > self.cap_avg:
+            raise RuntimeError("the staging areas of the arenas are too small for this group layout")
+        bases = self.map_group(device_infos, my_index)
+        sender_timeout = min(sender_timeout if sender_timeout else 10.0, 20.0)
+        reducer_timeout = max(min(reducer_timeout if reducer_timeout else 2 * sender_timeout, 40.0), 2 * sender_timeout)
+        g = _HrRound()
         g.n_peers, g.n_parts, g.me, g.max_local_parts = n, plan.n_parts, my_index, plan.max_local_parts
         g.epoch = (zlib.crc32(group_id) & 0x7FFFFFFF) | 1
-        g.alpha = alpha
-        g.sender_timeout_ns = int(min(sender_timeout if sender_timeout else 10.0, 20.0) * 1e9)
-        g.reducer_timeout_ns = int(min(reducer_timeout if reducer_timeout else 20.0, 40.0) * 1e9)
+        g.parity = self._round_seq & 1
+        g.done_slot = self._round_seq
+        g.alpha, g.my_weight = alpha, float(weight)
+        g.sender_timeout_ns, g.reducer_timeout_ns = int(sender_timeout * 1e9), int(reducer_timeout * 1e9)
         g.delta_stride = plan.delta_stride
-        for r, info in enumerate(device_infos):
-            base = self.base if r == my_index else self._map_peer(info)
-            lay = info["layout"]
-            g.weight[r] = float(weights[r])
+        for r in range(n):
             g.sends[r] = int(sends[r])
-            g.peer[r].data = base + lay["data"]
-            g.peer[r].outbox = base + lay["outbox"]
-            g.peer[r].deltabox = base + lay["deltabox"]
-            g.peer[r].ready = base + lay["ready"]
-            g.peer[r].delta_ready = base + lay["delta_ready"]
-            g.peer[r].avg = base + lay["avg"]
-        g.parts = plan.parts_dev.data_ptr()
-        for name in ("part_stats", "dstats", "bins", "bin_cnt", "dbins", "dbin_cnt", "borders", "dborders", "include",
-                     "apply_decision", "ban", "t_start", "status"):
+            g.base[r] = bases[r]
+        g.lay = self._layout_struct()
+        g.parts, g.items, g.pub_list = plan.parts_dev.data_ptr(), plan.items_dev.data_ptr(), plan.pub_dev.data_ptr()
+        g.n_send, g.n_reduce, g.n_apply = plan.n_send, plan.n_reduce, plan.n_apply
+        g.item_begin, g.item_end, g.queue_slot, g.final_stage = 0, plan.n_send + plan.n_reduce + plan.n_apply, 0, 1
+        for name in ("include", "apply_decision", "ban", "t_start", "status", "part_done", "dpart_done", "queue"):
             setattr(g, name, plan.scratch[name].data_ptr())
-        g.avg = self.base + self.layout["avg"]
-        plan._host_group = g  # keep the host copy alive until the async upload has been consumed
-        lib = self.lib
-        with torch.cuda.device(self.device):
-            _lib.check(lib.hm_memset_async(ctypes.c_void_p(plan.scratch_blob.data_ptr()), 0,
-                                           ctypes.c_ulonglong(plan.scratch_blob.numel()), stream), "memset", 0)
-            _lib.check(lib.hm_memcpy_h2d_async(ctypes.c_void_p(plan.group_dev.data_ptr()), ctypes.byref(g),
-                                               ctypes.c_ulonglong(ctypes.sizeof(g)), stream), "upload group", 0)
-        return plan
+        g.status_out = self._status_out.data_ptr()
+        g.code = self._code.data_ptr()
+        self._round_seq += 1
+        return plan, g, bases
 
-    def _launch(self, plan: _Plan, phase: int, items: str, mode: int, stream) -> None:
-        count = plan.counts[items]
-        if count == 0:
+    def _gate_params(self, g: _HrRound, bases: List[int], sender_timeout_ns: int) -> _HrGate:
+        gate = _HrGate()
+        gate.n_peers, gate.me, gate.parity, gate.epoch = g.n_peers, g.me, g.parity, g.epoch
+        prev_epoch, prev_bases = self._history.get(g.parity, (0, []))
+        gate.prev_epoch, gate.n_prev = prev_epoch, len(prev_bases)
+        for t, b in enumerate(prev_bases):
+            gate.prev_base[t] = b
+        for r in range(g.n_peers):
+            gate.base[r] = bases[r]
+        gate.ack_timeout_ns = min(int(g.reducer_timeout_ns), int(2e9))
+        gate.hello_timeout_ns = sender_timeout_ns
+        gate.lay = g.lay
+        gate.gate_status = self._gate_status.data_ptr()
+        self._history[g.parity] = (g.epoch, [b for r, b in enumerate(bases) if r != g.me][:MAX_PEERS])
+        return gate
+
+    def _launch_round(self, g: _HrRound, begin: int, end: int, slot: int, final: bool, stream, name: str) -> None:
+        g.item_begin, g.item_end, g.queue_slot, g.final_stage = begin, end, slot, int(final)
+        if end <= begin and not final:
             return
         with torch.cuda.device(self.device):
-            code = self.lib.hm_bf_launch(phase, ctypes.c_void_p(plan.group_dev.data_ptr()),
-                                         ctypes.c_void_p(plan.items[items].data_ptr()), count, mode, stream)
-        _lib.check(code, f"hm_bf_launch(phase={phase}, {items})")
+            code = self.lib.hm_br_round(ctypes.byref(g), self._sms, stream)
+        _lib.check(code, f"hm_br_round({name})")
         if self.launch_hook is not None:
-            self.launch_hook(items)  # benchmarks record an event after every launch of a round
+            self.launch_hook(name)  # benchmarks record an event after every launch of a round
 
-    # the three stages of a round; in normal operation they are launched back to back on one stream
-    def _stage_send(self, plan, stream) -> None:
-        self._launch(plan, PH_STATS, "enc_stats", 0, stream)
-        self._launch(plan, PH_BORDERS, "enc_borders", 0, stream)
-        self._launch(plan, PH_ENCODE, "enc", 0, stream)
-        self._launch(plan, PH_PUBLISH, "enc_publish", 0, stream)
-
-    def _stage_reduce(self, plan, stream) -> None:
-        self._launch(plan, PH_REDUCE, "reduce", 0, stream)
-        self._launch(plan, PH_BORDERS, "delta_borders", 1, stream)
-        self._launch(plan, PH_ENCODE, "delta", 1, stream)
-        self._launch(plan, PH_PUBLISH, "delta_publish", 1, stream)
-
-    def _stage_apply(self, plan, stream) -> None:
-        self._launch(plan, PH_APPLY, "apply", 0, stream)
-
-    def _read_status(self, plan: _Plan, stream) -> RoundStatus:
+    def _read_status(self, stream) -> RoundStatus:
         with torch.cuda.device(self.device):
-            _lib.check(self.lib.hm_memcpy_d2h(self._host_status, ctypes.c_void_p(plan.scratch["status"].data_ptr()),
+            _lib.check(self.lib.hm_memcpy_d2h(self._host_status, ctypes.c_void_p(self._status_out.data_ptr()),
                                               ctypes.c_ulonglong(32), stream), "read status", 0)
         banned, failed, elements = self._host_status[0], self._host_status[1], self._host_status[2]
         return RoundStatus([i for i in range(MAX_PEERS) if banned >> i & 1], [i for i in range(MAX_PEERS) if failed >> i & 1],
                            int(elements), sum(self.numels))
 
-    def run_round(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weights, alpha: float,
-                  sender_timeout: Optional[float], reducer_timeout: Optional[float]) -> RoundStatus:
-        """Run one all-reduce round with the mapped groupmates; blocks the calling thread until this GPU is done."""
+    def run_round(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weight: float,
+                  alpha: float, sender_timeout: Optional[float], reducer_timeout: Optional[float],
+                  wait: bool = True) -> Optional[RoundStatus]:
+        """Run one all-reduce round with the mapped groupmates. Blocks the calling thread until this GPU is done,
+        unless ``wait`` is False: then the round is only enqueued on the endpoint's stream (several rounds may be
+        queued back to back) and ``wait_round()`` returns the status of the last one."""
         # the caller's writes to the tensors must land before the round reads them: order the round's stream after the
         # caller's stream on the device (no host wait: that stream may hold work that depends on other ranks)
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         self._torch_stream.wait_event(ready)
-        plan = self._prepare(group_id=group_id, my_index=my_index, device_infos=device_infos, modes=modes,
-                             peer_fractions=peer_fractions, weights=weights, alpha=alpha,
-                             sender_timeout=sender_timeout, reducer_timeout=reducer_timeout, stream=self.stream)
-        with device_range("butterfly.send", self._torch_stream):
-            self._stage_send(plan, self.stream)
-        with device_range("butterfly.reduce", self._torch_stream):
-            self._stage_reduce(plan, self.stream)
-        with device_range("butterfly.apply", self._torch_stream):
-            self._stage_apply(plan, self.stream)
-        status = self._read_status(plan, self.stream)
+        plan, g, bases = self._prepare(group_id=group_id, my_index=my_index, device_infos=device_infos, modes=modes,
+                                       peer_fractions=peer_fractions, weight=weight, alpha=alpha,
+                                       sender_timeout=sender_timeout, reducer_timeout=reducer_timeout)
+        gate = self._gate_params(g, bases, int(g.sender_timeout_ns))
+        total = plan.n_send + plan.n_reduce + plan.n_apply
+        with device_range("butterfly.round", self._torch_stream):
+            with torch.cuda.device(self.device):
+                _lib.check(self.lib.hm_br_gate(ctypes.byref(gate), self.stream), "hm_br_gate")
+            if self.launch_hook is not None:
+                self.launch_hook("gate")
+            if self.fault_publish_half:
+                # injected on the host: this rank stalls after it has sent half of its parts
+                self._launch_round(g, 0, plan.send_cut, 0, False, self.stream, "send(half)")
+                self._launch_round(g, plan.n_send, total, 1, True, self.stream, "reduce+apply")
+            else:
+                self._launch_round(g, 0, total, 0, True, self.stream, "round")
+        return self.wait_round() if wait else None
+
+    def wait_round(self) -> RoundStatus:
+        """Wait for the rounds enqueued so far and return the status words of the last one."""
+        status = self._read_status(self.stream)
         self._last_round_end = time.monotonic()
         if DEBUG_CHECKS:
             self.check_canaries()
@@ -492,35 +597,51 @@ def run_group_emulated(endpoints: Sequence[DeviceEndpoint], *, weights: Sequence
                        peer_fractions: Sequence[float], modes: Optional[Sequence[AveragingMode]] = None,
                        alpha: float = 1.0, group_id: bytes = b"emulated", sender_timeout: float = 1.0,
                        reducer_timeout: float = 2.0, skip_send_of: Sequence[int] = (),
-                       publish_only_first_half_of: Sequence[int] = ()) -> List[RoundStatus]:
-    """Run a whole group inside one process, stage by stage: first every rank's send stage, then every rank's
-    reduce stage, then every rank's apply stage, so that no launch ever waits for a later one. Used when there are
+                       publish_only_first_half_of: Sequence[int] = (), members: Optional[Sequence[int]] = None,
+                       stop_after_stage: int = 3) -> List[RoundStatus]:
+    """Run a whole group inside one process, stage by stage: first every rank's send items, then every rank's
+    reduce items, then every rank's apply items, so that no launch ever waits for a later one. Used when there are
     fewer GPUs than ranks, and by tests that inject host-side faults: ``skip_send_of`` ranks never publish their
     parts (a sender that does not show up), ``publish_only_first_half_of`` ranks stall after half of their parts.
+    ``stop_after_stage`` (1 or 2) leaves the round unfinished, e.g. to let a rank begin its next round with another
+    group while a slow member of this one has not applied its results yet; ``finish_group_emulated`` completes it.
     """
     n = len(endpoints)
     modes = list(modes) if modes is not None else [AveragingMode.NODE] * n
     infos = [e.describe() for e in endpoints]
     streams = [ctypes.c_void_p(torch.cuda.current_stream(e.device).cuda_stream) for e in endpoints]
-    plans = [e._prepare(group_id=group_id, my_index=r, device_infos=infos, modes=modes, peer_fractions=peer_fractions,
-                        weights=weights, alpha=alpha, sender_timeout=sender_timeout, reducer_timeout=reducer_timeout,
-                        stream=streams[r]) for r, e in enumerate(endpoints)]
+    prepared = [e._prepare(group_id=group_id, my_index=r, device_infos=infos, modes=modes, peer_fractions=peer_fractions,
+                           weight=weights[r], alpha=alpha, sender_timeout=sender_timeout,
+                           reducer_timeout=reducer_timeout) for r, e in enumerate(endpoints)]
     for r, e in enumerate(endpoints):
+        plan, g, bases = prepared[r]
+        e._history[g.parity] = (g.epoch, [b for q, b in enumerate(bases) if q != r])
         if r in skip_send_of:
             continue
-        if r in publish_only_first_half_of:
-            full = plans[r].counts["enc_publish"]
-            plans[r].counts["enc_publish"] = full // 2
-            e._stage_send(plans[r], streams[r])
-            plans[r].counts["enc_publish"] = full
-        else:
-            e._stage_send(plans[r], streams[r])
+        end = plan.send_cut if r in publish_only_first_half_of else plan.n_send
+        e._launch_round(g, 0, end, 0, False, streams[r], "send")
     for e in endpoints:
         torch.cuda.synchronize(e.device)
+    if stop_after_stage < 2:
+        return prepared  # type: ignore[return-value]
     for r, e in enumerate(endpoints):
-        e._stage_reduce(plans[r], streams[r])
+        plan, g, _ = prepared[r]
+        e._launch_round(g, plan.n_send, plan.n_send + plan.n_reduce, 1, False, streams[r], "reduce")
     for e in endpoints:
         torch.cuda.synchronize(e.device)
-    for r, e in enumerate(endpoints):
-        e._stage_apply(plans[r], streams[r])
-    return [e._read_status(plans[r], streams[r]) for r, e in enumerate(endpoints)]
+    if stop_after_stage < 3:
+        return prepared  # type: ignore[return-value]
+    return finish_group_emulated(endpoints, prepared, only=members)
+
+
+def finish_group_emulated(endpoints: Sequence[DeviceEndpoint], prepared, only: Optional[Sequence[int]] = None
+                          ) -> List[RoundStatus]:
+    """Run the apply stage of a round started by ``run_group_emulated(..., stop_after_stage=2)`` for the ranks in
+    ``only`` (default: all) and return their status words."""
+    ranks = list(range(len(endpoints))) if only is None else list(only)
+    streams = {r: ctypes.c_void_p(torch.cuda.current_stream(endpoints[r].device).cuda_stream) for r in ranks}
+    for r in ranks:
+        plan, g, _ = prepared[r]
+        begin = plan.n_send + plan.n_reduce
+        endpoints[r]._launch_round(g, begin, begin + plan.n_apply, 2, True, streams[r], "apply")
+    return [endpoints[r]._read_status(streams[r]) for r in ranks]

@@ -173,3 +173,25 @@ def test_remote_work_items_are_interleaved_over_owners():
         assert [item for item in merged if owners_of_parts[item[0]] == owner] == \
                [item for item in items if owners_of_parts[item[0]] == owner]
     assert _interleave_by_owner([], [], first_owner=0, n_peers=4) == []
+
+
+def test_device_path_decision_on_described_arenas():
+    """The rule that decides between the device path and the RPC butterfly, on hand-made ``describe()`` blobs."""
+    from hivemind_b200.parallel.device_butterfly import peers_can_share_memory
+
+    layout = {"data": 0, "avg0": 1024}
+    a = dict(machine="m1", proc=b"A" * 16, dev=0, ptr=1, handle=b"h" * 64, layout=layout, total=100, supported=True)
+    b = dict(a, proc=b"B" * 16, dev=1)
+    assert peers_can_share_memory(a, [a, b]) and peers_can_share_memory(b, [a, b])
+    assert not peers_can_share_memory(a, [a])  # a group of one
+    assert not peers_can_share_memory(a, [a, None])  # a member without a device arena
+    assert not peers_can_share_memory(a, [a, dict(b, machine="m2")])
+    assert not peers_can_share_memory(a, [a, dict(b, total=101)])
+    assert not peers_can_share_memory(a, [a, dict(b, layout={"data": 0, "avg0": 2048})])
+    # two processes need handles on BOTH sides, whichever member asks (equal pids or device indices prove nothing)
+    no_handle = dict(b, handle=None)
+    assert not peers_can_share_memory(a, [a, no_handle]) and not peers_can_share_memory(no_handle, [a, no_handle])
+    # inside one process raw pointers are enough
+    same_proc = dict(a, dev=1, handle=None)
+    assert peers_can_share_memory(dict(a, handle=None), [dict(a, handle=None), same_proc])
+    assert not peers_can_share_memory(a, [a, dict(b, supported=False)])
