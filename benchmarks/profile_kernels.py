@@ -27,6 +27,7 @@ def main():
     parser.add_argument("--seq", type=int, default=512)
     parser.add_argument("--heads", type=int, default=16)
     parser.add_argument("--causal", action="store_true")
+    parser.add_argument("--skip-library", action="store_true", help="attention_compare: time only this package's kernels")
     parser.add_argument("--m", type=int, default=16384)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=1024)
@@ -97,7 +98,7 @@ def main():
 
         flops_fwd = 4.0 * b * nh * s * s * 64 * (0.5 if args.causal else 1.0)
         result = {}
-        for name, fn in (("ours", ours), ("library", library)):
+        for name, fn in (("ours", ours),) if args.skip_library else (("ours", ours), ("library", library)):
             fwd_ms = timed(fn)
             both_ms = timed(lambda: torch.autograd.grad(fn(), qkv, dout))
             result[name] = {"fwd_ms": fwd_ms, "fwd_tflops": flops_fwd / fwd_ms / 1e9, "fwd_bwd_ms": both_ms,

@@ -1,24 +1,27 @@
 """Forming all-reduce groups without a coordinator.
 
-Protocol (same messages and ordering rule as hivemind/averaging/matchmaking.py:24-550):
-every averager that wants a group *declares* itself under the current group key in the DHT with an expiration = the
-time it wants to start. A peer asks only peers that come *before* it in (expiration, peer id) order to lead it, so
-the earliest-expiring peer ends up as leader. A leader accepts followers (``ACCEPTED``), and either assembles the
-group at once when ``target_group_size`` is reached, or at its own expiration if at least ``min_group_size`` peers
-are present, else disbands. A leader that gets accepted by a better leader disbands and redirects its followers
-(``GROUP_DISBANDED`` + ``suggested_leader``). ``BEGIN_ALLREDUCE`` carries the shuffled peer order, a random group id
-and everybody's ``gather`` blob.
+Wire protocol and ordering rule (hivemind/averaging/matchmaking.py:24-550): every averager that wants a group
+*declares* itself under the current group key in the DHT, with an expiration equal to the time at which it wants to
+start. A peer only asks peers that come *before* it in (expiration, peer id) order to lead it, so the peer with the
+earliest expiration ends up leading. A leader answers ``ACCEPTED`` or a rejection code; it assembles the group at once
+when ``target_group_size`` is reached, or at its own expiration if at least ``min_group_size`` peers are present, and
+otherwise disbands. A leader that is itself accepted by an earlier peer lets its followers go and names that peer as
+``suggested_leader``. ``BEGIN_ALLREDUCE`` carries the shuffled peer order, a random group id and every member's
+``gather`` blob. Two peers that ask each other at the same moment are untangled by ``request_timeout``.
 
-Two-way waiting between peers that ask each other at the same moment is broken by ``request_timeout``.
+How this implementation is organised: one ``_Search`` object holds everything that belongs to a single
+``look_for_group`` call (the result future, the followers, the current leader, the declared expiration, the
+candidates already tried). The *courting loop* declares this peer, asks better-placed candidates one by one, and
+leads when its own time is up; ``rpc_join_group`` handlers of would-be followers read and update the same
+``_Search``. A single lock orders "I accept a follower" against "I am accepted as a follower".
 """
 from __future__ import annotations
 
 import asyncio
-import concurrent.futures
 import contextlib
 import random
 from math import isfinite
-from typing import AsyncIterator, Dict, Optional, Set, Tuple, Type
+from typing import AsyncIterator, Dict, List, Optional, Set, Tuple, Type
 
 from hivemind_b200.averaging.control import StepControl
 from hivemind_b200.averaging.group_info import GroupInfo
@@ -26,28 +29,52 @@ from hivemind_b200.averaging.key_manager import GroupKey, GroupKeyManager
 from hivemind_b200.dht import DHT, DHTID
 from hivemind_b200.p2p import P2P, P2PContext, P2PDaemonError, P2PHandlerError, PeerID, ServicerBase
 from hivemind_b200.proto import averaging_pb2
-from hivemind_b200.utils import DHTExpiration, TimedStorage, get_dht_time, get_logger
+from hivemind_b200.utils import DHTExpiration, get_dht_time, get_logger
 from hivemind_b200.utils.asyncio import anext, cancel_and_wait
 from hivemind_b200.utils.timed_storage import MAX_DHT_TIME_DISCREPANCY_SECONDS
 
 logger = get_logger(__name__)
 _Reply = averaging_pb2.MessageFromLeader
+_CANDIDATE_POLL_SECONDS = 0.05  # pause between two looks at the DHT while nobody suitable is declared
 
 
 class MatchmakingException(Exception):
     """Group formation failed in a way that the caller may retry."""
 
 
+class _Search:
+    """State of one ``look_for_group`` call."""
+
+    def __init__(self, step: StepControl):
+        self.step = step
+        self.outcome: asyncio.Future = asyncio.get_event_loop().create_future()  # GroupInfo
+        self.followers: Dict[PeerID, averaging_pb2.JoinRequest] = {}
+        self.leader: Optional[PeerID] = None            # set while somebody has accepted us
+        self.expiration: DHTExpiration = float("inf")   # what we declared; inf = nothing declared right now
+        self.declared_key: Optional[GroupKey] = None
+        self.end_time: DHTExpiration = step.deadline if step.deadline is not None else float("inf")
+        self.tried: Set[Tuple[PeerID, DHTExpiration]] = set()
+        self.changed = asyncio.Event()                   # pulsed when outcome, leader or followers change
+        self.saw_candidates = False
+
+    def pulse(self) -> None:
+        self.changed.set()
+
+    def desired_expiration(self, min_matchmaking_time: float) -> DHTExpiration:
+        return float(min(max(self.step.scheduled_time, get_dht_time() + min_matchmaking_time), self.end_time))
+
+
 class Matchmaking:
     def __init__(self, p2p: P2P, schema_hash: bytes, dht: DHT, *, servicer_type: Type[ServicerBase], prefix: str,
                  target_group_size: Optional[int], min_group_size: int, min_matchmaking_time: float,
                  request_timeout: float, client_mode: bool, initial_group_bits: str = ""):
-        assert "." not in prefix, "group prefix must be a string without ."
-        if request_timeout is None or request_timeout >= min_matchmaking_time:
-            logger.warning("request_timeout should be smaller than min_matchmaking_time; otherwise two peers that "
-                           "request each other simultaneously may block until matchmaking times out")
+        if "." in prefix:
+            raise ValueError("the averager prefix must not contain '.'")
         if not issubclass(servicer_type, ServicerBase):
-            raise TypeError("`servicer_type` is expected to be a ServicerBase subclass")
+            raise TypeError("servicer_type must derive from ServicerBase")
+        if request_timeout is None or request_timeout >= min_matchmaking_time:
+            logger.warning("request_timeout should be shorter than min_matchmaking_time: two peers that ask each other "
+                           "at the same moment only come apart when a request times out")
         self._p2p, self._servicer_type, self._prefix = p2p, servicer_type, prefix
         self.peer_id = p2p.peer_id
         self.schema_hash = schema_hash
@@ -55,393 +82,305 @@ class Matchmaking:
         self.target_group_size, self.min_group_size = target_group_size, min_group_size
         self.min_matchmaking_time, self.request_timeout = min_matchmaking_time, request_timeout
         self.client_mode = client_mode
-
-        self.lock_looking_for_group = asyncio.Lock()
-        self.lock_request_join_group = asyncio.Lock()
-        self.follower_was_discarded = asyncio.Event()
-        self.was_accepted_to_group = asyncio.Event()
-        self.assembled_group: asyncio.Future = asyncio.Future()
-
-        self.current_leader: Optional[PeerID] = None  # set while we follow somebody
-        self.current_followers: Dict[PeerID, averaging_pb2.JoinRequest] = {}  # peers that we accepted
-        self.potential_leaders = PotentialLeaders(self.peer_id, min_matchmaking_time, target_group_size)
-        self.step_control: Optional[StepControl] = None
+        self._one_search_at_a_time = asyncio.Lock()
+        self._membership = asyncio.Lock()   # accepting a follower vs. being accepted as one
+        self._search: Optional[_Search] = None
 
     # ------------------------------------------------------------------------------------------ status
     @property
     def is_looking_for_group(self) -> bool:
-        return self.lock_looking_for_group.locked()
+        return self._search is not None
+
+    @property
+    def current_leader(self) -> Optional[PeerID]:
+        return self._search.leader if self._search is not None else None
+
+    @property
+    def current_followers(self) -> Dict[PeerID, averaging_pb2.JoinRequest]:
+        return self._search.followers if self._search is not None else {}
 
     def __repr__(self) -> str:
-        state = "idle"
-        if self.is_looking_for_group:
-            state = f"following {self.current_leader}" if self.current_leader else f"leading {len(self.current_followers)} followers"
-        return (f"{type(self).__name__}(peer_id={self.peer_id}, {state}, key={self.group_key_manager.current_key}, "
+        if self._search is None:
+            role = "idle"
+        elif self._search.leader is not None:
+            role = f"following {self._search.leader}"
+        else:
+            role = f"leading {len(self._search.followers)} followers"
+        return (f"{type(self).__name__}(peer_id={self.peer_id}, {role}, key={self.group_key_manager.current_key}, "
                 f"client_mode={self.client_mode})")
 
-    @contextlib.asynccontextmanager
-    async def looking_for_group(self, step_control: StepControl):
-        async with self.lock_looking_for_group:
-            assert self.step_control is None
-            self.step_control = step_control
-            try:
-                yield
-            finally:
-                self.step_control = None
+    def _full(self, search: _Search) -> bool:
+        return self.target_group_size is not None and len(search.followers) + 1 >= self.target_group_size
+
+    def _viable(self, search: _Search) -> bool:
+        return len(search.followers) + 1 >= self.min_group_size
 
     # ------------------------------------------------------------------------------------------ entry point
     async def look_for_group(self, step: StepControl) -> Optional[GroupInfo]:
         """Find or lead a group before the step's deadline. Returns None if no group could be formed in time."""
-        if self.is_looking_for_group:
-            logger.info("Another look_for_group is already in progress. The current run will be scheduled after"
-                        " the existing group is either assembled or disbanded.")
-        async with self.looking_for_group(step):
-            search_task = asyncio.create_task(self._request_join_potential_leaders(step))
+        if self._one_search_at_a_time.locked():
+            logger.info("look_for_group is already running; this call waits for that search to end")
+        async with self._one_search_at_a_time:
+            search = self._search = _Search(step)
+            courting = asyncio.create_task(self._court(search))
             try:
-                return await asyncio.wait_for(self.assembled_group, timeout=step.get_timeout())
+                return await asyncio.wait_for(asyncio.shield(search.outcome), timeout=step.get_timeout())
             except asyncio.TimeoutError:
                 return None
-            except BaseException as e:
-                if len(self.current_followers) > 0:
-                    async with self.lock_request_join_group:
-                        await self.leader_disband_group()
-                if not self.assembled_group.done():
-                    self.assembled_group.set_exception(e)
-                raise
             finally:
-                await cancel_and_wait(search_task)
-                self.assembled_group.cancel()
-                while len(self.current_followers) > 0:
-                    await self.follower_was_discarded.wait()
-                    self.follower_was_discarded.clear()
-                # a new future for the next call of look_for_group
-                self.assembled_group = asyncio.Future()
-                self.was_accepted_to_group.clear()
+                await cancel_and_wait(courting)
+                if not search.outcome.done():
+                    search.outcome.cancel()
+                search.pulse()
+                # followers' handlers notice that the search is over, answer them and remove themselves
+                while search.followers:
+                    search.changed.clear()
+                    with contextlib.suppress(asyncio.TimeoutError):
+                        await asyncio.wait_for(search.changed.wait(), timeout=1.0)
+                await self._retract_declaration(search)
+                self._search = None
 
-    async def _request_join_potential_leaders(self, step: StepControl) -> GroupInfo:
-        """Ask better-placed peers to lead us, one at a time; lead ourselves when our own time runs out."""
-        assert self.is_looking_for_group
-        async with self.potential_leaders.begin_search(step, self.group_key_manager, declare=not self.client_mode):
-            while True:
-                try:
-                    next_leader = await self.potential_leaders.pop_next_leader()  # TimeoutError = our declaration expired
-                    group = await self._request_join_group(next_leader)
-                    if group is not None:
-                        return group
-                except asyncio.TimeoutError:
-                    async with self.lock_request_join_group:
-                        if self.assembled_group.done():
-                            return self.assembled_group.result()
-                        if len(self.current_followers) + 1 >= self.min_group_size:
-                            return await self.leader_assemble_group()  # good enough: run with whoever joined
-                        if len(self.current_followers) > 0:
-                            await self.leader_disband_group()
-                        continue  # nobody came: declare again and keep looking
-                except (concurrent.futures.CancelledError, asyncio.CancelledError):
-                    break
-                except Exception as e:
-                    if not self.assembled_group.done():
-                        self.assembled_group.set_exception(e)
-                    raise e
+    async def _court(self, search: _Search) -> None:
+        """Declare this peer, ask better-placed candidates to lead it, lead when its own time is up; repeat."""
+        try:
+            while not search.outcome.done():
+                if not self.client_mode:
+                    await self._declare(search)
+                else:
+                    search.expiration = search.desired_expiration(self.min_matchmaking_time)
+                search.saw_candidates = False
+                while get_dht_time() < search.expiration and not search.outcome.done():
+                    candidate = await self._next_candidate(search)
+                    if candidate is None:
+                        pause = min(_CANDIDATE_POLL_SECONDS, max(0.0, search.expiration - get_dht_time()))
+                        search.changed.clear()
+                        with contextlib.suppress(asyncio.TimeoutError):
+                            await asyncio.wait_for(search.changed.wait(), timeout=pause)
+                        continue
+                    await self._propose(search, candidate)
+                if search.outcome.done():
+                    return
+                # our own moment has come: go ahead with whoever joined, or start over
+                async with self._membership:
+                    if search.outcome.done():
+                        return
+                    if not self.client_mode and self._viable(search):
+                        await self._assemble_as_leader(search)
+                        return
+                    self._release_followers(search)
+                if not search.saw_candidates and not self.client_mode:
+                    await self.group_key_manager.update_key_on_not_enough_peers()
+                if get_dht_time() >= search.end_time:
+                    return
+        except asyncio.CancelledError:
+            raise
+        except Exception as e:
+            if not search.outcome.done():
+                search.outcome.set_exception(e)
+                search.pulse()
+
+    async def _declare(self, search: _Search) -> None:
+        search.declared_key = self.group_key_manager.current_key
+        search.expiration = search.desired_expiration(self.min_matchmaking_time)
+        await self.group_key_manager.declare_averager(search.declared_key, self.peer_id, expiration_time=search.expiration)
+
+    async def _retract_declaration(self, search: _Search) -> None:
+        key, expiration = search.declared_key, search.expiration
+        search.declared_key, search.expiration = None, float("inf")
+        if key is not None and expiration > get_dht_time():
+            with contextlib.suppress(Exception):
+                await asyncio.shield(self.group_key_manager.declare_averager(key, self.peer_id, expiration,
+                                                                             looking_for_group=False))
+
+    async def _next_candidate(self, search: _Search) -> Optional[PeerID]:
+        """The declared peer that precedes us most clearly in (expiration, id) order and was not asked yet."""
+        listing = await self.group_key_manager.get_averagers(self.group_key_manager.current_key, only_active=True)
+        mine = (search.expiration, self.peer_id.to_bytes())
+        best: Optional[Tuple[DHTExpiration, bytes, PeerID]] = None
+        for peer, expiration in listing:
+            if peer == self.peer_id:
+                continue
+            search.saw_candidates = True
+            if (peer, expiration) in search.tried or expiration > search.end_time:
+                continue
+            rank = (expiration, peer.to_bytes())
+            if rank < mine and (best is None or rank < best[:2]):
+                best = (expiration, peer.to_bytes(), peer)
+        if best is None:
+            return None
+        search.tried.add((best[2], best[0]))
+        return best[2]
 
     # ------------------------------------------------------------------------------------------ follower side
-    async def _request_join_group(self, leader: PeerID) -> Optional[GroupInfo]:
-        """Ask ``leader`` to take us in; returns the assembled group, or None if rejected / disbanded."""
-        assert self.is_looking_for_group and self.current_leader is None
+    def _promised_start(self, search: _Search) -> DHTExpiration:
+        """The latest moment by which we promise a leader to begin the all-reduce."""
+        if isfinite(search.expiration):
+            return search.expiration
+        return search.desired_expiration(self.min_matchmaking_time)
+
+    async def _propose(self, search: _Search, leader: PeerID) -> Optional[GroupInfo]:
+        """Ask ``leader`` to take us in. Returns the group if one was assembled with us in it."""
         stream: Optional[AsyncIterator[averaging_pb2.MessageFromLeader]] = None
         try:
-            async with self.lock_request_join_group:
-                leader_stub = self._servicer_type.get_stub(self._p2p, leader, namespace=self._prefix)
-                request_expiration_time = self.get_request_expiration_time()
-                stream = await leader_stub.rpc_join_group(averaging_pb2.JoinRequest(
-                    schema_hash=self.schema_hash, expiration=request_expiration_time, client_mode=self.client_mode,
-                    gather=self.step_control.data_for_gather, group_key=self.group_key_manager.current_key))
-                message = await asyncio.wait_for(anext(stream), timeout=self.request_timeout)
-                if message.code == averaging_pb2.ACCEPTED:
-                    logger.debug(f"{self.peer_id} - joining the group of {leader}, waiting for peers")
-                    self.current_leader = leader
-                    self.was_accepted_to_group.set()
-                    if len(self.current_followers) > 0:
-                        await self.leader_disband_group()
-
-            if message.code != averaging_pb2.ACCEPTED:
-                code = averaging_pb2.MessageCode.Name(message.code)
-                logger.debug(f"{self.peer_id} - requested {leader} to be my leader, but got rejected with {code}")
+            async with self._membership:
+                if search.outcome.done():
+                    return None
+                stub = self._servicer_type.get_stub(self._p2p, leader, namespace=self._prefix)
+                stream = await stub.rpc_join_group(averaging_pb2.JoinRequest(
+                    schema_hash=self.schema_hash, expiration=self._promised_start(search), client_mode=self.client_mode,
+                    gather=search.step.data_for_gather, group_key=self.group_key_manager.current_key))
+                verdict = await asyncio.wait_for(anext(stream), timeout=self.request_timeout)
+                if verdict.code == averaging_pb2.ACCEPTED:
+                    search.leader = leader
+                    self._release_followers(search)  # they are told to try our new leader
+            if verdict.code != averaging_pb2.ACCEPTED:
+                logger.debug(f"{self.peer_id}: {leader} declined to lead us "
+                             f"({averaging_pb2.MessageCode.Name(verdict.code)})")
                 return None
-
-            async with self.potential_leaders.pause_search():
-                time_to_expiration = max(0.0, self.potential_leaders.declared_expiration_time - get_dht_time())
-                message = await asyncio.wait_for(anext(stream), time_to_expiration + self.request_timeout)
-                if message.code == averaging_pb2.BEGIN_ALLREDUCE:
-                    async with self.lock_request_join_group:
-                        return await self.follower_assemble_group(leader, message)
-
-            if message.code in (averaging_pb2.GROUP_DISBANDED, averaging_pb2.CANCELLED):
-                if message.suggested_leader:
-                    suggested_leader = PeerID(message.suggested_leader)
-                    if suggested_leader != self.peer_id:
-                        logger.debug(f"{self} - leader disbanded group and redirected us to {suggested_leader}")
-                        self.current_leader = None
-                        try:
-                            await stream.aclose()
-                        except RuntimeError as e:
-                            logger.debug(e, exc_info=True)
-                        return await self._request_join_group(suggested_leader)
-                logger.debug(f"{self} - leader disbanded group")
-                return None
-
-            logger.debug(f"{self} - unexpected message from leader: {averaging_pb2.MessageCode.Name(message.code)}")
+            logger.debug(f"{self.peer_id}: accepted by {leader}, waiting for the group to fill")
+            patience = max(0.0, search.expiration - get_dht_time()) + self.request_timeout
+            verdict = await asyncio.wait_for(anext(stream), timeout=patience)
+            if verdict.code == averaging_pb2.BEGIN_ALLREDUCE:
+                async with self._membership:
+                    return await self._adopt_group(search, leader, verdict)
+            if verdict.code in (averaging_pb2.GROUP_DISBANDED, averaging_pb2.CANCELLED) and verdict.suggested_leader:
+                elsewhere = PeerID(verdict.suggested_leader)
+                if elsewhere != self.peer_id:
+                    logger.debug(f"{self.peer_id}: {leader} let its group go and points to {elsewhere}")
+                    search.leader = None
+                    await _close_stream(stream)
+                    stream = None
+                    return await self._propose(search, elsewhere)
+            logger.debug(f"{self.peer_id}: {leader} ended the group ({averaging_pb2.MessageCode.Name(verdict.code)})")
             return None
         except asyncio.TimeoutError:
-            logger.debug(f"{self} - potential leader {leader} did not respond within {self.request_timeout}")
+            logger.debug(f"{self.peer_id}: no answer from {leader} within {self.request_timeout} s")
             return None
         except (P2PDaemonError, P2PHandlerError, StopAsyncIteration) as e:
-            logger.debug(f"{self} - failed to request potential leader {leader}: {e!r}")
+            logger.debug(f"{self.peer_id}: asking {leader} failed: {e!r}")
             return None
         finally:
-            self.was_accepted_to_group.clear()
-            self.current_leader = None
+            if search.leader is not None:
+                search.leader = None
+                search.pulse()
             if stream is not None:
-                try:
-                    await stream.aclose()
-                except RuntimeError as e:
-                    logger.debug(e, exc_info=True)
+                await _close_stream(stream)
 
-    def get_request_expiration_time(self) -> float:
-        """The latest moment by which we promise to begin all-reduce with a leader."""
-        if isfinite(self.potential_leaders.declared_expiration_time):
-            return self.potential_leaders.declared_expiration_time
-        scheduled_time = max(self.step_control.scheduled_time, get_dht_time() + self.min_matchmaking_time)
-        return min(scheduled_time, self.potential_leaders.search_end_time)
+    async def _adopt_group(self, search: _Search, leader: PeerID, msg: averaging_pb2.MessageFromLeader) -> GroupInfo:
+        if search.outcome.done():
+            raise MatchmakingException("a group was announced to us after our search had ended")
+        if search.leader != leader:
+            raise MatchmakingException(f"{leader} announced a group but we follow {search.leader}")
+        members = tuple(PeerID(raw) for raw in msg.ordered_peer_ids)
+        if self.peer_id not in members or len(members) != len(msg.gathered):
+            raise MatchmakingException("the leader announced a malformed group")
+        group = GroupInfo(msg.group_id, members, tuple(msg.gathered))
+        await self.group_key_manager.update_key_on_group_assembled(group)
+        search.outcome.set_result(group)
+        search.pulse()
+        return group
 
     # ------------------------------------------------------------------------------------------ leader side
     async def rpc_join_group(self, request: averaging_pb2.JoinRequest, context: P2PContext
                              ) -> AsyncIterator[averaging_pb2.MessageFromLeader]:
         """Serve a peer that asks us to lead it: reject, or accept and later tell it how the group turned out."""
+        suitor, search = context.remote_id, None
         try:
-            async with self.lock_request_join_group:
-                reason_to_reject = self._check_reasons_to_reject(request, context)
-                if reason_to_reject is not None:
-                    yield reason_to_reject
+            async with self._membership:
+                search = self._search
+                refusal = self._reason_to_refuse(search, request, suitor)
+                if refusal is not None:
+                    search = None
+                    yield refusal
                     return
-                self.current_followers[context.remote_id] = request
+                search.followers[suitor] = request
                 yield _Reply(code=averaging_pb2.ACCEPTED)
-                if self.target_group_size is not None and len(self.current_followers) + 1 >= self.target_group_size:
-                    await self.leader_assemble_group()  # the group is full: begin right away
+                if self._full(search):
+                    await self._assemble_as_leader(search)  # complete: begin right away
 
-            # wait until the group is assembled, disbanded, or we are taken in by another leader
-            timeout = max(0.0, self.potential_leaders.declared_expiration_time - get_dht_time())
-            accepted_elsewhere = asyncio.create_task(self.was_accepted_to_group.wait())
-            try:
-                await asyncio.wait({self.assembled_group, accepted_elsewhere}, return_when=asyncio.FIRST_COMPLETED,
-                                   timeout=timeout)
-            finally:
-                accepted_elsewhere.cancel()
-            if not self.assembled_group.done() and not self.was_accepted_to_group.is_set():
-                async with self.lock_request_join_group:
-                    if self.assembled_group.done():
-                        pass  # assembled while we were waiting for the lock
-                    elif len(self.current_followers) + 1 >= self.min_group_size and self.is_looking_for_group:
-                        await self.leader_assemble_group()  # time is up, proceed with a smaller group
+            # until the group is settled, we are taken in elsewhere, or our declared time has come
+            while not search.outcome.done() and search.leader is None and suitor in search.followers:
+                remaining = search.expiration - get_dht_time()
+                if remaining <= 0:
+                    break
+                search.changed.clear()
+                with contextlib.suppress(asyncio.TimeoutError):
+                    await asyncio.wait_for(search.changed.wait(), timeout=remaining if isfinite(remaining) else None)
+            if not search.outcome.done() and search.leader is None and suitor in search.followers:
+                async with self._membership:
+                    if search.outcome.done():
+                        pass  # settled while we were waiting for the lock
+                    elif self._viable(search) and self._search is search:
+                        await self._assemble_as_leader(search)  # time is up: a smaller group will do
                     else:
-                        await self.leader_disband_group()
+                        self._release_followers(search)
 
-            if (self.was_accepted_to_group.is_set() or not self.assembled_group.done() or self.assembled_group.cancelled()
-                    or context.remote_id not in self.assembled_group.result()):
-                if self.current_leader is not None:
-                    yield _Reply(code=averaging_pb2.GROUP_DISBANDED, suggested_leader=self.current_leader.to_bytes())
-                else:
-                    yield _Reply(code=averaging_pb2.GROUP_DISBANDED)
+            group = search.outcome.result() if (search.outcome.done() and not search.outcome.cancelled()
+                                                and search.outcome.exception() is None) else None
+            if search.leader is not None or group is None or suitor not in group:
+                elsewhere = search.leader.to_bytes() if search.leader is not None else b""
+                yield _Reply(code=averaging_pb2.GROUP_DISBANDED, suggested_leader=elsewhere)
                 return
-
-            group_info = self.assembled_group.result()
-            yield _Reply(code=averaging_pb2.BEGIN_ALLREDUCE, group_id=group_info.group_id,
-                         ordered_peer_ids=[item.to_bytes() for item in group_info.peer_ids], gathered=group_info.gathered)
-        except (concurrent.futures.CancelledError, asyncio.CancelledError):
-            return  # the follower hung up
+            yield _Reply(code=averaging_pb2.BEGIN_ALLREDUCE, group_id=group.group_id, gathered=group.gathered,
+                         ordered_peer_ids=[member.to_bytes() for member in group.peer_ids])
+        except asyncio.CancelledError:
+            return  # the suitor hung up
         except Exception as e:
             logger.exception(e)
             yield _Reply(code=averaging_pb2.INTERNAL_ERROR)
         finally:
-            self.current_followers.pop(context.remote_id, None)
-            self.follower_was_discarded.set()
+            if search is not None:
+                search.followers.pop(suitor, None)
+                search.pulse()
 
-    def _check_reasons_to_reject(self, request: averaging_pb2.JoinRequest, context: P2PContext) -> Optional[_Reply]:
-        if not self.is_looking_for_group or self.assembled_group.done():
+    def _reason_to_refuse(self, search: Optional[_Search], request: averaging_pb2.JoinRequest, suitor: PeerID
+                          ) -> Optional[_Reply]:
+        if search is None or search.outcome.done():
             return _Reply(code=averaging_pb2.NOT_LOOKING_FOR_GROUP)
-        if not isinstance(request.schema_hash, bytes) or len(request.schema_hash) == 0 \
-                or not isinstance(request.expiration, DHTExpiration) or not isfinite(request.expiration) \
-                or self.client_mode or not isinstance(request.group_key, GroupKey):
+        well_formed = (isinstance(request.schema_hash, bytes) and len(request.schema_hash) > 0
+                       and isinstance(request.expiration, DHTExpiration) and isfinite(request.expiration)
+                       and isinstance(request.group_key, GroupKey))
+        if not well_formed or self.client_mode:
             return _Reply(code=averaging_pb2.PROTOCOL_VIOLATION)
         if request.schema_hash != self.schema_hash:
             return _Reply(code=averaging_pb2.BAD_SCHEMA_HASH)
         if request.group_key != self.group_key_manager.current_key:
             return _Reply(code=averaging_pb2.BAD_GROUP_KEY)
-        if self.potential_leaders.declared_group_key is None:
+        if search.declared_key is None:
             return _Reply(code=averaging_pb2.NOT_DECLARED)
-        if self.potential_leaders.declared_expiration_time > (request.expiration or float("inf")):
-            return _Reply(code=averaging_pb2.BAD_EXPIRATION_TIME)
-        if self.current_leader is not None:
-            return _Reply(code=averaging_pb2.NOT_A_LEADER, suggested_leader=self.current_leader.to_bytes())
-        if context.remote_id == self.peer_id or context.remote_id in self.current_followers:
+        if search.expiration > (request.expiration or float("inf")):
+            return _Reply(code=averaging_pb2.BAD_EXPIRATION_TIME)  # it should be leading us, not the other way round
+        if search.leader is not None:
+            return _Reply(code=averaging_pb2.NOT_A_LEADER, suggested_leader=search.leader.to_bytes())
+        if suitor == self.peer_id or suitor in search.followers:
             return _Reply(code=averaging_pb2.DUPLICATE_PEER_ID)
-        if self.target_group_size is not None and len(self.current_followers) + 1 >= self.target_group_size:
+        if self._full(search):
             return _Reply(code=averaging_pb2.GROUP_IS_FULL)
         return None
 
-    async def leader_assemble_group(self) -> GroupInfo:
-        """Close the group: fix the (shuffled) peer order, draw a group id, publish the result to the waiters."""
-        assert self.lock_looking_for_group.locked() and self.lock_request_join_group.locked() and not self.client_mode
-        assert not self.assembled_group.done()
-        group_id = DHTID.generate().to_bytes()
-        ordered_peer_ids = list(self.current_followers)
-        ordered_peer_ids.append(self.peer_id)
-        random.shuffle(ordered_peer_ids)
-        gathered = tuple(self.step_control.data_for_gather if peer_id == self.peer_id else self.current_followers[peer_id].gather
-                         for peer_id in ordered_peer_ids)
-        logger.debug(f"{self.peer_id} - assembled group of {len(ordered_peer_ids)} peers")
-        group_info = GroupInfo(group_id, tuple(ordered_peer_ids), gathered)
-        await self.group_key_manager.update_key_on_group_assembled(group_info)
-        self.assembled_group.set_result(group_info)
-        return group_info
+    async def _assemble_as_leader(self, search: _Search) -> GroupInfo:
+        """Close the group: shuffle the member order, draw a group id, let everybody who waits know."""
+        if self.client_mode or search.outcome.done():
+            raise MatchmakingException("cannot assemble a group now")
+        members: List[PeerID] = [*search.followers, self.peer_id]
+        random.shuffle(members)
+        blobs = tuple(search.step.data_for_gather if m == self.peer_id else search.followers[m].gather for m in members)
+        group = GroupInfo(DHTID.generate().to_bytes(), tuple(members), blobs)
+        logger.debug(f"{self.peer_id}: leading a group of {len(members)}")
+        await self.group_key_manager.update_key_on_group_assembled(group)
+        search.outcome.set_result(group)
+        search.pulse()
+        return group
 
-    async def follower_assemble_group(self, leader: PeerID, msg: averaging_pb2.MessageFromLeader) -> GroupInfo:
-        """Adopt the group announced by our leader."""
-        assert self.lock_looking_for_group.locked() and self.lock_request_join_group.locked()
-        assert not self.assembled_group.done()
-        assert self.current_leader == leader, f"averager does not follow {leader} (actual: {self.current_leader})"
-        group_id = msg.group_id
-        ordered_peer_ids = [PeerID(item) for item in msg.ordered_peer_ids]
-        assert self.peer_id in ordered_peer_ids, "Leader sent us group_peer_ids that does not contain us!"
-        assert len(ordered_peer_ids) == len(msg.gathered)
-        logger.debug(f"{self.peer_id} - follower assembled group with leader {leader}")
-        group_info = GroupInfo(group_id, tuple(ordered_peer_ids), tuple(msg.gathered))
-        await self.group_key_manager.update_key_on_group_assembled(group_info)
-        self.assembled_group.set_result(group_info)
-        return group_info
-
-    async def leader_disband_group(self) -> None:
-        """Let all accepted followers go (their handlers notice that they are no longer in ``current_followers``)."""
-        assert self.lock_request_join_group.locked() and not self.client_mode
-        self.current_followers.clear()
+    def _release_followers(self, search: _Search) -> None:
+        """Let the accepted followers go: their handlers see that they are no longer listed and answer them."""
+        if search.followers:
+            search.followers.clear()
+        search.pulse()
 
 
-class PotentialLeaders:
-    """Keeps our own declaration fresh in the DHT and maintains a queue of peers that could lead us."""
-
-    def __init__(self, peer_id: PeerID, min_matchmaking_time: DHTExpiration, target_group_size: Optional[int]):
-        self.peer_id, self.min_matchmaking_time = peer_id, min_matchmaking_time
-        self.target_group_size = target_group_size
-        self.running, self.update_triggered, self.update_finished = asyncio.Event(), asyncio.Event(), asyncio.Event()
-        self.declared_expiration, self.lock_search, self.lock_declare = asyncio.Event(), asyncio.Lock(), asyncio.Lock()
-        self.leader_queue = TimedStorage[PeerID, DHTExpiration]()
-        self.past_attempts: Set[Tuple[PeerID, DHTExpiration]] = set()
-        self.declared_expiration_time = float("inf")
-        self.declared_group_key: Optional[GroupKey] = None
-        self.max_assured_time = float("-inf")
-        self.search_end_time = float("inf")
-
-    @contextlib.asynccontextmanager
-    async def begin_search(self, step: StepControl, key_manager: GroupKeyManager, declare: bool = True):
-        async with self.lock_search:
-            self.running.set()
-            self.search_end_time = step.deadline if step.deadline is not None else float("inf")
-            update_queue_task = asyncio.create_task(self._update_queue_periodically(key_manager))
-            declare_averager_task = None
-            if declare:
-                declare_averager_task = asyncio.create_task(self._declare_averager_periodically(step, key_manager))
-            try:
-                yield self
-            finally:
-                await cancel_and_wait(update_queue_task)
-                if declare_averager_task is not None:
-                    await cancel_and_wait(declare_averager_task)
-                for field in (self.past_attempts, self.leader_queue, self.running, self.update_finished,
-                              self.update_triggered, self.declared_expiration):
-                    field.clear()
-                self.max_assured_time = float("-inf")
-                self.search_end_time = float("inf")
-
-    @contextlib.asynccontextmanager
-    async def pause_search(self):
-        was_running = self.running.is_set()
-        try:
-            self.running.clear()
-            yield
-        finally:
-            if was_running:
-                self.running.set()
-            else:
-                self.running.clear()
-
-    async def pop_next_leader(self) -> PeerID:
-        """The next peer to ask, i.e. one that precedes us in (expiration, id) order. Raises ``TimeoutError`` when
-        our own declaration was renewed in the meantime (the caller then decides whether to lead)."""
-        assert self.running.is_set(), "Not running search at the moment"
-        while True:
-            maybe_next_leader, entry = self.leader_queue.top() or (None, None)
-            if maybe_next_leader is None or self.max_assured_time <= entry.expiration_time <= self.search_end_time:
-                self.update_triggered.set()
-            if maybe_next_leader is None or ((entry.expiration_time, maybe_next_leader.to_bytes())
-                                             > (self.declared_expiration_time, self.peer_id.to_bytes())):
-                update_wait = asyncio.create_task(self.update_finished.wait())
-                declare_wait = asyncio.create_task(self.declared_expiration.wait())
-                try:
-                    await asyncio.wait({update_wait, declare_wait}, return_when=asyncio.FIRST_COMPLETED)
-                finally:
-                    update_wait.cancel()
-                    declare_wait.cancel()
-                self.declared_expiration.clear()
-                if self.update_finished.is_set():
-                    self.update_finished.clear()
-                    continue
-                raise asyncio.TimeoutError("pop_next_leader was invalidated: re-declared averager in background")
-            del self.leader_queue[maybe_next_leader]
-            self.past_attempts.add((maybe_next_leader, entry.expiration_time))
-            return maybe_next_leader
-
-    async def _update_queue_periodically(self, key_manager: GroupKeyManager) -> None:
-        DISCREPANCY = MAX_DHT_TIME_DISCREPANCY_SECONDS
-        while get_dht_time() < self.search_end_time:
-            new_peers = await key_manager.get_averagers(key_manager.current_key, only_active=True)
-            self.max_assured_time = max(self.max_assured_time, get_dht_time() + self.min_matchmaking_time - DISCREPANCY)
-            self.leader_queue.clear()
-            for peer, peer_expiration_time in new_peers:
-                if peer == self.peer_id or (peer, peer_expiration_time) in self.past_attempts:
-                    continue
-                self.leader_queue.store(peer, peer_expiration_time, peer_expiration_time)
-                self.max_assured_time = max(self.max_assured_time, peer_expiration_time - DISCREPANCY)
-            self.update_finished.set()
-            running_wait = asyncio.create_task(self.running.wait())
-            trigger_wait = asyncio.create_task(self.update_triggered.wait())
-            try:
-                await asyncio.wait({running_wait, trigger_wait}, return_when=asyncio.ALL_COMPLETED,
-                                   timeout=self.search_end_time - get_dht_time() if isfinite(self.search_end_time) else None)
-            finally:
-                running_wait.cancel()
-                trigger_wait.cancel()
-            self.update_triggered.clear()
-            await asyncio.sleep(0.005)  # the DHT shares this process: do not starve it while polling
-
-    async def _declare_averager_periodically(self, step: StepControl, key_manager: GroupKeyManager) -> None:
-        async with self.lock_declare:
-            try:
-                while True:
-                    await self.running.wait()
-                    new_expiration_time = float(min(max(step.scheduled_time, get_dht_time() + self.min_matchmaking_time),
-                                                    self.search_end_time))
-                    self.declared_group_key = group_key = key_manager.current_key
-                    self.declared_expiration_time = new_expiration_time
-                    self.declared_expiration.set()
-                    await key_manager.declare_averager(group_key, self.peer_id, expiration_time=new_expiration_time)
-                    await asyncio.sleep(max(0.0, self.declared_expiration_time - get_dht_time()))
-                    if self.running.is_set() and len(self.leader_queue) == 0:
-                        await key_manager.update_key_on_not_enough_peers()
-            finally:
-                if self.declared_group_key is not None:
-                    prev_declared_key, prev_expiration_time = self.declared_group_key, self.declared_expiration_time
-                    self.declared_group_key, self.declared_expiration_time = None, float("inf")
-                    self.leader_queue, self.max_assured_time = TimedStorage[PeerID, DHTExpiration](), float("-inf")
-                    if prev_expiration_time > get_dht_time():
-                        await asyncio.shield(key_manager.declare_averager(prev_declared_key, self.peer_id,
-                                                                          prev_expiration_time, looking_for_group=False))
+async def _close_stream(stream) -> None:
+    try:
+        await stream.aclose()
+    except RuntimeError as e:  # the generator is running in another task that is being cancelled
+        logger.debug(e, exc_info=True)
