@@ -1,26 +1,24 @@
 """``DHTNode``: one participant of the distributed hash table (asyncio, lives inside the DHT thread).
 
-Behaviour follows the reference node (hivemind/dht/node.py:45-937): ``store_many`` finds the ``num_replicas``
-nearest nodes to each key and stores there (and locally when this node is among the nearest); ``get_many`` answers
-from local storage / cache when the entry is fresh enough and otherwise traverses the DHT, merging dictionary
-values from every visited node; unresponsive peers are black-listed with exponential back-off; results can be
-cached locally and on the nearest node that did not have them; concurrent gets for one key share a single search.
+Behaviour contract (hivemind/dht/node.py:45-937): ``store_many`` finds the ``num_replicas`` nodes nearest to each key
+and stores there (and locally when this node is among them); ``get_many`` answers from local storage / cache when the
+entry is fresh enough and otherwise traverses the DHT, merging dictionary values from every node it visits;
+unresponsive peers are skipped for a while with exponential back-off; results can be cached locally and on the
+nearest node that did not have them; concurrent gets for one key share what any of them finds; cached entries that
+were used are re-fetched shortly before they expire.
+
+Decomposition used here: ``Blacklist`` (who not to ask), ``_Lookup`` (what one get request has collected for one
+key), ``_Replication`` (placing the records of one key on replicas), ``_CacheRefresher`` (the queue and task that keep
+used cache entries fresh) and ``DHTNode`` itself, which wires them to the protocol and to the graph traversal.
 """
 from __future__ import annotations
 
 import asyncio
-import dataclasses
 import os
 import random
 from collections import defaultdict
-from dataclasses import dataclass, field
-from functools import partial
-from typing import (Any, Awaitable, Callable, Collection, DefaultDict, Dict, Iterable, List, Optional, Sequence, Set,
-                    Tuple, Type, Union)
+from typing import Any, Awaitable, Collection, Dict, Iterable, List, Optional, Sequence, Set, Tuple, Type, Union
 
-from sortedcontainers import SortedSet
-
-from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.dht.crypto import DHTRecord, RecordValidatorBase
 from hivemind_b200.dht.protocol import DHTProtocol
 from hivemind_b200.dht.routing import BinaryDHTValue, DHTID, DHTKey, DHTValue, Subkey
@@ -28,27 +26,31 @@ from hivemind_b200.dht.storage import DictionaryDHTValue
 from hivemind_b200.dht.traverse import traverse_dht
 from hivemind_b200.p2p import P2P, PeerID
 from hivemind_b200.utils import MSGPackSerializer, SerializerBase, get_logger
+from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.utils.auth import AuthorizerBase
 from hivemind_b200.utils.multiaddr import Multiaddr
 from hivemind_b200.utils.timed_storage import DHTExpiration, TimedStorage, ValueWithExpiration, get_dht_time
 
 logger = get_logger(__name__)
 DEFAULT_NUM_WORKERS = int(os.getenv("HIVEMIND_DHT_NUM_WORKERS", 4))
+StoredPayload = Union[BinaryDHTValue, DictionaryDHTValue]
+GetResult = Optional[ValueWithExpiration[DHTValue]]
 
 
 class Blacklist:
-    """Peers that failed to respond are skipped for ``base_time * backoff_rate ** (failures - 1)`` seconds."""
+    """Peers that did not answer are left alone for ``base_time * backoff_rate ** (earlier bans)`` seconds."""
 
-    def __init__(self, base_time: float, backoff_rate: float, **kwargs):
+    def __init__(self, base_time: float, backoff_rate: float, **storage_kwargs):
         self.base_time, self.backoff = base_time, backoff_rate
-        self.banned_peers = TimedStorage[PeerID, int](**kwargs)
-        self.ban_counter: DefaultDict[PeerID, int] = defaultdict(int)
+        self.banned_peers = TimedStorage[PeerID, int](**storage_kwargs)
+        self.ban_counter: Dict[PeerID, int] = {}
 
     def register_failure(self, peer: PeerID) -> None:
-        if peer not in self.banned_peers and self.base_time > 0:
-            ban_duration = self.base_time * self.backoff ** self.ban_counter[peer]
-            self.banned_peers.store(peer, self.ban_counter[peer], expiration_time=get_dht_time() + ban_duration)
-            self.ban_counter[peer] += 1
+        if self.base_time <= 0 or peer in self.banned_peers:
+            return
+        strikes = self.ban_counter.get(peer, 0)
+        self.banned_peers.store(peer, strikes, expiration_time=get_dht_time() + self.base_time * self.backoff ** strikes)
+        self.ban_counter[peer] = strikes + 1
 
     def register_success(self, peer: PeerID) -> None:
         del self.banned_peers[peer]
@@ -62,94 +64,206 @@ class Blacklist:
         self.ban_counter.clear()
 
     def __repr__(self) -> str:
-        return (f"{type(self).__name__}(base_time={self.base_time}, backoff={self.backoff}, "
-                f"banned_peers={len(self.banned_peers)})")
+        return f"{type(self).__name__}(base_time={self.base_time}, backoff={self.backoff}, banned={len(self.banned_peers)})"
 
 
-class CacheRefreshQueue(TimedStorage[DHTID, DHTExpiration]):
-    """Keys whose cached value should be re-fetched shortly before it expires."""
+class _Lookup:
+    """What one get request knows about one key so far: the freshest payload, where it came from, and the future
+    that the caller awaits. ``horizon`` is the expiration time from which on a value is good enough to stop."""
 
-    frozen = True
+    __slots__ = ("key_id", "horizon", "payload", "freshest", "origin", "future", "_serializer", "_validator")
 
-
-@dataclass(init=True, repr=True, frozen=False, order=False)
-class _SearchState:
-    """Progress of one get request: the freshest value seen so far and who is waiting for it."""
-
-    key_id: DHTID
-    sufficient_expiration_time: DHTExpiration
-    binary_value: Optional[Union[BinaryDHTValue, DictionaryDHTValue]] = None
-    expiration_time: Optional[DHTExpiration] = None
-    source_node_id: Optional[DHTID] = None
-    future: asyncio.Future = field(default_factory=lambda: asyncio.get_event_loop().create_future())
-    serializer: Type[SerializerBase] = MSGPackSerializer
-    record_validator: Optional[RecordValidatorBase] = None
-
-    def add_candidate(self, candidate: Optional[ValueWithExpiration[Union[BinaryDHTValue, DictionaryDHTValue]]],
-                      source_node_id: Optional[DHTID]) -> None:
-        if self.finished or candidate is None:
-            return
-        elif isinstance(candidate.value, DictionaryDHTValue) and isinstance(self.binary_value, DictionaryDHTValue):
-            self.binary_value.maxsize = max(self.binary_value.maxsize, candidate.value.maxsize)
-            for subkey, subentry in candidate.value.items():
-                self.binary_value.store(subkey, subentry.value, subentry.expiration_time)
-        elif candidate.expiration_time > (self.expiration_time or float("-inf")):
-            self.binary_value = candidate.value
-        if candidate.expiration_time > (self.expiration_time or float("-inf")):
-            self.expiration_time = candidate.expiration_time
-            self.source_node_id = source_node_id
-            if self.expiration_time >= self.sufficient_expiration_time:
-                self.finish_search()
-
-    def add_done_callback(self, callback: Callable[["_SearchState"], Any]) -> None:
-        self.future.add_done_callback(lambda _future: callback(self))
-
-    def finish_search(self) -> None:
-        if self.future.done():
-            return
-        elif not self.found_something:
-            self.future.set_result(None)
-        elif isinstance(self.binary_value, BinaryDHTValue):
-            value_bytes = self.binary_value
-            if self.record_validator is not None:
-                record = DHTRecord(self.key_id.to_bytes(), DHTProtocol.IS_REGULAR_VALUE, value_bytes, self.expiration_time)
-                value_bytes = self.record_validator.strip_value(record)
-            self.future.set_result(ValueWithExpiration(self.serializer.loads(value_bytes), self.expiration_time))
-        elif isinstance(self.binary_value, DictionaryDHTValue):
-            dict_with_subkeys = {}
-            for subkey, (value_bytes, item_expiration_time) in self.binary_value.items():
-                if self.record_validator is not None:
-                    subkey_bytes = self.serializer.dumps(subkey)
-                    record = DHTRecord(self.key_id.to_bytes(), subkey_bytes, value_bytes, item_expiration_time)
-                    value_bytes = self.record_validator.strip_value(record)
-                dict_with_subkeys[subkey] = ValueWithExpiration(self.serializer.loads(value_bytes), item_expiration_time)
-            self.future.set_result(ValueWithExpiration(dict_with_subkeys, self.expiration_time))
-        else:
-            logger.error(f"invalid value type: {type(self.binary_value)}")
+    def __init__(self, key_id: DHTID, horizon: DHTExpiration, serializer: Type[SerializerBase],
+                 validator: Optional[RecordValidatorBase]):
+        self.key_id, self.horizon = key_id, horizon
+        self.payload: Optional[StoredPayload] = None
+        self.freshest: Optional[DHTExpiration] = None
+        self.origin: Optional[DHTID] = None
+        self.future: asyncio.Future = asyncio.get_event_loop().create_future()
+        self._serializer, self._validator = serializer, validator
 
     @property
     def found_something(self) -> bool:
-        return self.expiration_time is not None
+        return self.freshest is not None
 
     @property
     def finished(self) -> bool:
         return self.future.done()
 
-    def __lt__(self, other: "_SearchState") -> bool:
-        return self.sufficient_expiration_time < other.sufficient_expiration_time
+    def offer(self, candidate: Optional[ValueWithExpiration[StoredPayload]], origin: Optional[DHTID]) -> None:
+        """Take a payload reported by ``origin`` into account; dictionaries from different nodes are merged."""
+        if candidate is None or self.future.done():
+            return
+        payload, expiration = candidate.value, candidate.expiration_time
+        newer = self.freshest is None or expiration > self.freshest
+        if isinstance(payload, DictionaryDHTValue) and isinstance(self.payload, DictionaryDHTValue):
+            self.payload.maxsize = max(self.payload.maxsize, payload.maxsize)
+            for subkey, entry in payload.items():
+                self.payload.store(subkey, entry.value, entry.expiration_time)
+        elif newer:
+            self.payload = payload
+        if newer:
+            self.freshest, self.origin = expiration, origin
+            if expiration >= self.horizon:
+                self.settle()
 
-    def __hash__(self) -> int:
-        return hash(self.key_id)
+    def settle(self) -> None:
+        """Resolve the future with what has been collected (None if nothing was found)."""
+        if self.future.done():
+            return
+        if not self.found_something:
+            self.future.set_result(None)
+        elif isinstance(self.payload, DictionaryDHTValue):
+            decoded = {subkey: ValueWithExpiration(self._decode(self._serializer.dumps(subkey), raw, expiration), expiration)
+                       for subkey, (raw, expiration) in self.payload.items()}
+            self.future.set_result(ValueWithExpiration(decoded, self.freshest))
+        elif isinstance(self.payload, BinaryDHTValue):
+            value = self._decode(DHTProtocol.IS_REGULAR_VALUE, self.payload, self.freshest)
+            self.future.set_result(ValueWithExpiration(value, self.freshest))
+        else:
+            logger.error(f"a DHT payload of unexpected type {type(self.payload)} was dropped")
+
+    def _decode(self, subkey_bytes: bytes, raw: bytes, expiration: DHTExpiration) -> DHTValue:
+        if self._validator is not None:
+            raw = self._validator.strip_value(DHTRecord(self.key_id.to_bytes(), subkey_bytes, raw, expiration))
+        return self._serializer.loads(raw)
+
+
+class _CacheRefresher:
+    """Keeps cache entries that were actually used from going stale: each is looked up again
+    ``lead_time`` seconds before it expires, several at once when their deadlines are close."""
+
+    def __init__(self, node: "DHTNode", lead_time: Optional[float]):
+        self.node, self.lead_time = node, lead_time
+        self.queue = TimedStorage[DHTID, DHTExpiration]()
+        self.queue.frozen = True  # entries leave the queue only when this class removes them
+        self._wake = asyncio.Event()
+        self._task: Optional[asyncio.Task] = None
+
+    @property
+    def enabled(self) -> bool:
+        return self.lead_time is not None and self.lead_time > 0
+
+    def watch(self, key_id: DHTID, expiration: DHTExpiration) -> None:
+        if not self.enabled:
+            return
+        if self._task is None or self._task.done():
+            self._task = asyncio.create_task(self._run())
+        head = self.queue.top()
+        if head is None or expiration < head[1].expiration_time:
+            self._wake.set()  # the task must recompute when to get up
+        self.queue.store(key_id, value=expiration, expiration_time=expiration)
+
+    def stop(self) -> None:
+        if self._task is not None:
+            self._task.cancel()
+
+    async def _run(self) -> None:
+        while self.node.is_alive:
+            if len(self.queue) == 0:
+                await self._wake.wait()
+                self._wake.clear()
+                continue
+            key_id, (_, due) = self.queue.top()
+            try:
+                await asyncio.wait_for(self._wake.wait(), timeout=due - self.lead_time - get_dht_time())
+                self._wake.clear()
+                continue  # something more urgent may have arrived
+            except asyncio.TimeoutError:
+                pass
+            now, batch, latest = get_dht_time(), {key_id}, due
+            del self.queue[key_id]
+            while self.queue and len(batch) < self.node.chunk_size:
+                other, (_, other_due) = self.queue.top()
+                if other_due > now + self.lead_time:
+                    break
+                del self.queue[other]
+                batch.add(other)
+                latest = max(latest, other_due)
+            await self.node.get_many_by_id(batch, latest + self.lead_time + 1, _is_refresh=True)
+
+
+class _Replication:
+    """Places all records of one key id (one key, possibly several sub-keys) on ``num_replicas`` nodes."""
+
+    def __init__(self, node: "DHTNode", key_id: DHTID, original_key: DHTKey,
+                 records: List[Tuple[Subkey, DHTValue, DHTExpiration]], exclude_self: bool, first_reply_is_enough: bool):
+        self.node, self.key_id, self.original_key = node, key_id, original_key
+        self.exclude_self, self.first_reply_is_enough = exclude_self, first_reply_is_enough
+        protocol = node.protocol
+        self.subkeys = [subkey for subkey, _, _ in records]
+        self.expirations = [expiration for _, _, expiration in records]
+        self.wire_values: List[bytes] = []
+        for subkey, value, expiration in records:
+            raw = protocol.serializer.dumps(value)
+            if protocol.record_validator is not None:
+                raw = protocol.record_validator.sign_value(DHTRecord(key_id.to_bytes(), self._subkey_bytes(subkey), raw, expiration))
+            self.wire_values.append(raw)
+        self.accepted: Dict[Subkey, Optional[bool]] = {subkey: None for subkey in self.subkeys}
+        self.reported = {subkey: asyncio.Event() for subkey in self.subkeys}
+
+    def _subkey_bytes(self, subkey: Subkey) -> bytes:
+        protocol = self.node.protocol
+        return protocol.IS_REGULAR_VALUE if subkey is None else protocol.serializer.dumps(subkey)
+
+    def _store_here(self) -> None:
+        protocol = self.node.protocol
+        for subkey, raw, expiration in zip(self.subkeys, self.wire_values, self.expirations):
+            if protocol.record_validator is not None and not protocol.record_validator.validate(
+                    DHTRecord(self.key_id.to_bytes(), self._subkey_bytes(subkey), raw, expiration)):
+                self.accepted[subkey] = False
+                self.reported[subkey].set()
+                continue
+            self.accepted[subkey] = protocol.storage.store(self.key_id, raw, expiration, subkey=subkey)
+            if self.first_reply_is_enough:
+                self.reported[subkey].set()
+
+    def _absorb_reply(self, verdicts: Sequence[bool]) -> None:
+        for subkey, verdict in zip(self.subkeys, verdicts):
+            self.accepted[subkey] = verdict or self.accepted[subkey]
+            if self.first_reply_is_enough:
+                self.reported[subkey].set()
+
+    async def run(self, nearest: List[DHTID], address_of: Dict[DHTID, PeerID]) -> None:
+        """``nearest``: the nodes nearest to the key that the traversal found (never this node itself)."""
+        node = self.node
+        targets = list(nearest) if self.exclude_self else list(nearest) + [node.node_id]
+        targets.sort(key=self.key_id.xor_distance)
+        cursor, replicas, in_flight = 0, 0, set()
+        while replicas < node.num_replicas and (cursor < len(targets) or in_flight):
+            while cursor < len(targets) and replicas + len(in_flight) < node.num_replicas:
+                target = targets[cursor]
+                cursor += 1
+                if target == node.node_id:
+                    self._store_here()
+                    replicas += 1
+                else:
+                    in_flight.add(asyncio.create_task(node.protocol.call_store(
+                        address_of[target], keys=[self.key_id] * len(self.subkeys), values=self.wire_values,
+                        expiration_time=self.expirations, subkeys=self.subkeys)))
+            if in_flight:
+                done, in_flight = await asyncio.wait(in_flight, return_when=asyncio.FIRST_COMPLETED)
+                for task in done:
+                    if task.result() is not None:
+                        replicas += 1
+                        self._absorb_reply(task.result())
+        if node.cache_on_store:
+            node._note_own_store(self.key_id, self.subkeys, self.wire_values, self.expirations,
+                                 [self.accepted[subkey] for subkey in self.subkeys])
+        for event in self.reported.values():
+            event.set()
 
 
 class DHTNode:
     # fmt:off
     node_id: DHTID; is_alive: bool; peer_id: PeerID; num_replicas: int; num_workers: int; protocol: DHTProtocol
-    chunk_size: int; refresh_timeout: float; cache_locally: bool; cache_nearest: int; cache_refresh_before_expiry: float
-    cache_on_store: bool; reuse_get_requests: bool; pending_get_requests: DefaultDict[DHTID, SortedSet]
-    cache_refresh_task: Optional[asyncio.Task]; cache_refresh_evt: asyncio.Event; cache_refresh_queue: CacheRefreshQueue
-    blacklist: Blacklist
+    chunk_size: int; refresh_timeout: Optional[float]; cache_locally: bool; cache_nearest: int
+    cache_refresh_before_expiry: float; cache_on_store: bool; reuse_get_requests: bool; blacklist: Blacklist
     # fmt:on
+
+    def __init__(self, *, _initialized_with_create: bool = False):
+        if not _initialized_with_create:
+            raise RuntimeError("use `await DHTNode.create(...)`")
 
     @classmethod
     async def create(cls, p2p: Optional[P2P] = None, node_id: Optional[DHTID] = None,
@@ -165,76 +279,90 @@ class DHTNode:
         """Create a node, start (or adopt) its transport and bootstrap from ``initial_peers``.
 
         Extra ``kwargs`` go to ``P2P.create`` when the node owns its transport. See the module docstring for the
-        meaning of the caching and black-list options; defaults equal the reference's (node.py:99-128).
+        meaning of the caching and black-list options; the defaults are the reference's (node.py:99-128).
         """
         self = cls(_initialized_with_create=True)
-        self.node_id = node_id if node_id is not None else DHTID.generate()
+        self.node_id = DHTID.generate() if node_id is None else node_id
         self.num_replicas, self.num_workers, self.chunk_size = num_replicas, num_workers, chunk_size
-        self.is_alive = True
-        self.reuse_get_requests = reuse_get_requests
-        self.pending_get_requests = defaultdict(partial(SortedSet, key=lambda _res: -_res.sufficient_expiration_time))
-        self.refresh_timeout = refresh_timeout
+        self.refresh_timeout, self.reuse_get_requests = refresh_timeout, reuse_get_requests
         self.cache_locally, self.cache_nearest, self.cache_on_store = cache_locally, cache_nearest, cache_on_store
         self.cache_refresh_before_expiry = cache_refresh_before_expiry
         self.blacklist = Blacklist(blacklist_time, backoff_rate)
-        self.cache_refresh_queue = CacheRefreshQueue()
-        self.cache_refresh_evt = asyncio.Event()
-        self.cache_refresh_task = None
+        self._refresher = _CacheRefresher(self, cache_refresh_before_expiry)
+        self._open_lookups: Dict[DHTID, List[_Lookup]] = defaultdict(list)
+        self.is_alive = True
 
+        self._owns_p2p = p2p is None
         if p2p is None:
             if not kwargs.get("use_ipfs"):
                 kwargs["initial_peers"] = initial_peers
             p2p = await P2P.create(**kwargs)
-            self._should_shutdown_p2p = True
-        else:
-            if kwargs:
-                raise ValueError(f"**kwargs in DHTNode.create() should be empty if a P2P instance is provided, got {kwargs}")
-            self._should_shutdown_p2p = False
-        self.p2p = p2p
+        elif kwargs:
+            raise ValueError(f"a P2P instance was given, so DHTNode.create() takes no transport options; got {kwargs}")
+        self.p2p, self.peer_id = p2p, p2p.peer_id
         self.protocol = await DHTProtocol.create(p2p, self.node_id, bucket_size, depth_modulo, num_replicas, wait_timeout,
                                                  parallel_rpc, cache_size, client_mode, record_validator, authorizer)
-        self.peer_id = p2p.peer_id
-
         if initial_peers:
-            initial_peers = {PeerID.from_base58(Multiaddr(item)["p2p"]) for item in initial_peers}
-            bootstrap_timeout = bootstrap_timeout if bootstrap_timeout is not None else wait_timeout
-            start_time = get_dht_time()
-            ping_tasks = set(asyncio.create_task(self.protocol.call_ping(peer, validate=ensure_bootstrap_success, strict=strict))
-                             for peer in initial_peers)
-            finished_pings, unfinished_pings = await asyncio.wait(ping_tasks, return_when=asyncio.FIRST_COMPLETED)
-            if unfinished_pings:  # give the stragglers what is left of the bootstrap budget
-                finished_in_time, stragglers = await asyncio.wait(
-                    unfinished_pings, timeout=max(0.0, bootstrap_timeout - get_dht_time() + start_time))
-                for straggler in stragglers:
-                    straggler.cancel()
-                finished_pings |= finished_in_time
-            if not finished_pings or all(ping.exception() is None and ping.result() is None for ping in finished_pings):
-                message = "DHTNode bootstrap failed: none of the initial_peers responded to the ping."
-                if ensure_bootstrap_success:
-                    raise RuntimeError(f"{message} (set ensure_bootstrap_success=False to ignore)")
-                logger.warning(message)
-            if strict:
-                for task in asyncio.as_completed(finished_pings):
-                    await task  # propagate validation errors
-            # populate the routing table by looking for our own id
-            await asyncio.wait([asyncio.create_task(self.find_nearest_nodes([self.node_id])),
-                                asyncio.create_task(asyncio.sleep(bootstrap_timeout - get_dht_time() + start_time))],
-                               return_when=asyncio.FIRST_COMPLETED)
-        if self.refresh_timeout is not None:
-            spawn(self._refresh_routing_table(period=self.refresh_timeout))
+            budget = wait_timeout if bootstrap_timeout is None else bootstrap_timeout
+            await self._bootstrap({PeerID.from_base58(Multiaddr(addr)["p2p"]) for addr in initial_peers}, budget,
+                                  ensure_bootstrap_success, strict)
+        if refresh_timeout is not None:
+            spawn(self._keep_routing_table_fresh(refresh_timeout))
         return self
 
-    def __init__(self, *, _initialized_with_create: bool = False):
-        assert _initialized_with_create, "use `await DHTNode.create(...)`"
-        super().__init__()
+    async def _bootstrap(self, peers: Set[PeerID], budget: float, must_succeed: bool, strict: bool) -> None:
+        """Ping the initial peers (the first answer unblocks us, the rest get what is left of ``budget``), then look
+        for our own id so that the routing table fills up."""
+        began = get_dht_time()
+        pings = {asyncio.create_task(self.protocol.call_ping(peer, validate=must_succeed, strict=strict)) for peer in peers}
+        answered, waiting = await asyncio.wait(pings, return_when=asyncio.FIRST_COMPLETED)
+        if waiting:
+            more, late = await asyncio.wait(waiting, timeout=max(0.0, began + budget - get_dht_time()))
+            answered |= more
+            for ping in late:
+                ping.cancel()
+        if all(ping.exception() is None and ping.result() is None for ping in answered):
+            complaint = "DHTNode bootstrap failed: none of the initial_peers responded to the ping."
+            if must_succeed:
+                raise RuntimeError(f"{complaint} (set ensure_bootstrap_success=False to ignore)")
+            logger.warning(complaint)
+        if strict:
+            for ping in answered:
+                ping.result()  # a validation error of any initial peer is the caller's business
+        remaining = max(0.0, began + budget - get_dht_time())
+        with_deadline = asyncio.create_task(self.find_nearest_nodes([self.node_id]))
+        await asyncio.wait([with_deadline], timeout=remaining)
 
     async def shutdown(self) -> None:
         self.is_alive = False
-        if self.cache_refresh_task is not None:
-            self.cache_refresh_task.cancel()
+        self._refresher.stop()
         await self.protocol.shutdown()
-        if self._should_shutdown_p2p:
+        if self._owns_p2p:
             await self.p2p.shutdown()
+
+    async def get_visible_maddrs(self, latest: bool = False) -> List[Multiaddr]:
+        return await self.protocol.p2p.get_visible_maddrs(latest=latest)
+
+    # ---------------------------------------------------------------------------------------------- asking peers
+    def _without_banned(self, peers: Dict[DHTID, PeerID]) -> Dict[DHTID, PeerID]:
+        return {node: peer for node, peer in peers.items() if peer not in self.blacklist}
+
+    def _routing_neighbours(self, key_ids: Iterable[DHTID], count: int) -> Dict[DHTID, PeerID]:
+        known: Dict[DHTID, PeerID] = {}
+        for key_id in key_ids:
+            known.update(self.protocol.routing_table.get_nearest_neighbors(key_id, count, exclude=self.node_id))
+        return known
+
+    async def _ask(self, peer: PeerID, key_ids: Collection[DHTID]):
+        """``protocol.call_find`` that respects and feeds the black list; None if the peer is banned or silent."""
+        if peer in self.blacklist:
+            return None
+        reply = await self.protocol.call_find(peer, key_ids)
+        if not reply:
+            self.blacklist.register_failure(peer)
+            return None
+        self.blacklist.register_success(peer)
+        return {key_id: (payload, self._without_banned(neighbours)) for key_id, (payload, neighbours) in reply.items()}
 
     # ---------------------------------------------------------------------------------------------- find nodes
     async def find_nearest_nodes(self, queries: Collection[DHTID], k_nearest: Optional[int] = None,
@@ -243,46 +371,43 @@ class DHTNode:
                                  **kwargs) -> Dict[DHTID, Dict[DHTID, PeerID]]:
         """For every query id, the ``k_nearest`` nodes of the whole DHT nearest to it: ``{query: {node: peer}}``."""
         queries = tuple(queries)
-        k_nearest = k_nearest if k_nearest is not None else self.protocol.bucket_size
-        num_workers = num_workers if num_workers is not None else self.num_workers
-        beam_size = beam_size if beam_size is not None else max(self.protocol.bucket_size, k_nearest)
+        k_nearest = self.protocol.bucket_size if k_nearest is None else k_nearest
+        num_workers = self.num_workers if num_workers is None else num_workers
+        beam_size = max(self.protocol.bucket_size, k_nearest) if beam_size is None else beam_size
         if k_nearest > beam_size:
-            logger.warning("beam_size is too small: the search may miss some of the nearest nodes")
-        if node_to_peer_id is None:
-            node_to_peer_id = {}
-            for query in queries:
-                neighbors = self.protocol.routing_table.get_nearest_neighbors(query, beam_size, exclude=self.node_id)
-                node_to_peer_id.update(self._filter_blacklisted(dict(neighbors)))
+            logger.warning("beam_size is smaller than k_nearest: some of the nearest nodes may be missed")
+        address_of = node_to_peer_id
+        if address_of is None:
+            address_of = self._without_banned(self._routing_neighbours(queries, beam_size))
 
-        async def get_neighbors(peer: DHTID, queries: Collection[DHTID]) -> Dict[DHTID, Tuple[Tuple[DHTID], bool]]:
-            response = await self._call_find_with_blacklist(node_to_peer_id[peer], queries)
-            if not response:
-                return {query: ([], False) for query in queries}
-            output: Dict[DHTID, Tuple[Tuple[DHTID], bool]] = {}
-            for query, (_, peers) in response.items():
-                node_to_peer_id.update(peers)
-                output[query] = tuple(peers.keys()), False  # False: keep searching
-            return output
+        async def visit(node: DHTID, asked: Collection[DHTID]) -> Dict[DHTID, Tuple[Tuple[DHTID], bool]]:
+            reply = await self._ask(address_of[node], asked)
+            if reply is None:
+                return {query: ((), False) for query in asked}
+            hops = {}
+            for query, (_, neighbours) in reply.items():
+                address_of.update(neighbours)
+                hops[query] = (tuple(neighbours), False)  # False: this never ends a search early
+            return hops
 
-        nearest_nodes_per_query, visited_nodes = await traverse_dht(
-            queries, initial_nodes=list(node_to_peer_id), beam_size=beam_size, num_workers=num_workers,
-            queries_per_call=int(len(queries) ** 0.5), get_neighbors=get_neighbors,
+        found, _ = await traverse_dht(
+            queries, initial_nodes=list(address_of), beam_size=beam_size, num_workers=num_workers,
+            queries_per_call=int(len(queries) ** 0.5), get_neighbors=visit,
             visited_nodes={query: {self.node_id} for query in queries}, **kwargs)
-
-        nearest_nodes_with_peer_ids = {}
-        for query, nearest_nodes in nearest_nodes_per_query.items():
-            if not exclude_self:
-                nearest_nodes = sorted(nearest_nodes + [self.node_id], key=query.xor_distance)
-                node_to_peer_id[self.node_id] = self.peer_id
-            nearest_nodes_with_peer_ids[query] = {node: node_to_peer_id[node] for node in nearest_nodes[:k_nearest]}
-        return nearest_nodes_with_peer_ids
+        if not exclude_self:
+            address_of[self.node_id] = self.peer_id
+        nearest: Dict[DHTID, Dict[DHTID, PeerID]] = {}
+        for query, nodes in found.items():
+            nodes = list(nodes) if exclude_self else sorted([*nodes, self.node_id], key=query.xor_distance)
+            nearest[query] = {node: address_of[node] for node in nodes[:k_nearest]}
+        return nearest
 
     # ---------------------------------------------------------------------------------------------- store
     async def store(self, key: DHTKey, value: DHTValue, expiration_time: DHTExpiration,
                     subkey: Optional[Subkey] = None, **kwargs) -> bool:
         """Store one (key, [subkey,] value); True if at least one replica accepted it."""
-        store_ok = await self.store_many([key], [value], [expiration_time], subkeys=[subkey], **kwargs)
-        return store_ok[(key, subkey) if subkey is not None else key]
+        outcome = await self.store_many([key], [value], [expiration_time], subkeys=[subkey], **kwargs)
+        return outcome[key if subkey is None else (key, subkey)]
 
     async def store_many(self, keys: List[DHTKey], values: List[DHTValue],
                          expiration_time: Union[DHTExpiration, List[DHTExpiration]],
@@ -293,307 +418,170 @@ class DHTNode:
             expiration_time = [expiration_time] * len(keys)
         if subkeys is None:
             subkeys = [None] * len(keys)
-        assert len(keys) == len(subkeys) == len(values) == len(expiration_time), "inputs must have equal lengths"
+        if not (len(keys) == len(values) == len(subkeys) == len(expiration_time)):
+            raise ValueError("keys, values, subkeys and expiration times must have equal lengths")
 
-        key_id_to_data: DefaultDict[DHTID, List[Tuple[DHTKey, Subkey, DHTValue, DHTExpiration]]] = defaultdict(list)
+        by_key_id: Dict[DHTID, Tuple[DHTKey, List]] = {}
         for key, subkey, value, expiration in zip(keys, subkeys, values, expiration_time):
-            key_id_to_data[DHTID.generate(source=key)].append((key, subkey, value, expiration))
+            by_key_id.setdefault(DHTID.generate(source=key), (key, []))[1].append((subkey, value, expiration))
+        jobs = {key_id: _Replication(self, key_id, key, records, exclude_self, not await_all_replicas)
+                for key_id, (key, records) in by_key_id.items()}
+        address_of = self._routing_neighbours(jobs, self.protocol.bucket_size)
+        located: Set[DHTID] = set()
 
-        unfinished_key_ids = set(key_id_to_data.keys())
-        store_ok = {(key, subkey): None for key, subkey in zip(keys, subkeys)}
-        store_finished_events = {(key, subkey): asyncio.Event() for key, subkey in zip(keys, subkeys)}
+        async def place(key_id: DHTID, nearest: List[DHTID], _visited: Set[DHTID]) -> None:
+            located.add(key_id)
+            await jobs[key_id].run(nearest, address_of)
 
-        node_to_peer_id: Dict[DHTID, PeerID] = dict()
-        for key_id in unfinished_key_ids:
-            node_to_peer_id.update(self.protocol.routing_table.get_nearest_neighbors(
-                key_id, self.protocol.bucket_size, exclude=self.node_id))
-
-        async def on_found(key_id: DHTID, nearest_nodes: List[DHTID], visited_nodes: Set[DHTID]) -> None:
-            """The nearest nodes to ``key_id`` are known: send store requests to them."""
-            assert key_id in unfinished_key_ids, "internal error: traverse_dht finished the same query twice"
-            assert self.node_id not in nearest_nodes
-            unfinished_key_ids.remove(key_id)
-
-            num_successful_stores = 0
-            pending_store_tasks = set()
-            store_candidates = sorted(nearest_nodes + ([] if exclude_self else [self.node_id]),
-                                      key=key_id.xor_distance, reverse=True)  # pop() takes the nearest
-            [original_key, *_], current_subkeys, current_values, current_expirations = zip(*key_id_to_data[key_id])
-
-            key_bytes = key_id.to_bytes()
-            binary_values = []
-            stored_records = []
-            for subkey, value, expiration in zip(current_subkeys, current_values, current_expirations):
-                subkey_bytes = self.protocol.serializer.dumps(subkey)
-                value_bytes = self.protocol.serializer.dumps(value)
-                if self.protocol.record_validator is not None:
-                    if subkey is None:
-                        subkey_bytes = self.protocol.IS_REGULAR_VALUE
-                    record = DHTRecord(key_bytes, subkey_bytes, value_bytes, expiration)
-                    value_bytes = self.protocol.record_validator.sign_value(record)
-                binary_values.append(value_bytes)
-                stored_records.append((subkey, value_bytes, expiration))
-
-            while num_successful_stores < self.num_replicas and (store_candidates or pending_store_tasks):
-                while store_candidates and num_successful_stores + len(pending_store_tasks) < self.num_replicas:
-                    node_id: DHTID = store_candidates.pop()
-                    if node_id == self.node_id:
-                        num_successful_stores += 1
-                        for subkey, value_bytes, expiration in stored_records:
-                            if self.protocol.record_validator is not None:
-                                subkey_bytes = self.protocol.IS_REGULAR_VALUE if subkey is None else self.protocol.serializer.dumps(subkey)
-                                if not self.protocol.record_validator.validate(DHTRecord(key_bytes, subkey_bytes, value_bytes, expiration)):
-                                    store_ok[original_key, subkey] = False
-                                    store_finished_events[original_key, subkey].set()
-                                    continue
-                            store_ok[original_key, subkey] = self.protocol.storage.store(
-                                key_id, value_bytes, expiration, subkey=subkey)
-                            if not await_all_replicas:
-                                store_finished_events[original_key, subkey].set()
-                    else:
-                        pending_store_tasks.add(asyncio.create_task(self.protocol.call_store(
-                            node_to_peer_id[node_id], keys=[key_id] * len(current_values), values=binary_values,
-                            expiration_time=current_expirations, subkeys=current_subkeys)))
-
-                if pending_store_tasks:
-                    finished_store_tasks, pending_store_tasks = await asyncio.wait(
-                        pending_store_tasks, return_when=asyncio.FIRST_COMPLETED)
-                    for task in finished_store_tasks:
-                        if task.result() is not None:
-                            num_successful_stores += 1
-                            for subkey, store_status in zip(current_subkeys, task.result()):
-                                store_ok[original_key, subkey] = store_status or store_ok[original_key, subkey]
-                                if not await_all_replicas:
-                                    store_finished_events[original_key, subkey].set()
-
-            if self.cache_on_store:
-                self._update_cache_on_store(key_id, current_subkeys, binary_values, current_expirations,
-                                            store_ok=[store_ok[original_key, subkey] for subkey in current_subkeys])
-            for subkey, value_bytes, expiration in stored_records:
-                store_finished_events[original_key, subkey].set()
-
-        store_task = asyncio.create_task(self.find_nearest_nodes(
-            queries=set(unfinished_key_ids), k_nearest=self.num_replicas, node_to_peer_id=node_to_peer_id,
-            found_callback=on_found, exclude_self=exclude_self, **kwargs))
+        search = asyncio.create_task(self.find_nearest_nodes(
+            queries=set(jobs), k_nearest=self.num_replicas, node_to_peer_id=address_of, found_callback=place,
+            exclude_self=exclude_self, **kwargs))
         try:
-            await asyncio.gather(store_task, *(evt.wait() for evt in store_finished_events.values()))
-            assert len(unfinished_key_ids) == 0, "internal error: traverse_dht did not finish the search"
-            return {(key, subkey) if subkey is not None else key: status or False
-                    for (key, subkey), status in store_ok.items()}
-        except asyncio.CancelledError as e:
-            store_task.cancel()
-            raise e
+            await asyncio.gather(search, *(event.wait() for job in jobs.values() for event in job.reported.values()))
+        except asyncio.CancelledError:
+            search.cancel()
+            raise
+        if len(located) != len(jobs):
+            raise RuntimeError("the traversal ended without locating every key")
+        return {(key if subkey is None else (key, subkey)): bool(jobs[key_id].accepted[subkey])
+                for key_id, (key, records) in by_key_id.items() for subkey, _, _ in records}
 
-    def _update_cache_on_store(self, key_id: DHTID, subkeys: List[Subkey], binary_values: List[bytes],
-                               expirations: List[DHTExpiration], store_ok: List[bool]) -> None:
-        """A successful store also refreshes our own cached copy of the key (or invalidates a stale one)."""
-        for subkey, value_bytes, expiration_time, accepted in zip(subkeys, binary_values, expirations, store_ok):
-            if accepted:
-                self.protocol.cache.store(key_id, value_bytes, expiration_time, subkey=subkey)
-                self._schedule_for_refresh(key_id, expiration_time)
-            else:
-                rejected_value, rejected_expiration = self.protocol.cache.get(key_id) or (None, None)
-                if rejected_value is not None and subkey is None and rejected_expiration <= expiration_time:
-                    del self.protocol.cache[key_id]  # somebody holds a newer value: ours is stale
+    def _note_own_store(self, key_id: DHTID, subkeys: List[Subkey], raw_values: List[bytes],
+                        expirations: List[DHTExpiration], accepted: List[Optional[bool]]) -> None:
+        """What we have just stored is also what we would like to read back: refresh our cached copy (or drop a
+        cached value that turned out to be older than what the replicas hold)."""
+        cache = self.protocol.cache
+        for subkey, raw, expiration, ok in zip(subkeys, raw_values, expirations, accepted):
+            if ok:
+                cache.store(key_id, raw, expiration, subkey=subkey)
+                self._refresher.watch(key_id, expiration)
+            elif subkey is None:
+                cached = cache.get(key_id)
+                if cached is not None and cached.value is not None and cached.expiration_time <= expiration:
+                    del cache[key_id]
 
     # ---------------------------------------------------------------------------------------------- get
-    async def get(self, key: DHTKey, latest=False, **kwargs) -> Optional[ValueWithExpiration[DHTValue]]:
+    async def get(self, key: DHTKey, latest=False, **kwargs) -> GetResult:
         """The value under ``key`` (a dict of sub-key -> ValueWithExpiration for dictionaries) or None.
 
         :param latest: visit all nearest nodes and return the freshest value instead of stopping at the first hit
         """
         if latest:
             kwargs["sufficient_expiration_time"] = float("inf")
-        result = await self.get_many([key], **kwargs)
-        return result[key]
+        return (await self.get_many([key], **kwargs))[key]
 
     async def get_many(self, keys: Collection[DHTKey], sufficient_expiration_time: Optional[DHTExpiration] = None,
-                       **kwargs) -> Dict[DHTKey, Union[Optional[ValueWithExpiration[DHTValue]],
-                                                       Awaitable[Optional[ValueWithExpiration[DHTValue]]]]]:
+                       **kwargs) -> Dict[DHTKey, Union[GetResult, Awaitable[GetResult]]]:
         keys = tuple(keys)
-        key_ids = [DHTID.generate(key) for key in keys]
-        id_to_original_key = dict(zip(key_ids, keys))
-        results_by_id = await self.get_many_by_id(key_ids, sufficient_expiration_time, **kwargs)
-        return {id_to_original_key[key]: result_or_future for key, result_or_future in results_by_id.items()}
+        ids = [DHTID.generate(key) for key in keys]
+        by_id = await self.get_many_by_id(ids, sufficient_expiration_time, **kwargs)
+        return {key: by_id[key_id] for key, key_id in zip(keys, ids)}
 
     async def get_many_by_id(self, key_ids: Collection[DHTID], sufficient_expiration_time: Optional[DHTExpiration] = None,
                              num_workers: Optional[int] = None, beam_size: Optional[int] = None,
                              return_futures: bool = False, _is_refresh=False
-                             ) -> Dict[DHTID, Union[Optional[ValueWithExpiration[DHTValue]],
-                                                    Awaitable[Optional[ValueWithExpiration[DHTValue]]]]]:
+                             ) -> Dict[DHTID, Union[GetResult, Awaitable[GetResult]]]:
         """
         :param sufficient_expiration_time: stop as soon as a value expiring at or after this time is found
           (default: any unexpired value); ``float('inf')`` visits every nearest node
         :param return_futures: return ``{key: awaitable}`` immediately instead of waiting for all keys
         """
-        sufficient_expiration_time = sufficient_expiration_time or get_dht_time()
-        beam_size = beam_size if beam_size is not None else self.protocol.bucket_size
-        num_workers = num_workers if num_workers is not None else self.num_workers
-        search_results: Dict[DHTID, _SearchState] = {
-            key_id: _SearchState(key_id, sufficient_expiration_time, serializer=self.protocol.serializer,
-                                 record_validator=self.protocol.record_validator) for key_id in key_ids}
-
-        if not _is_refresh:
-            for key_id in key_ids:
-                search_results[key_id].add_done_callback(self._trigger_cache_refresh)
-
-        # if we have concurrent get request for some of the same keys, subscribe to their results
-        if self.reuse_get_requests:
-            for key_id, search_result in search_results.items():
-                self.pending_get_requests[key_id].add(search_result)
-                search_result.add_done_callback(self._reuse_finished_search_result)
-
-        # stage 1: check local storage and cache
-        for key_id in key_ids:
-            search_results[key_id].add_candidate(self.protocol.storage.get(key_id), source_node_id=self.node_id)
+        horizon = sufficient_expiration_time or get_dht_time()
+        beam_size = self.protocol.bucket_size if beam_size is None else beam_size
+        num_workers = self.num_workers if num_workers is None else num_workers
+        lookups = {key_id: _Lookup(key_id, horizon, self.protocol.serializer, self.protocol.record_validator)
+                   for key_id in key_ids}
+        for lookup in lookups.values():
             if not _is_refresh:
-                search_results[key_id].add_candidate(self.protocol.cache.get(key_id), source_node_id=self.node_id)
+                lookup.future.add_done_callback(lambda _f, lookup=lookup: self._after_cache_hit(lookup))
+            if self.reuse_get_requests:
+                self._open_lookups[lookup.key_id].append(lookup)
+                lookup.future.add_done_callback(lambda _f, lookup=lookup: self._share_with_open_lookups(lookup))
 
-        # stage 2: traverse the DHT for the keys that are still unfinished
-        unfinished_key_ids = [key_id for key_id in key_ids if not search_results[key_id].finished]
-        node_to_peer_id: Dict[DHTID, PeerID] = dict()
-        for key_id in unfinished_key_ids:
-            node_to_peer_id.update(self.protocol.routing_table.get_nearest_neighbors(
-                key_id, self.protocol.bucket_size, exclude=self.node_id))
-        node_to_peer_id = self._filter_blacklisted(node_to_peer_id)
+        # first what this node holds itself ...
+        for key_id, lookup in lookups.items():
+            lookup.offer(self.protocol.storage.get(key_id), origin=self.node_id)
+            if not _is_refresh:
+                lookup.offer(self.protocol.cache.get(key_id), origin=self.node_id)
+        # ... then the network, for the keys that are still open
+        open_ids = [key_id for key_id, lookup in lookups.items() if not lookup.finished]
+        address_of = self._without_banned(self._routing_neighbours(open_ids, self.protocol.bucket_size))
 
-        async def get_neighbors(peer: DHTID, queries: Collection[DHTID]) -> Dict[DHTID, Tuple[Tuple[DHTID], bool]]:
-            queries = list(queries)
-            response = await self._call_find_with_blacklist(node_to_peer_id[peer], queries)
-            if not response:
-                return {query: ([], False) for query in queries}
-            output: Dict[DHTID, Tuple[Tuple[DHTID], bool]] = {}
-            for key_id, (maybe_value_with_expiration, peers) in response.items():
-                node_to_peer_id.update(self._filter_blacklisted(peers))
-                search_results[key_id].add_candidate(maybe_value_with_expiration, source_node_id=peer)
-                output[key_id] = tuple(peers.keys()), search_results[key_id].finished
-            return output
+        async def visit(node: DHTID, asked: Collection[DHTID]) -> Dict[DHTID, Tuple[Tuple[DHTID], bool]]:
+            asked = list(asked)
+            reply = await self._ask(address_of[node], asked)
+            if reply is None:
+                return {key_id: ((), False) for key_id in asked}
+            hops = {}
+            for key_id, (payload, neighbours) in reply.items():
+                address_of.update(neighbours)
+                lookups[key_id].offer(payload, origin=node)
+                hops[key_id] = (tuple(neighbours), lookups[key_id].finished)
+            return hops
 
-        async def found_callback(key_id: DHTID, nearest_nodes: List[DHTID], _visited: Set[DHTID]):
-            search_results[key_id].finish_search()  # finish with whatever we have (possibly nothing)
-            self._cache_new_result(search_results[key_id], nearest_nodes, node_to_peer_id, _is_refresh=_is_refresh)
+        async def exhausted(key_id: DHTID, nearest: List[DHTID], _visited: Set[DHTID]) -> None:
+            lookups[key_id].settle()  # with whatever there is, possibly nothing
+            self._spread_result(lookups[key_id], nearest, address_of, _is_refresh)
 
         spawn(traverse_dht(
-            queries=list(unfinished_key_ids), initial_nodes=list(node_to_peer_id), beam_size=beam_size,
-            num_workers=num_workers, queries_per_call=min(int(len(unfinished_key_ids) ** 0.5), self.chunk_size),
-            get_neighbors=get_neighbors, visited_nodes={key_id: {self.node_id} for key_id in unfinished_key_ids},
-            found_callback=found_callback, await_all_tasks=False))
+            queries=open_ids, initial_nodes=list(address_of), beam_size=beam_size, num_workers=num_workers,
+            queries_per_call=min(int(len(open_ids) ** 0.5), self.chunk_size), get_neighbors=visit,
+            visited_nodes={key_id: {self.node_id} for key_id in open_ids}, found_callback=exhausted,
+            await_all_tasks=False))
 
         if return_futures:
-            return {key_id: search_result.future for key_id, search_result in search_results.items()}
+            return {key_id: lookup.future for key_id, lookup in lookups.items()}
         try:
-            return {key_id: await search_result.future for key_id, search_result in search_results.items()}
-        except asyncio.CancelledError as e:
-            for key_id, search_result in search_results.items():
-                search_result.future.cancel()
-            raise e
+            return {key_id: await lookup.future for key_id, lookup in lookups.items()}
+        except asyncio.CancelledError:
+            for lookup in lookups.values():
+                lookup.future.cancel()
+            raise
 
-    def _reuse_finished_search_result(self, finished: _SearchState) -> None:
-        pending_requests = self.pending_get_requests[finished.key_id]
-        if finished.found_something:
-            search_result = ValueWithExpiration(finished.binary_value, finished.expiration_time)
-            expiration_time_threshold = max(finished.expiration_time, finished.sufficient_expiration_time)
-            # share the result with requests that would be satisfied by it
-            while pending_requests and expiration_time_threshold >= pending_requests[-1].sufficient_expiration_time:
-                pending_requests[-1].add_candidate(search_result, source_node_id=finished.source_node_id)
-                pending_requests[-1].finish_search()
-                pending_requests.pop()
-        else:
-            pending_requests.discard(finished)
+    def _share_with_open_lookups(self, done: _Lookup) -> None:
+        """Concurrent requests for the same key profit from a finished one if its result is fresh enough for them."""
+        others = self._open_lookups[done.key_id]
+        if done in others:
+            others.remove(done)
+        if done.found_something and not done.future.cancelled():
+            good_until = max(done.freshest, done.horizon)
+            while True:  # settling a lookup runs this method again for it, which may shorten the list under us
+                other = next((o for o in others if o.horizon <= good_until), None)
+                if other is None:
+                    break
+                others.remove(other)
+                other.offer(ValueWithExpiration(done.payload, done.freshest), origin=done.origin)
+                other.settle()
+        if not others:
+            self._open_lookups.pop(done.key_id, None)
 
-    async def _call_find_with_blacklist(self, peer_id: PeerID, keys: Collection[DHTID]):
-        """Like ``protocol.call_find`` but skips banned peers and bans the ones that fail."""
-        if peer_id in self.blacklist:
-            return None
-        response = await self.protocol.call_find(peer_id, keys)
-        if response:
-            self.blacklist.register_success(peer_id)
-            return {key: (maybe_value, self._filter_blacklisted(nearest_peers))
-                    for key, (maybe_value, nearest_peers) in response.items()}
-        self.blacklist.register_failure(peer_id)
-        return None
+    def _after_cache_hit(self, lookup: _Lookup) -> None:
+        """A value that was served from our own cache is worth keeping fresh."""
+        if lookup.found_something and lookup.origin == self.node_id and lookup.key_id in self.protocol.cache:
+            self._refresher.watch(lookup.key_id, lookup.freshest)
 
-    def _filter_blacklisted(self, peer_ids: Dict[DHTID, PeerID]) -> Dict[DHTID, PeerID]:
-        return {key: peer for key, peer in peer_ids.items() if peer not in self.blacklist}
-
-    # ---------------------------------------------------------------------------------------------- cache upkeep
-    def _trigger_cache_refresh(self, search: _SearchState) -> None:
-        """A value that came from our cache is scheduled for a background refresh before it expires."""
-        if search.found_something and search.source_node_id == self.node_id:
-            if self.cache_refresh_before_expiry and search.key_id in self.protocol.cache:
-                self._schedule_for_refresh(search.key_id, search.expiration_time)
-
-    def _schedule_for_refresh(self, key_id: DHTID, expiration_time: DHTExpiration) -> None:
-        if self.cache_refresh_before_expiry is None or self.cache_refresh_before_expiry <= 0:
+    def _spread_result(self, lookup: _Lookup, nearest: List[DHTID], address_of: Dict[DHTID, PeerID],
+                       is_refresh: bool) -> None:
+        """After a search: cache the value here and on the nearest node(s) that did not supply it."""
+        if not lookup.found_something:
             return
-        if self.cache_refresh_task is None or self.cache_refresh_task.done() or self.cache_refresh_task.cancelled():
-            self.cache_refresh_task = asyncio.create_task(self._refresh_stale_cache_entries())
-            logger.debug("spawned cache refresh task")
-        earliest_key, earliest_item = self.cache_refresh_queue.top() or (None, None)
-        if earliest_item is None or expiration_time < earliest_item.expiration_time:
-            self.cache_refresh_evt.set()  # the refresher re-computes its wake-up time
-        self.cache_refresh_queue.store(key_id, value=expiration_time, expiration_time=expiration_time)
+        known_until = max([entry.expiration_time for entry in (self.protocol.storage.get(lookup.key_id),
+                                                               self.protocol.cache.get(lookup.key_id)) if entry is not None]
+                          or [float("-inf")])
+        if lookup.freshest <= known_until:
+            return
+        if self.cache_locally or is_refresh:
+            self.protocol.cache.store(lookup.key_id, lookup.payload, lookup.freshest)
+        helpers = [node for node in nearest if node != lookup.origin][:max(self.cache_nearest, 0)]
+        for node in helpers:
+            spawn(self.protocol.call_store(address_of[node], [lookup.key_id], [lookup.payload], [lookup.freshest],
+                                           in_cache=True))
 
-    async def _refresh_stale_cache_entries(self) -> None:
-        """Background task: shortly before a cached entry expires, look the key up again with a later horizon."""
+    # ---------------------------------------------------------------------------------------------- upkeep
+    async def _keep_routing_table_fresh(self, period: float) -> None:
+        """Every ``period`` seconds, look up a random id inside each bucket that nobody touched for that long."""
         while self.is_alive:
-            while len(self.cache_refresh_queue) == 0:
-                await self.cache_refresh_evt.wait()
-                self.cache_refresh_evt.clear()
-            key_id, (_, nearest_refresh_time) = self.cache_refresh_queue.top()
-            try:
-                # wake up earlier if a more urgent entry arrives
-                time_to_wait = nearest_refresh_time - self.cache_refresh_before_expiry - get_dht_time()
-                await asyncio.wait_for(self.cache_refresh_evt.wait(), timeout=time_to_wait)
-                self.cache_refresh_evt.clear()
-                continue
-            except asyncio.TimeoutError:
-                current_time = get_dht_time()
-                keys_to_refresh = {key_id}
-                max_expiration_time = nearest_refresh_time
-                del self.cache_refresh_queue[key_id]
-                while self.cache_refresh_queue and len(keys_to_refresh) < self.chunk_size:
-                    key_id, (_, nearest_refresh_time) = self.cache_refresh_queue.top()
-                    if nearest_refresh_time > current_time + self.cache_refresh_before_expiry:
-                        break
-                    del self.cache_refresh_queue[key_id]
-                    keys_to_refresh.add(key_id)
-                    max_expiration_time = max(max_expiration_time, nearest_refresh_time)
-                sufficient_expiration_time = max_expiration_time + self.cache_refresh_before_expiry + 1
-                await self.get_many_by_id(keys_to_refresh, sufficient_expiration_time, _is_refresh=True)
-
-    def _cache_new_result(self, search: _SearchState, nearest_nodes: List[DHTID],
-                          node_to_peer_id: Dict[DHTID, PeerID], _is_refresh: bool = False) -> None:
-        """After a successful search: cache locally and on the nearest nodes that did not have the value."""
-        if search.found_something:
-            _, storage_expiration_time = self.protocol.storage.get(search.key_id) or (None, -float("inf"))
-            _, cache_expiration_time = self.protocol.cache.get(search.key_id) or (None, -float("inf"))
-            if search.expiration_time > max(storage_expiration_time, cache_expiration_time):
-                if self.cache_locally or _is_refresh:
-                    self.protocol.cache.store(search.key_id, search.binary_value, search.expiration_time)
-                if self.cache_nearest:
-                    num_cached_nodes = 0
-                    for node_id in nearest_nodes:
-                        if node_id == search.source_node_id:
-                            continue
-                        spawn(self.protocol.call_store(
-                            node_to_peer_id[node_id], [search.key_id], [search.binary_value], [search.expiration_time],
-                            in_cache=True))
-                        num_cached_nodes += 1
-                        if num_cached_nodes >= self.cache_nearest:
-                            break
-
-    async def _refresh_routing_table(self, *, period: Optional[float]) -> None:
-        """Periodically look up a random id inside every bucket that has not been touched for ``period`` seconds."""
-        while self.is_alive and period is not None:
-            refresh_time = get_dht_time()
-            staleness_threshold = refresh_time - period
-            stale_buckets = [bucket for bucket in self.protocol.routing_table.buckets
-                             if bucket.last_updated < staleness_threshold]
-            for bucket in stale_buckets:
-                refresh_id = DHTID(random.randint(bucket.lower, bucket.upper - 1))
-                await self.find_nearest_nodes([refresh_id])
-            await asyncio.sleep(max(0.0, period - (get_dht_time() - refresh_time)))
-
-    async def get_visible_maddrs(self, latest: bool = False) -> List[Multiaddr]:
-        return await self.protocol.p2p.get_visible_maddrs(latest=latest)
+            began = get_dht_time()
+            for bucket in [b for b in self.protocol.routing_table.buckets if b.last_updated < began - period]:
+                await self.find_nearest_nodes([DHTID(random.randint(bucket.lower, bucket.upper - 1))])
+            await asyncio.sleep(max(0.0, period - (get_dht_time() - began)))

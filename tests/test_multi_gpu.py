@@ -83,6 +83,54 @@ def test_two_processes_average_over_ipc(tmp_path, codec_name, tol):
             assert rms <= tol * max(spread, 1.0), (codec_name, k, rms)
 
 
+STALL_CHILD = CHILD.replace(
+    'weight = 1.0 + rank',
+    'weight = 1.0\nif rank == world - 1:\n    averager._device_endpoint.fault_publish_half = True  # host-side injection'
+).replace('part_size_bytes=2 ** 16, sender_timeout=5.0', 'part_size_bytes=2 ** 16, sender_timeout=1.0')
+
+
+def test_peer_that_stalls_after_half_of_its_parts_is_excluded_from_the_rest(tmp_path):
+    """The fault variant of the averaging benchmark, injected on the host: the last rank launches its send items only
+    for the first half of the parts it owes, then carries on with its reduce and apply work. The other ranks wait
+    ``sender_timeout`` (1 s) once, ban it, and finish with the survivors' average for the parts it never published;
+    nobody hangs and every process leaves between rounds. NVLS is off and the kernels use plain peer loads."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, REPO_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+               MADDR_FILE=str(tmp_path / "maddrs.json"), OUT_PREFIX=str(tmp_path / "out"), NCCL_NVLS_ENABLE="0")
+    script = tmp_path / "child.py"
+    script.write_text(STALL_CHILD)
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world), "NoCompression"], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outputs.append(out)
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-2000:] for o in outputs)
+    data = [torch.load(str(tmp_path / f"out{r}.pt")) for r in range(world)]
+    stalled = world - 1
+    everybody = [sum(d["original"][k] for d in data) / world for k in range(2)]
+    survivors = [sum(d["original"][k] for r, d in enumerate(data) if r != stalled) / max(world - 1, 1) for k in range(2)]
+    saw_exclusion = False
+    for r, d in enumerate(data):
+        if r == stalled:
+            continue
+        for k in range(2):
+            got = d["result"][k]
+            with_all = (got - everybody[k]).abs() < 1e-4
+            without = (got - survivors[k]).abs() < 1e-4
+            if world == 2:  # the only survivor keeps its own values where the other one never showed up
+                without = (got - d["original"][k]).abs() < 1e-6
+            assert bool((with_all | without).all()), (r, k)
+            saw_exclusion = saw_exclusion or bool((without & ~with_all).any())
+    assert saw_exclusion, "the stalled rank was averaged in everywhere"
+
+
 MOE_CHILD = r'''
 import os, sys, torch
 import torch.distributed as dist
