@@ -47,7 +47,7 @@ class TorchAlbertForMaskedLM(nn.Module):
         self.layers = layers
         self.word = nn.Embedding(vocab, emb)
         self.pos = nn.Embedding(positions, emb)
-        self.type = nn.Embedding(2, emb)
+        self.token_type = nn.Embedding(2, emb)
         self.emb_ln = nn.LayerNorm(emb, eps=eps)
         self.emb_proj = nn.Linear(emb, hidden)
         self.layer = TorchAlbertLayer(hidden, heads, ffn, eps)
@@ -57,7 +57,7 @@ class TorchAlbertForMaskedLM(nn.Module):
 
     def forward(self, input_ids: torch.Tensor, labels: torch.Tensor, masked_positions: torch.Tensor) -> torch.Tensor:
         b, s = input_ids.shape
-        x = self.word(input_ids) + self.pos.weight[:s] + self.type.weight[0]
+        x = self.word(input_ids) + self.pos.weight[:s] + self.token_type.weight[0]
         x = self.emb_proj(self.emb_ln(x))
         for _ in range(self.layers):
             x = self.layer(x)

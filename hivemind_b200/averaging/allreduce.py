@@ -9,12 +9,17 @@ its senders keep their own values for that span. Semantics: hivemind/averaging/a
 
 On a single box with all peers on GPUs the same round is executed by the device butterfly
 (``hivemind_b200.parallel.device_butterfly``) instead; both paths share this file's modes and error types.
+
+The runner has two faces. As a *sender* (``run``) it opens one stream per reducer, feeds it from the part container
+and files the deltas that come back; its own span goes straight into the local reducer. As a *reducer*
+(``rpc_aggregate_part``) it takes one sender's stream, adds every part into the accumulator of that part and answers
+with the delta once all live senders have contributed.
 """
 from __future__ import annotations
 
 import asyncio
 from enum import Enum
-from typing import AsyncIterator, Optional, Sequence, Set, Tuple, Type
+from typing import AsyncIterator, List, Optional, Sequence, Set, Tuple, Type
 
 import torch
 
@@ -28,6 +33,7 @@ from hivemind_b200.utils.asyncio import (achain, aiter_with_timeout, amap_in_exe
 
 GroupID = bytes
 logger = get_logger(__name__)
+_Msg = averaging_pb2.AveragingData
 
 
 class AveragingMode(Enum):
@@ -56,49 +62,46 @@ class AllReduceRunner(ServicerBase):
                  tensors: Sequence[torch.Tensor], weight: Optional[float] = None, ordered_peer_ids: Sequence[PeerID],
                  peer_fractions: Tuple[float, ...], modes: Optional[Sequence[AveragingMode]] = None,
                  sender_timeout: Optional[float] = None, reducer_timeout: Optional[float] = None, **kwargs):
-        self._p2p = p2p
-        self.peer_id = p2p.peer_id
-        assert self.peer_id in ordered_peer_ids, "peer_id is not a part of the group"
-        if reducer_timeout is not None and (sender_timeout is None or reducer_timeout <= sender_timeout):
-            raise ValueError("If reducer_timeout is enabled, sender_timeout must be shorter than reducer_timeout. "
-                             "Otherwise, there is a chance that reducers will be banned while they await senders.")
+        self._p2p, self.peer_id = p2p, p2p.peer_id
+        if self.peer_id not in ordered_peer_ids:
+            raise ValueError("this peer is not a member of the group")
         if not issubclass(servicer_type, ServicerBase):
-            raise TypeError("`servicer_type` is expected to be a ServicerBase subclass")
+            raise TypeError("servicer_type must derive from ServicerBase")
+        if reducer_timeout is not None and (sender_timeout is None or reducer_timeout <= sender_timeout):
+            raise ValueError("reducer_timeout must be longer than sender_timeout: a reducer that is still waiting for a "
+                             "slow sender must not be written off by the other senders")
         self._servicer_type, self._prefix = servicer_type, prefix
-
-        modes = modes or tuple(AveragingMode.CLIENT if frac == 0 else AveragingMode.NODE for frac in peer_fractions)
-        assert len(modes) == len(ordered_peer_ids), "lists have inconsistent length"
-        assert any(mode != AveragingMode.CLIENT for mode in modes), "cannot run allreduce without reducers"
-        for mode, frac in zip(modes, peer_fractions):
-            assert mode != AveragingMode.CLIENT or frac == 0, "client-mode peer should have zero all-reduce fraction"
-        self.modes = modes
-        my_mode = modes[ordered_peer_ids.index(self.peer_id)]
-        if weight is None:
-            weight = float(my_mode != AveragingMode.AUX)
-        self.weight = weight
-
+        if not modes:
+            modes = tuple(AveragingMode.CLIENT if fraction == 0 else AveragingMode.NODE for fraction in peer_fractions)
+        if len(modes) != len(ordered_peer_ids) or len(peer_fractions) != len(ordered_peer_ids):
+            raise ValueError("modes, fractions and peer ids must describe the same members")
+        if all(mode == AveragingMode.CLIENT for mode in modes):
+            raise ValueError("a group of client-mode peers has nobody to reduce")
+        if any(mode == AveragingMode.CLIENT and fraction != 0 for mode, fraction in zip(modes, peer_fractions)):
+            raise ValueError("client-mode peers reduce nothing: their fraction must be 0")
+        self.modes, self.peer_fractions = modes, peer_fractions
         self.group_id, self.ordered_peer_ids = group_id, ordered_peer_ids
-        self.peer_fractions = peer_fractions
         self.sender_timeout, self.reducer_timeout = sender_timeout, reducer_timeout
+        self._my_index = list(ordered_peer_ids).index(self.peer_id)
+        self._i_send = modes[self._my_index] != AveragingMode.AUX
+        self.weight = float(self._i_send) if weight is None else weight
+        self.sender_peer_ids: List[PeerID] = [p for p, mode in zip(ordered_peer_ids, modes) if mode != AveragingMode.AUX]
+
         self._future: asyncio.Future = asyncio.Future()
-        self.all_senders_started = asyncio.Event()
         self.banned_senders: Set[PeerID] = set()
         self.banlock = asyncio.Lock()
-        self.active_senders: Set[PeerID] = set()
-        if my_mode != AveragingMode.AUX:
-            self.active_senders.add(self.peer_id)
-        if len(self.active_senders) == self._count_senders():
-            self.all_senders_started.set()
+        self.active_senders: Set[PeerID] = {self.peer_id} if self._i_send else set()
+        self.all_senders_started = asyncio.Event()
+        self._note_sender_progress()
 
-        self.sender_peer_ids = [peer_id for peer_id, mode in zip(ordered_peer_ids, modes) if mode != AveragingMode.AUX]
-        peer_id_index = self.ordered_peer_ids.index(self.peer_id)
         self.tensor_part_container = TensorPartContainer(tensors, peer_fractions, return_deltas=True, **kwargs)
-        self.parts_for_local_averaging = self.tensor_part_container.get_raw_input_parts(peer_id_index)
+        self.parts_for_local_averaging = self.tensor_part_container.get_raw_input_parts(self._my_index)
         self.tensor_part_reducer = TensorPartReducer(tuple(part.shape for part in self.parts_for_local_averaging),
                                                      len(self.sender_peer_ids))
 
-    def _count_senders(self) -> int:
-        return sum(mode != AveragingMode.AUX for mode in self.modes)
+    def _note_sender_progress(self) -> None:
+        if len(self.active_senders) >= len(self.sender_peer_ids):
+            self.all_senders_started.set()
 
     def __repr__(self) -> str:
         return f"{type(self).__name__}({self.peer_id}, group_size={self.group_size})"
@@ -117,184 +120,171 @@ class AllReduceRunner(ServicerBase):
         return self._servicer_type.get_stub(self._p2p, peer, namespace=self._prefix)
 
     def should_delay_results(self, peer_id: PeerID) -> bool:
-        return self.peer_fractions[self.ordered_peer_ids.index(peer_id)] == 0
+        """Peers that reduce nothing (clients) read results only after they have sent everything."""
+        return self.peer_fractions[list(self.ordered_peer_ids).index(peer_id)] == 0
 
-    # ------------------------------------------------------------------------------------------ driver
+    # ------------------------------------------------------------------------------------------ sender side
     async def run(self) -> AsyncIterator[torch.Tensor]:
         """Run the round; yields ``average - local`` for every local tensor, in order."""
-        pending_tasks = set()
-        if self.tensor_part_container.num_parts_by_peer[self.ordered_peer_ids.index(self.peer_id)] != 0:
-            pending_tasks.add(asyncio.create_task(self._handle_missing_senders()))
+        parts_per_reducer = self.tensor_part_container.num_parts_by_peer
+        helpers = set()
+        if parts_per_reducer[self._my_index] != 0:
+            helpers.add(asyncio.create_task(self._watch_for_absent_senders()))
         try:
-            if len(self.sender_peer_ids) == 0:
-                logger.debug(f"{self} - finished all-reduce early: all peers are auxiliaries ({self.modes})")
-                self.finalize()
-            elif self.peer_id in self.sender_peer_ids:
-                for peer_id, parts in zip(self.ordered_peer_ids, self.tensor_part_container.num_parts_by_peer):
-                    if parts != 0:
-                        pending_tasks.add(asyncio.create_task(self._communicate_with_peer(peer_id)))
-                async for averaged_tensor_delta in self.tensor_part_container.iterate_output_tensors():
-                    yield averaged_tensor_delta
-                self.finalize()
-            else:  # auxiliary peer: only reduce
+            if not self.sender_peer_ids:
+                logger.debug(f"{self}: nothing to average, every member is an auxiliary ({self.modes})")
+            elif self._i_send:
+                for reducer, count in zip(self.ordered_peer_ids, parts_per_reducer):
+                    if count != 0:
+                        helpers.add(asyncio.create_task(self._exchange_with(reducer)))
+                async for delta in self.tensor_part_container.iterate_output_tensors():
+                    yield delta
+            else:  # an auxiliary only reduces
                 await self.tensor_part_reducer.finished.wait()
-                self.finalize()
+            self.finalize()
         except BaseException as e:
             self.finalize(exception=e)
-            for task in pending_tasks:
+            for task in helpers:
                 task.cancel()
             raise
 
-    async def _handle_missing_senders(self) -> None:
-        """Ban senders that have not opened their stream to us within ``sender_timeout``."""
+    async def _watch_for_absent_senders(self) -> None:
+        """Senders that have not opened their stream to us within ``sender_timeout`` are written off."""
         try:
             await asyncio.wait_for(self.all_senders_started.wait(), self.sender_timeout)
         except asyncio.TimeoutError:
-            for peer_id in self.sender_peer_ids:
-                if peer_id not in self.active_senders and peer_id not in self.banned_senders:
-                    await self._ban_sender(peer_id)
+            for peer in self.sender_peer_ids:
+                if peer not in self.active_senders and peer not in self.banned_senders:
+                    await self._ban_sender(peer)
 
-    async def _communicate_with_peer(self, peer_id: PeerID) -> None:
-        """Send our parts of ``peer_id``'s span and collect the averaged deltas."""
-        peer_index = self.ordered_peer_ids.index(peer_id)
-        if peer_id == self.peer_id:
-            sender_index = self.sender_peer_ids.index(peer_id)
-            for part_index, tensor_part in enumerate(self.parts_for_local_averaging):
-                averaged_part = await self.tensor_part_reducer.accumulate_part(sender_index, part_index, tensor_part,
-                                                                               weight=self.weight)
-                self.tensor_part_container.register_processed_part(peer_index, part_index, averaged_part - tensor_part)
+    async def _exchange_with(self, reducer: PeerID) -> None:
+        """Deliver our parts of ``reducer``'s span and file the averaged deltas that come back."""
+        reducer_index = list(self.ordered_peer_ids).index(reducer)
+        container = self.tensor_part_container
+        if reducer == self.peer_id:
+            me_as_sender = self.sender_peer_ids.index(self.peer_id)
+            for part_index, part in enumerate(self.parts_for_local_averaging):
+                average = await self.tensor_part_reducer.accumulate_part(me_as_sender, part_index, part, weight=self.weight)
+                container.register_processed_part(reducer_index, part_index, average - part)
             return
         try:
-            done_sending = asyncio.Event()
-            inputs_aiter = attach_event_on_finished(self._generate_input_for_peer(peer_index), done_sending)
-            stream = await self._get_peer_stub(peer_id).rpc_aggregate_part(inputs_aiter)
-
+            everything_sent = asyncio.Event()
+            outgoing = attach_event_on_finished(self._generate_input_for_peer(reducer_index), everything_sent)
+            incoming = await self._get_peer_stub(reducer).rpc_aggregate_part(outgoing)
             if self.should_delay_results(self.peer_id):
-                await done_sending.wait()  # client-mode peers receive results only after they finished sending
+                await everything_sent.wait()
 
-            part_index = 0
+            def decode(message: _Msg) -> torch.Tensor:
+                if message.code != averaging_pb2.AVERAGED_PART:
+                    raise AllreduceException(f"{reducer} answered {averaging_pb2.MessageCode.Name(message.code)}")
+                return deserialize_torch_tensor(message.tensor_part)
 
-            def _try_deserialize(msg):
-                if msg.code != averaging_pb2.AVERAGED_PART:
-                    raise AllreduceException(f"{peer_id} sent {averaging_pb2.MessageCode.Name(msg.code)}")
-                return deserialize_torch_tensor(msg.tensor_part), msg
-
-            async for delta, msg in amap_in_executor(_try_deserialize, aiter_with_timeout(stream, self.reducer_timeout),
-                                                     max_prefetch=self.tensor_part_container.prefetch):
-                self.tensor_part_container.register_processed_part(peer_index, part_index, delta)
-                part_index += 1
-            if part_index != self.tensor_part_container.num_parts_by_peer[peer_index]:
-                raise AllreduceException(f"peer {peer_id} sent {part_index} parts, but we expected "
-                                         f"{self.tensor_part_container.num_parts_by_peer[peer_index]}")
+            received = 0
+            async for delta in amap_in_executor(decode, aiter_with_timeout(incoming, self.reducer_timeout),
+                                                max_prefetch=container.prefetch):
+                container.register_processed_part(reducer_index, received, delta)
+                received += 1
+            expected = container.num_parts_by_peer[reducer_index]
+            if received != expected:
+                raise AllreduceException(f"{reducer} returned {received} of {expected} parts")
         except BaseException as e:
-            if isinstance(e, Exception):
-                logger.debug(f"Caught {e!r} when communicating to {peer_id}", exc_info=True)
-            self.tensor_part_container.register_failed_reducer(peer_index)
+            container.register_failed_reducer(reducer_index)  # we keep our own values for that span
             if not isinstance(e, Exception):
                 raise
+            logger.debug(f"exchange with reducer {reducer} failed: {e!r}", exc_info=True)
 
     async def _generate_input_for_peer(self, peer_index: int) -> AsyncIterator[averaging_pb2.AveragingData]:
-        parts_aiter = self.tensor_part_container.iterate_input_parts_for(peer_index)
-        first_part = await anext(parts_aiter)
-        yield averaging_pb2.AveragingData(code=averaging_pb2.PART_FOR_AVERAGING, group_id=self.group_id,
-                                          tensor_part=first_part, weight=self.weight)
-        async for part in parts_aiter:
-            yield averaging_pb2.AveragingData(tensor_part=part, weight=self.weight)
+        """The messages we stream to the reducer with this index; only the first carries the group id."""
+        parts = self.tensor_part_container.iterate_input_parts_for(peer_index)
+        yield _Msg(code=averaging_pb2.PART_FOR_AVERAGING, group_id=self.group_id, tensor_part=await anext(parts),
+                   weight=self.weight)
+        async for part in parts:
+            yield _Msg(tensor_part=part, weight=self.weight)
 
     # ------------------------------------------------------------------------------------------ reducer side
     async def rpc_aggregate_part(self, stream: AsyncIterator[averaging_pb2.AveragingData], context: P2PContext
                                  ) -> AsyncIterator[averaging_pb2.AveragingData]:
         """A groupmate streams its parts of our span; answer each part with the averaged delta."""
-        sender_peer_id = context.remote_id
-        if sender_peer_id not in self.sender_peer_ids:
-            yield averaging_pb2.AveragingData(code=averaging_pb2.PROTOCOL_VIOLATION)
+        sender = context.remote_id
+        if sender not in self.sender_peer_ids:
+            yield _Msg(code=averaging_pb2.PROTOCOL_VIOLATION)
             return
-        self.active_senders.add(sender_peer_id)
-        if len(self.active_senders) == len(self.sender_peer_ids):
-            self.all_senders_started.set()
+        self.active_senders.add(sender)
+        self._note_sender_progress()
         try:
-            request: averaging_pb2.AveragingData = await asyncio.wait_for(anext(stream), self.sender_timeout)
-            reason_to_reject = self._check_reasons_to_reject(request, context)
-            if reason_to_reject:
-                yield reason_to_reject
+            opening: _Msg = await asyncio.wait_for(anext(stream), self.sender_timeout)
+            refusal = self._refusal_for(opening)
+            if refusal is not None:
+                yield refusal
                 return
-            if request.code == averaging_pb2.PART_FOR_AVERAGING:
-                sender_index = self.sender_peer_ids.index(sender_peer_id)
-                async for msg in self._accumulate_parts_streaming(achain(as_aiter(request), stream), sender_index):
-                    yield msg
-            else:
-                code = averaging_pb2.MessageCode.Name(request.code)
-                raise AllreduceException(f"{sender_peer_id} sent {code}, but we expected PART_FOR_AVERAGING")
+            if opening.code != averaging_pb2.PART_FOR_AVERAGING:
+                raise AllreduceException(f"{sender} opened with {averaging_pb2.MessageCode.Name(opening.code)}")
+            async for reply in self._reduce_stream(achain(as_aiter(opening), stream), self.sender_peer_ids.index(sender)):
+                yield reply
         except BaseException as e:
-            if isinstance(e, Exception):
-                await self._ban_sender(sender_peer_id)
-                if isinstance(e, (asyncio.TimeoutError, BannedException)):
-                    logger.debug(f"sender {sender_peer_id} was banned: {e!r}")
-                    yield averaging_pb2.AveragingData(code=averaging_pb2.CANCELLED)
-                else:
-                    logger.debug(f"caught {e!r} while reducing parts from {sender_peer_id}", exc_info=True)
-                    yield averaging_pb2.AveragingData(code=averaging_pb2.INTERNAL_ERROR)
-            else:
+            if not isinstance(e, Exception):
                 raise
+            await self._ban_sender(sender)
+            if isinstance(e, (asyncio.TimeoutError, BannedException)):
+                logger.debug(f"sender {sender} is out of this round: {e!r}")
+                yield _Msg(code=averaging_pb2.CANCELLED)
+            else:
+                logger.debug(f"reducing parts of {sender} failed: {e!r}", exc_info=True)
+                yield _Msg(code=averaging_pb2.INTERNAL_ERROR)
 
-    def _check_reasons_to_reject(self, request: averaging_pb2.AveragingData, context: P2PContext
-                                 ) -> Optional[averaging_pb2.AveragingData]:
-        if request.group_id != self.group_id:
-            return averaging_pb2.AveragingData(code=averaging_pb2.BAD_GROUP_ID)
+    def _refusal_for(self, opening: _Msg) -> Optional[_Msg]:
+        if opening.group_id != self.group_id:
+            return _Msg(code=averaging_pb2.BAD_GROUP_ID)
         if self._future.cancelled():
-            return averaging_pb2.AveragingData(code=averaging_pb2.CANCELLED)
+            return _Msg(code=averaging_pb2.CANCELLED)
         if self._future.done():
-            return averaging_pb2.AveragingData(code=averaging_pb2.INTERNAL_ERROR)
+            return _Msg(code=averaging_pb2.INTERNAL_ERROR)
         return None
 
-    async def _accumulate_parts_streaming(self, stream: AsyncIterator[averaging_pb2.AveragingData], sender_index: int):
-        part_index = 0
+    async def _reduce_stream(self, stream: AsyncIterator[_Msg], sender_index: int) -> AsyncIterator[_Msg]:
+        loop = asyncio.get_event_loop()
+        reduced = 0
+
+        def decode(message: _Msg):
+            return deserialize_torch_tensor(message.tensor_part), message.weight, message.tensor_part.compression
+
         try:
-            loop = asyncio.get_event_loop()
-            async for tensor_part, weight, part_compression in amap_in_executor(
-                    lambda msg: (deserialize_torch_tensor(msg.tensor_part), msg.weight, msg.tensor_part.compression),
-                    aiter_with_timeout(stream, self.sender_timeout), max_prefetch=self.tensor_part_container.prefetch):
+            async for part, weight, codec in amap_in_executor(decode, aiter_with_timeout(stream, self.sender_timeout),
+                                                              max_prefetch=self.tensor_part_container.prefetch):
                 try:
-                    averaged_part = await self.tensor_part_reducer.accumulate_part(sender_index, part_index,
-                                                                                   tensor_part, weight=weight)
-                    part_index += 1
+                    average = await self.tensor_part_reducer.accumulate_part(sender_index, reduced, part, weight=weight)
                 except BannedException:
-                    logger.debug(f"Sender {sender_index} is already banned")
+                    logger.debug(f"sender {sender_index} was banned while its part was waiting")
                     break
-                serialized_delta = await loop.run_in_executor(
-                    None, lambda: serialize_torch_tensor(averaged_part - tensor_part, part_compression))
-                yield averaging_pb2.AveragingData(code=averaging_pb2.AVERAGED_PART, tensor_part=serialized_delta)
+                reduced += 1
+                delta = await loop.run_in_executor(None, lambda: serialize_torch_tensor(average - part, codec))
+                yield _Msg(code=averaging_pb2.AVERAGED_PART, tensor_part=delta)
         finally:
-            if part_index != self.tensor_part_reducer.num_parts:
+            if reduced != self.tensor_part_reducer.num_parts:
                 await self._ban_sender(self.sender_peer_ids[sender_index])
 
     async def _ban_sender(self, peer_id: PeerID) -> None:
         async with self.banlock:
-            if peer_id not in self.banned_senders:
-                self.banned_senders.add(peer_id)
-                self.tensor_part_reducer.on_sender_failed(self.sender_peer_ids.index(peer_id))
+            if peer_id in self.banned_senders:
+                return
+            self.banned_senders.add(peer_id)
+            self.tensor_part_reducer.on_sender_failed(self.sender_peer_ids.index(peer_id))
 
     def finalize(self, *, cancel: bool = False, exception: Optional[BaseException] = None) -> bool:
-        """Finish the round, release buffers; returns True if this call changed the state."""
-        assert not cancel or not exception, "finalize accepts either exception or cancel, but not both"
-        pending_tasks = set()
-        if cancel or exception:
-            # tell peers that are still streaming to us that we are out
-            for peer_id, mode in zip(self.ordered_peer_ids, self.modes):
-                if peer_id != self.peer_id and mode != AveragingMode.CLIENT:
-                    pass  # their streams end when our handlers exit; nothing to send explicitly
-        if not self._future.done():
-            if cancel:
-                logger.debug(f"{self} - cancelled")
-                self._future.cancel()
-            elif exception:
-                logger.debug(f"{self} - caught {exception!r}")
-                self._future.set_exception(exception)
-            else:
-                logger.debug(f"{self} - finished")
-                self._future.set_result(None)
-            self.tensor_part_container.finalize()
-            self.tensor_part_reducer.finalize()
-            return True
-        logger.debug(f"{self} - attempted to finalize allreduce that is already finished: {self._future}")
-        return False
+        """Finish the round and release its buffers; returns True if this call changed the state. Streams to and
+        from groupmates end when their handlers see the released containers."""
+        if cancel and exception is not None:
+            raise ValueError("finalize takes cancel or an exception, not both")
+        if self._future.done():
+            logger.debug(f"{self}: already finalized ({self._future})")
+            return False
+        if cancel:
+            self._future.cancel()
+        elif exception is not None:
+            self._future.set_exception(exception)
+        else:
+            self._future.set_result(None)
+        logger.debug(f"{self}: finalized ({'cancelled' if cancel else repr(exception) if exception else 'ok'})")
+        self.tensor_part_container.finalize()
+        self.tensor_part_reducer.finalize()
+        return True

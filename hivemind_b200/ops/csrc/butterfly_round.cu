@@ -18,10 +18,10 @@
 //                          acknowledged that they are done, announces this GPU's round and waits (bounded) for every
 //                          groupmate's announcement, so that the big kernel does not occupy the SMs while a peer is
 //                          still busy elsewhere.
-//   round kernel         : a persistent grid (one 512-thread CTA per SM) that takes work items from a queue in a
+//   round kernel         : a persistent grid (two 256-thread CTAs per SM) that takes work items from a queue in a
 //                          fixed order: send items, then reduce items, then apply items. A CTA that waits for a
 //                          remote flag therefore never delays work that another GPU needs from this one.
-//     send   (part of a groupmate, chunk)  : 16384 values are read ONCE into registers; statistics, quantisation,
+//     send   (part of a groupmate, chunk)  : 8192 values are read ONCE into registers; statistics, quantisation,
 //                          per-bin sums and the record header are computed in the same CTA; the CTA that completes
 //                          a part publishes its flag together with this GPU's weight (64-bit store, release.sys).
 //     reduce (own part, chunk)             : waits (bounded) for the senders' flags; pulls each sender's chunk record
@@ -31,7 +31,7 @@
 //                          senders' vectors and publish the average itself.
 //     apply  (part of a groupmate, chunk)  : waits (bounded) for the owner's flag, x += alpha * decode(delta).
 //
-// Codecs work on chunks: every chunk of 16384 elements carries its own header (mean/std, codebook or block maxima),
+// Codecs work on chunks: every chunk of 8192 elements carries its own header (mean/std, codebook or block maxima),
 // which is what lets a CTA finish a chunk without a second launch. Records never leave this box.
 //
 // Buffers that other GPUs read (outbox, delta box, averages, flags) exist twice and alternate with the parity of
@@ -41,9 +41,10 @@
 #include "hb_codec.cuh"
 
 #define HR_MAX_PEERS 16
-#define HR_CHUNK 16384
-#define HR_THREADS 512
-#define HR_ROWS 8              // float4 groups per thread and chunk: 8 * 4 * 512 = 16384
+#define HR_CHUNK 8192
+#define HR_THREADS 256
+#define HR_ROWS 8              // float4 groups per thread and chunk: 8 * 4 * 256 = 8192
+#define HR_BLOCKS (HR_CHUNK / HB_BLOCK)   // block-wise quantization blocks per chunk
 #define HR_SAMPLE 2048         // sample size for quantile borders
 #define HR_RING 8              // acknowledgement ring entries
 
@@ -75,6 +76,7 @@ struct HrRound {
   int item_begin, item_end, queue_slot, final_stage;
   // per-round local scratch, all zero between rounds (the last CTA of a round clears it)
   int* include;                // [max_local_parts][HR_MAX_PEERS] 0 undecided, 1 / 3 included (parity 0 / 1), 2 left out
+  float* weights;              // [max_local_parts][HR_MAX_PEERS] weight of an included sender (written before its decision)
   int* apply_decision;         // [n_parts] same encoding
   int* ban;                    // [HR_MAX_PEERS]
   unsigned long long* t_start; // [2] start of the reduce / apply phase on this GPU
@@ -107,7 +109,7 @@ __host__ __device__ inline int hr_header_bytes(int codec) {
     case HB_MEANSTD16: return 16;
     case HB_QUANTILE8:
     case HB_UNIFORM8: return 1024;
-    case HB_BLOCKWISE8: return 16;   // four block maxima
+    case HB_BLOCKWISE8: return 16;   // block maxima (HR_BLOCKS floats, padded to 16 bytes)
     default: return 0;
   }
 }
@@ -133,8 +135,8 @@ struct HrShared {
   float red[4][HR_THREADS / 32];        // up to four simultaneous block reductions
   float cb[256];                        // codebook of the record being decoded
   float table[256];                     // borders (quantile) or code midpoints (block-wise) for bucketize
-  float hsum[8][256];                   // per warp-pair bin sums and counts: a skewed distribution would otherwise
-  int hcnt[8][256];                     //   serialise the whole CTA on a handful of addresses
+  float hsum[HR_THREADS / 64][256];     // per warp-pair bin sums and counts: a skewed distribution would otherwise
+  int hcnt[HR_THREADS / 64][256];       //   serialise the whole CTA on a handful of addresses
   float smp[HR_SAMPLE];
   float w[HR_MAX_PEERS];
   int inc[HR_MAX_PEERS];
@@ -257,7 +259,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
     // HB_UNIFORM8: 256 levels of width 6 sigma / 256 around the mean; the codebook holds the mean of every level
     const float scale = 6.f * sqrtf(s2[0] / fmaxf((float)n - 1.f, 1.f)) / 256.f;
     const float inv = (scale > 0.f && isfinite(scale)) ? 1.f / scale : 1.f;
-    for (int i = threadIdx.x; i < 8 * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
+    for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
     __syncthreads();
     const int hw = threadIdx.x >> 6;
 #pragma unroll
@@ -281,7 +283,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       float total = 0.f;
       int count = 0;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) { total += sh.hsum[w][threadIdx.x]; count += sh.hcnt[w][threadIdx.x]; }
+      for (int w = 0; w < HR_THREADS / 64; ++w) { total += sh.hsum[w][threadIdx.x]; count += sh.hcnt[w][threadIdx.x]; }
       reinterpret_cast<float*>(rec)[threadIdx.x] = total / (float)(count > 0 ? count : 1);
     }
     return;
@@ -292,7 +294,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
     while (stride * HR_SAMPLE < n) stride <<= 1;
     const int S = (n + stride - 1) / stride;
     for (int i = threadIdx.x; i < HR_SAMPLE; i += HR_THREADS) sh.smp[i] = INFINITY;
-    for (int i = threadIdx.x; i < 8 * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
+    for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
@@ -345,29 +347,30 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       float total = 0.f;
       int count = 0;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) { total += sh.hsum[w][threadIdx.x]; count += sh.hcnt[w][threadIdx.x]; }
+      for (int w = 0; w < HR_THREADS / 64; ++w) { total += sh.hsum[w][threadIdx.x]; count += sh.hcnt[w][threadIdx.x]; }
       reinterpret_cast<float*>(rec)[threadIdx.x] = total / (float)(count > 0 ? count : 1);
     }
     return;
   }
-  // HB_BLOCKWISE8: rows 2b and 2b + 1 of every thread belong to block b (4096 elements)
+  // HB_BLOCKWISE8: rows [b * RPB, (b + 1) * RPB) of every thread belong to block b (4096 elements)
   {
-    float m[4];
+    constexpr int RPB = HR_ROWS / HR_BLOCKS;
+    float m[HR_BLOCKS];
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
+    for (int b = 0; b < HR_BLOCKS; ++b) {
       m[b] = 0.f;
 #pragma unroll
-      for (int rr = 0; rr < 2; ++rr)
+      for (int rr = 0; rr < RPB; ++rr)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) m[b] = fmaxf(m[b], fabsf(v[2 * b + rr][k]));
+        for (int k = 0; k < 4; ++k) m[b] = fmaxf(m[b], fabsf(v[RPB * b + rr][k]));
     }
     if (threadIdx.x < 256) sh.table[threadIdx.x] = code_tables[256 + threadIdx.x];
-    hr_block_reduce<4, true>(m, sh);   // also orders the table writes before the reads below
-    if (threadIdx.x < 4) reinterpret_cast<float*>(rec)[threadIdx.x] = m[threadIdx.x];
+    hr_block_reduce<HR_BLOCKS, true>(m, sh);   // also orders the table writes before the reads below
+    if (threadIdx.x < HR_BLOCKS) reinterpret_cast<float*>(rec)[threadIdx.x] = m[threadIdx.x];
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
-      const float inv = 1.f / fmaxf(m[r >> 1], 1.17549435e-38f);
+      const float inv = 1.f / fmaxf(m[r / RPB], 1.17549435e-38f);
       unsigned char q[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) q[k] = (unsigned char)hb_bucketize(sh.table, v[r][k] * inv);
@@ -379,7 +382,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
 // Load what decoding a chunk record needs besides the payload: the codebook into shared memory, scalars into
 // registers. Every thread calls this; it ends with a barrier.
 __device__ __forceinline__ void hr_decode_setup(int codec, const unsigned char* rec, HrShared& sh, const float* code_tables,
-                                                float& mean, float& sd, float absmax[4]) {
+                                                float& mean, float& sd, float absmax[HR_BLOCKS]) {
   mean = 0.f;
   sd = 1.f;
   __syncthreads();   // the previous user of sh.cb is done
@@ -391,41 +394,59 @@ __device__ __forceinline__ void hr_decode_setup(int codec, const unsigned char* 
   } else if (codec == HB_BLOCKWISE8) {
     if (threadIdx.x < 256) sh.cb[threadIdx.x] = code_tables[threadIdx.x];
 #pragma unroll
-    for (int b = 0; b < 4; ++b) absmax[b] = reinterpret_cast<const float*>(rec)[b];
+    for (int b = 0; b < HR_BLOCKS; ++b) absmax[b] = reinterpret_cast<const float*>(rec)[b];
   }
   __syncthreads();
 }
 
+__device__ __forceinline__ int hr_ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int hr_cas_release_gpu(int* p, int expected, int desired) {
+  int old;
+  asm volatile("atom.release.gpu.global.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(p), "r"(expected), "r"(desired) : "memory");
+  return old;
+}
+
 // Bounded wait for a flag that a groupmate publishes in one of its two flag sets. Thread 0 polls; the outcome goes
 // into `decision` by compare-and-swap so that all CTAs that work on the same part agree: 1 / 3 = published (in flag
-// set 0 / 1), 2 = gave up. The winning flag is then read (again) with acquire semantics by this CTA, which is what
-// orders this CTA's reads of the groupmate's data after the groupmate's writes; its value is returned in *value.
+// set 0 / 1), 2 = gave up. Only the first CTA to get here talks to the groupmate: it reads the flag with
+// acquire.sys, notes the weight the flag carries in `weight_slot` and publishes the decision with release.gpu; every
+// later CTA reads the decision with acquire.gpu, which orders its reads of the groupmate's data after the
+// groupmate's writes just the same (the chain of release / acquire pairs is cumulative) at the price of a local load.
 __device__ int hr_wait_decide(const unsigned long long* flag0, const unsigned long long* flag1, bool wide, unsigned int want,
-                              int* decision, const int* ban_flag, unsigned long long deadline_ns, HrShared& sh,
-                              unsigned long long* value) {
+                              int* decision, float* weight_slot, const int* ban_flag, unsigned long long deadline_ns,
+                              HrShared& sh, float* weight) {
   if (threadIdx.x == 0) {
     auto load = [&](const unsigned long long* f) -> unsigned long long {
       return wide ? hr_ld_acquire_sys_u64(f) : (unsigned long long)hm_ld_acquire_sys(reinterpret_cast<const unsigned int*>(f));
     };
-    int d = *reinterpret_cast<volatile int*>(decision);
+    int d = hr_ld_acquire_gpu(decision);
     while (d == 0) {
-      const unsigned int v0 = (unsigned int)load(flag0), v1 = (unsigned int)load(flag1);
-      if (v0 == want) atomicCAS(decision, 0, 1);
-      else if (v1 == want) atomicCAS(decision, 0, 3);
-      else if (v0 == (want | HB_FAIL_BIT) || v1 == (want | HB_FAIL_BIT) ||
+      const unsigned long long v0 = load(flag0), v1 = load(flag1);
+      int verdict = 0;
+      if ((unsigned int)v0 == want) verdict = 1;
+      else if ((unsigned int)v1 == want) verdict = 3;
+      else if ((unsigned int)v0 == (want | HB_FAIL_BIT) || (unsigned int)v1 == (want | HB_FAIL_BIT) ||
                (ban_flag && *reinterpret_cast<const volatile int*>(ban_flag)) || hm_globaltimer_ns() > deadline_ns)
-        atomicCAS(decision, 0, 2);
-      else __nanosleep(200);
-      d = *reinterpret_cast<volatile int*>(decision);
+        verdict = 2;
+      if (verdict == 0) {
+        __nanosleep(200);
+      } else {
+        if (verdict != 2 && weight_slot != nullptr)
+          *weight_slot = __uint_as_float((unsigned int)((verdict == 1 ? v0 : v1) >> 32));
+        hr_cas_release_gpu(decision, 0, verdict);
+      }
+      d = hr_ld_acquire_gpu(decision);
     }
-    unsigned long long val = 0;
-    if (d == 1 || d == 3) val = load(d == 1 ? flag0 : flag1);
     sh.bcast = d;
-    sh.bcast64 = val;
+    sh.bcast64 = (weight_slot != nullptr && d != 2) ? (unsigned long long)__float_as_uint(*reinterpret_cast<volatile float*>(weight_slot)) : 0ull;
   }
   __syncthreads();
   const int out = sh.bcast;
-  *value = sh.bcast64;
+  *weight = __uint_as_float((unsigned int)sh.bcast64);
   __syncthreads();
   return out;
 }
@@ -440,13 +461,14 @@ __device__ __forceinline__ unsigned long long hr_phase_start(unsigned long long*
   return t;
 }
 
-// The CTA that completes the last chunk publishes the flag. Writes of all chunks happen-before the flag: every
-// CTA fences before its increment, and the publishing thread fences between its increment and the release store.
+// The CTA that completes the last chunk publishes the flag. Writes of all chunks happen-before the flag: thread 0
+// of every CTA fences (after a CTA barrier) before its increment, and the publishing thread fences between its
+// increment and the release store.
 __device__ __forceinline__ bool hr_chunk_done(int* counter, int n_chunks) {
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // every thread's writes of this chunk are ordered before thread 0's fence (CTA-scope barrier)
   bool last = false;
   if (threadIdx.x == 0) {
+    __threadfence_system();   // cumulative: makes the whole CTA's writes visible before the count moves
     last = atomicAdd(counter, 1) == n_chunks - 1;
     if (last) __threadfence_system();
   }
@@ -499,12 +521,13 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c, HrShared& sh) {
     }
     const unsigned long long* f0 = reinterpret_cast<const unsigned long long*>(g.base[s] + g.lay.ready[0]) + p;
     const unsigned long long* f1 = reinterpret_cast<const unsigned long long*>(g.base[s] + g.lay.ready[1]) + p;
-    unsigned long long val;
-    const int d = hr_wait_decide(f0, f1, true, g.epoch, g.include + (size_t)j * HR_MAX_PEERS + s, g.ban + s, deadline, sh, &val);
+    float w_s;
+    const size_t slot = (size_t)j * HR_MAX_PEERS + s;
+    const int d = hr_wait_decide(f0, f1, true, g.epoch, g.include + slot, g.weights + slot, g.ban + s, deadline, sh, &w_s);
     if (threadIdx.x == 0) {
       sh.inc[s] = (d == 1 || d == 3);
       sh.par[s] = d >> 1;
-      sh.w[s] = __uint_as_float((unsigned int)(val >> 32));
+      sh.w[s] = w_s;
       if (d == 2) {
         atomicExch(g.ban + s, 1);   // a sender that missed one part is left out of the later ones too
         atomicOr(g.status, 1ull << s);
@@ -569,11 +592,11 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c, HrShared& sh) {
     // compressed: pull the sender's chunk record once, keep a copy where its delta will be written
     const unsigned char* remote = g.base[s] + g.lay.outbox[sh.par[s]] + part.enc_off + (long long)c * stride;
     unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
-    float mean, sd, absmax[4] = {1.f, 1.f, 1.f, 1.f};
+    float mean, sd, absmax[HR_BLOCKS] = {};
     hr_decode_setup(codec, remote, sh, g.code, mean, sd, absmax);
     if (hdr == 1024) {
       if (threadIdx.x < 256) reinterpret_cast<float*>(local)[threadIdx.x] = sh.cb[threadIdx.x];
-    } else if (hdr == 16 && threadIdx.x < 4) {
+    } else if (hdr == 16 && threadIdx.x < 4) {   // mean / std or block maxima: one 16-byte header
       reinterpret_cast<float*>(local)[threadIdx.x] = reinterpret_cast<const float*>(remote)[threadIdx.x];
     }
     if (hb_elem_bytes(codec) == 2) {
@@ -595,7 +618,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c, HrShared& sh) {
 #pragma unroll
       for (int r = 0; r < HR_ROWS; ++r) {
         *reinterpret_cast<uchar4*>(local + hdr + hr_elem(r)) = raw[r];
-        const float a = codec == HB_BLOCKWISE8 ? absmax[r >> 1] : 1.f;
+        const float a = codec == HB_BLOCKWISE8 ? absmax[r / (HR_ROWS / HR_BLOCKS)] : 1.f;
         acc[r][0] = fmaf(w, sh.cb[raw[r].x] * a, acc[r][0]); acc[r][1] = fmaf(w, sh.cb[raw[r].y] * a, acc[r][1]);
         acc[r][2] = fmaf(w, sh.cb[raw[r].z] * a, acc[r][2]); acc[r][3] = fmaf(w, sh.cb[raw[r].w] * a, acc[r][3]);
       }
@@ -633,7 +656,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c, HrShared& sh) {
     if (s == me || !g.sends[s]) continue;
     if (codec != HB_NONE && sh.inc[s] && !dead) {
       unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
-      float mean, sd, absmax[4] = {1.f, 1.f, 1.f, 1.f};
+      float mean, sd, absmax[HR_BLOCKS] = {};
       hr_decode_setup(codec, local, sh, g.code, mean, sd, absmax);
       float d[HR_ROWS][4];
 #pragma unroll
@@ -665,9 +688,9 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c, HrShared& sh) {
   const size_t fidx = (size_t)me * g.max_local_parts + part.local_idx;
   const unsigned int* f0 = reinterpret_cast<const unsigned int*>(g.base[owner] + g.lay.dready[0]) + fidx;
   const unsigned int* f1 = reinterpret_cast<const unsigned int*>(g.base[owner] + g.lay.dready[1]) + fidx;
-  unsigned long long val;
+  float unused;
   const int d = hr_wait_decide(reinterpret_cast<const unsigned long long*>(f0), reinterpret_cast<const unsigned long long*>(f1),
-                               false, g.epoch, g.apply_decision + p, nullptr, deadline, sh, &val);
+                               false, g.epoch, g.apply_decision + p, nullptr, nullptr, deadline, sh, &unused);
   if (d == 2) {
     if (threadIdx.x == 0) {
       atomicOr(g.status + 1, 1ull << owner);
@@ -703,7 +726,7 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c, HrShared& sh) {
   const long long stride = hr_chunk_stride(codec);
   const int hdr = hr_header_bytes(codec);
   const unsigned char* rec = g.base[owner] + g.lay.deltabox[opar] + (size_t)me * g.delta_stride + part.span_off + (long long)c * stride;
-  float mean, sd, absmax[4] = {1.f, 1.f, 1.f, 1.f};
+  float mean, sd, absmax[HR_BLOCKS] = {};
   hr_decode_setup(codec, rec, sh, g.code, mean, sd, absmax);
   float dv[HR_ROWS][4];
 #pragma unroll
@@ -723,14 +746,12 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c, HrShared& sh) {
   }
 }
 
-__global__ void __launch_bounds__(HR_THREADS, 1) hr_round_kernel(const __grid_constant__ HrRound g) {
+__global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_constant__ HrRound g) {
   __shared__ HrShared sh;
-  for (;;) {
+  // Items are dealt round-robin. The list is ordered send, reduce, apply, so every CTA finishes its send items
+  // before it may wait for a groupmate, and nothing that a groupmate needs from this GPU queues up behind a wait.
+  for (int idx = g.item_begin + (int)blockIdx.x; idx < g.item_end; idx += (int)gridDim.x) {
     __syncthreads();
-    if (threadIdx.x == 0) sh.item = g.item_begin + atomicAdd(g.queue + g.queue_slot, 1);
-    __syncthreads();
-    const int idx = sh.item;
-    if (idx >= g.item_end) break;
     const int4 it = g.items[idx];
     if (idx < g.n_send) hr_send_item(g, it.x, it.y, it.z, sh);
     else if (idx < g.n_send + g.n_reduce) hr_reduce_item(g, it.x, it.y, sh);
@@ -745,10 +766,7 @@ __global__ void __launch_bounds__(HR_THREADS, 1) hr_round_kernel(const __grid_co
   }
   __syncthreads();
   if (!sh.bcast) return;
-  if (threadIdx.x == 0) {
-    g.queue[3] = 0;
-    g.queue[g.queue_slot] = 0;
-  }
+  if (threadIdx.x == 0) g.queue[3] = 0;
   if (!g.final_stage) return;
   __threadfence();
   if (threadIdx.x < 4) g.status_out[threadIdx.x] = *reinterpret_cast<volatile unsigned long long*>(g.status + threadIdx.x);
@@ -774,10 +792,17 @@ __global__ void __launch_bounds__(32) hr_gate_kernel(const __grid_constant__ HrG
     const unsigned int* ring = reinterpret_cast<const unsigned int*>(g.prev_base[t] + g.lay.done_ring);
     acked = false;
     for (;;) {
-      for (int k = 0; k < HR_RING; ++k) acked |= hm_ld_acquire_sys(ring + k) == g.prev_epoch;
+      // the whole ring in two 16-byte loads; the acknowledgement only has to precede this GPU's later writes, which
+      // the fence after the loop takes care of
+      uint4 lo, hi;
+      asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w) : "l"(ring));
+      asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(ring + 4));
+      const unsigned int e = g.prev_epoch;
+      acked = lo.x == e || lo.y == e || lo.z == e || lo.w == e || hi.x == e || hi.y == e || hi.z == e || hi.w == e;
       if (acked || hm_globaltimer_ns() - t0 > g.ack_timeout_ns) break;
       __nanosleep(500);
     }
+    __threadfence_system();
   }
   const unsigned int missing_ack = __ballot_sync(0xffffffffu, !acked);
   // 2. announce this GPU's round, then wait for everybody else's announcement
@@ -791,7 +816,9 @@ __global__ void __launch_bounds__(32) hr_gate_kernel(const __grid_constant__ HrG
     present = false;
     const unsigned long long t1 = hm_globaltimer_ns();
     for (;;) {
-      present = hm_ld_acquire_sys(hello) == g.epoch || hm_ld_acquire_sys(hello + 1) == g.epoch;
+      uint2 both;   // the flags of both parities at once
+      asm volatile("ld.acquire.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(both.x), "=r"(both.y) : "l"(hello) : "memory");
+      present = both.x == g.epoch || both.y == g.epoch;
       if (present || hm_globaltimer_ns() - t1 > g.hello_timeout_ns) break;
       __nanosleep(500);
     }

@@ -49,7 +49,7 @@ DEBUG_CHECKS = os.environ.get("HIVEMIND_B200_DEBUG", "0") == "1"
 EXIT_GRACE_SECONDS = 2.0  # how long after a round peers may still read this arena (see DeviceEndpoint.close)
 MAX_PEERS = 16
 ALIGN = 16  # elements: tensor starts and part boundaries are multiples of this, so every access is 16-byte aligned
-CHUNK = 16384  # elements per chunk record (HR_CHUNK in butterfly_round.cu)
+CHUNK = 8192  # elements per chunk record (HR_CHUNK in butterfly_round.cu)
 ACK_RING = 8
 DELTA_BOX_FACTOR = 1.5  # delta box capacity relative to the outbox: 1.0 suffices for equal spans
 _CODEC_IDS = {NoCompression: 0, ScaledFloat16Compression: 1, Float16Compression: 2, Quantile8BitQuantization: 3,
@@ -97,7 +97,8 @@ class _HrRound(ctypes.Structure):
                 ("items", ctypes.c_void_p), ("pub_list", ctypes.c_void_p), ("n_send", ctypes.c_int),
                 ("n_reduce", ctypes.c_int), ("n_apply", ctypes.c_int), ("item_begin", ctypes.c_int),
                 ("item_end", ctypes.c_int), ("queue_slot", ctypes.c_int), ("final_stage", ctypes.c_int),
-                ("include", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p),
+                ("include", ctypes.c_void_p), ("weights", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p),
+                ("ban", ctypes.c_void_p),
                 ("t_start", ctypes.c_void_p), ("status", ctypes.c_void_p), ("status_out", ctypes.c_void_p),
                 ("part_done", ctypes.c_void_p), ("dpart_done", ctypes.c_void_p), ("queue", ctypes.c_void_p),
                 ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint)]
@@ -463,7 +464,7 @@ class DeviceEndpoint:
         pub_dev = torch.tensor(pub_list if pub_list else [0], dtype=torch.int32).to(self.device)
         parts_dev = torch.from_numpy(table.view(np.uint8).copy()).to(self.device)
         slots = MAX_PEERS * max_local
-        sizes = [("include", slots * 4), ("dpart_done", slots * 4), ("apply_decision", n_parts * 4),
+        sizes = [("include", slots * 4), ("weights", slots * 4), ("dpart_done", slots * 4), ("apply_decision", n_parts * 4),
                  ("part_done", n_parts * 4), ("ban", MAX_PEERS * 4), ("t_start", 16), ("status", 32), ("queue", 16)]
         total = sum((b + 255) // 256 * 256 for _, b in sizes)
         blob = torch.zeros(total, dtype=torch.uint8, device=self.device)
@@ -514,7 +515,7 @@ class DeviceEndpoint:
         g.parts, g.items, g.pub_list = plan.parts_dev.data_ptr(), plan.items_dev.data_ptr(), plan.pub_dev.data_ptr()
         g.n_send, g.n_reduce, g.n_apply = plan.n_send, plan.n_reduce, plan.n_apply
         g.item_begin, g.item_end, g.queue_slot, g.final_stage = 0, plan.n_send + plan.n_reduce + plan.n_apply, 0, 1
-        for name in ("include", "apply_decision", "ban", "t_start", "status", "part_done", "dpart_done", "queue"):
+        for name in ("include", "weights", "apply_decision", "ban", "t_start", "status", "part_done", "dpart_done", "queue"):
             setattr(g, name, plan.scratch[name].data_ptr())
         g.status_out = self._status_out.data_ptr()
         g.code = self._code.data_ptr()
@@ -542,7 +543,7 @@ class DeviceEndpoint:
         if end <= begin and not final:
             return
         with torch.cuda.device(self.device):
-            code = self.lib.hm_br_round(ctypes.byref(g), self._sms, stream)
+            code = self.lib.hm_br_round(ctypes.byref(g), 2 * self._sms, stream)
         _lib.check(code, f"hm_br_round({name})")
         if self.launch_hook is not None:
             self.launch_hook(name)  # benchmarks record an event after every launch of a round
