@@ -203,20 +203,34 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
                                        group_id=f"w{size_mb}{codec_name}{i}".encode())
                 torch.cuda.synchronize()
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                total_ms = 0.0
+                total_ms, stage_ms = 0.0, {}
                 for i in range(rounds):
                     for e in endpoints:
                         e.tensor_views[0].normal_()  # fresh values every round (see _time_rounds)
+                    marks = []
+
+                    def mark(name, marks=marks):  # rank 0's launches: device time of each stage kernel by itself
+                        marks.append((name, torch.cuda.Event(enable_timing=True)))
+                        marks[-1][1].record()
+
+                    endpoints[0].launch_hook = mark
                     start.record()
                     run_group_emulated(endpoints, weights=[1.0] * n, peer_fractions=[1.0 / n] * n,
                                        group_id=f"t{size_mb}{codec_name}{i}".encode())
                     stop.record()
                     torch.cuda.synchronize()
+                    endpoints[0].launch_hook = None
                     total_ms += start.elapsed_time(stop)
+                    previous = start
+                    for name, event in marks:
+                        stage_ms.setdefault(name + "_ms", []).append(previous.elapsed_time(event))
+                        previous = event
                 ms = total_ms / rounds / n  # n ranks share one GPU: per-rank share of the time
                 for e in endpoints:
                     e.close()
-                stages = None
+                # time from the previous mark to the end of each of rank 0's launches; "send" follows the round's
+                # start directly, "reduce" and "apply" also contain the other ranks' launches of the stage before
+                stages = {name: sum(v) / len(v) for name, v in stage_ms.items()}
             nbytes = numel * 4
             bus = 2 * (n - 1) / n * nbytes / (ms / 1e3) / 1e9
             row = {"size_mb": size_mb, "codec": codec_name, "n_ranks": n, "ms_per_round": ms, "bus_gb_s": bus,

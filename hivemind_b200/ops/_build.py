@@ -24,9 +24,9 @@ CSRC_DIR = OPS_DIR / "csrc"
 KERNELS_SO = OPS_DIR / "libhm_kernels.so"
 NATIVE_DIR = OPS_DIR.parent / "native"
 DAEMON_BIN = NATIVE_DIR / "hmp2pd"
-HOSTLIB_SO = NATIVE_DIR / "libhm_host.so"
 
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+PRECISE_SOURCES = ("multi_tensor", "codec", "butterfly_round", "powersgd")
 
 
 def _find_nvcc() -> Optional[str]:
@@ -64,8 +64,7 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
         raise RuntimeError("nvcc not found; cannot build libhm_kernels.so")
     build_dir = OPS_DIR / "build"
     build_dir.mkdir(exist_ok=True)
-    common = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
-              "-I", str(CSRC_DIR)]
+    common = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-I", str(CSRC_DIR)]
     if ptxas_info:
         common += ["-Xptxas", "-v"]
     procs = []
@@ -75,7 +74,10 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
         objects.append(obj)
         if not force and not _stale(obj, [src] + headers):
             continue
-        cmd = common + ["-c", str(src), "-o", str(obj)]
+        # optimizer updates and codecs keep IEEE division, square roots and denormals (they are compared with, and
+        # interoperate with, plain PyTorch math); the tensor-core and activation kernels take the fast intrinsics
+        fast_math = [] if src.stem in PRECISE_SOURCES else ["--use_fast_math"]
+        cmd = common + fast_math + ["-c", str(src), "-o", str(obj)]
         if verbose:
             print(" ".join(cmd), flush=True)
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -90,16 +92,12 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
 
 
 def build_daemon(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the C++ transport daemon and the host runtime library."""
+    """Compile the C++ transport daemon."""
     cxx = shutil.which("g++") or "g++"
     daemon_src = sorted(NATIVE_DIR.glob("hmp2pd*.cpp"))
     headers = sorted(NATIVE_DIR.glob("*.h"))
     if daemon_src and (force or _stale(DAEMON_BIN, daemon_src + headers)):
         _run([cxx, "-O2", "-std=c++17", "-pthread", "-o", str(DAEMON_BIN), *map(str, daemon_src)], verbose)
-    host_src = sorted(NATIVE_DIR.glob("host_*.cpp"))
-    if host_src and (force or _stale(HOSTLIB_SO, host_src + headers)):
-        _run([cxx, "-O3", "-std=c++17", "-pthread", "-fPIC", "-shared", "-o", str(HOSTLIB_SO),
-              *map(str, host_src)], verbose)
     return DAEMON_BIN
 
 

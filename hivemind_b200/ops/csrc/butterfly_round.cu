@@ -482,7 +482,7 @@ __device__ void hr_send_item(const HrRound& g, int p, int c, int z, HrShared& sh
   const unsigned long long flag = (unsigned long long)g.epoch | ((unsigned long long)__float_as_uint(g.my_weight) << 32);
   if (p < 0) {
     // uncompressed parts: readers take the values from the vector itself, only the flags are published
-    if ((int)threadIdx.x < z) hr_st_release_sys_u64(ready + g.pub_list[c + threadIdx.x], flag);
+    for (int i = threadIdx.x; i < z; i += HR_THREADS) hr_st_release_sys_u64(ready + g.pub_list[c + i], flag);
     return;
   }
   const HrPart part = g.parts[p];

@@ -16,7 +16,10 @@
 //
 // Every wait on a peer's flag is bounded by `timeout_ns` on this GPU's globaltimer. A server that gives up on a
 // client treats it as having sent no rows; a client that gives up on a server gets zero answers and ok[row] = 0 for
-// those rows, which the combine step treats like an expert that did not respond.
+// those rows, which the combine step treats like an expert that did not respond. The server publishes the length of
+// every (expert, client) segment next to its first row, so a client whose rows the server did not take (it gave up
+// on that client's flag, or ran out of room) finds a shorter segment than it sent and marks the missing rows ok = 0
+// instead of reading somebody else's answers.
 #include "hm_common.cuh"
 
 #define MX_MAX_RANKS 16
@@ -28,9 +31,11 @@ struct HmMxPeers {
   unsigned char* rows[MX_MAX_RANKS];        // client buffer of every rank (this phase): [cap_send][hidden]
   const int* offsets[MX_MAX_RANKS];         // client row offsets by global expert: int[E + 1]
   unsigned char* answers[MX_MAX_RANKS];     // server buffer of every rank (this phase): [cap_recv][hidden]
-  const int* base_table[MX_MAX_RANKS];      // server layout of every rank: int[experts_per_rank][n_ranks]
+  const int* base_table[MX_MAX_RANKS];      // server layout of every rank: int[2][experts_per_rank][n_ranks]: first row of
+                                            // every (expert, client) segment, then the segment's length
   const unsigned int* rows_flag[MX_MAX_RANKS];
   const unsigned int* answers_flag[MX_MAX_RANKS];
+  int capacity;                             // rows of every answers buffer
 };
 
 // Bounded wait for *flag == want by one thread; returns false on timeout.
@@ -86,6 +91,7 @@ __global__ void __launch_bounds__(256) mx_layout_kernel(HmMxPeers p, unsigned in
       offs_pad[e] = cursor;
       for (int s = 0; s < R; ++s) {
         base_table[e * R + s] = cursor;
+        if (cursor + seg_count[e * R + s] > max_tiles * MX_TILE) seg_count[e * R + s] = max(0, max_tiles * MX_TILE - cursor);
         cursor += seg_count[e * R + s];
       }
       cursor = (cursor + MX_TILE - 1) / MX_TILE * MX_TILE;
@@ -170,14 +176,21 @@ __global__ void __launch_bounds__(128) mx_pull_kernel(HmMxPeers p, unsigned int 
     __syncthreads();
     const int st = state_s;
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * p.hidden_bytes);
-    if (st == 1) {
-      const int remote_row = p.base_table[d][(ge % EL) * p.n_ranks + p.me] + (row - my_offsets[ge]);
+    bool served = st == 1;
+    int remote_row = 0;
+    if (served) {
+      const int seg = (ge % EL) * p.n_ranks + p.me, local = row - my_offsets[ge];
+      const int* table = p.base_table[d];
+      remote_row = table[seg] + local;
+      served = local < table[EL * p.n_ranks + seg] && remote_row < p.capacity;   // did the server take this row?
+    }
+    if (served) {
       const uint4* src = reinterpret_cast<const uint4*>(p.answers[d] + (size_t)remote_row * p.hidden_bytes);
       for (int i = threadIdx.x; i < vec; i += blockDim.x) dst[i] = src[i];
     } else {
       for (int i = threadIdx.x; i < vec; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
     }
-    if (threadIdx.x == 0 && ok != nullptr) ok[row] = st == 1;
+    if (threadIdx.x == 0 && ok != nullptr) ok[row] = served;
     __syncthreads();
   }
 }

@@ -908,6 +908,28 @@ HM_API int hm_tc_gemm_grouped(const void* a, const void* b, void* d, void* aux, 
   }
 }
 
+// hm_tc_gemm_grouped for fp32 operands multiplied as tf32 (the low-rank products of PowerSGD over many matrices of
+// one shape in one launch). Same group modes and tables; K ranges of mode 2 are multiples of 32; block_n is 128, 64
+// or 32; D is fp32.
+HM_API int hm_tc_gemm_grouped_tf32(const void* a, const void* b, void* d, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldd, int a_mn, int b_mn, int reduce_add, float alpha,
+                                   int block_n, void* err, int sms, int group_mode, int num_groups,
+                                   const int* group_table, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if ((group_mode != 1 && group_mode != 2) || group_table == nullptr) return -17;
+  GemmCall c{a, b, d, nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, a_mn, b_mn, 1, 1, EPI_NONE, reduce_add, 1, alpha,
+             (int*)err, sms};
+  c.group_mode = group_mode;
+  c.num_groups = num_groups;
+  c.group_table = group_table;
+  switch (block_n) {
+    case 128: return dispatch_major<128, 4, true>(c, stream);
+    case 64: return dispatch_major<64, 6, true>(c, stream);
+    case 32: return dispatch_major<32, 8, true>(c, stream);
+    default: return -16;
+  }
+}
+
 // Two-CTA (cta_group::2) variant of hm_tc_gemm for bf16 operands: one 256x256 tile per pair of SMs.
 // Same arguments as hm_tc_gemm without `tf32` and `block_n`. Requirements: N and M arbitrary (edges are clipped by
 // TMA), the usual 16-byte alignment of leading dimensions.

@@ -99,3 +99,66 @@ def reconstruct_(out2d: torch.Tensor, p: torch.Tensor, q: torch.Tensor) -> None:
         tc_gemm(p, q, out=out2d, block_n=128 if n >= 128 else (64 if n >= 64 else 32))
     else:
         torch.matmul(p, q.t(), out=out2d)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the same three products for a STACK of matrices of one shape, one launch each (grouped modes of the tcgen05 kernel)
+_group_tables = {}
+
+
+def _group_table(device: torch.device, groups: int, step: int, per_tile: bool) -> torch.Tensor:
+    """Mode 1 (``per_tile``): the group of every 128-row tile of the stacked A / D; mode 2: row offsets of the groups
+    along the shared contraction axis. Cached: the tables depend only on the shapes."""
+    key = (device.index, groups, step, per_tile)
+    table = _group_tables.get(key)
+    if table is None:
+        if per_tile:
+            values = torch.arange(groups, dtype=torch.int32).repeat_interleave(step // 128)
+        else:
+            values = torch.arange(groups + 1, dtype=torch.int32) * step
+        table = _group_tables[key] = values.to(device)
+    return table
+
+
+def can_stack(rows: int, cols: int, r: int) -> bool:
+    """Whether matrices of this shape can go through the grouped launches (whole 128-row tiles in both directions)."""
+    return rows % 128 == 0 and cols % 128 == 0 and r % 4 == 0 and r <= 128
+
+
+def _grouped(a, b, d, m, n, k, a_mn, b_mn, mode, groups, table, reduce_add=False, alpha=1.0, block_n=None) -> None:
+    from hivemind_b200.ops.gemm import _err_flag
+
+    lib = _lib.load_library()
+    dev = a.device
+    with torch.cuda.device(dev):
+        code = lib.hm_tc_gemm_grouped_tf32(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(d), m, n, k, ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),
+            ctypes.c_longlong(d.stride(0)), int(a_mn), int(b_mn), int(reduce_add), ctypes.c_float(alpha),
+            block_n or _tile_n(n), _lib.ptr(_err_flag(dev)), _lib.sm_count(dev), mode, groups, _lib.ptr(table),
+            _lib.stream_ptr(dev))
+    _lib.check(code, "hm_tc_gemm_grouped_tf32")
+
+
+def compute_p_stacked_(p: torch.Tensor, m: torch.Tensor, q: torch.Tensor) -> None:
+    """``p[g] = m[g] @ q[g]`` for stacked ``m [G, rows, cols]``, ``q [G, cols, r]``, ``p [G, rows, r]`` (fp32, CUDA)."""
+    groups, rows, cols = m.shape
+    r = q.shape[2]
+    _grouped(m.view(groups * rows, cols), q.view(groups * cols, r), p.view(groups * rows, r), groups * rows, r, cols,
+             False, True, 1, groups, _group_table(m.device, groups, rows, True))
+
+
+def compute_q_stacked_(q: torch.Tensor, m: torch.Tensor, p: torch.Tensor) -> None:
+    """``q[g] = m[g].T @ p[g]`` for the same stacks: the contraction runs over each group's own rows."""
+    groups, rows, cols = m.shape
+    r = p.shape[2]
+    _grouped(m.view(groups * rows, cols), p.view(groups * rows, r), q.view(groups * cols, r), cols, r, groups * rows,
+             True, True, 2, groups, _group_table(m.device, groups, rows, False))
+
+
+def reconstruct_stacked_(out: torch.Tensor, p: torch.Tensor, q: torch.Tensor) -> None:
+    """``out[g] = p[g] @ q[g].T`` for ``out [G, rows, cols]``."""
+    groups, rows, cols = out.shape
+    r = p.shape[2]
+    _grouped(p.view(groups * rows, r), q.view(groups * cols, r), out.view(groups * rows, cols), groups * rows, cols, r,
+             False, False, 1, groups, _group_table(out.device, groups, rows, True), block_n=128)
+

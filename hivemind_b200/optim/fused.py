@@ -35,16 +35,20 @@ class _FusedBase(torch.optim.Optimizer):
             grads.append(p.grad if p.grad.is_contiguous() else p.grad.contiguous())
         return params, grads
 
-    def _step_count(self, group, params) -> int:
-        """All parameters of a group advance together; the counter is kept per parameter for state-dict parity."""
-        step = 0
-        for p in params:
+    def _advance_steps(self, params: List[torch.Tensor], grads: List[torch.Tensor]):
+        """Advance every parameter's own step counter and batch the parameters by the new value: a parameter that
+        sat out some steps (its gradient was None) must get the bias correction of ITS step count, so each batch
+        becomes one multi-tensor launch. Normally there is exactly one batch. Yields (step, params, grads)."""
+        batches = {}
+        for p, g in zip(params, grads):
             state = self.state[p]
             value = state.get("step", 0)
             value = int(value.item()) if isinstance(value, torch.Tensor) else int(value)
             state["step"] = value + 1
-            step = value + 1
-        return step
+            entry = batches.setdefault(value + 1, ([], []))
+            entry[0].append(p)
+            entry[1].append(g)
+        return [(step, ps, gs) for step, (ps, gs) in sorted(batches.items())]
 
 
 class FusedLAMB(_FusedBase):
@@ -72,12 +76,11 @@ class FusedLAMB(_FusedBase):
                     state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
                 if "_update" not in self.__dict__.setdefault("_scratch", {}).setdefault(id(p), {}):
                     self._scratch[id(p)]["_update"] = torch.empty_like(p, dtype=torch.float32)
-            step = self._step_count(group, params)
-            mt.lamb_step_(params, grads, [self.state[p]["exp_avg"] for p in params],
-                          [self.state[p]["exp_avg_sq"] for p in params],
-                          [self._scratch[id(p)]["_update"] for p in params], step=step, lr=group["lr"],
-                          betas=group["betas"], eps=group["eps"], weight_decay=group["weight_decay"],
-                          clamp_value=group["clamp_value"], debias=group["debias"])
+            for step, ps, gs in self._advance_steps(params, grads):
+                mt.lamb_step_(ps, gs, [self.state[p]["exp_avg"] for p in ps], [self.state[p]["exp_avg_sq"] for p in ps],
+                              [self._scratch[id(p)]["_update"] for p in ps], step=step, lr=group["lr"],
+                              betas=group["betas"], eps=group["eps"], weight_decay=group["weight_decay"],
+                              clamp_value=group["clamp_value"], debias=group["debias"])
             _bump_versions(params)
         return loss
 
@@ -103,11 +106,10 @@ class FusedAdam(_FusedBase):
                 if "exp_avg" not in state:
                     state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
                     state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
-            step = self._step_count(group, params)
-            mt.adam_step_(params, grads, [self.state[p]["exp_avg"] for p in params],
-                          [self.state[p]["exp_avg_sq"] for p in params], step=step, lr=group["lr"], betas=group["betas"],
-                          eps=group["eps"], weight_decay=group["weight_decay"],
-                          decoupled=group["decoupled_weight_decay"])
+            for step, ps, gs in self._advance_steps(params, grads):
+                mt.adam_step_(ps, gs, [self.state[p]["exp_avg"] for p in ps], [self.state[p]["exp_avg_sq"] for p in ps],
+                              step=step, lr=group["lr"], betas=group["betas"], eps=group["eps"],
+                              weight_decay=group["weight_decay"], decoupled=group["decoupled_weight_decay"])
             _bump_versions(params)
         return loss
 
@@ -135,14 +137,20 @@ class FusedSGD(_FusedBase):
             params, grads = self._collect(group)
             if not params:
                 continue
-            bufs, first = None, False
-            if group["momentum"] != 0:
-                first = any("momentum_buffer" not in self.state[p] for p in params)
-                for p in params:
-                    if "momentum_buffer" not in self.state[p]:
-                        self.state[p]["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32)
-                bufs = [self.state[p]["momentum_buffer"] for p in params]
-            mt.sgd_step_(params, grads, bufs, lr=group["lr"], momentum=group["momentum"], dampening=group["dampening"],
-                         weight_decay=group["weight_decay"], nesterov=group["nesterov"], first_step=first)
+            options = dict(lr=group["lr"], momentum=group["momentum"], dampening=group["dampening"],
+                           weight_decay=group["weight_decay"], nesterov=group["nesterov"])
+            if group["momentum"] == 0:
+                mt.sgd_step_(params, grads, None, first_step=False, **options)
+            else:
+                # a momentum buffer starts as a copy of the first gradient its parameter sees; parameters whose
+                # buffers already exist must not be reset because a late-comer in the same group gets its first
+                fresh = [i for i, p in enumerate(params) if "momentum_buffer" not in self.state[p]]
+                seasoned = [i for i, p in enumerate(params) if "momentum_buffer" in self.state[p]]
+                for i in fresh:
+                    self.state[params[i]]["momentum_buffer"] = torch.zeros_like(params[i], dtype=torch.float32)
+                for first, chosen in ((True, fresh), (False, seasoned)):
+                    if chosen:
+                        mt.sgd_step_([params[i] for i in chosen], [grads[i] for i in chosen],
+                                     [self.state[params[i]]["momentum_buffer"] for i in chosen], first_step=first, **options)
             _bump_versions(params)
         return loss

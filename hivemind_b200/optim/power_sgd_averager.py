@@ -63,18 +63,45 @@ class PowerSGDGradientAverager(GradientAverager):
             i for i, grad in enumerate(grads)
             if grad.ndim <= 1 or (1 - self.rank * sum(get_flatten_greedy_dims(grad)) / grad.numel()) < min_compression_ratio)
         compressed = [g for i, g in enumerate(grads) if i not in self._uncompressed_gradients_indexes]
-        self._dims = [get_flatten_greedy_dims(g) for g in compressed]
-        self._ms = [torch.zeros_like(g, dtype=torch.float32) for g in compressed]
+        dims = [get_flatten_greedy_dims(g) for g in compressed]
+        # Matrices of one shape are kept in stacks ([count, rows, cols] error feedback and averaged gradients,
+        # [count, rows, r] P, [count, cols, r] Q) so that each of the three products is ONE grouped launch per shape
+        # instead of one launch per matrix. The internal order of the compressed tensors is therefore "by shape";
+        # self._order[k] says which compressed gradient (in parameter order) is the k-th internally.
+        by_shape = {}
+        for i, (d, g) in enumerate(zip(dims, compressed)):
+            by_shape.setdefault((d[0], d[1], g.device), []).append(i)
+        self._order = [i for members in by_shape.values() for i in members]
+        self._dims = [dims[i] for i in self._order]
         make_q = torch.rand if q_init == "uniform" else torch.randn
-        self._qs = [make_q((dims[1], self.rank), device=g.device, dtype=torch.float32) for dims, g in zip(self._dims, compressed)]
-        self._ps = [torch.zeros((dims[0], self.rank), device=g.device, dtype=torch.float32) for dims, g in zip(self._dims, compressed)]
+        self._stacks, self._ms, self._qs, self._ps, stacked_grads = [], [], [], [], {}
+        for (rows, cols, device), members in by_shape.items():
+            count, first = len(members), len(self._ms)
+            m = torch.zeros(count, rows, cols, dtype=torch.float32, device=device)
+            g = torch.zeros(count, rows, cols, dtype=torch.float32, device=device)
+            q = make_q((count, cols, self.rank), device=device, dtype=torch.float32)
+            p = torch.zeros(count, rows, self.rank, dtype=torch.float32, device=device)
+            self._stacks.append(dict(first=first, count=count, rows=rows, cols=cols, m=m, g=g, p=p, q=q,
+                                     fused=device.type == "cuda" and ps_ops.can_stack(rows, cols, self.rank)))
+            for k, i in enumerate(members):
+                self._ms.append(m[k].view(compressed[i].shape))
+                self._qs.append(q[k])
+                self._ps.append(p[k])
+                stacked_grads[i] = g[k].view(compressed[i].shape)
+        if averaged_grads is None or len(averaged_grads) == 0:
+            it = iter(range(len(compressed)))
+            averaged_grads = [torch.zeros_like(g, dtype=torch.float32) if i in self._uncompressed_gradients_indexes
+                              else stacked_grads[next(it)] for i, g in enumerate(grads)]
+        else:
+            for stack in self._stacks:  # the caller's buffers are used as they are: no stacked launches for them
+                stack["fused"] = False
         self._p_endpoint = self._q_endpoint = None
         kwargs["use_device_path"] = False  # this class drives its own arenas (one per phase)
         super().__init__(self.parameters, dht=dht, prefix=prefix, reuse_grad_buffers=reuse_grad_buffers,
                          accumulate_grads_on=accumulate_grads_on, client_mode=client_mode, warn=warn,
-                         averaged_grads=averaged_grads or (), **kwargs)
+                         averaged_grads=averaged_grads, **kwargs)
         on_gpu = len(grads) > 0 and all(g.is_cuda for g in grads)
-        if on_gpu and self.mode != AveragingMode.CLIENT and self._ps:
+        if on_gpu and self._ps:
             self._setup_device_arenas()
 
     def _setup_device_arenas(self) -> None:
@@ -97,6 +124,16 @@ class PowerSGDGradientAverager(GradientAverager):
             for i, g in enumerate(averaged_grads):
                 new_averaged.append(next(it) if i in self._uncompressed_gradients_indexes else g)
         self._averaged_tensors = tuple(new_averaged)
+        # the stacks of P and Q are now runs of consecutive arena views
+        for stack in self._stacks:
+            first, count, rows, cols = stack["first"], stack["count"], stack["rows"], stack["cols"]
+            for name, endpoint, width in (("p", self._p_endpoint, rows), ("q", self._q_endpoint, cols)):
+                start, numel = endpoint.offsets[first], width * self.rank
+                contiguous = all(endpoint.offsets[first + k] == start + k * numel for k in range(count))
+                if contiguous:
+                    stack[name] = endpoint.flat[start:start + count * numel].view(count, width, self.rank)
+                else:
+                    stack["fused"] = False
         if not (self._p_endpoint.supported and self._q_endpoint.supported):
             self._p_endpoint = self._q_endpoint = None
 
@@ -174,21 +211,32 @@ class PowerSGDGradientAverager(GradientAverager):
             raise
 
     # ---------------------------------------------------------------------------------------------- the three stages
+    # All three run on the caller's stream without waiting on the host: the all-reduce rounds in between are ordered
+    # after them by an event (DeviceEndpoint.run_round) and block their own thread until the round's stream is done.
+    def _in_internal_order(self, compressed: Sequence[torch.Tensor]) -> list:
+        return [compressed[i] for i in self._order]
+
+    def _per_matrix(self, stack) -> range:
+        return range(stack["first"], stack["first"] + stack["count"])
+
     @traced("powersgd.compress_p")
     @torch.no_grad()
     def _begin_round(self, compressed: Sequence[torch.Tensor]) -> None:
         """m += g;  P = M Q."""
         if not self._ms:
             return
-        if all(m.device == g.device for m, g in zip(self._ms, compressed)):
-            mt.axpy_(self._ms, list(compressed), 1.0)
+        grads = self._in_internal_order(compressed)
+        if all(m.device == g.device for m, g in zip(self._ms, grads)):
+            mt.axpy_(self._ms, grads, 1.0)
         else:
-            for m, g in zip(self._ms, compressed):
+            for m, g in zip(self._ms, grads):
                 m.add_(g.to(m.device))
-        for p, q, m, dims in zip(self._ps, self._qs, self._ms, self._dims):
-            ps_ops.compute_p_(p, m.view(dims[0], dims[1]), q)
-        if self._ms[0].is_cuda:
-            torch.cuda.current_stream(self._ms[0].device).synchronize()
+        for stack in self._stacks:
+            if stack["fused"]:
+                ps_ops.compute_p_stacked_(stack["p"], stack["m"], stack["q"])
+            else:
+                for k in self._per_matrix(stack):
+                    ps_ops.compute_p_(self._ps[k], self._ms[k].view(*self._dims[k]), self._qs[k])
 
     @traced("powersgd.orthogonalize_q")
     @torch.no_grad()
@@ -201,10 +249,12 @@ class PowerSGDGradientAverager(GradientAverager):
         else:
             for p in self._ps:
                 orthogonalize_(p)
-        for p, q, m, dims in zip(self._ps, self._qs, self._ms, self._dims):
-            ps_ops.compute_q_(q, m.view(dims[0], dims[1]), p)
-        if self._ps[0].is_cuda:
-            torch.cuda.current_stream(self._ps[0].device).synchronize()
+        for stack in self._stacks:
+            if stack["fused"]:
+                ps_ops.compute_q_stacked_(stack["q"], stack["m"], stack["p"])
+            else:
+                for k in self._per_matrix(stack):
+                    ps_ops.compute_q_(self._qs[k], self._ms[k].view(*self._dims[k]), self._ps[k])
 
     @traced("powersgd.reconstruct")
     @torch.no_grad()
@@ -212,12 +262,17 @@ class PowerSGDGradientAverager(GradientAverager):
         """g^ = P Q^T;  m -= g^;  averaged gradient = g^."""
         if not self._ps:
             return
-        for p, q, grad, dims in zip(self._ps, self._qs, compressed, self._dims):
-            ps_ops.reconstruct_(grad.view(dims[0], dims[1]), p, q)
-        if all(m.device == g.device for m, g in zip(self._ms, compressed)):
-            mt.axpy_(self._ms, list(compressed), -1.0)
+        grads = self._in_internal_order(compressed)
+        for stack in self._stacks:
+            if stack["fused"]:
+                ps_ops.reconstruct_stacked_(stack["g"], stack["p"], stack["q"])
+            else:
+                for k in self._per_matrix(stack):
+                    ps_ops.reconstruct_(grads[k].view(*self._dims[k]), self._ps[k], self._qs[k])
+        if all(m.device == g.device for m, g in zip(self._ms, grads)):
+            mt.axpy_(self._ms, grads, -1.0)
         else:
-            for m, g in zip(self._ms, compressed):
+            for m, g in zip(self._ms, grads):
                 m.sub_(g.to(m.device))
 
     # ---------------------------------------------------------------------------------------------- state sharing

@@ -30,7 +30,8 @@ class _MxPeers(ctypes.Structure):
                 ("hidden_bytes", ctypes.c_int), ("timeout_ns", ctypes.c_ulonglong),
                 ("rows", ctypes.c_void_p * MAX_RANKS), ("offsets", ctypes.c_void_p * MAX_RANKS),
                 ("answers", ctypes.c_void_p * MAX_RANKS), ("base_table", ctypes.c_void_p * MAX_RANKS),
-                ("rows_flag", ctypes.c_void_p * MAX_RANKS), ("answers_flag", ctypes.c_void_p * MAX_RANKS)]
+                ("rows_flag", ctypes.c_void_p * MAX_RANKS), ("answers_flag", ctypes.c_void_p * MAX_RANKS),
+                ("capacity", ctypes.c_int)]
 
 
 class _RawCuda:
@@ -77,7 +78,7 @@ class PeerExpertExchange:
         for name, nbytes in (("fwd_rows", max_rows * self.row_bytes), ("bwd_rows", max_rows * self.row_bytes),
                              ("offsets", (self.num_experts + 1) * 4), ("fwd_answers", self.capacity * self.row_bytes),
                              ("bwd_answers", self.capacity * self.row_bytes),
-                             ("base_table", experts_per_rank * world * 4), ("flags", 256)):
+                             ("base_table", 2 * experts_per_rank * world * 4), ("flags", 256)):
             self.layout[name] = cursor
             cursor += (nbytes + 255) // 256 * 256
         self.arena_bytes = cursor
@@ -133,7 +134,7 @@ class PeerExpertExchange:
     def _peers(self, phase: int) -> _MxPeers:
         p = _MxPeers()
         p.n_ranks, p.me, p.experts_per_rank, p.hidden_bytes = self.world, self.rank, self.experts_per_rank, self.row_bytes
-        p.timeout_ns = self.timeout_ns
+        p.timeout_ns, p.capacity = self.timeout_ns, self.capacity
         rows_name, answers_name = ("fwd_rows", "fwd_answers") if phase == FORWARD else ("bwd_rows", "bwd_answers")
         for r, base in enumerate(self.peer_base):
             p.rows[r] = base + self.layout[rows_name]
@@ -164,12 +165,14 @@ class PeerExpertExchange:
     def server_gather(self, phase: int, epoch: int) -> GatheredRows:
         """Stage 2: wait for the clients, lay their rows out by (expert, client) and pull them over NVLink."""
         el, r = self.experts_per_rank, self.world
-        meta = torch.zeros(2 * el * r + el + 1 + self.max_tiles, dtype=torch.int32, device=self.device)
-        src_start, seg_count = meta[:el * r], meta[el * r:2 * el * r]
-        offs_pad = meta[2 * el * r:2 * el * r + el + 1]
-        tile_group = meta[2 * el * r + el + 1:]
+        meta = torch.zeros(el * r + el + 1 + self.max_tiles, dtype=torch.int32, device=self.device)
+        src_start = meta[:el * r]
+        offs_pad = meta[el * r:el * r + el + 1]
+        tile_group = meta[el * r + el + 1:]
         status = torch.zeros(1, dtype=torch.int64, device=self.device)  # own allocation: 8-byte aligned for atomics
-        base_table = self._view("base_table", el * r * 4).view(torch.int32)
+        # first rows and lengths of the (expert, client) segments live in the arena: the clients read both
+        tables = self._view("base_table", 2 * el * r * 4).view(torch.int32)
+        base_table, seg_count = tables[:el * r], tables[el * r:]
         gathered = torch.zeros(self.capacity, self.hidden, dtype=self.dtype, device=self.device)
         peers = self._peers(phase)
         with torch.cuda.device(self.device):

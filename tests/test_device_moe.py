@@ -489,3 +489,47 @@ def test_peer_exchange_stages_emulated_on_one_gpu():
     assert not ok[:total].any() and (out[:total] == 0).all()
     for e in exchanges:
         e.close()
+
+
+@pytest.mark.gpu
+def test_client_that_the_servers_gave_up_on_gets_failed_rows_not_somebody_elses():
+    """Host-side injection: client 2 skips its publish step, so every server's bounded wait for its flag runs out and
+    lays it out with zero rows. When that client later pulls, the segment lengths that the servers published tell it
+    that none of its rows were taken: ok = 0 and zeros, instead of rows of the clients that were served."""
+    from hivemind_b200.parallel.expert_exchange import FORWARD, PeerExpertExchange
+
+    torch.manual_seed(9)
+    world, per_rank, hidden, k = 3, 2, 128, 2
+    experts = world * per_rank
+    dev = torch.device("cuda", 0)
+    exchanges = [PeerExpertExchange(rank=r, world=world, experts_per_rank=per_rank, hidden=hidden, max_rows=200 * k,
+                                    device=dev, timeout=0.3) for r in range(world)]
+    for e in exchanges:
+        e.connect([x.descriptor for x in exchanges])
+    xs = [torch.randn(100, hidden, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    idxs = [torch.randint(0, experts, (100, k), dtype=torch.int32, device=dev) for _ in range(world)]
+    routed = [moe_ops.dispatch(x, idx, experts) for x, idx in zip(xs, idxs)]
+    late = 2
+    for r, e in enumerate(exchanges):
+        if r != late:
+            e.client_publish(routed[r].packed, routed[r].offsets, FORWARD, epoch=1)
+    torch.cuda.synchronize()
+    gathered = [e.server_gather(FORWARD, epoch=1) for e in exchanges]  # each waits 0.3 s for the late client, then goes on
+    torch.cuda.synchronize()
+    assert all(int(g.status[0]) == 1 << late for g in gathered)
+    for e, g in zip(exchanges, gathered):
+        e.server_publish(g.packed * 2, FORWARD, epoch=1)
+    # the late client publishes after the servers have moved on, then pulls
+    exchanges[late].client_publish(routed[late].packed, routed[late].offsets, FORWARD, epoch=1)
+    torch.cuda.synchronize()
+    for r, e in enumerate(exchanges):
+        total = int(routed[r].offsets[-1])
+        out, ok = e.client_pull(routed[r].offsets, routed[r].packed.shape[0], FORWARD, epoch=1)
+        torch.cuda.synchronize()
+        if r == late:
+            assert not ok[:total].any() and (out[:total] == 0).all()
+        else:
+            assert ok[:total].all()
+            assert torch.allclose(out[:total].float(), routed[r].packed[:total].float() * 2, rtol=1e-2, atol=1e-2)
+    for e in exchanges:
+        e.close()

@@ -327,3 +327,58 @@ def test_powersgd_products(m, n, r):
     check_kernel_errors()
     ref_o = P.double() @ Q.double().t()
     assert (out.double() - ref_o).abs().max().item() <= 2e-3 * ref_o.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("count,m,n,r", [(3, 1024, 512, 32), (5, 256, 1024, 8), (2, 3072, 1024, 32)])
+def test_powersgd_stacked_products_match_per_matrix_math(count, m, n, r):
+    """One grouped launch per product for a stack of equally shaped matrices (tf32) against fp64 matrix products."""
+    from hivemind_b200.ops import powersgd as ps
+    from hivemind_b200.ops.gemm import check_kernel_errors
+
+    torch.manual_seed(23)
+    M = torch.randn(count, m, n, device=_dev())
+    Q = torch.randn(count, n, r, device=_dev())
+    P = torch.full((count, m, r), float("nan"), device=_dev())
+    assert ps.can_stack(m, n, r)
+    ps.compute_p_stacked_(P, M, Q)
+    check_kernel_errors()
+    ref_p = M.double() @ Q.double()
+    assert (P.double() - ref_p).abs().max().item() <= 2e-3 * ref_p.abs().max().item() + 1e-2
+    Q2 = torch.full((count, n, r), float("nan"), device=_dev())
+    ps.compute_q_stacked_(Q2, M, P)
+    check_kernel_errors()
+    ref_q = M.double().transpose(1, 2) @ P.double()
+    assert (Q2.double() - ref_q).abs().max().item() <= 2e-3 * ref_q.abs().max().item() + 1e-2
+    out = torch.full((count, m, n), float("nan"), device=_dev())
+    ps.reconstruct_stacked_(out, P, Q)
+    check_kernel_errors()
+    ref_o = P.double() @ Q.double().transpose(1, 2)
+    assert (out.double() - ref_o).abs().max().item() <= 2e-3 * ref_o.abs().max().item() + 1e-2
+
+
+def test_powersgd_round_on_rank_deficient_gradient_matches_gram_schmidt_math():
+    """A gradient of true rank 8 compressed with r = 32: P = M Q has 24 dependent columns. The reference normalises
+    whatever Gram-Schmidt leaves of them (hivemind/utils/math.py:6-14), the batched CholeskyQR2 kernel drops them;
+    what matters is the gradient that comes out, g^ = P (M^T P)^T, which must be the same (here: M itself, since its
+    column space is captured either way)."""
+    from hivemind_b200.ops import powersgd as ps
+    from hivemind_b200.utils.math import orthogonalize_reference_
+
+    torch.manual_seed(29)
+    m, n, r = 1024, 512, 32
+    M = (torch.randn(m, 8, device=_dev()) @ torch.randn(8, n, device=_dev())) / 8 ** 0.5
+    Q = torch.randn(n, r, device=_dev())
+    P = torch.empty(m, r, device=_dev())
+    ps.compute_p_(P, M, Q)
+    # reference math in fp64 on the host
+    P_ref = orthogonalize_reference_((M.double() @ Q.double()).cpu())
+    g_ref = P_ref @ (M.double().cpu().t() @ P_ref).t()
+    # device path
+    ps.orthogonalize_batch_([P])
+    Q2 = torch.empty(n, r, device=_dev())
+    ps.compute_q_(Q2, M, P)
+    g = torch.empty(m, n, device=_dev())
+    ps.reconstruct_(g, P, Q2)
+    scale = M.abs().max().item()
+    assert (g_ref - M.double().cpu()).abs().max().item() < 1e-6 * scale + 1e-6  # the oracle recovers M
+    assert (g.double().cpu() - g_ref).abs().max().item() < 5e-3 * scale, (g.double().cpu() - g_ref).abs().max().item()

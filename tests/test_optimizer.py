@@ -309,3 +309,28 @@ def test_grad_scaler_defers_unscale_and_update_to_the_global_step():
         opt.shutdown()
     finally:
         dht.shutdown()
+
+
+def test_fused_optimizers_track_parameters_that_join_or_skip_steps():
+    """A parameter whose gradient is None in some steps keeps its own momentum buffer and step count, exactly like
+    the PyTorch optimizers (which skip such parameters): nobody else's momentum is reset when it joins, and its bias
+    correction uses its own number of steps."""
+    from hivemind_b200.optim.fused import FusedAdam, FusedSGD
+
+    torch.manual_seed(0)
+    for make_ours, make_ref in (
+            (lambda ps: FusedSGD(ps, lr=0.1, momentum=0.9), lambda ps: torch.optim.SGD(ps, lr=0.1, momentum=0.9)),
+            (lambda ps: FusedAdam(ps, lr=0.05), lambda ps: torch.optim.Adam(ps, lr=0.05))):
+        a, b = torch.randn(7, 3), torch.randn(5)
+        ours = [a.clone().requires_grad_(), b.clone().requires_grad_()]
+        ref = [a.clone().requires_grad_(), b.clone().requires_grad_()]
+        opt_ours, opt_ref = make_ours(ours), make_ref(ref)
+        for step in range(4):
+            grads = [torch.randn_like(a), torch.randn_like(b)]
+            for params in (ours, ref):
+                params[0].grad = grads[0].clone()
+                params[1].grad = grads[1].clone() if step in (1, 3) else None  # joins late, then skips a step
+            opt_ours.step()
+            opt_ref.step()
+        for mine, theirs in zip(ours, ref):
+            assert torch.allclose(mine, theirs, atol=1e-5, rtol=1e-5)
