@@ -38,7 +38,7 @@ namespace {
 constexpr int HD = 64;                    // head dimension
 constexpr int TILE = 128;                 // queries per tile, keys per block
 constexpr int TILE_BYTES = TILE * 128;    // 128 rows x 64 bf16
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 192;
 constexpr int BWD_THREADS = 320;
 constexpr int BWD_COMPUTE = 256;
 
@@ -95,27 +95,10 @@ struct FwdSmem {
   static constexpr int RING_OFF = TILE_BYTES;
   static constexpr int RING = 3;
   static constexpr int P_OFF = RING_OFF + RING * TILE_BYTES;     // two 16 KB slabs (keys 0..63, 64..127)
-  static constexpr int XCH_OFF = P_OFF + 2 * TILE_BYTES;         // float [2 parities][2 halves][128 rows]: row maxima / sums
-  static constexpr int BAR_OFF = XCH_OFF + 2 * 2 * TILE * 4;
-  static constexpr int NUM_BARS = 1 + 2 * RING + 4;
+  static constexpr int BAR_OFF = P_OFF + 2 * TILE_BYTES;
+  static constexpr int NUM_BARS = 1 + 2 * RING + 5;
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
 };
-
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t r[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-constexpr int FWD_SOFTMAX = 256;          // two warpgroups: each takes 64 of the 128 key columns of every row
-constexpr float RESCALE_THRESHOLD = 8.f;  // the running maximum is only replaced when it grew by more than 2^8
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_out,
@@ -133,7 +116,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + L::RING + s); };
   const uint32_t s_full = bar_base + 8u * (1 + 2 * L::RING);
-  const uint32_t s_empty = s_full + 8, p_full = s_full + 16, o_full = s_full + 24;
+  const uint32_t s_empty = s_full + 8, p_full = s_full + 16, o_full = s_full + 24, o_empty = s_full + 32;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::BAR_OFF + L::NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BAR_OFF + L::NUM_BARS * 8 + 4);
 
@@ -152,9 +135,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       mbar_init(kv_empty(s), 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, FWD_SOFTMAX);
-    mbar_init(p_full, FWD_SOFTMAX);
+    mbar_init(s_empty, 128);
+    mbar_init(p_full, 128);
     mbar_init(o_full, 1);
+    mbar_init(o_empty, 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -191,6 +175,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         const int t = 2 * j + 1, stage = t % L::RING, use = t / L::RING;
         if (!(where = __LINE__, mbar_wait(kv_full(stage), use & 1, abort_flag))) return false;
         if (!(where = __LINE__, mbar_wait(p_full, j & 1, abort_flag))) return false;
+        if (j > 0 && !(where = __LINE__, mbar_wait(o_empty, (j - 1) & 1, abort_flag))) return false;
         tc_fence_after();
         const uint32_t v_addr = smem_base + L::RING_OFF + stage * TILE_BYTES;
         const uint32_t p_addr = smem_base + L::P_OFF;
@@ -198,7 +183,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         for (int kk = 0; kk < TILE / 16; ++kk) {
           const uint64_t a_desc = make_smem_desc(p_addr + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 16, 1024);
           const uint64_t b_desc = make_smem_desc(v_addr + kk * 16 * 128, TILE_BYTES, 1024, 2);
-          tc_mma<false>(tmem_o, a_desc, b_desc, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates in TMEM
+          tc_mma<false>(tmem_o, a_desc, b_desc, IDESC_PV, kk > 0 ? 1u : 0u);
         }
         tc_commit(kv_empty(stage));
         tc_commit(o_full);
@@ -224,130 +209,133 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       if (!failed && !issue_pv(n_blocks - 1)) failed = true;
     }
   } else {
-    // ------------------------------------------------------------------ softmax + output (warps 2..9)
-    // Control flow is the same for all 256 threads whether or not a wait ran out (`ok` only gates the work), so
-    // that every named barrier is reached by all of them.
+    // ------------------------------------------------------------------ softmax + output (warps 2..5)
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const int q_idx = q0 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF);   // [parity][half][row]
-    float m_ref = -INFINITY;   // reference maximum (raw scores) that the exponentials of this row are taken against
-    float l_part = 0.f;        // this half's share of the row sum
+    uint8_t* p_smem = smem + L::P_OFF;
+    float o_acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+    float m_run = -INFINITY;   // running maximum of the raw (unscaled) scores
+    float l_run = 0.f;
     const float c = p.scale_log2;
-    bool ok = true;
 
     for (int j = 0; j < n_blocks; ++j) {
-      uint32_t r[64];
-      if (ok) ok = (where = __LINE__, warp_wait(s_full, j & 1, abort_flag));
-      const int key0 = j * TILE + half * 64;
-      const bool need_mask = (j * TILE + TILE > p.S) || (p.causal && j == q_tile);
+      if (!(where = __LINE__, warp_wait(s_full, j & 1, abort_flag))) { failed = true; break; }
+      tc_fence_after();
+      const int key0 = j * TILE;
+      const bool need_mask = (key0 + TILE > p.S) || (p.causal && j == q_tile);
       const int key_limit = p.causal ? min(p.S, q_idx + 1) : p.S;   // keys below this index are visible
-      float mx = -INFINITY;
-      if (ok) {
-        tc_fence_after();
-        tc_ld32(tmem_s + lane_base + (uint32_t)(half * 64), r);
-        tc_ld32(tmem_s + lane_base + (uint32_t)(half * 64 + 32), r + 32);
+      // pass 1: row maximum
+      float mx = m_run;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tc_ld32(tmem_s + lane_base + (uint32_t)(ch * 32), r);
         tc_wait_ld();
-        tc_fence_before();
-        mbar_arrive(s_empty);   // the scores are in registers: the next block's Q K^T may overwrite them
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (key0 + i < key_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i)
+            if (key0 + ch * 32 + i < key_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
-      // row maximum over both halves
-      float* slot = xch + ((j & 1) * 2 + half) * TILE + row;
-      *slot = mx;
-      named_bar_sync<FWD_SOFTMAX>();
-      mx = fmaxf(mx, xch[((j & 1) * 2 + (half ^ 1)) * TILE + row]);
-      // the reference maximum follows the running maximum lazily: O and l are only rescaled when it grew a lot
-      float alpha = 1.f;
-      bool rescale = false;
-      if (j == 0) {
-        m_ref = mx;
-      } else if ((mx - m_ref) * c > RESCALE_THRESHOLD) {   // false when both are -inf (NaN compares false)
-        alpha = fast_exp2((m_ref - mx) * c);
-        m_ref = mx;
-        rescale = true;
-      }
-      // the previous P V must have completed before P is overwritten (and before O is touched)
-      if (ok && j > 0) ok = (where = __LINE__, warp_wait(o_full, (j - 1) & 1, abort_flag));
-      if (ok && __any_sync(0xffffffffu, rescale)) {
-        uint32_t o[32];
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = fast_exp2((m_run - m_use) * c);   // 0 on the first block
+      m_run = mx;
+      // fold in the previous block's P V (also tells us that the P buffer may be overwritten)
+      if (j > 0) {
+        if (!(where = __LINE__, warp_wait(o_full, (j - 1) & 1, abort_flag))) { failed = true; break; }
         tc_fence_after();
-        tc_ld32(tmem_o + lane_base + (uint32_t)(half * 32), o);
-        tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tc_st32(tmem_o + lane_base + (uint32_t)(half * 32), o);
-        tc_wait_st();
-      }
-      if (ok) {
-        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const float neg_mc = -m_use * c;
-        float sum = 0.f;
-        uint8_t* p_row = smem + L::P_OFF + half * TILE_BYTES + row * 128;
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tc_ld32(tmem_o + lane_base + (uint32_t)(half * 32), r);
+          tc_wait_ld();
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = fast_exp2(fmaf(__uint_as_float(r[8 * q + i]), c, neg_mc));
-            if (need_mask && key0 + 8 * q + i >= key_limit) e[i] = 0.f;
-            sum += e[i];
-          }
-          uint4 o;
-          o.x = pack_bf16(e[0], e[1]);
-          o.y = pack_bf16(e[2], e[3]);
-          o.z = pack_bf16(e[4], e[5]);
-          o.w = pack_bf16(e[6], e[7]);
-          *reinterpret_cast<uint4*>(p_row + ((q ^ (row & 7)) << 4)) = o;
+          for (int i = 0; i < 32; ++i) o_acc[half * 32 + i] = (o_acc[half * 32 + i] + __uint_as_float(r[i])) * alpha;
         }
-        l_part = l_part * alpha + sum;
         tc_fence_before();
-        fence_proxy_async_smem();
-        mbar_arrive(p_full);
+        mbar_arrive(o_empty);
       }
-    }
-    if (ok) ok = (where = __LINE__, warp_wait(o_full, (n_blocks - 1) & 1, abort_flag));
-    // total row sum over both halves
-    xch[half * TILE + row] = l_part;
-    named_bar_sync<FWD_SOFTMAX>();
-    const float l_row = l_part + xch[(half ^ 1) * TILE + row];
-    if (ok) {
-      tc_fence_after();
-      const float inv_l = l_row > 0.f ? 1.f / l_row : 0.f;
-      uint8_t* stage_row = smem + L::P_OFF + row * 128;   // the last P V has completed: its operand buffer is free
-      uint32_t o[32];
-      tc_ld32(tmem_o + lane_base + (uint32_t)(half * 32), o);
-      tc_wait_ld();
+      // pass 2: exponentials, row sum, P as bf16 into the swizzled operand buffer
+      const float neg_mc = -m_use * c;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tc_ld32(tmem_s + lane_base + (uint32_t)(ch * 32), r);
+        tc_wait_ld();
+        float e[32];
+        if (need_mask) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 w;
-        w.x = pack_bf16(__uint_as_float(o[8 * q]) * inv_l, __uint_as_float(o[8 * q + 1]) * inv_l);
-        w.y = pack_bf16(__uint_as_float(o[8 * q + 2]) * inv_l, __uint_as_float(o[8 * q + 3]) * inv_l);
-        w.z = pack_bf16(__uint_as_float(o[8 * q + 4]) * inv_l, __uint_as_float(o[8 * q + 5]) * inv_l);
-        w.w = pack_bf16(__uint_as_float(o[8 * q + 6]) * inv_l, __uint_as_float(o[8 * q + 7]) * inv_l);
-        const int chunk = half * 4 + q;
-        *reinterpret_cast<uint4*>(stage_row + ((chunk ^ (row & 7)) << 4)) = w;
+          for (int i = 0; i < 32; ++i)
+            e[i] = (key0 + ch * 32 + i < key_limit) ? fast_exp2(fmaf(__uint_as_float(r[i]), c, neg_mc)) : 0.f;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) e[i] = fast_exp2(fmaf(__uint_as_float(r[i]), c, neg_mc));
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sum += e[i];
+        uint8_t* slab = p_smem + (ch >> 1) * TILE_BYTES + row * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack_bf16(e[8 * q], e[8 * q + 1]);
+          o.y = pack_bf16(e[8 * q + 2], e[8 * q + 3]);
+          o.z = pack_bf16(e[8 * q + 4], e[8 * q + 5]);
+          o.w = pack_bf16(e[8 * q + 6], e[8 * q + 7]);
+          const int chunk = (ch & 1) * 4 + q;
+          *reinterpret_cast<uint4*>(slab + ((chunk ^ (row & 7)) << 4)) = o;
+        }
       }
-      if (half == 0 && q_idx < p.S && p.lse != nullptr)
-        p.lse[((long long)batch * p.H + head) * p.S + q_idx] = (l_row > 0.f) ? m_ref * c + log2f(l_row) : -INFINITY;
+      l_run = l_run * alpha + sum;
+      tc_fence_before();
+      mbar_arrive(s_empty);        // this thread's reads of S_j are complete
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+    }
+    if (!failed) {
+      if (!(where = __LINE__, warp_wait(o_full, (n_blocks - 1) & 1, abort_flag))) failed = true;
+    }
+    if (!failed) {
+      tc_fence_after();
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint8_t* stage_row = p_smem + row * 128;   // the last P V has completed: its operand buffer is free
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tc_ld32(tmem_o + lane_base + (uint32_t)(half * 32), r);
+        tc_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = (o_acc[half * 32 + i] + __uint_as_float(r[i])) * inv_l;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+          o.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+          o.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+          o.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+          const int chunk = half * 4 + q;
+          *reinterpret_cast<uint4*>(stage_row + ((chunk ^ (row & 7)) << 4)) = o;
+        }
+      }
+      if (q_idx < p.S && p.lse != nullptr)
+        p.lse[((long long)batch * p.H + head) * p.S + q_idx] = (l_run > 0.f) ? m_run * c + log2f(l_run) : -INFINITY;
       fence_proxy_async_smem();
     }
-    named_bar_sync<FWD_SOFTMAX>();
+    // every softmax thread reaches this barrier, whether or not its waits succeeded
+    named_bar_sync<128>();
     if (threadIdx.x == 64 && !*abort_flag) {
       tma_store_3d(&map_out, smem_base + L::P_OFF, head * HD, q0, batch);
       tma_commit();
       tma_wait_all<0>();
     }
-    if (!ok) failed = true;
   }
 
   if (failed) {

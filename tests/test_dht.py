@@ -335,3 +335,78 @@ def test_node_caches_found_values_and_shares_concurrent_gets():
             await asyncio.gather(*[n.shutdown() for n in nodes])
 
     run(main())
+
+
+def test_cache_policies_replicas_and_unshared_gets():
+    """Knobs of the node that the other tests leave at their defaults: ``cache_locally=False`` keeps a reader's own
+    cache empty, ``cache_nearest=0`` asks nobody else to cache, ``cache_on_store=False`` does not prime the writer's
+    cache, ``reuse_get_requests=False`` lets concurrent gets search separately, ``exclude_self`` / ``num_replicas``
+    decide who holds a record, and a store with an older expiration never replaces a newer value."""
+    async def main():
+        plain = dict(num_replicas=2, cache_refresh_before_expiry=0)
+        nodes = await _swarm(5, cache_locally=False, cache_nearest=0, cache_on_store=False, reuse_get_requests=False, **plain)
+        try:
+            now = get_dht_time()
+            writer, reader = nodes[0], nodes[4]
+            assert await writer.store("k", "v1", now + 30)
+            key_id = DHTID.generate("k")
+            assert key_id not in writer.protocol.cache  # cache_on_store is off
+            assert sum(key_id in n.protocol.storage for n in nodes) == 2  # exactly num_replicas holders
+            assert (await reader.get("k")).value == "v1"
+            await asyncio.sleep(0.3)
+            assert key_id not in reader.protocol.cache  # neither locally ...
+            assert sum(key_id in n.protocol.cache for n in nodes) == 0  # ... nor on the nearest nodes
+            # an older record does not displace a newer one, a newer one does
+            assert not await writer.store("k", "stale", now + 10)
+            assert (await reader.get("k", latest=True)).value == "v1"
+            assert await writer.store("k", "v2", now + 40)
+            assert (await reader.get("k", latest=True)).value == "v2"
+            # exclude_self: the writer keeps no copy even if it is among the nearest nodes
+            for i in range(8):
+                await writer.store(f"x{i}", i, now + 30, exclude_self=True)
+            assert all(DHTID.generate(f"x{i}") not in writer.protocol.storage for i in range(8))
+            for i in range(8):
+                assert (await reader.get(f"x{i}")).value == i
+            # without request sharing every concurrent get runs its own traversal
+            searches = 0
+            original = reader.find_nearest_nodes
+
+            async def counting(*args, **kwargs):
+                nonlocal searches
+                searches += 1
+                return await original(*args, **kwargs)
+
+            reader.find_nearest_nodes = counting
+            results = await asyncio.gather(*[reader.get_many_by_id([key_id], float("inf")) for _ in range(4)])
+            assert all(r[key_id].value == "v2" for r in results)
+            futures = await reader.get_many(["k", "missing"], return_futures=True)
+            assert (await futures["k"]).value == "v2" and (await futures["missing"]) is None
+        finally:
+            await asyncio.gather(*[n.shutdown() for n in nodes])
+
+    run(main())
+
+
+def test_cached_values_are_refreshed_before_they_expire():
+    """A value that a node served from its cache is looked up again shortly before the cached copy expires, so a
+    reader keeps seeing the key while the writer keeps extending it."""
+    async def main():
+        nodes = await _swarm(4, num_replicas=1, cache_locally=True, cache_nearest=0, cache_refresh_before_expiry=1.0)
+        try:
+            writer, reader = nodes[0], nodes[3]
+            key_id = DHTID.generate("fresh")
+            assert await writer.store("fresh", "a", get_dht_time() + 2.0)
+            assert (await reader.get("fresh")).value == "a"
+            await asyncio.sleep(0.3)
+            if key_id in reader.protocol.storage:
+                return  # the reader happens to be the replica: nothing to cache
+            assert key_id in reader.protocol.cache
+            assert (await reader.get("fresh")).value == "a"  # served from the cache: schedules the refresh
+            assert await writer.store("fresh", "b", get_dht_time() + 30.0)
+            await asyncio.sleep(2.0)  # the first copy (2 s) has expired by now; the refresh fetched the new one
+            cached = reader.protocol.cache.get(key_id)
+            assert cached is not None and cached.expiration_time > get_dht_time() + 10
+        finally:
+            await asyncio.gather(*[n.shutdown() for n in nodes])
+
+    run(main())

@@ -282,3 +282,50 @@ def test_reference_import_paths_of_the_daemon_bindings():
     assert PeerID is p2p.PeerID and Client is ControlClient
     assert issubclass(ControlFailure, P2PDaemonError) and P2PHandlerError is p2p.P2PHandlerError
     assert PeerInfo is not None and StreamInfo is not None
+
+
+def test_a_thousand_futures_between_threads():
+    """Many futures set from worker threads and awaited from an event loop in another thread, with cancellations and
+    exceptions mixed in (the shape of the reference's stress test, tests/test_util_modules.py:285-331)."""
+    import concurrent.futures
+    import random
+
+    from hivemind_b200.utils import MPFuture
+
+    count = 1000
+    futures = [MPFuture() for _ in range(count)]
+    rng = random.Random(0)
+    plan = [rng.choice(("result", "exception", "cancel")) for _ in range(count)]
+
+    def producer(chunk):
+        for i in chunk:
+            if plan[i] == "result":
+                futures[i].set_result(i * i)
+            elif plan[i] == "exception":
+                futures[i].set_exception(ValueError(str(i)))
+            else:
+                futures[i].cancel()
+
+    async def consumer():
+        seen = []
+        for i, future in enumerate(futures):
+            try:
+                seen.append(("result", await future))
+            except ValueError as e:
+                seen.append(("exception", int(str(e))))
+            except (asyncio.CancelledError, concurrent.futures.CancelledError):
+                seen.append(("cancel", i))
+        return seen
+
+    with concurrent.futures.ThreadPoolExecutor(8) as pool:
+        loop_result = pool.submit(lambda: asyncio.new_event_loop().run_until_complete(consumer()))
+        time.sleep(0.05)  # the consumer is already waiting when the first futures are resolved
+        indices = list(range(count))
+        rng.shuffle(indices)
+        for k in range(8):
+            pool.submit(producer, indices[k::8])
+        seen = loop_result.result(timeout=60)
+    for i, (kind, value) in enumerate(seen):
+        assert kind == plan[i]
+        assert value == (i * i if kind == "result" else i)
+    assert all(f.done() for f in futures)
