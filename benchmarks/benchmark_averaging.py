@@ -107,6 +107,10 @@ def _time_rounds(endpoint, plan_args, rounds, warmup):
     all_marks = []
     if plan_args["barrier"] is not None:
         plan_args["barrier"]()
+    # the host needs longer to prepare a small round than the device needs to run it: a few milliseconds of busy-waiting
+    # at the head of the stream let the launches queue up, so that what is timed is the device, not Python
+    with torch.cuda.stream(stream):
+        torch.cuda._sleep(20_000_000)
     for i in range(warmup + rounds):
         # fresh values every round: repeated averaging of the same tensors converges, and the deltas of converged
         # peers are an unrepresentative (degenerate) input for the quantising codecs

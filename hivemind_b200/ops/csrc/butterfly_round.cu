@@ -42,8 +42,8 @@
 
 #define HR_MAX_PEERS 16
 #define HR_CHUNK 8192
-#define HR_THREADS 256
-#define HR_ROWS 8              // float4 groups per thread and chunk: 8 * 4 * 256 = 8192
+#define HR_THREADS 512
+#define HR_ROWS 4              // float4 groups per thread and chunk: 4 * 4 * 512 = 8192
 #define HR_BLOCKS (HR_CHUNK / HB_BLOCK)   // block-wise quantization blocks per chunk
 #define HR_SAMPLE 2048         // sample size for quantile borders
 #define HR_RING 8              // acknowledgement ring entries
@@ -70,21 +70,21 @@ struct HrRound {
   unsigned char* base[HR_MAX_PEERS];
   HrLayout lay;
   const HrPart* parts;
-  const int4* items;           // {part, chunk, -, -}; part == -1: publish pub_list[chunk .. chunk + z)
+  const int4* items;           // {part, first chunk, chunks, -}; part == -1: publish pub_list[y .. y + z)
   const int* pub_list;         // uncompressed parts this GPU sends: only their flags are published
   int n_send, n_reduce, n_apply;
   int item_begin, item_end, queue_slot, final_stage;
   // per-round local scratch, all zero between rounds (the last CTA of a round clears it)
-  int* include;                // [max_local_parts][HR_MAX_PEERS] 0 undecided, 1 / 3 included (parity 0 / 1), 2 left out
-  float* weights;              // [max_local_parts][HR_MAX_PEERS] weight of an included sender (written before its decision)
-  int* apply_decision;         // [n_parts] same encoding
+  // decisions: low word 0 undecided, 1 / 3 included (flag set 0 / 1), 2 left out; high word: the sender's weight
+  unsigned long long* include;         // [max_local_parts][HR_MAX_PEERS]
+  unsigned long long* apply_decision;  // [n_parts]
   int* ban;                    // [HR_MAX_PEERS]
   unsigned long long* t_start; // [2] start of the reduce / apply phase on this GPU
   unsigned long long* status;  // [0] banned sender mask [1] failed reducer mask [2] elements left unaveraged
   unsigned long long* status_out;
   int* part_done;              // [n_parts] chunks of a sent part that are complete
   int* dpart_done;             // [HR_MAX_PEERS][max_local_parts] chunks of a delta that are complete
-  int* queue;                  // [4]: three work queues (one per stage when stages are launched separately), CTAs done
+  int* queue;                  // [4]: [3] counts the CTAs that have finished
   const float* code;           // [512] block-wise code and midpoints between consecutive entries
   unsigned int done_slot;
 };
@@ -399,56 +399,16 @@ __device__ __forceinline__ void hr_decode_setup(int codec, const unsigned char* 
   __syncthreads();
 }
 
-__device__ __forceinline__ int hr_ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long hr_ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ int hr_cas_release_gpu(int* p, int expected, int desired) {
-  int old;
-  asm volatile("atom.release.gpu.global.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(p), "r"(expected), "r"(desired) : "memory");
+__device__ __forceinline__ unsigned long long hr_cas_release_gpu_u64(unsigned long long* p, unsigned long long expected,
+                                                                    unsigned long long desired) {
+  unsigned long long old;
+  asm volatile("atom.release.gpu.global.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "l"(p), "l"(expected), "l"(desired) : "memory");
   return old;
-}
-
-// Bounded wait for a flag that a groupmate publishes in one of its two flag sets. Thread 0 polls; the outcome goes
-// into `decision` by compare-and-swap so that all CTAs that work on the same part agree: 1 / 3 = published (in flag
-// set 0 / 1), 2 = gave up. Only the first CTA to get here talks to the groupmate: it reads the flag with
-// acquire.sys, notes the weight the flag carries in `weight_slot` and publishes the decision with release.gpu; every
-// later CTA reads the decision with acquire.gpu, which orders its reads of the groupmate's data after the
-// groupmate's writes just the same (the chain of release / acquire pairs is cumulative) at the price of a local load.
-__device__ int hr_wait_decide(const unsigned long long* flag0, const unsigned long long* flag1, bool wide, unsigned int want,
-                              int* decision, float* weight_slot, const int* ban_flag, unsigned long long deadline_ns,
-                              HrShared& sh, float* weight) {
-  if (threadIdx.x == 0) {
-    auto load = [&](const unsigned long long* f) -> unsigned long long {
-      return wide ? hr_ld_acquire_sys_u64(f) : (unsigned long long)hm_ld_acquire_sys(reinterpret_cast<const unsigned int*>(f));
-    };
-    int d = hr_ld_acquire_gpu(decision);
-    while (d == 0) {
-      const unsigned long long v0 = load(flag0), v1 = load(flag1);
-      int verdict = 0;
-      if ((unsigned int)v0 == want) verdict = 1;
-      else if ((unsigned int)v1 == want) verdict = 3;
-      else if ((unsigned int)v0 == (want | HB_FAIL_BIT) || (unsigned int)v1 == (want | HB_FAIL_BIT) ||
-               (ban_flag && *reinterpret_cast<const volatile int*>(ban_flag)) || hm_globaltimer_ns() > deadline_ns)
-        verdict = 2;
-      if (verdict == 0) {
-        __nanosleep(200);
-      } else {
-        if (verdict != 2 && weight_slot != nullptr)
-          *weight_slot = __uint_as_float((unsigned int)((verdict == 1 ? v0 : v1) >> 32));
-        hr_cas_release_gpu(decision, 0, verdict);
-      }
-      d = hr_ld_acquire_gpu(decision);
-    }
-    sh.bcast = d;
-    sh.bcast64 = (weight_slot != nullptr && d != 2) ? (unsigned long long)__float_as_uint(*reinterpret_cast<volatile float*>(weight_slot)) : 0ull;
-  }
-  __syncthreads();
-  const int out = sh.bcast;
-  *weight = __uint_as_float((unsigned int)sh.bcast64);
-  __syncthreads();
-  return out;
 }
 
 __device__ __forceinline__ unsigned long long hr_phase_start(unsigned long long* slot) {
@@ -461,78 +421,130 @@ __device__ __forceinline__ unsigned long long hr_phase_start(unsigned long long*
   return t;
 }
 
-// The CTA that completes the last chunk publishes the flag. Writes of all chunks happen-before the flag: thread 0
-// of every CTA fences (after a CTA barrier) before its increment, and the publishing thread fences between its
-// increment and the release store.
-__device__ __forceinline__ bool hr_chunk_done(int* counter, int n_chunks) {
-  __syncthreads();   // every thread's writes of this chunk are ordered before thread 0's fence (CTA-scope barrier)
-  bool last = false;
-  if (threadIdx.x == 0) {
-    __threadfence_system();   // cumulative: makes the whole CTA's writes visible before the count moves
-    last = atomicAdd(counter, 1) == n_chunks - 1;
-    if (last) __threadfence_system();
+// Bounded wait of ONE thread for a flag that a groupmate publishes in one of its two flag sets. The outcome goes
+// into `decision` by compare-and-swap, so that all CTAs that work on the same part agree; its low word says 1 / 3 =
+// published (in flag set 0 / 1) or 2 = gave up, its high word carries the weight that came with the flag. Only the
+// first CTA to get here talks to the groupmate: it reads the flag with acquire.sys and publishes the decision with
+// release.gpu; every later CTA finds the decision with ONE acquire.gpu load, which orders its reads of the
+// groupmate's data after the groupmate's writes just the same (release / acquire chains are cumulative). The clock
+// is only looked at while the flag is missing: the time limit runs from the moment this GPU first had to wait in
+// the phase (`t_start`).
+__device__ unsigned long long hr_decide(const unsigned long long* flag0, const unsigned long long* flag1, bool wide,
+                                        unsigned int want, unsigned long long* decision, const int* ban_flag,
+                                        unsigned long long* t_start, unsigned long long timeout_ns) {
+  auto load = [&](const unsigned long long* f) -> unsigned long long {
+    return wide ? hr_ld_acquire_sys_u64(f) : (unsigned long long)hm_ld_acquire_sys(reinterpret_cast<const unsigned int*>(f));
+  };
+  unsigned long long d = hr_ld_acquire_gpu_u64(decision);
+  unsigned long long deadline = 0;
+  while ((unsigned int)d == 0) {
+    const unsigned long long v0 = load(flag0), v1 = load(flag1);
+    unsigned long long verdict = 0;
+    if ((unsigned int)v0 == want) {
+      verdict = 1ull | (v0 & 0xffffffff00000000ull);
+    } else if ((unsigned int)v1 == want) {
+      verdict = 3ull | (v1 & 0xffffffff00000000ull);
+    } else {
+      if (deadline == 0) deadline = hr_phase_start(t_start) + timeout_ns;
+      if ((unsigned int)v0 == (want | HB_FAIL_BIT) || (unsigned int)v1 == (want | HB_FAIL_BIT) ||
+          (ban_flag && *reinterpret_cast<const volatile int*>(ban_flag)) || hm_globaltimer_ns() > deadline)
+        verdict = 2ull;
+    }
+    if (verdict == 0) __nanosleep(200);
+    else hr_cas_release_gpu_u64(decision, 0ull, verdict);
+    d = hr_ld_acquire_gpu_u64(decision);
   }
+  return d;
+}
+
+// Chunks [.., .. + add) of a part are complete; true for the thread whose increment completes the part. The caller
+// has passed a CTA barrier after the chunks' writes; the fence (cumulative) makes them visible system-wide before the
+// count moves, and the thread that completes the part fences again before it publishes the part's flag.
+__device__ __forceinline__ bool hr_chunks_done(int* counter, int add, int n_chunks) {
+  __threadfence_system();
+  const bool last = atomicAdd(counter, add) == n_chunks - add;
+  if (last) __threadfence_system();
   return last;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-__device__ void hr_send_item(const HrRound& g, int p, int c, int z, HrShared& sh) {
+__device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
   unsigned char* my = g.base[g.me];
   unsigned long long* ready = reinterpret_cast<unsigned long long*>(my + g.lay.ready[g.parity]);
   const unsigned long long flag = (unsigned long long)g.epoch | ((unsigned long long)__float_as_uint(g.my_weight) << 32);
   if (p < 0) {
     // uncompressed parts: readers take the values from the vector itself, only the flags are published
-    for (int i = threadIdx.x; i < z; i += HR_THREADS) hr_st_release_sys_u64(ready + g.pub_list[c + i], flag);
+    for (int i = threadIdx.x; i < z; i += HR_THREADS) hr_st_release_sys_u64(ready + g.pub_list[c0 + i], flag);
     return;
   }
   const HrPart part = g.parts[p];
-  const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
-  const float* x = reinterpret_cast<const float*>(my + g.lay.data) + part.start + lo;
-  float v[HR_ROWS][4];
+  const long long stride = hr_chunk_stride(part.codec);
+  for (int c = c0; c < c0 + z; ++c) {
+    const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
+    const float* x = reinterpret_cast<const float*>(my + g.lay.data) + part.start + lo;
+    float v[HR_ROWS][4];
+#pragma unroll
+    for (int r = 0; r < HR_ROWS; ++r) {
+      const int i = hr_elem(r);
+      if (i + 4 <= n) {
+        const float4 t = *reinterpret_cast<const float4*>(x + i);
+        v[r][0] = t.x; v[r][1] = t.y; v[r][2] = t.z; v[r][3] = t.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[r][k] = (i + k < n) ? x[i + k] : 0.f;
+      }
+    }
+    if (c != c0) __syncthreads();   // the previous chunk's encoder is done with the shared tables
+    hr_encode_chunk(v, n, part.codec, my + g.lay.outbox[g.parity] + part.enc_off + (long long)c * stride, sh, g.code);
+  }
+  const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
+  __syncthreads();
+  if (threadIdx.x == 0 && hr_chunks_done(g.part_done + p, z, n_chunks)) hr_st_release_sys_u64(ready + p, flag);
+}
+
+__device__ __forceinline__ void hr_load_rows(const float* __restrict__ src, int n, float4 (&rv)[HR_ROWS]) {
 #pragma unroll
   for (int r = 0; r < HR_ROWS; ++r) {
     const int i = hr_elem(r);
     if (i + 4 <= n) {
-      const float4 t = *reinterpret_cast<const float4*>(x + i);
-      v[r][0] = t.x; v[r][1] = t.y; v[r][2] = t.z; v[r][3] = t.w;
+      rv[r] = *reinterpret_cast<const float4*>(src + i);
     } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) v[r][k] = (i + k < n) ? x[i + k] : 0.f;
+      rv[r].x = i < n ? src[i] : 0.f;
+      rv[r].y = i + 1 < n ? src[i + 1] : 0.f;
+      rv[r].z = i + 2 < n ? src[i + 2] : 0.f;
+      rv[r].w = 0.f;
     }
   }
-  unsigned char* rec = my + g.lay.outbox[g.parity] + part.enc_off + (long long)c * hr_chunk_stride(part.codec);
-  hr_encode_chunk(v, n, part.codec, rec, sh, g.code);
-  const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
-  if (hr_chunk_done(g.part_done + p, n_chunks)) hr_st_release_sys_u64(ready + p, flag);
 }
 
-__device__ void hr_reduce_item(const HrRound& g, int p, int c, HrShared& sh) {
+__device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
   const HrPart part = g.parts[p];
   const int codec = part.codec, j = part.local_idx, me = g.me;
-  const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
   const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
-  const unsigned long long deadline = hr_phase_start(g.t_start) + g.sender_timeout_ns;
   unsigned char* my = g.base[me];
 
-  for (int s = 0; s < g.n_peers; ++s) {
-    if (s == me || !g.sends[s]) {
-      if (threadIdx.x == 0) sh.inc[s] = 0;
-      continue;
-    }
-    const unsigned long long* f0 = reinterpret_cast<const unsigned long long*>(g.base[s] + g.lay.ready[0]) + p;
-    const unsigned long long* f1 = reinterpret_cast<const unsigned long long*>(g.base[s] + g.lay.ready[1]) + p;
-    float w_s;
-    const size_t slot = (size_t)j * HR_MAX_PEERS + s;
-    const int d = hr_wait_decide(f0, f1, true, g.epoch, g.include + slot, g.weights + slot, g.ban + s, deadline, sh, &w_s);
-    if (threadIdx.x == 0) {
-      sh.inc[s] = (d == 1 || d == 3);
-      sh.par[s] = d >> 1;
-      sh.w[s] = w_s;
-      if (d == 2) {
+  // one lane per sender waits for (or looks up the decision about) that sender's flag
+  if (threadIdx.x < HR_MAX_PEERS) {
+    const int s = threadIdx.x;
+    int inc = 0, par = 0;
+    float w = 0.f;
+    if (s < g.n_peers && s != me && g.sends[s]) {
+      const unsigned long long* f0 = reinterpret_cast<const unsigned long long*>(g.base[s] + g.lay.ready[0]) + p;
+      const unsigned long long* f1 = reinterpret_cast<const unsigned long long*>(g.base[s] + g.lay.ready[1]) + p;
+      const unsigned long long d = hr_decide(f0, f1, true, g.epoch, g.include + (size_t)j * HR_MAX_PEERS + s, g.ban + s,
+                                             g.t_start, g.sender_timeout_ns);
+      const unsigned int v = (unsigned int)d;
+      inc = v == 1u || v == 3u;
+      par = (int)(v >> 1);
+      w = __uint_as_float((unsigned int)(d >> 32));
+      if (v == 2u) {
         atomicExch(g.ban + s, 1);   // a sender that missed one part is left out of the later ones too
         atomicOr(g.status, 1ull << s);
       }
     }
+    sh.inc[s] = inc;
+    sh.par[s] = par;
+    sh.w[s] = w;
   }
   __syncthreads();
 
@@ -543,205 +555,212 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c, HrShared& sh) {
   const bool dead = !(den > 0.f);
   const float inv_den = dead ? 0.f : 1.f / den;
   const float alpha_own = dead ? 0.f : g.alpha;
-  float* x_local = reinterpret_cast<float*>(my + g.lay.data) + part.start + lo;
   const long long stride = hr_chunk_stride(codec);
   const int hdr = hr_header_bytes(codec);
+  // every reducer walks the senders in its own rotation, so that at any moment the reducers of a group read from
+  // different GPUs instead of all draining the same sender's links
+  const int rot = (me + 1) % g.n_peers;
+  // uncompressed parts: the first sender's rows of the NEXT chunk are requested before this chunk's results are
+  // written, which keeps remote reads in flight while the CTA is busy with local memory
+  int first = -1;
+  if (codec == HB_NONE) {
+    for (int t = 0; t < g.n_peers && first < 0; ++t) {
+      const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
+      if (sh.inc[s]) first = s;
+    }
+  }
+  float4 ahead[HR_ROWS];
+  if (first >= 0)
+    hr_load_rows(reinterpret_cast<const float*>(g.base[first] + g.lay.data) + part.start + c0 * HR_CHUNK,
+                 min(HR_CHUNK, part.len - c0 * HR_CHUNK), ahead);
 
-  float acc[HR_ROWS][4];
+  for (int c = c0; c < c0 + z; ++c) {
+    const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
+    float* x_local = reinterpret_cast<float*>(my + g.lay.data) + part.start + lo;
+    float acc[HR_ROWS][4];
+    {
+      float4 own[HR_ROWS];
+      if (i_send) hr_load_rows(x_local, n, own);
 #pragma unroll
-  for (int r = 0; r < HR_ROWS; ++r) {
-    const int i = hr_elem(r);
-    if (i_send && i + 4 <= n) {
-      const float4 own = *reinterpret_cast<const float4*>(x_local + i);
-      acc[r][0] = g.my_weight * own.x; acc[r][1] = g.my_weight * own.y;
-      acc[r][2] = g.my_weight * own.z; acc[r][3] = g.my_weight * own.w;
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) acc[r][k] = (i_send && i + k < n) ? g.my_weight * x_local[i + k] : 0.f;
+      for (int r = 0; r < HR_ROWS; ++r) {
+        acc[r][0] = i_send ? g.my_weight * own[r].x : 0.f; acc[r][1] = i_send ? g.my_weight * own[r].y : 0.f;
+        acc[r][2] = i_send ? g.my_weight * own[r].z : 0.f; acc[r][3] = i_send ? g.my_weight * own[r].w : 0.f;
+      }
     }
-  }
-  // every reducer walks the senders in its own rotation (and every chunk starts one further), so that at any moment
-  // the reducers of a group read from different GPUs instead of all draining the same sender's links
-  const int rot = (me + 1 + c) % g.n_peers;
-  for (int t = 0; t < g.n_peers; ++t) {
-    const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
-    if (!sh.inc[s]) continue;
-    const float w = sh.w[s];
-    if (codec == HB_NONE) {
-      const float* __restrict__ rx = reinterpret_cast<const float*>(g.base[s] + g.lay.data) + part.start + lo;
-      float4 rv[HR_ROWS];
+    for (int t = 0; t < g.n_peers; ++t) {
+      const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
+      if (!sh.inc[s]) continue;
+      const float w = sh.w[s];
+      if (codec == HB_NONE) {
+        float4 rv[HR_ROWS];
+        if (s == first) {
 #pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) {   // all loads from the sender's memory are issued before the first use
-        const int i = hr_elem(r);
-        if (i + 4 <= n) {
-          rv[r] = *reinterpret_cast<const float4*>(rx + i);
+          for (int r = 0; r < HR_ROWS; ++r) rv[r] = ahead[r];
+          if (c + 1 < c0 + z)
+            hr_load_rows(reinterpret_cast<const float*>(g.base[s] + g.lay.data) + part.start + lo + HR_CHUNK,
+                         min(HR_CHUNK, part.len - lo - HR_CHUNK), ahead);
         } else {
-          rv[r].x = i < n ? rx[i] : 0.f;
-          rv[r].y = i + 1 < n ? rx[i + 1] : 0.f;
-          rv[r].z = i + 2 < n ? rx[i + 2] : 0.f;
-          rv[r].w = 0.f;
+          hr_load_rows(reinterpret_cast<const float*>(g.base[s] + g.lay.data) + part.start + lo, n, rv);
         }
-      }
 #pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) {
-        acc[r][0] = fmaf(w, rv[r].x, acc[r][0]); acc[r][1] = fmaf(w, rv[r].y, acc[r][1]);
-        acc[r][2] = fmaf(w, rv[r].z, acc[r][2]); acc[r][3] = fmaf(w, rv[r].w, acc[r][3]);
-      }
-      continue;
-    }
-    // compressed: pull the sender's chunk record once, keep a copy where its delta will be written
-    const unsigned char* remote = g.base[s] + g.lay.outbox[sh.par[s]] + part.enc_off + (long long)c * stride;
-    unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
-    float mean, sd, absmax[HR_BLOCKS] = {};
-    hr_decode_setup(codec, remote, sh, g.code, mean, sd, absmax);
-    if (hdr == 1024) {
-      if (threadIdx.x < 256) reinterpret_cast<float*>(local)[threadIdx.x] = sh.cb[threadIdx.x];
-    } else if (hdr == 16 && threadIdx.x < 4) {   // mean / std or block maxima: one 16-byte header
-      reinterpret_cast<float*>(local)[threadIdx.x] = reinterpret_cast<const float*>(remote)[threadIdx.x];
-    }
-    if (hb_elem_bytes(codec) == 2) {
-      uint2 raw[HR_ROWS];
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) raw[r] = *reinterpret_cast<const uint2*>(remote + hdr + (size_t)hr_elem(r) * 2);
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) {
-        *reinterpret_cast<uint2*>(local + hdr + (size_t)hr_elem(r) * 2) = raw[r];
-        const __half2 a = *reinterpret_cast<const __half2*>(&raw[r].x), b = *reinterpret_cast<const __half2*>(&raw[r].y);
-        float o[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) acc[r][k] = fmaf(w, fmaf(o[k], sd, mean), acc[r][k]);
-      }
-    } else {
-      uchar4 raw[HR_ROWS];
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) raw[r] = *reinterpret_cast<const uchar4*>(remote + hdr + hr_elem(r));
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) {
-        *reinterpret_cast<uchar4*>(local + hdr + hr_elem(r)) = raw[r];
-        const float a = codec == HB_BLOCKWISE8 ? absmax[r / (HR_ROWS / HR_BLOCKS)] : 1.f;
-        acc[r][0] = fmaf(w, sh.cb[raw[r].x] * a, acc[r][0]); acc[r][1] = fmaf(w, sh.cb[raw[r].y] * a, acc[r][1]);
-        acc[r][2] = fmaf(w, sh.cb[raw[r].z] * a, acc[r][2]); acc[r][3] = fmaf(w, sh.cb[raw[r].w] * a, acc[r][3]);
-      }
-    }
-  }
-  // the average; applied to this reducer's own values right here
-  float* avg_out = reinterpret_cast<float*>(my + g.lay.avg[g.parity]) + part.avg_off + lo;
-#pragma unroll
-  for (int r = 0; r < HR_ROWS; ++r) {
-    const int i = hr_elem(r);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) acc[r][k] *= inv_den;
-    if (i + 4 <= n) {
-      if (codec == HB_NONE) *reinterpret_cast<float4*>(avg_out + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
-      if (i_send) {
-        float4 own = *reinterpret_cast<const float4*>(x_local + i);
-        own.x = fmaf(alpha_own, acc[r][0] - own.x, own.x); own.y = fmaf(alpha_own, acc[r][1] - own.y, own.y);
-        own.z = fmaf(alpha_own, acc[r][2] - own.z, own.z); own.w = fmaf(alpha_own, acc[r][3] - own.w, own.w);
-        *reinterpret_cast<float4*>(x_local + i) = own;
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (i + k < n) {
-          if (codec == HB_NONE) avg_out[i + k] = acc[r][k];
-          if (i_send) x_local[i + k] = fmaf(alpha_own, acc[r][k] - x_local[i + k], x_local[i + k]);
-        } else {
-          acc[r][k] = 0.f;
+        for (int r = 0; r < HR_ROWS; ++r) {
+          acc[r][0] = fmaf(w, rv[r].x, acc[r][0]); acc[r][1] = fmaf(w, rv[r].y, acc[r][1]);
+          acc[r][2] = fmaf(w, rv[r].z, acc[r][2]); acc[r][3] = fmaf(w, rv[r].w, acc[r][3]);
         }
+        continue;
       }
-    }
-  }
-  // deltas: avg - decode(copy of the sender's record), encoded over the copy, one sender after the other
-  for (int s = 0; s < g.n_peers; ++s) {
-    if (s == me || !g.sends[s]) continue;
-    if (codec != HB_NONE && sh.inc[s] && !dead) {
+      // compressed: pull the sender's chunk record once, keep a copy where its delta will be written
+      const unsigned char* remote = g.base[s] + g.lay.outbox[sh.par[s]] + part.enc_off + (long long)c * stride;
       unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
       float mean, sd, absmax[HR_BLOCKS] = {};
-      hr_decode_setup(codec, local, sh, g.code, mean, sd, absmax);
-      float d[HR_ROWS][4];
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) {
-        const int i = hr_elem(r);
-        float o[4];
-        hr_decode_row(codec, local + hdr, i, mean, sd, sh.cb, absmax, o);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) d[r][k] = (i + k < n) ? acc[r][k] - o[k] : 0.f;
+      hr_decode_setup(codec, remote, sh, g.code, mean, sd, absmax);
+      if (hdr == 1024) {
+        if (threadIdx.x < 256) reinterpret_cast<float*>(local)[threadIdx.x] = sh.cb[threadIdx.x];
+      } else if (hdr == 16 && threadIdx.x < 4) {   // mean / std or block maxima: one 16-byte header
+        reinterpret_cast<float*>(local)[threadIdx.x] = reinterpret_cast<const float*>(remote)[threadIdx.x];
       }
-      __syncthreads();   // every thread has decoded with the old header before anybody writes the new one
-      hr_encode_chunk(d, n, codec, local, sh, g.code);
+      if (hb_elem_bytes(codec) == 2) {
+        uint2 raw[HR_ROWS];
+#pragma unroll
+        for (int r = 0; r < HR_ROWS; ++r) raw[r] = *reinterpret_cast<const uint2*>(remote + hdr + (size_t)hr_elem(r) * 2);
+#pragma unroll
+        for (int r = 0; r < HR_ROWS; ++r) {
+          *reinterpret_cast<uint2*>(local + hdr + (size_t)hr_elem(r) * 2) = raw[r];
+          const __half2 a = *reinterpret_cast<const __half2*>(&raw[r].x), b = *reinterpret_cast<const __half2*>(&raw[r].y);
+          float o[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[r][k] = fmaf(w, fmaf(o[k], sd, mean), acc[r][k]);
+        }
+      } else {
+        uchar4 raw[HR_ROWS];
+#pragma unroll
+        for (int r = 0; r < HR_ROWS; ++r) raw[r] = *reinterpret_cast<const uchar4*>(remote + hdr + hr_elem(r));
+#pragma unroll
+        for (int r = 0; r < HR_ROWS; ++r) {
+          *reinterpret_cast<uchar4*>(local + hdr + hr_elem(r)) = raw[r];
+          const float a = codec == HB_BLOCKWISE8 ? absmax[r / (HR_ROWS / HR_BLOCKS)] : 1.f;
+          acc[r][0] = fmaf(w, sh.cb[raw[r].x] * a, acc[r][0]); acc[r][1] = fmaf(w, sh.cb[raw[r].y] * a, acc[r][1]);
+          acc[r][2] = fmaf(w, sh.cb[raw[r].z] * a, acc[r][2]); acc[r][3] = fmaf(w, sh.cb[raw[r].w] * a, acc[r][3]);
+        }
+      }
     }
-    if (hr_chunk_done(g.dpart_done + (size_t)s * g.max_local_parts + j, n_chunks)) {
+    // the average; applied to this reducer's own values right here
+    float* avg_out = reinterpret_cast<float*>(my + g.lay.avg[g.parity]) + part.avg_off + lo;
+#pragma unroll
+    for (int r = 0; r < HR_ROWS; ++r) {
+      const int i = hr_elem(r);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[r][k] *= inv_den;
+      if (i + 4 <= n) {
+        if (codec == HB_NONE) *reinterpret_cast<float4*>(avg_out + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        if (i_send) {
+          float4 own = *reinterpret_cast<const float4*>(x_local + i);
+          own.x = fmaf(alpha_own, acc[r][0] - own.x, own.x); own.y = fmaf(alpha_own, acc[r][1] - own.y, own.y);
+          own.z = fmaf(alpha_own, acc[r][2] - own.z, own.z); own.w = fmaf(alpha_own, acc[r][3] - own.w, own.w);
+          *reinterpret_cast<float4*>(x_local + i) = own;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (i + k < n) {
+            if (codec == HB_NONE) avg_out[i + k] = acc[r][k];
+            if (i_send) x_local[i + k] = fmaf(alpha_own, acc[r][k] - x_local[i + k], x_local[i + k]);
+          } else {
+            acc[r][k] = 0.f;
+          }
+        }
+      }
+    }
+    // deltas: avg - decode(copy of the sender's record), encoded over the copy, one sender after the other
+    if (codec != HB_NONE && !dead) {
+      for (int s = 0; s < g.n_peers; ++s) {
+        if (!sh.inc[s]) continue;
+        unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
+        float mean, sd, absmax[HR_BLOCKS] = {};
+        hr_decode_setup(codec, local, sh, g.code, mean, sd, absmax);
+        float d[HR_ROWS][4];
+#pragma unroll
+        for (int r = 0; r < HR_ROWS; ++r) {
+          const int i = hr_elem(r);
+          float o[4];
+          hr_decode_row(codec, local + hdr, i, mean, sd, sh.cb, absmax, o);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) d[r][k] = (i + k < n) ? acc[r][k] - o[k] : 0.f;
+        }
+        __syncthreads();   // every thread has decoded with the old header before anybody writes the new one
+        hr_encode_chunk(d, n, codec, local, sh, g.code);
+      }
+    }
+  }
+  // one lane per sender counts the chunks of its delta; the lane that completes a part publishes its flag
+  __syncthreads();
+  if (threadIdx.x < g.n_peers) {
+    const int s = threadIdx.x;
+    if (s != me && g.sends[s] && hr_chunks_done(g.dpart_done + (size_t)s * g.max_local_parts + j, z, n_chunks)) {
       unsigned int* flag = reinterpret_cast<unsigned int*>(my + g.lay.dready[g.parity]) + (size_t)s * g.max_local_parts + j;
       hm_st_release_sys(flag, (sh.inc[s] && !dead) ? g.epoch : (g.epoch | HB_FAIL_BIT));
     }
   }
 }
 
-__device__ void hr_apply_item(const HrRound& g, int p, int c, HrShared& sh) {
+__device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
   if (!g.sends[g.me]) return;
   const HrPart part = g.parts[p];
   const int me = g.me, owner = part.owner, codec = part.codec;
   if (owner == me) return;   // the reduce item has already applied the average to this GPU's own span
-  const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
-  float* x = reinterpret_cast<float*>(g.base[me] + g.lay.data) + part.start + lo;
-  const unsigned long long deadline = hr_phase_start(g.t_start + 1) + g.reducer_timeout_ns;
-  const size_t fidx = (size_t)me * g.max_local_parts + part.local_idx;
-  const unsigned int* f0 = reinterpret_cast<const unsigned int*>(g.base[owner] + g.lay.dready[0]) + fidx;
-  const unsigned int* f1 = reinterpret_cast<const unsigned int*>(g.base[owner] + g.lay.dready[1]) + fidx;
-  float unused;
-  const int d = hr_wait_decide(reinterpret_cast<const unsigned long long*>(f0), reinterpret_cast<const unsigned long long*>(f1),
-                               false, g.epoch, g.apply_decision + p, nullptr, nullptr, deadline, sh, &unused);
+  if (threadIdx.x == 0) {
+    const size_t fidx = (size_t)me * g.max_local_parts + part.local_idx;
+    const unsigned int* f0 = reinterpret_cast<const unsigned int*>(g.base[owner] + g.lay.dready[0]) + fidx;
+    const unsigned int* f1 = reinterpret_cast<const unsigned int*>(g.base[owner] + g.lay.dready[1]) + fidx;
+    sh.bcast = (int)(unsigned int)hr_decide(reinterpret_cast<const unsigned long long*>(f0), reinterpret_cast<const unsigned long long*>(f1),
+                                            false, g.epoch, g.apply_decision + p, nullptr, g.t_start + 1, g.reducer_timeout_ns);
+  }
+  __syncthreads();
+  const int d = sh.bcast;
   if (d == 2) {
     if (threadIdx.x == 0) {
       atomicOr(g.status + 1, 1ull << owner);
-      atomicAdd(g.status + 2, (unsigned long long)n);
+      atomicAdd(g.status + 2, (unsigned long long)(min((c0 + z) * HR_CHUNK, part.len) - c0 * HR_CHUNK));
     }
     return;   // zero delta: keep the local values
   }
   const int opar = d >> 1;
   const float alpha = g.alpha;
-  if (codec == HB_NONE) {
-    const float* __restrict__ avg = reinterpret_cast<const float*>(g.base[owner] + g.lay.avg[opar]) + part.avg_off + lo;
-    float4 av[HR_ROWS];
+  const long long stride = hr_chunk_stride(codec);
+  const int hdr = hr_header_bytes(codec);
+  for (int c = c0; c < c0 + z; ++c) {
+    const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
+    float* x = reinterpret_cast<float*>(g.base[me] + g.lay.data) + part.start + lo;
+    float dv[HR_ROWS][4];
+    if (codec == HB_NONE) {
+      float4 av[HR_ROWS];
+      hr_load_rows(reinterpret_cast<const float*>(g.base[owner] + g.lay.avg[opar]) + part.avg_off + lo, n, av);
 #pragma unroll
-    for (int r = 0; r < HR_ROWS; ++r) {
-      const int i = hr_elem(r);
-      if (i + 4 <= n) av[r] = *reinterpret_cast<const float4*>(avg + i);
+      for (int r = 0; r < HR_ROWS; ++r) { dv[r][0] = av[r].x; dv[r][1] = av[r].y; dv[r][2] = av[r].z; dv[r][3] = av[r].w; }
+    } else {
+      const unsigned char* rec = g.base[owner] + g.lay.deltabox[opar] + (size_t)me * g.delta_stride + part.span_off + (long long)c * stride;
+      float mean, sd, absmax[HR_BLOCKS] = {};
+      hr_decode_setup(codec, rec, sh, g.code, mean, sd, absmax);
+#pragma unroll
+      for (int r = 0; r < HR_ROWS; ++r) hr_decode_row(codec, rec + hdr, hr_elem(r), mean, sd, sh.cb, absmax, dv[r]);
     }
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
       if (i + 4 <= n) {
         float4 xv = *reinterpret_cast<const float4*>(x + i);
-        xv.x = fmaf(alpha, av[r].x - xv.x, xv.x); xv.y = fmaf(alpha, av[r].y - xv.y, xv.y);
-        xv.z = fmaf(alpha, av[r].z - xv.z, xv.z); xv.w = fmaf(alpha, av[r].w - xv.w, xv.w);
+        if (codec == HB_NONE) {
+          xv.x = fmaf(alpha, dv[r][0] - xv.x, xv.x); xv.y = fmaf(alpha, dv[r][1] - xv.y, xv.y);
+          xv.z = fmaf(alpha, dv[r][2] - xv.z, xv.z); xv.w = fmaf(alpha, dv[r][3] - xv.w, xv.w);
+        } else {
+          xv.x = fmaf(alpha, dv[r][0], xv.x); xv.y = fmaf(alpha, dv[r][1], xv.y);
+          xv.z = fmaf(alpha, dv[r][2], xv.z); xv.w = fmaf(alpha, dv[r][3], xv.w);
+        }
         *reinterpret_cast<float4*>(x + i) = xv;
       } else {
         for (int k = 0; k < 4; ++k)
-          if (i + k < n) x[i + k] = fmaf(alpha, avg[i + k] - x[i + k], x[i + k]);
+          if (i + k < n) x[i + k] = codec == HB_NONE ? fmaf(alpha, dv[r][k] - x[i + k], x[i + k]) : fmaf(alpha, dv[r][k], x[i + k]);
       }
-    }
-    return;
-  }
-  const long long stride = hr_chunk_stride(codec);
-  const int hdr = hr_header_bytes(codec);
-  const unsigned char* rec = g.base[owner] + g.lay.deltabox[opar] + (size_t)me * g.delta_stride + part.span_off + (long long)c * stride;
-  float mean, sd, absmax[HR_BLOCKS] = {};
-  hr_decode_setup(codec, rec, sh, g.code, mean, sd, absmax);
-  float dv[HR_ROWS][4];
-#pragma unroll
-  for (int r = 0; r < HR_ROWS; ++r) hr_decode_row(codec, rec + hdr, hr_elem(r), mean, sd, sh.cb, absmax, dv[r]);
-#pragma unroll
-  for (int r = 0; r < HR_ROWS; ++r) {
-    const int i = hr_elem(r);
-    if (i + 4 <= n) {
-      float4 xv = *reinterpret_cast<const float4*>(x + i);
-      xv.x = fmaf(alpha, dv[r][0], xv.x); xv.y = fmaf(alpha, dv[r][1], xv.y);
-      xv.z = fmaf(alpha, dv[r][2], xv.z); xv.w = fmaf(alpha, dv[r][3], xv.w);
-      *reinterpret_cast<float4*>(x + i) = xv;
-    } else {
-      for (int k = 0; k < 4; ++k)
-        if (i + k < n) x[i + k] = fmaf(alpha, dv[r][k], x[i + k]);
     }
   }
 }
@@ -754,8 +773,8 @@ __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_co
     __syncthreads();
     const int4 it = g.items[idx];
     if (idx < g.n_send) hr_send_item(g, it.x, it.y, it.z, sh);
-    else if (idx < g.n_send + g.n_reduce) hr_reduce_item(g, it.x, it.y, sh);
-    else hr_apply_item(g, it.x, it.y, sh);
+    else if (idx < g.n_send + g.n_reduce) hr_reduce_item(g, it.x, it.y, it.z, sh);
+    else hr_apply_item(g, it.x, it.y, it.z, sh);
   }
   // the last CTA to leave closes the round: acknowledges that this GPU has finished reading its groupmates'
   // arenas, hands the status words to the host and clears the scratch for the next round
@@ -771,8 +790,8 @@ __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_co
   __threadfence();
   if (threadIdx.x < 4) g.status_out[threadIdx.x] = *reinterpret_cast<volatile unsigned long long*>(g.status + threadIdx.x);
   __syncthreads();
-  for (int i = threadIdx.x; i < g.max_local_parts * HR_MAX_PEERS; i += HR_THREADS) { g.include[i] = 0; g.dpart_done[i] = 0; }
-  for (int i = threadIdx.x; i < g.n_parts; i += HR_THREADS) { g.apply_decision[i] = 0; g.part_done[i] = 0; }
+  for (int i = threadIdx.x; i < g.max_local_parts * HR_MAX_PEERS; i += HR_THREADS) { g.include[i] = 0ull; g.dpart_done[i] = 0; }
+  for (int i = threadIdx.x; i < g.n_parts; i += HR_THREADS) { g.apply_decision[i] = 0ull; g.part_done[i] = 0; }
   if (threadIdx.x < HR_MAX_PEERS) g.ban[threadIdx.x] = 0;
   if (threadIdx.x < 2) g.t_start[threadIdx.x] = 0;
   if (threadIdx.x < 4) g.status[threadIdx.x] = 0;

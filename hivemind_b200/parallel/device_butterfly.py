@@ -51,6 +51,8 @@ MAX_PEERS = 16
 ALIGN = 16  # elements: tensor starts and part boundaries are multiples of this, so every access is 16-byte aligned
 CHUNK = 8192  # elements per chunk record (HR_CHUNK in butterfly_round.cu)
 ACK_RING = 8
+CTAS_PER_SM = 2  # the round kernel keeps two 512-thread CTAs on every SM
+ITEM_CHUNKS = int(os.environ.get("HIVEMIND_B200_ITEM_CHUNKS", "0"))  # chunks per work item; 0 = chosen per layout
 DELTA_BOX_FACTOR = 1.5  # delta box capacity relative to the outbox: 1.0 suffices for equal spans
 _CODEC_IDS = {NoCompression: 0, ScaledFloat16Compression: 1, Float16Compression: 2, Quantile8BitQuantization: 3,
               Uniform8BitQuantization: 4, BlockwiseQuantization: 5}
@@ -97,8 +99,7 @@ class _HrRound(ctypes.Structure):
                 ("items", ctypes.c_void_p), ("pub_list", ctypes.c_void_p), ("n_send", ctypes.c_int),
                 ("n_reduce", ctypes.c_int), ("n_apply", ctypes.c_int), ("item_begin", ctypes.c_int),
                 ("item_end", ctypes.c_int), ("queue_slot", ctypes.c_int), ("final_stage", ctypes.c_int),
-                ("include", ctypes.c_void_p), ("weights", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p),
-                ("ban", ctypes.c_void_p),
+                ("include", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p),
                 ("t_start", ctypes.c_void_p), ("status", ctypes.c_void_p), ("status_out", ctypes.c_void_p),
                 ("part_done", ctypes.c_void_p), ("dpart_done", ctypes.c_void_p), ("queue", ctypes.c_void_p),
                 ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint)]
@@ -182,6 +183,7 @@ class _Plan:
     needed_outbox: int
     needed_delta: int
     needed_avg: int
+    rounds: Dict[Tuple, "_HrRound"] = field(default_factory=dict)  # parameter blocks by (groupmates, timeouts)
 
 
 def _interleave_by_owner(items: List[Tuple[int, int, int, int]], owners: List[int], first_owner: int,
@@ -320,6 +322,9 @@ class DeviceEndpoint:
         self._history: Dict[int, Tuple[int, List[int]]] = {}  # parity -> (epoch, bases of that round's groupmates)
         self._sms = _lib.sm_count(self.device)
         self.fault_publish_half = False  # host-side fault injection: publish only the first half of the parts sent
+        self._gate = _HrGate()  # the gate kernel's parameter block (launches copy it, so one instance serves all rounds)
+        self._gate.lay = self._layout_struct()
+        self._gate.gate_status = self._gate_status.data_ptr()
 
     # ---------------------------------------------------------------------------------------------- handles
     def describe(self) -> Optional[dict]:
@@ -432,8 +437,17 @@ class DeviceEndpoint:
         delta_stride = (max(span_bytes) + 255) // 256 * 256
         needed_delta = n_peers * delta_stride
 
-        def chunks_of(p):
-            return range((int(table[p]["len"]) + CHUNK - 1) // CHUNK)
+        def n_chunks(p):
+            return (int(table[p]["len"]) + CHUNK - 1) // CHUNK
+
+        # an item is a run of consecutive chunks of one part: long enough to spread the cost of looking up flags and
+        # of the fence behind its results, short enough that every CTA of the grid gets several items per stage
+        busiest = max(sum(n_chunks(p) for p in range(n_parts) if table[p]["owner"] == r) for r in range(n_peers))
+        run = ITEM_CHUNKS if ITEM_CHUNKS > 0 else max(1, min(8, busiest // (CTAS_PER_SM * self._sms * 6)))
+
+        def runs_of(p):
+            total = n_chunks(p)
+            return [(p, c, min(run, total - c), 0) for c in range(0, total, run)]
 
         i_send = sends[my_index]
         mine = [p for p in range(n_parts) if table[p]["owner"] == my_index]
@@ -454,17 +468,17 @@ class DeviceEndpoint:
                     send_items.append((-1, len(pub_list), 1, 0))
                 pub_list.append(p)
             else:
-                send_items += [(p, c, 0, 0) for c in chunks_of(p)]
-        reduce_items = [(p, c, 0, 0) for p in mine for c in chunks_of(p)]
-        apply_items = _interleave_by_owner([(p, c, 0, 0) for p in theirs for c in chunks_of(p)],
-                                           [int(table[p]["owner"]) for p in theirs for _ in chunks_of(p)],
+                send_items += runs_of(p)
+        reduce_items = [item for p in mine for item in runs_of(p)]
+        apply_items = _interleave_by_owner([item for p in theirs for item in runs_of(p)],
+                                           [int(table[p]["owner"]) for p in theirs for _ in runs_of(p)],
                                            first_owner=(my_index + 1) % n_peers, n_peers=n_peers)
         items = send_items + reduce_items + apply_items
         items_dev = torch.tensor(items if items else [(0, 0, 0, 0)], dtype=torch.int32).to(self.device)
         pub_dev = torch.tensor(pub_list if pub_list else [0], dtype=torch.int32).to(self.device)
         parts_dev = torch.from_numpy(table.view(np.uint8).copy()).to(self.device)
         slots = MAX_PEERS * max_local
-        sizes = [("include", slots * 4), ("weights", slots * 4), ("dpart_done", slots * 4), ("apply_decision", n_parts * 4),
+        sizes = [("include", slots * 8), ("dpart_done", slots * 4), ("apply_decision", n_parts * 8),
                  ("part_done", n_parts * 4), ("ban", MAX_PEERS * 4), ("t_start", 16), ("status", 32), ("queue", 16)]
         total = sum((b + 255) // 256 * 256 for _, b in sizes)
         blob = torch.zeros(total, dtype=torch.uint8, device=self.device)
@@ -491,39 +505,49 @@ class DeviceEndpoint:
 
     def _prepare(self, *, group_id: bytes, my_index: int, device_infos, modes, peer_fractions, weight: float, alpha,
                  sender_timeout, reducer_timeout) -> Tuple[_Plan, _HrRound, List[int]]:
-        """Part table, work list and the kernel parameter block of one round; also advances the round counter."""
+        """Part table, work list and the kernel parameter block of one round; also advances the round counter.
+
+        The parameter block of a (layout, groupmates, timeouts) combination is built once and kept: a later round of
+        the same combination only changes the epoch, the parity and the weights."""
         n = len(device_infos)
         sends = [m != AveragingMode.AUX for m in modes]
         plan = self._make_plan(n, my_index, peer_fractions, sends)
-        if plan.needed_outbox > self.cap_outbox or plan.needed_delta > self.cap_delta or plan.needed_avg > self.cap_avg:
-            raise RuntimeError("the staging areas of the arenas are too small for this group layout")
         bases = self.map_group(device_infos, my_index)
-        sender_timeout = min(sender_timeout if sender_timeout else 10.0, 20.0)
-        reducer_timeout = max(min(reducer_timeout if reducer_timeout else 2 * sender_timeout, 40.0), 2 * sender_timeout)
-        g = _HrRound()
-        g.n_peers, g.n_parts, g.me, g.max_local_parts = n, plan.n_parts, my_index, plan.max_local_parts
+        key = (tuple(bases), sender_timeout, reducer_timeout)
+        template = plan.rounds.get(key)
+        if template is None:
+            if plan.needed_outbox > self.cap_outbox or plan.needed_delta > self.cap_delta or plan.needed_avg > self.cap_avg:
+                raise RuntimeError("the staging areas of the arenas are too small for this group layout")
+            sender_timeout = min(sender_timeout if sender_timeout else 10.0, 20.0)
+            reducer_timeout = max(min(reducer_timeout if reducer_timeout else 2 * sender_timeout, 40.0), 2 * sender_timeout)
+            g = _HrRound()
+            g.n_peers, g.n_parts, g.me, g.max_local_parts = n, plan.n_parts, my_index, plan.max_local_parts
+            g.sender_timeout_ns, g.reducer_timeout_ns = int(sender_timeout * 1e9), int(reducer_timeout * 1e9)
+            g.delta_stride = plan.delta_stride
+            for r in range(n):
+                g.sends[r] = int(sends[r])
+                g.base[r] = bases[r]
+            g.lay = self._layout_struct()
+            g.parts, g.items, g.pub_list = plan.parts_dev.data_ptr(), plan.items_dev.data_ptr(), plan.pub_dev.data_ptr()
+            g.n_send, g.n_reduce, g.n_apply = plan.n_send, plan.n_reduce, plan.n_apply
+            for name in ("include", "apply_decision", "ban", "t_start", "status", "part_done", "dpart_done", "queue"):
+                setattr(g, name, plan.scratch[name].data_ptr())
+            g.status_out = self._status_out.data_ptr()
+            g.code = self._code.data_ptr()
+            if len(plan.rounds) > 8:
+                plan.rounds.pop(next(iter(plan.rounds)))
+            plan.rounds[key] = template = g
+        g = _HrRound.from_buffer_copy(template)  # rounds may overlap (one being finished while the next is prepared)
+        g.item_begin, g.item_end, g.queue_slot, g.final_stage = 0, plan.n_send + plan.n_reduce + plan.n_apply, 0, 1
         g.epoch = (zlib.crc32(group_id) & 0x7FFFFFFF) | 1
         g.parity = self._round_seq & 1
         g.done_slot = self._round_seq
         g.alpha, g.my_weight = alpha, float(weight)
-        g.sender_timeout_ns, g.reducer_timeout_ns = int(sender_timeout * 1e9), int(reducer_timeout * 1e9)
-        g.delta_stride = plan.delta_stride
-        for r in range(n):
-            g.sends[r] = int(sends[r])
-            g.base[r] = bases[r]
-        g.lay = self._layout_struct()
-        g.parts, g.items, g.pub_list = plan.parts_dev.data_ptr(), plan.items_dev.data_ptr(), plan.pub_dev.data_ptr()
-        g.n_send, g.n_reduce, g.n_apply = plan.n_send, plan.n_reduce, plan.n_apply
-        g.item_begin, g.item_end, g.queue_slot, g.final_stage = 0, plan.n_send + plan.n_reduce + plan.n_apply, 0, 1
-        for name in ("include", "weights", "apply_decision", "ban", "t_start", "status", "part_done", "dpart_done", "queue"):
-            setattr(g, name, plan.scratch[name].data_ptr())
-        g.status_out = self._status_out.data_ptr()
-        g.code = self._code.data_ptr()
         self._round_seq += 1
         return plan, g, bases
 
     def _gate_params(self, g: _HrRound, bases: List[int], sender_timeout_ns: int) -> _HrGate:
-        gate = _HrGate()
+        gate = self._gate
         gate.n_peers, gate.me, gate.parity, gate.epoch = g.n_peers, g.me, g.parity, g.epoch
         prev_epoch, prev_bases = self._history.get(g.parity, (0, []))
         gate.prev_epoch, gate.n_prev = prev_epoch, len(prev_bases)
@@ -533,8 +557,6 @@ class DeviceEndpoint:
             gate.base[r] = bases[r]
         gate.ack_timeout_ns = min(int(g.reducer_timeout_ns), int(2e9))
         gate.hello_timeout_ns = sender_timeout_ns
-        gate.lay = g.lay
-        gate.gate_status = self._gate_status.data_ptr()
         self._history[g.parity] = (g.epoch, [b for r, b in enumerate(bases) if r != g.me][:MAX_PEERS])
         return gate
 
@@ -543,7 +565,7 @@ class DeviceEndpoint:
         if end <= begin and not final:
             return
         with torch.cuda.device(self.device):
-            code = self.lib.hm_br_round(ctypes.byref(g), 2 * self._sms, stream)
+            code = self.lib.hm_br_round(ctypes.byref(g), CTAS_PER_SM * self._sms, stream)
         _lib.check(code, f"hm_br_round({name})")
         if self.launch_hook is not None:
             self.launch_hook(name)  # benchmarks record an event after every launch of a round
