@@ -94,11 +94,16 @@ class AlbertLayer(nn.Module):
         nh = self.num_heads
         qkv = linear(x, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight))
         ctx = attention(qkv, nh)  # reads the packed projections, writes [b, s, h]: no transposes around it
-        attn = linear(ctx, self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight))
-        x = layer_norm(attn, self.attn_ln_weight, self.attn_ln_bias, self.eps, residual=x)
+        # the biases in front of the two LayerNorms get their gradients from the LayerNorm backward pass
+        attn = linear(ctx, self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight),
+                      skip_bias_grad=True)
+        x = layer_norm(attn, self.attn_ln_weight, self.attn_ln_bias, self.eps, residual=x,
+                       producer_bias=self.attn_out_bias)
         inter = linear(x, self.ffn_weight, self.ffn_bias, activation="gelu", weight_lp=lp.get(self.ffn_weight))
-        out = linear(inter, self.ffn_out_weight, self.ffn_out_bias, weight_lp=lp.get(self.ffn_out_weight))
-        return layer_norm(out, self.ffn_ln_weight, self.ffn_ln_bias, self.eps, residual=x)
+        out = linear(inter, self.ffn_out_weight, self.ffn_out_bias, weight_lp=lp.get(self.ffn_out_weight),
+                     skip_bias_grad=True)
+        return layer_norm(out, self.ffn_ln_weight, self.ffn_ln_bias, self.eps, residual=x,
+                          producer_bias=self.ffn_out_bias)
 
 
 class AlbertForMaskedLM(nn.Module):

@@ -138,12 +138,14 @@ struct HrShared {
   float hsum[HR_THREADS / 64][256];     // per warp-pair bin sums and counts: a skewed distribution would otherwise
   int hcnt[HR_THREADS / 64][256];       //   serialise the whole CTA on a handful of addresses
   float smp[HR_SAMPLE];
+  float code[256];                      // block-wise code and the midpoints between its entries: loaded once per CTA
+  float mid[256];
   float w[HR_MAX_PEERS];
   int inc[HR_MAX_PEERS];
   int par[HR_MAX_PEERS];
-  int item;
+  int order[HR_MAX_PEERS];              // included senders in this reducer's rotation order
+  int n_inc;
   int bcast;
-  unsigned long long bcast64;
 };
 
 // element index inside the chunk handled by (row r, thread, k)
@@ -168,42 +170,10 @@ __device__ __forceinline__ void hr_block_reduce(float (&v)[N], HrShared& sh) {
   }
 }
 
-// Decode this thread's 32 elements of a chunk record (header already consumed by the caller: `cb` holds the
-// codebook for the 8-bit codecs, mean / std / block maxima are passed in).
-__device__ __forceinline__ void hr_decode_row(int codec, const unsigned char* payload, int i, float mean, float sd,
-                                              const float* cb, const float* absmax, float out[4]) {
-  switch (codec) {
-    case HB_FLOAT16:
-    case HB_MEANSTD16: {
-      const uint2 x = *reinterpret_cast<const uint2*>(payload + (size_t)i * 2);
-      const __half2 a = *reinterpret_cast<const __half2*>(&x.x), b = *reinterpret_cast<const __half2*>(&x.y);
-      out[0] = __low2float(a); out[1] = __high2float(a); out[2] = __low2float(b); out[3] = __high2float(b);
-      if (codec == HB_MEANSTD16) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) out[k] = fmaf(out[k], sd, mean);
-      }
-      return;
-    }
-    case HB_UNIFORM8:
-    case HB_QUANTILE8: {
-      const uchar4 q = *reinterpret_cast<const uchar4*>(payload + i);
-      out[0] = cb[q.x]; out[1] = cb[q.y]; out[2] = cb[q.z]; out[3] = cb[q.w];
-      return;
-    }
-    default: {  // HB_BLOCKWISE8
-      const uchar4 q = *reinterpret_cast<const uchar4*>(payload + i);
-      const float a = absmax[i / HB_BLOCK];
-      out[0] = cb[q.x] * a; out[1] = cb[q.y] * a; out[2] = cb[q.z] * a; out[3] = cb[q.w] * a;
-      return;
-    }
-  }
-}
-
 // Encode the chunk held in registers (v[r][k] = element hr_elem(r) + k, elements >= n are zero) into `rec`
 // (header + payload). Every thread of the CTA calls this. Elements >= n still get payload bytes (of value zero or
 // whatever zero maps to); they are never decoded.
-__device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, unsigned char* rec, HrShared& sh,
-                                const float* code_tables) {
+__device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, unsigned char* rec, HrShared& sh) {
   unsigned char* payload = rec + hr_header_bytes(codec);
   if (codec == HB_FLOAT16) {
 #pragma unroll
@@ -364,8 +334,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
 #pragma unroll
         for (int k = 0; k < 4; ++k) m[b] = fmaxf(m[b], fabsf(v[RPB * b + rr][k]));
     }
-    if (threadIdx.x < 256) sh.table[threadIdx.x] = code_tables[256 + threadIdx.x];
-    hr_block_reduce<HR_BLOCKS, true>(m, sh);   // also orders the table writes before the reads below
+    hr_block_reduce<HR_BLOCKS, true>(m, sh);
     if (threadIdx.x < HR_BLOCKS) reinterpret_cast<float*>(rec)[threadIdx.x] = m[threadIdx.x];
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
@@ -373,30 +342,102 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       const float inv = 1.f / fmaxf(m[r / RPB], 1.17549435e-38f);
       unsigned char q[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) q[k] = (unsigned char)hb_bucketize(sh.table, v[r][k] * inv);
+      for (int k = 0; k < 4; ++k) q[k] = (unsigned char)hb_bucketize(sh.mid, v[r][k] * inv);
       *reinterpret_cast<uchar4*>(payload + i) = make_uchar4(q[0], q[1], q[2], q[3]);
     }
   }
 }
 
-// Load what decoding a chunk record needs besides the payload: the codebook into shared memory, scalars into
-// registers. Every thread calls this; it ends with a barrier.
-__device__ __forceinline__ void hr_decode_setup(int codec, const unsigned char* rec, HrShared& sh, const float* code_tables,
-                                                float& mean, float& sd, float absmax[HR_BLOCKS]) {
+// What a thread holds of a chunk that it has requested ahead of time: its rows of the payload (or of the fp32 vector
+// for uncompressed parts) and its share of the header. Remote reads are issued one chunk before they are used, so
+// that NVLink latency is spent while the CTA works on the previous chunk.
+struct HrAhead {
+  uint32_t w[HR_ROWS * 4];   // uncompressed: HR_ROWS float4; 16-bit codecs: HR_ROWS uint2; 8-bit codecs: HR_ROWS words
+  float4 hdr;                // 16-byte headers whole (every thread); 1 KB codebooks: entry threadIdx.x in hdr.x
+};
+
+__device__ __forceinline__ void hr_fetch(int codec, const unsigned char* src, int n, HrAhead& a) {
+  if (codec == HB_NONE) {
+    const float* x = reinterpret_cast<const float*>(src);
+#pragma unroll
+    for (int r = 0; r < HR_ROWS; ++r) {
+      const int i = hr_elem(r);
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i + 4 <= n) {
+        t = *reinterpret_cast<const float4*>(x + i);
+      } else {
+        if (i < n) t.x = x[i];
+        if (i + 1 < n) t.y = x[i + 1];
+        if (i + 2 < n) t.z = x[i + 2];
+      }
+      a.w[4 * r] = __float_as_uint(t.x); a.w[4 * r + 1] = __float_as_uint(t.y);
+      a.w[4 * r + 2] = __float_as_uint(t.z); a.w[4 * r + 3] = __float_as_uint(t.w);
+    }
+    return;
+  }
+  const int hdr = hr_header_bytes(codec);
+  if (hdr == 1024) {
+    if (threadIdx.x < 256) a.hdr.x = reinterpret_cast<const float*>(src)[threadIdx.x];
+  } else if (hdr == 16) {
+    a.hdr = *reinterpret_cast<const float4*>(src);
+  }
+  if (hb_elem_bytes(codec) == 2) {
+#pragma unroll
+    for (int r = 0; r < HR_ROWS; ++r) {
+      const uint2 t = *reinterpret_cast<const uint2*>(src + hdr + (size_t)hr_elem(r) * 2);
+      a.w[2 * r] = t.x; a.w[2 * r + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < HR_ROWS; ++r) a.w[r] = *reinterpret_cast<const uint32_t*>(src + hdr + hr_elem(r));
+  }
+}
+
+// Make a fetched record decodable: the codebook of an 8-bit record goes to shared memory (two barriers), the scalars of
+// the other headers are handed back in registers. `copy` (optional) receives the header as well.
+__device__ __forceinline__ void hr_open(int codec, const HrAhead& a, HrShared& sh, unsigned char* copy, float& mean, float& sd,
+                                        float absmax[HR_BLOCKS]) {
   mean = 0.f;
   sd = 1.f;
-  __syncthreads();   // the previous user of sh.cb is done
-  if (codec == HB_MEANSTD16) {
-    mean = reinterpret_cast<const float*>(rec)[0];
-    sd = reinterpret_cast<const float*>(rec)[1];
-  } else if (codec == HB_UNIFORM8 || codec == HB_QUANTILE8) {
-    if (threadIdx.x < 256) sh.cb[threadIdx.x] = reinterpret_cast<const float*>(rec)[threadIdx.x];
-  } else if (codec == HB_BLOCKWISE8) {
-    if (threadIdx.x < 256) sh.cb[threadIdx.x] = code_tables[threadIdx.x];
-#pragma unroll
-    for (int b = 0; b < HR_BLOCKS; ++b) absmax[b] = reinterpret_cast<const float*>(rec)[b];
+  if (codec == HB_UNIFORM8 || codec == HB_QUANTILE8) {
+    __syncthreads();   // the previous user of sh.cb is done
+    if (threadIdx.x < 256) {
+      sh.cb[threadIdx.x] = a.hdr.x;
+      if (copy) reinterpret_cast<float*>(copy)[threadIdx.x] = a.hdr.x;
+    }
+    __syncthreads();
+    return;
   }
-  __syncthreads();
+  if (codec == HB_MEANSTD16) {
+    mean = a.hdr.x;
+    sd = a.hdr.y;
+  } else if (codec == HB_BLOCKWISE8) {
+    absmax[0] = a.hdr.x;
+    if (HR_BLOCKS > 1) absmax[HR_BLOCKS - 1] = a.hdr.y;
+  }
+  if (copy && threadIdx.x == 0 && hr_header_bytes(codec) == 16) *reinterpret_cast<float4*>(copy) = a.hdr;
+}
+
+// Decode row r of a fetched record.
+__device__ __forceinline__ void hr_decode_ahead(int codec, const HrAhead& a, int r, float mean, float sd, const HrShared& sh,
+                                                const float* absmax, float out[4]) {
+  if (codec == HB_NONE) {
+    out[0] = __uint_as_float(a.w[4 * r]); out[1] = __uint_as_float(a.w[4 * r + 1]);
+    out[2] = __uint_as_float(a.w[4 * r + 2]); out[3] = __uint_as_float(a.w[4 * r + 3]);
+  } else if (hb_elem_bytes(codec) == 2) {
+    const __half2 lo = *reinterpret_cast<const __half2*>(&a.w[2 * r]), hi = *reinterpret_cast<const __half2*>(&a.w[2 * r + 1]);
+    out[0] = __low2float(lo); out[1] = __high2float(lo); out[2] = __low2float(hi); out[3] = __high2float(hi);
+    if (codec == HB_MEANSTD16) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[k] = fmaf(out[k], sd, mean);
+    }
+  } else {
+    const uint32_t q = a.w[r];
+    const float* cb = codec == HB_BLOCKWISE8 ? sh.code : sh.cb;
+    const float m = codec == HB_BLOCKWISE8 ? absmax[r / (HR_ROWS / HR_BLOCKS)] : 1.f;
+    out[0] = cb[q & 255u] * m; out[1] = cb[(q >> 8) & 255u] * m;
+    out[2] = cb[(q >> 16) & 255u] * m; out[3] = cb[q >> 24] * m;
+  }
 }
 
 __device__ __forceinline__ unsigned long long hr_ld_acquire_gpu_u64(const unsigned long long* p) {
@@ -495,26 +536,11 @@ __device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& s
       }
     }
     if (c != c0) __syncthreads();   // the previous chunk's encoder is done with the shared tables
-    hr_encode_chunk(v, n, part.codec, my + g.lay.outbox[g.parity] + part.enc_off + (long long)c * stride, sh, g.code);
+    hr_encode_chunk(v, n, part.codec, my + g.lay.outbox[g.parity] + part.enc_off + (long long)c * stride, sh);
   }
   const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
   __syncthreads();
   if (threadIdx.x == 0 && hr_chunks_done(g.part_done + p, z, n_chunks)) hr_st_release_sys_u64(ready + p, flag);
-}
-
-__device__ __forceinline__ void hr_load_rows(const float* __restrict__ src, int n, float4 (&rv)[HR_ROWS]) {
-#pragma unroll
-  for (int r = 0; r < HR_ROWS; ++r) {
-    const int i = hr_elem(r);
-    if (i + 4 <= n) {
-      rv[r] = *reinterpret_cast<const float4*>(src + i);
-    } else {
-      rv[r].x = i < n ? src[i] : 0.f;
-      rv[r].y = i + 1 < n ? src[i + 1] : 0.f;
-      rv[r].z = i + 2 < n ? src[i + 2] : 0.f;
-      rv[r].w = 0.f;
-    }
-  }
 }
 
 __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
@@ -522,9 +548,12 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
   const int codec = part.codec, j = part.local_idx, me = g.me;
   const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
   unsigned char* my = g.base[me];
+  // every reducer walks the senders in its own rotation, so that at any moment the reducers of a group read from
+  // different GPUs instead of all draining the same sender's links
+  const int rot = (me + 1) % g.n_peers;
 
   // one lane per sender waits for (or looks up the decision about) that sender's flag
-  if (threadIdx.x < HR_MAX_PEERS) {
+  if (threadIdx.x < 32) {
     const int s = threadIdx.x;
     int inc = 0, par = 0;
     float w = 0.f;
@@ -542,106 +571,78 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
         atomicOr(g.status, 1ull << s);
       }
     }
-    sh.inc[s] = inc;
-    sh.par[s] = par;
-    sh.w[s] = w;
+    if (s < HR_MAX_PEERS) {
+      sh.inc[s] = inc;
+      sh.par[s] = par;
+      sh.w[s] = w;
+    }
+    const unsigned int mask = __ballot_sync(0xffffffffu, inc != 0);
+    if (s == 0) {
+      int k = 0;
+      for (int t = 0; t < g.n_peers; ++t) {
+        const int q = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
+        if (mask >> q & 1u) sh.order[k++] = q;
+      }
+      sh.n_inc = k;
+    }
   }
   __syncthreads();
 
   const bool i_send = g.sends[me] != 0;
+  const int n_inc = sh.n_inc;
   float den = i_send ? g.my_weight : 0.f;
-  for (int s = 0; s < g.n_peers; ++s) if (sh.inc[s]) den += sh.w[s];
+  for (int k = 0; k < n_inc; ++k) den += sh.w[sh.order[k]];
   // a total weight of zero (every member tagging along) averages nothing: values stay, deltas are reported as failed
   const bool dead = !(den > 0.f);
   const float inv_den = dead ? 0.f : 1.f / den;
   const float alpha_own = dead ? 0.f : g.alpha;
   const long long stride = hr_chunk_stride(codec);
   const int hdr = hr_header_bytes(codec);
-  // every reducer walks the senders in its own rotation, so that at any moment the reducers of a group read from
-  // different GPUs instead of all draining the same sender's links
-  const int rot = (me + 1) % g.n_peers;
-  // uncompressed parts: the first sender's rows of the NEXT chunk are requested before this chunk's results are
-  // written, which keeps remote reads in flight while the CTA is busy with local memory
-  int first = -1;
-  if (codec == HB_NONE) {
-    for (int t = 0; t < g.n_peers && first < 0; ++t) {
-      const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
-      if (sh.inc[s]) first = s;
-    }
-  }
-  float4 ahead[HR_ROWS];
-  if (first >= 0)
-    hr_load_rows(reinterpret_cast<const float*>(g.base[first] + g.lay.data) + part.start + c0 * HR_CHUNK,
-                 min(HR_CHUNK, part.len - c0 * HR_CHUNK), ahead);
+
+  // where sender s keeps chunk c of this part
+  auto source = [&](int s, int c) -> const unsigned char* {
+    if (codec == HB_NONE) return g.base[s] + g.lay.data + (size_t)(part.start + (long long)c * HR_CHUNK) * 4;
+    return g.base[s] + g.lay.outbox[sh.par[s]] + part.enc_off + (long long)c * stride;
+  };
+  auto chunk_len = [&](int c) { return min(HR_CHUNK, part.len - c * HR_CHUNK); };
+  const int total = z * n_inc;
+  HrAhead ahead;
+  if (total > 0) hr_fetch(codec, source(sh.order[0], c0), chunk_len(c0), ahead);
 
   for (int c = c0; c < c0 + z; ++c) {
-    const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
+    const int lo = c * HR_CHUNK, n = chunk_len(c);
     float* x_local = reinterpret_cast<float*>(my + g.lay.data) + part.start + lo;
     float acc[HR_ROWS][4];
-    {
-      float4 own[HR_ROWS];
-      if (i_send) hr_load_rows(x_local, n, own);
 #pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) {
-        acc[r][0] = i_send ? g.my_weight * own[r].x : 0.f; acc[r][1] = i_send ? g.my_weight * own[r].y : 0.f;
-        acc[r][2] = i_send ? g.my_weight * own[r].z : 0.f; acc[r][3] = i_send ? g.my_weight * own[r].w : 0.f;
-      }
+    for (int r = 0; r < HR_ROWS; ++r) {
+      const int i = hr_elem(r);
+      float4 own = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i_send && i + 4 <= n) own = *reinterpret_cast<const float4*>(x_local + i);
+      acc[r][0] = g.my_weight * own.x; acc[r][1] = g.my_weight * own.y;
+      acc[r][2] = g.my_weight * own.z; acc[r][3] = g.my_weight * own.w;
     }
-    for (int t = 0; t < g.n_peers; ++t) {
-      const int s = rot + t < g.n_peers ? rot + t : rot + t - g.n_peers;
-      if (!sh.inc[s]) continue;
+    for (int k = 0; k < n_inc; ++k) {
+      const int s = sh.order[k];
       const float w = sh.w[s];
-      if (codec == HB_NONE) {
-        float4 rv[HR_ROWS];
-        if (s == first) {
-#pragma unroll
-          for (int r = 0; r < HR_ROWS; ++r) rv[r] = ahead[r];
-          if (c + 1 < c0 + z)
-            hr_load_rows(reinterpret_cast<const float*>(g.base[s] + g.lay.data) + part.start + lo + HR_CHUNK,
-                         min(HR_CHUNK, part.len - lo - HR_CHUNK), ahead);
-        } else {
-          hr_load_rows(reinterpret_cast<const float*>(g.base[s] + g.lay.data) + part.start + lo, n, rv);
-        }
-#pragma unroll
-        for (int r = 0; r < HR_ROWS; ++r) {
-          acc[r][0] = fmaf(w, rv[r].x, acc[r][0]); acc[r][1] = fmaf(w, rv[r].y, acc[r][1]);
-          acc[r][2] = fmaf(w, rv[r].z, acc[r][2]); acc[r][3] = fmaf(w, rv[r].w, acc[r][3]);
-        }
-        continue;
+      const HrAhead cur = ahead;
+      {   // request the next (chunk, sender) before working on this one
+        const int k2 = k + 1 < n_inc ? k + 1 : 0, c2 = k + 1 < n_inc ? c : c + 1;
+        if (c2 < c0 + z) hr_fetch(codec, source(sh.order[k2], c2), chunk_len(c2), ahead);
       }
-      // compressed: pull the sender's chunk record once, keep a copy where its delta will be written
-      const unsigned char* remote = g.base[s] + g.lay.outbox[sh.par[s]] + part.enc_off + (long long)c * stride;
       unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
       float mean, sd, absmax[HR_BLOCKS] = {};
-      hr_decode_setup(codec, remote, sh, g.code, mean, sd, absmax);
-      if (hdr == 1024) {
-        if (threadIdx.x < 256) reinterpret_cast<float*>(local)[threadIdx.x] = sh.cb[threadIdx.x];
-      } else if (hdr == 16 && threadIdx.x < 4) {   // mean / std or block maxima: one 16-byte header
-        reinterpret_cast<float*>(local)[threadIdx.x] = reinterpret_cast<const float*>(remote)[threadIdx.x];
-      }
-      if (hb_elem_bytes(codec) == 2) {
-        uint2 raw[HR_ROWS];
+      hr_open(codec, cur, sh, codec == HB_NONE ? nullptr : local, mean, sd, absmax);
 #pragma unroll
-        for (int r = 0; r < HR_ROWS; ++r) raw[r] = *reinterpret_cast<const uint2*>(remote + hdr + (size_t)hr_elem(r) * 2);
+      for (int r = 0; r < HR_ROWS; ++r) {
+        // compressed records: keep a copy where this sender's delta will be written
+        if (hb_elem_bytes(codec) == 2)
+          *reinterpret_cast<uint2*>(local + hdr + (size_t)hr_elem(r) * 2) = make_uint2(cur.w[2 * r], cur.w[2 * r + 1]);
+        else if (hb_elem_bytes(codec) == 1)
+          *reinterpret_cast<uint32_t*>(local + hdr + hr_elem(r)) = cur.w[r];
+        float o[4];
+        hr_decode_ahead(codec, cur, r, mean, sd, sh, absmax, o);
 #pragma unroll
-        for (int r = 0; r < HR_ROWS; ++r) {
-          *reinterpret_cast<uint2*>(local + hdr + (size_t)hr_elem(r) * 2) = raw[r];
-          const __half2 a = *reinterpret_cast<const __half2*>(&raw[r].x), b = *reinterpret_cast<const __half2*>(&raw[r].y);
-          float o[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) acc[r][k] = fmaf(w, fmaf(o[k], sd, mean), acc[r][k]);
-        }
-      } else {
-        uchar4 raw[HR_ROWS];
-#pragma unroll
-        for (int r = 0; r < HR_ROWS; ++r) raw[r] = *reinterpret_cast<const uchar4*>(remote + hdr + hr_elem(r));
-#pragma unroll
-        for (int r = 0; r < HR_ROWS; ++r) {
-          *reinterpret_cast<uchar4*>(local + hdr + hr_elem(r)) = raw[r];
-          const float a = codec == HB_BLOCKWISE8 ? absmax[r / (HR_ROWS / HR_BLOCKS)] : 1.f;
-          acc[r][0] = fmaf(w, sh.cb[raw[r].x] * a, acc[r][0]); acc[r][1] = fmaf(w, sh.cb[raw[r].y] * a, acc[r][1]);
-          acc[r][2] = fmaf(w, sh.cb[raw[r].z] * a, acc[r][2]); acc[r][3] = fmaf(w, sh.cb[raw[r].w] * a, acc[r][3]);
-        }
+        for (int q = 0; q < 4; ++q) acc[r][q] = fmaf(w, o[q], acc[r][q]);
       }
     }
     // the average; applied to this reducer's own values right here
@@ -650,8 +651,8 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc[r][k] *= inv_den;
-      if (i + 4 <= n) {
+      for (int q = 0; q < 4; ++q) acc[r][q] = (i + q < n) ? acc[r][q] * inv_den : 0.f;
+      if (i + 4 <= n) {   // parts are whole multiples of four elements
         if (codec == HB_NONE) *reinterpret_cast<float4*>(avg_out + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
         if (i_send) {
           float4 own = *reinterpret_cast<const float4*>(x_local + i);
@@ -659,36 +660,29 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
           own.z = fmaf(alpha_own, acc[r][2] - own.z, own.z); own.w = fmaf(alpha_own, acc[r][3] - own.w, own.w);
           *reinterpret_cast<float4*>(x_local + i) = own;
         }
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (i + k < n) {
-            if (codec == HB_NONE) avg_out[i + k] = acc[r][k];
-            if (i_send) x_local[i + k] = fmaf(alpha_own, acc[r][k] - x_local[i + k], x_local[i + k]);
-          } else {
-            acc[r][k] = 0.f;
-          }
-        }
       }
     }
     // deltas: avg - decode(copy of the sender's record), encoded over the copy, one sender after the other
     if (codec != HB_NONE && !dead) {
-      for (int s = 0; s < g.n_peers; ++s) {
-        if (!sh.inc[s]) continue;
+      __syncthreads();   // the copies' 16-byte headers were written by thread 0
+      for (int k = 0; k < n_inc; ++k) {
+        const int s = sh.order[k];
         unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
+        HrAhead mine;
+        hr_fetch(codec, local, n, mine);
         float mean, sd, absmax[HR_BLOCKS] = {};
-        hr_decode_setup(codec, local, sh, g.code, mean, sd, absmax);
+        hr_open(codec, mine, sh, nullptr, mean, sd, absmax);
         float d[HR_ROWS][4];
 #pragma unroll
         for (int r = 0; r < HR_ROWS; ++r) {
           const int i = hr_elem(r);
           float o[4];
-          hr_decode_row(codec, local + hdr, i, mean, sd, sh.cb, absmax, o);
+          hr_decode_ahead(codec, mine, r, mean, sd, sh, absmax, o);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) d[r][k] = (i + k < n) ? acc[r][k] - o[k] : 0.f;
+          for (int q = 0; q < 4; ++q) d[r][q] = (i + q < n) ? acc[r][q] - o[q] : 0.f;
         }
-        __syncthreads();   // every thread has decoded with the old header before anybody writes the new one
-        hr_encode_chunk(d, n, codec, local, sh, g.code);
+        __syncthreads();   // every thread has decoded with the old codebook before anybody writes the new one
+        hr_encode_chunk(d, n, codec, local, sh);
       }
     }
   }
@@ -727,46 +721,45 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& 
   const int opar = d >> 1;
   const float alpha = g.alpha;
   const long long stride = hr_chunk_stride(codec);
-  const int hdr = hr_header_bytes(codec);
+  auto source = [&](int c) -> const unsigned char* {
+    if (codec == HB_NONE) return g.base[owner] + g.lay.avg[opar] + (size_t)(part.avg_off + (long long)c * HR_CHUNK) * 4;
+    return g.base[owner] + g.lay.deltabox[opar] + (size_t)me * g.delta_stride + part.span_off + (long long)c * stride;
+  };
+  auto chunk_len = [&](int c) { return min(HR_CHUNK, part.len - c * HR_CHUNK); };
+  HrAhead ahead;
+  hr_fetch(codec, source(c0), chunk_len(c0), ahead);
   for (int c = c0; c < c0 + z; ++c) {
-    const int lo = c * HR_CHUNK, n = min(HR_CHUNK, part.len - lo);
+    const int lo = c * HR_CHUNK, n = chunk_len(c);
     float* x = reinterpret_cast<float*>(g.base[me] + g.lay.data) + part.start + lo;
-    float dv[HR_ROWS][4];
-    if (codec == HB_NONE) {
-      float4 av[HR_ROWS];
-      hr_load_rows(reinterpret_cast<const float*>(g.base[owner] + g.lay.avg[opar]) + part.avg_off + lo, n, av);
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) { dv[r][0] = av[r].x; dv[r][1] = av[r].y; dv[r][2] = av[r].z; dv[r][3] = av[r].w; }
-    } else {
-      const unsigned char* rec = g.base[owner] + g.lay.deltabox[opar] + (size_t)me * g.delta_stride + part.span_off + (long long)c * stride;
-      float mean, sd, absmax[HR_BLOCKS] = {};
-      hr_decode_setup(codec, rec, sh, g.code, mean, sd, absmax);
-#pragma unroll
-      for (int r = 0; r < HR_ROWS; ++r) hr_decode_row(codec, rec + hdr, hr_elem(r), mean, sd, sh.cb, absmax, dv[r]);
-    }
+    const HrAhead cur = ahead;
+    if (c + 1 < c0 + z) hr_fetch(codec, source(c + 1), chunk_len(c + 1), ahead);
+    float mean, sd, absmax[HR_BLOCKS] = {};
+    hr_open(codec, cur, sh, nullptr, mean, sd, absmax);
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
-      if (i + 4 <= n) {
-        float4 xv = *reinterpret_cast<const float4*>(x + i);
-        if (codec == HB_NONE) {
-          xv.x = fmaf(alpha, dv[r][0] - xv.x, xv.x); xv.y = fmaf(alpha, dv[r][1] - xv.y, xv.y);
-          xv.z = fmaf(alpha, dv[r][2] - xv.z, xv.z); xv.w = fmaf(alpha, dv[r][3] - xv.w, xv.w);
-        } else {
-          xv.x = fmaf(alpha, dv[r][0], xv.x); xv.y = fmaf(alpha, dv[r][1], xv.y);
-          xv.z = fmaf(alpha, dv[r][2], xv.z); xv.w = fmaf(alpha, dv[r][3], xv.w);
-        }
-        *reinterpret_cast<float4*>(x + i) = xv;
+      if (i + 4 > n) continue;   // parts are whole multiples of four elements
+      float dv[4];
+      hr_decode_ahead(codec, cur, r, mean, sd, sh, absmax, dv);
+      float4 xv = *reinterpret_cast<const float4*>(x + i);
+      if (codec == HB_NONE) {   // the record is the average itself
+        xv.x = fmaf(alpha, dv[0] - xv.x, xv.x); xv.y = fmaf(alpha, dv[1] - xv.y, xv.y);
+        xv.z = fmaf(alpha, dv[2] - xv.z, xv.z); xv.w = fmaf(alpha, dv[3] - xv.w, xv.w);
       } else {
-        for (int k = 0; k < 4; ++k)
-          if (i + k < n) x[i + k] = codec == HB_NONE ? fmaf(alpha, dv[r][k] - x[i + k], x[i + k]) : fmaf(alpha, dv[r][k], x[i + k]);
+        xv.x = fmaf(alpha, dv[0], xv.x); xv.y = fmaf(alpha, dv[1], xv.y);
+        xv.z = fmaf(alpha, dv[2], xv.z); xv.w = fmaf(alpha, dv[3], xv.w);
       }
+      *reinterpret_cast<float4*>(x + i) = xv;
     }
   }
 }
 
 __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_constant__ HrRound g) {
   __shared__ HrShared sh;
+  if (threadIdx.x < 256) {
+    sh.code[threadIdx.x] = g.code[threadIdx.x];
+    sh.mid[threadIdx.x] = g.code[256 + threadIdx.x];
+  }
   // Items are dealt round-robin. The list is ordered send, reduce, apply, so every CTA finishes its send items
   // before it may wait for a groupmate, and nothing that a groupmate needs from this GPU queues up behind a wait.
   for (int idx = g.item_begin + (int)blockIdx.x; idx < g.item_end; idx += (int)gridDim.x) {

@@ -322,6 +322,131 @@ colstrip_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// One-pass LayerNorm backward for bf16 rows (the default when the row fits): a CTA streams tiles of R rows of dy and
+// of the normalised input into shared memory with asynchronous copies (two tiles in flight), takes the two row sums
+// with one warp per row, and then switches to a column view: every thread owns eight columns, writes dx for the
+// tile's rows and keeps the column sums of dy * xhat, dy and dx in registers until the CTA has run out of tiles.
+// HBM sees dy and the input once and dx once; dxsum (optional) is the bias gradient of the layer whose output was
+// normalised.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int R>
+__global__ void __launch_bounds__(256)
+ln_bwd_tile_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ zin,
+                   const float* __restrict__ gamma, const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                   float* __restrict__ dxsum, int rows, int H, int gp_log2) {
+  extern __shared__ __align__(16) unsigned char ln_smem[];
+  const int G = H >> 3;                        // 16-byte column groups per row
+  const int GP = 1 << gp_log2, RP = 256 >> gp_log2;   // threads per row (power of two >= G), rows in flight in the column view
+  const size_t tile_bytes = (size_t)R * H * 2;
+  float* s_gamma = reinterpret_cast<float*>(ln_smem + 4 * tile_bytes);
+  float* s_stat = s_gamma + H;                 // [R][4]: mean, rstd, mean(g dy), mean(g dy xhat)
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cg = tid & (GP - 1), rsub = tid >> gp_log2;
+  const int num_tiles = (rows + R - 1) / R;
+  const float inv_h = 1.f / (float)H;
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(ln_smem);
+
+  auto issue = [&](int tile, int stage) {
+    const int row0 = tile * R, nrows = min(R, rows - row0);
+    const int vectors = nrows * G;             // the rows of a tile are contiguous in memory
+    const char* src_d = reinterpret_cast<const char*>(dy + (size_t)row0 * H);
+    const char* src_z = reinterpret_cast<const char*>(zin + (size_t)row0 * H);
+    const uint32_t dst = smem_base + (uint32_t)(stage * 2 * tile_bytes);
+    for (int v = tid; v < vectors; v += 256) {
+      cp_async16(dst + v * 16, src_d + (size_t)v * 16);
+      cp_async16(dst + (uint32_t)tile_bytes + v * 16, src_z + (size_t)v * 16);
+    }
+  };
+
+  for (int i = tid; i < H; i += 256) s_gamma[i] = gamma[i];
+  float g8[8], a8[8], b8[8], c8[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    g8[k] = cg < G ? gamma[cg * 8 + k] : 0.f;
+    a8[k] = b8[k] = c8[k] = 0.f;
+  }
+  int tile = blockIdx.x, stage = 0;
+  if (tile < num_tiles) issue(tile, 0);
+  cp_async_commit();
+  for (; tile < num_tiles; tile += gridDim.x, stage ^= 1) {
+    const int next = tile + gridDim.x;
+    if (next < num_tiles) issue(next, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();                        // everything but the newest group has landed: this tile is here
+    __syncthreads();
+    const int row0 = tile * R, nrows = min(R, rows - row0);
+    const __nv_bfloat16* t_dy = reinterpret_cast<const __nv_bfloat16*>(ln_smem + stage * 2 * tile_bytes);
+    const __nv_bfloat16* t_z = reinterpret_cast<const __nv_bfloat16*>(ln_smem + stage * 2 * tile_bytes + tile_bytes);
+    // row view: one warp per row
+    for (int r = warp; r < nrows; r += 8) {
+      const float mean = mean_in[row0 + r], rstd = rstd_in[row0 + r];
+      float s1 = 0.f, s2 = 0.f;
+      for (int c = lane; c < G; c += 32) {
+        float d[8], z[8];
+        ld8<__nv_bfloat16>(t_dy + r * H + c * 8, d);
+        ld8<__nv_bfloat16>(t_z + r * H + c * 8, z);
+        const float4 ga = reinterpret_cast<const float4*>(s_gamma + c * 8)[0], gb = reinterpret_cast<const float4*>(s_gamma + c * 8)[1];
+        const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float gd = d[k] * g[k];
+          s1 += gd;
+          s2 = fmaf(gd, (z[k] - mean) * rstd, s2);
+        }
+      }
+      s1 = hm_warp_sum(s1);
+      s2 = hm_warp_sum(s2);
+      if (lane == 0) reinterpret_cast<float4*>(s_stat)[r] = make_float4(mean, rstd, s1 * inv_h, s2 * inv_h);
+    }
+    __syncthreads();
+    // column view
+    if (cg < G) {
+      for (int r = rsub; r < nrows; r += RP) {
+        const float4 st = reinterpret_cast<const float4*>(s_stat)[r];
+        float d[8], z[8], o[8];
+        ld8<__nv_bfloat16>(t_dy + r * H + cg * 8, d);
+        ld8<__nv_bfloat16>(t_z + r * H + cg * 8, z);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float xh = (z[k] - st.x) * st.y;
+          o[k] = st.y * (d[k] * g8[k] - st.z - xh * st.w);
+          a8[k] = fmaf(d[k], xh, a8[k]);
+          b8[k] += d[k];
+          c8[k] += o[k];
+        }
+        st8<__nv_bfloat16>(dx + (size_t)(row0 + r) * H + cg * 8, o);
+      }
+    }
+    __syncthreads();                           // the tile may be overwritten by the copy issued in the next iteration
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // column sums: fold the RP row lanes through shared memory, then one atomic per column and CTA
+  float* red = reinterpret_cast<float*>(ln_smem);   // [RP][GP * 8]
+#pragma unroll 1
+  for (int pass = 0; pass < 3; ++pass) {
+    float* dst = pass == 0 ? dgamma : (pass == 1 ? dbeta : dxsum);
+    if (dst == nullptr) continue;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) red[(rsub * GP + cg) * 8 + k] = pass == 0 ? a8[k] : (pass == 1 ? b8[k] : c8[k]);
+    __syncthreads();
+    for (int col = tid; col < H; col += 256) {
+      float t = 0.f;
+      for (int rs = 0; rs < RP; ++rs) t += red[rs * GP * 8 + col];
+      atomicAdd(dst + col, t);
+    }
+    __syncthreads();
+  }
+}
+
 template <typename T>
 static int colstrip_grid(long long rows, int H, int sms, dim3* grid, int* rows_per_strip) {
   const int gx = (H + 255) / 256;
@@ -576,6 +701,40 @@ HM_API int hm_layernorm_bwd(const void* dy, const void* zin, const void* gamma, 
                             cudaStream_t stream) {
   if (rows <= 0) return 0;
   HM_LN_DISPATCH(ln_bwd_launch, dy, zin, gamma, mean, rstd, dx, dgamma, dbeta, rows, H, sms, stream);
+}
+
+// One-pass backward (bf16, H a multiple of 8 up to 2048). dgamma / dbeta / dxsum are fp32 [H] buffers that the kernel
+// ADDS to (any of them may be null). Returns -1 when the shape is not covered; the caller then uses hm_layernorm_bwd.
+HM_API int hm_layernorm_bwd_fused(const void* dy, const void* zin, const void* gamma, const void* mean, const void* rstd,
+                                  void* dx, void* dgamma, void* dbeta, void* dxsum, int rows, int H, int dtype, int sms,
+                                  cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype != HM_BF16 || H % 8 != 0 || H > 2048 || H < 64) return -1;
+  int gp_log2 = 3;
+  while ((1 << gp_log2) < H / 8) ++gp_log2;
+  const bool small = H <= 1024;
+  const int R = small ? 8 : 4;
+  if ((256 >> gp_log2) > R) return -1;
+  const size_t smem = (size_t)4 * R * H * 2 + (size_t)H * 4 + (size_t)R * 16;
+  const int tiles = (rows + R - 1) / R;
+  const int per_sm = (int)((size_t)200 * 1024 / smem);
+  int blocks = sms * (per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm));
+  if (blocks > tiles) blocks = tiles;
+  cudaError_t e;
+  if (small) {
+    e = cudaFuncSetAttribute(ln_bwd_tile_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    ln_bwd_tile_kernel<8><<<blocks, 256, smem, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)zin, (const float*)gamma, (const float*)mean, (const float*)rstd,
+        (__nv_bfloat16*)dx, (float*)dgamma, (float*)dbeta, (float*)dxsum, rows, H, gp_log2);
+  } else {
+    e = cudaFuncSetAttribute(ln_bwd_tile_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    ln_bwd_tile_kernel<4><<<blocks, 256, smem, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)zin, (const float*)gamma, (const float*)mean, (const float*)rstd,
+        (__nv_bfloat16*)dx, (float*)dgamma, (float*)dbeta, (float*)dxsum, rows, H, gp_log2);
+  }
+  return (int)cudaGetLastError();
 }
 
 HM_API int hm_bias_gelu_fwd(const void* x, const void* bias, void* y, long long rows, int H, int dtype, int sms,

@@ -176,7 +176,8 @@ class _LinearFn(torch.autograd.Function):
     """y = act(x W^T + b) with bf16 tensor-core GEMMs and fp32 weight-gradient accumulation."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, weight_lp, activation):
+    def forward(ctx, x, weight, bias, weight_lp, activation, skip_bias_grad=False):
+        ctx.skip_bias_grad = skip_bias_grad
         in_f = x.shape[-1]
         x2 = x.reshape(-1, in_f)
         if x2.dtype != torch.bfloat16:
@@ -211,7 +212,8 @@ class _LinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         lib = _lib.load_library()
         dev = x2.device
-        need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], bias is not None and ctx.needs_input_grad[2]
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_b = bias is not None and ctx.needs_input_grad[2] and not ctx.skip_bias_grad
         grad_b = None
         if need_b:
             use_b_buf = bias.grad is not None and bias.grad.dtype == torch.float32 and bias.grad.is_contiguous()
@@ -245,19 +247,25 @@ class _LinearFn(torch.autograd.Function):
             gw = weight.grad if use_w_buf else torch.zeros(weight.shape, dtype=torch.float32, device=dev)
             tc_gemm(dy2, x2, a_mn=True, b_mn=True, out=gw, reduce_add=True, splits=splits, pair=use_pair)
             grad_w = None if use_w_buf else gw.to(weight.dtype)
-        return grad_x, grad_w, grad_b, None, None
+        return grad_x, grad_w, grad_b, None, None, None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           activation: Optional[str] = None, weight_lp: Optional[torch.Tensor] = None) -> torch.Tensor:
+           activation: Optional[str] = None, weight_lp: Optional[torch.Tensor] = None,
+           skip_bias_grad: bool = False) -> torch.Tensor:
     """``act(x @ weight.T + bias)`` with ``activation`` in (None, "gelu") (tanh-GELU).
 
     ``weight`` is the (fp32 or bf16) parameter that receives the gradient; ``weight_lp`` is an optional
     up-to-date bf16 copy of it, which saves the cast. CUDA inputs run on the tcgen05 kernel in bf16 with fp32
     accumulation; CPU inputs run the PyTorch formula in the input dtype.
+
+    ``skip_bias_grad``: the caller obtains the bias gradient elsewhere (``layer_norm(..., producer_bias=bias)`` takes
+    it in the pass that produces this layer's output gradient), so this call leaves ``bias.grad`` alone.
     """
     in_f, out_f = weight.shape[1], weight.shape[0]
     if _lib.use_kernels(x, weight) and in_f % 8 == 0 and out_f % 8 == 0:
-        return _LinearFn.apply(x, weight, bias, weight_lp, activation)
+        return _LinearFn.apply(x, weight, bias, weight_lp, activation, skip_bias_grad)
+    if bias is not None and skip_bias_grad:
+        bias = bias.detach()
     y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
     return F.gelu(y, approximate="tanh") if activation == "gelu" else y

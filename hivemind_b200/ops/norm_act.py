@@ -27,9 +27,10 @@ def gelu_tanh_reference(x: torch.Tensor) -> torch.Tensor:
 
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, gamma, beta, eps, return_sum=False):
+    def forward(ctx, x, residual, gamma, beta, eps, return_sum=False, producer_bias=None):
         ctx.set_materialize_grads(False)
         ctx.return_sum = return_sum
+        ctx.producer_bias = producer_bias
         h = x.shape[-1]
         x2 = x.reshape(-1, h).contiguous()
         r2 = residual.reshape(-1, h).contiguous() if residual is not None else None
@@ -62,7 +63,9 @@ class _LayerNormFn(torch.autograd.Function):
         rows = zin.shape[0]
         if dy is None:  # only the sum was used downstream
             dz = dz if dz is not None else torch.zeros(ctx.shape, dtype=zin.dtype, device=zin.device)
-            return dz, (dz if ctx.has_residual else None), None, None, None, None
+            pb = ctx.producer_bias
+            db = None if pb is None else dz.reshape(-1, h).sum(0, dtype=torch.float32).to(pb.dtype)
+            return dz, (dz if ctx.has_residual else None), None, None, None, None, db
         dy2 = dy.reshape(-1, h).contiguous()
         if dy2.dtype != zin.dtype:
             dy2 = dy2.to(zin.dtype)
@@ -78,34 +81,74 @@ class _LayerNormFn(torch.autograd.Function):
         else:
             dgb = torch.zeros(2, h, dtype=torch.float32, device=zin.device)
             dgamma, dbeta = dgb[0], dgb[1]
+        # the bias of the layer that produced the normalised tensor (if the caller named it): its gradient is the
+        # column sum of dx, which the one-pass kernel takes along the way
+        pb = ctx.producer_bias
+        pb_direct = pb is not None and dz is None and pb.grad is not None and pb.grad.dtype == torch.float32 \
+            and pb.grad.is_contiguous()
+        dxsum = None
+        if pb is not None and dz is None:
+            dxsum = pb.grad if pb_direct else torch.zeros(h, dtype=torch.float32, device=zin.device)
         with torch.cuda.device(zin.device):
-            code = lib.hm_layernorm_bwd(_lib.ptr(dy2), _lib.ptr(zin), _lib.ptr(g32), _lib.ptr(mean), _lib.ptr(rstd),
-                                        _lib.ptr(dx), _lib.ptr(dgamma), _lib.ptr(dbeta), rows, h,
-                                        _lib.dtype_code(zin.dtype), _lib.sm_count(zin.device),
-                                        _lib.stream_ptr(zin.device))
+            code = lib.hm_layernorm_bwd_fused(_lib.ptr(dy2), _lib.ptr(zin), _lib.ptr(g32), _lib.ptr(mean),
+                                              _lib.ptr(rstd), _lib.ptr(dx), _lib.ptr(dgamma), _lib.ptr(dbeta),
+                                              _lib.ptr(dxsum), rows, h, _lib.dtype_code(zin.dtype),
+                                              _lib.sm_count(zin.device), _lib.stream_ptr(zin.device))
+            if code == -1:  # shape or dtype outside the one-pass kernel: row pass + column-strip pass
+                code = lib.hm_layernorm_bwd(_lib.ptr(dy2), _lib.ptr(zin), _lib.ptr(g32), _lib.ptr(mean),
+                                            _lib.ptr(rstd), _lib.ptr(dx), _lib.ptr(dgamma), _lib.ptr(dbeta), rows, h,
+                                            _lib.dtype_code(zin.dtype), _lib.sm_count(zin.device),
+                                            _lib.stream_ptr(zin.device))
+                if dxsum is not None:
+                    from hivemind_b200.ops.gemm import colsum_
+                    colsum_(dxsum, dx)
         _lib.check(code, "hm_layernorm_bwd")
         dx = dx.view(ctx.shape)
         if dz is not None:
             dx.add_(dz.reshape(ctx.shape))
+        grad_pb = None
+        if pb is not None and not pb_direct:
+            grad_pb = (dxsum if dxsum is not None else dx.reshape(-1, h).sum(0, dtype=torch.float32)).to(pb.dtype)
         if direct:
-            return dx, (dx if ctx.has_residual else None), None, None, None, None
+            return dx, (dx if ctx.has_residual else None), None, None, None, None, grad_pb
         return (dx, (dx if ctx.has_residual else None), dgamma.to(ctx.param_dtype[0]), dbeta.to(ctx.param_dtype[1]),
-                None, None)
+                None, None, grad_pb)
 
 
 def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
-               residual: Optional[torch.Tensor] = None, return_sum: bool = False):
+               residual: Optional[torch.Tensor] = None, return_sum: bool = False,
+               producer_bias: Optional[torch.Tensor] = None):
     """``LayerNorm(x + residual)`` over the last dimension (``residual`` optional), statistics in fp32.
 
     With ``return_sum`` the result is ``(LayerNorm(x + residual), x + residual)``: the second tensor is the updated
     residual stream of a pre-LayerNorm transformer, produced by the same kernel pass.
+
+    ``producer_bias``: the bias parameter of the linear layer whose output is ``x``, when that layer was called with
+    ``skip_bias_grad=True``. The gradient of that bias is the column sum of this function's input gradient, which the
+    backward kernel computes in the pass that produces the input gradient; it is delivered to the parameter from here.
     """
     h = x.shape[-1]
     if _kernel_ok(x, h):
-        return _LayerNormFn.apply(x, residual, gamma, beta, eps, return_sum)
+        return _LayerNormFn.apply(x, residual, gamma, beta, eps, return_sum, producer_bias)
+    if producer_bias is not None:
+        x = _ColumnSumTap.apply(x, producer_bias)
     z = x if residual is None else x + residual
     y = F.layer_norm(z.to(torch.float32), (h,), gamma.to(torch.float32), beta.to(torch.float32), eps).to(x.dtype)
     return (y, z) if return_sum else y
+
+
+class _ColumnSumTap(torch.autograd.Function):
+    """Identity on ``x`` whose backward also hands the column sums of the gradient to ``bias`` (PyTorch path of
+    ``layer_norm(..., producer_bias=...)``)."""
+
+    @staticmethod
+    def forward(ctx, x, bias):
+        ctx.bias_dtype = bias.dtype
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dx):
+        return dx, dx.reshape(-1, dx.shape[-1]).sum(0, dtype=torch.float32).to(ctx.bias_dtype)
 
 
 class _BiasGeluFn(torch.autograd.Function):

@@ -52,7 +52,9 @@ ALIGN = 16  # elements: tensor starts and part boundaries are multiples of this,
 CHUNK = 8192  # elements per chunk record (HR_CHUNK in butterfly_round.cu)
 ACK_RING = 8
 CTAS_PER_SM = 2  # the round kernel keeps two 512-thread CTAs on every SM
-ITEM_CHUNKS = int(os.environ.get("HIVEMIND_B200_ITEM_CHUNKS", "0"))  # chunks per work item; 0 = chosen per layout
+GRID_CTAS = 296  # CTAs of the round kernel on a B200; a constant, because all members must derive the same part table
+MAX_PART_CHUNKS = 16
+ITEM_CHUNKS = int(os.environ.get("HIVEMIND_B200_ITEM_CHUNKS", "0"))  # chunks per work item; 0 = one item per part
 DELTA_BOX_FACTOR = 1.5  # delta box capacity relative to the outbox: 1.0 suffices for equal spans
 _CODEC_IDS = {NoCompression: 0, ScaledFloat16Compression: 1, Float16Compression: 2, Quantile8BitQuantization: 3,
               Uniform8BitQuantization: 4, BlockwiseQuantization: 5}
@@ -69,6 +71,17 @@ def codec_id(compression: CompressionBase, info: CompressionInfo) -> Optional[in
     while isinstance(compression, AdaptiveCompressionBase):
         compression = compression.choose_compression(info)
     return _CODEC_IDS.get(type(compression))
+
+
+def device_part_chunks(total_elements: int, n_peers: int) -> int:
+    """Chunks per part on the device path. A part is the unit of flag publication and (by default) one work item of
+    one CTA, so parts are cut such that a reducer's span falls into whole waves of ``GRID_CTAS`` parts of at most
+    ``MAX_PART_CHUNKS`` chunks: long enough to spread the fixed cost of an item, short enough that groupmates can start
+    on a part soon after its owner has finished it. (The ``part_size_bytes`` of the RPC path plays no part here:
+    these parts never leave the box.)"""
+    span = -(-(-(-total_elements // CHUNK)) // max(n_peers, 1))
+    waves = max(1, -(-span // (GRID_CTAS * MAX_PART_CHUNKS)))
+    return max(1, -(-span // (GRID_CTAS * waves)))
 
 
 def chunk_stride(codec: int) -> int:
@@ -256,12 +269,14 @@ class DeviceEndpoint:
             if c == CODEC_NONE:
                 avg_cursor += padded
         self.total = max(cursor, ALIGN)
-        part_lens = [max(ALIGN, int(part_size_bytes / (4 * r)) // ALIGN * ALIGN) for r in self.ratios]
-        self.max_parts = sum((n + pl - 1) // pl for n, pl in zip(self.numels, part_lens)) + MAX_PEERS + len(tensors)
-        # staging capacities by codec: records exist only for compressed tensors, averages only for uncompressed ones
+        # flag pages hold the largest part table that any group size can produce
+        self.max_parts = max(sum(-(-n // (device_part_chunks(sum(self.numels), peers) * CHUNK)) for n in self.numels)
+                             for peers in range(1, MAX_PEERS + 1)) + MAX_PEERS + len(tensors)
+        # staging capacities by codec: records exist only for compressed tensors, averages only for uncompressed ones.
+        # Parts are whole chunks except where a tensor ends or a peer's share ends: at most MAX_PEERS + 1 extra records
         self.cap_avg = max(avg_cursor * 4, 256)
-        self.cap_outbox = max(256, sum(((n + CHUNK - 1) // CHUNK + (n + pl - 1) // pl + MAX_PEERS + 1) * chunk_stride(c)
-                                       for n, pl, c in zip(self.numels, part_lens, codecs) if c != CODEC_NONE))
+        self.cap_outbox = max(256, sum(((n + CHUNK - 1) // CHUNK + MAX_PEERS + 1) * chunk_stride(c)
+                                       for n, c in zip(self.numels, codecs) if c != CODEC_NONE))
         self.cap_delta = int(self.cap_outbox * DELTA_BOX_FACTOR) + (1 << 12) if self.cap_outbox > 256 else 256
         self.layout: Dict[str, int] = {}
         self._guards: Dict[str, int] = {}
@@ -293,6 +308,7 @@ class DeviceEndpoint:
             lo = self.layout[name]
             self._bytes[lo:self._guards[name]].zero_()
         flat = self._bytes[self.layout["data"]:self.layout["data"] + self.total * 4].view(torch.float32)
+        flat.zero_()  # the padding between tensors is averaged along with them: it must hold numbers
         self.flat = flat
         self.tensor_views = []
         with torch.no_grad():
@@ -416,8 +432,9 @@ class DeviceEndpoint:
         return plan
 
     def _build_plan(self, n_peers: int, my_index: int, peer_fractions: Sequence[float], sends: Sequence[bool]) -> _Plan:
-        specs = compute_part_layout(self.numels, [4] * len(self.numels), self.ratios, peer_fractions,
-                                    self.part_size_bytes, align=ALIGN)
+        part_bytes = device_part_chunks(sum(self.numels), n_peers) * CHUNK * 4
+        specs = compute_part_layout(self.numels, [4] * len(self.numels), [1.0] * len(self.numels), peer_fractions,
+                                    part_bytes, align=ALIGN)
         specs = [s for s in specs if s.length > 0]
         n_parts = len(specs)
         if n_parts > self.max_parts:
@@ -429,7 +446,9 @@ class DeviceEndpoint:
             rec = record_bytes(codec, s.length)
             start = self.offsets[s.tensor_index] + s.start
             avg_off = self.avg_offsets[s.tensor_index] + s.start if codec == CODEC_NONE else 0
-            table[p] = (start, enc_cursor, span_bytes[s.owner], avg_off, s.length, s.owner, local_count[s.owner], codec)
+            # kernels move four elements at a time; a tensor's last part borrows from the zero padding behind it
+            length = (s.length + 3) // 4 * 4
+            table[p] = (start, enc_cursor, span_bytes[s.owner], avg_off, length, s.owner, local_count[s.owner], codec)
             enc_cursor += rec
             span_bytes[s.owner] += rec
             local_count[s.owner] += 1
@@ -440,10 +459,8 @@ class DeviceEndpoint:
         def n_chunks(p):
             return (int(table[p]["len"]) + CHUNK - 1) // CHUNK
 
-        # an item is a run of consecutive chunks of one part: long enough to spread the cost of looking up flags and
-        # of the fence behind its results, short enough that every CTA of the grid gets several items per stage
-        busiest = max(sum(n_chunks(p) for p in range(n_parts) if table[p]["owner"] == r) for r in range(n_peers))
-        run = ITEM_CHUNKS if ITEM_CHUNKS > 0 else max(1, min(8, busiest // (CTAS_PER_SM * self._sms * 6)))
+        # an item is a run of consecutive chunks of one part; by default the whole part (see device_part_chunks)
+        run = ITEM_CHUNKS if ITEM_CHUNKS > 0 else MAX_PART_CHUNKS
 
         def runs_of(p):
             total = n_chunks(p)

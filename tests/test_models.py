@@ -164,3 +164,25 @@ def test_albert_matches_reference_cpu():
 @pytest.mark.gpu
 def test_albert_matches_reference_gpu():
     _check_albert(torch.device("cuda"), loss_tol=5e-3, grad_tol=6e-2)
+
+
+def test_producer_bias_contract_on_the_pytorch_path():
+    """linear(skip_bias_grad=True) leaves the bias gradient to layer_norm(producer_bias=...), exactly once."""
+    import torch.nn.functional as F
+
+    from hivemind_b200.ops.gemm import linear
+    from hivemind_b200.ops.norm_act import layer_norm
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 5, 16, requires_grad=True)
+    w = torch.randn(24, 16, requires_grad=True)
+    bias = torch.randn(24, requires_grad=True)
+    g, b = torch.rand(24, requires_grad=True), torch.randn(24, requires_grad=True)
+    res = torch.randn(6, 5, 24, requires_grad=True)
+    y = layer_norm(linear(x, w, bias, skip_bias_grad=True), g, b, 1e-5, residual=res, producer_bias=bias)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, biasr, gr, br, resr = (t.detach().clone().requires_grad_() for t in (x, w, bias, g, b, res))
+    F.layer_norm(F.linear(xr, wr, biasr) + resr, (24,), gr, br, 1e-5).backward(dy)
+    for mine, ref in ((x, xr), (w, wr), (bias, biasr), (g, gr), (b, br), (res, resr)):
+        assert torch.allclose(mine.grad, ref.grad, atol=1e-4, rtol=1e-4)

@@ -37,6 +37,41 @@ def test_layernorm_fwd_bwd(dtype, h):
     assert torch.allclose(b.grad, br.grad, atol=tol * 30, rtol=tol)
 
 
+@pytest.mark.parametrize("h,rows", [(256, 3001), (768, 1111), (1024, 20000), (2048, 515), (128, 999)])
+@pytest.mark.parametrize("grads_exist", [False, True])
+def test_layernorm_backward_delivers_the_gradient_of_the_producing_bias(h, rows, grads_exist):
+    """linear(skip_bias_grad) -> layer_norm(producer_bias): one pass gives dx, dgamma, dbeta and the bias gradient."""
+    from hivemind_b200.ops.gemm import linear
+    from hivemind_b200.ops.norm_act import layer_norm
+
+    torch.manual_seed(1)
+    dev = _dev()
+    inp = torch.randn(rows, 64, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(h, 64, device=dev) * 0.2).requires_grad_()
+    bias = torch.randn(h, device=dev).requires_grad_()
+    r = torch.randn(rows, h, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    g = (torch.rand(h, device=dev) + 0.5).requires_grad_()
+    b = torch.randn(h, device=dev).requires_grad_()
+    if grads_exist:  # fp32 .grad buffers with content: the kernels add to them in place
+        for t in (w, bias, g, b):
+            t.grad = torch.ones_like(t)
+    y = layer_norm(linear(inp, w, bias, skip_bias_grad=True), g, b, 1e-12, residual=r, producer_bias=bias)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ir, wr, biasr, rr, gr, br = (t.detach().float().requires_grad_() for t in (inp, w, bias, r, g, b))
+    lin = F.linear(ir, wr.bfloat16().float(), biasr).bfloat16().float()
+    yr = F.layer_norm(lin + rr, (h,), gr, br, 1e-12)
+    yr.backward(dy.float())
+    base = 1.0 if grads_exist else 0.0
+    scale = math.sqrt(rows)
+    assert torch.allclose(r.grad.float(), rr.grad, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(bias.grad - base, biasr.grad, atol=0.03 * scale, rtol=2e-2)
+    assert torch.allclose(g.grad - base, gr.grad, atol=0.03 * scale, rtol=2e-2)
+    assert torch.allclose(b.grad - base, br.grad, atol=0.03 * scale, rtol=2e-2)
+    assert torch.allclose(w.grad - base, wr.grad, atol=0.03 * scale, rtol=3e-2)
+    assert torch.allclose(inp.grad.float(), ir.grad, atol=5e-2, rtol=5e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_bias_gelu(dtype):
     from hivemind_b200.ops.norm_act import bias_gelu
