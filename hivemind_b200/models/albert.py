@@ -21,7 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from hivemind_b200.ops.attention import attention
-from hivemind_b200.ops.gemm import linear
+from hivemind_b200.ops.gemm import feed_forward, linear
 from hivemind_b200.ops.norm_act import layer_norm
 
 
@@ -92,16 +92,17 @@ class AlbertLayer(nn.Module):
     def forward(self, x: torch.Tensor, lp: _LowPrecisionCache) -> torch.Tensor:
         b, s, h = x.shape
         nh = self.num_heads
-        qkv = linear(x, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight))
+        # passthrough: the residual branch's gradient joins the projection's input gradient in that GEMM's epilogue
+        qkv, x = linear(x, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight), passthrough=True)
         ctx = attention(qkv, nh)  # reads the packed projections, writes [b, s, h]: no transposes around it
         # the biases in front of the two LayerNorms get their gradients from the LayerNorm backward pass
         attn = linear(ctx, self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight),
                       skip_bias_grad=True)
         x = layer_norm(attn, self.attn_ln_weight, self.attn_ln_bias, self.eps, residual=x,
                        producer_bias=self.attn_out_bias)
-        inter = linear(x, self.ffn_weight, self.ffn_bias, activation="gelu", weight_lp=lp.get(self.ffn_weight))
-        out = linear(inter, self.ffn_out_weight, self.ffn_out_bias, weight_lp=lp.get(self.ffn_out_weight),
-                     skip_bias_grad=True)
+        out, x = feed_forward(x, self.ffn_weight, self.ffn_bias, self.ffn_out_weight, self.ffn_out_bias,
+                              w1_lp=lp.get(self.ffn_weight), w2_lp=lp.get(self.ffn_out_weight),
+                              skip_out_bias_grad=True, passthrough=True)
         return layer_norm(out, self.ffn_ln_weight, self.ffn_ln_bias, self.eps, residual=x,
                           producer_bias=self.ffn_out_bias)
 

@@ -132,11 +132,12 @@ __device__ __forceinline__ void hr_st_release_sys_u64(unsigned long long* p, uns
 }
 
 struct HrShared {
-  float red[4][HR_THREADS / 32];        // up to four simultaneous block reductions
-  float cb[256];                        // codebook of the record being decoded
-  float table[256];                     // borders (quantile) or code midpoints (block-wise) for bucketize
+  double redd[2][2][HR_THREADS / 32];   // two alternating scratch copies for block-wide sums (one barrier per reduction)
+  float redf[2][2][HR_THREADS / 32];    //   and maxima
+  float cb[2][256];                     // codebook of the record being decoded (two alternating copies)
+  float table[256];                     // quantile borders for bucketize
   float hsum[HR_THREADS / 64][256];     // per warp-pair bin sums and counts: a skewed distribution would otherwise
-  int hcnt[HR_THREADS / 64][256];       //   serialise the whole CTA on a handful of addresses
+  int hcnt[HR_THREADS / 64][256];       //   serialise the whole CTA on a handful of addresses. Zero between uses.
   float smp[HR_SAMPLE];
   float code[256];                      // block-wise code and the midpoints between its entries: loaded once per CTA
   float mid[256];
@@ -148,32 +149,93 @@ struct HrShared {
   int bcast;
 };
 
+// Per-thread bookkeeping with the same value in every thread of the CTA: which scratch copy comes next.
+struct HrThread {
+  int red = 0, cb = 0;
+};
+
 // element index inside the chunk handled by (row r, thread, k)
 __device__ __forceinline__ int hr_elem(int r) { return (r * HR_THREADS + (int)threadIdx.x) * 4; }
 
-// up to four block-wide sums / maxima at once; every thread gets the results
-template <int N, bool MAX>
-__device__ __forceinline__ void hr_block_reduce(float (&v)[N], HrShared& sh) {
+// Block-wide sums of two doubles (or maxima of two floats); every thread gets the results. One barrier: consecutive
+// reductions alternate between two scratch copies, and a thread can only get to the reduction after next once all
+// threads have passed the barrier of the next one, i.e. have finished reading this one's copy.
+__device__ __forceinline__ void hr_block_sum2(double& a, double& b, HrShared& sh, HrThread& th) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-  for (int i = 0; i < N; ++i) v[i] = MAX ? hm_warp_max(v[i]) : hm_warp_sum(v[i]);
-  __syncthreads();
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  double(*buf)[HR_THREADS / 32] = sh.redd[th.red++ & 1];
   if (lane == 0) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) sh.red[i][warp] = v[i];
+    buf[0][warp] = a;
+    buf[1][warp] = b;
   }
   __syncthreads();
+  a = lane < HR_THREADS / 32 ? buf[0][lane] : 0.0;
+  b = lane < HR_THREADS / 32 ? buf[1][lane] : 0.0;
 #pragma unroll
-  for (int i = 0; i < N; ++i) {
-    float r = lane < HR_THREADS / 32 ? sh.red[i][lane] : 0.f;   // maxima here are of absolute values
-    v[i] = MAX ? hm_warp_max(r) : hm_warp_sum(r);
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+}
+__device__ __forceinline__ void hr_block_max2(float& a, float& b, HrShared& sh, HrThread& th) {   // of absolute values
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = hm_warp_max(a);
+  b = hm_warp_max(b);
+  float(*buf)[HR_THREADS / 32] = sh.redf[th.red++ & 1];
+  if (lane == 0) {
+    buf[0][warp] = a;
+    buf[1][warp] = b;
+  }
+  __syncthreads();
+  a = hm_warp_max(lane < HR_THREADS / 32 ? buf[0][lane] : 0.f);
+  b = hm_warp_max(lane < HR_THREADS / 32 ? buf[1][lane] : 0.f);
+}
+
+// Quantise with the bin index `bin(x)`, add every value to its bin's sum and count, then (after a barrier) write the
+// bins' means as the record's codebook and leave the histogram zeroed for its next user.
+template <typename BinFn>
+__device__ __forceinline__ void hr_quantise_with_bin_means(const float (&v)[HR_ROWS][4], int n, unsigned char* rec,
+                                                           unsigned char* payload, HrShared& sh, BinFn bin) {
+  const int hw = threadIdx.x >> 6;
+#pragma unroll
+  for (int r = 0; r < HR_ROWS; ++r) {
+    const int i = hr_elem(r);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int b = bin(v[r][k]);
+      packed |= (uint32_t)b << (8 * k);
+      if (i + k < n) {
+        atomicAdd(&sh.hsum[hw][b], v[r][k]);
+        atomicAdd(&sh.hcnt[hw][b], 1);
+      }
+    }
+    *reinterpret_cast<uint32_t*>(payload + i) = packed;
+  }
+  __syncthreads();
+  if (threadIdx.x < 256) {
+    float total = 0.f;
+    int count = 0;
+#pragma unroll
+    for (int w = 0; w < HR_THREADS / 64; ++w) {
+      total += sh.hsum[w][threadIdx.x];
+      count += sh.hcnt[w][threadIdx.x];
+      sh.hsum[w][threadIdx.x] = 0.f;
+      sh.hcnt[w][threadIdx.x] = 0;
+    }
+    reinterpret_cast<float*>(rec)[threadIdx.x] = total / (float)(count > 0 ? count : 1);
   }
 }
 
 // Encode the chunk held in registers (v[r][k] = element hr_elem(r) + k, elements >= n are zero) into `rec`
 // (header + payload). Every thread of the CTA calls this. Elements >= n still get payload bytes (of value zero or
-// whatever zero maps to); they are never decoded.
-__device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, unsigned char* rec, HrShared& sh) {
+// whatever zero maps to); they are never decoded. The bin histogram in shared memory is zero on entry and on return;
+// a caller may start the next encode (or hr_open) without a barrier in between.
+__device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, unsigned char* rec, HrShared& sh, HrThread& th) {
   unsigned char* payload = rec + hr_header_bytes(codec);
   if (codec == HB_FLOAT16) {
 #pragma unroll
@@ -189,26 +251,23 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
     return;
   }
   if (codec == HB_MEANSTD16 || codec == HB_UNIFORM8) {
-    float s1[1] = {0.f}, s2[1] = {0.f};
+    // sum and sum of squares in double precision (padding elements are zero): one reduction, no cancellation to
+    // speak of even when the mean dwarfs the spread
+    double s1 = 0.0, s2 = 0.0;
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) s1[0] += v[r][k];   // padding elements are zero
-    hr_block_reduce<1, false>(s1, sh);
-    const float mean = s1[0] / (float)n;
-    // centred second pass over the registers: no cancellation
-#pragma unroll
-    for (int r = 0; r < HR_ROWS; ++r) {
-      const int i = hr_elem(r);
-#pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float d = (i + k < n) ? v[r][k] - mean : 0.f;
-        s2[0] = fmaf(d, d, s2[0]);
+        const double x = (double)v[r][k];
+        s1 += x;
+        s2 = fma(x, x, s2);
       }
-    }
-    hr_block_reduce<1, false>(s2, sh);
+    hr_block_sum2(s1, s2, sh, th);
+    const double mean_d = s1 / (double)n;
+    const double m2 = fmax(s2 - s1 * mean_d, 0.0);   // centred sum of squares
+    const float mean = (float)mean_d;
     if (codec == HB_MEANSTD16) {
-      const float sd = fmaxf(sqrtf(s2[0] / (float)n), 1.1920929e-07f);
+      const float sd = fmaxf((float)sqrt(m2 / (double)n), 1.1920929e-07f);
       const float inv = 1.f / sd;
       if (threadIdx.x == 0) {
         reinterpret_cast<float*>(rec)[0] = mean;
@@ -227,35 +286,12 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       return;
     }
     // HB_UNIFORM8: 256 levels of width 6 sigma / 256 around the mean; the codebook holds the mean of every level
-    const float scale = 6.f * sqrtf(s2[0] / fmaxf((float)n - 1.f, 1.f)) / 256.f;
+    const float scale = 6.f * (float)sqrt(m2 / fmax((double)n - 1.0, 1.0)) / 256.f;
     const float inv = (scale > 0.f && isfinite(scale)) ? 1.f / scale : 1.f;
-    for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
-    __syncthreads();
-    const int hw = threadIdx.x >> 6;
-#pragma unroll
-    for (int r = 0; r < HR_ROWS; ++r) {
-      const int i = hr_elem(r);
-      unsigned char q[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        int b = (int)rintf((v[r][k] - mean) * inv) + 128;
-        b = b < 0 ? 0 : (b > 255 ? 255 : b);
-        q[k] = (unsigned char)b;
-        if (i + k < n) {
-          atomicAdd(&sh.hsum[hw][b], v[r][k]);
-          atomicAdd(&sh.hcnt[hw][b], 1);
-        }
-      }
-      *reinterpret_cast<uchar4*>(payload + i) = make_uchar4(q[0], q[1], q[2], q[3]);
-    }
-    __syncthreads();
-    if (threadIdx.x < 256) {
-      float total = 0.f;
-      int count = 0;
-#pragma unroll
-      for (int w = 0; w < HR_THREADS / 64; ++w) { total += sh.hsum[w][threadIdx.x]; count += sh.hcnt[w][threadIdx.x]; }
-      reinterpret_cast<float*>(rec)[threadIdx.x] = total / (float)(count > 0 ? count : 1);
-    }
+    hr_quantise_with_bin_means(v, n, rec, payload, sh, [&](float x) {
+      const int b = (int)rintf((x - mean) * inv) + 128;
+      return b < 0 ? 0 : (b > 255 ? 255 : b);
+    });
     return;
   }
   if (codec == HB_QUANTILE8) {
@@ -263,9 +299,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
     int stride = 1;
     while (stride * HR_SAMPLE < n) stride <<= 1;
     const int S = (n + stride - 1) / stride;
-    for (int i = threadIdx.x; i < HR_SAMPLE; i += HR_THREADS) sh.smp[i] = INFINITY;
-    for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
-    __syncthreads();
+    for (int i = S + threadIdx.x; i < HR_SAMPLE; i += HR_THREADS) sh.smp[i] = INFINITY;
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
@@ -274,7 +308,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
         if (i + k < n && ((i + k) & (stride - 1)) == 0) sh.smp[(i + k) / stride] = v[r][k];
     }
     __syncthreads();
-    for (int size = 2; size <= HR_SAMPLE; size <<= 1) {
+    for (int size = 2; size <= HR_SAMPLE; size <<= 1) {   // bitonic sort
       for (int st = size >> 1; st > 0; st >>= 1) {
         for (int t = threadIdx.x; t < HR_SAMPLE / 2; t += HR_THREADS) {
           const int i = 2 * t - (t & (st - 1));
@@ -296,35 +330,13 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       sh.table[threadIdx.x] = b;
     }
     __syncthreads();
-    const int hw = threadIdx.x >> 6;
-#pragma unroll
-    for (int r = 0; r < HR_ROWS; ++r) {
-      const int i = hr_elem(r);
-      unsigned char q[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int b = hb_bucketize(sh.table, v[r][k]);
-        q[k] = (unsigned char)b;
-        if (i + k < n) {
-          atomicAdd(&sh.hsum[hw][b], v[r][k]);
-          atomicAdd(&sh.hcnt[hw][b], 1);
-        }
-      }
-      *reinterpret_cast<uchar4*>(payload + i) = make_uchar4(q[0], q[1], q[2], q[3]);
-    }
-    __syncthreads();
-    if (threadIdx.x < 256) {
-      float total = 0.f;
-      int count = 0;
-#pragma unroll
-      for (int w = 0; w < HR_THREADS / 64; ++w) { total += sh.hsum[w][threadIdx.x]; count += sh.hcnt[w][threadIdx.x]; }
-      reinterpret_cast<float*>(rec)[threadIdx.x] = total / (float)(count > 0 ? count : 1);
-    }
+    hr_quantise_with_bin_means(v, n, rec, payload, sh, [&](float x) { return hb_bucketize(sh.table, x); });
     return;
   }
   // HB_BLOCKWISE8: rows [b * RPB, (b + 1) * RPB) of every thread belong to block b (4096 elements)
   {
     constexpr int RPB = HR_ROWS / HR_BLOCKS;
+    static_assert(HR_BLOCKS == 2, "two block maxima travel in one reduction");
     float m[HR_BLOCKS];
 #pragma unroll
     for (int b = 0; b < HR_BLOCKS; ++b) {
@@ -334,16 +346,16 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
 #pragma unroll
         for (int k = 0; k < 4; ++k) m[b] = fmaxf(m[b], fabsf(v[RPB * b + rr][k]));
     }
-    hr_block_reduce<HR_BLOCKS, true>(m, sh);
+    hr_block_max2(m[0], m[1], sh, th);
     if (threadIdx.x < HR_BLOCKS) reinterpret_cast<float*>(rec)[threadIdx.x] = m[threadIdx.x];
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
       const float inv = 1.f / fmaxf(m[r / RPB], 1.17549435e-38f);
-      unsigned char q[4];
+      uint32_t packed = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) q[k] = (unsigned char)hb_bucketize(sh.mid, v[r][k] * inv);
-      *reinterpret_cast<uchar4*>(payload + i) = make_uchar4(q[0], q[1], q[2], q[3]);
+      for (int k = 0; k < 4; ++k) packed |= (uint32_t)hb_bucketize(sh.mid, v[r][k] * inv) << (8 * k);
+      *reinterpret_cast<uint32_t*>(payload + i) = packed;
     }
   }
 }
@@ -393,20 +405,21 @@ __device__ __forceinline__ void hr_fetch(int codec, const unsigned char* src, in
   }
 }
 
-// Make a fetched record decodable: the codebook of an 8-bit record goes to shared memory (two barriers), the scalars of
-// the other headers are handed back in registers. `copy` (optional) receives the header as well.
-__device__ __forceinline__ void hr_open(int codec, const HrAhead& a, HrShared& sh, unsigned char* copy, float& mean, float& sd,
-                                        float absmax[HR_BLOCKS]) {
+// Make a fetched record decodable: the codebook of an 8-bit record goes to shared memory (one barrier; consecutive
+// records alternate between two copies), the scalars of the other headers are handed back in registers. `copy`
+// (optional) receives the header as well. Returns the codebook to decode with.
+__device__ __forceinline__ const float* hr_open(int codec, const HrAhead& a, HrShared& sh, HrThread& th, unsigned char* copy,
+                                                float& mean, float& sd, float absmax[HR_BLOCKS]) {
   mean = 0.f;
   sd = 1.f;
   if (codec == HB_UNIFORM8 || codec == HB_QUANTILE8) {
-    __syncthreads();   // the previous user of sh.cb is done
+    float* cb = sh.cb[th.cb++ & 1];
     if (threadIdx.x < 256) {
-      sh.cb[threadIdx.x] = a.hdr.x;
+      cb[threadIdx.x] = a.hdr.x;
       if (copy) reinterpret_cast<float*>(copy)[threadIdx.x] = a.hdr.x;
     }
     __syncthreads();
-    return;
+    return cb;
   }
   if (codec == HB_MEANSTD16) {
     mean = a.hdr.x;
@@ -416,10 +429,11 @@ __device__ __forceinline__ void hr_open(int codec, const HrAhead& a, HrShared& s
     if (HR_BLOCKS > 1) absmax[HR_BLOCKS - 1] = a.hdr.y;
   }
   if (copy && threadIdx.x == 0 && hr_header_bytes(codec) == 16) *reinterpret_cast<float4*>(copy) = a.hdr;
+  return sh.code;
 }
 
 // Decode row r of a fetched record.
-__device__ __forceinline__ void hr_decode_ahead(int codec, const HrAhead& a, int r, float mean, float sd, const HrShared& sh,
+__device__ __forceinline__ void hr_decode_ahead(int codec, const HrAhead& a, int r, float mean, float sd, const float* cb,
                                                 const float* absmax, float out[4]) {
   if (codec == HB_NONE) {
     out[0] = __uint_as_float(a.w[4 * r]); out[1] = __uint_as_float(a.w[4 * r + 1]);
@@ -433,7 +447,6 @@ __device__ __forceinline__ void hr_decode_ahead(int codec, const HrAhead& a, int
     }
   } else {
     const uint32_t q = a.w[r];
-    const float* cb = codec == HB_BLOCKWISE8 ? sh.code : sh.cb;
     const float m = codec == HB_BLOCKWISE8 ? absmax[r / (HR_ROWS / HR_BLOCKS)] : 1.f;
     out[0] = cb[q & 255u] * m; out[1] = cb[(q >> 8) & 255u] * m;
     out[2] = cb[(q >> 16) & 255u] * m; out[3] = cb[q >> 24] * m;
@@ -509,7 +522,7 @@ __device__ __forceinline__ bool hr_chunks_done(int* counter, int add, int n_chun
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-__device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
+__device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& sh, HrThread& th) {
   unsigned char* my = g.base[g.me];
   unsigned long long* ready = reinterpret_cast<unsigned long long*>(my + g.lay.ready[g.parity]);
   const unsigned long long flag = (unsigned long long)g.epoch | ((unsigned long long)__float_as_uint(g.my_weight) << 32);
@@ -535,15 +548,14 @@ __device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& s
         for (int k = 0; k < 4; ++k) v[r][k] = (i + k < n) ? x[i + k] : 0.f;
       }
     }
-    if (c != c0) __syncthreads();   // the previous chunk's encoder is done with the shared tables
-    hr_encode_chunk(v, n, part.codec, my + g.lay.outbox[g.parity] + part.enc_off + (long long)c * stride, sh);
+    hr_encode_chunk(v, n, part.codec, my + g.lay.outbox[g.parity] + part.enc_off + (long long)c * stride, sh, th);
   }
   const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
   __syncthreads();
   if (threadIdx.x == 0 && hr_chunks_done(g.part_done + p, z, n_chunks)) hr_st_release_sys_u64(ready + p, flag);
 }
 
-__device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
+__device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared& sh, HrThread& th) {
   const HrPart part = g.parts[p];
   const int codec = part.codec, j = part.local_idx, me = g.me;
   const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
@@ -631,7 +643,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
       }
       unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
       float mean, sd, absmax[HR_BLOCKS] = {};
-      hr_open(codec, cur, sh, codec == HB_NONE ? nullptr : local, mean, sd, absmax);
+      const float* cb = hr_open(codec, cur, sh, th, codec == HB_NONE ? nullptr : local, mean, sd, absmax);
 #pragma unroll
       for (int r = 0; r < HR_ROWS; ++r) {
         // compressed records: keep a copy where this sender's delta will be written
@@ -640,7 +652,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
         else if (hb_elem_bytes(codec) == 1)
           *reinterpret_cast<uint32_t*>(local + hdr + hr_elem(r)) = cur.w[r];
         float o[4];
-        hr_decode_ahead(codec, cur, r, mean, sd, sh, absmax, o);
+        hr_decode_ahead(codec, cur, r, mean, sd, cb, absmax, o);
 #pragma unroll
         for (int q = 0; q < 4; ++q) acc[r][q] = fmaf(w, o[q], acc[r][q]);
       }
@@ -664,25 +676,24 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
     }
     // deltas: avg - decode(copy of the sender's record), encoded over the copy, one sender after the other
     if (codec != HB_NONE && !dead) {
-      __syncthreads();   // the copies' 16-byte headers were written by thread 0
+      if (hdr == 16) __syncthreads();   // the copies' 16-byte headers were written by thread 0
       for (int k = 0; k < n_inc; ++k) {
         const int s = sh.order[k];
         unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
         HrAhead mine;
         hr_fetch(codec, local, n, mine);
         float mean, sd, absmax[HR_BLOCKS] = {};
-        hr_open(codec, mine, sh, nullptr, mean, sd, absmax);
+        const float* cb = hr_open(codec, mine, sh, th, nullptr, mean, sd, absmax);
         float d[HR_ROWS][4];
 #pragma unroll
         for (int r = 0; r < HR_ROWS; ++r) {
           const int i = hr_elem(r);
           float o[4];
-          hr_decode_ahead(codec, mine, r, mean, sd, sh, absmax, o);
+          hr_decode_ahead(codec, mine, r, mean, sd, cb, absmax, o);
 #pragma unroll
           for (int q = 0; q < 4; ++q) d[r][q] = (i + q < n) ? acc[r][q] - o[q] : 0.f;
         }
-        __syncthreads();   // every thread has decoded with the old codebook before anybody writes the new one
-        hr_encode_chunk(d, n, codec, local, sh);
+        hr_encode_chunk(d, n, codec, local, sh, th);
       }
     }
   }
@@ -697,7 +708,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
   }
 }
 
-__device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& sh) {
+__device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& sh, HrThread& th) {
   if (!g.sends[g.me]) return;
   const HrPart part = g.parts[p];
   const int me = g.me, owner = part.owner, codec = part.codec;
@@ -734,13 +745,13 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& 
     const HrAhead cur = ahead;
     if (c + 1 < c0 + z) hr_fetch(codec, source(c + 1), chunk_len(c + 1), ahead);
     float mean, sd, absmax[HR_BLOCKS] = {};
-    hr_open(codec, cur, sh, nullptr, mean, sd, absmax);
+    const float* cb = hr_open(codec, cur, sh, th, nullptr, mean, sd, absmax);
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
       const int i = hr_elem(r);
       if (i + 4 > n) continue;   // parts are whole multiples of four elements
       float dv[4];
-      hr_decode_ahead(codec, cur, r, mean, sd, sh, absmax, dv);
+      hr_decode_ahead(codec, cur, r, mean, sd, cb, absmax, dv);
       float4 xv = *reinterpret_cast<const float4*>(x + i);
       if (codec == HB_NONE) {   // the record is the average itself
         xv.x = fmaf(alpha, dv[0] - xv.x, xv.x); xv.y = fmaf(alpha, dv[1] - xv.y, xv.y);
@@ -756,18 +767,20 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& 
 
 __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_constant__ HrRound g) {
   __shared__ HrShared sh;
+  HrThread th;
   if (threadIdx.x < 256) {
     sh.code[threadIdx.x] = g.code[threadIdx.x];
     sh.mid[threadIdx.x] = g.code[256 + threadIdx.x];
   }
+  for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
   // Items are dealt round-robin. The list is ordered send, reduce, apply, so every CTA finishes its send items
   // before it may wait for a groupmate, and nothing that a groupmate needs from this GPU queues up behind a wait.
   for (int idx = g.item_begin + (int)blockIdx.x; idx < g.item_end; idx += (int)gridDim.x) {
     __syncthreads();
     const int4 it = g.items[idx];
-    if (idx < g.n_send) hr_send_item(g, it.x, it.y, it.z, sh);
-    else if (idx < g.n_send + g.n_reduce) hr_reduce_item(g, it.x, it.y, it.z, sh);
-    else hr_apply_item(g, it.x, it.y, it.z, sh);
+    if (idx < g.n_send) hr_send_item(g, it.x, it.y, it.z, sh, th);
+    else if (idx < g.n_send + g.n_reduce) hr_reduce_item(g, it.x, it.y, it.z, sh, th);
+    else hr_apply_item(g, it.x, it.y, it.z, sh, th);
   }
   // the last CTA to leave closes the round: acknowledges that this GPU has finished reading its groupmates'
   // arenas, hands the status words to the host and clears the scratch for the next round

@@ -36,6 +36,9 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles, num_splits, kblocks_per_split, total_kblocks;
   int epi, out_f32, reduce_add, has_aux;
   const float* bias;
+  const __nv_bfloat16* add;   // optional bf16 [M][N] (row stride ld_add) combined with the result before it is stored:
+  long long ld_add;           //   add_mode 0: result + add;  1: result * gelu_tanh'(add)
+  int add_mode;
   float alpha;
   int* err;
   // Grouped problems (many experts in one launch). Mode 1: the rows of A and D are split into groups of whole
@@ -257,13 +260,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int half = 0; half < boxes_per_store; ++half) {
           uint32_t r[32];
           tc_ld32(t_addr + (uint32_t)(c0 + half * COLS_PER_BOX), r);
+          const int gcol0 = n_tile * BLOCK_N + c0 + half * COLS_PER_BOX;
+          // the addend's 64 bytes of this thread's row travel while the accumulator is read
+          uint4 addend[4] = {};
+          if (p.add != nullptr) {
+            const long long grow = (long long)m_tile * BLOCK_M + row;
+            if (grow < p.M) {
+#pragma unroll
+              for (int ch = 0; ch < 4; ++ch)
+                if (gcol0 + 8 * ch < p.N) addend[ch] = *reinterpret_cast<const uint4*>(p.add + grow * p.ld_add + gcol0 + 8 * ch);
+            }
+          }
           tc_wait_ld();
           float v[32];
-          const int gcol0 = n_tile * BLOCK_N + c0 + half * COLS_PER_BOX;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             v[j] = __uint_as_float(r[j]) * p.alpha;
             if (p.epi != EPI_NONE && bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(bias + gcol0 + j);
+          }
+          if (p.add != nullptr) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&addend[ch]);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (p.add_mode == 0) {
+                  v[8 * ch + 2 * q] += __low2float(h[q]);
+                  v[8 * ch + 2 * q + 1] += __high2float(h[q]);
+                } else {
+                  v[8 * ch + 2 * q] *= hm_gelu_tanh_grad(__low2float(h[q]));
+                  v[8 * ch + 2 * q + 1] *= hm_gelu_tanh_grad(__high2float(h[q]));
+                }
+              }
+            }
           }
           // 16-byte chunks of this thread's row, XOR-swizzled like the tensor map (chunk ^= row & 7)
           if (p.out_f32) {
@@ -713,6 +742,9 @@ struct GemmCall {
   int sms;
   int group_mode = 0, num_groups = 1;
   const int* group_table = nullptr;
+  const void* add = nullptr;
+  long long ldadd = 0;
+  int add_mode = 0;
 };
 
 template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN>
@@ -755,6 +787,7 @@ int launch(const GemmCall& c, cudaStream_t stream) {
   if (p.num_splits > 1 && !c.reduce_add) return -13;
   p.epi = c.epi; p.out_f32 = c.out_f32; p.reduce_add = c.reduce_add; p.has_aux = c.aux != nullptr;
   p.bias = c.bias; p.alpha = c.alpha; p.err = c.err;
+  p.add = (const __nv_bfloat16*)c.add; p.ld_add = c.ldadd; p.add_mode = c.add_mode;
   p.group_mode = c.group_mode; p.num_groups = c.num_groups; p.group_table = c.group_table;
   p.group_b_rows = B_MN ? c.K : c.N; p.group_d_rows = c.M; p.group_bias = c.N;
   if (c.group_mode == 2) { p.num_splits = 1; p.kblocks_per_split = p.total_kblocks; }
@@ -808,6 +841,7 @@ int launch_pair(const GemmCall& c, cudaStream_t stream) {
   if (p.num_splits > 1 && !c.reduce_add) return -13;
   p.epi = c.epi; p.out_f32 = c.out_f32; p.reduce_add = c.reduce_add; p.has_aux = c.aux != nullptr;
   p.bias = c.bias; p.alpha = c.alpha; p.err = c.err;
+  p.add = (const __nv_bfloat16*)c.add; p.ld_add = c.ldadd; p.add_mode = c.add_mode;
   p.group_mode = c.group_mode; p.num_groups = c.num_groups; p.group_table = c.group_table;
   p.group_b_rows = 0; p.group_d_rows = c.M; p.group_bias = 0;
   if (c.group_mode == 2) { p.num_splits = 1; p.kblocks_per_split = p.total_kblocks; }
@@ -873,6 +907,29 @@ HM_API int hm_tc_gemm(const void* a, const void* b, void* d, void* aux, const vo
       default: return -16;
     }
   }
+  switch (block_n) {
+    case 256: return dispatch_major<256, 4, false>(c, stream);
+    case 128: return dispatch_major<128, 6, false>(c, stream);
+    case 64: return dispatch_major<64, 8, false>(c, stream);
+    default: return -16;
+  }
+}
+
+// hm_tc_gemm for bf16 operands and a bf16 result with a second input in the epilogue: `add` is a bf16 [M][N] matrix
+// with row stride ldadd (elements; rows 16-byte aligned).
+//   add_mode 0: D = alpha * A B^T (+ bias) + add       (input-gradient GEMM of a layer whose input also feeds a
+//                                                       residual connection: the two gradients meet in the epilogue)
+//   add_mode 1: D = (alpha * A B^T) * gelu_tanh'(add)  (input-gradient GEMM behind a GELU: `add` holds the
+//                                                       pre-activation values)
+HM_API int hm_tc_gemm_add(const void* a, const void* b, void* d, const void* add, const void* bias, int M, int N, int K,
+                          long long lda, long long ldb, long long ldd, long long ldadd, int a_mn, int b_mn, int epi,
+                          int add_mode, float alpha, int block_n, void* err, int sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (epi == EPI_BIAS_GELU || (ldadd % 8) != 0 || (N % 8) != 0) return -18;
+  GemmCall c{a, b, d, nullptr, (const float*)bias, M, N, K, lda, ldb, ldd, 0, a_mn, b_mn, 0, 0, epi, 0, 1, alpha, (int*)err, sms};
+  c.add = add;
+  c.ldadd = ldadd;
+  c.add_mode = add_mode;
   switch (block_n) {
     case 256: return dispatch_major<256, 4, false>(c, stream);
     case 128: return dispatch_major<128, 6, false>(c, stream);

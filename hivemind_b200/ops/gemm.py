@@ -60,13 +60,16 @@ def tc_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool 
             out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
             bias: Optional[torch.Tensor] = None, gelu: bool = False, aux: Optional[torch.Tensor] = None,
             reduce_add: bool = False, splits: int = 1, alpha: float = 1.0,
-            block_n: Optional[int] = None, pair: Optional[bool] = None) -> torch.Tensor:
+            block_n: Optional[int] = None, pair: Optional[bool] = None, add: Optional[torch.Tensor] = None,
+            add_is_gelu_input: bool = False) -> torch.Tensor:
     """``D[M,N] = epi(alpha * sum_k A(m,k) B(n,k))``.
 
     :param a: ``[M, K]`` (or ``[K, M]`` when ``a_mn``), bf16 or fp32 (fp32 is multiplied as tf32)
     :param b: ``[N, K]`` (or ``[K, N]`` when ``b_mn``), same dtype as ``a``
     :param out: destination ``[M, N]`` (bf16 or fp32); with ``reduce_add`` the result is added to it (fp32 only)
     :param bias: fp32 ``[N]`` added before the optional tanh-GELU; ``aux`` (bf16) receives the pre-GELU values
+    :param add: bf16 ``[M, N]`` added to the result in the epilogue (bf16 output, no GELU, one-CTA kernel); with
+      ``add_is_gelu_input`` the result is instead multiplied by ``gelu_tanh'(add)`` (backward through a GELU)
     :param splits: split-K factor (needs ``reduce_add``)
     :param pair: use the two-CTA kernel (one 256x256 tile per pair of SMs, bf16 only); default: when the problem
       has at least one full 256x256 tile and ``HIVEMIND_B200_GEMM_PAIR`` is not ``0``
@@ -89,6 +92,13 @@ def tc_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool 
             aux.copy_(res)
         if gelu:
             res = F.gelu(res, approximate="tanh")
+        if add is not None and add_is_gelu_input:
+            z = add.to(torch.float32).requires_grad_()
+            with torch.enable_grad():
+                (dz,) = torch.autograd.grad(F.gelu(z, approximate="tanh").sum(), z)
+            res = res * dz
+        elif add is not None:
+            res = res + add.to(torch.float32)
         if reduce_add:
             out.add_(res.to(out.dtype))
         else:
@@ -108,6 +118,18 @@ def tc_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool 
     if block_n is None:
         block_n = _pick_block_n(n, m, tf32, sms)
     epi = EPI_BIAS_GELU if gelu else (EPI_BIAS if bias is not None else EPI_NONE)
+    if add is not None:
+        assert not tf32 and not gelu and aux is None and not reduce_add and out.dtype == torch.bfloat16 and not pair
+        assert add.dtype == torch.bfloat16 and add.shape == (m, n) and add.stride(1) == 1
+        with torch.cuda.device(a.device):
+            code = lib.hm_tc_gemm_add(
+                _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(add), _lib.ptr(bias), m, n, k,
+                ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(out.stride(0)),
+                ctypes.c_longlong(add.stride(0)), int(a_mn), int(b_mn), epi, int(add_is_gelu_input),
+                ctypes.c_float(alpha), block_n,
+                _lib.ptr(_err_flag(a.device)), sms, _lib.stream_ptr(a.device))
+        _lib.check(code, "hm_tc_gemm_add")
+        return out
     if pair is None:
         pair = _PAIR_DEFAULT and not tf32 and m >= 256 and n >= 256 and block_n == 256
     if pair:
@@ -172,18 +194,52 @@ def _split_k_for(m: int, n: int, k: int, sms: int, pair: bool = False) -> int:
     return best
 
 
+def _as_rows(t: torch.Tensor, width: int) -> torch.Tensor:
+    """``t`` as a contiguous bf16 matrix with ``width`` columns."""
+    t2 = t.reshape(-1, width)
+    if t2.dtype != torch.bfloat16:
+        t2 = t2.to(torch.bfloat16)
+    return t2 if t2.is_contiguous() else t2.contiguous()
+
+
+def _weight_grad(weight: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor) -> Optional[torch.Tensor]:
+    """``dW = dy2^T x2`` accumulated in fp32. With an fp32 ``weight.grad`` in place the GEMM adds straight into it and
+    None is returned (nothing is left for autograd to accumulate); otherwise the gradient is returned."""
+    out_f, in_f, tokens = dy2.shape[1], x2.shape[1], dy2.shape[0]
+    # weight gradients contract over all tokens with both operands MN-major: the two-CTA kernel is about
+    # 1.5x faster than the one-CTA kernel on these (1280 vs 800 TFLOP/s for 4096 x 1024 x 16384)
+    use_pair = out_f >= 256 and in_f >= 256
+    splits = _split_k_for(out_f, in_f, tokens, _lib.sm_count(dy2.device), pair=use_pair)
+    in_place = weight.grad is not None and weight.grad.dtype == torch.float32 and weight.grad.is_contiguous()
+    gw = weight.grad if in_place else torch.zeros(weight.shape, dtype=torch.float32, device=dy2.device)
+    tc_gemm(dy2, x2, a_mn=True, b_mn=True, out=gw, reduce_add=True, splits=splits, pair=use_pair)
+    return None if in_place else gw.to(weight.dtype)
+
+
+def _bias_grad_buffer(bias: torch.Tensor, width: int, device: torch.device):
+    """fp32 buffer that column-sum kernels add the bias gradient to, and whether it is ``bias.grad`` itself."""
+    in_place = bias.grad is not None and bias.grad.dtype == torch.float32 and bias.grad.is_contiguous()
+    return (bias.grad if in_place else torch.zeros(width, dtype=torch.float32, device=device)), in_place
+
+
+def _skip_rows(dskip: Optional[torch.Tensor], width: int) -> Optional[torch.Tensor]:
+    """The gradient that came back through a passed-through input, as the bf16 matrix the GEMM epilogue adds."""
+    if dskip is None:
+        return None
+    skip2 = dskip.reshape(-1, width)
+    if skip2.dtype != torch.bfloat16 or skip2.stride(1) != 1 or skip2.stride(0) % 8 != 0:
+        skip2 = skip2.to(torch.bfloat16).contiguous()
+    return skip2
+
+
 class _LinearFn(torch.autograd.Function):
     """y = act(x W^T + b) with bf16 tensor-core GEMMs and fp32 weight-gradient accumulation."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, weight_lp, activation, skip_bias_grad=False):
+    def forward(ctx, x, weight, bias, weight_lp, activation, skip_bias_grad=False, passthrough=False):
         ctx.skip_bias_grad = skip_bias_grad
-        in_f = x.shape[-1]
-        x2 = x.reshape(-1, in_f)
-        if x2.dtype != torch.bfloat16:
-            x2 = x2.to(torch.bfloat16)
-        if not x2.is_contiguous():
-            x2 = x2.contiguous()
+        ctx.set_materialize_grads(False)
+        x2 = _as_rows(x, x.shape[-1])
         w = weight_lp if weight_lp is not None else weight.detach().to(torch.bfloat16)
         b32 = None
         if bias is not None:
@@ -197,27 +253,24 @@ class _LinearFn(torch.autograd.Function):
         ctx.bias = bias
         ctx.x_shape = x.shape
         ctx.x_dtype = x.dtype
-        return y.view(*x.shape[:-1], w.shape[0])
+        y = y.view(*x.shape[:-1], w.shape[0])
+        return (y, x.view_as(x)) if passthrough else y
 
     @staticmethod
-    def backward(ctx, dy):
-        from hivemind_b200.ops.norm_act import _BiasGeluFn  # noqa: F401  (kernel shared with bias_gelu)
+    def backward(ctx, dy, dskip=None):
+        if dy is None:  # only the passed-through input was used downstream
+            return dskip, None, None, None, None, None, None
         x2, w, pre = ctx.saved_tensors
         weight, bias = ctx.weight, ctx.bias
         out_f = w.shape[0]
-        dy2 = dy.reshape(-1, out_f)
-        if dy2.dtype != torch.bfloat16:
-            dy2 = dy2.to(torch.bfloat16)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
+        dy2 = _as_rows(dy, out_f)
         lib = _lib.load_library()
         dev = x2.device
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         need_b = bias is not None and ctx.needs_input_grad[2] and not ctx.skip_bias_grad
         grad_b = None
         if need_b:
-            use_b_buf = bias.grad is not None and bias.grad.dtype == torch.float32 and bias.grad.is_contiguous()
-            gb = bias.grad if use_b_buf else torch.zeros(out_f, dtype=torch.float32, device=dev)
+            gb, b_in_place = _bias_grad_buffer(bias, out_f, dev)
         if pre is not None:
             # d(pre) = dy * gelu'(pre); the same kernel also accumulates the bias gradient column sums
             dpre = torch.empty_like(pre)
@@ -230,29 +283,94 @@ class _LinearFn(torch.autograd.Function):
         elif need_b:
             colsum_(gb, dy2)
         if need_b:
-            grad_b = None if use_b_buf else gb.to(bias.dtype)
+            grad_b = None if b_in_place else gb.to(bias.dtype)
         grad_x = None
         if need_x:
-            grad_x = tc_gemm(dy2, w, b_mn=True, out_dtype=torch.bfloat16).view(ctx.x_shape)
+            # the gradient that arrived through the passed-through input is added in the GEMM's epilogue
+            skip2 = _skip_rows(dskip, x2.shape[1])
+            grad_x = tc_gemm(dy2, w, b_mn=True, out_dtype=torch.bfloat16, add=skip2, pair=False if skip2 is not None else None)
+            grad_x = grad_x.view(ctx.x_shape)
             if grad_x.dtype != ctx.x_dtype:
                 grad_x = grad_x.to(ctx.x_dtype)
-        grad_w = None
-        if need_w:
-            tokens = dy2.shape[0]
-            # weight gradients contract over all tokens with both operands MN-major: the two-CTA kernel is about
-            # 1.5x faster than the one-CTA kernel on these (1280 vs 800 TFLOP/s for 4096 x 1024 x 16384)
-            use_pair = out_f >= 256 and x2.shape[1] >= 256
-            splits = _split_k_for(out_f, x2.shape[1], tokens, _lib.sm_count(dev), pair=use_pair)
-            use_w_buf = weight.grad is not None and weight.grad.dtype == torch.float32 and weight.grad.is_contiguous()
-            gw = weight.grad if use_w_buf else torch.zeros(weight.shape, dtype=torch.float32, device=dev)
-            tc_gemm(dy2, x2, a_mn=True, b_mn=True, out=gw, reduce_add=True, splits=splits, pair=use_pair)
-            grad_w = None if use_w_buf else gw.to(weight.dtype)
-        return grad_x, grad_w, grad_b, None, None, None
+        elif dskip is not None:
+            grad_x = dskip
+        grad_w = _weight_grad(weight, dy2, x2) if need_w else None
+        return grad_x, grad_w, grad_b, None, None, None, None
+
+
+class _FeedForwardFn(torch.autograd.Function):
+    """``gelu(x W1^T + b1) W2^T + b2`` as ONE autograd node, so that the backward pass can keep its intermediate
+    results inside GEMM epilogues: the derivative of the GELU is applied where the gradient of the hidden activations
+    is produced, and the gradient of a passed-through input is added where the input gradient is produced."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, w1_lp, w2_lp, skip_out_bias_grad, passthrough):
+        ctx.set_materialize_grads(False)
+        ctx.skip_out_bias_grad = skip_out_bias_grad
+        x2 = _as_rows(x, x.shape[-1])
+        w1b = w1_lp if w1_lp is not None else w1.detach().to(torch.bfloat16)
+        w2b = w2_lp if w2_lp is not None else w2.detach().to(torch.bfloat16)
+        pre = torch.empty((x2.shape[0], w1b.shape[0]), dtype=torch.bfloat16, device=x.device)
+        inter = tc_gemm(x2, w1b, bias=b1.detach().to(torch.float32), gelu=True, aux=pre, out_dtype=torch.bfloat16)
+        out = tc_gemm(inter, w2b, bias=b2.detach().to(torch.float32), out_dtype=torch.bfloat16)
+        ctx.save_for_backward(x2, w1b, w2b, pre, inter)
+        ctx.params = (w1, b1, w2, b2)
+        ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
+        out = out.view(*x.shape[:-1], w2b.shape[0])
+        return (out, x.view_as(x)) if passthrough else out
+
+    @staticmethod
+    def backward(ctx, dout, dskip=None):
+        if dout is None:
+            return (dskip,) + (None,) * 8
+        x2, w1b, w2b, pre, inter = ctx.saved_tensors
+        w1, b1, w2, b2 = ctx.params
+        need = ctx.needs_input_grad
+        dev = x2.device
+        dout2 = _as_rows(dout, w2b.shape[0])
+        grad_b2 = None
+        if need[4] and not ctx.skip_out_bias_grad:
+            gb2, in_place = _bias_grad_buffer(b2, w2b.shape[0], dev)
+            colsum_(gb2, dout2)
+            grad_b2 = None if in_place else gb2.to(b2.dtype)
+        # gradient of the pre-activations: (dout W2) * gelu'(pre), the product taken in the GEMM's epilogue
+        dpre = tc_gemm(dout2, w2b, b_mn=True, out_dtype=torch.bfloat16, add=pre, add_is_gelu_input=True, pair=False)
+        grad_w2 = _weight_grad(w2, dout2, inter) if need[3] else None
+        grad_b1 = None
+        if need[2]:
+            gb1, in_place = _bias_grad_buffer(b1, w1b.shape[0], dev)
+            colsum_(gb1, dpre)
+            grad_b1 = None if in_place else gb1.to(b1.dtype)
+        grad_x = None
+        if need[0]:
+            skip2 = _skip_rows(dskip, x2.shape[1])
+            grad_x = tc_gemm(dpre, w1b, b_mn=True, out_dtype=torch.bfloat16, add=skip2,
+                             pair=False if skip2 is not None else None).view(ctx.x_shape)
+            if grad_x.dtype != ctx.x_dtype:
+                grad_x = grad_x.to(ctx.x_dtype)
+        elif dskip is not None:
+            grad_x = dskip
+        grad_w1 = _weight_grad(w1, dpre, x2) if need[1] else None
+        return grad_x, grad_w1, grad_b1, grad_w2, grad_b2, None, None, None, None
+
+
+def feed_forward(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor, b2: torch.Tensor, *,
+                 w1_lp: Optional[torch.Tensor] = None, w2_lp: Optional[torch.Tensor] = None,
+                 skip_out_bias_grad: bool = False, passthrough: bool = False):
+    """``gelu_tanh(x @ w1.T + b1) @ w2.T + b2``. On CUDA this is one autograd node (four GEMMs forward and backward
+    plus two column sums); elsewhere it is two ``linear`` calls. ``skip_out_bias_grad`` and ``passthrough`` mean what
+    they mean for ``linear``: ``b2``'s gradient is taken by the LayerNorm that follows, and the returned copy of ``x``
+    carries the residual connection's gradient into the input-gradient GEMM."""
+    if _lib.use_kernels(x, w1, w2) and all(d % 8 == 0 for d in (*w1.shape, *w2.shape)):
+        return _FeedForwardFn.apply(x, w1, b1, w2, b2, w1_lp, w2_lp, skip_out_bias_grad, passthrough)
+    inter = linear(x, w1, b1, activation="gelu", weight_lp=w1_lp)
+    out = linear(inter, w2, b2, weight_lp=w2_lp, skip_bias_grad=skip_out_bias_grad)
+    return (out, x) if passthrough else out
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            activation: Optional[str] = None, weight_lp: Optional[torch.Tensor] = None,
-           skip_bias_grad: bool = False) -> torch.Tensor:
+           skip_bias_grad: bool = False, passthrough: bool = False):
     """``act(x @ weight.T + bias)`` with ``activation`` in (None, "gelu") (tanh-GELU).
 
     ``weight`` is the (fp32 or bf16) parameter that receives the gradient; ``weight_lp`` is an optional
@@ -261,11 +379,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
     ``skip_bias_grad``: the caller obtains the bias gradient elsewhere (``layer_norm(..., producer_bias=bias)`` takes
     it in the pass that produces this layer's output gradient), so this call leaves ``bias.grad`` alone.
+
+    ``passthrough``: return ``(y, x)``. Use the returned ``x`` for the residual connection around the layer: the
+    gradient that comes back through it is then added inside the input-gradient GEMM instead of by a separate pass.
     """
     in_f, out_f = weight.shape[1], weight.shape[0]
     if _lib.use_kernels(x, weight) and in_f % 8 == 0 and out_f % 8 == 0:
-        return _LinearFn.apply(x, weight, bias, weight_lp, activation, skip_bias_grad)
+        return _LinearFn.apply(x, weight, bias, weight_lp, activation, skip_bias_grad, passthrough)
     if bias is not None and skip_bias_grad:
         bias = bias.detach()
     y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
-    return F.gelu(y, approximate="tanh") if activation == "gelu" else y
+    y = F.gelu(y, approximate="tanh") if activation == "gelu" else y
+    return (y, x) if passthrough else y

@@ -186,3 +186,21 @@ def test_producer_bias_contract_on_the_pytorch_path():
     F.layer_norm(F.linear(xr, wr, biasr) + resr, (24,), gr, br, 1e-5).backward(dy)
     for mine, ref in ((x, xr), (w, wr), (bias, biasr), (g, gr), (b, br), (res, resr)):
         assert torch.allclose(mine.grad, ref.grad, atol=1e-4, rtol=1e-4)
+
+
+def test_feed_forward_on_the_pytorch_path_is_two_linears():
+    import torch.nn.functional as F
+
+    from hivemind_b200.ops.gemm import feed_forward
+
+    torch.manual_seed(1)
+    x = torch.randn(4, 7, 16, requires_grad=True)
+    w1, b1 = torch.randn(32, 16, requires_grad=True), torch.randn(32, requires_grad=True)
+    w2, b2 = torch.randn(16, 32, requires_grad=True), torch.randn(16, requires_grad=True)
+    out, skip = feed_forward(x, w1, b1, w2, b2, passthrough=True)
+    (out + skip).sum().backward()
+    refs = [t.detach().clone().requires_grad_() for t in (x, w1, b1, w2, b2)]
+    xr, w1r, b1r, w2r, b2r = refs
+    (F.linear(F.gelu(F.linear(xr, w1r, b1r), approximate="tanh"), w2r, b2r) + xr).sum().backward()
+    for mine, ref in zip((x, w1, b1, w2, b2), refs):
+        assert torch.allclose(mine.grad, ref.grad, atol=1e-4, rtol=1e-4)

@@ -323,6 +323,75 @@ def test_linear_autograd():
     assert torch.allclose(w.grad, ref, atol=0.5, rtol=3e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 256, 512), (4096, 1024, 3072), (129, 72, 64)])
+def test_tc_gemm_addend_epilogue(m, n, k):
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(5)
+    a = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(k, n, device=_dev(), dtype=torch.bfloat16)
+    wide = torch.randn(m, n + 8, device=_dev(), dtype=torch.bfloat16) * 30
+    add = wide[:, :n]  # a strided addend: rows 16-byte aligned, not contiguous
+    out = tc_gemm(a, b, b_mn=True, out_dtype=torch.bfloat16, add=add, pair=False)
+    check_kernel_errors()
+    ref = a.double() @ b.double() + add.double()
+    err = (out.double() - ref).abs()
+    assert (err <= 0.01 * ref.abs() + 0.02 * math.sqrt(k)).all()
+    plain = tc_gemm(a, b, b_mn=True, out_dtype=torch.bfloat16, pair=False)
+    assert ((out.float() - plain.float()) - add.float()).abs().max().item() < 0.02 * ref.abs().max().item()
+
+
+def test_linear_passthrough_adds_the_residual_gradient_in_the_gemm():
+    from hivemind_b200.ops.gemm import check_kernel_errors, linear
+
+    torch.manual_seed(14)
+    x = torch.randn(4, 130, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 256, device=_dev()) * 0.05).requires_grad_()
+    b = torch.randn(384, device=_dev()).requires_grad_()
+    y, skip = linear(x, w, b, passthrough=True)
+    dy, dskip = torch.randn_like(y), torch.randn_like(skip)
+    torch.autograd.backward([y, skip], [dy, dskip])
+    check_kernel_errors()
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.linear(xr, wr.to(torch.bfloat16).float(), br)
+    torch.autograd.backward([yr, xr * 1.0], [dy.float(), dskip.float()])
+    assert torch.allclose(x.grad.float(), xr.grad, atol=6e-2, rtol=3e-2)
+    assert torch.allclose(w.grad, wr.grad, atol=0.35, rtol=3e-2)
+    # only the passed-through tensor used: the gradient goes straight through
+    x.grad = None
+    _, skip = linear(x, w, b, passthrough=True)
+    skip.backward(dskip)
+    assert torch.equal(x.grad, dskip)
+
+
+@pytest.mark.parametrize("passthrough", [False, True])
+def test_feed_forward_node_matches_fp32_math(passthrough):
+    from hivemind_b200.ops.gemm import check_kernel_errors, feed_forward
+
+    torch.manual_seed(15)
+    dev = _dev()
+    x = torch.randn(3, 200, 256, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w1 = (torch.randn(1024, 256, device=dev) * 0.05).requires_grad_()
+    b1 = torch.randn(1024, device=dev).requires_grad_()
+    w2 = (torch.randn(256, 1024, device=dev) * 0.05).requires_grad_()
+    b2 = torch.randn(256, device=dev).requires_grad_()
+    res = feed_forward(x, w1, b1, w2, b2, passthrough=passthrough)
+    out, skip = res if passthrough else (res, None)
+    dout = torch.randn_like(out)
+    dskip = torch.randn_like(x) if passthrough else None
+    torch.autograd.backward([out] + ([skip] if passthrough else []), [dout] + ([dskip] if passthrough else []))
+    check_kernel_errors()
+    xr, w1r, b1r, w2r, b2r = (t.detach().float().requires_grad_() for t in (x, w1, b1, w2, b2))
+    inter = F.gelu(F.linear(xr, w1r.bfloat16().float(), b1r), approximate="tanh")
+    outr = F.linear(inter, w2r.bfloat16().float(), b2r)
+    torch.autograd.backward([outr] + ([xr * 1.0] if passthrough else []),
+                            [dout.float()] + ([dskip.float()] if passthrough else []))
+    assert torch.allclose(out.float(), outr, atol=6e-2, rtol=3e-2)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=6e-2, rtol=3e-2)
+    for mine, ref in ((w1, w1r), (b1, b1r), (w2, w2r), (b2, b2r)):
+        assert torch.allclose(mine.grad, ref.grad, atol=0.4, rtol=3e-2), (mine.grad - ref.grad).abs().max()
+
+
 def test_orthogonalize_matches_gram_schmidt():
     from hivemind_b200.ops.powersgd import orthogonalize_batch_
     from hivemind_b200.utils.math import orthogonalize_reference_
@@ -415,5 +484,6 @@ def test_powersgd_round_on_rank_deficient_gradient_matches_gram_schmidt_math():
     g = torch.empty(m, n, device=_dev())
     ps.reconstruct_(g, P, Q2)
     scale = M.abs().max().item()
-    assert (g_ref - M.double().cpu()).abs().max().item() < 1e-6 * scale + 1e-6  # the oracle recovers M
+    # the oracle recovers M up to what fp32 rounding of M adds outside its eight directions (about 6e-4 here)
+    assert (g_ref - M.double().cpu()).abs().max().item() < 2e-3 * scale
     assert (g.double().cpu() - g_ref).abs().max().item() < 5e-3 * scale, (g.double().cpu() - g_ref).abs().max().item()
