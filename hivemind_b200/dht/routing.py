@@ -7,12 +7,12 @@ cover the id space; a full bucket splits if it contains our own id or if its dep
 """
 from __future__ import annotations
 
+import bisect
 import hashlib
 import heapq
 import os
 import random
 from collections.abc import Iterable
-from itertools import chain
 from typing import Any, Dict, List, Optional, Sequence, Set, Tuple, Union
 
 from hivemind_b200.p2p import PeerID
@@ -65,13 +65,21 @@ class DHTID(int):
         return self.to_bytes()
 
 
+ID_BITS = DHTID.HASH_NBYTES * 8
+
+
 class KBucket:
-    """Nodes whose ids fall in [lower, upper); at most ``size`` live entries plus a replacement list."""
+    """Peers whose ids lie in ``[lower, upper)``, a power-of-two slice of the id space ``depth`` halvings deep.
+
+    Up to ``size`` peers are live members, kept from least to most recently seen; newcomers beyond that wait as
+    replacements (freshest last) until a member is removed. ``request_ping_node`` hands out, one at a time, the
+    stalest members that have not been probed since they were last heard from.
+    """
 
     def __init__(self, lower: int, upper: int, size: int, depth: int = 0):
-        assert upper - lower == 2 ** (DHTID.HASH_NBYTES * 8 - depth)
+        assert upper - lower == 1 << (ID_BITS - depth), "a bucket covers exactly 2^(bits - depth) ids"
         self.lower, self.upper, self.size, self.depth = lower, upper, size, depth
-        self.nodes_to_peer_id: Dict[DHTID, PeerID] = {}
+        self.nodes_to_peer_id: Dict[DHTID, PeerID] = {}      # insertion order = order of last contact
         self.replacement_nodes: Dict[DHTID, PeerID] = {}
         self.nodes_requested_for_ping: Set[DHTID] = set()
         self.last_updated = get_dht_time()
@@ -80,49 +88,47 @@ class KBucket:
         return self.lower <= node_id < self.upper
 
     def add_or_update_node(self, node_id: DHTID, peer_id: PeerID) -> bool:
-        """Returns False if the bucket is full (the node then waits in the replacement list)."""
-        if node_id in self.nodes_requested_for_ping:
-            self.nodes_requested_for_ping.remove(node_id)
+        """Record a contact with ``node_id``. False means the bucket is full and the node is only a replacement."""
         self.last_updated = get_dht_time()
-        if node_id in self.nodes_to_peer_id:
-            del self.nodes_to_peer_id[node_id]  # move to the most-recently-seen end
-            self.nodes_to_peer_id[node_id] = peer_id
-        elif len(self.nodes_to_peer_id) < self.size:
-            self.nodes_to_peer_id[node_id] = peer_id
-        else:
-            self.replacement_nodes.pop(node_id, None)
-            self.replacement_nodes[node_id] = peer_id
-            return False
-        return True
+        self.nodes_requested_for_ping.discard(node_id)  # it just answered (or called): no need to probe it
+        known = self.nodes_to_peer_id.pop(node_id, None) is not None
+        if known or len(self.nodes_to_peer_id) < self.size:
+            self.nodes_to_peer_id[node_id] = peer_id  # (re)inserted at the fresh end
+            return True
+        self.replacement_nodes.pop(node_id, None)
+        self.replacement_nodes[node_id] = peer_id
+        return False
 
     def request_ping_node(self) -> Optional[Tuple[DHTID, PeerID]]:
-        """The least-recently-seen node that has not been asked yet, if any."""
-        for uid, peer_id in self.nodes_to_peer_id.items():
-            if uid not in self.nodes_requested_for_ping:
-                self.nodes_requested_for_ping.add(uid)
-                return uid, peer_id
-        return None
+        """The stalest member not yet handed out for probing, if there is one."""
+        candidate = next((uid for uid in self.nodes_to_peer_id if uid not in self.nodes_requested_for_ping), None)
+        if candidate is None:
+            return None
+        self.nodes_requested_for_ping.add(candidate)
+        return candidate, self.nodes_to_peer_id[candidate]
 
     def __getitem__(self, node_id: DHTID) -> PeerID:
-        return self.nodes_to_peer_id[node_id] if node_id in self.nodes_to_peer_id else self.replacement_nodes[node_id]
+        member = self.nodes_to_peer_id.get(node_id)
+        return member if member is not None else self.replacement_nodes[node_id]
 
     def __delitem__(self, node_id: DHTID) -> None:
-        if not (node_id in self.nodes_to_peer_id or node_id in self.replacement_nodes):
+        was_member = self.nodes_to_peer_id.pop(node_id, None) is not None
+        was_spare = self.replacement_nodes.pop(node_id, None) is not None
+        if not (was_member or was_spare):
             raise KeyError(f"KBucket does not contain node id={node_id}")
-        self.replacement_nodes.pop(node_id, None)
-        if node_id in self.nodes_to_peer_id:
-            del self.nodes_to_peer_id[node_id]
-            if self.replacement_nodes:  # promote the freshest replacement
-                newnode_id, newnode = self.replacement_nodes.popitem()
-                self.nodes_to_peer_id[newnode_id] = newnode
+        if was_member and self.replacement_nodes:  # the freshest replacement takes the free seat
+            promoted, address = self.replacement_nodes.popitem()
+            self.nodes_to_peer_id[promoted] = address
 
     def split(self) -> Tuple["KBucket", "KBucket"]:
-        midpoint = (self.lower + self.upper) // 2
-        left = KBucket(self.lower, midpoint, self.size, self.depth + 1)
-        right = KBucket(midpoint, self.upper, self.size, self.depth + 1)
-        for node_id, peer_id in chain(self.nodes_to_peer_id.items(), self.replacement_nodes.items()):
-            (left if int(node_id) < midpoint else right).add_or_update_node(node_id, peer_id)
-        return left, right
+        """Two buckets of half the range; members and replacements are re-seated in their order of last contact."""
+        middle = self.lower + (self.upper - self.lower) // 2
+        halves = (KBucket(self.lower, middle, self.size, self.depth + 1),
+                  KBucket(middle, self.upper, self.size, self.depth + 1))
+        for group in (self.nodes_to_peer_id, self.replacement_nodes):
+            for node_id, peer_id in group.items():
+                halves[int(node_id) >= middle].add_or_update_node(node_id, peer_id)
+        return halves
 
     def __repr__(self) -> str:
         return (f"{type(self).__name__}({len(self.nodes_to_peer_id)} nodes, {len(self.replacement_nodes)} replacements, "
@@ -130,63 +136,65 @@ class KBucket:
 
 
 class RoutingTable:
+    """K-buckets in id order plus the two directories (node id <-> transport peer id) of everybody in them."""
+
     def __init__(self, node_id: DHTID, bucket_size: int, depth_modulo: int):
         self.node_id, self.bucket_size, self.depth_modulo = node_id, bucket_size, depth_modulo
         self.buckets = [KBucket(node_id.MIN, node_id.MAX, bucket_size)]
+        self._lower_bounds = [int(node_id.MIN)]  # of self.buckets, for bisection
         self.peer_id_to_uid: Dict[PeerID, DHTID] = {}
         self.uid_to_peer_id: Dict[DHTID, PeerID] = {}
 
     def get_bucket_index(self, node_id: DHTID) -> int:
-        lo, hi = 0, len(self.buckets)
-        while hi - lo > 1:
-            mid = (lo + hi) // 2
-            if node_id >= self.buckets[mid].lower:
-                lo = mid
-            else:
-                hi = mid
-        assert self.buckets[lo].has_in_range(node_id)
-        return lo
+        index = bisect.bisect_right(self._lower_bounds, int(node_id)) - 1
+        assert self.buckets[index].has_in_range(node_id)
+        return index
+
+    def _may_split(self, bucket: KBucket) -> bool:
+        # our own neighbourhood is always refined; elsewhere only depths that are not a multiple of depth_modulo
+        return bucket.has_in_range(self.node_id) or bucket.depth % self.depth_modulo != 0
 
     def add_or_update_node(self, node_id: DHTID, peer_id: PeerID) -> Optional[Tuple[DHTID, PeerID]]:
         """Insert or refresh a node. If its bucket is full and cannot split, returns a node that should be pinged."""
-        bucket_index = self.get_bucket_index(node_id)
-        bucket = self.buckets[bucket_index]
-        store_success = bucket.add_or_update_node(node_id, peer_id)
-        if node_id in bucket.nodes_to_peer_id or node_id in bucket.replacement_nodes:
-            self.uid_to_peer_id[node_id] = peer_id
+        while True:
+            index = self.get_bucket_index(node_id)
+            bucket = self.buckets[index]
+            seated = bucket.add_or_update_node(node_id, peer_id)
+            self.uid_to_peer_id[node_id] = peer_id  # members and replacements are both listed
             self.peer_id_to_uid[peer_id] = node_id
-        if not store_success:
-            if bucket.has_in_range(self.node_id) or bucket.depth % self.depth_modulo != 0:
-                self.split_bucket(bucket_index)
-                return self.add_or_update_node(node_id, peer_id)
-            return bucket.request_ping_node()
-        return None
+            if seated:
+                return None
+            if not self._may_split(bucket):
+                return bucket.request_ping_node()
+            self.split_bucket(index)
 
     def split_bucket(self, index: int) -> None:
-        first, second = self.buckets[index].split()
-        self.buckets[index] = first
-        self.buckets.insert(index + 1, second)
+        low, high = self.buckets[index].split()
+        self.buckets[index:index + 1] = [low, high]
+        self._lower_bounds[index:index + 1] = [low.lower, high.lower]
 
     def get(self, *, node_id: Optional[DHTID] = None, peer_id: Optional[PeerID] = None, default=None):
         assert (node_id is None) != (peer_id is None), "specify either node_id or peer_id, not both"
-        if node_id is not None:
-            return self.uid_to_peer_id.get(node_id, default)
-        return self.peer_id_to_uid.get(peer_id, default)
+        directory, key = (self.uid_to_peer_id, node_id) if node_id is not None else (self.peer_id_to_uid, peer_id)
+        return directory.get(key, default)
+
+    def _directory_for(self, item: Union[DHTID, PeerID]):
+        return self.uid_to_peer_id if isinstance(item, DHTID) else self.peer_id_to_uid
 
     def __getitem__(self, item: Union[DHTID, PeerID]) -> Union[PeerID, DHTID]:
-        return self.uid_to_peer_id[item] if isinstance(item, DHTID) else self.peer_id_to_uid[item]
+        return self._directory_for(item)[item]
 
     def __setitem__(self, node_id: DHTID, peer_id: PeerID):
         raise NotImplementedError("use add_or_update_node: it may return a node that must be pinged first")
 
     def __contains__(self, item: Union[DHTID, PeerID]) -> bool:
-        return (item in self.uid_to_peer_id) if isinstance(item, DHTID) else (item in self.peer_id_to_uid)
+        return item in self._directory_for(item)
 
     def __delitem__(self, node_id: DHTID) -> None:
         del self.buckets[self.get_bucket_index(node_id)][node_id]
-        node_peer_id = self.uid_to_peer_id.pop(node_id)
-        if self.peer_id_to_uid.get(node_peer_id) == node_id:
-            del self.peer_id_to_uid[node_peer_id]
+        address = self.uid_to_peer_id.pop(node_id)
+        if self.peer_id_to_uid.get(address) == node_id:
+            del self.peer_id_to_uid[address]
 
     def get_nearest_neighbors(self, query_id: DHTID, k: int, exclude: Optional[DHTID] = None) -> List[Tuple[DHTID, PeerID]]:
         """The k known nodes nearest to ``query_id`` by XOR distance, nearest first.

@@ -23,26 +23,38 @@ logger = get_logger(__name__)
 
 
 class GradScaler(TorchGradScaler):
+    """See the module docstring. State on top of torch's scaler:
+
+    * ``_inside_global_step`` - set by ``running_global_step()``; only then are gradients really unscaled and the
+      wrapped optimizer really stepped through the scaler;
+    * ``_stepped`` - a global step went through since the last ``update()``: the scale may grow;
+    * ``_handover`` - torch keys its per-optimizer records by ``id(optimizer)``; the collaborative optimizer is
+      unscaled under its own id, its inner torch optimizer is stepped under another, so the record is carried over;
+    * ``_partial`` - optimizers whose records describe a local (accumulating) step and must be forgotten at the next
+      ``update()`` that does not change the scale.
+    """
+
     def __init__(self, *args, **kwargs):
-        if args and isinstance(args[0], str) or "device" in kwargs:
-            super().__init__(*args, **kwargs)
-        else:
-            super().__init__("cuda" if torch.cuda.is_available() else "cpu", *args, **kwargs)
-        self._is_running_global_step = False
-        self._is_ready_to_update = False
-        self._inner_optimizer_states = {}
-        self._optimizer_states_to_reset = set()
+        names_device = bool(args and isinstance(args[0], str)) or "device" in kwargs
+        if not names_device:
+            args = ("cuda" if torch.cuda.is_available() else "cpu", *args)
+        super().__init__(*args, **kwargs)
+        self._inside_global_step = False
+        self._stepped = False
+        self._handover: Dict[int, dict] = {}
+        self._partial = set()
         self._lock = threading.RLock()
 
     @contextlib.contextmanager
     def running_global_step(self):
         """Inside this context ``unscale_`` and ``step`` act for real (the collaborative optimizer enters it)."""
         with self._lock:
-            previous, self._is_running_global_step = self._is_running_global_step, True
+            outer = self._inside_global_step
+            self._inside_global_step = True
             try:
                 yield
             finally:
-                self._is_running_global_step = previous
+                self._inside_global_step = outer
 
     @staticmethod
     def _is_collaborative(optimizer) -> bool:
@@ -50,56 +62,63 @@ class GradScaler(TorchGradScaler):
 
         return isinstance(optimizer, Optimizer)
 
+    @staticmethod
+    def _overflows(found_inf_per_device: Dict[torch.device, torch.Tensor]) -> float:
+        return sum(flag.item() for flag in found_inf_per_device.values())
+
     def unscale_(self, optimizer: TorchOptimizer) -> bool:
+        """True if the gradients were unscaled (global step); otherwise only overflow was looked for."""
+        assert self._is_collaborative(optimizer), "this scaler is meant for hivemind_b200.Optimizer"
         with self._lock:
-            assert self._is_collaborative(optimizer), "this scaler is meant for hivemind_b200.Optimizer"
-            if self._is_running_global_step:
-                super().unscale_(optimizer)
-                # the inner optimizer will look for its own record when ``step`` is called on it
-                self._inner_optimizer_states[id(optimizer.opt)] = deepcopy(self._per_optimizer_states[id(optimizer)])
-                return True
-            self._check_inf_per_device(optimizer)  # only record overflow; gradients stay scaled
-            self._optimizer_states_to_reset.add(id(optimizer))
-            return False
+            if not self._inside_global_step:
+                self._check_inf_per_device(optimizer)  # gradients keep their scale while they accumulate
+                self._partial.add(id(optimizer))
+                return False
+            super().unscale_(optimizer)
+            self._handover[id(optimizer.opt)] = deepcopy(self._per_optimizer_states[id(optimizer)])
+            return True
+
+    def _global_step(self, inner: TorchOptimizer, *args, **kwargs) -> None:
+        if self._stepped:
+            logger.warning("Please call grad_scaler.update() after each step")
+        record = self._handover.pop(id(inner), None)
+        if record is not None:
+            self._per_optimizer_states[id(inner)] = record
+        stage = self._per_optimizer_states[id(inner)]["stage"]
+        assert stage == OptState.UNSCALED, "the collaborative optimizer unscales before it steps its inner optimizer"
+        if self.are_grads_finite(inner, use_cached=True):
+            super().step(inner, *args, **kwargs)
+        else:
+            logger.warning("Skipping global step due to gradient over/underflow")
+        self._stepped = True
 
     def step(self, optimizer: TorchOptimizer, *args, **kwargs) -> bool:
-        if self._is_running_global_step and not self._is_collaborative(optimizer):
+        """True if this was the inner optimizer's step of a global step."""
+        if self._inside_global_step and not self._is_collaborative(optimizer):
             with self._lock:
-                if self._is_ready_to_update:
-                    logger.warning("Please call grad_scaler.update() after each step")
-                saved = self._inner_optimizer_states.pop(id(optimizer), None)
-                if saved is not None:
-                    self._per_optimizer_states[id(optimizer)] = saved
-                assert self._per_optimizer_states[id(optimizer)]["stage"] == OptState.UNSCALED, \
-                    "InternalError: Optimizer should have called .unscale internally before invoking grad_scaler.step"
-                if self.are_grads_finite(optimizer, use_cached=True):
-                    super().step(optimizer, *args, **kwargs)
-                else:
-                    logger.warning("Skipping global step due to gradient over/underflow")
-                self._is_ready_to_update = True
-                return True
-        super().step(optimizer)
-        self._optimizer_states_to_reset.add(id(optimizer))
+                self._global_step(optimizer, *args, **kwargs)
+            return True
+        super().step(optimizer)  # a local step of the collaborative optimizer: it accumulates and reports progress
+        self._partial.add(id(optimizer))
         return False
 
     def update(self, new_scale: Optional[float] = None) -> bool:
+        """Change the scale only after a global step or on overflow; True if torch's update ran."""
         with self._lock:
-            total_infs = 0
-            for optimizer_state in self._per_optimizer_states.values():
-                total_infs += sum(v.item() for v in optimizer_state["found_inf_per_device"].values())
-            if self._is_ready_to_update or total_infs != 0:
+            overflow = any(self._overflows(record["found_inf_per_device"]) for record in self._per_optimizer_states.values())
+            if self._stepped or overflow:
                 super().update(new_scale)
-                self._is_ready_to_update = False
+                self._stepped = False
                 return True
-            for opt_id in self._optimizer_states_to_reset:
-                self._per_optimizer_states[opt_id] = _refresh_per_optimizer_state()
-            self._optimizer_states_to_reset.clear()
+            while self._partial:
+                self._per_optimizer_states[self._partial.pop()] = _refresh_per_optimizer_state()
             return False
 
     def _unscale_grads_(self, optimizer: TorchOptimizer, inv_scale: torch.Tensor, found_inf: torch.Tensor,
                         allow_fp16: bool) -> Dict[torch.device, torch.Tensor]:
+        # master parameters may be fp16 / bf16 here
         return super()._unscale_grads_(optimizer, inv_scale, found_inf, allow_fp16=True)
 
     def are_grads_finite(self, optimizer: TorchOptimizer, use_cached: bool = False) -> bool:
-        found = self._found_inf_per_device(optimizer) if use_cached else self._check_inf_per_device(optimizer)
-        return not sum(v.item() for v in found.values())
+        flags = self._found_inf_per_device(optimizer) if use_cached else self._check_inf_per_device(optimizer)
+        return not self._overflows(flags)

@@ -9,9 +9,8 @@ from __future__ import annotations
 
 from concurrent.futures import ThreadPoolExecutor
 from contextlib import nullcontext
-from itertools import chain
 from threading import Event, Lock
-from typing import Iterator, Optional, Sequence
+from typing import Iterator, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -39,117 +38,126 @@ class TrainingAverager(DecentralizedAverager):
                  parameter_names: Optional[Sequence[str]] = None, initialize_optimizer: bool = True, **kwargs):
         if initialize_optimizer:
             initialize_optimizer_state_(opt)
-        if parameter_names is None:
-            parameter_names = tuple(i for group in opt.param_groups for i in range(len(group["params"])))
-        self.opt, self.extra_tensors, self.local_step = opt, tuple(extra_tensors), 0
-        self.opt_statistics = tuple(average_opt_statistics)
+        self.opt = opt
         self.average_parameters, self.average_gradients = average_parameters, average_gradients
-        self.parameter_names = parameter_names
+        self.opt_statistics = tuple(average_opt_statistics)
+        self.extra_tensors = tuple(extra_tensors)
+        self.parameter_names = tuple(parameter_names) if parameter_names is not None else tuple(range(len(self._params())))
+        assert len(self.parameter_names) == len(self._params()), "one name per optimized parameter"
+        self.local_step = 0
         self.step_executor = ThreadPoolExecutor(max_workers=1)
         self.lock_averager_step = Lock()
-        self.pending_updates_done = Event()
+        self.pending_updates_done = Event()  # clear while local tensors are being read or written by a step
         self.pending_updates_done.set()
+        sections = list(self._sections())
         with torch.no_grad():
-            averaged_tensors = [tensor.detach().float().clone() for tensor in self.local_tensors()]
-        super().__init__(averaged_tensors=averaged_tensors, tensor_infos=list(self.tensor_infos()), **kwargs)
+            shadows = [tensor.detach().float().clone() for _, _, tensor in sections]
+        infos = [CompressionInfo.from_tensor(tensor, key=key, role=role) for role, key, tensor in sections]
+        super().__init__(averaged_tensors=shadows, tensor_infos=infos, **kwargs)
 
+    # ------------------------------------------------------------------------------------------ what is averaged
+    def _params(self) -> List[torch.Tensor]:
+        return [p for group in self.opt.param_groups for p in group["params"]]
+
+    def _sections(self, replace_none: bool = True) -> Iterator[Tuple[TensorRole, object, torch.Tensor]]:
+        """(role, key, tensor) of everything that takes part in a round, in averaging order: parameters, gradients,
+        the chosen optimizer statistics, extras. A parameter without a gradient contributes zeros."""
+        named = list(zip(self.parameter_names, self._params()))
+        if self.average_parameters:
+            for name, p in named:
+                yield TensorRole.PARAMETER, name, p
+        if self.average_gradients:
+            for name, p in named:
+                if p.grad is not None:
+                    yield TensorRole.GRADIENT, name, p.grad
+                elif replace_none:
+                    yield TensorRole.GRADIENT, name, torch.zeros_like(p)
+        for statistic in self.opt_statistics:
+            for name, p in named:
+                yield TensorRole.OPTIMIZER, (name, statistic), self.opt.state[p][statistic]
+        for index, extra in enumerate(self.extra_tensors):
+            yield TensorRole.UNSPECIFIED, index, extra
+
+    def local_tensors(self, replace_none: bool = True) -> Iterator[torch.Tensor]:
+        """Local tensors in averaging order: parameters, gradients, optimizer statistics, extras."""
+        return (tensor for _, _, tensor in self._sections(replace_none))
+
+    def tensor_infos(self) -> Iterator[CompressionInfo]:
+        return (CompressionInfo.from_tensor(tensor, key=key, role=role) for role, key, tensor in self._sections())
+
+    # ------------------------------------------------------------------------------------------ one round
     def step(self, data_lock: Optional[Lock] = None, wait: bool = True, **kwargs):
         """Average with peers; ``data_lock`` is held only while local tensors are read or written."""
         if not wait:
             return self.step_executor.submit(self.step, data_lock, wait=True, **kwargs)
-        use_old_local_tensors = data_lock is not None
-        data_lock = data_lock if data_lock is not None else nullcontext()
-        local_tensors = list(self.local_tensors())
+        concurrent_training = data_lock is not None  # the model may change between the two copies
+        guard = data_lock if concurrent_training else nullcontext()
+        local = list(self.local_tensors())
         with self.lock_averager_step, torch.no_grad():
-            self.pending_updates_done.clear()
-            with data_lock, self.get_tensors() as averaged_tensors:
-                assert len(local_tensors) == len(averaged_tensors), "The number of optimized parameters should not change."
-                if use_old_local_tensors:
-                    old_local_tensors = tuple(x.detach().float().clone() for x in local_tensors)
-                _bulk_copy(list(averaged_tensors), local_tensors)
-            self.pending_updates_done.set()
+            snapshot = self._copy_in(local, guard, keep_snapshot=concurrent_training)
             gathered = super().step(**kwargs)
             if gathered is not None:
-                self.pending_updates_done.clear()
-                with data_lock, self.get_tensors() as averaged_tensors:
-                    if len(averaged_tensors) != len(local_tensors):
-                        raise RuntimeError("The number of optimized parameters should not change.")
-                    if use_old_local_tensors:
-                        # the model moved on while we averaged: add only what averaging changed
-                        same = all(l.device == a.device and l.dtype == torch.float32 for l, a in zip(local_tensors, averaged_tensors))
-                        if same:
-                            mt.delta_update_(local_tensors, list(averaged_tensors), list(old_local_tensors))
-                        else:
-                            for local, new, old in zip(local_tensors, averaged_tensors, old_local_tensors):
-                                local.add_((new - old).to(local.device, local.dtype))
-                    else:
-                        _bulk_copy(local_tensors, list(averaged_tensors))
-                self.pending_updates_done.set()
+                self._copy_out(local, guard, snapshot)
             self.local_step += 1
             return gathered
 
-    def local_tensors(self, replace_none: bool = True) -> Iterator[torch.Tensor]:
-        """Local tensors in averaging order: parameters, gradients, optimizer statistics, extras."""
-        if self.average_parameters:
-            for group in self.opt.param_groups:
-                yield from group["params"]
-        if self.average_gradients:
-            for group in self.opt.param_groups:
-                for param in group["params"]:
-                    if param.grad is not None:
-                        yield param.grad
-                    elif replace_none:
-                        yield torch.zeros_like(param)
-        for stats in self.opt_statistics:
-            for group in self.opt.param_groups:
-                for param in group["params"]:
-                    yield self.opt.state[param][stats]
-        yield from iter(self.extra_tensors)
+    def _copy_in(self, local: List[torch.Tensor], guard, keep_snapshot: bool) -> Optional[List[torch.Tensor]]:
+        self.pending_updates_done.clear()
+        try:
+            with guard, self.get_tensors() as shadows:
+                if len(shadows) != len(local):
+                    raise RuntimeError("the set of optimized tensors changed since the averager was created")
+                snapshot = [t.detach().float().clone() for t in local] if keep_snapshot else None
+                _bulk_copy(list(shadows), local)
+            return snapshot
+        finally:
+            self.pending_updates_done.set()
 
-    def tensor_infos(self):
-        params = tuple(param for group in self.opt.param_groups for param in group["params"])
-        assert len(params) == len(self.parameter_names)
-        if self.average_parameters:
-            for param, key in zip(params, self.parameter_names):
-                yield CompressionInfo.from_tensor(param, key=key, role=TensorRole.PARAMETER)
-        if self.average_gradients:
-            for param, key in zip(params, self.parameter_names):
-                if param.grad is not None:
-                    grad = param.grad if param.grad is not None else torch.zeros_like(param)
-                    yield CompressionInfo.from_tensor(grad, key=key, role=TensorRole.GRADIENT)
-        for stats in self.opt_statistics:
-            for param, key in zip(params, self.parameter_names):
-                yield CompressionInfo.from_tensor(self.opt.state[param][stats], key=(key, stats), role=TensorRole.OPTIMIZER)
-        for i, extra_tensor in enumerate(self.extra_tensors):
-            yield CompressionInfo.from_tensor(extra_tensor, key=i, role=TensorRole.UNSPECIFIED)
+    def _copy_out(self, local: List[torch.Tensor], guard, snapshot: Optional[List[torch.Tensor]]) -> None:
+        self.pending_updates_done.clear()
+        try:
+            with guard, self.get_tensors() as shadows:
+                shadows = list(shadows)
+                if len(shadows) != len(local):
+                    raise RuntimeError("the set of optimized tensors changed since the averager was created")
+                if snapshot is None:
+                    _bulk_copy(local, shadows)
+                elif all(l.device == a.device and l.dtype == torch.float32 for l, a in zip(local, shadows)):
+                    mt.delta_update_(local, shadows, snapshot)  # local += averaged - what went into the round
+                else:
+                    for mine, averaged, before in zip(local, shadows, snapshot):
+                        mine.add_((averaged - before).to(mine.device, mine.dtype))
+        finally:
+            self.pending_updates_done.set()
 
+    # ------------------------------------------------------------------------------------------ state transfer
     def get_current_state(self):
         """(metadata, tensors, infos): parameters, extras, then optimizer tensors (same layout as the state averager)."""
         with torch.no_grad():
-            optimized_parameters = tuple(param.detach().cpu() for group in self.opt.param_groups for param in group["params"])
-            parameter_infos = [CompressionInfo.from_tensor(param, key=key, role=TensorRole.PARAMETER)
-                               for param, key in zip(optimized_parameters, self.parameter_names)]
-            extra_tensors = tuple(tensor.detach().cpu() for tensor in self.extra_tensors)
-            extra_infos = [CompressionInfo.from_tensor(t, key=i, role=TensorRole.UNSPECIFIED) for i, t in enumerate(extra_tensors)]
+            tensors, infos = [], []
+            for name, p in zip(self.parameter_names, self._params()):
+                tensors.append(p.detach().cpu())
+                infos.append(CompressionInfo.from_tensor(tensors[-1], key=name, role=TensorRole.PARAMETER))
+            for index, extra in enumerate(self.extra_tensors):
+                tensors.append(extra.detach().cpu())
+                infos.append(CompressionInfo.from_tensor(tensors[-1], key=index, role=TensorRole.UNSPECIFIED))
             optimizer_metadata, optimizer_tensors = dump_optimizer_state(self.opt)
-            optimizer_infos = [CompressionInfo.from_tensor(t, key=i, role=TensorRole.OPTIMIZER) for i, t in enumerate(optimizer_tensors)]
+            for index, t in enumerate(optimizer_tensors):
+                tensors.append(t)
+                infos.append(CompressionInfo.from_tensor(t, key=index, role=TensorRole.OPTIMIZER))
         metadata = dict(step=self.local_step, group_bits=self.get_group_bits(), optimizer_metadata=optimizer_metadata)
-        return metadata, list(chain(optimized_parameters, extra_tensors, optimizer_tensors)), \
-            list(chain(parameter_infos, extra_infos, optimizer_infos))
+        return metadata, tensors, infos
 
     def load_state_from_peers(self, **kwargs):
-        parameters_and_extras = [param for group in self.opt.param_groups for param in group["params"]]
-        parameters_and_extras.extend(self.extra_tensors)
-        num_local = len(parameters_and_extras)
-        loaded_state = super().load_state_from_peers(**kwargs)
-        if loaded_state is None:
+        targets = self._params() + list(self.extra_tensors)
+        loaded = super().load_state_from_peers(**kwargs)
+        if loaded is None:
             return
-        metadata, flat_tensors = loaded_state
-        loaded_parameters_and_extras, loaded_opt_tensors = flat_tensors[:num_local], flat_tensors[num_local:]
+        metadata, flat = loaded
         with torch.no_grad():
-            for local_param, loaded_param in zip(parameters_and_extras, loaded_parameters_and_extras):
-                local_param[...] = loaded_param.to(local_param.device, local_param.dtype)
-            load_optimizer_state(self.opt, metadata["optimizer_metadata"], loaded_opt_tensors)
+            for mine, theirs in zip(targets, flat[:len(targets)]):
+                mine.copy_(theirs.to(mine.device, mine.dtype))
+            load_optimizer_state(self.opt, metadata["optimizer_metadata"], flat[len(targets):])
         self.local_step = max(self.local_step, metadata["step"])
 
 
