@@ -27,6 +27,9 @@ import tempfile
 import threading
 import time
 
+# stdout carries exactly one JSON line: whatever NCCL has to say (its version banner, warnings) goes to stderr
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
 BASELINE_SAMPLES_PER_SEC = 20.924  # the only Optimizer throughput in the reference tree: examples/albert/README.md:96
 
 

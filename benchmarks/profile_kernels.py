@@ -22,7 +22,10 @@ from hivemind_b200.ops.norm_act import layer_norm
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", required=True,
-                        choices=["gemm", "gemm_dw", "gemm_compare", "ln_fwd", "ln_bwd", "gelu_bwd", "attention_compare"])
+                        choices=["gemm", "gemm_dw", "gemm_compare", "ln_fwd", "ln_bwd", "gelu_bwd", "attention_compare",
+                                 "codec", "lamb", "powersgd", "ffn"])
+    parser.add_argument("--codec", default="uniform8", help="codec mode: float16, meanstd16, uniform8, quantile8 or blockwise8")
+    parser.add_argument("--mb", type=float, default=256.0, help="codec / lamb modes: megabytes of fp32 data")
     parser.add_argument("--batch", type=int, default=32)
     parser.add_argument("--seq", type=int, default=512)
     parser.add_argument("--heads", type=int, default=16)
@@ -108,7 +111,67 @@ def main():
                           "result": result, "note": "library = scaled_dot_product_attention including the transposes "
                                                     "and the stacked q/k/v gradient that surround it in a model"}))
         return
-    if args.kernel == "gemm":
+    if args.kernel == "codec":
+        # whole-tensor encoders of ops/codec.py (statistics / borders / encode kernels of ops/csrc/codec.cu)
+        from hivemind_b200.compression.quantization import dynamic_code_table
+        from hivemind_b200.ops import codec as codecs
+
+        x = torch.randn(int(args.mb * 2 ** 20 / 4), device=dev)
+        code = dynamic_code_table().to(dev) if args.codec == "blockwise8" else None
+        run = {"float16": lambda: codecs.encode_float16(x), "meanstd16": lambda: codecs.encode_scaled_float16(x),
+               "uniform8": lambda: codecs.encode_uniform8(x), "quantile8": lambda: codecs.encode_quantile8(x),
+               "blockwise8": lambda: codecs.encode_blockwise8(x, code)}[args.codec]
+        work = 4.0 * x.numel() * (1.5 if args.codec in ("float16", "meanstd16") else 1.25)  # read fp32, write the code
+        unit = "GB/s"
+    elif args.kernel == "lamb":
+        # one fused LAMB step over ALBERT-large-like parameters (fp32 master weights, bf16 model copy)
+        from hivemind_b200.optim.fused import FusedLAMB
+
+        n = int(args.mb * 2 ** 20 / 4)
+        params = [torch.randn(n // 8, device=dev, requires_grad=True) for _ in range(8)]
+        for p in params:
+            p.grad = torch.randn_like(p)
+        opt = FusedLAMB(params, lr=1e-3, weight_decay=0.01)
+        run = opt.step
+        work = 4.0 * n * 7  # read p, g, m, v; write p, m, v
+        unit = "GB/s"
+    elif args.kernel == "powersgd":
+        # one PowerSGD compression of a stack of 24 matrices of 1024 x 4096 at rank 32: P = M Q, orthogonalise, Q = M^T P
+        from hivemind_b200.ops import powersgd as ps
+
+        groups, rows, cols, r = 24, 1024, 4096, 32
+        m = torch.randn(groups, rows, cols, device=dev)
+        q = torch.randn(groups, cols, r, device=dev)
+        p_ = torch.empty(groups, rows, r, device=dev)
+
+        def run():
+            ps.compute_p_stacked_(p_, m, q)
+            ps.orthogonalize_batch_(list(p_.unbind(0)))
+            ps.compute_q_stacked_(q, m, p_)
+
+        work = 2 * 2.0 * groups * rows * cols * r
+        unit = "TFLOP/s"
+    elif args.kernel == "ffn":
+        # forward + backward of the feed-forward node (four GEMMs each way, GELU derivative and residual gradient in
+        # GEMM epilogues) on ALBERT-large's shapes
+        from hivemind_b200.ops.gemm import feed_forward
+
+        x = torch.randn(args.rows // 2, args.hidden, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w1 = (torch.randn(4 * args.hidden, args.hidden, device=dev) * 0.02).requires_grad_()
+        w2 = (torch.randn(args.hidden, 4 * args.hidden, device=dev) * 0.02).requires_grad_()
+        b1, b2 = torch.zeros(4 * args.hidden, device=dev, requires_grad=True), torch.zeros(args.hidden, device=dev, requires_grad=True)
+        for t in (w1, w2, b1, b2):
+            t.grad = torch.zeros_like(t)
+        w1_lp, w2_lp = w1.detach().bfloat16(), w2.detach().bfloat16()
+        dout = torch.randn(args.rows // 2, args.hidden, device=dev, dtype=torch.bfloat16)
+
+        def run():
+            out, skip = feed_forward(x, w1, b1, w2, b2, w1_lp=w1_lp, w2_lp=w2_lp, passthrough=True)
+            torch.autograd.backward([out, skip], [dout, dout])
+
+        work = 6 * 2.0 * (args.rows // 2) * args.hidden * 4 * args.hidden
+        unit = "TFLOP/s"
+    elif args.kernel == "gemm":
         a = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)
         b = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16)
         out = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)

@@ -85,8 +85,9 @@ struct HrRound {
   int* part_done;              // [n_parts] chunks of a sent part that are complete
   int* dpart_done;             // [HR_MAX_PEERS][max_local_parts] chunks of a delta that are complete
   int* queue;                  // [4]: [3] counts the CTAs that have finished
-  const float* code;           // [512] block-wise code and midpoints between consecutive entries
+  const float* code;           // block-wise code [256], midpoints between consecutive entries [256], search table [16384 B]
   unsigned int done_slot;
+  int uses_blockwise;          // some part uses the block-wise codec: CTAs load the search table
 };
 
 struct HrGate {
@@ -136,11 +137,17 @@ struct HrShared {
   float redf[2][2][HR_THREADS / 32];    //   and maxima
   float cb[2][256];                     // codebook of the record being decoded (two alternating copies)
   float table[256];                     // quantile borders for bucketize
-  float hsum[HR_THREADS / 64][256];     // per warp-pair bin sums and counts: a skewed distribution would otherwise
-  int hcnt[HR_THREADS / 64][256];       //   serialise the whole CTA on a handful of addresses. Zero between uses.
+  // Per warp-pair bin sums and counts (a skewed distribution would otherwise serialise the whole CTA on a handful of
+  // addresses), zero between uses. Sums are integers: fixed-point offsets from a reference value of the bin, because
+  // shared memory adds integers natively, whereas a float add there is a compare-and-swap loop. The two outermost
+  // bins (open-ended, rarely hit) keep float sums.
+  int hfix[HR_THREADS / 64][256];
+  int hcnt[HR_THREADS / 64][256];
+  float hedge[HR_THREADS / 64][2];
   float smp[HR_SAMPLE];
   float code[256];                      // block-wise code and the midpoints between its entries: loaded once per CTA
   float mid[256];
+  unsigned char lut[1 << 14];           // where the search for a value's code starts (see hr_code_index)
   float w[HR_MAX_PEERS];
   int inc[HR_MAX_PEERS];
   int par[HR_MAX_PEERS];
@@ -195,11 +202,25 @@ __device__ __forceinline__ void hr_block_max2(float& a, float& b, HrShared& sh, 
   b = hm_warp_max(lane < HR_THREADS / 32 ? buf[1][lane] : 0.f);
 }
 
-// Quantise with the bin index `bin(x)`, add every value to its bin's sum and count, then (after a barrier) write the
-// bins' means as the record's codebook and leave the histogram zeroed for its next user.
-template <typename BinFn>
+// Index of the block-wise code entry nearest to x in [-1, 1] = number of midpoints below x. The top 14 bits of the
+// value's order-preserving key (float bits with the sign handled) pick a starting count from a table; at most a
+// few midpoints lie inside one such slice of the number line, and they are stepped over one by one.
+__device__ __forceinline__ int hr_code_index(const HrShared& sh, float x) {
+  unsigned int u = __float_as_uint(x);
+  u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;
+  int b = sh.lut[u >> 18];
+  while (b < 255 && sh.mid[b] < x) ++b;
+  return b;
+}
+
+// Quantise with the bin index `bin(x)`, note every value in its bin, then (after a barrier) write the bins' means as
+// the record's codebook and leave the histogram zeroed for its next user. A value enters its bin's sum as the integer
+// (x - ref(bin)) * to_fixed, where the caller guarantees |.| <= 2^17 for the inner bins (8192 of them cannot overflow);
+// the outermost bins add x itself to a float.
+template <typename BinFn, typename RefFn>
 __device__ __forceinline__ void hr_quantise_with_bin_means(const float (&v)[HR_ROWS][4], int n, unsigned char* rec,
-                                                           unsigned char* payload, HrShared& sh, BinFn bin) {
+                                                           unsigned char* payload, HrShared& sh, float to_fixed,
+                                                           BinFn bin, RefFn ref) {
   const int hw = threadIdx.x >> 6;
 #pragma unroll
   for (int r = 0; r < HR_ROWS; ++r) {
@@ -207,27 +228,39 @@ __device__ __forceinline__ void hr_quantise_with_bin_means(const float (&v)[HR_R
     uint32_t packed = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const int b = bin(v[r][k]);
+      const float x = v[r][k];
+      const int b = bin(x);
       packed |= (uint32_t)b << (8 * k);
       if (i + k < n) {
-        atomicAdd(&sh.hsum[hw][b], v[r][k]);
         atomicAdd(&sh.hcnt[hw][b], 1);
+        if (b == 0 || b == 255) atomicAdd(&sh.hedge[hw][b & 1], x);
+        else atomicAdd(&sh.hfix[hw][b], __float2int_rn((x - ref(b)) * to_fixed));
       }
     }
     *reinterpret_cast<uint32_t*>(payload + i) = packed;
   }
   __syncthreads();
   if (threadIdx.x < 256) {
-    float total = 0.f;
+    const int b = threadIdx.x;
+    long long fixed = 0;
     int count = 0;
+    float edge = 0.f;
 #pragma unroll
     for (int w = 0; w < HR_THREADS / 64; ++w) {
-      total += sh.hsum[w][threadIdx.x];
-      count += sh.hcnt[w][threadIdx.x];
-      sh.hsum[w][threadIdx.x] = 0.f;
-      sh.hcnt[w][threadIdx.x] = 0;
+      fixed += sh.hfix[w][b];
+      count += sh.hcnt[w][b];
+      sh.hfix[w][b] = 0;
+      sh.hcnt[w][b] = 0;
+      if (b == 0 || b == 255) {
+        edge += sh.hedge[w][b & 1];
+        sh.hedge[w][b & 1] = 0.f;
+      }
     }
-    reinterpret_cast<float*>(rec)[threadIdx.x] = total / (float)(count > 0 ? count : 1);
+    const float members = (float)(count > 0 ? count : 1);
+    float mean;
+    if (b == 0 || b == 255) mean = edge / members;
+    else mean = count > 0 ? ref(b) + (to_fixed > 0.f ? (float)fixed / (to_fixed * members) : 0.f) : 0.f;
+    reinterpret_cast<float*>(rec)[b] = mean;
   }
 }
 
@@ -288,10 +321,14 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
     // HB_UNIFORM8: 256 levels of width 6 sigma / 256 around the mean; the codebook holds the mean of every level
     const float scale = 6.f * (float)sqrt(m2 / fmax((double)n - 1.0, 1.0)) / 256.f;
     const float inv = (scale > 0.f && isfinite(scale)) ? 1.f / scale : 1.f;
-    hr_quantise_with_bin_means(v, n, rec, payload, sh, [&](float x) {
-      const int b = (int)rintf((x - mean) * inv) + 128;
-      return b < 0 ? 0 : (b > 255 ? 255 : b);
-    });
+    // inner levels hold values within half a level of their centre: offsets of at most 2^15 units of scale / 2^16
+    hr_quantise_with_bin_means(
+        v, n, rec, payload, sh, 65536.f * inv,
+        [&](float x) {
+          const int b = __float2int_rn((x - mean) * inv) + 128;
+          return b < 0 ? 0 : (b > 255 ? 255 : b);
+        },
+        [&](int b) { return fmaf((float)(b - 128), scale > 0.f && isfinite(scale) ? scale : 1.f, mean); });
     return;
   }
   if (codec == HB_QUANTILE8) {
@@ -330,7 +367,13 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       sh.table[threadIdx.x] = b;
     }
     __syncthreads();
-    hr_quantise_with_bin_means(v, n, rec, payload, sh, [&](float x) { return hb_bucketize(sh.table, x); });
+    // inner bin b holds values in (table[b - 1], table[b]]: offsets from the lower border, in units of the whole
+    // range of borders / 2^17
+    const float range = sh.table[254] - sh.table[0];
+    const float to_fixed = (range > 0.f && isfinite(range)) ? 131072.f / range : 0.f;
+    hr_quantise_with_bin_means(
+        v, n, rec, payload, sh, to_fixed, [&](float x) { return hb_bucketize(sh.table, x); },
+        [&](int b) { return sh.table[b - 1]; });
     return;
   }
   // HB_BLOCKWISE8: rows [b * RPB, (b + 1) * RPB) of every thread belong to block b (4096 elements)
@@ -354,7 +397,7 @@ __device__ void hr_encode_chunk(const float (&v)[HR_ROWS][4], int n, int codec, 
       const float inv = 1.f / fmaxf(m[r / RPB], 1.17549435e-38f);
       uint32_t packed = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) packed |= (uint32_t)hb_bucketize(sh.mid, v[r][k] * inv) << (8 * k);
+      for (int k = 0; k < 4; ++k) packed |= (uint32_t)hr_code_index(sh, v[r][k] * inv) << (8 * k);
       *reinterpret_cast<uint32_t*>(payload + i) = packed;
     }
   }
@@ -772,7 +815,12 @@ __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_co
     sh.code[threadIdx.x] = g.code[threadIdx.x];
     sh.mid[threadIdx.x] = g.code[256 + threadIdx.x];
   }
-  for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hsum[0][0])[i] = 0.f; (&sh.hcnt[0][0])[i] = 0; }
+  for (int i = threadIdx.x; i < (HR_THREADS / 64) * 256; i += HR_THREADS) { (&sh.hfix[0][0])[i] = 0; (&sh.hcnt[0][0])[i] = 0; }
+  if (threadIdx.x < (HR_THREADS / 64) * 2) (&sh.hedge[0][0])[threadIdx.x] = 0.f;
+  if (g.uses_blockwise) {
+    const uint4* src = reinterpret_cast<const uint4*>(g.code + 512);
+    for (int i = threadIdx.x; i < (1 << 14) / 16; i += HR_THREADS) reinterpret_cast<uint4*>(sh.lut)[i] = src[i];
+  }
   // Items are dealt round-robin. The list is ordered send, reduce, apply, so every CTA finishes its send items
   // before it may wait for a groupmate, and nothing that a groupmate needs from this GPU queues up behind a wait.
   for (int idx = g.item_begin + (int)blockIdx.x; idx < g.item_end; idx += (int)gridDim.x) {

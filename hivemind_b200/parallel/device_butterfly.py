@@ -115,7 +115,7 @@ class _HrRound(ctypes.Structure):
                 ("include", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p),
                 ("t_start", ctypes.c_void_p), ("status", ctypes.c_void_p), ("status_out", ctypes.c_void_p),
                 ("part_done", ctypes.c_void_p), ("dpart_done", ctypes.c_void_p), ("queue", ctypes.c_void_p),
-                ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint)]
+                ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint), ("uses_blockwise", ctypes.c_int)]
 
 
 class _HrGate(ctypes.Structure):
@@ -133,7 +133,9 @@ _code_lock = threading.Lock()
 
 
 def _code_table_on(device: torch.device) -> torch.Tensor:
-    """[512] fp32 on the device: the block-wise code (sorted) and the midpoints between consecutive entries."""
+    """On the device: the block-wise code (256 fp32, sorted), the midpoints between consecutive entries (256 fp32, the
+    last one +inf) and a 16 KB table that starts the search for a value's code: entry k is the number of midpoints
+    below the smallest float whose order-preserving key (sign-flipped bits) has k as its top 14 bits."""
     with _code_lock:
         table = _code_tables.get(device.index)
         if table is None:
@@ -144,7 +146,12 @@ def _code_table_on(device: torch.device) -> torch.Tensor:
             assert lib.hm_br_chunk() == CHUNK
             code = dynamic_code_table().to(torch.float32)
             mid = torch.cat([(code[:-1] + code[1:]) * 0.5, torch.tensor([float("inf")])])
-            table = torch.cat([code, mid]).to(device)
+            keys = (torch.arange(1 << 14, dtype=torch.int64) << 18).numpy().astype(np.uint32)
+            bits = np.where(keys >> 31 != 0, keys ^ np.uint32(0x80000000), ~keys)  # undo the order-preserving map
+            lowest = torch.from_numpy(bits.view(np.float32).copy())
+            lowest = torch.nan_to_num(lowest, nan=float("inf"), posinf=float("inf"), neginf=-float("inf"))
+            start = torch.bucketize(lowest, mid[:255].contiguous()).to(torch.uint8)  # midpoints strictly below the value
+            table = torch.cat([code, mid, torch.from_numpy(start.numpy().view(np.float32).copy())]).to(device)
             _code_tables[device.index] = table
         return table
 
@@ -551,6 +558,7 @@ class DeviceEndpoint:
                 setattr(g, name, plan.scratch[name].data_ptr())
             g.status_out = self._status_out.data_ptr()
             g.code = self._code.data_ptr()
+            g.uses_blockwise = int(any(c == 5 for c in self.codecs))
             if len(plan.rounds) > 8:
                 plan.rounds.pop(next(iter(plan.rounds)))
             plan.rounds[key] = template = g

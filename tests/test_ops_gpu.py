@@ -323,6 +323,29 @@ def test_linear_autograd():
     assert torch.allclose(w.grad, ref, atol=0.5, rtol=3e-2)
 
 
+@pytest.mark.parametrize("m,n,k,a_mn,b_mn", [(512, 384, 1024, False, False), (1000, 264, 4096, False, True),
+                                             (256, 1024, 16384, True, True)])
+def test_tc_gemm_bf16_inputs_fp32_output_is_exact_up_to_fp32_accumulation(m, n, k, a_mn, b_mn):
+    """bf16 products are exact in fp32, so against fp64 the only error is the fp32 accumulation: a bound relative to
+    sum |a||b| (not to the size of the output) that a dropped k-block, a wrong swizzle or a stale accumulator breaks."""
+    from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
+
+    torch.manual_seed(m + k)
+    a = torch.randn((k, m) if a_mn else (m, k), device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn((k, n) if b_mn else (n, k), device=_dev(), dtype=torch.bfloat16)
+    d = tc_gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    check_kernel_errors()
+    a64 = (a.t() if a_mn else a).double()
+    b64 = (b if b_mn else b.t()).double()
+    ref, mass = a64 @ b64, a64.abs() @ b64.abs()
+    assert d.dtype == torch.float32
+    assert ((d.double() - ref).abs() <= 1e-5 * mass + 1e-30).all(), ((d.double() - ref).abs() / mass).max().item()
+    # split-K with fp32 reduce-add keeps the same bound
+    acc = torch.zeros(m, n, device=_dev(), dtype=torch.float32)
+    tc_gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, reduce_add=True, splits=4)
+    assert ((acc.double() - ref).abs() <= 1e-5 * mass + 1e-30).all()
+
+
 @pytest.mark.parametrize("m,n,k", [(300, 256, 512), (4096, 1024, 3072), (129, 72, 64)])
 def test_tc_gemm_addend_epilogue(m, n, k):
     from hivemind_b200.ops.gemm import check_kernel_errors, tc_gemm
