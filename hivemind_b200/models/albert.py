@@ -13,6 +13,7 @@ fp32 accumulation; bf16 copies of the weights are refreshed lazily when a parame
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
@@ -23,6 +24,9 @@ import torch.nn.functional as F
 from hivemind_b200.ops.attention import attention
 from hivemind_b200.ops.gemm import feed_forward, linear
 from hivemind_b200.ops.norm_act import layer_norm
+
+# HIVEMIND_B200_FUSE_EPILOGUES=0 runs the encoder with one autograd node per layer (no epilogue fusion across layers)
+_FUSE_EPILOGUES = os.environ.get("HIVEMIND_B200_FUSE_EPILOGUES", "1") != "0"
 
 
 @dataclass
@@ -90,8 +94,14 @@ class AlbertLayer(nn.Module):
             nn.init.normal_(w, std=cfg.initializer_range)
 
     def forward(self, x: torch.Tensor, lp: _LowPrecisionCache) -> torch.Tensor:
-        b, s, h = x.shape
         nh = self.num_heads
+        if not _FUSE_EPILOGUES:  # every layer its own autograd node (kept for ablation runs)
+            qkv = linear(x, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight))
+            attn = linear(attention(qkv, nh), self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight))
+            x = layer_norm(attn, self.attn_ln_weight, self.attn_ln_bias, self.eps, residual=x)
+            inter = linear(x, self.ffn_weight, self.ffn_bias, activation="gelu", weight_lp=lp.get(self.ffn_weight))
+            out = linear(inter, self.ffn_out_weight, self.ffn_out_bias, weight_lp=lp.get(self.ffn_out_weight))
+            return layer_norm(out, self.ffn_ln_weight, self.ffn_ln_bias, self.eps, residual=x)
         # passthrough: the residual branch's gradient joins the projection's input gradient in that GEMM's epilogue
         qkv, x = linear(x, self.qkv_weight, self.qkv_bias, weight_lp=lp.get(self.qkv_weight), passthrough=True)
         ctx = attention(qkv, nh)  # reads the packed projections, writes [b, s, h]: no transposes around it

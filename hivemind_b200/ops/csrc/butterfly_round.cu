@@ -529,8 +529,18 @@ __device__ __forceinline__ unsigned long long hr_phase_start(unsigned long long*
 __device__ unsigned long long hr_decide(const unsigned long long* flag0, const unsigned long long* flag1, bool wide,
                                         unsigned int want, unsigned long long* decision, const int* ban_flag,
                                         unsigned long long* t_start, unsigned long long timeout_ns) {
+  // both flag sets are polled with relaxed loads (independent of each other: one round trip instead of two); the
+  // fence behind a hit turns the load that saw the flag into an acquire
   auto load = [&](const unsigned long long* f) -> unsigned long long {
-    return wide ? hr_ld_acquire_sys_u64(f) : (unsigned long long)hm_ld_acquire_sys(reinterpret_cast<const unsigned int*>(f));
+    unsigned long long v;
+    if (wide) {
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+    } else {
+      unsigned int w;
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(w) : "l"(f) : "memory");
+      v = w;
+    }
+    return v;
   };
   unsigned long long d = hr_ld_acquire_gpu_u64(decision);
   unsigned long long deadline = 0;
@@ -547,8 +557,12 @@ __device__ unsigned long long hr_decide(const unsigned long long* flag0, const u
           (ban_flag && *reinterpret_cast<const volatile int*>(ban_flag)) || hm_globaltimer_ns() > deadline)
         verdict = 2ull;
     }
-    if (verdict == 0) __nanosleep(200);
-    else hr_cas_release_gpu_u64(decision, 0ull, verdict);
+    if (verdict == 0) {
+      __nanosleep(200);
+    } else {
+      if (verdict != 2ull) __threadfence_system();
+      hr_cas_release_gpu_u64(decision, 0ull, verdict);
+    }
     d = hr_ld_acquire_gpu_u64(decision);
   }
   return d;

@@ -717,7 +717,7 @@ HM_API int hm_layernorm_bwd_fused(const void* dy, const void* zin, const void* g
   if ((256 >> gp_log2) > R) return -1;
   const size_t smem = (size_t)4 * R * H * 2 + (size_t)H * 4 + (size_t)R * 16;
   const int tiles = (rows + R - 1) / R;
-  const int per_sm = (int)((size_t)200 * 1024 / smem);
+  const int per_sm = (int)((size_t)224 * 1024 / (smem + 1024));   // 227 KB per SM, 1 KB per CTA reserved by the driver
   int blocks = sms * (per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm));
   if (blocks > tiles) blocks = tiles;
   cudaError_t e;

@@ -70,7 +70,7 @@ struct SmemLayout {
 };
 
 // ---------------------------------------------------------------------------------------------
-template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN>
+template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN, bool ADD = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_aux,
@@ -247,8 +247,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
       const int n_valid = min(BLOCK_N, p.N - n_tile * BLOCK_N);
+      // Second epilogue input (p.add): this thread's 128 bytes of the NEXT 64-column group are requested while the
+      // current group is converted and stored, so that only the first group of a tile waits for global memory.
+      const long long add_row = (long long)m_tile * BLOCK_M + row;
+      auto load_group = [&](int c_base, uint4 (&dst)[8]) {
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const int gcol = n_tile * BLOCK_N + c_base + 8 * ch;
+          dst[ch] = make_uint4(0u, 0u, 0u, 0u);
+          if (add_row < p.M && c_base + 8 * ch < n_valid && gcol < p.N)
+            dst[ch] = *reinterpret_cast<const uint4*>(p.add + add_row * p.ld_add + gcol);
+        }
+      };
+      uint4 add_cur[8], add_next[8];
+      if (ADD) load_group(0, add_cur);
       for (int c0 = 0; c0 < BLOCK_N; c0 += COLS_PER_BOX * boxes_per_store) {
         if (c0 >= n_valid) break;  // columns beyond N: nothing to store (uniform across the CTA)
+        if (ADD && c0 + 64 < n_valid) load_group(c0 + 64, add_next);
         // the staging buffer we are about to fill must have been read by its previous TMA store
         if (epi_tid == 0) {
           if (p.has_aux) tma_wait_read<0>(); else tma_wait_read<1>();
@@ -261,16 +276,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint32_t r[32];
           tc_ld32(t_addr + (uint32_t)(c0 + half * COLS_PER_BOX), r);
           const int gcol0 = n_tile * BLOCK_N + c0 + half * COLS_PER_BOX;
-          // the addend's 64 bytes of this thread's row travel while the accumulator is read
-          uint4 addend[4] = {};
-          if (p.add != nullptr) {
-            const long long grow = (long long)m_tile * BLOCK_M + row;
-            if (grow < p.M) {
-#pragma unroll
-              for (int ch = 0; ch < 4; ++ch)
-                if (gcol0 + 8 * ch < p.N) addend[ch] = *reinterpret_cast<const uint4*>(p.add + grow * p.ld_add + gcol0 + 8 * ch);
-            }
-          }
           tc_wait_ld();
           float v[32];
 #pragma unroll
@@ -278,10 +283,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             v[j] = __uint_as_float(r[j]) * p.alpha;
             if (p.epi != EPI_NONE && bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(bias + gcol0 + j);
           }
-          if (p.add != nullptr) {
+          if (ADD) {
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&addend[ch]);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&add_cur[ch]);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 if (p.add_mode == 0) {
@@ -293,6 +298,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
               }
             }
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) add_cur[ch] = add_cur[4 + ch];   // the second half's columns move up
           }
           // 16-byte chunks of this thread's row, XOR-swizzled like the tensor map (chunk ^= row & 7)
           if (p.out_f32) {
@@ -334,6 +341,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           else tma_store_2d(&map_d, smem_u32(stage_main), gc, gr);
           if (p.has_aux) tma_store_2d(&map_aux, smem_u32(stage_aux), gc, gr);
           tma_commit();
+        }
+        if (ADD) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) add_cur[ch] = add_next[ch];
         }
         flip ^= 1;
         (void)out_elem;
@@ -747,7 +758,7 @@ struct GemmCall {
   int add_mode = 0;
 };
 
-template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN>
+template <int BLOCK_N, int STAGES, bool TF32, bool A_MN, bool B_MN, bool ADD = false>
 int launch(const GemmCall& c, cudaStream_t stream) {
   using L = SmemLayout<BLOCK_N, STAGES>;
   constexpr int ELEM = TF32 ? 4 : 2;
@@ -794,7 +805,7 @@ int launch(const GemmCall& c, cudaStream_t stream) {
   const int tiles = p.num_m_tiles * p.num_n_tiles * (c.group_mode == 2 ? c.num_groups : p.num_splits);
   if (tiles <= 0 || p.total_kblocks <= 0) return 0;
   const int grid = tiles < c.sms ? tiles : c.sms;
-  auto kern = tc_gemm_kernel<BLOCK_N, STAGES, TF32, A_MN, B_MN>;
+  auto kern = tc_gemm_kernel<BLOCK_N, STAGES, TF32, A_MN, B_MN, ADD>;
   const int smem = L::TOTAL + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
@@ -930,10 +941,11 @@ HM_API int hm_tc_gemm_add(const void* a, const void* b, void* d, const void* add
   c.add = add;
   c.ldadd = ldadd;
   c.add_mode = add_mode;
+  if (a_mn) return -18;   // the variants with a second epilogue input exist for row-major A (activations or their gradients)
   switch (block_n) {
-    case 256: return dispatch_major<256, 4, false>(c, stream);
-    case 128: return dispatch_major<128, 6, false>(c, stream);
-    case 64: return dispatch_major<64, 8, false>(c, stream);
+    case 256: return b_mn ? launch<256, 4, false, false, true, true>(c, stream) : launch<256, 4, false, false, false, true>(c, stream);
+    case 128: return b_mn ? launch<128, 6, false, false, true, true>(c, stream) : launch<128, 6, false, false, false, true>(c, stream);
+    case 64: return b_mn ? launch<64, 8, false, false, true, true>(c, stream) : launch<64, 8, false, false, false, true>(c, stream);
     default: return -16;
   }
 }

@@ -299,9 +299,9 @@ class _LinearFn(torch.autograd.Function):
 
 
 class _FeedForwardFn(torch.autograd.Function):
-    """``gelu(x W1^T + b1) W2^T + b2`` as ONE autograd node, so that the backward pass can keep its intermediate
-    results inside GEMM epilogues: the derivative of the GELU is applied where the gradient of the hidden activations
-    is produced, and the gradient of a passed-through input is added where the input gradient is produced."""
+    """``gelu(x W1^T + b1) W2^T + b2`` as ONE autograd node: the backward pass applies the GELU derivative in place on
+    the hidden gradient (one pass that also yields ``b1``'s gradient), adds the gradient of a passed-through input in
+    the epilogue of the input-gradient GEMM, and leaves ``b2``'s gradient to the LayerNorm behind the block."""
 
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, w1_lp, w2_lp, skip_out_bias_grad, passthrough):
@@ -333,13 +333,21 @@ class _FeedForwardFn(torch.autograd.Function):
             gb2, in_place = _bias_grad_buffer(b2, w2b.shape[0], dev)
             colsum_(gb2, dout2)
             grad_b2 = None if in_place else gb2.to(b2.dtype)
-        # gradient of the pre-activations: (dout W2) * gelu'(pre), the product taken in the GEMM's epilogue
-        dpre = tc_gemm(dout2, w2b, b_mn=True, out_dtype=torch.bfloat16, add=pre, add_is_gelu_input=True, pair=False)
+        # gradient of the pre-activations: (dout W2) * gelu'(pre). The derivative runs as its own pass over the GEMM's
+        # output (in place, with the column sums for b1 taken along the way): applied in the GEMM's epilogue it made
+        # that epilogue longer than the tile's MMAs (0.21 ms instead of 0.11 + 0.04 ms on 16384 x 4096 x 1024)
+        dpre = tc_gemm(dout2, w2b, b_mn=True, out_dtype=torch.bfloat16)
         grad_w2 = _weight_grad(w2, dout2, inter) if need[3] else None
-        grad_b1 = None
+        grad_b1, gb1, in_place = None, None, False
         if need[2]:
             gb1, in_place = _bias_grad_buffer(b1, w1b.shape[0], dev)
-            colsum_(gb1, dpre)
+        lib = _lib.load_library()
+        with torch.cuda.device(dev):
+            code = lib.hm_bias_gelu_bwd(_lib.ptr(dpre), _lib.ptr(pre), _lib.ptr(None), _lib.ptr(dpre), _lib.ptr(gb1),
+                                        ctypes.c_longlong(pre.shape[0]), w1b.shape[0], _lib.HM_BF16,
+                                        _lib.sm_count(dev), _lib.stream_ptr(dev))
+        _lib.check(code, "hm_bias_gelu_bwd")
+        if need[2]:
             grad_b1 = None if in_place else gb1.to(b1.dtype)
         grad_x = None
         if need[0]:
