@@ -195,3 +195,23 @@ def test_device_path_decision_on_described_arenas():
     same_proc = dict(a, dev=1, handle=None)
     assert peers_can_share_memory(dict(a, handle=None), [dict(a, handle=None), same_proc])
     assert not peers_can_share_memory(a, [a, dict(b, supported=False)])
+
+
+def test_device_parts_come_in_whole_waves_of_the_grid():
+    """Part sizing of the device butterfly: a reducer's span is cut into at most GRID_CTAS x waves parts of at most
+    MAX_PART_CHUNKS chunks, every member derives the same size from (total elements, group size) alone, and small
+    tensors fall apart into single chunks (maximum parallelism)."""
+    from hivemind_b200.parallel.device_butterfly import CHUNK, GRID_CTAS, MAX_PART_CHUNKS, device_part_chunks
+
+    for total in (1, 255, CHUNK, 3 * CHUNK + 5, 2 ** 20, 2 ** 26, 2 ** 28 + 12345, 2 ** 30):
+        for peers in (1, 2, 3, 4, 8, 16):
+            chunks = device_part_chunks(total, peers)
+            span = -(-(-(-total // CHUNK)) // peers)
+            assert 1 <= chunks <= MAX_PART_CHUNKS
+            parts = -(-span // chunks)
+            waves = -(-parts // GRID_CTAS)
+            assert parts <= GRID_CTAS * waves
+            if span <= GRID_CTAS:
+                assert chunks == 1
+            else:  # the last wave is at least two thirds full: no CTA idles for most of a stage
+                assert parts > GRID_CTAS * (waves - 1) + GRID_CTAS * 2 // 3 or chunks == MAX_PART_CHUNKS
