@@ -54,6 +54,9 @@ def compute_schema_hash(tensors: Sequence[torch.Tensor]) -> bytes:
     return DHTID.generate(source=schema_dicts).to_bytes()
 
 
+_REHOMING_ANNOUNCED = False
+
+
 class DecentralizedAverager(ServicerBase):
     """
     :param averaged_tensors: tensors to average; the averager keeps references (CUDA tensors may be re-homed into a
@@ -159,6 +162,11 @@ class DecentralizedAverager(ServicerBase):
             infos = tensor_infos or tuple(CompressionInfo.from_tensor(t, key=i) for i, t in enumerate(self._averaged_tensors))
             self._device_endpoint = DeviceEndpoint(self._averaged_tensors, compression, infos, part_size_bytes)
             self._averaged_tensors = tuple(self._device_endpoint.tensor_views)
+            global _REHOMING_ANNOUNCED
+            if not _REHOMING_ANNOUNCED:  # once per process: the tensors passed in are no longer the averaged ones
+                _REHOMING_ANNOUNCED = True
+                logger.info("CUDA tensors given to an averager were copied into a peer-mappable device arena; "
+                            "get_tensors() returns the live (arena) tensors, use_device_path=False keeps them in place")
 
         self._ready = MPFuture()
         self._thread: Optional[LoopThread] = None

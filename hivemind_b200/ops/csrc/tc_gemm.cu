@@ -63,8 +63,11 @@ struct SmemLayout {
   static constexpr int B_BYTES = BLOCK_N * ROW_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int OUT_BYTES = BLOCK_M * ROW_BYTES;  // one staged box: 128 rows x 128 B
+  // Staging boxes for the TMA stores: two alternate; the three-stage form of the 256-wide tile (used when a second
+  // output, the pre-activation values, is written) has four, so that both outputs alternate as well.
+  static constexpr int NUM_OUT = (BLOCK_N == 256 && STAGES == 3) ? 4 : 2;
   static constexpr int OUT_OFF = STAGES * STAGE_BYTES;
-  static constexpr int BAR_OFF = OUT_OFF + 2 * OUT_BYTES;
+  static constexpr int BAR_OFF = OUT_OFF + NUM_OUT * OUT_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
 };
@@ -224,7 +227,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quad = warp & 3;               // TMEM lane quarter this warp may read
     const int row = quad * 32 + lane;        // row inside the tile
     const int epi_tid = threadIdx.x - 64;
-    uint8_t* out_buf[2] = {smem + L::OUT_OFF, smem + L::OUT_OFF + L::OUT_BYTES};
+    uint8_t* out_buf[4] = {smem + L::OUT_OFF, smem + L::OUT_OFF + L::OUT_BYTES,
+                           smem + L::OUT_OFF + (L::NUM_OUT == 4 ? 2 : 0) * L::OUT_BYTES,
+                           smem + L::OUT_OFF + (L::NUM_OUT == 4 ? 3 : 1) * L::OUT_BYTES};
+    constexpr bool AUX_ALTERNATES = L::NUM_OUT == 4;
     constexpr int COLS_PER_BOX = 32;          // accumulator columns handled per tcgen05.ld
     const int out_elem = p.out_f32 ? 4 : 2;
     const int boxes_per_store = p.out_f32 ? 1 : 2;  // 128 B rows: 32 fp32 or 64 bf16
@@ -266,11 +272,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (ADD && c0 + 64 < n_valid) load_group(c0 + 64, add_next);
         // the staging buffer we are about to fill must have been read by its previous TMA store
         if (epi_tid == 0) {
-          if (p.has_aux) tma_wait_read<0>(); else tma_wait_read<1>();
+          if (p.has_aux && !AUX_ALTERNATES) tma_wait_read<0>(); else tma_wait_read<1>();
         }
         epi_bar_sync();
-        uint8_t* stage_main = p.has_aux ? out_buf[0] : out_buf[flip];
-        uint8_t* stage_aux = out_buf[1];
+        uint8_t* stage_main = (p.has_aux && !AUX_ALTERNATES) ? out_buf[0] : out_buf[flip];
+        uint8_t* stage_aux = AUX_ALTERNATES ? out_buf[2 + flip] : out_buf[1];
 #pragma unroll 1
         for (int half = 0; half < boxes_per_store; ++half) {
           uint32_t r[32];
@@ -279,9 +285,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_wait_ld();
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = __uint_as_float(r[j]) * p.alpha;
-            if (p.epi != EPI_NONE && bias != nullptr && gcol0 + j < p.N) v[j] += __ldg(bias + gcol0 + j);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          if (p.epi != EPI_NONE && bias != nullptr) {
+            if (gcol0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(bias) + 4u * gcol0) & 15u) == 0) {   // whole box, aligned: eight 16-byte loads
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + gcol0) + q);
+                v[4 * q] += b4.x; v[4 * q + 1] += b4.y; v[4 * q + 2] += b4.z; v[4 * q + 3] += b4.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (gcol0 + j < p.N) v[j] += __ldg(bias + gcol0 + j);
+            }
           }
           if (ADD) {
 #pragma unroll
@@ -919,7 +935,8 @@ HM_API int hm_tc_gemm(const void* a, const void* b, void* d, void* aux, const vo
     }
   }
   switch (block_n) {
-    case 256: return dispatch_major<256, 4, false>(c, stream);
+    case 256: return (aux && !a_mn && !b_mn) ? launch<256, 3, false, false, false>(c, stream)
+                                             : dispatch_major<256, 4, false>(c, stream);
     case 128: return dispatch_major<128, 6, false>(c, stream);
     case 64: return dispatch_major<64, 8, false>(c, stream);
     default: return -16;
