@@ -184,8 +184,9 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
                 infos = [None] * world
                 dist.all_gather_object(infos, endpoint.describe())
                 n = world
+                my_weight = 0.5 + 1.5 * ((rank * 0.37 + 0.11) % 1.0)  # per-peer weights spread over [0.5, 2)
                 kwargs = dict(my_index=rank, device_infos=infos, modes=[AveragingMode.NODE] * n,
-                              peer_fractions=[1.0 / n] * n, weight=1.0, alpha=1.0, sender_timeout=10.0,
+                              peer_fractions=[1.0 / n] * n, weight=my_weight, alpha=1.0, sender_timeout=10.0,
                               reducer_timeout=20.0)
                 ms, stages = _time_rounds(endpoint, dict(tag=f"{size_mb}-{codec_name}", kwargs=kwargs,
                                                          barrier=dist.barrier, verbose=VERBOSE_ROUNDS), rounds, warmup)

@@ -197,11 +197,18 @@ async def amap_in_executor(func: Callable[..., T], *iterables: AsyncIterable, ma
             async for args in azip(*iterables):
                 await queue.put(loop.run_in_executor(executor, func, *args))
             await queue.put(None)
+        except asyncio.CancelledError:
+            raise  # the consumer is gone (it cancels the producer on its way out): nobody is left to tell
         except BaseException as e:
-            fut = loop.create_future()
-            fut.set_exception(e)
-            await queue.put(fut)
-            raise
+            # an error of the source belongs to the consumer: it travels through the queue as a failed future and is
+            # raised where the consumer awaits it. The producer itself ends quietly.
+            failed = loop.create_future()
+            failed.set_exception(e)
+            try:
+                await queue.put(failed)
+            except BaseException:
+                failed.exception()  # undeliverable: mark it as seen, so that the loop does not report it at collection
+                raise
 
     producer = asyncio.create_task(_produce())
     try:

@@ -93,7 +93,7 @@ def test_fault_tolerance(fault0: Fault, fault1: Fault):
     for i in range(5):
         averagers.append(FaultyAverager(
             _make_tensors(), DHT(initial_peers=dht.get_visible_maddrs(), start=True), prefix="test",
-            request_timeout=0.5, min_matchmaking_time=1.5, next_chunk_timeout=0.5, allreduce_timeout=5,
+            request_timeout=0.5, min_matchmaking_time=1.5, next_chunk_timeout=1.0, allreduce_timeout=6,
             part_size_bytes=2 ** 16, client_mode=(i == 1), start=True,
             fault=fault0 if i == 0 else fault1 if i == 1 else Fault.NONE))
     try:
@@ -110,7 +110,7 @@ def test_fault_tolerance(fault0: Fault, fault1: Fault):
             with averager.get_tensors() as tensors:
                 before.append(torch.cat([t.flatten() for t in tensors]))
 
-        futures = [averager.step(timeout=8, wait=False, allow_retries=False) for averager in averagers]
+        futures = [averager.step(timeout=10, wait=False, allow_retries=False) for averager in averagers]
         for averager, future in zip(averagers, futures):
             if averager.fault == Fault.CANCEL:
                 future.cancel()
