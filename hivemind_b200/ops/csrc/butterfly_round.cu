@@ -569,10 +569,12 @@ __device__ unsigned long long hr_decide(const unsigned long long* flag0, const u
 }
 
 // Chunks [.., .. + add) of a part are complete; true for the thread whose increment completes the part. The caller
-// has passed a CTA barrier after the chunks' writes; the fence (cumulative) makes them visible system-wide before the
-// count moves, and the thread that completes the part fences again before it publishes the part's flag.
+// has passed a CTA barrier after the chunks' writes. The count lives on this GPU, so the fence in front of it only
+// has to order the CTA's writes for this GPU's other CTAs (gpu scope); the thread that completes the part then
+// fences at system scope before it publishes the part's flag, and that release carries everything that
+// happened before it, the other CTAs' chunks included, to the groupmate that acquires the flag.
 __device__ __forceinline__ bool hr_chunks_done(int* counter, int add, int n_chunks) {
-  __threadfence_system();
+  __threadfence();
   const bool last = atomicAdd(counter, add) == n_chunks - add;
   if (last) __threadfence_system();
   return last;
@@ -848,7 +850,7 @@ __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_co
   // arenas, hands the status words to the host and clears the scratch for the next round
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence();   // gpu scope: the last CTA's system-scope release below carries it further
     sh.bcast = atomicAdd(g.queue + 3, 1) == (int)gridDim.x - 1;
   }
   __syncthreads();

@@ -64,7 +64,7 @@ def test_weighted_allreduce_with_modes(n_clients, n_aux):
     tensors = [[torch.randn(123), torch.randn(3, 50), torch.zeros(0)] for _ in range(n_peers)]
     weights = [random.uniform(0.5, 2.0) for _ in range(n_peers)]
     averagers = [DecentralizedAverager([t.clone() for t in tensors[i]], dhts[i], start=True, prefix="mygroup",
-                                       target_group_size=n_peers, min_matchmaking_time=2.0, request_timeout=1.0,
+                                       target_group_size=n_peers, min_matchmaking_time=4.0, request_timeout=1.0,
                                        client_mode=modes[i] == "client", auxiliary=modes[i] == "aux",
                                        part_size_bytes=256)
                  for i in range(n_peers)]
