@@ -22,7 +22,7 @@ import torch.nn.functional as F
 
 from hivemind_b200.models.albert import _LowPrecisionCache
 from hivemind_b200.ops.attention import attention
-from hivemind_b200.ops.gemm import linear
+from hivemind_b200.ops.gemm import feed_forward, linear
 from hivemind_b200.ops.norm_act import layer_norm
 
 
@@ -87,8 +87,8 @@ class GPT2Block(nn.Module):
         ctx = attention(qkv, nh, causal=True)
         attn = linear(ctx, self.attn_out_weight, self.attn_out_bias, weight_lp=lp.get(self.attn_out_weight))
         normed, stream = layer_norm(attn, self.ln_2_weight, self.ln_2_bias, self.eps, residual=stream, return_sum=True)
-        inter = linear(normed, self.ffn_weight, self.ffn_bias, activation="gelu", weight_lp=lp.get(self.ffn_weight))
-        out = linear(inter, self.ffn_out_weight, self.ffn_out_bias, weight_lp=lp.get(self.ffn_out_weight))
+        out = feed_forward(normed, self.ffn_weight, self.ffn_bias, self.ffn_out_weight, self.ffn_out_bias,
+                           w1_lp=lp.get(self.ffn_weight), w2_lp=lp.get(self.ffn_out_weight))
         return layer_norm(out, next_ln_weight, next_ln_bias, self.eps, residual=stream, return_sum=True)
 
 

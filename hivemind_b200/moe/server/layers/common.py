@@ -14,7 +14,7 @@ import torch
 from torch import nn
 
 from hivemind_b200.moe.server.layers.custom_experts import register_expert_class
-from hivemind_b200.ops.gemm import linear
+from hivemind_b200.ops.gemm import feed_forward, linear
 from hivemind_b200.ops.norm_act import layer_norm
 
 
@@ -46,8 +46,10 @@ class FeedforwardBlock(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         up, down, norm = self.ffn, self.ffn_output, self.layer_norm
-        update = linear(linear(x, up.weight, up.bias, activation="gelu"), down.weight, down.bias)
-        return layer_norm(update.to(x.dtype), norm.weight, norm.bias, norm.eps, residual=x)
+        # one autograd node for both products; the residual's gradient joins the input gradient inside a GEMM and the
+        # output bias gets its gradient from the LayerNorm's backward pass
+        update, skip = feed_forward(x, up.weight, up.bias, down.weight, down.bias, skip_out_bias_grad=True, passthrough=True)
+        return layer_norm(update.to(x.dtype), norm.weight, norm.bias, norm.eps, residual=skip, producer_bias=down.bias)
 
 
 class TransformerEncoderLayer(nn.Module):

@@ -415,6 +415,30 @@ def test_feed_forward_node_matches_fp32_math(passthrough):
         assert torch.allclose(mine.grad, ref.grad, atol=0.4, rtol=3e-2), (mine.grad - ref.grad).abs().max()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ffn_expert_block_on_cuda_matches_its_fp32_formula(dtype):
+    """The ``ffn`` expert of the MoE server (one feed-forward node + LayerNorm with the producer's bias gradient)."""
+    from hivemind_b200.moe.server.layers.common import FeedforwardBlock
+
+    torch.manual_seed(21)
+    block = FeedforwardBlock(256).to(_dev())
+    x = torch.randn(300, 256, device=_dev(), dtype=dtype, requires_grad=True)
+    y = block(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref = FeedforwardBlock(256).to(_dev())
+    ref.load_state_dict(block.state_dict())
+    xr = x.detach().float().requires_grad_()
+    inner = F.gelu(F.linear(xr, ref.ffn.weight, ref.ffn.bias), approximate="tanh")
+    yr = F.layer_norm(xr + F.linear(inner, ref.ffn_output.weight, ref.ffn_output.bias), (256,), ref.layer_norm.weight,
+                      ref.layer_norm.bias, 1e-12)
+    yr.backward(dy.float())
+    assert y.dtype == dtype and torch.allclose(y.float(), yr, atol=6e-2, rtol=3e-2)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=8e-2, rtol=5e-2)
+    for mine, theirs in zip(block.parameters(), ref.parameters()):
+        assert torch.allclose(mine.grad.float(), theirs.grad, atol=0.5, rtol=5e-2), (mine.grad.float() - theirs.grad).abs().max()
+
+
 def test_orthogonalize_matches_gram_schmidt():
     from hivemind_b200.ops.powersgd import orthogonalize_batch_
     from hivemind_b200.utils.math import orthogonalize_reference_
