@@ -18,18 +18,22 @@
 //                          acknowledged that they are done, announces this GPU's round and waits (bounded) for every
 //                          groupmate's announcement, so that the big kernel does not occupy the SMs while a peer is
 //                          still busy elsewhere.
-//   round kernel         : a persistent grid (two 256-thread CTAs per SM) that takes work items from a queue in a
-//                          fixed order: send items, then reduce items, then apply items. A CTA that waits for a
-//                          remote flag therefore never delays work that another GPU needs from this one.
-//     send   (part of a groupmate, chunk)  : 8192 values are read ONCE into registers; statistics, quantisation,
-//                          per-bin sums and the record header are computed in the same CTA; the CTA that completes
-//                          a part publishes its flag together with this GPU's weight (64-bit store, release.sys).
-//     reduce (own part, chunk)             : waits (bounded) for the senders' flags; pulls each sender's chunk record
-//                          over NVLink once (keeping a local copy), accumulates in registers, applies the average to
-//                          its own values, and for every sender encodes  avg - decode(copy)  in place: no separate
-//                          statistics / encode / publish passes. Uncompressed parts are read straight from the
-//                          senders' vectors and publish the average itself.
-//     apply  (part of a groupmate, chunk)  : waits (bounded) for the owner's flag, x += alpha * decode(delta).
+//   round kernel         : a persistent grid (two 512-thread CTAs per SM). Work items are runs of consecutive chunks
+//                          of one part (by default the whole part), listed send, reduce, apply and dealt round-robin:
+//                          a CTA finishes its send items before it may wait for a groupmate, so a wait for a
+//                          remote flag never delays work that another GPU needs from this one.
+//     send   (part of a groupmate)         : every chunk of 8192 values is read ONCE into registers; statistics,
+//                          quantisation, per-bin sums and the record header are computed by the same CTA; the CTA
+//                          that completes a part publishes its flag together with this GPU's weight (64-bit store,
+//                          release.sys).
+//     reduce (own part)                    : one lane per sender waits (bounded) for that sender's flag; the CTA then
+//                          pulls each sender's chunk record over NVLink once, one chunk ahead of its use (keeping a
+//                          local copy), accumulates in registers, applies the average to its own values, and for
+//                          every sender encodes  avg - decode(copy)  in place: no separate statistics / encode /
+//                          publish passes. Uncompressed parts are read straight from the senders' vectors and
+//                          publish the average itself.
+//     apply  (part of a groupmate)         : waits (bounded) for the owner's flag, x += alpha * decode(delta), the
+//                          records again requested one chunk ahead.
 //
 // Codecs work on chunks: every chunk of 8192 elements carries its own header (mean/std, codebook or block maxima),
 // which is what lets a CTA finish a chunk without a second launch. Records never leave this box.
@@ -123,11 +127,6 @@ HM_API long long hm_br_record_bytes(int codec, int len) {
   return hr_chunk_stride(codec) * ((len + HR_CHUNK - 1) / HR_CHUNK);
 }
 
-__device__ __forceinline__ unsigned long long hr_ld_acquire_sys_u64(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void hr_st_release_sys_u64(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
