@@ -259,12 +259,11 @@ class DeviceEndpoint:
         assert all(t.device == self.device for t in tensors), "all averaged tensors must live on one GPU"
         self.lib = _lib.load_library()
         self._code = _code_table_on(self.device)
-        self.part_size_bytes = part_size_bytes
+        self.part_size_bytes = part_size_bytes  # the RPC path's part size; device parts are sized by device_part_chunks
         self.numels = [t.numel() for t in tensors]
         self.codecs = [codec_id(compression, info) for info in tensor_infos]
         self.supported = all(c is not None for c in self.codecs)
         codecs = [c if c is not None else 0 for c in self.codecs]
-        self.ratios = [{0: 1.0, 1: 0.5, 2: 0.5}.get(c, 0.25) for c in codecs]
         # flat layout: every tensor starts on an ALIGN-element boundary; uncompressed tensors also get a place in
         # the (compact) average buffer
         self.offsets, self.avg_offsets, cursor, avg_cursor = [], [], 0, 0
