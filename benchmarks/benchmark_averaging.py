@@ -21,6 +21,7 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
+import numpy as np
 import torch
 
 from hivemind_b200 import DHT, DecentralizedAverager
@@ -94,6 +95,33 @@ def benchmark_swarm(num_peers, target_group_size, num_rounds, min_matchmaking_ti
 
 
 VERBOSE_ROUNDS = False
+TRACE_ROUND = False
+
+
+def _print_round_trace(endpoint, kwargs, label, rank):
+    """One more round with the kernel's per-CTA time stamps switched on; prints, per rank, when (microseconds after the
+    first CTA of this GPU started, median and maximum over CTAs) the CTAs entered their first reduce item, knew about
+    its flags, left it, entered their first apply item, knew about its flag, left it, and finished."""
+    trace = endpoint.enable_trace()
+    with torch.cuda.stream(torch.cuda.ExternalStream(endpoint.stream.value, device=endpoint.device)):
+        trace.zero_()
+        endpoint.tensor_views[0].normal_()
+    endpoint.run_round(group_id=f"trace-{label}".encode(), **kwargs)
+    stamps = trace.cpu().numpy().astype("float64")
+    started = stamps[:, 0][stamps[:, 0] > 0]
+    if len(started) == 0:
+        return
+    origin = started.min()
+    names = {1: "reduce entered", 8: "reduce flags known", 2: "first reduce item left", 3: "last reduce item left",
+             4: "apply entered", 9: "apply flag known", 5: "first apply item left", 6: "last item left"}
+    row = {}
+    for column, name in names.items():
+        values = stamps[:, column][stamps[:, column] > 0]
+        if len(values):
+            rel = (values - origin) / 1e3
+            row[name] = [round(float(np.median(rel)), 1), round(float(rel.max()), 1)]
+    print(json.dumps({"trace": label, "rank": rank, "ctas": int(len(started)), "items_per_cta_max": int(stamps[:, 7].max()),
+                      "us_after_start_median_max": row}), flush=True)
 
 
 def _time_rounds(endpoint, plan_args, rounds, warmup):
@@ -195,6 +223,9 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
                 ms = float(t[0])
                 stages = {name: float(v) for name, v in zip(stages, t[1:])}
                 dist.barrier()
+                if TRACE_ROUND:
+                    _print_round_trace(endpoint, kwargs, f"{size_mb} MB {codec_name}", rank)
+                    dist.barrier()
                 endpoint.close()
             else:
                 n = emulate_ranks
@@ -276,8 +307,11 @@ if __name__ == "__main__":
     parser.add_argument("--emulate-ranks", type=int, default=4)
     parser.add_argument("--part-size-bytes", type=int, default=2 ** 19)
     parser.add_argument("--verbose-rounds", action="store_true", help="print every launch of every timed round")
+    parser.add_argument("--trace-round", action="store_true",
+                        help="device mode with several GPUs: after the timed rounds, one round with per-CTA time stamps")
     args = parser.parse_args()
     VERBOSE_ROUNDS = args.verbose_rounds
+    TRACE_ROUND = args.trace_round
     if args.increase_file_limit:
         increase_file_limit()
     if args.mode == "device":

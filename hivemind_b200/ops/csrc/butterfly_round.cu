@@ -92,6 +92,7 @@ struct HrRound {
   const float* code;           // block-wise code [256], midpoints between consecutive entries [256], search table [16384 B]
   unsigned int done_slot;
   int uses_blockwise;          // some part uses the block-wise codec: CTAs load the search table
+  unsigned long long* trace;   // optional [gridDim.x][12] globaltimer stamps per CTA (see hr_round_kernel); null = off
 };
 
 struct HrGate {
@@ -127,8 +128,12 @@ HM_API long long hm_br_record_bytes(int codec, int len) {
   return hr_chunk_stride(codec) * ((len + HR_CHUNK - 1) / HR_CHUNK);
 }
 
-__device__ __forceinline__ void hr_st_release_sys_u64(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+// Flag stores that follow an explicit system-scope fence of the same thread (fence + strong write = release pattern)
+__device__ __forceinline__ void hr_st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void hr_st_relaxed_sys_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 struct HrShared {
@@ -158,6 +163,7 @@ struct HrShared {
 // Per-thread bookkeeping with the same value in every thread of the CTA: which scratch copy comes next.
 struct HrThread {
   int red = 0, cb = 0;
+  unsigned long long* stamps = nullptr;   // this CTA's row of the optional trace (thread 0 writes)
 };
 
 // element index inside the chunk handled by (row r, thread, k)
@@ -500,10 +506,10 @@ __device__ __forceinline__ unsigned long long hr_ld_acquire_gpu_u64(const unsign
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ unsigned long long hr_cas_release_gpu_u64(unsigned long long* p, unsigned long long expected,
+__device__ __forceinline__ unsigned long long hr_cas_relaxed_gpu_u64(unsigned long long* p, unsigned long long expected,
                                                                     unsigned long long desired) {
   unsigned long long old;
-  asm volatile("atom.release.gpu.global.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "l"(p), "l"(expected), "l"(desired) : "memory");
+  asm volatile("atom.relaxed.gpu.global.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "l"(p), "l"(expected), "l"(desired) : "memory");
   return old;
 }
 
@@ -520,8 +526,8 @@ __device__ __forceinline__ unsigned long long hr_phase_start(unsigned long long*
 // Bounded wait of ONE thread for a flag that a groupmate publishes in one of its two flag sets. The outcome goes
 // into `decision` by compare-and-swap, so that all CTAs that work on the same part agree; its low word says 1 / 3 =
 // published (in flag set 0 / 1) or 2 = gave up, its high word carries the weight that came with the flag. Only the
-// first CTA to get here talks to the groupmate: it reads the flag with acquire.sys and publishes the decision with
-// release.gpu; every later CTA finds the decision with ONE acquire.gpu load, which orders its reads of the
+// first CTA to get here talks to the groupmate: it polls the flag, fences and publishes the decision; every later
+// CTA finds the decision with ONE acquire.gpu load, which orders its reads of the
 // groupmate's data after the groupmate's writes just the same (release / acquire chains are cumulative). The clock
 // is only looked at while the flag is missing: the time limit runs from the moment this GPU first had to wait in
 // the phase (`t_start`).
@@ -559,8 +565,10 @@ __device__ unsigned long long hr_decide(const unsigned long long* flag0, const u
     if (verdict == 0) {
       __nanosleep(200);
     } else {
+      // the fence makes the poll that saw the flag an acquire, and is the release half for the CTAs that will read
+      // the decision (fence + strong write); a give-up verdict has no data behind it
       if (verdict != 2ull) __threadfence_system();
-      hr_cas_release_gpu_u64(decision, 0ull, verdict);
+      hr_cas_relaxed_gpu_u64(decision, 0ull, verdict);
     }
     d = hr_ld_acquire_gpu_u64(decision);
   }
@@ -585,8 +593,10 @@ __device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& s
   unsigned long long* ready = reinterpret_cast<unsigned long long*>(my + g.lay.ready[g.parity]);
   const unsigned long long flag = (unsigned long long)g.epoch | ((unsigned long long)__float_as_uint(g.my_weight) << 32);
   if (p < 0) {
-    // uncompressed parts: readers take the values from the vector itself, only the flags are published
-    for (int i = threadIdx.x; i < z; i += HR_THREADS) hr_st_release_sys_u64(ready + g.pub_list[c0 + i], flag);
+    // uncompressed parts: readers take the values from the vector itself (written before this kernel began), only
+    // the flags are published: one fence per thread, then plain flag stores
+    if ((int)threadIdx.x < z) __threadfence_system();
+    for (int i = threadIdx.x; i < z; i += HR_THREADS) hr_st_relaxed_sys_u64(ready + g.pub_list[c0 + i], flag);
     return;
   }
   const HrPart part = g.parts[p];
@@ -610,7 +620,7 @@ __device__ void hr_send_item(const HrRound& g, int p, int c0, int z, HrShared& s
   }
   const int n_chunks = (part.len + HR_CHUNK - 1) / HR_CHUNK;
   __syncthreads();
-  if (threadIdx.x == 0 && hr_chunks_done(g.part_done + p, z, n_chunks)) hr_st_release_sys_u64(ready + p, flag);
+  if (threadIdx.x == 0 && hr_chunks_done(g.part_done + p, z, n_chunks)) hr_st_relaxed_sys_u64(ready + p, flag);
 }
 
 __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared& sh, HrThread& th) {
@@ -657,6 +667,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
     }
   }
   __syncthreads();
+  if (th.stamps != nullptr && threadIdx.x == 0 && th.stamps[8] == 0) th.stamps[8] = hm_globaltimer_ns();
 
   const bool i_send = g.sends[me] != 0;
   const int n_inc = sh.n_inc;
@@ -676,12 +687,48 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
   };
   auto chunk_len = [&](int c) { return min(HR_CHUNK, part.len - c * HR_CHUNK); };
   const int total = z * n_inc;
+  // One remote sender (a group of two, or everybody else left out): its record stays in registers until the delta
+  // has been encoded, so no copy is written and read back
+  const bool single = n_inc == 1 && codec != HB_NONE && !dead;
   HrAhead ahead;
   if (total > 0) hr_fetch(codec, source(sh.order[0], c0), chunk_len(c0), ahead);
 
   for (int c = c0; c < c0 + z; ++c) {
     const int lo = c * HR_CHUNK, n = chunk_len(c);
     float* x_local = reinterpret_cast<float*>(my + g.lay.data) + part.start + lo;
+    if (single) {
+      // row by row: average, own values updated, delta taken, while the record is in registers
+      const int s = sh.order[0];
+      const float w = sh.w[s];
+      const HrAhead cur = ahead;
+      if (c + 1 < c0 + z) hr_fetch(codec, source(s, c + 1), chunk_len(c + 1), ahead);
+      float mean, sd, absmax[HR_BLOCKS] = {};
+      const float* cb = hr_open(codec, cur, sh, th, nullptr, mean, sd, absmax);
+      float d1[HR_ROWS][4];
+#pragma unroll
+      for (int r = 0; r < HR_ROWS; ++r) {
+        const int i = hr_elem(r);
+        const bool inside = i + 4 <= n;   // parts are whole multiples of four elements
+        float4 own = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i_send && inside) own = *reinterpret_cast<const float4*>(x_local + i);
+        float o[4];
+        hr_decode_ahead(codec, cur, r, mean, sd, cb, absmax, o);
+        const float mine4[4] = {own.x, own.y, own.z, own.w};
+        float a[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          a[q] = fmaf(w, o[q], g.my_weight * mine4[q]) * inv_den;
+          d1[r][q] = inside ? a[q] - o[q] : 0.f;
+        }
+        if (i_send && inside)
+          *reinterpret_cast<float4*>(x_local + i) =
+              make_float4(fmaf(alpha_own, a[0] - own.x, own.x), fmaf(alpha_own, a[1] - own.y, own.y),
+                          fmaf(alpha_own, a[2] - own.z, own.z), fmaf(alpha_own, a[3] - own.w, own.w));
+      }
+      hr_encode_chunk(d1, n, codec,
+                      my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride, sh, th);
+      continue;
+    }
     float acc[HR_ROWS][4];
 #pragma unroll
     for (int r = 0; r < HR_ROWS; ++r) {
@@ -700,14 +747,15 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
         if (c2 < c0 + z) hr_fetch(codec, source(sh.order[k2], c2), chunk_len(c2), ahead);
       }
       unsigned char* local = my + g.lay.deltabox[g.parity] + (size_t)s * g.delta_stride + part.span_off + (long long)c * stride;
+      const bool keep_copy = codec != HB_NONE;
       float mean, sd, absmax[HR_BLOCKS] = {};
-      const float* cb = hr_open(codec, cur, sh, th, codec == HB_NONE ? nullptr : local, mean, sd, absmax);
+      const float* cb = hr_open(codec, cur, sh, th, keep_copy ? local : nullptr, mean, sd, absmax);
 #pragma unroll
       for (int r = 0; r < HR_ROWS; ++r) {
-        // compressed records: keep a copy where this sender's delta will be written
-        if (hb_elem_bytes(codec) == 2)
+        // several senders: keep a copy of each record where that sender's delta will be written
+        if (keep_copy && hb_elem_bytes(codec) == 2)
           *reinterpret_cast<uint2*>(local + hdr + (size_t)hr_elem(r) * 2) = make_uint2(cur.w[2 * r], cur.w[2 * r + 1]);
-        else if (hb_elem_bytes(codec) == 1)
+        else if (keep_copy && hb_elem_bytes(codec) == 1)
           *reinterpret_cast<uint32_t*>(local + hdr + hr_elem(r)) = cur.w[r];
         float o[4];
         hr_decode_ahead(codec, cur, r, mean, sd, cb, absmax, o);
@@ -724,7 +772,9 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
       for (int q = 0; q < 4; ++q) acc[r][q] = (i + q < n) ? acc[r][q] * inv_den : 0.f;
       if (i + 4 <= n) {   // parts are whole multiples of four elements
         if (codec == HB_NONE) *reinterpret_cast<float4*>(avg_out + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
-        if (i_send) {
+        if (i_send && alpha_own == 1.f) {   // the usual case: the average replaces the values, no second read
+          *reinterpret_cast<float4*>(x_local + i) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        } else if (i_send && alpha_own != 0.f) {
           float4 own = *reinterpret_cast<const float4*>(x_local + i);
           own.x = fmaf(alpha_own, acc[r][0] - own.x, own.x); own.y = fmaf(alpha_own, acc[r][1] - own.y, own.y);
           own.z = fmaf(alpha_own, acc[r][2] - own.z, own.z); own.w = fmaf(alpha_own, acc[r][3] - own.w, own.w);
@@ -761,7 +811,7 @@ __device__ void hr_reduce_item(const HrRound& g, int p, int c0, int z, HrShared&
     const int s = threadIdx.x;
     if (s != me && g.sends[s] && hr_chunks_done(g.dpart_done + (size_t)s * g.max_local_parts + j, z, n_chunks)) {
       unsigned int* flag = reinterpret_cast<unsigned int*>(my + g.lay.dready[g.parity]) + (size_t)s * g.max_local_parts + j;
-      hm_st_release_sys(flag, (sh.inc[s] && !dead) ? g.epoch : (g.epoch | HB_FAIL_BIT));
+      hr_st_relaxed_sys_u32(flag, (sh.inc[s] && !dead) ? g.epoch : (g.epoch | HB_FAIL_BIT));
     }
   }
 }
@@ -779,6 +829,7 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& 
                                             false, g.epoch, g.apply_decision + p, nullptr, g.t_start + 1, g.reducer_timeout_ns);
   }
   __syncthreads();
+  if (th.stamps != nullptr && threadIdx.x == 0 && th.stamps[9] == 0) th.stamps[9] = hm_globaltimer_ns();
   const int d = sh.bcast;
   if (d == 2) {
     if (threadIdx.x == 0) {
@@ -810,6 +861,10 @@ __device__ void hr_apply_item(const HrRound& g, int p, int c0, int z, HrShared& 
       if (i + 4 > n) continue;   // parts are whole multiples of four elements
       float dv[4];
       hr_decode_ahead(codec, cur, r, mean, sd, cb, absmax, dv);
+      if (codec == HB_NONE && alpha == 1.f) {   // the average replaces the values: nothing to read
+        *reinterpret_cast<float4*>(x + i) = make_float4(dv[0], dv[1], dv[2], dv[3]);
+        continue;
+      }
       float4 xv = *reinterpret_cast<const float4*>(x + i);
       if (codec == HB_NONE) {   // the record is the average itself
         xv.x = fmaf(alpha, dv[0] - xv.x, xv.x); xv.y = fmaf(alpha, dv[1] - xv.y, xv.y);
@@ -838,12 +893,33 @@ __global__ void __launch_bounds__(HR_THREADS, 2) hr_round_kernel(const __grid_co
   }
   // Items are dealt round-robin. The list is ordered send, reduce, apply, so every CTA finishes its send items
   // before it may wait for a groupmate, and nothing that a groupmate needs from this GPU queues up behind a wait.
+  // With g.trace set, thread 0 stamps: [0] start, [1] / [2] first reduce item entered / left, [3] last reduce item
+  // left, [4] / [5] first apply item entered / left, [6] last item left, [7] items done by this CTA, [8] / [9] the
+  // moment the first reduce / apply item knew about its flags (the waits end there).
+  unsigned long long* stamps = g.trace != nullptr ? g.trace + 12 * (size_t)blockIdx.x : nullptr;
+  th.stamps = stamps;
+  if (stamps != nullptr && threadIdx.x == 0) stamps[0] = hm_globaltimer_ns();
+  int seen_reduce = 0, seen_apply = 0, n_items = 0;
   for (int idx = g.item_begin + (int)blockIdx.x; idx < g.item_end; idx += (int)gridDim.x) {
     __syncthreads();
     const int4 it = g.items[idx];
-    if (idx < g.n_send) hr_send_item(g, it.x, it.y, it.z, sh, th);
-    else if (idx < g.n_send + g.n_reduce) hr_reduce_item(g, it.x, it.y, it.z, sh, th);
+    const int kind = idx < g.n_send ? 0 : (idx < g.n_send + g.n_reduce ? 1 : 2);
+    if (stamps != nullptr && threadIdx.x == 0) {
+      if (kind == 1 && !seen_reduce) stamps[1] = hm_globaltimer_ns();
+      if (kind == 2 && !seen_apply) stamps[4] = hm_globaltimer_ns();
+    }
+    if (kind == 0) hr_send_item(g, it.x, it.y, it.z, sh, th);
+    else if (kind == 1) hr_reduce_item(g, it.x, it.y, it.z, sh, th);
     else hr_apply_item(g, it.x, it.y, it.z, sh, th);
+    if (stamps != nullptr && threadIdx.x == 0) {
+      const unsigned long long now = hm_globaltimer_ns();
+      if (kind == 1) { if (!seen_reduce) stamps[2] = now; stamps[3] = now; }
+      if (kind == 2 && !seen_apply) stamps[5] = now;
+      stamps[6] = now;
+      stamps[7] = (unsigned long long)(++n_items);
+    }
+    seen_reduce |= kind == 1;
+    seen_apply |= kind == 2;
   }
   // the last CTA to leave closes the round: acknowledges that this GPU has finished reading its groupmates'
   // arenas, hands the status words to the host and clears the scratch for the next round

@@ -115,7 +115,8 @@ class _HrRound(ctypes.Structure):
                 ("include", ctypes.c_void_p), ("apply_decision", ctypes.c_void_p), ("ban", ctypes.c_void_p),
                 ("t_start", ctypes.c_void_p), ("status", ctypes.c_void_p), ("status_out", ctypes.c_void_p),
                 ("part_done", ctypes.c_void_p), ("dpart_done", ctypes.c_void_p), ("queue", ctypes.c_void_p),
-                ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint), ("uses_blockwise", ctypes.c_int)]
+                ("code", ctypes.c_void_p), ("done_slot", ctypes.c_uint), ("uses_blockwise", ctypes.c_int),
+                ("trace", ctypes.c_void_p)]
 
 
 class _HrGate(ctypes.Structure):
@@ -344,6 +345,7 @@ class DeviceEndpoint:
         self._history: Dict[int, Tuple[int, List[int]]] = {}  # parity -> (epoch, bases of that round's groupmates)
         self._sms = _lib.sm_count(self.device)
         self.fault_publish_half = False  # host-side fault injection: publish only the first half of the parts sent
+        self.trace: Optional[torch.Tensor] = None  # see enable_trace()
         self._gate = _HrGate()  # the gate kernel's parameter block (launches copy it, so one instance serves all rounds)
         self._gate.lay = self._layout_struct()
         self._gate.gate_status = self._gate_status.data_ptr()
@@ -390,6 +392,16 @@ class DeviceEndpoint:
             self.supported = False
             logger.warning("could not map a groupmate's device arena; this peer uses the RPC butterfly from now on")
             raise
+
+    def enable_trace(self) -> torch.Tensor:
+        """Let the round kernel stamp, per CTA, when it started, entered and left its first reduce and apply items,
+        learned about their flags and finished (12 ``globaltimer`` values per CTA, zero where a CTA had no such item).
+        The tensor is overwritten by every round; zero it between rounds that are to be compared."""
+        if self.trace is None:
+            with torch.cuda.stream(self._torch_stream):
+                self.trace = torch.zeros(CTAS_PER_SM * self._sms, 12, dtype=torch.int64, device=self.device)
+                self._torch_stream.synchronize()
+        return self.trace
 
     def check_canaries(self) -> None:
         """Raise if any kernel (of this GPU or of a groupmate) wrote past the end of one of the arena's regions.
@@ -563,6 +575,7 @@ class DeviceEndpoint:
             plan.rounds[key] = template = g
         g = _HrRound.from_buffer_copy(template)  # rounds may overlap (one being finished while the next is prepared)
         g.item_begin, g.item_end, g.queue_slot, g.final_stage = 0, plan.n_send + plan.n_reduce + plan.n_apply, 0, 1
+        g.trace = self.trace.data_ptr() if self.trace is not None else None
         g.epoch = (zlib.crc32(group_id) & 0x7FFFFFFF) | 1
         g.parity = self._round_seq & 1
         g.done_slot = self._round_seq
