@@ -235,14 +235,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         uint32_t r[32];
         tc_ld32(tmem_s + lane_base + (uint32_t)(ch * 32), r);
         tc_wait_ld();
+        // four independent chains; measured neutral against one chain of 32 (the pass waits on TMEM loads, not on these)
+        float m4[4] = {mx, -INFINITY, -INFINITY, -INFINITY};
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (key0 + ch * 32 + i < key_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+            if (key0 + ch * 32 + i < key_limit) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              m4[q] = fmaxf(m4[q], fmaxf(__uint_as_float(r[i + 2 * q]), __uint_as_float(r[i + 2 * q + 1])));
+          }
         }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = fast_exp2((m_run - m_use) * c);   // 0 on the first block
@@ -279,8 +286,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) e[i] = fast_exp2(fmaf(__uint_as_float(r[i]), c, neg_mc));
         }
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sum += e[i];
+        for (int i = 0; i < 32; ++i) s4[i & 3] += e[i];
+        sum += (s4[0] + s4[1]) + (s4[2] + s4[3]);
         uint8_t* slab = p_smem + (ch >> 1) * TILE_BYTES + row * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
