@@ -27,8 +27,24 @@ import tempfile
 import threading
 import time
 
-# stdout carries exactly one JSON line: whatever NCCL has to say (its version banner, warnings) goes to stderr
-os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+# stdout carries exactly one JSON line. Libraries write to file descriptor 1 as they please (NCCL prints its version
+# banner there when NCCL_DEBUG=VERSION, whatever NCCL_DEBUG_FILE says), so descriptor 1 is pointed at stderr for the
+# whole run and the result line goes out through a private duplicate of the original stdout.
+_RESULT_FD = None
+
+
+def _claim_stdout() -> None:
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit(result: dict) -> None:
+    _claim_stdout()
+    os.write(_RESULT_FD, (json.dumps(result) + "\n").encode())
+
 
 BASELINE_SAMPLES_PER_SEC = 20.924  # the only Optimizer throughput in the reference tree: examples/albert/README.md:96
 
@@ -37,7 +53,7 @@ def _reference_arm(args) -> None:
     reason = ("the reference cannot be installed offline: its build downloads the Go p2pd binary "
               "(setup.py:126-162, urlopen fails without network) and needs grpc_tools to compile protos")
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}))
+        _emit({"impl": "reference", "unavailable": reason})
 
 
 class ClockSampler:
@@ -88,6 +104,7 @@ class ClockSampler:
 
 
 def main() -> None:
+    _claim_stdout()
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=3, help="timed collaborative optimizer steps (epochs)")
@@ -152,7 +169,7 @@ def main() -> None:
         clocks = sampler.stop() if rank == 0 else {}
         e2e = baseline(args.steps, 1, end_to_end=True) if not args.no_e2e else None
         if rank == 0:
-            print(json.dumps({
+            _emit({
                 "metric": "Optimizer samples/s (ALBERT-large)", "value": res["value"], "unit": "samples/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": res["ms_per_step"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": res["value"] / BASELINE_SAMPLES_PER_SEC,
@@ -160,7 +177,7 @@ def main() -> None:
                 "e2e": None if e2e is None else {"value": e2e["value"], "unit": "samples/s"},
                 "config": {"model": "albert-large, plain PyTorch modules", "global_batch": args.target_batch_size,
                            "micro_batch_per_gpu": args.micro_batch, "seq_len": seq_len, "parallelism": f"dp{world}",
-                           "what": res["what"]}}))
+                           "what": res["what"]}})
         if world > 1:
             dist.destroy_process_group()
         return
@@ -270,7 +287,7 @@ def main() -> None:
         except Exception as e:  # the context number must never cost the headline number
             torch_nccl = {"error": repr(e)}
     if rank == 0:
-        print(json.dumps({
+        _emit({
             "metric": "Optimizer samples/s (ALBERT-large)", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": value / BASELINE_SAMPLES_PER_SEC, "dtype": "bf16", "data": "synthetic",
@@ -285,7 +302,7 @@ def main() -> None:
                        "samples_in_timed_region": samples,
                        "l2": "activations of one micro-batch (>2 GB) exceed the 126 MB L2; no explicit flush",
                        "baseline_note": "vs_baseline divides by the only Optimizer throughput printed in the "
-                                        "reference tree (20.924 samples/s, one trainer, unspecified GPU)"}}))
+                                        "reference tree (20.924 samples/s, one trainer, unspecified GPU)"}})
     if world > 1:
         dist.destroy_process_group()
 
