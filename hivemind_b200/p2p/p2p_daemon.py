@@ -129,22 +129,34 @@ class P2P:
         self._alive = True
         ready = asyncio.get_event_loop().create_future()
         loop = asyncio.get_event_loop()
-        self._reader_thread = threading.Thread(target=self._read_outputs, args=(loop, ready), daemon=True)
+        # the thread gets the child process, not this object: a bound method would keep the instance alive, and with it
+        # the daemon that __del__ is there to stop
+        self._reader_thread = threading.Thread(target=self._read_outputs, args=(self._child, loop, ready), daemon=True)
         self._reader_thread.start()
         try:
             await asyncio.wait_for(ready, startup_timeout)
         except asyncio.TimeoutError:
             await self.shutdown()
-            raise P2PDaemonError(f"transport daemon failed to start in {startup_timeout:.1f} seconds")
+            raise P2PDaemonError(f"Daemon failed to start in {startup_timeout:.1f} seconds")
         self._client = await DaemonClient.create(self._control_path, os.path.join(self._workdir, f"h-{secrets.token_hex(4)}.sock"),
                                                  persistent_conn_max_msg_size=persistent_conn_max_msg_size)
         await self._ping_daemon()
+        connected, problems = 0, []
         for peer in initial_peers or []:
             peer = Multiaddr(peer)
             try:
-                await self._client.connect(PeerID.from_base58(peer["p2p"]), [peer])
+                remote = PeerID.from_base58(peer["p2p"])
+                await self._client.connect(remote, [peer])
+                if not await self._answers(remote):  # the daemon only notes the address; see whether anybody is there
+                    raise P2PDaemonError("no answer")
+                connected += 1
             except Exception as e:
+                problems.append(f"{peer}: {e!r}")
                 logger.warning(f"could not connect to initial peer {peer}: {e!r}")
+        if initial_peers and connected == 0:
+            # like the reference's daemon, which refuses to start when no bootstrap peer answers
+            await self.shutdown()
+            raise P2PDaemonError("failed to connect to bootstrap peers: " + "; ".join(problems))
         return self
 
     @staticmethod
@@ -172,6 +184,18 @@ class P2P:
         """Write a fresh RSA identity (protobuf ``crypto.pb.PrivateKey``) to ``identity_path``."""
         P2P._write_identity(identity_path, rsa.generate_private_key(public_exponent=65537, key_size=2048))
 
+    async def _answers(self, peer_id: PeerID, timeout: float = 3.5) -> bool:
+        """True if a daemon with this id answers a call to a handler that nobody registers ("not supported" is an
+        answer; an unknown address, a refused connection or silence is not)."""
+        try:
+            await asyncio.wait_for(self._client.call_unary_handler(peer_id, "__identity_probe__", b""), timeout)
+        except P2PHandlerError as e:
+            text = str(e).lower()
+            return not any(word in text for word in ("address unknown", "connect", "unreachable", "refused"))
+        except (P2PDaemonError, asyncio.TimeoutError):
+            return False
+        return True
+
     @classmethod
     async def is_identity_taken(cls, peer_id: PeerID, initial_peers: Sequence[Union[Multiaddr, str]]) -> bool:
         """True if a peer with this id answers on the network reachable through ``initial_peers``."""
@@ -179,13 +203,7 @@ class P2P:
         try:
             if any(info.peer_id == peer_id for info in await probe.list_peers()):
                 return True
-            try:
-                await asyncio.wait_for(probe._client.call_unary_handler(peer_id, "__identity_probe__", b""), 3.5)
-            except P2PHandlerError as e:
-                return "address unknown" not in str(e)  # somebody answered (even if only "not supported")
-            except (P2PDaemonError, asyncio.TimeoutError):
-                return False
-            return True
+            return await probe._answers(peer_id)
         finally:
             await probe.shutdown()
 
@@ -456,11 +474,12 @@ class P2P:
                         os.unlink(os.path.join(self._workdir, entry))
                 os.rmdir(self._workdir)
 
-    def _read_outputs(self, loop: asyncio.AbstractEventLoop, ready: asyncio.Future) -> None:
+    @staticmethod
+    def _read_outputs(child: Optional[subprocess.Popen], loop: asyncio.AbstractEventLoop, ready: asyncio.Future) -> None:
         """Runs in a thread: wait for the daemon's "Ready" line, then forward its stderr to the logger."""
-        child = self._child
         if child is None:
             return
+        last_words: List[str] = []
         try:
             for line in child.stdout:
                 line = line.strip()
@@ -470,11 +489,13 @@ class P2P:
             for line in child.stderr:
                 line = line.rstrip()
                 if line:
+                    last_words = (last_words + [line])[-5:]
                     logger.debug(line if line.startswith("[hmp2pd]") else f"[hmp2pd] {line}")
         except Exception:
             pass
         finally:
             if not ready.done():
+                said = (": " + " | ".join(last_words)) if last_words else ""
                 with suppress(RuntimeError):
                     loop.call_soon_threadsafe(
-                        lambda: ready.done() or ready.set_exception(P2PDaemonError("transport daemon exited at start")))
+                        lambda: ready.done() or ready.set_exception(P2PDaemonError("transport daemon exited at start" + said)))

@@ -280,3 +280,100 @@ def test_dead_daemon_is_reported_and_shutdown_is_idempotent():
         assert not node.is_alive
 
     run(main())
+
+
+def test_start_up_failures_say_why():
+    """Reference cases test_startup_error_message (tests/test_p2p_daemon.py:44-56): unreachable bootstrap peers and an
+    impossible start-up time limit end in P2PDaemonError with a message that names the cause."""
+    async def main():
+        import socket
+
+        with socket.socket() as probe:  # a port that nobody listens on
+            probe.bind(("127.0.0.1", 0))
+            port = probe.getsockname()[1]
+        nobody = f"/ip4/127.0.0.1/tcp/{port}/p2p/QmdaK4LUeQaKhqSFPRu9N7MvXUEWDxWwtCvPrS444tCgd1"
+        with pytest.raises(P2PDaemonError, match=r"(?i)failed to connect to bootstrap peers"):
+            await P2P.create(initial_peers=[nobody])
+        with pytest.raises(P2PDaemonError, match=r"Daemon failed to start in .+ seconds"):
+            await P2P.create(startup_timeout=0.0001)
+
+    run(main())
+
+
+def test_daemon_dies_with_its_owner_and_identities_are_exclusive(tmp_path):
+    """Reference cases test_daemon_killed_on_del and test_check_if_identity_free (tests/test_p2p_daemon.py:28-42,
+    64-86): dropping the last reference to a P2P instance ends its daemon process; an identity that answers on the
+    network cannot be used by a second peer, a fresh one can."""
+    async def main():
+        import gc
+        import os
+
+        instance = await P2P.create()
+        pid = instance._child.pid
+        os.kill(pid, 0)  # alive
+        del instance
+        gc.collect()
+        for _ in range(50):
+            await asyncio.sleep(0.1)
+            try:
+                os.kill(pid, 0)
+                with open(f"/proc/{pid}/stat") as f:
+                    if f.read().split()[2] == "Z":  # a zombie counts as dead: nobody will wait for it after __del__
+                        break
+            except (ProcessLookupError, FileNotFoundError):
+                break
+        else:
+            raise AssertionError("the daemon outlived its owner")
+
+        taken, free = str(tmp_path / "taken.key"), str(tmp_path / "free.key")
+        P2P.generate_identity(taken)
+        P2P.generate_identity(free)
+        first = await P2P.create(identity_path=taken)
+        maddrs = await first.get_visible_maddrs()
+        assert await P2P.is_identity_taken(first.peer_id, maddrs)
+        with pytest.raises(P2PDaemonError, match="already in use"):
+            await P2P.create(identity_path=taken, initial_peers=maddrs)
+        other = await P2P.create(identity_path=free, initial_peers=maddrs)
+        assert other.peer_id != first.peer_id and not await P2P.is_identity_taken(PeerID.from_base58(
+            "QmdaK4LUeQaKhqSFPRu9N7MvXUEWDxWwtCvPrS444tCgd1"), maddrs)
+        await other.shutdown()
+        await first.shutdown()
+
+    run(main())
+
+
+def test_removed_handlers_stop_answering():
+    """Reference cases test_removing_unary_handlers / test_removing_stream_handlers (tests/test_p2p_daemon.py:362-420)."""
+    async def main():
+        server, client = await _pair()
+
+        async def double(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+            return test_pb2.TestResponse(number=2 * request.number)
+
+        async def count(request: test_pb2.TestRequest, context: P2PContext) -> AsyncIterator[test_pb2.TestResponse]:
+            for i in range(request.number):
+                yield test_pb2.TestResponse(number=i)
+
+        await server.add_protobuf_handler("double", double, test_pb2.TestRequest)
+        await server.add_protobuf_handler("count", count, test_pb2.TestRequest, stream_output=True)
+        reply = await client.call_protobuf_handler(server.peer_id, "double", test_pb2.TestRequest(number=21), test_pb2.TestResponse)
+        assert reply.number == 42
+        stream = await client.iterate_protobuf_handler(server.peer_id, "count", test_pb2.TestRequest(number=3), test_pb2.TestResponse)
+        assert [item.number async for item in stream] == [0, 1, 2]
+
+        await server.remove_protobuf_handler("double")
+        await server.remove_protobuf_handler("count", stream_output=True)
+        with pytest.raises((P2PHandlerError, P2PDaemonError)):
+            await client.call_protobuf_handler(server.peer_id, "double", test_pb2.TestRequest(number=1), test_pb2.TestResponse)
+        with pytest.raises((P2PHandlerError, P2PDaemonError)):
+            stream = await client.iterate_protobuf_handler(server.peer_id, "count", test_pb2.TestRequest(number=3), test_pb2.TestResponse)
+            async for _ in stream:
+                pass
+        # a handler can be registered again under the same name
+        await server.add_protobuf_handler("double", double, test_pb2.TestRequest)
+        reply = await client.call_protobuf_handler(server.peer_id, "double", test_pb2.TestRequest(number=4), test_pb2.TestResponse)
+        assert reply.number == 8
+        await client.shutdown()
+        await server.shutdown()
+
+    run(main())
