@@ -410,3 +410,82 @@ def test_cached_values_are_refreshed_before_they_expire():
             await asyncio.gather(*[n.shutdown() for n in nodes])
 
     run(main())
+
+
+def test_protocol_level_ping_store_find_between_three_peers():
+    """The three RPCs of the protocol, used directly (behaviours of the reference's tests/test_dht_protocol.py:67-146):
+    a ping returns the callee's node id and teaches both routing tables, a find returns the stored value with its
+    expiration plus the nearest OTHER nodes the callee knows, sub-key stores build a dictionary value, a peer that does
+    not exist yields None, and a client-mode protocol can do all of this without being added to anybody's table."""
+    from hivemind_b200.dht.protocol import DHTProtocol
+    from hivemind_b200.dht.storage import DictionaryDHTValue
+    from hivemind_b200.p2p import P2P, PeerID
+    from hivemind_b200.utils import MSGPackSerializer
+
+    async def main():
+        async def make(initial_peers=(), client_mode=False):
+            p2p = await P2P.create(initial_peers=list(initial_peers))
+            protocol = await DHTProtocol.create(p2p, DHTID.generate(), bucket_size=20, depth_modulo=5, num_replicas=3,
+                                                wait_timeout=5, client_mode=client_mode)
+            return p2p, protocol
+
+        p2p1, peer1 = await make()
+        maddrs1 = await p2p1.get_visible_maddrs()
+        p2p2, peer2 = await make(maddrs1)
+        assert await peer2.call_ping(p2p1.peer_id) == peer1.node_id  # now 1 and 2 know each other
+        await asyncio.sleep(0.2)
+        try:
+            for client_mode in (True, False):
+                p2p, me = await make(maddrs1, client_mode)
+                assert await me.call_ping(p2p1.peer_id) == peer1.node_id
+                key, value, expiration = DHTID.generate(), [random.random(), {"ololo": "pyshpysh"}], get_dht_time() + 1e3
+                assert all(await me.call_store(p2p1.peer_id, [key], [MSGPackSerializer.dumps(value)], expiration))
+
+                (found, found_expiration), nearest = (await me.call_find(p2p1.peer_id, [key]))[key]
+                assert MSGPackSerializer.loads(found) == value and found_expiration == expiration
+                assert nearest.get(peer2.node_id) == p2p2.peer_id  # peer 1 recommends peer 2 ...
+                assert me.node_id not in nearest  # ... never the caller itself
+
+                missing = DHTID.generate()
+                nothing, nearest2 = (await me.call_find(p2p2.peer_id, [missing]))[missing]
+                assert nothing is None and nearest2.get(peer1.node_id) == p2p1.peer_id
+
+                assert not await me.call_find(PeerID.from_base58("QmdaK4LUeQaKhqSFPRu9N7MvXUEWDxWwtCvPrS444tCgd1"), [key])
+
+                nested, first, second = DHTID.generate(), [1.5, "x"], "abacaba"
+                assert all(await me.call_store(p2p1.peer_id, [nested], [MSGPackSerializer.dumps(first)], [expiration], subkeys=["foo"]))
+                assert all(await me.call_store(p2p1.peer_id, [nested], [MSGPackSerializer.dumps(second)], [expiration + 5], subkeys=["bar"]))
+                (dictionary, latest), _ = (await me.call_find(p2p1.peer_id, [nested]))[nested]
+                assert isinstance(dictionary, DictionaryDHTValue) and latest == expiration + 5
+                assert dictionary.data["foo"] == (MSGPackSerializer.dumps(first), expiration)
+                assert dictionary.data["bar"] == (MSGPackSerializer.dumps(second), expiration + 5)
+
+                # a client asks but is never listed; a full node is
+                await asyncio.sleep(0.2)
+                assert (me.node_id in peer1.routing_table) == (not client_mode)
+                await p2p.shutdown()
+        finally:
+            await p2p2.shutdown()
+            await p2p1.shutdown()
+
+    asyncio.run(asyncio.wait_for(main(), 90))
+
+
+def test_dht_refuses_to_start_without_a_reachable_bootstrap_peer():
+    """Reference case test_startup_error (tests/test_dht.py:24-35): the error of the background node reaches the caller
+    of ``DHT(start=True)``, and the next instance starts normally."""
+    import socket
+
+    from hivemind_b200 import DHT
+    from hivemind_b200.p2p import P2PDaemonError
+
+    with socket.socket() as probe:  # a port that nobody listens on
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    with pytest.raises(P2PDaemonError, match=r"(?i)failed to connect to bootstrap peers"):
+        DHT(initial_peers=[f"/ip4/127.0.0.1/tcp/{port}/p2p/QmdaK4LUeQaKhqSFPRu9N7MvXUEWDxWwtCvPrS444tCgd1"], start=True)
+    dht = DHT(start=True)
+    try:
+        assert dht.store("still", "works", get_dht_time() + 30) and dht.get("still").value == "works"
+    finally:
+        dht.shutdown()
