@@ -247,6 +247,9 @@ async def attach_event_on_finished(iterable: AsyncIterable[T], event: asyncio.Ev
 class _AsyncContextWrapper(AbstractAsyncContextManager):
     """Enter a blocking context manager in a worker thread so that the event loop stays responsive."""
 
+    # every coroutine that waits for a blocking context holds one worker thread, and a waiter that never gets a thread
+    # can never be woken; the pool therefore has to be far larger than the default (cpu count + 4)
+    MAX_WAITERS = 4096
     EXECUTOR_PID = None
     CONTEXT_EXECUTOR = None
     EXECUTOR_LOCK = threading.Lock()
@@ -259,7 +262,7 @@ class _AsyncContextWrapper(AbstractAsyncContextManager):
         if os.getpid() != cls.EXECUTOR_PID:
             with cls.EXECUTOR_LOCK:
                 if os.getpid() != cls.EXECUTOR_PID:
-                    cls.CONTEXT_EXECUTOR = ThreadPoolExecutor(max_workers=float("inf") if False else 1024)
+                    cls.CONTEXT_EXECUTOR = ThreadPoolExecutor(max_workers=cls.MAX_WAITERS)
                     cls.EXECUTOR_PID = os.getpid()
         return cls.CONTEXT_EXECUTOR
 

@@ -2,6 +2,7 @@
 multiaddr (modelled on the reference's tests/test_util_modules.py and tests/test_multiaddr.py)."""
 import asyncio
 import concurrent.futures
+import os
 import threading
 import time
 
@@ -164,6 +165,41 @@ def test_asyncio_helpers():
         async with enter_asynchronously(lock):
             assert lock.locked()
         assert not lock.locked()
+
+    asyncio.new_event_loop().run_until_complete(scenario())
+
+
+def test_enter_asynchronously_survives_a_flood_of_waiters():
+    """Far more coroutines than a default thread pool has workers queue on two locks taken in nested order; with too
+    few worker threads the holder of the first lock could never get a thread for the second and all would stall
+    (the case of hivemind tests/test_util_modules.py::test_async_context_flooding)."""
+    outer, inner = threading.Lock(), threading.Lock()
+    entered = []
+
+    async def visitor(index):
+        async with enter_asynchronously(outer):
+            await asyncio.sleep(0)
+            async with enter_asynchronously(inner):
+                assert outer.locked() and inner.locked()
+                entered.append(index)
+                await asyncio.sleep(0)
+
+    async def scenario():
+        n_visitors = 8 * (os.cpu_count() or 1) + 200
+        ticks = 0
+
+        async def heartbeat():
+            nonlocal ticks
+            while True:
+                ticks += 1
+                await asyncio.sleep(0.005)
+
+        beat = asyncio.create_task(heartbeat())
+        await asyncio.wait_for(asyncio.gather(*(visitor(i) for i in range(n_visitors))), timeout=60)
+        beat.cancel()
+        assert sorted(entered) == list(range(n_visitors))
+        assert ticks > 1, "the event loop was blocked while the visitors waited for the locks"
+        assert not outer.locked() and not inner.locked()
 
     asyncio.new_event_loop().run_until_complete(scenario())
 
