@@ -3,6 +3,11 @@
 ``num_peers`` nodes (threads of this process, each with its own transport daemon) form a DHT; ``num_threads``
 workers repeatedly store batches of random keys through random "store peers" and read them back through random
 "get peers", while a fraction of the peers is shut down along the way. Prints one JSON line.
+
+``--num_experts N`` switches to the workload whose numbers the reference publishes (docs/user/benchmarks.md:60-90):
+one peer declares ``N`` random expert uids of a three-level grid in batches of ``--expert_batch_size``, another peer
+then looks all of them up in batches of the same size; nobody is shut down and the getter does not cache. The line
+reports seconds per stored (key, subkey) record and per looked-up uid, the way the reference's console output does.
 """
 import argparse
 import asyncio
@@ -106,6 +111,105 @@ async def benchmark_dht(num_peers, initial_peers, random_seed, num_threads, tota
         peer.shutdown()
 
 
+def _host_peers(count, bootstrap, initial_peers, wait_timeout, seed, report, stop):
+    """Body of a helper process: runs ``count`` DHT peers until ``stop`` is set, reports their addresses."""
+    random.seed(seed)
+    known = list(bootstrap)
+    peers = []
+    for _ in range(count):
+        peer = DHT(initial_peers=random.sample(known, min(initial_peers, len(known))), start=True,
+                   wait_timeout=wait_timeout, cache_locally=False, cache_nearest=0)
+        peers.append(peer)
+        known.append(str(peer.get_visible_maddrs()[0]))
+    report.put(count)
+    stop.wait()
+    alive = sum(p.is_alive() for p in peers)
+    for peer in peers:
+        peer.shutdown()
+    report.put(alive)
+
+
+async def benchmark_experts(num_peers, initial_peers, random_seed, num_experts, expert_batch_size, wait_timeout,
+                            expiration, num_processes):
+    """One peer declares ``num_experts`` uids, another looks them up; the other peers only route and hold records.
+
+    The peers of one process share an interpreter lock, so ``num_processes`` helper processes host equal shares of the
+    swarm (the reference forks one process per peer); the declaring and the reading peer live in this process.
+    """
+    import multiprocessing as mp
+
+    from hivemind_b200.moe.server.dht_handler import declare_experts, get_experts
+
+    random.seed(random_seed)
+    loop = asyncio.get_event_loop()
+    in_thread = lambda fn, *a, **kw: loop.run_in_executor(None, lambda: fn(*a, **kw))  # noqa: E731
+    created = time.perf_counter()
+    local_count = num_peers if num_processes <= 0 else max(2, min(initial_peers, num_peers))
+    peers = []
+    for _ in range(local_count):
+        neighbors = [str(m) for p in random.sample(peers, min(initial_peers, len(peers))) for m in p.get_visible_maddrs()]
+        peers.append(await in_thread(DHT, initial_peers=neighbors, start=True, wait_timeout=wait_timeout,
+                                     cache_locally=False, cache_nearest=0))
+    helpers = []
+    if num_processes > 0:
+        ctx = mp.get_context("spawn")
+        bootstrap = [str(p.get_visible_maddrs()[0]) for p in peers]
+        remaining = num_peers - local_count
+        for index in range(num_processes):
+            share = remaining // num_processes + (index < remaining % num_processes)
+            if share == 0:
+                continue
+            report, stop = ctx.Queue(), ctx.Event()
+            process = ctx.Process(target=_host_peers, daemon=True,
+                                  args=(share, bootstrap, initial_peers, wait_timeout, random_seed + 1 + index, report, stop))
+            process.start()
+            helpers.append((process, report, stop, share))
+        for _, report, _, share in helpers:
+            assert await in_thread(report.get) == share
+    creation_seconds = time.perf_counter() - created
+    store_peer, get_peer = random.sample(peers, 2)
+    uids = sorted({f"expert.{random.randint(0, 999)}.{random.randint(0, 999)}.{random.randint(0, 999)}"
+                   for _ in range(num_experts)})
+    random.shuffle(uids)
+    batches = [uids[i: i + expert_batch_size] for i in range(0, len(uids), expert_batch_size)]
+
+    records = records_ok = 0
+    store_seconds = 0.0
+    for batch in batches:
+        started = time.perf_counter()
+        outcome = await in_thread(declare_experts, store_peer, batch, get_dht_time() + expiration)
+        store_seconds += time.perf_counter() - started
+        records += len(outcome)
+        records_ok += sum(map(bool, outcome.values()))
+
+    found = 0
+    get_seconds = 0.0
+    for batch in batches:
+        started = time.perf_counter()
+        experts = await in_thread(get_experts, get_peer, batch)
+        get_seconds += time.perf_counter() - started
+        found += sum(e is not None and e.uid == uid for e, uid in zip(experts, batch))
+
+    alive = sum(p.is_alive() for p in peers)
+    for _, _, stop, _ in helpers:
+        stop.set()
+    for process, report, _, _ in helpers:
+        alive += await in_thread(report.get)
+        process.join(timeout=30)
+    print(json.dumps({"benchmark": "dht_experts", "peers": num_peers, "processes": 1 + len(helpers),
+                      "peers_created_per_second": num_peers / creation_seconds,
+                      "unique_uids": len(uids), "stored_records": records, "store_success_rate": records_ok / max(records, 1),
+                      "mean_store_seconds_per_record": store_seconds / max(records, 1), "store_seconds": store_seconds,
+                      "get_success_rate": found / max(len(uids), 1),
+                      "mean_get_seconds_per_uid": get_seconds / max(len(uids), 1), "get_seconds": get_seconds,
+                      "node_survival_rate": alive / num_peers,
+                      "reference_published": {"peers": 1024, "mean_store_seconds_per_record": 0.01487,
+                                              "mean_get_seconds_per_uid": 0.00664, "peers_created_per_second": 9.74}}),
+          flush=True)
+    for peer in peers:
+        peer.shutdown()
+
+
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
     parser.add_argument("--num_peers", type=int, default=16)
@@ -122,7 +226,17 @@ if __name__ == "__main__":
     parser.add_argument("--latest", type=bool, default=True)
     parser.add_argument("--failure_rate", type=float, default=0.1)
     parser.add_argument("--increase_file_limit", action="store_true")
+    parser.add_argument("--num_experts", type=int, default=0, help="> 0: the declare / get experts workload")
+    parser.add_argument("--expert_batch_size", type=int, default=64)
+    parser.add_argument("--num_processes", type=int, default=0,
+                        help="helper processes that host the peers of the expert workload (0: all in this process)")
     args = vars(parser.parse_args())
     if args.pop("increase_file_limit"):
         increase_file_limit()
-    asyncio.run(benchmark_dht(**args))
+    if args["num_experts"] > 0:
+        asyncio.run(benchmark_experts(args["num_peers"], args["initial_peers"], args["random_seed"], args["num_experts"],
+                                      args["expert_batch_size"], args["wait_timeout"], args["expiration"],
+                                      args["num_processes"]))
+    else:
+        args.pop("num_experts"), args.pop("expert_batch_size"), args.pop("num_processes")
+        asyncio.run(benchmark_dht(**args))

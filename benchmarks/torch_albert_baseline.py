@@ -9,9 +9,7 @@ device like ``bench.py`` times its own arm.
 """
 from __future__ import annotations
 
-import math
-import os
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist

@@ -15,11 +15,9 @@ from __future__ import annotations
 
 import asyncio
 import contextlib
-import hashlib
 import os
 import random
 import threading
-import weakref
 from typing import Any, AsyncIterator, Dict, Optional, Sequence, Tuple, Union
 
 import numpy as np
@@ -38,7 +36,7 @@ from hivemind_b200.dht import DHT, DHTID
 from hivemind_b200.p2p import P2P, P2PContext, P2PDaemonError, P2PHandlerError, PeerID, ServicerBase
 from hivemind_b200.p2p.control import DispatchFailure
 from hivemind_b200.proto import averaging_pb2
-from hivemind_b200.utils import MPFuture, MSGPackSerializer, TensorDescriptor, get_logger
+from hivemind_b200.utils import MPFuture, MSGPackSerializer, get_logger
 from hivemind_b200.utils.asyncio import (LoopThread, achain, aiter_with_timeout, anext, as_aiter, azip,
                                          enter_asynchronously)
 from hivemind_b200.utils.timed_storage import DHTExpiration, ValueWithExpiration, get_dht_time

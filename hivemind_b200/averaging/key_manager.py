@@ -16,7 +16,7 @@ import numpy as np
 from hivemind_b200.averaging.group_info import GroupInfo
 from hivemind_b200.dht import DHT
 from hivemind_b200.p2p import PeerID
-from hivemind_b200.utils import DHTExpiration, ValueWithExpiration, get_dht_time, get_logger
+from hivemind_b200.utils import DHTExpiration, get_logger
 
 GroupKey = str
 GROUP_PATTERN = re.compile("^(([^.])+)[.]0b[01]*$")  # e.g. bert_exp4_averaging.0b01001101

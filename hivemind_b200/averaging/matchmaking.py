@@ -31,7 +31,6 @@ from hivemind_b200.p2p import P2P, P2PContext, P2PDaemonError, P2PHandlerError, 
 from hivemind_b200.proto import averaging_pb2
 from hivemind_b200.utils import DHTExpiration, get_dht_time, get_logger
 from hivemind_b200.utils.asyncio import anext, cancel_and_wait
-from hivemind_b200.utils.timed_storage import MAX_DHT_TIME_DISCREPANCY_SECONDS
 
 logger = get_logger(__name__)
 _Reply = averaging_pb2.MessageFromLeader

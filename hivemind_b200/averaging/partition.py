@@ -11,7 +11,7 @@ from __future__ import annotations
 import asyncio
 from collections import deque
 from dataclasses import dataclass
-from typing import AsyncIterable, AsyncIterator, Deque, List, Optional, Sequence, Tuple, TypeVar, Union
+from typing import AsyncIterable, AsyncIterator, Deque, List, Optional, Sequence, Tuple, TypeVar
 
 import numpy as np
 import torch

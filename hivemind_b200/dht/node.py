@@ -17,7 +17,7 @@ import asyncio
 import os
 import random
 from collections import defaultdict
-from typing import Any, Awaitable, Collection, Dict, Iterable, List, Optional, Sequence, Set, Tuple, Type, Union
+from typing import Awaitable, Collection, Dict, Iterable, List, Optional, Sequence, Set, Tuple, Type, Union
 
 from hivemind_b200.dht.crypto import DHTRecord, RecordValidatorBase
 from hivemind_b200.dht.protocol import DHTProtocol
@@ -25,7 +25,7 @@ from hivemind_b200.dht.routing import BinaryDHTValue, DHTID, DHTKey, DHTValue, S
 from hivemind_b200.dht.storage import DictionaryDHTValue
 from hivemind_b200.dht.traverse import traverse_dht
 from hivemind_b200.p2p import P2P, PeerID
-from hivemind_b200.utils import MSGPackSerializer, SerializerBase, get_logger
+from hivemind_b200.utils import SerializerBase, get_logger
 from hivemind_b200.utils.asyncio import spawn
 from hivemind_b200.utils.auth import AuthorizerBase
 from hivemind_b200.utils.multiaddr import Multiaddr
@@ -345,6 +345,8 @@ class DHTNode:
 
     # ---------------------------------------------------------------------------------------------- asking peers
     def _without_banned(self, peers: Dict[DHTID, PeerID]) -> Dict[DHTID, PeerID]:
+        if not self.blacklist.ban_counter:  # nobody has ever failed (or everybody has answered since)
+            return peers
         return {node: peer for node, peer in peers.items() if peer not in self.blacklist}
 
     def _routing_neighbours(self, key_ids: Iterable[DHTID], count: int) -> Dict[DHTID, PeerID]:

@@ -49,6 +49,7 @@ class DHTProtocol(ServicerBase):
 
     serializer = MSGPackSerializer
     RESERVED_SUBKEYS = IS_REGULAR_VALUE, IS_DICTIONARY = serializer.dumps(None), b""
+    MAX_KNOWN_PAIRS = 2 ** 16  # (node id, peer id) objects kept for reuse when find replies are decoded
 
     def __init__(self, *, _initialized_with_create: bool = False):
         if not _initialized_with_create:
@@ -66,6 +67,7 @@ class DHTProtocol(ServicerBase):
         self.client_mode, self.record_validator, self.authorizer = client_mode, record_validator, authorizer
         self.storage, self.cache = DHTLocalStorage(), DHTLocalStorage(maxsize=cache_size)
         self.routing_table = RoutingTable(node_id, bucket_size, depth_modulo)
+        self._known_pairs: Dict[bytes, Tuple[DHTID, PeerID]] = {}
         self.rpc_semaphore = asyncio.Semaphore(2 ** 15 if parallel_rpc is None else parallel_rpc)
         # clients are never routed to, so they announce no id and serve no requests
         self.node_info = dht_pb2.NodeInfo() if client_mode else dht_pb2.NodeInfo(node_id=node_id.to_bytes())
@@ -212,13 +214,22 @@ class DHTProtocol(ServicerBase):
         outcome: FindOutcome = {}
         for key_id, result in zip(keys, reply.results):
             try:
-                neighbours = {DHTID.from_bytes(node): PeerID.from_base58(address.decode("ascii"))
-                              for node, address in zip(result.nearest_node_ids, result.nearest_peer_ids)}
+                neighbours = dict(map(self._node_and_peer, result.nearest_node_ids, result.nearest_peer_ids))
                 outcome[key_id] = self._decode_find_result(key_id, result), neighbours
             except Exception as e:
                 logger.debug(f"undecodable find result from {peer}: {e!r}")
                 return None
         return outcome
+
+    def _node_and_peer(self, node_bytes: bytes, peer_bytes: bytes) -> Tuple[DHTID, PeerID]:
+        """(node id, peer id) objects for a routing entry of a reply. A swarm of n peers mentions the same n pairs
+        over and over (up to ``bucket_size`` per key and reply), so the objects are made once and shared."""
+        pair = self._known_pairs.get(node_bytes)
+        if pair is None or pair[1].to_bytes() != peer_bytes:
+            if len(self._known_pairs) >= self.MAX_KNOWN_PAIRS:
+                self._known_pairs.clear()
+            pair = self._known_pairs[node_bytes] = (DHTID.from_bytes(node_bytes), PeerID(peer_bytes))
+        return pair
 
     def _decode_find_result(self, key_id: DHTID, result: dht_pb2.FindResult
                             ) -> Optional[ValueWithExpiration[StoredPayload]]:
@@ -250,7 +261,7 @@ class DHTProtocol(ServicerBase):
                                             expiration_time=held.expiration_time)
             for node, address in self.routing_table.get_nearest_neighbors(key_id, k=self.bucket_size, exclude=sender):
                 result.nearest_node_ids.append(node.to_bytes())
-                result.nearest_peer_ids.append(address.to_base58().encode("ascii"))
+                result.nearest_peer_ids.append(address.to_bytes())
             results.append(result)
         return dht_pb2.FindResponse(results=results, peer=self.node_info)
 

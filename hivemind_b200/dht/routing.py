@@ -42,9 +42,9 @@ class DHTID(int):
         return cls(int(cls.HASH_FUNC(source).hexdigest(), 16))
 
     def xor_distance(self, other: Union["DHTID", Sequence["DHTID"]]) -> Union[int, List[int]]:
-        if isinstance(other, Iterable):
-            return [int(self) ^ int(o) for o in other]
-        return int(self) ^ int(other)
+        if isinstance(other, int):  # the common case, checked first: it is on the path of every routing decision
+            return int(self) ^ int(other)
+        return [int(self) ^ int(o) for o in other]
 
     @classmethod
     def longest_common_prefix_length(cls, *ids: "DHTID") -> int:
@@ -56,6 +56,8 @@ class DHTID(int):
 
     @classmethod
     def from_bytes(cls, raw: bytes, byteorder: str = "big", *, signed: bool = False) -> "DHTID":
+        if len(raw) <= cls.HASH_NBYTES and not signed:
+            return int.__new__(cls, int.from_bytes(raw, byteorder))  # cannot leave the id range: no check needed
         return DHTID(super().from_bytes(raw, byteorder=byteorder, signed=signed))
 
     def __repr__(self) -> str:

@@ -12,7 +12,6 @@ fp32 accumulation; bf16 copies of the weights are refreshed lazily when a parame
 """
 from __future__ import annotations
 
-import math
 import os
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple

@@ -28,7 +28,7 @@ from hivemind_b200.moe.client.expert import DUMMY, RemoteExpert, expert_backward
 from hivemind_b200.moe.client.remote_expert_worker import RemoteExpertWorker
 from hivemind_b200.moe.expert_uid import UID_DELIMITER
 from hivemind_b200.p2p.control import P2PDaemonError
-from hivemind_b200.utils import nested_flatten, nested_map, nested_pack
+from hivemind_b200.utils import nested_flatten, nested_pack
 from hivemind_b200.utils.logging import get_logger
 
 logger = get_logger(__name__)

@@ -9,7 +9,6 @@ Tensors are deserialised on the handler's loop, queued into the expert's ``TaskP
 """
 from __future__ import annotations
 
-import asyncio
 from typing import AsyncIterator, Dict, List, Optional, Sequence
 
 import torch

@@ -15,7 +15,7 @@ import time
 from abc import ABCMeta, abstractmethod
 from collections import deque
 from concurrent.futures import Future
-from typing import Any, Callable, Deque, List, NamedTuple, Optional, Sequence, Tuple
+from typing import Any, Callable, Deque, List, NamedTuple, Optional, Tuple
 
 import torch
 

@@ -21,7 +21,6 @@ import torch.nn.functional as F
 
 from hivemind_b200.ops import _lib
 from hivemind_b200.ops.gemm import EPI_BIAS, EPI_BIAS_GELU, EPI_NONE, _err_flag
-from hivemind_b200.ops.moe import TILE_ROWS
 
 LN_EPS = 1e-12
 

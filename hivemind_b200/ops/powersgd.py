@@ -5,7 +5,7 @@ Reference math: hivemind/optim/power_sgd_averager.py:150-183 and hivemind/utils/
 from __future__ import annotations
 
 import ctypes
-from typing import List, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

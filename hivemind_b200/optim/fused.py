@@ -10,7 +10,7 @@ checkpoints and peer-to-peer state downloads stay interchangeable. CPU tensors r
 """
 from __future__ import annotations
 
-from typing import Iterable, List, Optional, Tuple
+from typing import Iterable, List, Tuple
 
 import torch
 

@@ -17,7 +17,7 @@ import torch
 from hivemind_b200.averaging import DecentralizedAverager, StepControl
 from hivemind_b200.dht import DHT
 from hivemind_b200.ops import multi_tensor as mt
-from hivemind_b200.utils import DHTExpiration, get_dht_time, get_logger
+from hivemind_b200.utils import DHTExpiration, get_logger
 
 logger = get_logger(__name__)
 TGradientAverager = "GradientAverager"

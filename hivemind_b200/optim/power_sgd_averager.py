@@ -24,7 +24,7 @@ from hivemind_b200.averaging.allreduce import AveragingMode
 from hivemind_b200.averaging.group_info import GroupInfo
 from hivemind_b200.averaging.load_balancing import load_balance_peers
 from hivemind_b200.averaging.matchmaking import MatchmakingException
-from hivemind_b200.compression import CompressionInfo, NoCompression, TensorRole
+from hivemind_b200.compression import CompressionInfo, TensorRole
 from hivemind_b200.dht import DHT
 from hivemind_b200.ops import multi_tensor as mt
 from hivemind_b200.ops import powersgd as ps_ops

@@ -10,8 +10,7 @@ from __future__ import annotations
 import asyncio
 import os
 import struct
-import uuid
-from typing import Awaitable, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Awaitable, Callable, Dict, Optional, Sequence, Tuple
 
 from hivemind_b200.p2p.datastructures import PeerID, PeerInfo, StreamInfo
 from hivemind_b200.utils.logging import get_logger
@@ -98,6 +97,11 @@ async def read_frame(reader: asyncio.StreamReader) -> Tuple[int, _Reader]:
 
 def _peer_bytes(peer_id: PeerID) -> bytes:
     return peer_id.to_base58().encode("ascii")
+
+
+def _new_call_id() -> bytes:
+    """16 random bytes: call ids of different peers meet in one table inside the callee's daemon."""
+    return os.urandom(16)
 
 
 class DaemonClient:
@@ -303,17 +307,17 @@ class DaemonClient:
         return await fut
 
     async def add_unary_handler(self, proto: str, handler: UnaryHandler, balanced: bool = False) -> None:
-        call_id = uuid.uuid4().bytes
+        call_id = _new_call_id()
         await self._request(_Writer(P_ADD_UNARY_HANDLER).blob(call_id).blob(proto.encode()).u8(int(balanced)).finish(), call_id)
         self.unary_handlers[proto] = handler
 
     async def remove_unary_handler(self, proto: str) -> None:
-        call_id = uuid.uuid4().bytes
+        call_id = _new_call_id()
         await self._request(_Writer(P_REMOVE_UNARY_HANDLER).blob(call_id).blob(proto.encode()).finish(), call_id)
         self.unary_handlers.pop(proto, None)
 
     async def call_unary_handler(self, peer_id: PeerID, proto: str, data: bytes) -> bytes:
-        call_id = uuid.uuid4().bytes
+        call_id = _new_call_id()
         frame = _Writer(P_CALL_UNARY).blob(call_id).blob(_peer_bytes(peer_id)).blob(proto.encode()).blob(data).finish()
         try:
             return await self._request(frame, call_id)

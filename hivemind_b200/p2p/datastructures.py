@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import hashlib
 from dataclasses import dataclass
-from typing import Any, List, Sequence, Union
+from typing import Any, List, Optional, Sequence, Union
 
 from cryptography.hazmat.primitives import serialization
 
@@ -21,15 +21,32 @@ _MAX_INLINE_KEY_LENGTH = 42
 
 
 class PeerID:
+    """A peer's identity: the multihash bytes; the base58 text form is derived the first time somebody asks for it
+    (routing replies create thousands of these per second and almost never print them)."""
+
+    __slots__ = ("_bytes", "_text")
+
     def __init__(self, peer_id_bytes: bytes) -> None:
         self._bytes = bytes(peer_id_bytes)
-        self._b58_str = b58encode(self._bytes)
+        self._text: Optional[str] = None
+
+    @property
+    def _b58_str(self) -> str:
+        if self._text is None:
+            self._text = b58encode(self._bytes)
+        return self._text
 
     def to_bytes(self) -> bytes:
         return self._bytes
 
     def to_base58(self) -> str:
         return self._b58_str
+
+    def __getstate__(self):
+        return (self._bytes,)
+
+    def __setstate__(self, state):
+        (self._bytes,), self._text = state, None
 
     @property
     def xor_id(self) -> int:
@@ -63,7 +80,9 @@ class PeerID:
 
     @classmethod
     def from_base58(cls, b58_encoded: str) -> "PeerID":
-        return cls(b58decode(b58_encoded))
+        peer_id = cls(b58decode(b58_encoded))
+        peer_id._text = b58_encoded
+        return peer_id
 
     @classmethod
     def from_identity(cls, data: bytes) -> "PeerID":

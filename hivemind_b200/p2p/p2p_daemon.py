@@ -19,15 +19,14 @@ import tempfile
 import threading
 from contextlib import closing, suppress
 from dataclasses import dataclass
-from typing import Any, AsyncIterator, Awaitable, Callable, List, Optional, Sequence, Tuple, Type, TypeVar, Union
+from typing import AsyncIterator, Awaitable, Callable, List, Optional, Sequence, Tuple, Type, TypeVar, Union
 
 from cryptography.hazmat.primitives import serialization
 from cryptography.hazmat.primitives.asymmetric import rsa
 from google.protobuf.message import Message
 
 from hivemind_b200.ops import _build
-from hivemind_b200.p2p.control import (DEFAULT_MAX_MSG_SIZE, MAX_UNARY_PAYLOAD_SIZE, DaemonClient, P2PDaemonError,
-                                       P2PHandlerError)
+from hivemind_b200.p2p.control import DEFAULT_MAX_MSG_SIZE, DaemonClient, P2PDaemonError, P2PHandlerError
 from hivemind_b200.p2p.datastructures import PeerID, PeerInfo, StreamInfo
 from hivemind_b200.proto import crypto_pb2
 from hivemind_b200.utils.asyncio import as_aiter, asingle

@@ -14,7 +14,7 @@ than ``k_min`` live experts raises, and a token with no expert yields zeros (or 
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist

@@ -7,7 +7,7 @@ import os
 import threading
 from concurrent.futures import ThreadPoolExecutor
 from contextlib import AbstractAsyncContextManager, AbstractContextManager
-from typing import AsyncIterable, AsyncIterator, Awaitable, Callable, Coroutine, Iterable, Optional, Tuple, TypeVar, Union
+from typing import AsyncIterable, AsyncIterator, Awaitable, Callable, Coroutine, Iterable, Optional, Tuple, TypeVar
 
 from hivemind_b200.utils.logging import get_logger
 

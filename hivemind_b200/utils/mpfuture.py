@@ -10,7 +10,7 @@ from __future__ import annotations
 import asyncio
 import concurrent.futures as base
 import threading
-from typing import Any, Callable, Generic, Optional, TypeVar
+from typing import Generic, Optional, TypeVar
 
 ResultType = TypeVar("ResultType")
 

@@ -5,7 +5,7 @@ from ipaddress import ip_address
 from typing import List, Sequence
 
 from hivemind_b200.utils.logging import TextStyle, get_logger
-from hivemind_b200.utils.multiaddr import Multiaddr, protocols
+from hivemind_b200.utils.multiaddr import Multiaddr
 
 LOCALHOST = "127.0.0.1"
 logger = get_logger(__name__)

@@ -6,7 +6,7 @@
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass
-from typing import Any, Optional, Tuple
+from typing import Tuple
 
 import numpy as np
 import torch

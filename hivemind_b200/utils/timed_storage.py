@@ -112,6 +112,8 @@ class TimedStorage(Generic[KeyType, ValueType]):
         self._heap.clear()
 
     def __contains__(self, key: KeyType) -> bool:
+        if not self.data:
+            return False
         self.remove_outdated()
         return key in self.data
 

@@ -13,7 +13,7 @@ import torch
 
 from hivemind_b200.averaging.partition import (AllreduceException, BannedException, TensorPartContainer,
                                                TensorPartReducer)
-from hivemind_b200.compression import Float16Compression, NoCompression, deserialize_torch_tensor
+from hivemind_b200.compression import Float16Compression, deserialize_torch_tensor
 
 
 def _run(coro):

@@ -4,7 +4,6 @@ import asyncio
 from datetime import datetime, timedelta, timezone
 from typing import Optional
 
-import pytest
 
 from hivemind_b200.proto import dht_pb2
 from hivemind_b200.proto.auth_pb2 import AccessToken

@@ -4,9 +4,8 @@ import asyncio
 import pytest
 import torch
 
-from hivemind_b200.compression import (BlockwiseQuantization, CompressionInfo, Float16Compression, NoCompression,
-                                       PerTensorCompression, Quantile8BitQuantization, RoleAdaptiveCompression,
-                                       ScaledFloat16Compression, SizeAdaptiveCompression, TensorRole,
+from hivemind_b200.compression import (CompressionInfo, Float16Compression, NoCompression, PerTensorCompression,
+                                       RoleAdaptiveCompression, SizeAdaptiveCompression, TensorRole,
                                        Uniform8BitQuantization, combine_from_streaming, deserialize_tensor_stream,
                                        deserialize_torch_tensor, serialize_torch_tensor, split_for_streaming)
 from hivemind_b200.compression.quantization import dynamic_code_table

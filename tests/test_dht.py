@@ -15,7 +15,7 @@ from hivemind_b200.dht.traverse import simple_traverse_dht, traverse_dht
 from hivemind_b200.dht.validation import DHTRecord
 from hivemind_b200.p2p import PeerID
 from hivemind_b200.utils import MSGPackSerializer, get_dht_time
-from hivemind_b200.utils.timed_storage import TimedStorage, ValueWithExpiration
+from hivemind_b200.utils.timed_storage import TimedStorage
 
 
 def run(coro, timeout=120):

@@ -7,7 +7,6 @@ import pickle
 from typing import Dict
 
 import pydantic.v1 as pydantic
-import pytest
 
 from hivemind_b200.dht.crypto import RSASignatureValidator
 from hivemind_b200.dht.schema import BytesWithPublicKey, SchemaValidator

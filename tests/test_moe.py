@@ -6,7 +6,6 @@ test_connection_handler.py and the MoE parts of test_training.py.
 import asyncio
 import random
 import time
-from pathlib import Path
 
 import numpy as np
 import pytest
@@ -15,8 +14,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from hivemind_b200.dht import DHT
-from hivemind_b200.moe import (ModuleBackend, RemoteExpert, RemoteMixtureOfExperts, RemoteSwitchMixtureOfExperts, Server,
-                               background_server, declare_experts, get_experts, register_expert_class)
+from hivemind_b200.moe import (ModuleBackend, RemoteExpert, RemoteMixtureOfExperts, RemoteSwitchMixtureOfExperts,
+                               Server, background_server, declare_experts, get_experts)
 from hivemind_b200.moe.client.beam_search import MoEBeamSearcher
 from hivemind_b200.moe.client.expert import DUMMY, create_remote_experts
 from hivemind_b200.moe.client.moe import _RemoteCallMany

@@ -6,7 +6,6 @@ import os
 import threading
 import time
 
-import numpy as np
 import pytest
 import torch
 
