@@ -42,6 +42,12 @@ class SchemaValidator(RecordValidatorBase):
         for field in schema.__fields__.values():
             field.required = False  # a record carries one key at a time
 
+    def __setstate__(self, state: Dict[str, Any]) -> None:
+        # model classes are pickled by reference: an interpreter that has just imported them has the unadjusted ones
+        self.__dict__.update(state)
+        for schema in self._schemas:
+            self._patch_schema(schema)
+
     def validate(self, record: DHTRecord) -> bool:
         if record.key not in self._key_id_to_field_name:
             if not self._allow_extra_keys:

@@ -3,6 +3,7 @@
 Behaviours pinned by the reference in tests/test_dht_crypto.py, tests/test_dht_schema.py and
 tests/test_dht_validation.py, restated for this package's classes.
 """
+import dataclasses
 import pickle
 from typing import Dict
 
@@ -149,3 +150,39 @@ def test_unparseable_records_are_rejected_not_raised():
     from hivemind_b200.dht.routing import DHTID
     broken = DHTRecord(DHTID.generate(source="number").to_bytes(), b"", b"\xc1 not msgpack", get_dht_time() + 10)
     assert validator.validate(broken) is False
+
+
+class _Trainer(pydantic.BaseModel):
+    step: pydantic.StrictInt
+    scores: Dict[BytesWithPublicKey, pydantic.StrictFloat]
+
+
+def _validate_elsewhere(pickled_validator: bytes, records, answers) -> None:
+    validator = pickle.loads(pickled_validator)
+    answers.put([validator.validate(record) for record in records])
+
+
+def test_validators_work_after_travelling_to_another_process():
+    """A schema validator adjusts its model classes when it is built (every field optional, no extra fields); a fresh
+    interpreter imports the unadjusted classes, so the adjustment has to travel with the validator
+    (the case of hivemind tests/test_dht_schema.py::test_sending_validator_instance_between_processes)."""
+    import multiprocessing as mp
+
+    signer = RSASignatureValidator(RSAPrivateKey())
+    owner = signer.local_public_key
+    validator = CompositeValidator([SchemaValidator(_Trainer, allow_extra_keys=False, prefix="run"), signer])
+    records = [_record("run_step", 3), _record("run_step", "3"), _record("run_scores", 0.5, subkey=owner),
+               _record("run_scores", 0.5, subkey=b"nobody"), _record("other", 1)]
+    records = [dataclasses.replace(record, value=signer.sign_value(record)) if owner in record.subkey else record
+               for record in records]
+    here = [validator.validate(record) for record in records]
+    assert here == [True, False, True, False, False]
+
+    ctx = mp.get_context("spawn")
+    answers = ctx.Queue()
+    child = ctx.Process(target=_validate_elsewhere, args=(pickle.dumps(validator), records, answers))
+    child.start()
+    try:
+        assert answers.get(timeout=120) == here
+    finally:
+        child.join(timeout=30)
