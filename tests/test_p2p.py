@@ -377,3 +377,128 @@ def test_removed_handlers_stop_answering():
         await server.shutdown()
 
     run(main())
+
+
+def _serve_in_child(addresses, stop) -> None:
+    """Body of a child process: one peer with a unary and a binary stream handler, until ``stop`` is set."""
+    async def main():
+        server = await P2P.create()
+
+        async def double(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+            return test_pb2.TestResponse(number=2 * request.number)
+
+        async def upper(info, reader, writer):
+            await P2P.send_raw_data((await P2P.receive_raw_data(reader)).upper(), writer)
+
+        await server.add_protobuf_handler("double", double, test_pb2.TestRequest)
+        await server.add_binary_stream_handler("upper", upper)
+        addresses.put(([str(m) for m in await server.get_visible_maddrs()], server.peer_id.to_base58()))
+        while not stop.is_set():
+            await asyncio.sleep(0.05)
+        await server.shutdown()
+
+    asyncio.new_event_loop().run_until_complete(main())
+
+
+def test_calls_between_processes_and_a_peer_that_disappears():
+    """Reference cases test_call_peer_different_processes / test_error_closes_connection (tests/test_p2p_daemon.py):
+    handlers in another process answer; once that process is gone (killed, so it says no goodbye) a call ends in an
+    error within its time limit instead of hanging, and the caller's own daemon keeps serving other peers."""
+    import multiprocessing as mp
+    import os
+    import signal
+
+    ctx = mp.get_context("spawn")
+    addresses, stop = ctx.Queue(), ctx.Event()
+    child = ctx.Process(target=_serve_in_child, args=(addresses, stop), daemon=True)
+    child.start()
+    maddrs, peer_text = addresses.get(timeout=120)
+    remote = PeerID.from_base58(peer_text)
+
+    async def main():
+        client = await P2P.create(initial_peers=maddrs)
+        out = await client.call_protobuf_handler(remote, "double", test_pb2.TestRequest(number=21), test_pb2.TestResponse)
+        assert out.number == 42
+        _, reader, writer = await client.call_binary_stream_handler(remote, "upper")
+        await P2P.send_raw_data(b"between processes", writer)
+        assert await P2P.receive_raw_data(reader) == b"BETWEEN PROCESSES"
+        writer.close()
+
+        os.kill(child.pid, signal.SIGKILL)  # the exact process started above
+        child.join(timeout=30)
+        with pytest.raises((P2PHandlerError, P2PDaemonError, asyncio.TimeoutError, ConnectionError)):
+            await asyncio.wait_for(client.call_protobuf_handler(remote, "double", test_pb2.TestRequest(number=1),
+                                                                test_pb2.TestResponse), timeout=15)
+
+        bystander = await P2P.create(initial_peers=await client.get_visible_maddrs())
+
+        async def hello(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+            return test_pb2.TestResponse(number=request.number + 1)
+
+        await client.add_protobuf_handler("hello", hello, test_pb2.TestRequest)
+        out = await bystander.call_protobuf_handler(client.peer_id, "hello", test_pb2.TestRequest(number=1),
+                                                    test_pb2.TestResponse)
+        assert out.number == 2
+        await bystander.shutdown()
+        await client.shutdown()
+
+    try:
+        run(main())
+    finally:
+        stop.set()
+        if child.is_alive():
+            child.join(timeout=10)
+
+
+def test_handlers_on_different_replicas_and_a_replica_that_leaves():
+    """Reference cases test_handlers_on_different_replicas and test_daemon_replica_does_not_affect_primary: each
+    replica of one daemon serves the handlers that it registered; shutting a replica down removes its handlers only."""
+    async def main():
+        primary = await P2P.create()
+        replica = await P2P.replicate(primary.daemon_listen_maddr)
+        client = await P2P.create(initial_peers=await primary.get_visible_maddrs())
+
+        def answer(offset):
+            async def handler(request: test_pb2.TestRequest, context: P2PContext) -> test_pb2.TestResponse:
+                return test_pb2.TestResponse(number=request.number + offset)
+            return handler
+
+        async def echo(tag):
+            async def handler(info, reader, writer):
+                await P2P.send_raw_data(tag + await P2P.receive_raw_data(reader), writer)
+            return handler
+
+        await primary.add_protobuf_handler("plus_one", answer(1), test_pb2.TestRequest)
+        await replica.add_protobuf_handler("plus_ten", answer(10), test_pb2.TestRequest)
+        await primary.add_binary_stream_handler("tag_p", await echo(b"p:"))
+        await replica.add_binary_stream_handler("tag_r", await echo(b"r:"))
+
+        async def call(name):
+            return (await client.call_protobuf_handler(primary.peer_id, name, test_pb2.TestRequest(number=1),
+                                                       test_pb2.TestResponse)).number
+
+        async def stream(name):
+            _, reader, writer = await client.call_binary_stream_handler(primary.peer_id, name)
+            await P2P.send_raw_data(b"x", writer)
+            try:
+                return await P2P.receive_raw_data(reader)
+            finally:
+                writer.close()
+
+        assert await call("plus_one") == 2 and await call("plus_ten") == 11
+        assert await stream("tag_p") == b"p:x" and await stream("tag_r") == b"r:x"
+
+        await replica.shutdown()
+        assert primary.is_alive
+        assert await call("plus_one") == 2 and await stream("tag_p") == b"p:x"
+        with pytest.raises((P2PHandlerError, P2PDaemonError)):
+            await call("plus_ten")
+        with pytest.raises((P2PHandlerError, P2PDaemonError, asyncio.IncompleteReadError, ConnectionError)):
+            await stream("tag_r")
+        # the name is free again for whoever is still there
+        await primary.add_protobuf_handler("plus_ten", answer(100), test_pb2.TestRequest)
+        assert await call("plus_ten") == 101
+        await client.shutdown()
+        await primary.shutdown()
+
+    run(main())
