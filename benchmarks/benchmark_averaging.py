@@ -67,14 +67,15 @@ def benchmark_swarm(num_peers, target_group_size, num_rounds, min_matchmaking_ti
         with lock:
             to_close.extend([averager, dht])
         for step in range(num_rounds):
+            reason = ""
             try:
                 success = averager.step(timeout=round_timeout) is not None
-            except Exception:
-                success = False
+            except Exception as e:
+                success, reason = False, f" ({e!r})"
             with lock:
                 stats["ok"] += int(success)
                 stats["total"] += 1
-            logger.info(f"Averager {index}: {'finished' if success else 'failed'} step #{step}")
+            logger.info(f"Averager {index}: {'finished' if success else 'failed'} step #{step}{reason}")
 
     threads = []
     for i in range(num_peers):

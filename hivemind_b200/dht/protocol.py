@@ -212,9 +212,15 @@ class DHTProtocol(ServicerBase):
             logger.debug(f"{peer} answered {len(reply.results)} of {len(keys)} keys; the reply is ignored")
             return None
         outcome: FindOutcome = {}
+        known_pairs = self._known_pairs
         for key_id, result in zip(keys, reply.results):
             try:
-                neighbours = dict(map(self._node_and_peer, result.nearest_node_ids, result.nearest_peer_ids))
+                neighbours = {}
+                for node_bytes, peer_bytes in zip(result.nearest_node_ids, result.nearest_peer_ids):
+                    pair = known_pairs.get(node_bytes)
+                    if pair is None or pair[1].to_bytes() != peer_bytes:
+                        pair = self._node_and_peer(node_bytes, peer_bytes)
+                    neighbours[pair[0]] = pair[1]
                 outcome[key_id] = self._decode_find_result(key_id, result), neighbours
             except Exception as e:
                 logger.debug(f"undecodable find result from {peer}: {e!r}")

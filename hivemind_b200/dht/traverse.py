@@ -78,8 +78,10 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
     search_finished = asyncio.Event()
     wake = asyncio.Event()
 
+    # ids are ints: ``a ^ b`` is the XOR metric without a Python-level call, which matters in these inner loops
     for q in queries:
-        cands = [(q.xor_distance(n), n) for n in initial_nodes if n not in visited[q]]
+        already = visited[q]
+        cands = [(q ^ n, n) for n in initial_nodes if n not in already]
         heapq.heapify(cands)
         candidates[q] = cands
         best = [(-d, n) for d, n in heapq.nsmallest(beam_size, cands)]
@@ -129,8 +131,8 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
                 continue
             _, peer = heapq.heappop(candidates[q])
             # piggy-back other queries that have not asked this peer yet, nearest-first
-            extra = sorted((o for o in unfinished if o != q and peer not in visited[o]),
-                           key=lambda o: o.xor_distance(peer))[:max(0, queries_per_call - 1)]
+            extra = heapq.nsmallest(max(0, queries_per_call - 1),
+                                    (o for o in unfinished if o != q and peer not in visited[o]), key=peer.__xor__)
             batch = [q] + extra
             for o in batch:
                 visited[o].add(peer)
@@ -146,16 +148,18 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
                 if o not in unfinished:
                     continue
                 neighbors, should_stop = response.get(o, ((), False))
+                seen, best, frontier = known[o], nearest[o], candidates[o]
                 for n in neighbors:
-                    if n in known[o]:
+                    if n in seen:
                         continue
-                    known[o].add(n)
-                    d = o.xor_distance(n)
-                    if d <= upper_bound(o) or len(nearest[o]) < beam_size:
-                        heapq.heappush(candidates[o], (d, n))
-                        heapq.heappush(nearest[o], (-d, n))
-                        if len(nearest[o]) > beam_size:
-                            heapq.heappop(nearest[o])
+                    seen.add(n)
+                    d = o ^ n
+                    if len(best) < beam_size:
+                        heapq.heappush(frontier, (d, n))
+                        heapq.heappush(best, (-d, n))
+                    elif d <= -best[0][0]:
+                        heapq.heappush(frontier, (d, n))
+                        heapq.heappushpop(best, (-d, n))
                 if should_stop:
                     finish(o)
             wake.set()
