@@ -21,6 +21,10 @@
 // Call sites served: the expert FFN of hivemind/moe/server/layers/common.py:17-30, the transformer
 // blocks of the ALBERT / GPT-2 shaped models, and PowerSGD's P = M Q, Q = M^T P
 // (hivemind/optim/power_sgd_averager.py:158-170).
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
 #include "tc_ptx.cuh"
 
 namespace {
@@ -739,9 +743,46 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// A tensor map is a pure function of (address, element type, extents, pitch, box, swizzle), and a training step asks
+// for the same few dozen combinations over and over (weights, activations and gradients keep their addresses in the
+// caching allocator), so encoded maps are kept and looked up instead of being encoded by the driver for every launch.
+struct MapKey {
+  const void* base;
+  long long rows, cols, ld;
+  int elem_bytes, box_cols, box_rows, flags;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && elem_bytes == o.elem_bytes &&
+           box_cols == o.box_cols && box_rows == o.box_rows && flags == o.flags;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    unsigned long long h = 1469598103934665603ull;
+    auto mix = [&h](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
+    mix((unsigned long long)reinterpret_cast<uintptr_t>(k.base));
+    mix((unsigned long long)k.rows); mix((unsigned long long)k.cols); mix((unsigned long long)k.ld);
+    mix(((unsigned long long)(unsigned)k.elem_bytes << 32) | (unsigned)k.box_cols);
+    mix(((unsigned long long)(unsigned)k.box_rows << 32) | (unsigned)k.flags);
+    return (size_t)h;
+  }
+};
+constexpr size_t MAX_CACHED_MAPS = 8192;
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
 // 2-D map over a row-major matrix [rows][cols] with leading dimension ld (elements); box = box_cols x box_rows.
 int make_map(CUtensorMap* map, const void* base, int elem_bytes, bool is_f32, long long rows, long long cols,
              long long ld, int box_cols, int box_rows, bool atom32 = false) {
+  const MapKey key{base, rows, cols, ld, elem_bytes, box_cols, box_rows, (is_f32 ? 1 : 0) | (atom32 ? 2 : 0)};
+  static const bool use_cache = [] {  // HIVEMIND_B200_MAP_CACHE=0 encodes every map afresh (for comparison)
+    const char* v = std::getenv("HIVEMIND_B200_MAP_CACHE");
+    return !(v && v[0] == '0');
+  }();
+  if (use_cache) {
+    std::lock_guard<std::mutex> guard(g_map_mutex);
+    auto hit = g_map_cache.find(key);
+    if (hit != g_map_cache.end()) { *map = hit->second; return 0; }
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -10;
   ensure_context_on_this_thread();
@@ -754,7 +795,12 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, bool is_f32, lo
                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  if (r != CUDA_SUCCESS) return -12;
+  if (!use_cache) return 0;
+  std::lock_guard<std::mutex> guard(g_map_mutex);
+  if (g_map_cache.size() >= MAX_CACHED_MAPS) g_map_cache.clear();
+  g_map_cache.emplace(key, *map);
+  return 0;
 }
 
 struct GemmCall {
