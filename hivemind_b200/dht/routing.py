@@ -12,7 +12,6 @@ import hashlib
 import heapq
 import os
 import random
-from collections.abc import Iterable
 from typing import Any, Dict, List, Optional, Sequence, Set, Tuple, Union
 
 from hivemind_b200.p2p import PeerID

@@ -1,222 +1,228 @@
+"""``Multiaddr``: an immutable, self-describing network address such as ``/ip4/127.0.0.1/tcp/4001/p2p/Qm...``.
+
+The object holds the canonical binary form; text is produced on demand. It behaves like a read-only ordered mapping
+from protocols to values (``keys()`` / ``values()`` / ``items()``, ``addr["tcp"]``, ``"p2p" in addr``), and addresses
+nest: ``encapsulate`` appends components, ``decapsulate`` removes a suffix. Same interface as the class the reference
+vendors from py-multiaddr (hivemind/utils/multiaddr/multiaddr.py:76-258).
+"""
 from __future__ import annotations
 
-import ipaddress
-from dataclasses import dataclass
+import collections.abc
 from typing import Iterator, List, Optional, Tuple, Union
 
-from hivemind_b200.utils.base58 import b58decode, b58encode, varint_decode, varint_encode
-from hivemind_b200.utils.multiaddr import protocols as P
+from hivemind_b200.utils.multiaddr import exceptions, protocols
+from hivemind_b200.utils.multiaddr.protocols import Protocol, protocol_with_code, protocol_with_name  # noqa: F401
+from hivemind_b200.utils.multiaddr.transforms import bytes_iter, bytes_to_string, string_to_bytes
+
+__all__ = ("Multiaddr", "MultiAddrKeys", "MultiAddrItems", "MultiAddrValues")
 
 
-@dataclass(frozen=True)
-class Protocol:
-    code: int
-    name: str
-    size: int  # bits; 0 = no value; -1 = variable length
-    path: bool = False  # the value swallows the rest of the address (unix paths)
+def _decoded_components(raw: bytes) -> Iterator[Tuple[Protocol, Optional[str]]]:
+    for _, proto, codec, value in bytes_iter(raw):
+        if codec.SIZE == 0:
+            yield proto, None
+            continue
+        try:
+            yield proto, codec.to_string(proto, value)
+        except Exception as e:
+            raise exceptions.BinaryParseError(str(e), raw, proto.name, e) from e
 
 
-_BY_NAME = {name: Protocol(code, name, size, path=(name == "unix")) for code, name, size in P.TABLE}
-_BY_NAME["ipfs"] = _BY_NAME["p2p"]  # legacy alias
-_BY_CODE = {proto.code: proto for proto in _BY_NAME.values()}
+class _View:
+    """Shared behaviour of the three views: sized, comparable with any sequence of the same elements."""
+
+    def __init__(self, mapping: "Multiaddr"):
+        self._mapping = mapping
+
+    def __len__(self) -> int:
+        return sum(1 for _ in bytes_iter(self._mapping.to_bytes()))
+
+    def __eq__(self, other) -> bool:
+        try:
+            return list(self) == list(other)
+        except TypeError:
+            return NotImplemented
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({list(self)!r})"
 
 
-def protocol_with_name(name: str) -> Protocol:
-    try:
-        return _BY_NAME[name]
-    except KeyError:
-        raise ValueError(f"unknown multiaddr protocol {name!r}") from None
+class MultiAddrKeys(_View, collections.abc.KeysView, collections.abc.Sequence):
+    """The protocols of an address, in order; membership accepts a protocol object, a name or a code."""
+
+    def __contains__(self, proto) -> bool:
+        try:
+            wanted = protocols.REGISTRY.find(proto)
+        except (exceptions.ProtocolNotFoundError, TypeError):
+            return False
+        return any(present == wanted for present in self)
+
+    def __getitem__(self, index):
+        return list(self)[index]
+
+    def __iter__(self) -> Iterator[Protocol]:
+        for _, proto, _, _ in bytes_iter(self._mapping.to_bytes()):
+            yield proto
+
+    __hash__ = collections.abc.KeysView._hash
 
 
-def protocol_with_code(code: int) -> Protocol:
-    try:
-        return _BY_CODE[code]
-    except KeyError:
-        raise ValueError(f"unknown multiaddr protocol code {code:#x}") from None
+class MultiAddrItems(_View, collections.abc.ItemsView, collections.abc.Sequence):
+    """``(protocol, value text or None)`` pairs, in order."""
+
+    def __contains__(self, item) -> bool:
+        try:
+            proto, value = item
+            wanted = protocols.REGISTRY.find(proto)
+        except (exceptions.ProtocolNotFoundError, TypeError, ValueError):
+            return False
+        return any(present == wanted and held == value for present, held in self)
+
+    def __getitem__(self, index):
+        return list(self)[index]
+
+    def __iter__(self) -> Iterator[Tuple[Protocol, Optional[str]]]:
+        return _decoded_components(self._mapping.to_bytes())
 
 
-def _value_to_bytes(proto: Protocol, value: str) -> bytes:
-    if proto.name == "ip4":
-        return ipaddress.IPv4Address(value).packed
-    if proto.name == "ip6":
-        return ipaddress.IPv6Address(value).packed
-    if proto.name in ("tcp", "udp"):
-        port = int(value)
-        if not 0 <= port < 65536:
-            raise ValueError(f"port out of range: {value}")
-        return port.to_bytes(2, "big")
-    if proto.name == "p2p":
-        raw = b58decode(value)
-        return varint_encode(len(raw)) + raw
-    raw = value.encode("utf-8")
-    if proto.name == "unix" and not raw.startswith(b"/"):
-        raw = b"/" + raw
-    return varint_encode(len(raw)) + raw
+class MultiAddrValues(_View, collections.abc.ValuesView, collections.abc.Sequence):
+    """The values, in order (None for protocols without one)."""
+
+    def __contains__(self, value) -> bool:
+        return any(held == value for held in self)
+
+    def __getitem__(self, index):
+        return list(self)[index]
+
+    def __iter__(self) -> Iterator[Optional[str]]:
+        for _, value in _decoded_components(self._mapping.to_bytes()):
+            yield value
 
 
-def _value_from_bytes(proto: Protocol, buf: bytes, offset: int) -> Tuple[str, int]:
-    if proto.size > 0:
-        n = proto.size // 8
-        chunk = buf[offset:offset + n]
-        if len(chunk) != n:
-            raise ValueError("truncated multiaddr")
-        if proto.name == "ip4":
-            return str(ipaddress.IPv4Address(chunk)), offset + n
-        if proto.name == "ip6":
-            return str(ipaddress.IPv6Address(chunk)), offset + n
-        return str(int.from_bytes(chunk, "big")), offset + n
-    length, offset = varint_decode(buf, offset)
-    chunk = buf[offset:offset + length]
-    if len(chunk) != length:
-        raise ValueError("truncated multiaddr")
-    if proto.name == "p2p":
-        return b58encode(chunk), offset + length
-    return chunk.decode("utf-8"), offset + length
+class Multiaddr(collections.abc.Mapping):
+    """Build from text (``"/ip4/1.2.3.4/tcp/80"``), from the binary form, or from another ``Multiaddr``."""
 
+    __slots__ = ("_bytes",)
 
-class Multiaddr:
-    """Immutable multiaddr; construct from text (``"/ip4/.../tcp/..."``), bytes, or another Multiaddr."""
-
-    __slots__ = ("_parts",)
-
-    def __init__(self, addr: Union[str, bytes, "Multiaddr"] = ""):
+    def __init__(self, addr: Union[str, bytes, "Multiaddr"] = "/"):
         if isinstance(addr, Multiaddr):
-            self._parts = list(addr._parts)
-        elif isinstance(addr, (bytes, bytearray)):
-            self._parts = self._parse_bytes(bytes(addr))
+            self._bytes = addr._bytes
+        elif isinstance(addr, (bytes, bytearray, memoryview)):
+            raw = bytes(addr)
+            for _ in _decoded_components(raw):  # refuse what cannot be read back
+                pass
+            self._bytes = raw
         elif isinstance(addr, str):
-            self._parts = self._parse_text(addr)
+            self._bytes = string_to_bytes(addr) if addr.strip("/") else b""
         else:
-            raise TypeError(f"cannot build a Multiaddr from {type(addr)}")
+            raise TypeError(f"MultiAddr must be bytes, str or another MultiAddr instance, not {type(addr).__name__}")
 
-    @staticmethod
-    def _parse_text(text: str) -> List[Tuple[Protocol, Optional[str]]]:
-        text = text.rstrip("/") if text != "/" else ""
-        if not text:
-            return []
-        if not text.startswith("/"):
-            raise ValueError(f"a multiaddr must begin with '/': {text!r}")
-        items = text.split("/")[1:]
-        parts, i = [], 0
-        while i < len(items):
-            proto = protocol_with_name(items[i])
-            i += 1
-            if proto.size == 0:
-                parts.append((proto, None))
-                continue
-            if i >= len(items):
-                raise ValueError(f"protocol {proto.name} requires a value: {text!r}")
-            if proto.path:
-                value = "/" + "/".join(items[i:])
-                i = len(items)
-            else:
-                value = items[i]
-                i += 1
-            _value_to_bytes(proto, value)  # validates
-            parts.append((proto, value))
-        return parts
+    @classmethod
+    def _from_canonical_bytes(cls, raw: bytes) -> "Multiaddr":
+        result = cls.__new__(cls)
+        result._bytes = raw
+        return result
 
-    @staticmethod
-    def _parse_bytes(buf: bytes) -> List[Tuple[Protocol, Optional[str]]]:
-        parts, offset = [], 0
-        while offset < len(buf):
-            code, offset = varint_decode(buf, offset)
-            proto = protocol_with_code(code)
-            if proto.size == 0:
-                parts.append((proto, None))
-                continue
-            value, offset = _value_from_bytes(proto, buf, offset)
-            parts.append((proto, value))
-        return parts
+    @classmethod
+    def join(cls, *addrs: Union[str, bytes, "Multiaddr"]) -> "Multiaddr":
+        """One address made of the components of all the given ones, in order."""
+        return cls._from_canonical_bytes(b"".join(cls(addr).to_bytes() for addr in addrs))
 
+    # --- forms -----------------------------------------------------------------------------------------------
     def to_bytes(self) -> bytes:
-        out = bytearray()
-        for proto, value in self._parts:
-            out += varint_encode(proto.code)
-            if value is not None:
-                out += _value_to_bytes(proto, value)
-        return bytes(out)
+        return self._bytes
 
-    def __bytes__(self) -> bytes:
-        return self.to_bytes()
+    __bytes__ = to_bytes
 
     def __str__(self) -> str:
-        chunks = []
-        for proto, value in self._parts:
-            chunks.append("/" + proto.name)
-            if value is not None:
-                chunks.append(value if proto.path else "/" + value)
-        return "".join(chunks) or "/"
+        return bytes_to_string(self._bytes) or "/"
 
     def __repr__(self) -> str:
         return f"<Multiaddr {self}>"
 
     def __eq__(self, other) -> bool:
-        if isinstance(other, str):
+        if isinstance(other, str):  # convenience that the framework's own code relies on
             try:
                 other = Multiaddr(other)
-            except ValueError:
+            except exceptions.ParseError:
                 return False
-        return isinstance(other, Multiaddr) and str(self) == str(other)
+        if not isinstance(other, Multiaddr):
+            return NotImplemented
+        return self._bytes == other._bytes
 
     def __hash__(self) -> int:
-        return hash(str(self))
+        return hash(self._bytes)
 
-    def __iter__(self) -> Iterator[Tuple[Protocol, Optional[str]]]:
-        return iter(self._parts)
+    # --- mapping ---------------------------------------------------------------------------------------------
+    def __iter__(self) -> Iterator[Protocol]:
+        return iter(MultiAddrKeys(self))
 
-    def protocols(self) -> List[Protocol]:
-        return [proto for proto, _ in self._parts]
+    def __len__(self) -> int:
+        return len(MultiAddrKeys(self))
 
-    def items(self) -> List[Tuple[Protocol, Optional[str]]]:
-        return list(self._parts)
+    def __contains__(self, proto) -> bool:
+        return proto in MultiAddrKeys(self)
 
-    def values(self) -> List[Optional[str]]:
-        return [value for _, value in self._parts]
+    def keys(self) -> MultiAddrKeys:
+        return MultiAddrKeys(self)
 
-    def value_for_protocol(self, proto: Union[int, str]) -> Optional[str]:
-        """The value of the first component with this protocol; raises LookupError if absent."""
-        for p, value in self._parts:
-            if p.code == proto or p.name == proto:
+    def values(self) -> MultiAddrValues:
+        return MultiAddrValues(self)
+
+    def items(self) -> MultiAddrItems:
+        return MultiAddrItems(self)
+
+    def protocols(self) -> MultiAddrKeys:
+        """The protocols this address goes through, outermost first."""
+        return MultiAddrKeys(self)
+
+    def value_for_protocol(self, proto: Union[Protocol, str, int]) -> Optional[str]:
+        """The value of the first component of this protocol (None if the protocol has no value);
+        ``ProtocolLookupError`` (a ``LookupError``) if the address does not contain the protocol."""
+        wanted = protocols.REGISTRY.find(proto)
+        for present, value in self.items():
+            if present == wanted:
                 return value
-        raise LookupError(f"{self} has no {proto} component")
+        raise exceptions.ProtocolLookupError(wanted, str(self))
 
-    def __getitem__(self, proto: Union[int, str]) -> Optional[str]:
+    def __getitem__(self, proto: Union[Protocol, str, int]) -> Optional[str]:
         return self.value_for_protocol(proto)
 
-    def __contains__(self, proto: Union[int, str]) -> bool:
-        return any(p.code == proto or p.name == proto for p, _ in self._parts)
+    # --- nesting ---------------------------------------------------------------------------------------------
+    def _component_spans(self) -> List[Tuple[int, int, Protocol]]:
+        spans, offset = [], 0
+        for header, proto, _, value in bytes_iter(self._bytes):
+            spans.append((offset, offset + header + len(value), proto))
+            offset += header + len(value)
+        return spans
 
-    def encapsulate(self, other: Union[str, "Multiaddr"]) -> "Multiaddr":
-        result = Multiaddr(self)
-        result._parts.extend(Multiaddr(other)._parts)
-        return result
+    def split(self, maxsplit: int = -1) -> List["Multiaddr"]:
+        """One address per component; with ``maxsplit`` >= 0 the last element keeps everything beyond that many."""
+        pieces, spans = [], self._component_spans()
+        for index, (start, stop, _) in enumerate(spans):
+            if index == maxsplit:
+                pieces.append(self._from_canonical_bytes(self._bytes[start:]))
+                break
+            pieces.append(self._from_canonical_bytes(self._bytes[start:stop]))
+        return pieces
 
-    def decapsulate(self, other: Union[str, "Multiaddr"]) -> "Multiaddr":
-        """Remove the last occurrence of ``other`` and everything after it."""
-        mine, theirs = str(self), str(Multiaddr(other))
-        index = mine.rfind(theirs)
-        return Multiaddr(self) if index < 0 else Multiaddr(mine[:index])
+    def encapsulate(self, other: Union[str, bytes, "Multiaddr"]) -> "Multiaddr":
+        """This address with ``other`` nested inside it: ``/ip4/1.2.3.4`` + ``/tcp/80`` -> ``/ip4/1.2.3.4/tcp/80``."""
+        return self._from_canonical_bytes(self._bytes + Multiaddr(other).to_bytes())
+
+    def decapsulate(self, other: Union[str, bytes, "Multiaddr"]) -> "Multiaddr":
+        """This address up to (not including) the last place where ``other`` begins; unchanged if it never does."""
+        suffix = Multiaddr(other).to_bytes()
+        if not suffix:
+            return self
+        for start, _, _ in reversed(self._component_spans()):
+            if self._bytes.startswith(suffix, start):
+                return self._from_canonical_bytes(self._bytes[:start])
+        return self
 
     def decapsulate_code(self, code: int) -> "Multiaddr":
-        for i in range(len(self._parts) - 1, -1, -1):
-            if self._parts[i][0].code == code:
-                result = Multiaddr()
-                result._parts = self._parts[:i]
-                return result
-        return Multiaddr(self)
-
-    def split(self) -> List["Multiaddr"]:
-        out = []
-        for part in self._parts:
-            m = Multiaddr()
-            m._parts = [part]
-            out.append(m)
-        return out
-
-    @classmethod
-    def join(cls, *addrs: Union[str, "Multiaddr"]) -> "Multiaddr":
-        result = cls()
-        for a in addrs:
-            result._parts.extend(cls(a)._parts)
-        return result
+        """This address up to (not including) the last component whose protocol has this code."""
+        for start, _, proto in reversed(self._component_spans()):
+            if proto.code == code:
+                return self._from_canonical_bytes(self._bytes[:start])
+        return self
