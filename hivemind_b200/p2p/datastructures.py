@@ -42,6 +42,8 @@ class PeerID:
     def to_base58(self) -> str:
         return self._b58_str
 
+    to_string = to_base58
+
     def __getstate__(self):
         return (self._bytes,)
 
@@ -118,6 +120,16 @@ class StreamInfo:
     def __repr__(self) -> str:
         return f"<StreamInfo peer_id={self.peer_id} addr={self.addr} proto={self.proto}>"
 
+    def to_protobuf(self):
+        """The ``p2pd_pb2.StreamInfo`` form (peer id and address in their binary forms)."""
+        from hivemind_b200.proto import p2pd_pb2
+
+        return p2pd_pb2.StreamInfo(peer=self.peer_id.to_bytes(), addr=self.addr.to_bytes(), proto=self.proto)
+
+    @classmethod
+    def from_protobuf(cls, message) -> "StreamInfo":
+        return cls(peer_id=PeerID(message.peer), addr=Multiaddr(message.addr), proto=message.proto)
+
 
 class PeerInfo:
     def __init__(self, peer_id: PeerID, addrs: Sequence[Multiaddr]) -> None:
@@ -129,3 +141,13 @@ class PeerInfo:
 
     def __repr__(self) -> str:
         return f"PeerInfo(peer_id={self.peer_id!r}, addrs={self.addrs!r})"
+
+    @classmethod
+    def from_protobuf(cls, message) -> "PeerInfo":
+        """From a ``p2pd_pb2.PeerInfo`` (or any message with ``id`` and repeated binary ``addrs``)."""
+        return cls(PeerID(message.id), [Multiaddr(raw) for raw in message.addrs])
+
+    def to_protobuf(self):
+        from hivemind_b200.proto import p2pd_pb2
+
+        return p2pd_pb2.PeerInfo(id=self.peer_id.to_bytes(), addrs=[addr.to_bytes() for addr in self.addrs])
