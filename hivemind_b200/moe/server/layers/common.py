@@ -28,6 +28,12 @@ def _sequences(batch_size: int, hid_dim: int, length: int = 128) -> torch.Tensor
     return torch.empty((batch_size, length, hid_dim))
 
 
+def gelu_fast(x: torch.Tensor) -> torch.Tensor:
+    """The tanh approximation of GELU that the ``ffn`` and ``transformer`` experts use
+    (hivemind/moe/server/layers/common.py:12-14 writes the formula out)."""
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
 ffn_sample_input = nop_sample_input = _rows
 transformer_sample_input = _sequences
 

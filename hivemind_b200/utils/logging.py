@@ -45,7 +45,7 @@ class TextStyle:
         return cls._codes[name] if cls.enabled else ""
 
 
-class _Formatter(logging.Formatter):
+class CustomFormatter(logging.Formatter):
     _level_colors = {logging.DEBUG: "PURPLE", logging.INFO: "BLUE", logging.WARNING: "ORANGE", logging.ERROR: "RED",
                      logging.CRITICAL: "RED"}
 
@@ -77,7 +77,7 @@ def _init() -> None:
         colors = _env_flag("HIVEMIND_COLORS", None)
         TextStyle.enabled = colors if colors is not None else (hasattr(sys.stderr, "isatty") and sys.stderr.isatty())
         _handler = logging.StreamHandler()
-        _handler.setFormatter(_Formatter(bool(_env_flag("HIVEMIND_ALWAYS_LOG_CALLER", False))))
+        _handler.setFormatter(CustomFormatter(bool(_env_flag("HIVEMIND_ALWAYS_LOG_CALLER", False))))
         _attach(HandlerMode.IN_HIVEMIND)
 
 
