@@ -54,10 +54,15 @@ class BatchSource:
         rows = torch.randint(0, self.tokens.shape[0], (self.args.per_device_train_batch_size,), generator=self.generator)
         ids = self.tokens[rows, :self.args.seq_length].clone()
         n_mask = max(1, int(round(0.15 * self.args.seq_length)))
-        pos = torch.rand(ids.shape, generator=self.generator).argsort(dim=1)[:, :n_mask].contiguous()
+        # padding and the [CLS] / [SEP] / [MASK] pieces (the lowest ids of the vocabulary) are never masked: they sort
+        # behind every ordinary token, and a short sequence that still reaches them scores nothing there
+        special = ids <= self.cfg.mask_token_id
+        order = torch.rand(ids.shape, generator=self.generator).masked_fill_(special, 2.0)
+        pos = order.argsort(dim=1)[:, :n_mask].contiguous()
+        originals, untouched = ids.gather(1, pos), special.gather(1, pos)
         labels = torch.full_like(ids, -100)
-        labels.scatter_(1, pos, ids.gather(1, pos))
-        ids.scatter_(1, pos, self.cfg.mask_token_id)
+        labels.scatter_(1, pos, originals.masked_fill(untouched, -100))
+        ids.scatter_(1, pos, torch.where(untouched, originals, torch.full_like(originals, self.cfg.mask_token_id)))
         batch = {"input_ids": ids, "labels": labels, "masked_positions": pos}
         return {k: v.pin_memory() for k, v in batch.items()} if torch.cuda.is_available() else batch
 

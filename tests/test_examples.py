@@ -65,3 +65,56 @@ def test_powersgd_benchmark_runs_on_cpu_with_two_ranks():
         assert row["config"]["model"] == "gpt2-tiny"
         if averager == "powersgd":
             assert row["averaged_elements_per_round"] < row["parameters"]  # factors are smaller than the gradients
+
+
+def test_tokenized_corpus_feeds_the_trainer(tmp_path):
+    """examples/albert/tokenize_corpus.py on a small synthetic corpus (training its own SentencePiece model), then
+    one trainer for two epochs on the resulting file; the batch source never masks padding or marker tokens."""
+    import random
+
+    import torch
+
+    rng = random.Random(0)
+    words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta", "eta", "theta", "iota", "kappa", "lambda", "mu"]
+    with open(tmp_path / "corpus.txt", "w") as corpus:
+        for title in range(25):
+            corpus.write(f" = Document {title} = \n")
+            for _ in range(rng.randint(2, 9)):
+                corpus.write(" ".join(rng.choice(words) for _ in range(rng.randint(3, 14))).capitalize() + ". ")
+            corpus.write("\n\n")
+    tokens_path = tmp_path / "tokens.pt"
+    done = subprocess.run([sys.executable, os.path.join(ROOT, "examples/albert/tokenize_corpus.py"), "--text",
+                           str(tmp_path / "corpus.txt"), "--out", str(tokens_path), "--train_vocab_size", "64",
+                           "--seq_length", "32"], capture_output=True, text=True, env=ENV, timeout=120)
+    assert done.returncode == 0, done.stderr[-2000:]
+    data = torch.load(tokens_path)
+    ids, special = data["input_ids"], data["special_ids"]
+    assert ids.dtype == torch.int64 and ids.shape[1] == 32 and ids.shape[0] >= 25
+    assert special == {"<pad>": 0, "<unk>": 1, "[CLS]": 2, "[SEP]": 3, "[MASK]": 4}
+    assert (ids[:, 0] == special["[CLS]"]).all() and ((ids == special["[SEP]"]).sum(1) == 1).all()
+    assert not (ids == special["[MASK]"]).any() and ids.max() < data["vocab_size"] <= 64
+    after_sep = (ids == special["[SEP]"]).cumsum(1).roll(1, dims=1)
+    after_sep[:, 0] = 0
+    assert (ids[after_sep.bool()] == special["<pad>"]).all(), "only padding follows [SEP]"
+
+    sys.path.insert(0, os.path.join(ROOT, "examples", "albert"))
+    try:
+        from arguments import TrainingArguments
+        from run_trainer import BatchSource
+
+        from hivemind_b200.models.albert import AlbertConfig
+        args = TrainingArguments(dataset_path=str(tokens_path), seq_length=32, per_device_train_batch_size=16)
+        batch = BatchSource(AlbertConfig.tiny(), args, seed=1).next()
+    finally:
+        sys.path.pop(0)
+    scored = batch["labels"] != -100
+    assert scored.any() and (batch["labels"][scored] > special["[MASK]"]).all(), "markers and padding are never targets"
+    assert (batch["input_ids"][scored] == special["[MASK]"]).all()
+    assert (batch["input_ids"][:, 0] == special["[CLS]"]).all()
+
+    log = open(tmp_path / "trainer.log", "w")
+    trainer = subprocess.run([sys.executable, os.path.join(ROOT, "examples/albert/run_trainer.py"), *COMMON, *TRAIN,
+                              "--run_id", "tokenized_test", "--dataset_path", str(tokens_path), "--max_epochs", "2",
+                              "--output_dir", str(tmp_path / "out")], stderr=log, stdout=log, env=ENV, timeout=240)
+    assert trainer.returncode == 0 and "step 2" in (tmp_path / "trainer.log").read_text(), \
+        (tmp_path / "trainer.log").read_text()[-2000:]
