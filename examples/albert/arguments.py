@@ -65,6 +65,9 @@ class TrainingArguments:
     max_epochs: Optional[int] = field(default=None, metadata={"help": "stop after this many collaborative steps"})
     dataset_path: Optional[str] = field(default=None, metadata={
         "help": "a torch file with int64 'input_ids' [n, seq]; default: synthetic token ids"})
+    sentence_order: bool = field(default=False, metadata={
+        "help": "train sentence-order prediction next to the masked LM (every peer of a run must agree); the dataset "
+                "then needs two-segment rows (tokenize_corpus.py --sentence_order), synthetic data gets random ones"})
     output_dir: str = field(default="outputs", metadata={"help": "where local checkpoints are written"})
     save_steps: int = field(default=500, metadata={"help": "save a local checkpoint every N collaborative steps (0 = never)"})
     backup_every_steps: int = field(default=10, metadata={"help": "keep an in-memory copy of the weights every N collaborative steps (rolled back to on NaN)"})

@@ -22,7 +22,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import torch
 
 import hivemind_b200 as hivemind
-from hivemind_b200.models.albert import AlbertConfig, AlbertForMaskedLM, make_mlm_batch
+from hivemind_b200.models.albert import AlbertConfig, AlbertForMaskedLM, AlbertForPreTraining, make_mlm_batch
 from hivemind_b200.optim.fused import FusedLAMB
 from hivemind_b200.optim.power_sgd_averager import PowerSGDGradientAverager
 from hivemind_b200.utils.logging import get_logger, use_hivemind_log_handler
@@ -43,14 +43,28 @@ class BatchSource:
         self.cfg, self.args = cfg, args
         self.generator = torch.Generator().manual_seed(seed)
         self.tokens = None
+        self.token_types = self.sentence_order = None
         if args.dataset_path:
-            self.tokens = torch.load(args.dataset_path)["input_ids"].to(torch.int64)
+            data = torch.load(args.dataset_path)
+            self.tokens = data["input_ids"].to(torch.int64)
             assert self.tokens.shape[1] >= args.seq_length, "sequences in the dataset are shorter than --seq_length"
+            if args.sentence_order:
+                assert "sentence_order_label" in data, "--sentence_order needs a dataset made with --sentence_order"
+                assert self.tokens.shape[1] == args.seq_length, "two-segment rows cannot be shortened"
+                self.token_types, self.sentence_order = data["token_type_ids"], data["sentence_order_label"]
 
     def next(self):
         if self.tokens is None:
-            return make_mlm_batch(self.cfg, self.args.per_device_train_batch_size, self.args.seq_length,
-                                  generator=self.generator, pin=True)
+            batch = make_mlm_batch(self.cfg, self.args.per_device_train_batch_size, self.args.seq_length,
+                                   generator=self.generator, pin=not self.args.sentence_order)
+            if self.args.sentence_order:  # synthetic segments: the second one starts somewhere in the middle half
+                size, length = self.args.per_device_train_batch_size, self.args.seq_length
+                starts = torch.randint(length // 4, max(length // 4 + 1, 3 * length // 4), (size, 1), generator=self.generator)
+                batch["token_type_ids"] = (torch.arange(length).unsqueeze(0) >= starts).long()
+                batch["sentence_order_label"] = torch.randint(0, 2, (size,), generator=self.generator)
+                if torch.cuda.is_available():
+                    batch = {k: v.pin_memory() for k, v in batch.items()}
+            return batch
         rows = torch.randint(0, self.tokens.shape[0], (self.args.per_device_train_batch_size,), generator=self.generator)
         ids = self.tokens[rows, :self.args.seq_length].clone()
         n_mask = max(1, int(round(0.15 * self.args.seq_length)))
@@ -64,6 +78,9 @@ class BatchSource:
         labels.scatter_(1, pos, originals.masked_fill(untouched, -100))
         ids.scatter_(1, pos, torch.where(untouched, originals, torch.full_like(originals, self.cfg.mask_token_id)))
         batch = {"input_ids": ids, "labels": labels, "masked_positions": pos}
+        if self.sentence_order is not None:
+            batch["token_type_ids"] = self.token_types[rows]
+            batch["sentence_order_label"] = self.sentence_order[rows]
         return {k: v.pin_memory() for k, v in batch.items()} if torch.cuda.is_available() else batch
 
 
@@ -80,7 +97,7 @@ def main():
     torch.manual_seed(args.seed)  # every peer starts from the same weights; late joiners download the current state
     cfg = AlbertConfig.large() if args.model == "large" else AlbertConfig.tiny()
     args.seq_length = min(args.seq_length, cfg.max_position_embeddings)
-    model = AlbertForMaskedLM(cfg).to(device)
+    model = (AlbertForPreTraining(cfg) if args.sentence_order else AlbertForMaskedLM(cfg)).to(device)
 
     validators, local_public_key = utils.make_validators(base.run_id)
     dht = hivemind.DHT(start=True, initial_peers=base.initial_peers, client_mode=opt_args.client_mode,
@@ -142,7 +159,7 @@ def main():
     try:
         while True:
             batch = {k: v.to(device, non_blocking=True) for k, v in source.next().items()}
-            loss = model(batch["input_ids"], batch["labels"], masked_positions=batch["masked_positions"])
+            loss = model(**batch)
             loss.backward()
             local_steps += 1
             loss_sum += float(loss.item())

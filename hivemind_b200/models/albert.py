@@ -164,10 +164,15 @@ class AlbertForMaskedLM(nn.Module):
         :param masked_positions: optional ``[batch, n]`` indices of the scored positions of each sequence; passing
           them avoids a device-to-host synchronisation to find the labelled rows
         """
-        b, s = input_ids.shape
-        hidden = self.encode(input_ids, token_type_ids).reshape(b * s, -1)
+        return self.masked_lm_loss(self.encode(input_ids, token_type_ids), labels, masked_positions)
+
+    def masked_lm_loss(self, hidden: torch.Tensor, labels: torch.Tensor,
+                       masked_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Mean cross-entropy of the tied decoder over the scored positions of ``hidden`` (``[batch, seq, hidden]``)."""
+        b, s = labels.shape
+        hidden = hidden.reshape(b * s, -1)
         if masked_positions is not None:
-            rows = (masked_positions + torch.arange(b, device=input_ids.device).unsqueeze(1) * s).reshape(-1)
+            rows = (masked_positions + torch.arange(b, device=labels.device).unsqueeze(1) * s).reshape(-1)
         else:
             rows = (labels.reshape(-1) != -100).nonzero(as_tuple=True)[0]
         picked = hidden.index_select(0, rows)
@@ -184,6 +189,39 @@ class AlbertForMaskedLM(nn.Module):
         h, f, L, s = c.hidden_size, c.intermediate_size, c.num_hidden_layers, c.max_position_embeddings
         per_layer = 2 * (4 * h * h + 2 * h * f) + 4 * s * h
         return 3.0 * (L * per_layer + 2 * c.embedding_size * h)
+
+
+class AlbertForPreTraining(AlbertForMaskedLM):
+    """The two pre-training objectives of ALBERT: masked LM plus sentence-order prediction, a two-way classifier on the
+    ``tanh``-pooled first token that tells whether two consecutive segments come in their original order (the model
+    that the reference's example trains, examples/albert/run_trainer.py:204-227, there taken from ``transformers``)."""
+
+    def __init__(self, cfg: AlbertConfig):
+        super().__init__(cfg)
+        h = cfg.hidden_size
+        self.pooler_weight = nn.Parameter(torch.empty(h, h))
+        self.pooler_bias = nn.Parameter(torch.zeros(h))
+        self.sop_weight = nn.Parameter(torch.empty(2, h))
+        self.sop_bias = nn.Parameter(torch.zeros(2))
+        for w in (self.pooler_weight, self.sop_weight):
+            nn.init.normal_(w, std=cfg.initializer_range)
+
+    def sentence_order_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        pooled = torch.tanh(linear(hidden[:, 0].contiguous(), self.pooler_weight, self.pooler_bias,
+                                   weight_lp=self._lp.get(self.pooler_weight)).float())
+        # two output columns are no work for a tensor-core tile: this product stays a plain matmul
+        return pooled @ self.sop_weight.float().t() + self.sop_bias.float()
+
+    def forward(self, input_ids: torch.Tensor, labels: torch.Tensor, masked_positions: Optional[torch.Tensor] = None,
+                token_type_ids: Optional[torch.Tensor] = None,
+                sentence_order_label: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Masked-LM loss, plus the sentence-order loss when ``sentence_order_label`` (``[batch]``, 0 = original order,
+        1 = swapped) is given."""
+        hidden = self.encode(input_ids, token_type_ids)
+        loss = self.masked_lm_loss(hidden, labels, masked_positions)
+        if sentence_order_label is not None:
+            loss = loss + F.cross_entropy(self.sentence_order_logits(hidden), sentence_order_label)
+        return loss
 
 
 def make_mlm_batch(cfg: AlbertConfig, batch: int, seq: int, generator: Optional[torch.Generator] = None,

@@ -112,9 +112,28 @@ def test_tokenized_corpus_feeds_the_trainer(tmp_path):
     assert (batch["input_ids"][scored] == special["[MASK]"]).all()
     assert (batch["input_ids"][:, 0] == special["[CLS]"]).all()
 
-    log = open(tmp_path / "trainer.log", "w")
-    trainer = subprocess.run([sys.executable, os.path.join(ROOT, "examples/albert/run_trainer.py"), *COMMON, *TRAIN,
-                              "--run_id", "tokenized_test", "--dataset_path", str(tokens_path), "--max_epochs", "2",
-                              "--output_dir", str(tmp_path / "out")], stderr=log, stdout=log, env=ENV, timeout=240)
-    assert trainer.returncode == 0 and "step 2" in (tmp_path / "trainer.log").read_text(), \
-        (tmp_path / "trainer.log").read_text()[-2000:]
+    # the same corpus as rows of two segments, for both of ALBERT's objectives
+    pairs_path = tmp_path / "pairs.pt"
+    done = subprocess.run([sys.executable, os.path.join(ROOT, "examples/albert/tokenize_corpus.py"), "--text",
+                           str(tmp_path / "corpus.txt"), "--out", str(pairs_path), "--train_vocab_size", "64",
+                           "--seq_length", "32", "--sentence_order"], capture_output=True, text=True, env=ENV, timeout=120)
+    assert done.returncode == 0, done.stderr[-2000:]
+    pairs = torch.load(pairs_path)
+    rows, kinds, order = pairs["input_ids"], pairs["token_type_ids"], pairs["sentence_order_label"]
+    assert rows.shape == kinds.shape and order.shape == (rows.shape[0],) and set(order.tolist()) == {0, 1}
+    assert ((rows == special["[SEP]"]).sum(1) == 2).all() and (rows[:, 0] == special["[CLS]"]).all()
+    first_sep = (rows == special["[SEP]"]).float().argmax(1)
+    columns = torch.arange(32).unsqueeze(0)
+    real = rows != special["<pad>"]
+    assert (kinds[real & (columns <= first_sep.unsqueeze(1))] == 0).all(), "segment A and its [SEP] are type 0"
+    assert (kinds[real & (columns > first_sep.unsqueeze(1))] == 1).all(), "segment B and its [SEP] are type 1"
+    assert (kinds[~real] == 0).all()
+
+    for name, dataset, extra in (("plain", tokens_path, []), ("pairs", pairs_path, ["--sentence_order", "true"])):
+        log = open(tmp_path / f"trainer_{name}.log", "w")
+        trainer = subprocess.run([sys.executable, os.path.join(ROOT, "examples/albert/run_trainer.py"), *COMMON, *TRAIN,
+                                  "--run_id", f"tokenized_{name}", "--dataset_path", str(dataset), "--max_epochs", "2",
+                                  "--output_dir", str(tmp_path / f"out_{name}"), *extra],
+                                 stderr=log, stdout=log, env=ENV, timeout=240)
+        text = (tmp_path / f"trainer_{name}.log").read_text()
+        assert trainer.returncode == 0 and "step 2" in text, text[-2000:]

@@ -102,12 +102,12 @@ def test_layer_norm_return_sum_gpu():
         assert ((got.float() - ref).norm() / ref.norm()).item() < 2e-2
 
 
-def _albert_reference_loss(cfg, p, batch):
-    """Textbook ALBERT (factorised embeddings, one shared post-LayerNorm block, tied decoder) in fp64."""
-    ids, labels = batch["input_ids"], batch["labels"]
+def _albert_reference_hidden(cfg, p, ids, token_type_ids=None):
+    """Textbook ALBERT encoder (factorised embeddings, one shared post-LayerNorm block) in the precision of ``p``."""
     b, s = ids.shape
     e, h = cfg.embedding_size, cfg.hidden_size
-    x = p["word_embeddings"][ids] + p["position_embeddings"][:s] + p["token_type_embeddings"][0]
+    types = p["token_type_embeddings"][0] if token_type_ids is None else p["token_type_embeddings"][token_type_ids]
+    x = p["word_embeddings"][ids] + p["position_embeddings"][:s] + types
     x = F.layer_norm(x, (e,), p["emb_ln_weight"], p["emb_ln_bias"], cfg.layer_norm_eps)
     x = x @ p["emb_proj_weight"].T + p["emb_proj_bias"]
     g = lambda name: p[f"layer.{name}"]
@@ -121,10 +121,22 @@ def _albert_reference_loss(cfg, p, batch):
         inter = F.gelu(x @ g("ffn_weight").T + g("ffn_bias"), approximate="tanh")
         x = F.layer_norm(x + inter @ g("ffn_out_weight").T + g("ffn_out_bias"), (h,), g("ffn_ln_weight"),
                          g("ffn_ln_bias"), cfg.layer_norm_eps)
+    return x
+
+
+def _albert_reference_loss(cfg, p, batch, token_type_ids=None, sentence_order_label=None):
+    """Masked-LM loss with the tied decoder, plus the sentence-order loss when its labels are given; fp64."""
+    ids, labels = batch["input_ids"], batch["labels"]
+    b, s = ids.shape
+    x = _albert_reference_hidden(cfg, p, ids, token_type_ids)
     z = F.gelu(x @ p["head_dense_weight"].T + p["head_dense_bias"], approximate="tanh")
-    z = F.layer_norm(z, (e,), p["head_ln_weight"], p["head_ln_bias"], cfg.layer_norm_eps)
+    z = F.layer_norm(z, (cfg.embedding_size,), p["head_ln_weight"], p["head_ln_bias"], cfg.layer_norm_eps)
     logits = z @ p["word_embeddings"].T + p["decoder_bias"]
-    return F.cross_entropy(logits.view(b * s, -1), labels.reshape(-1), ignore_index=-100)
+    loss = F.cross_entropy(logits.view(b * s, -1), labels.reshape(-1), ignore_index=-100)
+    if sentence_order_label is not None:
+        pooled = torch.tanh(x[:, 0] @ p["pooler_weight"].T + p["pooler_bias"])
+        loss = loss + F.cross_entropy(pooled @ p["sop_weight"].T + p["sop_bias"], sentence_order_label)
+    return loss
 
 
 def _check_albert(device, loss_tol, grad_tol):
@@ -155,6 +167,46 @@ def _check_albert(device, loss_tol, grad_tol):
     # finding the labelled rows on the fly gives the same loss as passing their positions
     again = model(batch["input_ids"], batch["labels"])
     assert torch.allclose(again.float(), loss.detach().float(), rtol=5 * loss_tol + 1e-6)
+
+
+def _check_albert_pretraining(device, loss_tol, grad_tol):
+    """Both objectives (masked LM + sentence order) with two segment types against the fp64 restatement."""
+    from hivemind_b200.models.albert import AlbertConfig, AlbertForPreTraining, make_mlm_batch
+
+    torch.manual_seed(0)
+    cfg = AlbertConfig.tiny()
+    model = AlbertForPreTraining(cfg).to(device)
+    with torch.no_grad():
+        for name, q in model.named_parameters():
+            if q.ndim == 1:
+                q.add_(0.1 * torch.randn_like(q))
+    batch = {k: v.to(device) for k, v in make_mlm_batch(cfg, 5, 48, generator=torch.Generator().manual_seed(2)).items()}
+    token_types = (torch.arange(48, device=device).unsqueeze(0) >= torch.tensor([[20], [24], [30], [10], [40]], device=device)).long()
+    order = torch.tensor([0, 1, 1, 0, 1], device=device)
+    loss = model(batch["input_ids"], batch["labels"], masked_positions=batch["masked_positions"],
+                 token_type_ids=token_types, sentence_order_label=order)
+    loss.backward()
+    params = {name: q.detach().double().requires_grad_(True) for name, q in model.named_parameters()}
+    ref_loss = _albert_reference_loss(cfg, params, batch, token_types, order)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) <= loss_tol * abs(ref_loss.item()), (loss.item(), ref_loss.item())
+    for name, q in model.named_parameters():
+        ref = params[name].grad.to(q.grad.dtype)
+        err = (q.grad - ref).norm() / ref.norm().clamp_min(1e-6)
+        assert err.item() <= grad_tol, (name, err.item())
+    # without sentence-order labels the model is the masked-LM model
+    mlm_only = model(batch["input_ids"], batch["labels"], masked_positions=batch["masked_positions"], token_type_ids=token_types)
+    ref_mlm = _albert_reference_loss(cfg, params, batch, token_types)
+    assert abs(mlm_only.item() - ref_mlm.item()) <= loss_tol * abs(ref_mlm.item())
+
+
+def test_albert_pretraining_matches_reference_cpu():
+    _check_albert_pretraining(torch.device("cpu"), loss_tol=1e-5, grad_tol=1e-4)
+
+
+@pytest.mark.gpu
+def test_albert_pretraining_matches_reference_gpu():
+    _check_albert_pretraining(torch.device("cuda"), loss_tol=5e-3, grad_tol=6e-2)
 
 
 def test_albert_matches_reference_cpu():
