@@ -461,6 +461,37 @@ def test_server_checkpoint_restart(tmp_path, hidden_dim=16):
             dht.shutdown()
 
 
+def test_training_through_a_chain_of_remote_experts(max_steps=100, threshold=0.9):
+    """Two remote experts stacked inside an ordinary ``nn.Sequential``: gradients cross two RPC hops and both experts
+    learn on the server side (the case of hivemind tests/test_training.py::test_training)."""
+    from sklearn.datasets import load_digits
+
+    torch.manual_seed(0)
+    digits = load_digits(n_class=2)
+    features = torch.tensor(digits["data"], dtype=torch.float32)
+    labels = torch.tensor(digits["target"])
+    with background_server(expert_uids=["expert.0", "expert.1"], device="cpu", hidden_dim=64, num_handlers=1,
+                           optim_cls=lambda p: torch.optim.SGD(p, lr=0.05)) as info:
+        dht = DHT(initial_peers=info.addrs, start=True)
+        try:
+            first, second = get_experts(dht, ["expert.0", "expert.1"])
+            model = nn.Sequential(second, nn.ReLU(), first, nn.Linear(64, 2))
+            opt = torch.optim.SGD(model.parameters(), lr=0.05)
+            accuracy = 0.0
+            for step in range(max_steps):
+                logits = model(features)
+                loss = F.cross_entropy(logits, labels)
+                opt.zero_grad()
+                loss.backward()
+                opt.step()
+                accuracy = (logits.argmax(1) == labels).float().mean().item()
+                if accuracy >= threshold:
+                    break
+            assert accuracy >= threshold, accuracy
+        finally:
+            dht.shutdown()
+
+
 def test_moe_training(max_steps=100, threshold=0.9):
     from sklearn.datasets import load_digits
 
