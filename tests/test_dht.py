@@ -489,3 +489,73 @@ def test_dht_refuses_to_start_without_a_reachable_bootstrap_peer():
         assert dht.store("still", "works", get_dht_time() + 30) and dht.get("still").value == "works"
     finally:
         dht.shutdown()
+
+
+def test_odd_keys_subkeys_and_values_survive_the_network():
+    """Falsy and structured keys, sub-keys and values (0, "", False, (), []) are stored and found like any other
+    (the case of hivemind tests/test_dht_node.py::test_dhtnode_edge_cases)."""
+    from itertools import product
+
+    async def scenario():
+        first = await DHTNode.create(parallel_rpc=4)
+        maddrs = await first.get_visible_maddrs()
+        others = [await DHTNode.create(initial_peers=maddrs, parallel_rpc=4) for _ in range(3)]
+        peers = [first] + others
+        subkeys = [0, "", False, True, "abyrvalg", 4555]
+        keys = subkeys + [()]
+        values = subkeys + [[]]
+        rng = random.Random(0)
+        try:
+            for key, subkey, value in product(keys, subkeys, values):
+                assert await rng.choice(peers).store(key=key, subkey=subkey, value=value, expiration_time=get_dht_time() + 999)
+                found = await rng.choice(peers).get(key=key, latest=True)
+                assert found is not None and subkey in found.value, (key, subkey, value)
+                assert found.value[subkey].value == value, (key, subkey, value, found.value[subkey])
+        finally:
+            for node in peers:
+                await node.shutdown()
+
+    asyncio.new_event_loop().run_until_complete(asyncio.wait_for(scenario(), 240))
+
+
+@pytest.mark.parametrize("bucket_size,depth_modulo,fewest,most", [(20, 5, 45, 65), (50, 5, 35, 45), (20, 10, 650, 800),
+                                                                  (20, 1, 7, 15)])
+def test_bucket_splitting_statistics(bucket_size, depth_modulo, fewest, most):
+    """How far a table of 10 000 random nodes splits depends on the bucket size and on how often buckets that do not
+    hold our own id may split (``depth_modulo``); the ranges are those the reference's routing table satisfies
+    (tests/test_routing.py::test_routing_table_parameters)."""
+    rng = random.Random(bucket_size * 100 + depth_modulo)
+    table = RoutingTable(DHTID.generate(), bucket_size=bucket_size, depth_modulo=depth_modulo)
+    for port in rng.sample(range(1_000_000), 10_000):
+        table.add_or_update_node(DHTID.generate(), PeerID(port.to_bytes(4, "big")))
+    assert table.buckets[0].lower == DHTID.MIN and table.buckets[-1].upper == DHTID.MAX
+    for left, right in zip(table.buckets, table.buckets[1:]):
+        assert left.upper == right.lower, "buckets tile the id space without gaps"
+    for bucket in table.buckets:
+        assert len(bucket.nodes_to_peer_id) <= bucket.size
+        assert not bucket.replacement_nodes or len(bucket.nodes_to_peer_id) == bucket.size, "spares only wait for full buckets"
+    assert fewest <= len(table.buckets) <= most, len(table.buckets)
+
+
+def test_a_large_table_keeps_about_a_thousand_active_nodes_and_a_small_one_keeps_all():
+    for table_size, fewest, most in [(10, 10, 10), (10_000, 800, 1100)]:
+        rng = random.Random(table_size)
+        table = RoutingTable(DHTID.generate(), bucket_size=20, depth_modulo=5)
+        for port in rng.sample(range(1_000_000), table_size):
+            table.add_or_update_node(DHTID.generate(), PeerID(port.to_bytes(4, "big")))
+        active = sum(len(bucket.nodes_to_peer_id) for bucket in table.buckets)
+        assert fewest <= active <= most, active
+        spares = sum(len(bucket.replacement_nodes) for bucket in table.buckets)
+        assert len(table.peer_id_to_uid) == len(table.uid_to_peer_id) == active + spares == table_size
+
+
+def test_id_prefix_depth():
+    for _ in range(100):
+        shared_bits = random.randint(0, 159)
+        one = DHTID.generate()
+        other = DHTID(int(one) ^ (1 << (159 - shared_bits)) ^ random.getrandbits(159 - shared_bits))
+        assert DHTID.longest_common_prefix_length(one, other) == shared_bits
+    ids = [DHTID.generate() for _ in range(8)]
+    assert DHTID.longest_common_prefix_length(*ids) == min(
+        DHTID.longest_common_prefix_length(a, b) for a in ids for b in ids if a != b)
+    assert DHTID.longest_common_prefix_length(ids[0], ids[0]) == 160

@@ -564,3 +564,15 @@ def test_remote_expert_worker_concurrency():
     futures = [RemoteExpertWorker.run_coroutine(nap(i), return_future=True) for i in range(20)]
     assert [f.result(5) for f in futures] == list(range(20))
     assert time.perf_counter() - started < 1.5
+
+
+def test_background_servers_share_or_differ_in_identity(tmp_path):
+    """Servers started with the same identity file have one peer id, a server without it gets its own
+    (the case of hivemind tests/test_start_server.py::test_background_server_identity_path)."""
+    from functools import partial
+
+    identity = str(tmp_path / "server.id")
+    start = partial(background_server, num_experts=1, device="cpu", hidden_dim=4, num_handlers=1, expert_cls="nop")
+    with start(identity_path=identity) as first, start(identity_path=identity) as second, start() as third:
+        assert first.peer_id == second.peer_id != third.peer_id
+        assert all(str(addr).endswith(info.peer_id.to_base58()) for info in (first, second, third) for addr in info.addrs)

@@ -334,3 +334,24 @@ def test_fused_optimizers_track_parameters_that_join_or_skip_steps():
             opt_ref.step()
         for mine, theirs in zip(ours, ref):
             assert torch.allclose(mine, theirs, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("factory", ["plain", "powersgd"])
+def test_grad_averager_refuses_buffers_of_the_wrong_shape(factory):
+    """Pre-allocated ``averaged_grads`` have to match the parameters one by one
+    (the case of hivemind tests/test_optimizer.py::test_grad_averager_wrong_shape)."""
+    from functools import partial
+
+    from hivemind_b200 import DHT
+    from hivemind_b200.optim.grad_averager import GradientAverager
+    from hivemind_b200.optim.power_sgd_averager import PowerSGDGradientAverager
+
+    make = GradientAverager if factory == "plain" else partial(PowerSGDGradientAverager, averager_rank=1)
+    model = torch.nn.ParameterDict({"w": torch.nn.Parameter(torch.zeros(5, 5))})
+    dht = DHT(start=True)
+    try:
+        with pytest.raises(ValueError):
+            make(model.parameters(), dht=dht, prefix="wrong_shape", target_group_size=2, reuse_grad_buffers=False,
+                 start=True, averaged_grads=[torch.zeros(5, 5, 1)])
+    finally:
+        dht.shutdown()
