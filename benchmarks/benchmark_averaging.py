@@ -95,6 +95,42 @@ def benchmark_swarm(num_peers, target_group_size, num_rounds, min_matchmaking_ti
         item.shutdown()
 
 
+def benchmark_rpc_payload(num_peers, size_mb, codec_name, rounds, part_size_bytes, min_matchmaking_time):
+    """Throughput of the RPC butterfly on CPU tensors: ``num_peers`` averagers of this process (one DHT node and one
+    transport daemon each) average one tensor of ``size_mb`` megabytes; a round is timed from ``step()`` to the last
+    peer's result, so it contains the matchmaking wait. Prints one JSON line per codec with the best round."""
+    from hivemind_b200.compression import (BlockwiseQuantization, Float16Compression, NoCompression,
+                                           ScaledFloat16Compression, Uniform8BitQuantization)
+    codec = {"none": NoCompression, "float16": Float16Compression, "scaled_float16": ScaledFloat16Compression,
+             "uniform8": Uniform8BitQuantization, "blockwise8": BlockwiseQuantization}[codec_name]()
+    numel = int(size_mb * 1e6 / 4)
+    root = DHT(start=True)
+    dhts = [root] + [DHT(initial_peers=root.get_visible_maddrs(), start=True) for _ in range(num_peers - 1)]
+    averagers = [DecentralizedAverager([torch.randn(numel)], dht, prefix="rpc_payload", target_group_size=num_peers,
+                                       min_matchmaking_time=min_matchmaking_time, compression=codec, start=True,
+                                       part_size_bytes=part_size_bytes) for dht in dhts]
+    expected = sum(a._averaged_tensors[0][:1000].clone() for a in averagers) / num_peers
+    best = None
+    try:
+        for _ in range(rounds):
+            started, cpu_started = time.perf_counter(), time.process_time()
+            controls = [averager.step(wait=False, timeout=600) for averager in averagers]
+            for control in controls:
+                control.result()
+            elapsed, cpu = time.perf_counter() - started, time.process_time() - cpu_started
+            if best is None or elapsed < best[0]:
+                best = (elapsed, cpu)
+        error = max(float((a._averaged_tensors[0][:1000] - expected).abs().max()) for a in averagers)
+    finally:
+        for item in averagers + dhts:
+            item.shutdown()
+    net = max(best[0] - min_matchmaking_time, 1e-6)
+    print(json.dumps({"benchmark": "averaging_rpc_payload", "peers": num_peers, "payload_mb_per_peer": size_mb,
+                      "codec": codec_name, "part_size_bytes": part_size_bytes, "seconds_per_round": best[0],
+                      "seconds_after_matchmaking": net, "payload_mb_per_s_per_peer": size_mb / net,
+                      "process_cpu_seconds": best[1], "max_abs_error_vs_mean": error}), flush=True)
+
+
 VERBOSE_ROUNDS = False
 TRACE_ROUND = False
 
@@ -290,7 +326,7 @@ def benchmark_device(sizes_mb, codecs, rounds, warmup, emulate_ranks, part_size_
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
-    parser.add_argument("--mode", choices=["swarm", "device"], default="swarm")
+    parser.add_argument("--mode", choices=["swarm", "device", "rpc_payload"], default="swarm")
     parser.add_argument("--num_peers", type=int, default=16)
     parser.add_argument("--target_group_size", type=int, default=4)
     parser.add_argument("--num_rounds", type=int, default=5)
@@ -315,7 +351,11 @@ if __name__ == "__main__":
     TRACE_ROUND = args.trace_round
     if args.increase_file_limit:
         increase_file_limit()
-    if args.mode == "device":
+    if args.mode == "rpc_payload":
+        for size_mb in args.sizes_mb:
+            for codec_name in args.codecs:
+                benchmark_rpc_payload(args.num_peers, size_mb, codec_name, args.rounds, args.part_size_bytes, 0.5)
+    elif args.mode == "device":
         benchmark_device(args.sizes_mb, args.codecs, args.rounds, args.warmup, args.emulate_ranks, args.part_size_bytes)
     else:
         benchmark_swarm(args.num_peers, args.target_group_size, args.num_rounds, args.min_matchmaking_time,
