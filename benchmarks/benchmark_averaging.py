@@ -95,14 +95,67 @@ def benchmark_swarm(num_peers, target_group_size, num_rounds, min_matchmaking_ti
         item.shutdown()
 
 
+def _rpc_payload_peer(maddrs, numel, codec_name, rounds, part_size_bytes, min_matchmaking_time, num_peers, ready, go):
+    """Body of a helper process of ``benchmark_rpc_payload``: one averager that steps whenever it is told to."""
+    torch.set_num_threads(2)
+    dht = DHT(initial_peers=maddrs, start=True)
+    averager = DecentralizedAverager([torch.randn(numel)], dht, prefix="rpc_payload", target_group_size=num_peers,
+                                     min_matchmaking_time=min_matchmaking_time, compression=CODECS[codec_name](),
+                                     start=True, part_size_bytes=part_size_bytes)
+    ready.put(True)
+    for _ in range(rounds):
+        go.get()
+        averager.step(timeout=600)
+    ready.put(True)
+    averager.shutdown()
+    dht.shutdown()
+
+
+def benchmark_rpc_payload_processes(num_peers, size_mb, codec_name, rounds, part_size_bytes, min_matchmaking_time):
+    """Like ``benchmark_rpc_payload`` with every peer but the first in a process of its own (no shared interpreter
+    lock, as in a real swarm); the first peer's ``step()`` is timed."""
+    import multiprocessing as mp
+
+    numel = int(size_mb * 1e6 / 4)
+    torch.set_num_threads(2)
+    root = DHT(start=True)
+    ctx = mp.get_context("spawn")
+    ready, go = ctx.Queue(), ctx.Queue()
+    maddrs = [str(m) for m in root.get_visible_maddrs()]
+    helpers = [ctx.Process(target=_rpc_payload_peer, daemon=True,
+                           args=(maddrs, numel, codec_name, rounds, part_size_bytes, min_matchmaking_time, num_peers, ready, go))
+               for _ in range(num_peers - 1)]
+    for helper in helpers:
+        helper.start()
+    averager = DecentralizedAverager([torch.randn(numel)], root, prefix="rpc_payload", target_group_size=num_peers,
+                                     min_matchmaking_time=min_matchmaking_time, compression=CODECS[codec_name](),
+                                     start=True, part_size_bytes=part_size_bytes)
+    for _ in helpers:
+        ready.get()
+    best = None
+    for _ in range(rounds):
+        for _ in helpers:
+            go.put(True)
+        started = time.perf_counter()
+        averager.step(timeout=600)
+        elapsed = time.perf_counter() - started
+        best = elapsed if best is None else min(best, elapsed)
+    for helper in helpers:
+        ready.get()
+        helper.join(timeout=30)
+    averager.shutdown()
+    root.shutdown()
+    print(json.dumps({"benchmark": "averaging_rpc_payload", "peers": num_peers, "processes": num_peers,
+                      "payload_mb_per_peer": size_mb, "codec": codec_name, "part_size_bytes": part_size_bytes,
+                      "seconds_per_round": best, "payload_mb_per_s_per_peer": size_mb / best}), flush=True)
+
+
 def benchmark_rpc_payload(num_peers, size_mb, codec_name, rounds, part_size_bytes, min_matchmaking_time):
     """Throughput of the RPC butterfly on CPU tensors: ``num_peers`` averagers of this process (one DHT node and one
     transport daemon each) average one tensor of ``size_mb`` megabytes; a round is timed from ``step()`` to the last
-    peer's result, so it contains the matchmaking wait. Prints one JSON line per codec with the best round."""
-    from hivemind_b200.compression import (BlockwiseQuantization, Float16Compression, NoCompression,
-                                           ScaledFloat16Compression, Uniform8BitQuantization)
-    codec = {"none": NoCompression, "float16": Float16Compression, "scaled_float16": ScaledFloat16Compression,
-             "uniform8": Uniform8BitQuantization, "blockwise8": BlockwiseQuantization}[codec_name]()
+    peer's result, so it contains the time to form the group (a full group closes at once, well before
+    ``min_matchmaking_time``). Prints one JSON line per codec with the best round."""
+    codec = CODECS[codec_name]()
     numel = int(size_mb * 1e6 / 4)
     root = DHT(start=True)
     dhts = [root] + [DHT(initial_peers=root.get_visible_maddrs(), start=True) for _ in range(num_peers - 1)]
@@ -124,10 +177,9 @@ def benchmark_rpc_payload(num_peers, size_mb, codec_name, rounds, part_size_byte
     finally:
         for item in averagers + dhts:
             item.shutdown()
-    net = max(best[0] - min_matchmaking_time, 1e-6)
-    print(json.dumps({"benchmark": "averaging_rpc_payload", "peers": num_peers, "payload_mb_per_peer": size_mb,
-                      "codec": codec_name, "part_size_bytes": part_size_bytes, "seconds_per_round": best[0],
-                      "seconds_after_matchmaking": net, "payload_mb_per_s_per_peer": size_mb / net,
+    print(json.dumps({"benchmark": "averaging_rpc_payload", "peers": num_peers, "processes": 1,
+                      "payload_mb_per_peer": size_mb, "codec": codec_name, "part_size_bytes": part_size_bytes,
+                      "seconds_per_round": best[0], "payload_mb_per_s_per_peer": size_mb / best[0],
                       "process_cpu_seconds": best[1], "max_abs_error_vs_mean": error}), flush=True)
 
 
@@ -343,6 +395,8 @@ if __name__ == "__main__":
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--emulate-ranks", type=int, default=4)
     parser.add_argument("--part-size-bytes", type=int, default=2 ** 19)
+    parser.add_argument("--peer-processes", action="store_true",
+                        help="rpc_payload mode: every peer in a process of its own instead of threads of this one")
     parser.add_argument("--verbose-rounds", action="store_true", help="print every launch of every timed round")
     parser.add_argument("--trace-round", action="store_true",
                         help="device mode with several GPUs: after the timed rounds, one round with per-CTA time stamps")
@@ -354,7 +408,8 @@ if __name__ == "__main__":
     if args.mode == "rpc_payload":
         for size_mb in args.sizes_mb:
             for codec_name in args.codecs:
-                benchmark_rpc_payload(args.num_peers, size_mb, codec_name, args.rounds, args.part_size_bytes, 0.5)
+                run = benchmark_rpc_payload_processes if args.peer_processes else benchmark_rpc_payload
+                run(args.num_peers, size_mb, codec_name, args.rounds, args.part_size_bytes, 0.5)
     elif args.mode == "device":
         benchmark_device(args.sizes_mb, args.codecs, args.rounds, args.warmup, args.emulate_ranks, args.part_size_bytes)
     else:
