@@ -194,7 +194,9 @@ class Matchmaking:
     async def _next_candidate(self, search: _Search) -> Optional[PeerID]:
         """The declared peer that precedes us most clearly in (expiration, id) order and was not asked yet."""
         listing = await self.group_key_manager.get_averagers(self.group_key_manager.current_key, only_active=True)
-        mine = (search.expiration, self.peer_id.to_bytes())
+        # a client-mode peer never leads, so nobody is "behind" it: it may ask any declared peer, whereas a regular peer
+        # only asks those whose turn to lead comes before its own (hivemind/averaging/matchmaking.py:392-401)
+        mine = (float("inf"), b"") if self.client_mode else (search.expiration, self.peer_id.to_bytes())
         best: Optional[Tuple[DHTExpiration, bytes, PeerID]] = None
         for peer, expiration in listing:
             if peer == self.peer_id:
@@ -213,8 +215,10 @@ class Matchmaking:
     # ------------------------------------------------------------------------------------------ follower side
     def _promised_start(self, search: _Search) -> DHTExpiration:
         """The latest moment by which we promise a leader to begin the all-reduce."""
-        if isfinite(search.expiration):
+        if isfinite(search.expiration) and not self.client_mode:
             return search.expiration
+        # nothing was declared (client mode): promise afresh, so that a leader that declared after our search began
+        # does not take us for a peer that ought to be leading it
         return search.desired_expiration(self.min_matchmaking_time)
 
     async def _propose(self, search: _Search, leader: PeerID) -> Optional[GroupInfo]:

@@ -87,14 +87,24 @@ def _make_tensors():
     (Fault.NONE, Fault.CANCEL),
 ])
 def test_fault_tolerance(fault0: Fault, fault1: Fault):
+    """Five peers in ONE group, two of them faulty. Whether all five find each other within the matchmaking window is
+    not what this test is about (on a loaded machine a peer can come late and the others start without it, which
+    changes every expected value), so an attempt whose group came out smaller is repeated."""
+    for attempt in range(4):
+        if _fault_tolerance_scenario(fault0, fault1):
+            return
+    pytest.fail("the five peers did not assemble into one group in four attempts")
+
+
+def _fault_tolerance_scenario(fault0: Fault, fault1: Fault) -> bool:
     torch.manual_seed(0)
     dht = DHT(start=True)
     averagers = []
     for i in range(5):
         averagers.append(FaultyAverager(
             _make_tensors(), DHT(initial_peers=dht.get_visible_maddrs(), start=True), prefix="test",
-            request_timeout=0.5, min_matchmaking_time=1.5, next_chunk_timeout=1.0, allreduce_timeout=6,
-            part_size_bytes=2 ** 16, client_mode=(i == 1), start=True,
+            request_timeout=0.5, min_matchmaking_time=2.0, target_group_size=5, next_chunk_timeout=1.0,
+            allreduce_timeout=6, part_size_bytes=2 ** 16, client_mode=(i == 1), start=True,
             fault=fault0 if i == 0 else fault1 if i == 1 else Fault.NONE))
     try:
         numerators, denominator = [0, 0, 0, 0], 0
@@ -114,8 +124,14 @@ def test_fault_tolerance(fault0: Fault, fault1: Fault):
         for averager, future in zip(averagers, futures):
             if averager.fault == Fault.CANCEL:
                 future.cancel()
+        group_sizes = []
         for future in futures[2:]:
-            assert future.result(timeout=30) is not None  # the healthy peers always finish
+            gathered = future.result(timeout=30)
+            assert gathered is not None  # the healthy peers always finish
+            group_sizes.append(len(gathered))
+        if Fault.CANCEL not in (fault0, fault1) and any(size != len(averagers) for size in group_sizes):
+            print(f"group sizes {group_sizes}: somebody missed the matchmaking window, repeating the attempt")
+            return False  # not the scenario under test
 
         for averager, previous in zip(averagers[2:], before[2:]):
             with averager.get_tensors() as tensors:
@@ -130,6 +146,7 @@ def test_fault_tolerance(fault0: Fault, fault1: Fault):
                 assert torch.all(torch.minimum(to_reference, to_local) < 1e-5)  # the average, or the old value
             else:
                 assert (to_reference < 1e-5).float().mean() > 0.5
+        return True
     finally:
         for averager in averagers:
             averager.shutdown()

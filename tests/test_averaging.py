@@ -215,3 +215,27 @@ def test_device_parts_come_in_whole_waves_of_the_grid():
                 assert chunks == 1
             else:  # the last wave is at least two thirds full: no CTA idles for most of a stage
                 assert parts > GRID_CTAS * (waves - 1) + GRID_CTAS * 2 // 3 or chunks == MAX_PART_CHUNKS
+
+
+def test_a_client_that_starts_searching_first_still_joins_the_group():
+    """A client-mode peer cannot lead, so it has to be able to join peers that declared themselves AFTER its own
+    search began (their turn to lead comes later than the moment the client first promised). With a full group the
+    round starts at once; a client that had to sit out its own matchmaking window first would join seconds later,
+    or miss a group that closes in the meantime."""
+    dhts = launch_dht_instances(3)
+    averagers = [DecentralizedAverager([torch.full((16,), float(i))], dhts[i], start=True, prefix="late_leaders",
+                                       target_group_size=3, min_matchmaking_time=4.0, request_timeout=1.0,
+                                       client_mode=(i == 0)) for i in range(3)]
+    try:
+        started = time.perf_counter()
+        client_step = averagers[0].step(wait=False, timeout=20, allow_retries=False)
+        time.sleep(0.1)  # the client has found the group key empty by now
+        others = [averager.step(wait=False, timeout=20, allow_retries=False) for averager in averagers[1:]]
+        for control in [client_step] + others:
+            assert len(control.result(30)) == 3
+        assert time.perf_counter() - started < 3.0, "the client waited out its own window before it asked anybody"
+        for averager in averagers:
+            with averager.get_tensors() as tensors:
+                assert torch.allclose(tensors[0], torch.full((16,), 1.0))
+    finally:
+        _shutdown(*averagers, *dhts)
