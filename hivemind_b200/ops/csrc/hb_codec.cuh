@@ -1,4 +1,4 @@
-// Codec geometry and small device helpers shared by the whole-tensor codec kernels (butterfly.cu) and the fused
+// Codec geometry and small device helpers shared by the whole-tensor codec kernels (codec.cu) and the fused
 // butterfly round kernel (butterfly_round.cu). Codec math follows hivemind/compression/floating.py:18-64 and
 // hivemind/compression/quantization.py:60-153.
 #pragma once
