@@ -98,7 +98,17 @@ class GradScaler(TorchGradScaler):
             with self._lock:
                 self._global_step(optimizer, *args, **kwargs)
             return True
-        super().step(optimizer)  # a local step of the collaborative optimizer: it accumulates and reports progress
+        # A local step of the collaborative optimizer: it accumulates and reports progress. The optimizer is handed this
+        # scaler explicitly (torch's own ``step`` does the same for optimizers whose ``step`` takes ``grad_scaler``,
+        # but announces that it will stop doing so).
+        if not self._enabled:
+            optimizer.step(*args, **kwargs)
+            return False
+        record = self._per_optimizer_states[id(optimizer)]
+        if record["stage"] is OptState.STEPPED:
+            raise RuntimeError("step() has already been called since the last update().")
+        optimizer.step(*args, **{**kwargs, "grad_scaler": self})
+        record["stage"] = OptState.STEPPED
         self._partial.add(id(optimizer))
         return False
 
