@@ -195,7 +195,8 @@ class Matchmaking:
         """The declared peer that precedes us most clearly in (expiration, id) order and was not asked yet."""
         listing = await self.group_key_manager.get_averagers(self.group_key_manager.current_key, only_active=True)
         # a client-mode peer never leads, so nobody is "behind" it: it may ask any declared peer, whereas a regular peer
-        # only asks those whose turn to lead comes before its own (hivemind/averaging/matchmaking.py:392-401)
+        # only asks those whose turn to lead comes before its own (hivemind/averaging/matchmaking.py:477-480, where a
+        # client's own expiration stays infinite because it never declares itself, and :254-260 for the promise)
         mine = (float("inf"), b"") if self.client_mode else (search.expiration, self.peer_id.to_bytes())
         best: Optional[Tuple[DHTExpiration, bytes, PeerID]] = None
         for peer, expiration in listing:
