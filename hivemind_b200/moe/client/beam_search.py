@@ -5,7 +5,7 @@ expert's score is the sum of its coordinates' scores. The search keeps the ``bea
 dimension; each DHT prefix entry maps "next coordinate" to one example expert below it, so that only
 ``O(beam_size * dims)`` DHT reads are needed however sparse the grid is. Misses can be written back as short-lived
 "nothing here" records (negative caching) so that other peers skip dead prefixes
-(reference: hivemind/moe/client/beam_search.py:26-420).
+(reference: hivemind/moe/client/beam_search.py:26-401).
 """
 from __future__ import annotations
 

@@ -3,7 +3,7 @@
 The call is an autograd function: forward serialises the inputs with the compression the expert's schema asks for,
 sends them (one unary message, or a chunked stream above ``MAX_UNARY_PAYLOAD_SIZE``) and returns the outputs;
 backward sends inputs and output gradients and returns input gradients — the server re-runs the forward pass and
-also trains the expert (reference: hivemind/moe/client/expert.py:33-243).
+also trains the expert (reference: hivemind/moe/client/expert.py:33-233).
 """
 from __future__ import annotations
 

@@ -2,7 +2,7 @@
 
 ``RemoteExpert.forward`` is a blocking autograd function, but the RPCs behind it are coroutines; this helper owns
 a daemon loop thread, started lazily and re-created after ``fork`` (reference:
-hivemind/moe/client/remote_expert_worker.py:11-48).
+hivemind/moe/client/remote_expert_worker.py:11-36).
 """
 from __future__ import annotations
 

@@ -1,6 +1,6 @@
 """Periodic expert checkpoints: ``<dir>/<uid>/checkpoint_<timestamp>.pt`` plus a ``checkpoint_last.pt`` link.
 
-Same on-disk layout as the reference (hivemind/moe/server/checkpoints.py:36-80) so that a server restarted with the
+Same on-disk layout as the reference (hivemind/moe/server/checkpoints.py:36-75) so that a server restarted with the
 same ``checkpoint_dir`` finds its experts again. A checkpoint is written under a temporary name inside the expert's
 directory and renamed, so a reader never sees a half-written file.
 """

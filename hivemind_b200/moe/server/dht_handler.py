@@ -3,7 +3,7 @@
 ``declare_experts`` stores, for each uid, ``uid -> peer id`` and for every proper prefix a dictionary entry
 ``prefix[next coordinate] -> (uid, peer id)`` (the index that beam search walks); ``DHTHandlerThread`` repeats that
 every ``update_period`` seconds so that the records outlive their expiration only while the server lives
-(reference: hivemind/moe/server/dht_handler.py:22-116).
+(reference: hivemind/moe/server/dht_handler.py:22-108).
 """
 from __future__ import annotations
 

@@ -1,6 +1,6 @@
 """``Server``: hosts experts — connection handlers in front, one ``Runtime`` behind, DHT declarations on the side.
 
-Behavioural contract from the reference (hivemind/moe/server/server.py:36-420): ``Server.create`` builds N identical
+Behavioural contract from the reference (hivemind/moe/server/server.py:36-411): ``Server.create`` builds N identical
 experts of a registered class with uids drawn from a pattern such as ``ffn.[0:32].[0:256]`` (skipping uids already
 taken in the DHT), restores checkpoints, and starts; a running server answers forward/backward RPCs and re-declares
 its experts every ``update_period`` seconds. Everything runs as threads of one process that owns one GPU: handler
