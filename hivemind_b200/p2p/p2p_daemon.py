@@ -17,6 +17,7 @@ import secrets
 import subprocess
 import tempfile
 import threading
+import time
 from contextlib import closing, suppress
 from dataclasses import dataclass
 from typing import AsyncIterator, Awaitable, Callable, List, Optional, Sequence, Tuple, Type, TypeVar, Union
@@ -124,6 +125,7 @@ class P2P:
         # same switch as for the reference's Go daemon (hivemind/p2p/p2p_daemon.py:222): the daemon's own log
         if os.environ.get("GOLOG_LOG_LEVEL", "").strip().lower() == "debug":
             args.append("--verbose")
+        spawned = time.monotonic()
         self._child = subprocess.Popen(args, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, bufsize=1)
         self._alive = True
         ready = asyncio.get_event_loop().create_future()
@@ -134,6 +136,10 @@ class P2P:
         self._reader_thread.start()
         try:
             await asyncio.wait_for(ready, startup_timeout)
+            # the limit is on the daemon, not on how promptly this loop gets to look: a daemon that needed longer has
+            # failed even if it is up by the time a busy loop checks
+            if time.monotonic() - spawned > startup_timeout:
+                raise asyncio.TimeoutError
         except asyncio.TimeoutError:
             await self.shutdown()
             raise P2PDaemonError(f"Daemon failed to start in {startup_timeout:.1f} seconds")
