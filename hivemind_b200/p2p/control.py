@@ -12,6 +12,7 @@ import os
 import struct
 from typing import Awaitable, Callable, Dict, Optional, Sequence, Tuple
 
+from hivemind_b200.p2p.chunked_reader import open_unix_stream, start_unix_stream_server
 from hivemind_b200.p2p.datastructures import PeerID, PeerInfo, StreamInfo
 from hivemind_b200.utils.logging import get_logger
 from hivemind_b200.utils.multiaddr import Multiaddr
@@ -128,7 +129,7 @@ class DaemonClient:
         self = cls(control_path, listen_path, **kwargs)
         if os.path.exists(listen_path):
             os.unlink(listen_path)
-        self._listener = await asyncio.start_unix_server(self._on_inbound_stream, path=listen_path)
+        self._listener = await start_unix_stream_server(self._on_inbound_stream, listen_path)
         await self._open_persistent()
         return self
 
@@ -152,7 +153,7 @@ class DaemonClient:
             pass
 
     async def _command(self, frame: bytes) -> Tuple[asyncio.StreamReader, asyncio.StreamWriter, _Reader]:
-        reader, writer = await asyncio.open_unix_connection(self.control_path, limit=2 ** 20)
+        reader, writer = await open_unix_stream(self.control_path, limit=2 ** 20)
         try:
             writer.write(frame)
             await writer.drain()

@@ -129,3 +129,104 @@ def test_client_commands_against_a_scripted_daemon(tmp_path):
             await server.wait_closed()
 
     run(main())
+
+
+def test_chunked_stream_reader_matches_the_standard_reader_on_random_traffic():
+    """Blocks of random sizes go in, reads of random sizes come out: same bytes, same EOF behaviour as
+    ``asyncio.StreamReader`` (whose interface it keeps for ``read`` / ``readexactly`` / ``at_eof``)."""
+    import asyncio
+    import random
+
+    from hivemind_b200.p2p.chunked_reader import ChunkedStreamReader
+
+    async def scenario():
+        rng = random.Random(0)
+        payload = bytes(rng.getrandbits(8) for _ in range(200_000))
+        for trial in range(20):
+            ours, theirs = ChunkedStreamReader(limit=4096), asyncio.StreamReader(limit=4096)
+            cursor = 0
+            while cursor < len(payload):
+                step = rng.choice([1, 7, 100, 4096, 65536])
+                for reader in (ours, theirs):
+                    reader.feed_data(payload[cursor:cursor + step])
+                cursor += step
+            for reader in (ours, theirs):
+                reader.feed_eof()
+            collected = []
+            while True:
+                if rng.random() < 0.5:
+                    n = rng.choice([1, 2, 9, 1000, 50_000])
+                    a, b = await ours.read(n), await theirs.read(n)
+                else:
+                    n = rng.choice([1, 8, 333, 70_000])
+                    results = []
+                    for reader in (ours, theirs):
+                        try:
+                            results.append(await reader.readexactly(n))
+                        except asyncio.IncompleteReadError as e:
+                            results.append(("incomplete", e.partial, e.expected))
+                    a, b = results
+                assert a == b
+                collected.append(a if isinstance(a, bytes) else a[1])
+                assert ours.at_eof() == theirs.at_eof()
+                if ours.at_eof():
+                    break
+            assert b"".join(collected) == payload
+            assert await ours.read(10) == b"" and await ours.read() == b""
+        assert await ChunkedStreamReader().read(0) == b"" and await ChunkedStreamReader().readexactly(0) == b""
+        with pytest.raises(ValueError):
+            await ChunkedStreamReader().readexactly(-1)
+        with pytest.raises(NotImplementedError):
+            await ChunkedStreamReader().readline()
+
+    asyncio.new_event_loop().run_until_complete(scenario())
+
+
+def test_chunked_stream_reader_waits_pauses_and_reports_errors():
+    import asyncio
+
+    from hivemind_b200.p2p.chunked_reader import ChunkedStreamReader
+
+    class FakeTransport:
+        def __init__(self):
+            self.paused, self.events = False, []
+
+        def pause_reading(self):
+            self.paused = True
+            self.events.append("pause")
+
+        def resume_reading(self):
+            self.paused = False
+            self.events.append("resume")
+
+    async def scenario():
+        reader, transport = ChunkedStreamReader(limit=100), FakeTransport()
+        reader.set_transport(transport)
+        pending = asyncio.ensure_future(reader.readexactly(250))  # larger than twice the limit
+        await asyncio.sleep(0)
+        for _ in range(5):
+            reader.feed_data(b"x" * 60)  # the third block crosses the high-water mark and pauses the transport
+            await asyncio.sleep(0)  # ... the waiting read resumes it: it still needs bytes
+        assert await asyncio.wait_for(pending, 1) == b"x" * 250
+        assert transport.events[:2] == ["pause", "resume"] and not transport.paused
+        assert await reader.read(1000) == b"x" * 50
+
+        reader.feed_data(b"y" * 300)
+        assert transport.paused
+        assert await reader.read(250) == b"y" * 250 and not transport.paused, "draining below the limit resumes"
+
+        waiting = asyncio.ensure_future(reader.read(10))
+        await asyncio.sleep(0)
+        reader.feed_data(b"tail")
+        assert await asyncio.wait_for(waiting, 1) == b"yyyyyyyyyy"
+
+        broken = ChunkedStreamReader()
+        waiter = asyncio.ensure_future(broken.readexactly(4))
+        await asyncio.sleep(0)
+        broken.set_exception(ConnectionResetError("peer went away"))
+        with pytest.raises(ConnectionResetError):
+            await waiter
+        with pytest.raises(ConnectionResetError):
+            await broken.read(1)
+
+    asyncio.new_event_loop().run_until_complete(scenario())
