@@ -25,7 +25,7 @@ import torch
 
 from hivemind_b200.averaging.partition import AllreduceException, BannedException, TensorPartContainer, TensorPartReducer
 from hivemind_b200.compression import deserialize_torch_tensor, serialize_torch_tensor
-from hivemind_b200.compression.serialization import RawMessage, _varint
+from hivemind_b200.compression.serialization import RawMessage, TensorView, _varint, split_length_delimited_field
 from hivemind_b200.p2p import P2P, P2PContext, PeerID, ServicerBase, StubBase
 from hivemind_b200.proto import averaging_pb2
 from hivemind_b200.utils import get_logger
@@ -36,6 +36,24 @@ GroupID = bytes
 logger = get_logger(__name__)
 _Msg = averaging_pb2.AveragingData
 _TENSOR_PART_TAG = bytes([(4 << 3) | 2])  # AveragingData.tensor_part: field 4, length-delimited
+
+
+class PartMessage:
+    """A received ``AveragingData`` whose tensor part is not parsed: the half-megabyte payload stays a view of the
+    received bytes until a codec reads it (``FromString`` is what the RPC layer calls on arrival). Attribute access
+    is that of the generated message for the fields this protocol uses."""
+
+    __slots__ = ("code", "group_id", "peer_id", "weight", "tensor_part")
+    _NO_TENSOR = averaging_pb2.AveragingData().tensor_part
+
+    @classmethod
+    def FromString(cls, payload: bytes) -> "PartMessage":
+        part, rest = split_length_delimited_field(memoryview(payload), 4)
+        small = _Msg.FromString(rest)
+        self = cls()
+        self.code, self.group_id, self.peer_id, self.weight = small.code, small.group_id, small.peer_id, small.weight
+        self.tensor_part = TensorView(part) if part is not None else cls._NO_TENSOR
+        return self
 
 
 def _part_message(tensor_part, **small_fields) -> RawMessage:

@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from hivemind_b200.utils.asyncio import spawn
-from hivemind_b200.averaging.allreduce import AllreduceException, AllReduceRunner, AveragingMode, GroupID
+from hivemind_b200.averaging.allreduce import AllreduceException, AllReduceRunner, AveragingMode, GroupID, PartMessage
 from hivemind_b200.averaging.control import AveragingStage, StepControl
 from hivemind_b200.averaging.group_info import GroupInfo
 from hivemind_b200.averaging.load_balancing import load_balance_peers
@@ -469,8 +469,8 @@ class DecentralizedAverager(ServicerBase):
         async for response in self._matchmaking.rpc_join_group(request, context):
             yield response
 
-    async def rpc_aggregate_part(self, stream: AsyncIterator[averaging_pb2.AveragingData], context: P2PContext
-                                 ) -> AsyncIterator[averaging_pb2.AveragingData]:
+    async def rpc_aggregate_part(self, stream: AsyncIterator[PartMessage], context: P2PContext
+                                 ) -> AsyncIterator[PartMessage]:
         """A groupmate sends us parts of the span that we reduce; forwarded to the round's ``AllReduceRunner``."""
         request = await anext(stream)
         if request.group_id not in self._running_groups:

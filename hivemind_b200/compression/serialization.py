@@ -2,7 +2,7 @@
 hivemind/utils/streaming.py:14-46)."""
 from __future__ import annotations
 
-from typing import AsyncIterator, Dict, Iterable, Iterator, List, Optional
+from typing import AsyncIterator, Dict, Iterable, Iterator, List, Optional, Tuple
 
 import torch
 
@@ -207,3 +207,78 @@ async def deserialize_tensor_stream_into(stream: AsyncIterator[Iterable[runtime_
                 parts.append(chunk)
     finish()
     return tensors
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Reading large tensors off the wire without parsing them: a received message is scanned once at field level, the
+# tensor's ``buffer`` stays a view of the received bytes, and only the remaining (small) fields go through protobuf.
+# The views quack like the generated messages for everything the codecs and the averaging code read from them.
+# ---------------------------------------------------------------------------------------------------------------
+
+
+def _read_varint(view: memoryview, offset: int) -> Tuple[int, int]:
+    value = shift = 0
+    while True:
+        byte = view[offset]
+        offset += 1
+        value |= (byte & 0x7F) << shift
+        if not byte & 0x80:
+            return value, offset
+        shift += 7
+        if shift > 63:
+            raise ValueError("malformed varint in a protobuf message")
+
+
+def split_length_delimited_field(message: memoryview, field_number: int) -> Tuple[Optional[memoryview], bytes]:
+    """Scan the top level of a serialized protobuf ``message``: returns a view of the (last) length-delimited value of
+    ``field_number`` and the bytes of all other fields, which are a valid serialized message of the same type."""
+    wanted, others, offset, end = None, [], 0, len(message)
+    while offset < end:
+        start = offset
+        tag, offset = _read_varint(message, offset)
+        number, wire_type = tag >> 3, tag & 7
+        if wire_type == 0:
+            _, offset = _read_varint(message, offset)
+        elif wire_type == 1:
+            offset += 8
+        elif wire_type == 5:
+            offset += 4
+        elif wire_type == 2:
+            length, offset = _read_varint(message, offset)
+            if number == field_number:
+                wanted = message[offset:offset + length]
+                offset += length
+                if offset > end:
+                    raise ValueError("truncated protobuf message")
+                continue
+            offset += length
+        else:
+            raise ValueError(f"unsupported protobuf wire type {wire_type}")
+        if offset > end:
+            raise ValueError("truncated protobuf message")
+        others.append(message[start:offset])
+    return wanted, b"".join(others)
+
+
+class TensorView:
+    """A received ``runtime_pb2.Tensor`` whose ``buffer`` is a view of the bytes it arrived in."""
+
+    __slots__ = ("buffer", "_meta")
+
+    def __init__(self, serialized: memoryview):
+        buffer, rest = split_length_delimited_field(serialized, 1)
+        self.buffer = buffer if buffer is not None else memoryview(b"")
+        self._meta = runtime_pb2.Tensor.FromString(rest)
+
+    size = property(lambda self: self._meta.size)
+    dtype = property(lambda self: self._meta.dtype)
+    compression = property(lambda self: self._meta.compression)
+    requires_grad = property(lambda self: self._meta.requires_grad)
+    chunks = property(lambda self: self._meta.chunks)
+
+    def to_message(self) -> runtime_pb2.Tensor:
+        """An ordinary protobuf message with the same content (copies the buffer)."""
+        message = runtime_pb2.Tensor()
+        message.CopyFrom(self._meta)
+        message.buffer = bytes(self.buffer)
+        return message

@@ -1,5 +1,6 @@
 """Codec accuracy and round trips on CPU (thresholds of the reference's tests/test_compression.py:33-119)."""
 import asyncio
+import struct
 
 import pytest
 import torch
@@ -103,3 +104,48 @@ def test_dynamic_code_table_shape():
     assert code.numel() == 256 and float(code.max()) == 1.0 and (code == 0).any()
     assert torch.equal(code, code.sort().values) and float(code.min()) < -0.9
     assert len(set(code.tolist())) >= 255
+
+
+def test_received_messages_can_be_read_without_parsing_the_payload():
+    """``split_length_delimited_field`` / ``TensorView`` / ``PartMessage``: the big ``buffer`` field stays a view of the
+    received bytes, everything else equals what protobuf parses, for every codec and for odd messages."""
+    from hivemind_b200.averaging.allreduce import PartMessage, _part_message
+    from hivemind_b200.compression.serialization import TensorView, split_length_delimited_field
+    from hivemind_b200.proto import averaging_pb2, runtime_pb2
+
+    torch.manual_seed(0)
+    tensor = torch.randn(3, 777)
+    for name in runtime_pb2.CompressionType.keys():
+        codec = runtime_pb2.CompressionType.Value(name)
+        serialized = serialize_torch_tensor(tensor, codec)
+        wire = serialized.SerializeToString()
+        view = TensorView(memoryview(wire))
+        assert (list(view.size), view.dtype, view.compression, view.requires_grad, view.chunks) == (
+            list(serialized.size), serialized.dtype, serialized.compression, serialized.requires_grad, serialized.chunks)
+        assert bytes(view.buffer) == serialized.buffer and view.to_message() == serialized
+        assert view.buffer.obj is wire, "the payload is a view of the received bytes, not a copy"
+        assert torch.equal(deserialize_torch_tensor(view), deserialize_torch_tensor(serialized))
+
+        outer = _part_message(serialized, code=averaging_pb2.PART_FOR_AVERAGING, group_id=b"g" * 20, weight=0.75)
+        parsed = averaging_pb2.AveragingData.FromString(outer.SerializeToString())
+        lazy = PartMessage.FromString(outer.SerializeToString())
+        assert parsed.tensor_part == serialized and parsed.weight == 0.75, "any protobuf parser reads the raw form"
+        assert (lazy.code, lazy.group_id, lazy.peer_id, lazy.weight) == (parsed.code, parsed.group_id, parsed.peer_id, 0.75)
+        assert torch.equal(deserialize_torch_tensor(lazy.tensor_part), deserialize_torch_tensor(serialized))
+
+    # messages without a tensor, with fields in another order, with unknown fields of every wire type
+    bare = PartMessage.FromString(averaging_pb2.AveragingData(code=averaging_pb2.CANCELLED).SerializeToString())
+    assert bare.code == averaging_pb2.CANCELLED and len(bare.tensor_part.buffer) == 0 and bare.weight == 0.0
+    inner = runtime_pb2.Tensor(buffer=b"abc", dtype="uint8", size=[3]).SerializeToString()
+    shuffled = (b"\x22" + bytes([len(inner)]) + inner      # tensor_part first
+                + b"\x29" + struct.pack("<d", 2.5)           # weight (fixed64)
+                + b"\x98\x06\x07"                          # unknown field 99, varint
+                + b"\x9d\x06" + b"\x01\x02\x03\x04"       # unknown field 99, fixed32
+                + b"\x08\x05")                             # code last
+    lazy = PartMessage.FromString(shuffled)
+    assert (lazy.code, lazy.weight, bytes(lazy.tensor_part.buffer), lazy.tensor_part.dtype) == (5, 2.5, b"abc", "uint8")
+    wanted, rest = split_length_delimited_field(memoryview(shuffled), 4)
+    assert bytes(wanted) == inner and averaging_pb2.AveragingData.FromString(rest).code == 5
+    for broken in (b"\x22\x7f" + b"x", b"\x08", b"\x0b", b"\x29\x00"):
+        with pytest.raises((ValueError, IndexError)):
+            split_length_delimited_field(memoryview(broken), 4)
