@@ -307,10 +307,11 @@ class AllReduceRunner(ServicerBase):
         if self._future.done():
             logger.debug(f"{self}: already finalized ({self._future})")
             return False
-        if cancel:
+        if cancel or isinstance(exception, asyncio.CancelledError):
             self._future.cancel()
         elif exception is not None:
             self._future.set_exception(exception)
+            self._future.exception()  # the future only records how the round ended; nobody awaits it
         else:
             self._future.set_result(None)
         logger.debug(f"{self}: finalized ({'cancelled' if cancel else repr(exception) if exception else 'ok'})")

@@ -398,6 +398,9 @@ class P2P:
 
         # requests start flowing right away, even if the caller reads the responses later
         writing_task = asyncio.create_task(_write_to_stream())
+        # its outcome is collected below when the responses end normally; if the caller leaves earlier, a failure of
+        # the writing side (typically: the connection went away) has nobody to report to
+        writing_task.add_done_callback(lambda task: task.cancelled() or task.exception())
 
         async def _read_from_stream() -> AsyncIterator[Message]:
             with closing(writer):
