@@ -119,6 +119,7 @@ class DaemonClient:
         self._pers_writer: Optional[asyncio.StreamWriter] = None
         self._pers_task: Optional[asyncio.Task] = None
         self._pending: Dict[bytes, asyncio.Future] = {}
+        self._caller_ids: Dict[bytes, PeerID] = {}
         self._serving: Dict[bytes, asyncio.Task] = {}
         self._write_lock = asyncio.Lock()
         self._closed = False
@@ -267,7 +268,7 @@ class DaemonClient:
                             fut.set_result(data)
                 elif msg_type == P_REQUEST:
                     call_id, peer, proto, data = body.blob(), body.blob(), body.blob().decode("utf-8"), body.blob()
-                    task = asyncio.create_task(self._serve_unary(call_id, PeerID.from_base58(peer.decode("ascii")), proto, data))
+                    task = asyncio.create_task(self._serve_unary(call_id, self._caller_id(peer), proto, data))
                     self._serving[call_id] = task
                     task.add_done_callback(lambda _t, cid=call_id: self._serving.pop(cid, None))
                 elif msg_type == P_CANCEL:
@@ -300,6 +301,16 @@ class DaemonClient:
             await self._send_persistent(frame)
         except Exception:
             pass
+
+    def _caller_id(self, text: bytes) -> PeerID:
+        """The ``PeerID`` for the base58 text that the daemon puts in front of an incoming call; the same few callers
+        come back thousands of times, so the decoded ids are kept."""
+        known = self._caller_ids.get(text)
+        if known is None:
+            if len(self._caller_ids) >= 4096:
+                self._caller_ids.clear()
+            known = self._caller_ids[text] = PeerID.from_base58(text.decode("ascii"))
+        return known
 
     async def _request(self, frame: bytes, call_id: bytes) -> bytes:
         fut = asyncio.get_event_loop().create_future()
