@@ -265,9 +265,9 @@ class DHTProtocol(ServicerBase):
             else:
                 result = dht_pb2.FindResult(type=dht_pb2.FOUND_REGULAR, value=held.value,
                                             expiration_time=held.expiration_time)
-            for node, address in self.routing_table.get_nearest_neighbors(key_id, k=self.bucket_size, exclude=sender):
-                result.nearest_node_ids.append(node.to_bytes())
-                result.nearest_peer_ids.append(address.to_bytes())
+            nearest = self.routing_table.get_nearest_neighbors(key_id, k=self.bucket_size, exclude=sender)
+            result.nearest_node_ids.extend([node.to_bytes() for node, _ in nearest])
+            result.nearest_peer_ids.extend([address.to_bytes() for _, address in nearest])
             results.append(result)
         return dht_pb2.FindResponse(results=results, peer=self.node_info)
 
