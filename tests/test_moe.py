@@ -354,7 +354,6 @@ def test_connection_handler_rpcs(hidden_dim=16):
         RemoteExpertWorker.run_coroutine(_exercise())
         # a large batch goes through the streamed RPCs (over the unary payload limit)
         expert = create_remote_experts([ExpertInfo("expert.0", dht.peer_id)], client)[0]
-        big = torch.randn(4096, hidden_dim * 16)[:, :hidden_dim].contiguous().repeat(1, 1)
         wide = torch.randn(40000, hidden_dim)  # 2.5 MB > 2 MiB unary limit
         with pytest.raises(Exception):
             expert(wide)  # exceeds max_batch_size on the server: the error is propagated, not a hang

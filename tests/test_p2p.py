@@ -81,11 +81,10 @@ def test_unary_and_errors_and_cancel():
         await asyncio.sleep(0.3)
         task.cancel()
         await asyncio.wait_for(cancelled.wait(), 5)  # the cancel reaches the remote handler
-        # a large unary payload (1 MiB) survives the trip
-        big = test_pb2.TestRequest(number=7)
+        # a handler that was withdrawn is gone for callers
         await server.remove_protobuf_handler("square")
         with pytest.raises(P2PHandlerError):
-            await client.call_protobuf_handler(server.peer_id, "square", big, test_pb2.TestResponse)
+            await client.call_protobuf_handler(server.peer_id, "square", test_pb2.TestRequest(number=7), test_pb2.TestResponse)
         await client.shutdown()
         await server.shutdown()
 
