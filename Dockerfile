@@ -11,7 +11,7 @@ RUN python3 -m venv /opt/venv
 ENV PATH="/opt/venv/bin:${PATH}"
 RUN pip install --no-cache-dir torch --index-url https://download.pytorch.org/whl/cu128
 RUN pip install --no-cache-dir numpy msgpack protobuf cryptography pydantic scipy pyyaml sortedcontainers packaging \
-    pytest pytest-timeout scikit-learn
+    pytest pytest-timeout scikit-learn sentencepiece idna
 
 WORKDIR /workspace/hivemind_b200
 COPY . .
