@@ -5,6 +5,8 @@ import subprocess
 import sys
 import time
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ENV = dict(os.environ, PYTHONPATH=ROOT, PYTHONUNBUFFERED="1")
 COMMON = ["--run_id", "example_test", "--host_maddrs", "/ip4/127.0.0.1/tcp/0"]
@@ -74,6 +76,7 @@ def test_tokenized_corpus_feeds_the_trainer(tmp_path):
 
     import torch
 
+    pytest.importorskip("sentencepiece")
     rng = random.Random(0)
     words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta", "eta", "theta", "iota", "kappa", "lambda", "mu"]
     with open(tmp_path / "corpus.txt", "w") as corpus:
