@@ -25,7 +25,8 @@ import torch
 
 from hivemind_b200.averaging.partition import AllreduceException, BannedException, TensorPartContainer, TensorPartReducer
 from hivemind_b200.compression import deserialize_torch_tensor, serialize_torch_tensor
-from hivemind_b200.compression.serialization import RawMessage, TensorView, _varint, split_length_delimited_field
+from hivemind_b200.compression.serialization import (RawMessage, TensorView, _varint, is_light_to_decode,
+                                                     is_light_to_encode, split_length_delimited_field)
 from hivemind_b200.p2p import P2P, P2PContext, PeerID, ServicerBase, StubBase
 from hivemind_b200.proto import averaging_pb2
 from hivemind_b200.utils import get_logger
@@ -210,7 +211,8 @@ class AllReduceRunner(ServicerBase):
 
             received = 0
             async for delta in amap_in_executor(decode, aiter_with_timeout(incoming, self.reducer_timeout),
-                                                max_prefetch=container.prefetch):
+                                                max_prefetch=container.prefetch,
+                                                inline=lambda message: is_light_to_decode(message.tensor_part)):
                 container.register_processed_part(reducer_index, received, delta)
                 received += 1
             expected = container.num_parts_by_peer[reducer_index]
@@ -279,14 +281,18 @@ class AllReduceRunner(ServicerBase):
 
         try:
             async for part, weight, codec in amap_in_executor(decode, aiter_with_timeout(stream, self.sender_timeout),
-                                                              max_prefetch=self.tensor_part_container.prefetch):
+                                                              max_prefetch=self.tensor_part_container.prefetch,
+                                                              inline=lambda message: is_light_to_decode(message.tensor_part)):
                 try:
                     average = await self.tensor_part_reducer.accumulate_part(sender_index, reduced, part, weight=weight)
                 except BannedException:
                     logger.debug(f"sender {sender_index} was banned while its part was waiting")
                     break
                 reduced += 1
-                delta = await loop.run_in_executor(None, lambda: serialize_torch_tensor(average - part, codec))
+                if is_light_to_encode(part, codec):
+                    delta = serialize_torch_tensor(average - part, codec)
+                else:
+                    delta = await loop.run_in_executor(None, lambda: serialize_torch_tensor(average - part, codec))
                 yield _part_message(delta, code=averaging_pb2.AVERAGED_PART)
         finally:
             if reduced != self.tensor_part_reducer.num_parts:

@@ -16,7 +16,9 @@ from typing import AsyncIterable, AsyncIterator, Deque, List, Optional, Sequence
 import numpy as np
 import torch
 
-from hivemind_b200.compression import CompressionBase, CompressionInfo, NoCompression
+from hivemind_b200.compression import (CompressionBase, CompressionInfo, Float16Compression, NoCompression,
+                                       ScaledFloat16Compression)
+from hivemind_b200.compression.serialization import is_light_to_encode
 from hivemind_b200.proto import runtime_pb2
 from hivemind_b200.utils import amap_in_executor, as_aiter, get_logger
 
@@ -137,8 +139,10 @@ class TensorPartContainer:
         assert not self._inputs_consumed_by_peer[peer_index], "input parts of a given peer are already deallocated."
         self._inputs_consumed_by_peer[peer_index] = True
         parts_aiter = as_aiter(*self._input_parts_by_peer[peer_index])
-        async for serialized_part in amap_in_executor(lambda x_and_info: self.compression.compress(*x_and_info),
-                                                      parts_aiter, max_prefetch=self.prefetch):
+        light = isinstance(self.compression, (NoCompression, Float16Compression, ScaledFloat16Compression))
+        async for serialized_part in amap_in_executor(
+                lambda x_and_info: self.compression.compress(*x_and_info), parts_aiter, max_prefetch=self.prefetch,
+                inline=lambda x_and_info: light and is_light_to_encode(x_and_info[0], runtime_pb2.CompressionType.NONE)):
             yield serialized_part
         self._input_parts_by_peer[peer_index].clear()
 

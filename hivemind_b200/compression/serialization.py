@@ -282,3 +282,20 @@ class TensorView:
         message.CopyFrom(self._meta)
         message.buffer = bytes(self.buffer)
         return message
+
+
+# Codecs whose work on a part of a megabyte or so is a type conversion or less: cheaper to run where the data is than
+# to hand to another thread (the quantising codecs sort, search or histogram and do belong in a thread).
+_LIGHT_CODECS = (CompressionType.NONE, CompressionType.FLOAT16, CompressionType.MEANSTD_16BIT)
+LIGHT_WORK_MAX_BYTES = 4 * 2 ** 20
+
+
+def is_light_to_decode(serialized_tensor) -> bool:
+    """Whether decoding this message is too little work to be worth a trip through a thread pool."""
+    return serialized_tensor.compression in _LIGHT_CODECS and len(serialized_tensor.buffer) <= LIGHT_WORK_MAX_BYTES
+
+
+def is_light_to_encode(tensor: torch.Tensor, compression_type: int) -> bool:
+    """The same question before encoding ``tensor`` with the codec of this wire type."""
+    return (compression_type in _LIGHT_CODECS and not tensor.is_cuda
+            and tensor.numel() * tensor.element_size() <= LIGHT_WORK_MAX_BYTES)

@@ -186,16 +186,32 @@ async def cancel_and_wait(awaitable: Awaitable) -> bool:
 
 
 async def amap_in_executor(func: Callable[..., T], *iterables: AsyncIterable, max_prefetch: int = 1,
-                           executor: Optional[ThreadPoolExecutor] = None) -> AsyncIterator[T]:
-    """Map ``func`` over async iterables in a thread pool, keeping at most ``max_prefetch`` results in flight."""
+                           executor: Optional[ThreadPoolExecutor] = None,
+                           inline: Optional[Callable[..., bool]] = None) -> AsyncIterator[T]:
+    """Map ``func`` over async iterables in a thread pool, keeping at most ``max_prefetch`` results in flight.
+
+    :param inline: if given and ``inline(*args)`` is true, ``func(*args)`` runs in the event loop itself: handing an
+      item to a thread and waking the loop again costs more than, say, viewing half a megabyte as a tensor
+    """
     assert max_prefetch > 0, "max_prefetch must be positive"
     loop = asyncio.get_event_loop()
     queue: asyncio.Queue = asyncio.Queue(max_prefetch)
 
+    def _computed_here(args) -> asyncio.Future:
+        done = loop.create_future()
+        try:
+            done.set_result(func(*args))
+        except Exception as e:
+            done.set_exception(e)
+        return done
+
     async def _produce():
         try:
             async for args in azip(*iterables):
-                await queue.put(loop.run_in_executor(executor, func, *args))
+                if inline is not None and inline(*args):
+                    await queue.put(_computed_here(args))
+                else:
+                    await queue.put(loop.run_in_executor(executor, func, *args))
             await queue.put(None)
         except asyncio.CancelledError:
             raise  # the consumer is gone (it cancels the producer on its way out): nobody is left to tell
