@@ -364,3 +364,32 @@ def test_a_thousand_futures_between_threads():
         assert kind == plan[i]
         assert value == (i * i if kind == "result" else i)
     assert all(f.done() for f in futures)
+
+
+def test_amap_in_executor_mixes_inline_and_threaded_items_in_order():
+    """Items that ``inline`` picks are computed in the loop's own thread, the others in the pool; results come out in
+    input order either way, and an exception of either kind is raised at its position."""
+    async def scenario():
+        loop_thread = threading.get_ident()
+        where = {}
+
+        def work(x):
+            where[x] = threading.get_ident()
+            if x == 7:
+                raise ValueError("seven")
+            time.sleep(0.01 if x % 2 else 0)
+            return x * x
+
+        results = [r async for r in amap_in_executor(work, as_aiter(*range(6)), max_prefetch=3,
+                                                      inline=lambda x: x % 2 == 0)]
+        assert results == [x * x for x in range(6)]
+        assert all(where[x] == loop_thread for x in (0, 2, 4)) and all(where[x] != loop_thread for x in (1, 3, 5))
+
+        for failing_inline in (True, False):
+            seen = []
+            with pytest.raises(ValueError, match="seven"):
+                async for r in amap_in_executor(work, as_aiter(5, 6, 7, 8), inline=lambda x: failing_inline):
+                    seen.append(r)
+            assert seen == [25, 36]
+
+    asyncio.new_event_loop().run_until_complete(scenario())
