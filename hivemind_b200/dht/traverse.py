@@ -71,7 +71,7 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
     unfinished = set(queries)
     candidates: Dict[DHTID, List[Tuple[int, DHTID]]] = {}
     nearest: Dict[DHTID, List[Tuple[int, DHTID]]] = {}
-    known: Dict[DHTID, Set[DHTID]] = {q: set(initial_nodes) for q in queries}
+    known: Dict[DHTID, Set[DHTID]] = {}
     visited: Dict[DHTID, Set[DHTID]] = {q: set((visited_nodes or {}).get(q, ())) for q in queries}
     active = Counter({q: 0 for q in queries})
     pending_tasks: Set[asyncio.Task] = set()
@@ -81,10 +81,14 @@ async def traverse_dht(queries: Collection[DHTID], initial_nodes: List[DHTID], b
     # ids are ints: ``a ^ b`` is the XOR metric without a Python-level call, which matters in these inner loops
     for q in queries:
         already = visited[q]
-        cands = [(q ^ n, n) for n in initial_nodes if n not in already]
+        # Of the starting nodes only the beam_size nearest can ever be visited: the search never goes beyond the
+        # beam_size-th best node known, and nodes only get added to that set. The others are dropped here, which keeps
+        # the per-query heaps and sets small when many queries share one long list of starting nodes.
+        cands = heapq.nsmallest(beam_size, [(q ^ n, n) for n in initial_nodes if n not in already])
+        known[q] = {n for _, n in cands}
         heapq.heapify(cands)
         candidates[q] = cands
-        best = [(-d, n) for d, n in heapq.nsmallest(beam_size, cands)]
+        best = [(-d, n) for d, n in cands]
         heapq.heapify(best)
         nearest[q] = best
 
