@@ -67,7 +67,7 @@ class DHTProtocol(ServicerBase):
         self.client_mode, self.record_validator, self.authorizer = client_mode, record_validator, authorizer
         self.storage, self.cache = DHTLocalStorage(), DHTLocalStorage(maxsize=cache_size)
         self.routing_table = RoutingTable(node_id, bucket_size, depth_modulo)
-        self._known_pairs: Dict[bytes, Tuple[DHTID, PeerID]] = {}
+        self._known_pairs: Dict[bytes, Tuple[DHTID, PeerID, bytes]] = {}
         self.rpc_semaphore = asyncio.Semaphore(2 ** 15 if parallel_rpc is None else parallel_rpc)
         # clients are never routed to, so they announce no id and serve no requests
         self.node_info = dht_pb2.NodeInfo() if client_mode else dht_pb2.NodeInfo(node_id=node_id.to_bytes())
@@ -218,7 +218,7 @@ class DHTProtocol(ServicerBase):
                 neighbours = {}
                 for node_bytes, peer_bytes in zip(result.nearest_node_ids, result.nearest_peer_ids):
                     pair = known_pairs.get(node_bytes)
-                    if pair is None or pair[1].to_bytes() != peer_bytes:
+                    if pair is None or pair[2] != peer_bytes:
                         pair = self._node_and_peer(node_bytes, peer_bytes)
                     neighbours[pair[0]] = pair[1]
                 outcome[key_id] = self._decode_find_result(key_id, result), neighbours
@@ -227,14 +227,14 @@ class DHTProtocol(ServicerBase):
                 return None
         return outcome
 
-    def _node_and_peer(self, node_bytes: bytes, peer_bytes: bytes) -> Tuple[DHTID, PeerID]:
+    def _node_and_peer(self, node_bytes: bytes, peer_bytes: bytes) -> Tuple[DHTID, PeerID, bytes]:
         """(node id, peer id) objects for a routing entry of a reply. A swarm of n peers mentions the same n pairs
         over and over (up to ``bucket_size`` per key and reply), so the objects are made once and shared."""
         pair = self._known_pairs.get(node_bytes)
-        if pair is None or pair[1].to_bytes() != peer_bytes:
+        if pair is None or pair[2] != peer_bytes:
             if len(self._known_pairs) >= self.MAX_KNOWN_PAIRS:
                 self._known_pairs.clear()
-            pair = self._known_pairs[node_bytes] = (DHTID.from_bytes(node_bytes), PeerID(peer_bytes))
+            pair = self._known_pairs[node_bytes] = (DHTID.from_bytes(node_bytes), PeerID(peer_bytes), peer_bytes)
         return pair
 
     def _decode_find_result(self, key_id: DHTID, result: dht_pb2.FindResult
