@@ -355,3 +355,35 @@ def test_grad_averager_refuses_buffers_of_the_wrong_shape(factory):
                  start=True, averaged_grads=[torch.zeros(5, 5, 1)])
     finally:
         dht.shutdown()
+
+
+def test_user_supplied_gradient_buffers_receive_the_average():
+    """Buffers passed as ``averaged_grads`` are the averaged tensors themselves on the CPU path: after a round the
+    caller finds the result in the objects it handed in (on CUDA the tensors move into a device arena and
+    ``get_tensors()`` is the way to read them, which the averager says in its log)."""
+    from hivemind_b200 import DHT
+
+    first = DHT(start=True)
+    second = DHT(initial_peers=first.get_visible_maddrs(), start=True)
+    models = [torch.nn.Linear(3, 2) for _ in range(2)]
+    buffers = [[torch.zeros_like(p) for p in model.parameters()] for model in models]
+    averagers = [GradientAverager(model.parameters(), dht=dht, prefix="own_buffers", target_group_size=2,
+                                  min_matchmaking_time=1.0, reuse_grad_buffers=False, start=True, averaged_grads=own)
+                 for model, dht, own in zip(models, (first, second), buffers)]
+    try:
+        for index, (model, averager) in enumerate(zip(models, averagers)):
+            model(torch.ones(4, 3) * (index + 1)).sum().backward()
+            averager.accumulate_grads_(batch_size=4)
+        expected = [(a.grad + b.grad) / 2 for a, b in zip(models[0].parameters(), models[1].parameters())]
+        controls = [averager.step(wait=False, timeout=30) for averager in averagers]
+        for control in controls:
+            control.result(60)
+        for own in buffers:
+            for buffer, reference in zip(own, expected):
+                assert torch.allclose(buffer, reference, atol=1e-6), "the caller's own buffer holds the average"
+        with averagers[0].use_averaged_gradients():
+            for p, reference in zip(models[0].parameters(), expected):
+                assert torch.allclose(p.grad, reference, atol=1e-6)
+    finally:
+        for item in (*averagers, second, first):
+            item.shutdown()
