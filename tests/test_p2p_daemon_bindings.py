@@ -185,6 +185,10 @@ def test_peer_ids_and_infos_convert_to_and_from_messages():
     assert sorted([PeerID(b"\x12\x01b"), PeerID(b"\x12\x01a")])[0] == PeerID(b"\x12\x01a")
     with pytest.raises(TypeError):
         peer_id < PEER_TEXT
+    import copy
+    import pickle
+    for twin in (pickle.loads(pickle.dumps(peer_id)), copy.copy(peer_id), copy.deepcopy(peer_id), PeerID(PEER_BYTES)):
+        assert twin == peer_id and twin.to_base58() == PEER_TEXT and hash(twin) == hash(peer_id)
 
     info = PeerInfo(peer_id, [ADDR, Multiaddr("/ip6/::1/udp/9/quic")])
     message = info.to_protobuf()
