@@ -101,6 +101,17 @@ def get_chunk_size(num_elements: int, min_chunk_size: int) -> int:
     return min_chunk_size + (leftover - 1) // num_chunks + 1
 
 
+def _linear_quantiles(values: np.ndarray, points: np.ndarray, out: np.ndarray) -> None:
+    """``np.quantile(values, points, out=out)`` (linear interpolation between order statistics) by way of one full
+    sort, which for a few hundred quantiles of 10**5 values is an order of magnitude faster than numpy's selection."""
+    ordered = np.sort(values)
+    position = points.astype(np.float64) * (len(ordered) - 1)
+    below = np.floor(position).astype(np.int64)
+    above = np.minimum(below + 1, len(ordered) - 1)
+    low, high = ordered[below].astype(np.float64), ordered[above].astype(np.float64)
+    out[:] = low + (high - low) * (position - below)
+
+
 def quantile_qq_approximation(array: np.ndarray, n_quantiles: int, min_chunk_size: int = 10 ** 5) -> np.ndarray:
     """Approximate uniform quantiles: exact quantiles of chunks (in a thread pool), then quantiles of those."""
     flat = np.ascontiguousarray(array.T if (not array.data.c_contiguous and array.data.f_contiguous) else array).reshape(-1)
@@ -108,7 +119,7 @@ def quantile_qq_approximation(array: np.ndarray, n_quantiles: int, min_chunk_siz
     chunk_size = get_chunk_size(len(flat), min_chunk_size)
     num_chunks = (len(flat) - 1) // chunk_size + 1
     table = np.empty((num_chunks, n_quantiles), dtype=flat.dtype)
-    jobs = [EXECUTOR.submit(np.quantile, flat[i * chunk_size:(i + 1) * chunk_size], points, out=table[i])
+    jobs = [EXECUTOR.submit(_linear_quantiles, flat[i * chunk_size:(i + 1) * chunk_size], points, table[i])
             for i in range(num_chunks)]
     for job in jobs:
         job.result()
