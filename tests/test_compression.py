@@ -149,3 +149,24 @@ def test_received_messages_can_be_read_without_parsing_the_payload():
     for broken in (b"\x22\x7f" + b"x", b"\x08", b"\x0b", b"\x29\x00"):
         with pytest.raises((ValueError, IndexError)):
             split_length_delimited_field(memoryview(broken), 4)
+
+
+def test_sorted_quantiles_agree_with_numpy():
+    """The quantile codec takes chunk quantiles from one sort; they must be numpy's linear-interpolation quantiles."""
+    import numpy as np
+
+    from hivemind_b200.compression.quantization import _linear_quantiles, quantile_qq_approximation
+
+    rng = np.random.default_rng(0)
+    points = np.linspace(0, 1, 257, dtype=np.float32)
+    for n in (1, 2, 7, 1000, 100_003):
+        for values in (rng.standard_normal(n), rng.integers(0, 5, n).astype(np.float64), -np.sort(rng.standard_normal(n))):
+            values = values.astype(np.float32)
+            out = np.empty(257, dtype=np.float32)
+            _linear_quantiles(values, points, out)
+            assert np.allclose(out, np.quantile(values, points), atol=5e-5, rtol=1e-5)
+            assert out[0] == values.min() and out[-1] == values.max() and np.all(np.diff(out) >= 0)
+    # the two-level approximation for large inputs stays close to the exact quantiles
+    big = rng.standard_normal(700_000).astype(np.float32)
+    approx, exact = quantile_qq_approximation(big, 257), np.quantile(big, points)
+    assert np.abs(approx - exact)[8:-8].max() < 0.02
